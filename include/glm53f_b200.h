@@ -1,0 +1,223 @@
+/*
+ * glm53f_b200.h - C ABI of the B200 decode engine for the GLM-5.3-Flash architecture.
+ *
+ * The library behind this header (libglm53f_b200.so) is hand-written CUDA for sm_100a. It
+ * replaces one path of josesilva05/glm-5.3-flash-in-c: the per-token forward pass that its
+ * model driver hands to a backend (src/model/glm53f_model.c:382-384) and the numeric ops
+ * that pass is made of (include/glm53f/glm53f.h:136-360). Nothing here takes or returns a
+ * torch type; every argument is a plain pointer, size or handle.
+ *
+ * Three groups of entry points:
+ *
+ *   1. ENGINE      create / load / finalize / forward / reset / free. This is the contract
+ *                  of the reference backend ABI (src/gpu/glm53f_gpu.h:38-50) with the
+ *                  reference's opaque `struct Glm53fModel *` argument replaced by a flat
+ *                  config plus tensors loaded by checkpoint name (the name table of
+ *                  src/model/glm53f_bind.c:139-206,311-317 and src/io/glm53f_load.c:11).
+ *   2. LAYER OPS   one entry point per op function of the reference, host buffers in and
+ *                  out, running on the loaded layer's weights and the engine's session
+ *                  state. These are what the parity tests and the benchmark call.
+ *   3. DEVICE OPS  the same hot ops with device pointers and no copies, for callers that
+ *                  already hold activations in HBM (the reference's gk_* launcher layer,
+ *                  src/gpu/glm53f_gpu_kernels.h:18-93).
+ *
+ * Error convention (reference: glm53f_model.h:61-64, glm53f_gpu_kernels.cu:668-686): every
+ * int function returns 0 on success and -1 on failure; on failure outputs are untouched or
+ * undefined, a message is kept for g5b_last_error(), and nothing falls back to a CPU
+ * implementation. The library has no CPU compute path at all.
+ *
+ * Threading: one caller thread per engine, like the reference model (not re-entrant).
+ */
+#ifndef GLM53F_B200_H
+#define GLM53F_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Storage formats of a weight matrix (reference: enum at glm53f.h:122; int4 is an
+ * approximation format of the reference's SSD cache and is not part of this engine). */
+#define G5B_DT_F32  0
+#define G5B_DT_BF16 1
+#define G5B_DT_FP8  2   /* E4M3FN codes + FP32 block scales ("weight_scale_inv") */
+
+/* Engine limits (reference: glm53f.h:42-45,377; glm53f_cfg.h:259-283). */
+#define G5B_MAX_LAYERS    256
+#define G5B_MAX_TOPK      64
+#define G5B_MAX_HC        8
+#define G5B_MAX_EXPERTS   1024
+#define G5B_MAX_POSITIONS 32768
+
+/* Model shape. Field for field the information of the reference's Glm53fCfg
+ * (glm53f.h:48-95) without its layer-type arrays, which are passed beside it. */
+typedef struct g5b_config {
+    int32_t hidden, n_layers, vocab;
+    float   rms_eps;
+    int32_t hc_mult, hc_iters;           /* mHC residual streams, Sinkhorn iterations */
+    float   hc_eps;
+    int32_t kda_heads, kda_head_dim, conv_k;
+    float   gate_lb;                      /* KDA gate lower bound (-5) */
+    int32_t mla_heads, q_lora, kv_lora, qk_nope, v_head;
+    int32_t index_topk, index_kpool, index_heads, index_dim;
+    int32_t n_experts, topk, n_shared, moe_inter, dense_inter;
+    float   routed_scale;
+    int32_t norm_topk;
+    float   swiglu_limit;
+    int32_t fp8_block_r, fp8_block_c;     /* 128 x 128 in the released checkpoint */
+} g5b_config;
+
+/* One tensor handed to a loader. FP8 tensors carry their scale grid
+ * [ceil(rows/fp8_block_r)][ceil(cols/fp8_block_c)] in scale_inv. Vectors use rows = n,
+ * cols = 1. `on_device` != 0 means data/scale_inv already live in the engine GPU's memory
+ * (the engine copies them device to device into its own layout). */
+typedef struct g5b_tensor {
+    const void  *data;
+    const float *scale_inv;
+    int32_t      dtype, rows, cols, on_device;
+} g5b_tensor;
+
+typedef struct g5b_engine g5b_engine;
+
+/* Message of the most recent failure on this thread ("" if none). */
+const char *g5b_last_error(void);
+
+/* ------------------------------------------------------------------- ENGINE ---- */
+
+/* Number of CUDA devices; 0 if none. Replaces glm53f_gpu_device_count (glm53f_gpu.h:42). */
+int g5b_device_count(void);
+
+/* Create an engine on one GPU for `cap` positions per session. is_mla / is_dense hold
+ * cfg->n_layers flags each (the reference's Glm53fCfg.is_mla / is_dense). Routed experts are
+ * expert-parallel: this engine owns experts [ep_rank*n_experts/ep_size,
+ * (ep_rank+1)*n_experts/ep_size) of every MoE layer and only those are accepted by
+ * g5b_engine_load; the trunk is replicated. ep_size = 1 keeps everything on this GPU.
+ * Replaces glm53f_gpu_create (glm53f_gpu.h:46), which placed whole layers on devices and left
+ * routed experts on the CPU. Returns NULL on failure. */
+g5b_engine *g5b_engine_create(const g5b_config *cfg, const uint8_t *is_mla,
+                              const uint8_t *is_dense, int cap, int device,
+                              int ep_rank, int ep_size);
+
+/* Upload one checkpoint tensor by its name below "model.language_model." (for example
+ * "layers.3.self_attn.q_a_proj.weight", "layers.3.mlp.experts.17.down_proj.weight",
+ * "embed_tokens.weight", "norm.weight") or "lm_head.weight". Names, shapes and dtypes follow
+ * glm53f_bind.c:139-206,311-317 and glm53f_load.c:11-63; a wrong shape or dtype is refused.
+ * Replaces upload_layer (src/gpu/glm53f_gpu.c:662-708) and the SSD expert cache
+ * (src/cache/glm53f_cache.c): every routed expert becomes HBM resident. An expert outside
+ * this engine's expert-parallel range is ignored and reported as success. */
+int g5b_engine_load(g5b_engine *e, const char *name, const g5b_tensor *t);
+
+/* Fill one routed expert of a MoE layer with synthetic weights generated on the GPU: E4M3
+ * codes uniform over the 254 finite codes from a counter-based hash of (seed, layer, expert,
+ * matrix, element index), so the CPU can regenerate any single expert bit for bit. Scale
+ * grids (three, in gate/up/down order, host memory) are uploaded as given. */
+int g5b_engine_fill_expert(g5b_engine *e, int layer, int expert, uint64_t seed,
+                           const float *gate_s, const float *up_s, const float *down_s);
+
+/* Check that every tensor the config implies has been loaded, then allocate the session
+ * state (KDA recurrent + conv state, MLA latent cache, DSA indexer state) and work buffers. */
+int g5b_engine_finalize(g5b_engine *e);
+
+/* Feed T tokens after the positions already consumed. logits (vocab floats, may be NULL)
+ * receives the last position's logits; argmax_all (T ints, may be NULL) the argmax at every
+ * position. Same contract as glm53f_model_forward / glm53f_gpu_forward
+ * (glm53f_model.h:59-64, glm53f_gpu.h:49-50). */
+int g5b_engine_forward(g5b_engine *e, const int *ids, int T, float *logits, int *argmax_all);
+
+/* Forget every carried position (glm53f_gpu_reset, glm53f_gpu.h:53). */
+void g5b_engine_reset(g5b_engine *e);
+void g5b_engine_free(g5b_engine *e);       /* glm53f_gpu_free, glm53f_gpu.h:47 */
+int  g5b_engine_cached(const g5b_engine *e);  /* positions consumed so far */
+
+/* Greedy decode on the device: feed `first` and generate n tokens without returning to the
+ * host between steps (the reference's CLI loop, src/cli/glm53f_run.c:469-524, round-trips
+ * logits to the host and takes the argmax there). out receives n token ids. */
+int g5b_engine_decode_greedy(g5b_engine *e, int first, int n, int *out);
+
+/* Expert-parallel wiring for ep_size > 1: every rank exports a handle to its exchange buffer,
+ * the caller gathers all handles (any transport) and gives each rank the full table. */
+size_t g5b_engine_ep_handle_bytes(void);
+int    g5b_engine_ep_export(g5b_engine *e, void *handle_out);
+int    g5b_engine_ep_connect(g5b_engine *e, const void *all_handles /* ep_size entries */);
+
+/* ---------------------------------------------------------------- LAYER OPS ---- */
+/* Host buffers in and out. Activations are FP32 like the reference's. `layer` indexes the
+ * engine's loaded layers; ops that carry state read and advance the engine's session state of
+ * that layer exactly as the forward pass would. */
+
+/* y[T][rows] = W x[T][cols] for any loaded matrix, by tensor name (glm53f_mm / _mm_batch,
+ * glm53f.h:137,142). */
+int g5b_op_matvec(g5b_engine *e, const char *name, const float *x, int T, float *y);
+
+/* A matrix that is not part of a model: upload, multiply, discard. */
+int g5b_matvec_host(const g5b_tensor *w, int br, int bc, const float *x, int T, float *y,
+                    int device);
+
+/* glm53f_rmsnorm (glm53f.h:165); w may be NULL. */
+int g5b_rmsnorm_host(float *y, const float *x, const float *w, int n, int rows, float eps,
+                     int device);
+/* glm53f_swiglu_clamp (glm53f.h:168) over rows of [gate | up]. */
+int g5b_swiglu_host(float *y, const float *gu, int n, int rows, float limit, int device);
+/* glm53f_shortconv (glm53f.h:171). state [channels][k-1] is read and updated. */
+int g5b_shortconv_host(float *y, const float *x, const float *w, float *state, int channels,
+                       int k, int T, int device);
+
+/* site 0 = attention, 1 = feed-forward. glm53f_hc_pre / glm53f_hc_post (glm53f.h:300-304):
+ * h is [T][M][hidden]; x [T][hidden], post [T][M], comb [T][M*M]. */
+int g5b_op_hc_pre(g5b_engine *e, int layer, int site, const float *h, int T, float *x,
+                  float *post, float *comb);
+int g5b_op_hc_post(g5b_engine *e, float *h, const float *y, const float *post,
+                   const float *comb, int T);
+
+/* glm53f_kda_layer (glm53f.h:309): x [T][hidden] -> out [T][hidden], state advanced. */
+int g5b_op_kda(g5b_engine *e, int layer, const float *x, int T, float *out);
+/* glm53f_mla with the latent cache plus glm53f_dsa_append / _select (glm53f.h:318-337):
+ * appends T positions at the engine's cached position and attends. sel_out (may be NULL)
+ * receives, for the LAST query, the selected positions; n_sel_out their count or -1 when the
+ * query attended densely. Advances nothing but the layer's caches. */
+int g5b_op_mla(g5b_engine *e, int layer, const float *x, int T, int cached, float *out,
+               int *sel_out, int *n_sel_out);
+/* glm53f_router (glm53f.h:340): idx/w [T][topk]. */
+int g5b_op_router(g5b_engine *e, int layer, const float *x, int T, int *idx, float *w);
+/* glm53f_moe (glm53f.h:348); with_shared = 0 gives glm53f_moe_routed (glm53f.h:344). */
+int g5b_op_moe(g5b_engine *e, int layer, const float *x, int T, float *out, int with_shared);
+/* glm53f_mlp on a dense layer's gate/up/down (glm53f.h:352). */
+int g5b_op_mlp(g5b_engine *e, int layer, const float *x, int T, float *out);
+/* glm53f_decoder_layer (glm53f.h:358): h [T][M][hidden] in place at position `cached`. */
+int g5b_op_decoder_layer(g5b_engine *e, int layer, float *h, int T, int cached);
+
+/* Session state access, to seed a layer without replaying a context (the reference's tests
+ * fill Glm53fModel.state / ckv / idx directly). kind: 0 KDA state [H*D*D + 3*H*D*(k-1)],
+ * 1 MLA latent cache [cap][kv_lora], 2 DSA state (k | gate | pool keys, glm53f_dsa.c:44-53).
+ * Values cross as FP32; `count` floats starting at float offset `offset`. */
+int g5b_state_write(g5b_engine *e, int layer, int kind, size_t offset, const float *src,
+                    size_t count);
+int g5b_state_read(g5b_engine *e, int layer, int kind, size_t offset, float *dst,
+                   size_t count);
+
+/* --------------------------------------------------------------- DEVICE OPS ---- */
+/* Device pointers on the engine's GPU, launched on the engine's stream, no host copies and
+ * no synchronisation (call g5b_engine_sync to wait). */
+int   g5b_dev_moe(g5b_engine *e, int layer, const float *x_dev, int T, float *out_dev);
+int   g5b_dev_kda(g5b_engine *e, int layer, const float *x_dev, int T, float *out_dev);
+int   g5b_dev_mla(g5b_engine *e, int layer, const float *x_dev, int T, int cached,
+                  float *out_dev);
+int   g5b_dev_decoder_layer(g5b_engine *e, int layer, float *h_dev, int T, int cached);
+int   g5b_engine_sync(g5b_engine *e);
+void *g5b_engine_stream(g5b_engine *e);            /* the cudaStream_t ops are launched on */
+/* Kernels this library has launched since it was loaded (benchmark bookkeeping). */
+uint64_t g5b_launch_count(void);
+/* Time `iters` back-to-back launches of the batch-1..64 MoE layer between two CUDA events on
+ * the engine's stream, after writing `flush_bytes` to a scratch buffer before each launch
+ * (0 = no flush). Returns the mean milliseconds per launch in *ms_out; per-kernel means of
+ * the router / gate-up / down kernels in kern_ms[3] when not NULL. */
+int g5b_time_moe(g5b_engine *e, int layer, const float *x_dev, int T, float *out_dev,
+                 int iters, size_t flush_bytes, float *ms_out, float *kern_ms);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* GLM53F_B200_H */
