@@ -1,0 +1,300 @@
+"""Benchmark of the decode hot path: one full-size MoE layer of the GLM-5.3-Flash architecture
+(hidden 4096, 288 routed experts + 1 shared of inter 2048, top-8 sigmoid router, FP8 E4M3 codes
+with 128x128 block scales), batch 1 - the configuration the expert-GEMV roofline is quoted on.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one pass of the layer over one batch. Prints ONE JSON line:
+  value        decode tokens/s through the layer with inputs resident in HBM (CUDA events on the
+               engine's stream around each step, L2 flushed before each step), all GPUs summed
+  e2e          the same through the host-buffer C-ABI call (pinned host memory in and out)
+  roofline     the gate/up expert kernel: algorithmic bytes / its event-timed duration against
+               the measured HBM copy bandwidth
+  cpu_baseline the reference's own CPU implementation (glm53f_moe) on this box's host cores
+  extra        batch 8 and 64 of the same layer, and per-phase times
+With N > 1 (launched by torchrun, one rank per GPU) every rank serves its own stream of tokens
+through its own replica of the layer (weak scaling, no data-path collective: sequences are
+independent); the time is the maximum over ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+SEED = 0
+EXPERT_BYTES = 3 * 2048 * 4096 + 3 * 16 * 32 * 4            # codes + block scales of one expert
+GATEUP_BYTES = 2 * 2048 * 4096 + 2 * 16 * 32 * 4            # what the gate/up kernel reads per expert
+ROUTER_BYTES = 288 * 4096 * 2
+FLUSH_BYTES = 256 << 20                                     # > 126 MB of L2
+# dram__bytes_read.sum + dram__bytes_write.sum of one gate/up launch at batch 1 (profiles/), or None
+GATEUP_TRAFFIC_NCU = None
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.rows, self.proc, self.gpu = [], None, gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                pass
+        sm, mx, reasons = [], 0, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1])); mx = max(mx, float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_reference_moe(steps: int, warmup: int, batch: int = 1, threads: int | None = None):
+    """The reference's glm53f_moe (oracle/_ref, built from the unmodified reference sources) on the
+    host cores, on the same layer: `steps` calls on a rotating set of 4 seeded inputs. Falls back to
+    this repo's CPU restatement when the reference objects are absent. Returns a dict."""
+    import synth
+    from oracle import binding
+    spec = synth.layer_spec("moe")
+    trunk = synth.moe_layer_trunk(spec, SEED)
+    xs = [synth.moe_inputs(spec.cfg, batch, SEED + i) for i in range(4)]
+    kind = "reference" if binding.have_ref() else "port"
+    router = binding.OracleModel(spec.cfg, spec.is_mla, spec.is_dense, 8, 2)
+    for name, (arr, dt, sc) in trunk.items():
+        if "mlp.gate." in name:
+            router.load(name, arr, dt, sc)
+    chosen = np.concatenate([router.op_router(0, x)[0].ravel() for x in xs])
+    router.close()
+    cls = binding.RefModel if kind == "reference" else binding.OracleModel
+    m = cls(spec.cfg, spec.is_mla, spec.is_dense, 8, 2)
+    keep = ("mlp.gate.weight", "mlp.gate.e_score_correction_bias", "mlp.shared_experts")
+    for name, (arr, dt, sc) in trunk.items():
+        if any(k in name for k in keep):
+            m.load(name, arr, dt, sc)
+    c = spec.cfg
+    for ex in sorted(set(int(e) for e in chosen)):
+        gs, us, ds = synth.expert_scales(c, 0, ex, SEED)
+        for which, (nm, shape, sc) in enumerate((("gate", (c.moe_inter, c.hidden), gs), ("up", (c.moe_inter, c.hidden), us),
+                                                 ("down", (c.hidden, c.moe_inter), ds))):
+            codes = binding.synth_codes(SEED, 0, ex, which, c.moe_inter * c.hidden).reshape(shape)
+            m.load(f"layers.0.mlp.experts.{ex}.{nm}_proj.weight", codes, synth.DT_FP8, sc)
+    cores = threads or os.cpu_count() or 1
+    try:                                            # the thread count of the OpenMP runtime the CPU library uses
+        C.CDLL("libgomp.so.1", mode=C.RTLD_GLOBAL).omp_set_num_threads(cores)
+    except OSError:
+        pass
+    for i in range(warmup):
+        m.op_moe(0, xs[i % 4])
+    t0 = time.perf_counter()
+    for i in range(steps):
+        m.op_moe(0, xs[i % 4])
+    dt = time.perf_counter() - t0
+    m.close()
+    return {"value": batch * steps / dt, "unit": "tokens/s", "cores": cores, "kind": kind,
+            "ms_per_step": 1e3 * dt / steps,
+            "sample": f"{steps} calls of glm53f_moe at batch {batch} on 4 rotating seeded inputs, "
+                      f"{len(set(chosen.tolist()))} distinct routed experts + shared resident in RAM"}
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    steps = max(3, min(args.steps, 40))
+    r = cpu_reference_moe(steps, max(1, min(args.warmup, 3)))
+    line = {"impl": "reference", "metric": "decode tokens/s through one full-size MoE layer, batch 1",
+            "value": r["value"], "unit": "tokens/s", "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 3),
+            "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "fp8_e4m3 weights, f32 activations", "data": "synthetic",
+            "config": {"workload": "config 2: single MoE layer decode, hidden 4096, inter 2048, 288+1 experts, top-8, batch 1"},
+            "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": r["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def time_batch(pkg, eng, torch, B, steps, warmup, flush=FLUSH_BYTES):
+    """Device-resident timing of the MoE layer at batch B: (ms per step list, phase ms, launches)."""
+    import synth
+    L = pkg.lib()
+    x = torch.from_numpy(synth.moe_inputs(eng.cfg, B, SEED)).cuda()
+    out = torch.empty_like(x)
+    torch.cuda.synchronize()
+    each = np.zeros(max(steps, warmup, 1), np.float32)
+    tot = C.c_float(0)
+    assert L.g5b_time_op(eng.handle, b"moe", 0, x.data_ptr(), B, 0, out.data_ptr(), warmup, flush,
+                         C.byref(tot), each.ctypes.data) == 0, L.g5b_last_error()
+    ms4 = (C.c_float * 8)()
+    cnt = C.c_long(0)
+    L.g5b_engine_profile_read(eng.handle, ms4, 8, C.byref(cnt), 1)
+    n0 = L.g5b_launch_count()
+    assert L.g5b_time_op(eng.handle, b"moe", 0, x.data_ptr(), B, 0, out.data_ptr(), steps, flush,
+                         C.byref(tot), each.ctypes.data) == 0, L.g5b_last_error()
+    launches = L.g5b_launch_count() - n0 - (steps if flush else 0)
+    L.g5b_engine_profile_read(eng.handle, ms4, 8, C.byref(cnt), 1)
+    phases = [ms4[i] / max(1, cnt.value) for i in range(4)]
+    return each[:steps].astype(float), phases, int(launches), out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+    import synth
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    L = pkg.lib()                                   # raises when the CUDA library is missing
+    if not torch.cuda.is_available() or L.g5b_device_count() < 1:
+        raise SystemExit("bench.py needs a CUDA device: the engine has no CPU path")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    warmup = max(3, args.warmup)
+    spec, trunk, eng = synth.build_moe_layer_engine(SEED, device=local, options={"profile": 1})
+    sampler = ClockSampler(local)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- headline: batch 1, device resident
+    barrier()
+    sampler.start()
+    each, phases, launches, _ = time_batch(pkg, eng, torch, 1, args.steps, warmup)
+    barrier()
+    clocks = sampler.stop()
+    total_ms = float(each.sum())
+    if world > 1:
+        t = torch.tensor([total_ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    value = world * 1 * 1e3 / ms_per_step
+
+    # ---- end to end: host buffers (pinned) through the C-ABI op, H2D and D2H inside the timing
+    xh = torch.from_numpy(synth.moe_inputs(spec.cfg, 1, SEED)).pin_memory()
+    oh = torch.empty_like(xh).pin_memory()
+    xn, on = xh.numpy(), oh.numpy()
+    for _ in range(warmup):
+        assert L.g5b_op_moe(eng.handle, 0, xn.ctypes.data, 1, on.ctypes.data, 1) == 0
+    flush = torch.empty(FLUSH_BYTES // 4, dtype=torch.float32, device="cuda")
+    e2e_s = 0.0
+    barrier()
+    for _ in range(args.steps):
+        flush.zero_()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        assert L.g5b_op_moe(eng.handle, 0, xn.ctypes.data, 1, on.ctypes.data, 1) == 0
+        e2e_s += time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e = {"value": world * args.steps / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": int(xn.nbytes),
+           "d2h_bytes_per_step": int(on.nbytes), "ms_per_step": 1e3 * e2e_s / args.steps}
+
+    # ---- roofline of the dominant kernel (gate/up + SwiGLU of the 8 routed + 1 shared experts)
+    peak, peak_kind = measured_peaks()
+    gateup_ms = phases[1]
+    achieved = 9 * GATEUP_BYTES / (gateup_ms * 1e-3) / 1e9 if gateup_ms > 0 else 0.0
+    roofline = {"bound": "hbm", "kernel": "expert_kernel<gate/up> (8 routed + 1 shared expert, batch 1)",
+                "achieved": achieved, "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s",
+                "frac": achieved / peak, "traffic": GATEUP_TRAFFIC_NCU,
+                "algorithmic_bytes_per_launch": 9 * GATEUP_BYTES, "ms_per_launch": gateup_ms,
+                "layer": {"algorithmic_bytes_per_step": 9 * EXPERT_BYTES + ROUTER_BYTES,
+                          "achieved": (9 * EXPERT_BYTES + ROUTER_BYTES) / (ms_per_step * 1e-3) / 1e9,
+                          "frac": (9 * EXPERT_BYTES + ROUTER_BYTES) / (ms_per_step * 1e-3) / 1e9 / peak}}
+
+    extra = {"phase_ms_b1": {"router+plan": phases[0], "gate_up": phases[1], "down": phases[2], "combine": phases[3]}}
+    if rank == 0:
+        for B in (8, 64):
+            eb, ph, _, _ = time_batch(pkg, eng, torch, B, max(10, args.steps // 10), 3)
+            idx, _ = eng.op_router(0, synth.moe_inputs(spec.cfg, B, SEED))
+            distinct = int(len(set(idx.ravel().tolist())))
+            ms = float(eb.mean())
+            extra[f"batch{B}"] = {"tokens_per_s": B * 1e3 / ms, "ms_per_step": ms, "distinct_experts": distinct,
+                                  "achieved_GBps": ((distinct + 1) * EXPERT_BYTES + ROUTER_BYTES) / (ms * 1e-3) / 1e9,
+                                  "phase_ms": ph}
+    eng.close()
+
+    cpu = None
+    if rank == 0 and not args.no_cpu_baseline:
+        cpu = cpu_reference_moe(steps=60, warmup=2)
+        one = cpu_reference_moe(steps=30, warmup=1, threads=1)
+        cpu = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        cpu["one_thread_value"] = one["value"]
+
+    if rank == 0:
+        line = {"metric": "decode tokens/s through one full-size MoE layer, batch 1", "value": value, "unit": "tokens/s",
+                "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms_per_step,
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "fp8_e4m3 weights, f32 activations and accumulation", "data": "synthetic",
+                "config": {"workload": "config 2: single MoE layer decode, hidden 4096, inter 2048, 288+1 experts, "
+                                       "top-8, batch 1", "l2": f"flushed before every step ({FLUSH_BYTES >> 20} MiB write)",
+                           "parallelism": f"{world} independent replica(s), one token stream each"},
+                "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
+                "extra": extra}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -20,10 +20,13 @@ PREFIX = "model.language_model."
 _ST_DTYPES = {"F32": (np.float32, DT_F32), "BF16": (np.uint16, DT_BF16), "F8_E4M3": (np.uint8, DT_FP8)}
 
 
-def read_config(path: str):
-    """Returns (Config, is_mla list, is_dense list, eos ids)."""
-    with open(path) as f:
-        top = json.load(f)
+def read_config(path_or_dict):
+    """config.json (a path, or its parsed content) -> (Config, is_mla list, is_dense list, eos ids)."""
+    if isinstance(path_or_dict, dict):
+        top = path_or_dict
+    else:
+        with open(path_or_dict) as f:
+            top = json.load(f)
     t = top.get("text_config", top)
     q = top.get("quantization_config") or {}
     la = t["linear_attn_config"]

@@ -1,0 +1,1222 @@
+// engine.cu - the engine object behind include/glm53f_b200.h: HBM-resident weights loaded by
+// checkpoint name, per-session state, and the sequencing of kernels for one forward pass.
+//
+// Replaces the host side of the reference's CUDA backend (src/gpu/glm53f_gpu.c): its placement of
+// whole layers on devices, the FP32 widening copies for cuBLAS, the per-MoE-layer round trip of
+// activations to the CPU for the routed experts (:1024-1040), and the blocking copies between
+// every step. Here nothing leaves the GPU between the token ids going in and the logits (or the
+// arg-max) coming out: router, expert selection, DSA selection, embedding gather and arg-max all
+// run on the device, and every routed expert of this engine's expert-parallel range is resident.
+#include <math.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "kernels.h"
+
+namespace g5b {
+extern unsigned long long g_launches;
+
+static thread_local char g_err[512] = "";
+static int fail(const char *fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof g_err, fmt, ap);
+    va_end(ap);
+    fprintf(stderr, "glm53f_b200: %s\n", g_err);
+    return -1;
+}
+#define CU(call)                                                                           \
+    do {                                                                                   \
+        cudaError_t e_ = (call);                                                           \
+        if (e_ != cudaSuccess) return fail("%s: %s", #call, cudaGetErrorString(e_));       \
+    } while (0)
+
+constexpr int CHUNK = 32;       // positions one pass of a layer works on (sizes the work buffers)
+constexpr int PROF_SLOTS = 8;
+
+struct Layer {
+    HcW    hc[2];
+    float *in_norm = nullptr, *post_norm = nullptr;
+    bool   is_mla = false, is_dense = false;
+    // KDA
+    DMat   kq, kk, kv, f_a, f_b, kb, g_a, g_b, ko;
+    float *q_conv = nullptr, *k_conv = nullptr, *v_conv = nullptr, *A_log = nullptr, *dt_bias = nullptr,
+          *o_norm = nullptr;
+    // MLA + indexer
+    DMat   q_a, q_b, kv_a, kv_b, mo, wq_b, wk, wproj, igate;
+    float *q_a_norm = nullptr, *kv_a_norm = nullptr, *k_norm_w = nullptr, *k_norm_b = nullptr, *ape = nullptr;
+    // feed-forward
+    DMat   d_gate, d_up, d_down, sh_gate, sh_up, sh_down;
+    DMat   router;
+    float *bias = nullptr;
+    uint8_t *expert_slab = nullptr;
+    size_t   expert_stride = 0;
+    int      expert_dt = -1;
+    std::vector<ExpertW> table;          // n_local routed + 1 shared (host mirror)
+    std::vector<uint8_t> have;           // [n_local][3]
+    ExpertW *table_dev = nullptr;
+    // session state
+    float *kda_state = nullptr;
+    void  *latent = nullptr;
+    float *idx_state = nullptr;
+};
+
+struct Target { int kind; DMat *mat; float **vec; int rows, cols; };   // kind 0 matrix, 1 vector
+
+}  // namespace g5b
+
+using namespace g5b;
+
+struct g5b_engine {
+    g5b_config c;
+    int cap = 0, cached = 0, device = 0, ep_rank = 0, ep_size = 1, n_local0 = 0, n_local = 0;
+    bool finalized = false;
+    int latent_bf16 = 0, profile = 0, partial = 0;
+    cudaStream_t st = nullptr;
+    std::vector<Layer> L;
+    std::vector<std::unordered_map<std::string, Target>> names;   // per layer
+    DMat embed, lm_head;
+    float *norm = nullptr;
+    std::vector<void *> owned;
+
+    // work buffers (CHUNK positions)
+    float *h = nullptr; size_t h_tokens = 0;
+    int   *ids_dev = nullptr; size_t ids_cap = 0;
+    float *inv0, *inv1, *mix, *xc, *xn, *y, *post, *comb;
+    float *kq, *kk, *kv, *kz, *kgb, *ko, *kbraw, *klr;
+    float *mq_raw, *mct, *mwk, *mgate, *mwp, *mq, *mqidx, *mcb, *macc, *mscore, *minvq;
+    double *mqa, *mdsc;
+    int   *msel, *mnsel;
+    float *rscore, *rw, *act, *contrib, *gu, *dact;
+    int   *ridx;
+    MoePlan plan;
+    float *xm, *inv_head, *logits, *am_v;
+    int   *am_i, *am_out;
+    void  *flush_buf = nullptr; size_t flush_bytes = 0;
+    cudaEvent_t prof_ev[PROF_SLOTS + 1];
+    float prof_ms[PROF_SLOTS];
+    long  prof_n = 0;
+
+    int dalloc(void **p, size_t bytes)
+    {
+        if (bytes == 0) bytes = 16;
+        CU(cudaMalloc(p, bytes));
+        CU(cudaMemsetAsync(*p, 0, bytes, st));
+        owned.push_back(*p);
+        return 0;
+    }
+};
+
+// ------------------------------------------------------------------ creation ----
+extern "C" const char *g5b_last_error(void) { return g_err; }
+
+extern "C" int g5b_device_count(void)
+{
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) return 0;
+    return n;
+}
+
+extern "C" uint64_t g5b_launch_count(void) { return g_launches; }
+
+static void add_mat(g5b_engine *e, int l, const char *nm, DMat *m, int rows, int cols)
+{
+    e->names[l][nm] = Target{0, m, nullptr, rows, cols};
+}
+static void add_vec(g5b_engine *e, int l, const char *nm, float **v, int n)
+{
+    e->names[l][nm] = Target{1, nullptr, v, n, 1};
+}
+
+// The tensors a layer consists of: names, shapes as the reference binds them
+// (src/model/glm53f_bind.c:139-206).
+static void plan_layer(g5b_engine *e, int l)
+{
+    const g5b_config &c = e->c;
+    Layer &w = e->L[l];
+    const int E = c.hidden, M = c.hc_mult, MIX = (2 + M) * M;
+    add_vec(e, l, "input_layernorm.weight", &w.in_norm, E);
+    add_vec(e, l, "post_attention_layernorm.weight", &w.post_norm, E);
+    add_mat(e, l, "hc_attn_fn", &w.hc[0].fn, MIX, M * E);
+    add_vec(e, l, "hc_attn_base", &w.hc[0].base, MIX);
+    add_vec(e, l, "hc_attn_scale", &w.hc[0].scale, 3);
+    add_mat(e, l, "hc_ffn_fn", &w.hc[1].fn, MIX, M * E);
+    add_vec(e, l, "hc_ffn_base", &w.hc[1].base, MIX);
+    add_vec(e, l, "hc_ffn_scale", &w.hc[1].scale, 3);
+    if (w.is_mla) {
+        const int H = c.mla_heads, IH = c.index_heads, ID = c.index_dim;
+        add_mat(e, l, "self_attn.q_a_proj.weight", &w.q_a, c.q_lora, E);
+        add_vec(e, l, "self_attn.q_a_layernorm.weight", &w.q_a_norm, c.q_lora);
+        add_mat(e, l, "self_attn.q_b_proj.weight", &w.q_b, H * c.qk_nope, c.q_lora);
+        add_mat(e, l, "self_attn.kv_a_proj_with_mqa.weight", &w.kv_a, c.kv_lora, E);
+        add_vec(e, l, "self_attn.kv_a_layernorm.weight", &w.kv_a_norm, c.kv_lora);
+        add_mat(e, l, "self_attn.kv_b_proj.weight", &w.kv_b, H * (c.qk_nope + c.v_head), c.kv_lora);
+        add_mat(e, l, "self_attn.o_proj.weight", &w.mo, E, H * c.v_head);
+        add_mat(e, l, "self_attn.indexer.wq_b.weight", &w.wq_b, IH * ID, c.q_lora);
+        add_mat(e, l, "self_attn.indexer.wk.weight", &w.wk, ID, E);
+        add_vec(e, l, "self_attn.indexer.k_norm.weight", &w.k_norm_w, ID);
+        add_vec(e, l, "self_attn.indexer.k_norm.bias", &w.k_norm_b, ID);
+        add_mat(e, l, "self_attn.indexer.weights_proj.weight", &w.wproj, IH, E);
+        add_mat(e, l, "self_attn.indexer.index_kpool_compress_gate", &w.igate, ID, E);
+        add_vec(e, l, "self_attn.indexer.index_kpool_compress_ape", &w.ape, c.index_kpool * ID);
+    } else {
+        const int H = c.kda_heads, D = c.kda_head_dim, P = H * D;
+        add_mat(e, l, "self_attn.q_proj.weight", &w.kq, P, E);
+        add_mat(e, l, "self_attn.k_proj.weight", &w.kk, P, E);
+        add_mat(e, l, "self_attn.v_proj.weight", &w.kv, P, E);
+        add_vec(e, l, "self_attn.q_conv1d.weight", &w.q_conv, P * c.conv_k);
+        add_vec(e, l, "self_attn.k_conv1d.weight", &w.k_conv, P * c.conv_k);
+        add_vec(e, l, "self_attn.v_conv1d.weight", &w.v_conv, P * c.conv_k);
+        add_mat(e, l, "self_attn.f_a_proj.weight", &w.f_a, D, E);
+        add_mat(e, l, "self_attn.f_b_proj.weight", &w.f_b, P, D);
+        add_vec(e, l, "self_attn.A_log", &w.A_log, H);
+        add_vec(e, l, "self_attn.dt_bias", &w.dt_bias, P);
+        add_mat(e, l, "self_attn.b_proj.weight", &w.kb, H, E);
+        add_mat(e, l, "self_attn.g_a_proj.weight", &w.g_a, D, E);
+        add_mat(e, l, "self_attn.g_b_proj.weight", &w.g_b, P, D);
+        add_vec(e, l, "self_attn.o_norm.weight", &w.o_norm, D);
+        add_mat(e, l, "self_attn.o_proj.weight", &w.ko, E, P);
+    }
+    if (w.is_dense) {
+        add_mat(e, l, "mlp.gate_proj.weight", &w.d_gate, c.dense_inter, E);
+        add_mat(e, l, "mlp.up_proj.weight", &w.d_up, c.dense_inter, E);
+        add_mat(e, l, "mlp.down_proj.weight", &w.d_down, E, c.dense_inter);
+    } else {
+        const int SI = c.moe_inter * c.n_shared;
+        add_mat(e, l, "mlp.gate.weight", &w.router, c.n_experts, E);
+        add_vec(e, l, "mlp.gate.e_score_correction_bias", &w.bias, c.n_experts);
+        add_mat(e, l, "mlp.shared_experts.gate_proj.weight", &w.sh_gate, SI, E);
+        add_mat(e, l, "mlp.shared_experts.up_proj.weight", &w.sh_up, SI, E);
+        add_mat(e, l, "mlp.shared_experts.down_proj.weight", &w.sh_down, E, SI);
+    }
+}
+
+extern "C" g5b_engine *g5b_engine_create(const g5b_config *cfg, const uint8_t *is_mla,
+                                         const uint8_t *is_dense, int cap, int device, int ep_rank,
+                                         int ep_size)
+{
+    g_err[0] = 0;
+    const g5b_config &c = *cfg;
+    if (c.n_layers < 1 || c.n_layers > G5B_MAX_LAYERS || c.topk < 1 || c.topk > G5B_MAX_TOPK ||
+        c.hc_mult < 1 || c.hc_mult > G5B_MAX_HC || c.n_experts > G5B_MAX_EXPERTS || c.conv_k > 17 ||
+        c.kda_head_dim > 512 || c.kv_lora > 1024 || c.index_heads > 256 || c.index_dim > 512 ||
+        cap > G5B_MAX_POSITIONS || c.index_kpool < 1) {
+        fail("config outside the engine limits");
+        return nullptr;
+    }
+    if (ep_size < 1 || ep_rank < 0 || ep_rank >= ep_size || (c.n_experts % ep_size) != 0) {
+        fail("expert-parallel rank %d of %d does not divide %d experts", ep_rank, ep_size, c.n_experts);
+        return nullptr;
+    }
+    if (device < 0 || device >= g5b_device_count()) {
+        fail("CUDA device %d is not available (this library has no CPU path)", device);
+        return nullptr;
+    }
+    if (cudaSetDevice(device) != cudaSuccess) { fail("cudaSetDevice(%d) failed", device); return nullptr; }
+    g5b_engine *e = new g5b_engine();
+    e->c = c;
+    e->cap = cap < 1 ? 1 : cap;
+    e->device = device;
+    e->ep_rank = ep_rank; e->ep_size = ep_size;
+    e->n_local = c.n_experts / ep_size;
+    e->n_local0 = ep_rank * e->n_local;
+    if (cudaStreamCreateWithFlags(&e->st, cudaStreamNonBlocking) != cudaSuccess) {
+        fail("cannot create a stream"); delete e; return nullptr;
+    }
+    for (int i = 0; i <= PROF_SLOTS; i++) cudaEventCreate(&e->prof_ev[i]);
+    memset(e->prof_ms, 0, sizeof e->prof_ms);
+    e->L.resize(c.n_layers);
+    e->names.resize(c.n_layers);
+    for (int l = 0; l < c.n_layers; l++) {
+        e->L[l].is_mla = is_mla[l] != 0;
+        e->L[l].is_dense = is_dense[l] != 0;
+        plan_layer(e, l);
+    }
+    return e;
+}
+
+extern "C" int g5b_engine_set_option(g5b_engine *e, const char *name, int value)
+{
+    if (!strcmp(name, "latent_bf16")) {
+        if (e->finalized) return fail("latent_bf16 must be set before finalize");
+        e->latent_bf16 = value != 0;
+        return 0;
+    }
+    if (!strcmp(name, "profile")) { e->profile = value; return 0; }
+    if (!strcmp(name, "allow_partial")) { e->partial = value != 0; return 0; }
+    return fail("unknown option %s", name);
+}
+
+// ------------------------------------------------------------------- loading ----
+static size_t elt(int dt) { return dt == G5B_DT_F32 ? 4 : dt == G5B_DT_BF16 ? 2 : 1; }
+
+static int copy_in(g5b_engine *e, void *dst, const void *src, size_t bytes, int on_device)
+{
+    CU(cudaMemcpyAsync(dst, src, bytes, on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, e->st));
+    CU(cudaStreamSynchronize(e->st));
+    return 0;
+}
+
+static int upload_mat(g5b_engine *e, DMat *m, const g5b_tensor *t, int rows, int cols, const char *name)
+{
+    if (t->rows != rows || t->cols != cols)
+        return fail("%s is %d x %d, the config implies %d x %d", name, t->rows, t->cols, rows, cols);
+    if (t->dtype < 0 || t->dtype > 2) return fail("%s has a dtype this engine cannot multiply", name);
+    m->dt = t->dtype; m->rows = rows; m->cols = cols;
+    if (e->dalloc(&m->w, (size_t)rows * cols * elt(t->dtype))) return -1;
+    if (copy_in(e, m->w, t->data, (size_t)rows * cols * elt(t->dtype), t->on_device)) return -1;
+    if (t->dtype == G5B_DT_FP8) {
+        if (!t->scale_inv || e->c.fp8_block_r < 1 || e->c.fp8_block_c < 1)
+            return fail("%s is FP8 but has no scale grid / the config has no block size", name);
+        m->br = e->c.fp8_block_r; m->bc = e->c.fp8_block_c;
+        m->scols = (cols + m->bc - 1) / m->bc;
+        const size_t ns = (size_t)((rows + m->br - 1) / m->br) * m->scols;
+        if (e->dalloc((void **)&m->s, ns * 4)) return -1;
+        if (copy_in(e, m->s, t->scale_inv, ns * 4, t->on_device)) return -1;
+    }
+    return 0;
+}
+
+// Vectors are widened to FP32 on the way in (reference: src/model/glm53f_bind.c:130-133).
+static int upload_vec(g5b_engine *e, float **v, const g5b_tensor *t, size_t n, const char *name)
+{
+    if ((size_t)t->rows * (size_t)t->cols != n)
+        return fail("%s has %zu values, the config implies %zu", name, (size_t)t->rows * (size_t)t->cols, n);
+    if (t->on_device) return fail("%s: vectors are loaded from host memory", name);
+    std::vector<float> tmp(n);
+    if (t->dtype == G5B_DT_F32) memcpy(tmp.data(), t->data, n * 4);
+    else if (t->dtype == G5B_DT_BF16) {
+        const uint16_t *s = (const uint16_t *)t->data;
+        for (size_t i = 0; i < n; i++) { uint32_t u = (uint32_t)s[i] << 16; memcpy(&tmp[i], &u, 4); }
+    } else return fail("%s must be a float vector", name);
+    if (e->dalloc((void **)v, n * 4)) return -1;
+    return copy_in(e, *v, tmp.data(), n * 4, 0);
+}
+
+// Per layer, every local expert in one slab: [gate | up | down codes][gate | up | down scales],
+// each part 256-byte aligned, so an expert is one contiguous ~25 MB range of HBM.
+static size_t up256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+static int ensure_expert_slab(g5b_engine *e, Layer &w, int dt)
+{
+    if (w.expert_slab) {
+        if (w.expert_dt != dt) return fail("routed experts of one layer must share a dtype");
+        return 0;
+    }
+    const g5b_config &c = e->c;
+    const size_t mat = up256((size_t)c.moe_inter * c.hidden * elt(dt));
+    size_t sc = 0;
+    if (dt == G5B_DT_FP8) {
+        const int br = c.fp8_block_r, bc = c.fp8_block_c;
+        if (br < 1 || bc < 1) return fail("FP8 experts need the config's block size");
+        sc = up256((size_t)((c.moe_inter + br - 1) / br) * ((c.hidden + bc - 1) / bc) * 4) * 2 +
+             up256((size_t)((c.hidden + br - 1) / br) * ((c.moe_inter + bc - 1) / bc) * 4);
+    }
+    w.expert_stride = 3 * mat + sc;
+    w.expert_dt = dt;
+    if (e->dalloc((void **)&w.expert_slab, w.expert_stride * (size_t)e->n_local)) return -1;
+    w.table.assign((size_t)e->n_local + 1, ExpertW{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr});
+    w.have.assign((size_t)e->n_local * 3, 0);
+    for (int i = 0; i < e->n_local; i++) {
+        uint8_t *base = w.expert_slab + (size_t)i * w.expert_stride;
+        ExpertW &x = w.table[i];
+        x.gate = base; x.up = base + mat; x.down = base + 2 * mat;
+        if (dt == G5B_DT_FP8) {
+            const int br = c.fp8_block_r, bc = c.fp8_block_c;
+            const size_t gs = up256((size_t)((c.moe_inter + br - 1) / br) * ((c.hidden + bc - 1) / bc) * 4);
+            x.gate_s = (const float *)(base + 3 * mat);
+            x.up_s   = (const float *)(base + 3 * mat + gs);
+            x.down_s = (const float *)(base + 3 * mat + 2 * gs);
+        }
+    }
+    return 0;
+}
+
+static int load_expert_part(g5b_engine *e, int l, int ex, int which, const g5b_tensor *t, const char *name)
+{
+    const g5b_config &c = e->c;
+    Layer &w = e->L[l];
+    if (ex < e->n_local0 || ex >= e->n_local0 + e->n_local) return 0;   // another rank's expert
+    const int rows = which == 2 ? c.hidden : c.moe_inter, cols = which == 2 ? c.moe_inter : c.hidden;
+    if (t->rows != rows || t->cols != cols)
+        return fail("%s is %d x %d, the config implies %d x %d", name, t->rows, t->cols, rows, cols);
+    if (ensure_expert_slab(e, w, t->dtype)) return -1;
+    ExpertW &x = w.table[ex - e->n_local0];
+    const uint8_t *dstw = which == 0 ? x.gate : which == 1 ? x.up : x.down;
+    const float *dsts = which == 0 ? x.gate_s : which == 1 ? x.up_s : x.down_s;
+    if (copy_in(e, (void *)dstw, t->data, (size_t)rows * cols * elt(t->dtype), t->on_device)) return -1;
+    if (t->dtype == G5B_DT_FP8) {
+        if (!t->scale_inv) return fail("%s is FP8 but has no scale grid", name);
+        const size_t ns = (size_t)((rows + c.fp8_block_r - 1) / c.fp8_block_r) * ((cols + c.fp8_block_c - 1) / c.fp8_block_c);
+        if (copy_in(e, (void *)dsts, t->scale_inv, ns * 4, t->on_device)) return -1;
+    }
+    w.have[(size_t)(ex - e->n_local0) * 3 + which] = 1;
+    return 0;
+}
+
+extern "C" int g5b_engine_load(g5b_engine *e, const char *name, const g5b_tensor *t)
+{
+    if (e->finalized) return fail("load after finalize");
+    CU(cudaSetDevice(e->device));
+    const g5b_config &c = e->c;
+    if (!strcmp(name, "embed_tokens.weight")) {
+        if (t->dtype == G5B_DT_FP8) return fail("an FP8 embedding table is not supported");
+        return upload_mat(e, &e->embed, t, c.vocab, c.hidden, name);
+    }
+    if (!strcmp(name, "lm_head.weight")) return upload_mat(e, &e->lm_head, t, c.vocab, c.hidden, name);
+    if (!strcmp(name, "norm.weight")) return upload_vec(e, &e->norm, t, (size_t)c.hidden, name);
+    int l = -1, used = 0;
+    if (sscanf(name, "layers.%d.%n", &l, &used) != 1 || l < 0 || l >= c.n_layers)
+        return fail("unknown tensor %s", name);
+    const char *rest = name + used;
+    int ex = -1, n2 = 0;
+    if (!e->L[l].is_dense && sscanf(rest, "mlp.experts.%d.%n", &ex, &n2) == 1) {
+        if (ex < 0 || ex >= c.n_experts) return fail("%s: expert out of range", name);
+        const char *p = rest + n2;
+        const int which = !strcmp(p, "gate_proj.weight") ? 0 : !strcmp(p, "up_proj.weight") ? 1
+                        : !strcmp(p, "down_proj.weight") ? 2 : -1;
+        if (which < 0) return fail("unknown tensor %s", name);
+        return load_expert_part(e, l, ex, which, t, name);
+    }
+    auto it = e->names[l].find(rest);
+    if (it == e->names[l].end()) return fail("tensor %s does not belong to layer %d of this config", name, l);
+    const Target &tg = it->second;
+    if (tg.kind == 0) return upload_mat(e, tg.mat, t, tg.rows, tg.cols, name);
+    return upload_vec(e, tg.vec, t, (size_t)tg.rows, name);
+}
+
+extern "C" int g5b_engine_fill_expert(g5b_engine *e, int layer, int expert, uint64_t seed,
+                                      const float *gate_s, const float *up_s, const float *down_s)
+{
+    if (e->finalized) return fail("fill after finalize");
+    CU(cudaSetDevice(e->device));
+    const g5b_config &c = e->c;
+    if (layer < 0 || layer >= c.n_layers || e->L[layer].is_dense) return fail("layer %d is not a MoE layer", layer);
+    if (expert < e->n_local0 || expert >= e->n_local0 + e->n_local) return 0;
+    Layer &w = e->L[layer];
+    if (ensure_expert_slab(e, w, G5B_DT_FP8)) return -1;
+    ExpertW &x = w.table[expert - e->n_local0];
+    const size_t n = (size_t)c.moe_inter * c.hidden;
+    if (n % 4) return fail("synthetic experts need moe_inter * hidden to be a multiple of 4");
+    fill_codes(e->st, (uint8_t *)x.gate, seed, layer, expert, 0, n);
+    fill_codes(e->st, (uint8_t *)x.up, seed, layer, expert, 1, n);
+    fill_codes(e->st, (uint8_t *)x.down, seed, layer, expert, 2, n);
+    const int br = c.fp8_block_r, bc = c.fp8_block_c;
+    const size_t gs = (size_t)((c.moe_inter + br - 1) / br) * ((c.hidden + bc - 1) / bc);
+    const size_t ds = (size_t)((c.hidden + br - 1) / br) * ((c.moe_inter + bc - 1) / bc);
+    if (copy_in(e, (void *)x.gate_s, gate_s, gs * 4, 0) || copy_in(e, (void *)x.up_s, up_s, gs * 4, 0) ||
+        copy_in(e, (void *)x.down_s, down_s, ds * 4, 0)) return -1;
+    w.have[(size_t)(expert - e->n_local0) * 3 + 0] = w.have[(size_t)(expert - e->n_local0) * 3 + 1] =
+        w.have[(size_t)(expert - e->n_local0) * 3 + 2] = 1;
+    return 0;
+}
+
+template <typename T>
+static int walloc(g5b_engine *e, T **p, size_t count) { return e->dalloc((void **)p, count * sizeof(T)); }
+
+extern "C" int g5b_engine_finalize(g5b_engine *e)
+{
+    if (e->finalized) return 0;
+    CU(cudaSetDevice(e->device));
+    const g5b_config &c = e->c;
+    // A missing tensor must fail here: running with a NULL or zero weight gives plausible, wrong
+    // tokens (the reference's bind refuses for the same reason, src/model/glm53f_bind.h:3-6).
+    // Single-layer harnesses may leave embeddings and the head out; forward then refuses.
+    for (int l = 0; l < c.n_layers; l++) {
+        Layer &w = e->L[l];
+        for (auto &kv : e->names[l]) {
+            const Target &t = kv.second;
+            const bool ok = t.kind == 0 ? t.mat->loaded() : (*t.vec != nullptr);
+            if (!ok && !e->partial) return fail("layer %d: tensor %s was never loaded", l, kv.first.c_str());
+        }
+        if (!w.is_dense && (w.expert_slab || !e->partial)) {
+            if (!w.expert_slab) return fail("layer %d: no routed expert was loaded", l);
+            if (w.router.dt == G5B_DT_FP8) return fail("layer %d: the router must be BF16 or FP32", l);
+            for (int i = 0; i < e->n_local; i++)
+                for (int k = 0; k < 3; k++)
+                    if (!w.have[(size_t)i * 3 + k])
+                        return fail("layer %d: routed expert %d is incomplete", l, e->n_local0 + i);
+            if (c.n_shared == 1 && w.sh_gate.dt == w.expert_dt) {
+                ExpertW &s = w.table[e->n_local];
+                s.gate = (const uint8_t *)w.sh_gate.w; s.up = (const uint8_t *)w.sh_up.w; s.down = (const uint8_t *)w.sh_down.w;
+                s.gate_s = w.sh_gate.s; s.up_s = w.sh_up.s; s.down_s = w.sh_down.s;
+            }
+            if (walloc(e, &w.table_dev, w.table.size())) return -1;
+            CU(cudaMemcpyAsync(w.table_dev, w.table.data(), w.table.size() * sizeof(ExpertW), cudaMemcpyHostToDevice, e->st));
+            CU(cudaStreamSynchronize(e->st));
+        }
+        // session state (reference: src/model/glm53f_model.c:194-228, always the latent form here)
+        if (w.is_mla) {
+            if (e->dalloc(&w.latent, (size_t)e->cap * c.kv_lora * (e->latent_bf16 ? 2 : 4))) return -1;
+            const size_t ni = (size_t)2 * e->cap * c.index_dim +
+                              (size_t)((e->cap + c.index_kpool - 1) / c.index_kpool) * c.index_dim;
+            if (walloc(e, &w.idx_state, ni)) return -1;
+        } else {
+            const size_t P = (size_t)c.kda_heads * c.kda_head_dim;
+            if (walloc(e, &w.kda_state, P * c.kda_head_dim + 3 * P * (size_t)(c.conv_k - 1))) return -1;
+        }
+    }
+    const size_t N = CHUNK, E = c.hidden, M = c.hc_mult, MIX = (2 + M) * M;
+    const size_t P = (size_t)c.kda_heads * c.kda_head_dim, D = c.kda_head_dim;
+    const size_t H = c.mla_heads, KL = c.kv_lora, stride = (size_t)c.index_topk + c.index_kpool;
+    const size_t K = c.topk, I = c.moe_inter, SI = (size_t)c.moe_inter * c.n_shared;
+    const size_t DI = c.dense_inter > (int)SI ? c.dense_inter : SI;
+    if (walloc(e, &e->inv0, N) || walloc(e, &e->inv1, N) || walloc(e, &e->mix, N * MIX) ||
+        walloc(e, &e->xc, N * E) || walloc(e, &e->xn, N * E) || walloc(e, &e->y, N * E) ||
+        walloc(e, &e->post, N * M) || walloc(e, &e->comb, N * M * M)) return -1;
+    if (walloc(e, &e->kq, N * P) || walloc(e, &e->kk, N * P) || walloc(e, &e->kv, N * P) ||
+        walloc(e, &e->kz, N * P) || walloc(e, &e->kgb, N * P) || walloc(e, &e->ko, N * P) ||
+        walloc(e, &e->kbraw, N * c.kda_heads) || walloc(e, &e->klr, N * 2 * D)) return -1;
+    if (walloc(e, &e->mq_raw, N * c.q_lora) || walloc(e, &e->mct, N * KL) || walloc(e, &e->mwk, N * c.index_dim) ||
+        walloc(e, &e->mgate, N * c.index_dim) || walloc(e, &e->mwp, N * c.index_heads) ||
+        walloc(e, &e->mq, N * H * c.qk_nope) || walloc(e, &e->mqidx, N * (size_t)c.index_heads * c.index_dim) ||
+        walloc(e, &e->mcb, N * H * KL) || walloc(e, &e->macc, N * H * c.v_head) ||
+        walloc(e, &e->mscore, N * ((size_t)e->cap / c.index_kpool + 1)) || walloc(e, &e->minvq, N) ||
+        walloc(e, &e->mqa, N * H * KL) || walloc(e, &e->mdsc, N * H * stride) ||
+        walloc(e, &e->msel, N * stride) || walloc(e, &e->mnsel, N)) return -1;
+    const size_t pairs = N * K + N;
+    if (walloc(e, &e->rscore, N * c.n_experts) || walloc(e, &e->rw, N * K) || walloc(e, &e->ridx, N * K) ||
+        walloc(e, &e->act, pairs * (I > SI ? I : SI)) || walloc(e, &e->contrib, pairs * E) ||
+        walloc(e, &e->gu, N * 2 * DI) || walloc(e, &e->dact, N * DI)) return -1;
+    e->plan.max_slots = (int)((N * K < (size_t)e->n_local ? N * K : (size_t)e->n_local) + 1);
+    e->plan.max_pairs = (int)pairs;
+    if (walloc(e, &e->plan.n_slots, 1) || walloc(e, &e->plan.slot_expert, e->plan.max_slots) ||
+        walloc(e, &e->plan.slot_off, e->plan.max_slots) || walloc(e, &e->plan.slot_cnt, e->plan.max_slots) ||
+        walloc(e, &e->plan.pair_tok, pairs) || walloc(e, &e->plan.pair_dst, pairs)) return -1;
+    if (walloc(e, &e->xm, N * E) || walloc(e, &e->inv_head, N) || walloc(e, &e->logits, N * (size_t)c.vocab) ||
+        walloc(e, &e->am_v, N * 64) || walloc(e, &e->am_i, N * 64) || walloc(e, &e->am_out, (size_t)e->cap + N)) return -1;
+    CU(cudaStreamSynchronize(e->st));
+    e->finalized = true;
+    return 0;
+}
+
+// ------------------------------------------------------------------ sub-blocks ----
+static MoeShape moe_shape(const g5b_engine *e, const Layer &w)
+{
+    const g5b_config &c = e->c;
+    MoeShape s;
+    s.E = c.hidden; s.I = c.moe_inter; s.NE = c.n_experts; s.K = c.topk;
+    s.br = c.fp8_block_r; s.bc = c.fp8_block_c; s.dt = w.expert_dt < 0 ? G5B_DT_FP8 : w.expert_dt;
+    s.n_local0 = e->n_local0; s.n_local = e->n_local;
+    s.limit = c.swiglu_limit; s.routed_scale = c.routed_scale; s.norm_topk = c.norm_topk;
+    return s;
+}
+
+static void prof_mark(g5b_engine *e, int slot)
+{
+    if (e->profile) cudaEventRecord(e->prof_ev[slot], e->st);
+}
+static void prof_collect(g5b_engine *e, int nslots)
+{
+    if (!e->profile) return;
+    cudaEventSynchronize(e->prof_ev[nslots]);
+    for (int i = 0; i < nslots; i++) {
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, e->prof_ev[i], e->prof_ev[i + 1]);
+        e->prof_ms[i] += ms;
+    }
+    e->prof_n++;
+}
+
+// x [n][E] (already normalised) -> out [n][E]. Router, plan, experts, combine.
+static int run_moe(g5b_engine *e, Layer &w, const float *x, int n, float *out, int with_shared)
+{
+    const g5b_config &c = e->c;
+    if (!w.table_dev || !w.router.loaded() || !w.bias || (with_shared && !w.sh_down.loaded()))
+        return fail("this layer's MoE weights were not loaded");
+    const MoeShape s = moe_shape(e, w);
+    const bool shared_in_plan = with_shared && c.n_shared == 1 && w.sh_gate.dt == s.dt;
+    prof_mark(e, 0);
+    router_topk(e->st, e->ridx, e->rw, x, c.hidden, w.router.w, w.router.dt, w.bias,
+                reinterpret_cast<double *>(e->rscore), n, s);
+    moe_plan(e->st, e->plan, e->ridx, n, s, shared_in_plan ? 1 : 0);
+    prof_mark(e, 1);
+    moe_gateup(e->st, e->act, x, c.hidden, w.table_dev, e->plan, n, s);
+    prof_mark(e, 2);
+    moe_down(e->st, e->contrib, e->act, w.table_dev, e->plan, n, s);
+    prof_mark(e, 3);
+    if (with_shared && !shared_in_plan) {
+        // a shared expert of another width or format goes through the plain MLP path
+        const int SI = c.moe_inter * c.n_shared;
+        GemvSeg g[2] = {make_seg(w.sh_gate, x, c.hidden, e->gu, 2 * SI), make_seg(w.sh_up, x, c.hidden, e->gu + SI, 2 * SI)};
+        gemv_batch(e->st, g, 2, n);
+        swiglu(e->st, e->dact, e->gu, SI, n, c.swiglu_limit);
+        gemv(e->st, w.sh_down, e->dact, SI, e->contrib + (size_t)n * c.topk * c.hidden, c.hidden, n);
+    }
+    moe_combine(e->st, out, c.hidden, e->contrib, e->rw, n, s, with_shared);
+    prof_mark(e, 4);
+    prof_collect(e, 4);
+    return 0;
+}
+
+static int run_mlp(g5b_engine *e, Layer &w, const float *x, int n, float *out)
+{
+    const g5b_config &c = e->c;
+    const int DI = c.dense_inter;
+    if (!w.d_gate.loaded() || !w.d_up.loaded() || !w.d_down.loaded()) return fail("this layer's dense MLP was not loaded");
+    GemvSeg g[2] = {make_seg(w.d_gate, x, c.hidden, e->gu, 2 * DI), make_seg(w.d_up, x, c.hidden, e->gu + DI, 2 * DI)};
+    gemv_batch(e->st, g, 2, n);
+    swiglu(e->st, e->dact, e->gu, DI, n, c.swiglu_limit);
+    gemv(e->st, w.d_down, e->dact, DI, out, c.hidden, n);
+    return 0;
+}
+
+static int run_kda(g5b_engine *e, Layer &w, const float *x, int n, float *out)
+{
+    const g5b_config &c = e->c;
+    const int E = c.hidden, H = c.kda_heads, D = c.kda_head_dim, P = H * D;
+    if (!w.kq.loaded() || !w.ko.loaded() || !w.g_b.loaded() || !w.f_b.loaded() || !w.kda_state || !w.dt_bias)
+        return fail("this layer's KDA weights were not loaded");
+    float *lrf = e->klr, *lrg = e->klr + (size_t)CHUNK * D;
+    GemvSeg a[6] = {make_seg(w.kq, x, E, e->kq, P), make_seg(w.kk, x, E, e->kk, P), make_seg(w.kv, x, E, e->kv, P),
+                    make_seg(w.kb, x, E, e->kbraw, H), make_seg(w.f_a, x, E, lrf, D), make_seg(w.g_a, x, E, lrg, D)};
+    gemv_batch(e->st, a, 6, n);
+    GemvSeg b[2] = {make_seg(w.f_b, lrf, D, e->kz, P), make_seg(w.g_b, lrg, D, e->kgb, P)};
+    gemv_batch(e->st, b, 2, n);
+    KdaShape ks{H, D, c.conv_k, c.gate_lb, c.rms_eps};
+    kda_core(e->st, e->ko, e->kq, e->kk, e->kv, e->kz, e->kbraw, e->kgb, w.q_conv, w.k_conv, w.v_conv,
+             w.A_log, w.dt_bias, w.o_norm, w.kda_state, n, ks);
+    gemv(e->st, w.ko, e->ko, P, out, E, n);
+    return 0;
+}
+
+static MlaShape mla_shape(const g5b_engine *e)
+{
+    const g5b_config &c = e->c;
+    MlaShape s;
+    s.H = c.mla_heads; s.qn = c.qk_nope; s.vh = c.v_head; s.KL = c.kv_lora; s.q_lora = c.q_lora;
+    s.E = c.hidden; s.cap = e->cap; s.ID = c.index_dim; s.IH = c.index_heads; s.KP = c.index_kpool;
+    s.topk = c.index_topk; s.rms_eps = c.rms_eps; s.latent_bf16 = e->latent_bf16;
+    return s;
+}
+
+static int run_mla(g5b_engine *e, Layer &w, const float *x, int n, int cached, float *out)
+{
+    const g5b_config &c = e->c;
+    const int E = c.hidden;
+    const MlaShape s = mla_shape(e);
+    if (!w.q_a.loaded() || !w.kv_b.loaded() || !w.mo.loaded() || !w.wq_b.loaded() || !w.ape || !w.latent)
+        return fail("this layer's MLA weights were not loaded");
+    if (cached + n > e->cap) return fail("MLA cache position %d beyond capacity %d", cached + n - 1, e->cap);
+    GemvSeg a[5] = {make_seg(w.q_a, x, E, e->mq_raw, c.q_lora), make_seg(w.kv_a, x, E, e->mct, c.kv_lora),
+                    make_seg(w.wk, x, E, e->mwk, c.index_dim), make_seg(w.igate, x, E, e->mgate, c.index_dim),
+                    make_seg(w.wproj, x, E, e->mwp, c.index_heads)};
+    gemv_batch(e->st, a, 5, n);
+    rms_factor(e->st, e->mq_raw, c.q_lora, c.q_lora, n, c.rms_eps, e->minvq);
+    mla_store(e->st, w.latent, w.idx_state, e->mct, w.kv_a_norm, e->mwk, e->mgate, w.k_norm_w, w.k_norm_b,
+              w.ape, n, cached, s);
+    // q = q_b(RMSNorm(q_a x)) and the indexer query, the norm applied on the way into the product
+    GemvSeg b[2] = {make_seg(w.q_b, e->mq_raw, c.q_lora, e->mq, c.mla_heads * c.qk_nope, e->minvq, w.q_a_norm),
+                    make_seg(w.wq_b, e->mq_raw, c.q_lora, e->mqidx, c.index_heads * c.index_dim, e->minvq, w.q_a_norm)};
+    gemv_batch(e->st, b, 2, n);
+    dsa_select(e->st, e->msel, e->mnsel, w.idx_state, e->mqidx, e->mwp, e->mscore, n, cached, s);
+    mla_absorb(e->st, e->mqa, e->mq, w.kv_b, n, s);
+    mla_attend(e->st, e->mcb, e->mqa, w.latent, e->msel, e->mnsel, e->mdsc, n, cached, s);
+    mla_vout(e->st, e->macc, e->mcb, w.kv_b, n, s);
+    gemv(e->st, w.mo, e->macc, c.mla_heads * c.v_head, out, E, n);
+    return 0;
+}
+
+static int run_hc_pre(g5b_engine *e, const HcW &hw, const float *h, int n)
+{
+    if (!hw.fn.loaded() || !hw.base || !hw.scale) return fail("this layer's mHC weights were not loaded");
+    const g5b_config &c = e->c;
+    const int M = c.hc_mult, E = c.hidden, MIX = (2 + M) * M;
+    rms_factor(e->st, h, M * E, M * E, n, c.rms_eps, e->inv0);
+    gemv(e->st, hw.fn, h, M * E, e->mix, MIX, n, e->inv0, nullptr);
+    hc_finish(e->st, e->xc, e->post, e->comb, h, e->mix, hw, n, M, E, c.hc_iters, c.hc_eps);
+    return 0;
+}
+
+// One decoder layer over n <= CHUNK positions (reference: glm53f_decoder_layer,
+// src/core/glm53f_ops.c:1400-1433).
+static int run_layer(g5b_engine *e, int l, float *h, int n, int cached)
+{
+    const g5b_config &c = e->c;
+    Layer &w = e->L[l];
+    const int M = c.hc_mult, E = c.hidden;
+    for (int site = 0; site < 2; site++) {
+        if (run_hc_pre(e, w.hc[site], h, n)) return -1;
+        if (!w.in_norm || !w.post_norm) return fail("this layer's norms were not loaded");
+        rms_factor(e->st, e->xc, E, E, n, c.rms_eps, e->inv1);
+        rms_apply(e->st, e->xn, e->xc, site ? w.post_norm : w.in_norm, e->inv1, E, E, n);
+        int rc;
+        if (site == 0) rc = w.is_mla ? run_mla(e, w, e->xn, n, cached, e->y) : run_kda(e, w, e->xn, n, e->y);
+        else           rc = w.is_dense ? run_mlp(e, w, e->xn, n, e->y) : run_moe(e, w, e->xn, n, e->y, 1);
+        if (rc) return rc;
+        hc_post(e->st, h, e->y, e->post, e->comb, n, M, E);
+    }
+    return 0;
+}
+
+static int ensure_h(g5b_engine *e, size_t tokens)
+{
+    if (tokens <= e->h_tokens) return 0;
+    const size_t per = (size_t)e->c.hc_mult * e->c.hidden;
+    if (e->h) cudaFree(e->h);
+    e->h = nullptr; e->h_tokens = 0;
+    CU(cudaMalloc((void **)&e->h, tokens * per * 4));
+    e->h_tokens = tokens;
+    return 0;
+}
+
+static int ensure_ids(g5b_engine *e, size_t n)
+{
+    if (n <= e->ids_cap) return 0;
+    if (e->ids_dev) cudaFree(e->ids_dev);
+    e->ids_dev = nullptr; e->ids_cap = 0;
+    CU(cudaMalloc((void **)&e->ids_dev, n * 4));
+    e->ids_cap = n;
+    return 0;
+}
+
+// Layers over T positions whose ids are already on the device, then the head for positions
+// [first, T): logits of position t land in e->logits row (t - first) % CHUNK, arg-max in
+// e->am_out[t].
+static int forward_device(g5b_engine *e, const int *ids_dev, int T, bool all_positions, float *logits_host,
+                          int *argmax_host)
+{
+    const g5b_config &c = e->c;
+    const int M = c.hc_mult, E = c.hidden;
+    if (!e->embed.loaded() || !e->lm_head.loaded() || !e->norm)
+        return fail("forward needs embed_tokens, norm and lm_head");
+    if (ensure_h(e, (size_t)T)) return -1;
+    embed_rows(e->st, e->h, e->embed, ids_dev, T, M);
+    for (int l = 0; l < c.n_layers; l++)
+        for (int t0 = 0; t0 < T; t0 += CHUNK) {
+            const int n = T - t0 < CHUNK ? T - t0 : CHUNK;
+            if (run_layer(e, l, e->h + (size_t)t0 * M * E, n, e->cached + t0)) return -1;
+        }
+    const int first = all_positions ? 0 : T - 1;
+    for (int t0 = first; t0 < T; t0 += CHUNK) {
+        const int n = T - t0 < CHUNK ? T - t0 : CHUNK;
+        head_mean(e->st, e->xm, e->h + (size_t)t0 * M * E, n, M, E);
+        rms_factor(e->st, e->xm, E, E, n, c.rms_eps, e->inv_head);
+        gemv(e->st, e->lm_head, e->xm, E, e->logits, c.vocab, n, e->inv_head, e->norm);
+        argmax_rows(e->st, e->am_out + t0, e->logits, c.vocab, n, e->am_v, e->am_i);
+        if (logits_host && t0 + n == T)
+            CU(cudaMemcpyAsync(logits_host, e->logits + (size_t)(n - 1) * c.vocab, (size_t)c.vocab * 4,
+                               cudaMemcpyDeviceToHost, e->st));
+    }
+    if (argmax_host)
+        CU(cudaMemcpyAsync(argmax_host, e->am_out + first, (size_t)(T - first) * 4, cudaMemcpyDeviceToHost, e->st));
+    return 0;
+}
+
+extern "C" int g5b_engine_forward(g5b_engine *e, const int *ids, int T, float *logits, int *argmax_all)
+{
+    if (!e->finalized) return fail("forward before finalize");
+    CU(cudaSetDevice(e->device));
+    if (T < 1) return fail("forward needs at least one token");
+    if (e->cached + T > e->cap)
+        return fail("%d cached + %d new positions exceed the session capacity %d", e->cached, T, e->cap);
+    for (int t = 0; t < T; t++)
+        if (ids[t] < 0 || ids[t] >= e->c.vocab) return fail("token id %d outside the vocabulary", ids[t]);
+    if (ensure_ids(e, (size_t)T)) return -1;
+    CU(cudaMemcpyAsync(e->ids_dev, ids, (size_t)T * 4, cudaMemcpyHostToDevice, e->st));
+    if (forward_device(e, e->ids_dev, T, argmax_all != nullptr, logits, argmax_all)) return -1;
+    CU(cudaStreamSynchronize(e->st));
+    CU(cudaGetLastError());
+    e->cached += T;
+    return 0;
+}
+
+// Greedy decode without host round trips: each step's arg-max (already in device memory) is the
+// next step's token id.
+extern "C" int g5b_engine_decode_greedy(g5b_engine *e, int first, int n, int *out)
+{
+    if (!e->finalized) return fail("decode before finalize");
+    CU(cudaSetDevice(e->device));
+    if (n < 1 || e->cached + n > e->cap) return fail("decode of %d tokens exceeds the session capacity", n);
+    if (first < 0 || first >= e->c.vocab) return fail("token id %d outside the vocabulary", first);
+    if (ensure_ids(e, (size_t)n + 1)) return -1;
+    CU(cudaMemcpyAsync(e->ids_dev, &first, 4, cudaMemcpyHostToDevice, e->st));
+    for (int i = 0; i < n; i++) {
+        if (forward_device(e, e->ids_dev + i, 1, false, nullptr, nullptr)) return -1;
+        CU(cudaMemcpyAsync(e->ids_dev + i + 1, e->am_out, 4, cudaMemcpyDeviceToDevice, e->st));
+        e->cached += 1;
+    }
+    CU(cudaMemcpyAsync(out, e->ids_dev + 1, (size_t)n * 4, cudaMemcpyDeviceToHost, e->st));
+    CU(cudaStreamSynchronize(e->st));
+    CU(cudaGetLastError());
+    return 0;
+}
+
+extern "C" void g5b_engine_reset(g5b_engine *e)
+{
+    cudaSetDevice(e->device);
+    const g5b_config &c = e->c;
+    const size_t P = (size_t)c.kda_heads * c.kda_head_dim;
+    for (auto &w : e->L)
+        if (w.kda_state) cudaMemsetAsync(w.kda_state, 0, (P * c.kda_head_dim + 3 * P * (size_t)(c.conv_k - 1)) * 4, e->st);
+    cudaStreamSynchronize(e->st);
+    e->cached = 0;
+}
+
+extern "C" int g5b_engine_cached(const g5b_engine *e) { return e->cached; }
+
+extern "C" void g5b_engine_free(g5b_engine *e)
+{
+    if (!e) return;
+    cudaSetDevice(e->device);
+    cudaStreamSynchronize(e->st);
+    for (void *p : e->owned) cudaFree(p);
+    if (e->h) cudaFree(e->h);
+    if (e->ids_dev) cudaFree(e->ids_dev);
+    if (e->flush_buf) cudaFree(e->flush_buf);
+    for (int i = 0; i <= PROF_SLOTS; i++) cudaEventDestroy(e->prof_ev[i]);
+    cudaStreamDestroy(e->st);
+    delete e;
+}
+
+extern "C" int g5b_engine_sync(g5b_engine *e)
+{
+    CU(cudaSetDevice(e->device));
+    CU(cudaStreamSynchronize(e->st));
+    CU(cudaGetLastError());
+    return 0;
+}
+
+extern "C" void *g5b_engine_stream(g5b_engine *e) { return (void *)e->st; }
+
+// -------------------------------------------------------------- device-pointer ops ----
+static int check_layer(g5b_engine *e, int layer, int n)
+{
+    if (!e->finalized) return fail("op before finalize");
+    if (layer < 0 || layer >= e->c.n_layers) return fail("layer %d out of range", layer);
+    if (n < 1 || n > CHUNK) return fail("ops take 1..%d positions per call, got %d", CHUNK, n);
+    if (cudaSetDevice(e->device) != cudaSuccess) return fail("cudaSetDevice failed");
+    return 0;
+}
+
+extern "C" int g5b_dev_moe(g5b_engine *e, int layer, const float *x_dev, int T, float *out_dev)
+{
+    if (check_layer(e, layer, T)) return -1;
+    if (e->L[layer].is_dense) return fail("layer %d has a dense MLP", layer);
+    return run_moe(e, e->L[layer], x_dev, T, out_dev, 1);
+}
+
+extern "C" int g5b_dev_kda(g5b_engine *e, int layer, const float *x_dev, int T, float *out_dev)
+{
+    if (check_layer(e, layer, T)) return -1;
+    if (e->L[layer].is_mla) return fail("layer %d is an MLA layer", layer);
+    return run_kda(e, e->L[layer], x_dev, T, out_dev);
+}
+
+extern "C" int g5b_dev_mla(g5b_engine *e, int layer, const float *x_dev, int T, int cached, float *out_dev)
+{
+    if (check_layer(e, layer, T)) return -1;
+    if (!e->L[layer].is_mla) return fail("layer %d is a KDA layer", layer);
+    return run_mla(e, e->L[layer], x_dev, T, cached, out_dev);
+}
+
+extern "C" int g5b_dev_decoder_layer(g5b_engine *e, int layer, float *h_dev, int T, int cached)
+{
+    if (check_layer(e, layer, T)) return -1;
+    return run_layer(e, layer, h_dev, T, cached);
+}
+
+// ------------------------------------------------------------------ host-buffer ops ----
+struct Staged {
+    g5b_engine *e;
+    std::vector<void *> bufs;
+    ~Staged() { for (void *p : bufs) cudaFree(p); }
+    float *in(const float *src, size_t n)
+    {
+        void *p = nullptr;
+        if (cudaMalloc(&p, n * 4 + 16) != cudaSuccess) return nullptr;
+        bufs.push_back(p);
+        if (src) cudaMemcpyAsync(p, src, n * 4, cudaMemcpyHostToDevice, e->st);
+        else     cudaMemsetAsync(p, 0, n * 4, e->st);
+        return (float *)p;
+    }
+    int out(float *dst, const float *src, size_t n)
+    {
+        CU(cudaMemcpyAsync(dst, src, n * 4, cudaMemcpyDeviceToHost, e->st));
+        CU(cudaStreamSynchronize(e->st));
+        CU(cudaGetLastError());
+        return 0;
+    }
+};
+
+// Ops accept any T: the host entry points walk it in CHUNK-sized pieces.
+#define FOR_CHUNKS(T) for (int t0 = 0, n_ = 0; (n_ = (T) - t0 < CHUNK ? (T) - t0 : CHUNK), t0 < (T); t0 += CHUNK)
+
+// Host buffers through the engine's own staging rows (no allocation per call): copy a piece in,
+// run, copy the result out; one wait at the end. With pinned host memory the copies overlap the
+// kernels of the neighbouring pieces.
+template <typename F>
+static int host_op(g5b_engine *e, const float *x, int T, float *out, F &&run)
+{
+    const size_t E = e->c.hidden;
+    FOR_CHUNKS(T) {
+        CU(cudaMemcpyAsync(e->xn, x + t0 * E, n_ * E * 4, cudaMemcpyHostToDevice, e->st));
+        if (run(e->xn, n_, e->y, t0)) return -1;
+        CU(cudaMemcpyAsync(out + t0 * E, e->y, n_ * E * 4, cudaMemcpyDeviceToHost, e->st));
+    }
+    CU(cudaStreamSynchronize(e->st));
+    CU(cudaGetLastError());
+    return 0;
+}
+
+extern "C" int g5b_op_moe(g5b_engine *e, int layer, const float *x, int T, float *out, int with_shared)
+{
+    if (check_layer(e, layer, 1)) return -1;
+    if (e->L[layer].is_dense) return fail("layer %d has a dense MLP", layer);
+    return host_op(e, x, T, out, [&](const float *xd, int n, float *od, int) {
+        return run_moe(e, e->L[layer], xd, n, od, with_shared);
+    });
+}
+
+extern "C" int g5b_op_router(g5b_engine *e, int layer, const float *x, int T, int *idx, float *w)
+{
+    if (check_layer(e, layer, 1)) return -1;
+    if (e->L[layer].is_dense) return fail("layer %d has a dense MLP", layer);
+    const size_t E = e->c.hidden, K = e->c.topk;
+    Layer &lw = e->L[layer];
+    Staged s{e};
+    float *xd = s.in(x, (size_t)T * E);
+    if (!xd) return fail("out of device memory");
+    const MoeShape ms = moe_shape(e, lw);
+    FOR_CHUNKS(T) {
+        router_topk(e->st, e->ridx, e->rw, xd + t0 * E, (int)E, lw.router.w, lw.router.dt, lw.bias,
+                    reinterpret_cast<double *>(e->rscore), n_, ms);
+        CU(cudaMemcpyAsync(idx + t0 * K, e->ridx, n_ * K * 4, cudaMemcpyDeviceToHost, e->st));
+        CU(cudaMemcpyAsync(w + t0 * K, e->rw, n_ * K * 4, cudaMemcpyDeviceToHost, e->st));
+        CU(cudaStreamSynchronize(e->st));
+    }
+    CU(cudaGetLastError());
+    return 0;
+}
+
+extern "C" int g5b_op_mlp(g5b_engine *e, int layer, const float *x, int T, float *out)
+{
+    if (check_layer(e, layer, 1)) return -1;
+    if (!e->L[layer].is_dense) return fail("layer %d is a MoE layer", layer);
+    return host_op(e, x, T, out, [&](const float *xd, int n, float *od, int) {
+        return run_mlp(e, e->L[layer], xd, n, od);
+    });
+}
+
+extern "C" int g5b_op_kda(g5b_engine *e, int layer, const float *x, int T, float *out)
+{
+    if (check_layer(e, layer, 1)) return -1;
+    if (e->L[layer].is_mla) return fail("layer %d is an MLA layer", layer);
+    return host_op(e, x, T, out, [&](const float *xd, int n, float *od, int) {
+        return run_kda(e, e->L[layer], xd, n, od);
+    });
+}
+
+extern "C" int g5b_op_mla(g5b_engine *e, int layer, const float *x, int T, int cached, float *out,
+                          int *sel_out, int *n_sel_out)
+{
+    if (check_layer(e, layer, 1)) return -1;
+    if (!e->L[layer].is_mla) return fail("layer %d is a KDA layer", layer);
+    int last_n = 0;
+    if (host_op(e, x, T, out, [&](const float *xd, int n, float *od, int t0) {
+            last_n = n;
+            return run_mla(e, e->L[layer], xd, n, cached + t0, od);
+        })) return -1;
+    if (n_sel_out) {
+        int ns = 0;
+        CU(cudaMemcpyAsync(&ns, e->mnsel + last_n - 1, 4, cudaMemcpyDeviceToHost, e->st));
+        CU(cudaStreamSynchronize(e->st));
+        *n_sel_out = ns;
+        if (sel_out && ns > 0) {
+            CU(cudaMemcpyAsync(sel_out, e->msel + (size_t)(last_n - 1) * (e->c.index_topk + e->c.index_kpool),
+                               (size_t)ns * 4, cudaMemcpyDeviceToHost, e->st));
+            CU(cudaStreamSynchronize(e->st));
+        }
+    }
+    return 0;
+}
+
+extern "C" int g5b_op_hc_pre(g5b_engine *e, int layer, int site, const float *h, int T, float *x,
+                             float *post, float *comb)
+{
+    if (check_layer(e, layer, 1)) return -1;
+    const size_t E = e->c.hidden, M = e->c.hc_mult;
+    Staged s{e};
+    float *hd = s.in(h, (size_t)T * M * E);
+    if (!hd) return fail("out of device memory");
+    FOR_CHUNKS(T) {
+        if (run_hc_pre(e, e->L[layer].hc[site ? 1 : 0], hd + t0 * M * E, n_)) return -1;
+        CU(cudaMemcpyAsync(x + t0 * E, e->xc, n_ * E * 4, cudaMemcpyDeviceToHost, e->st));
+        CU(cudaMemcpyAsync(post + t0 * M, e->post, n_ * M * 4, cudaMemcpyDeviceToHost, e->st));
+        CU(cudaMemcpyAsync(comb + t0 * M * M, e->comb, n_ * M * M * 4, cudaMemcpyDeviceToHost, e->st));
+        CU(cudaStreamSynchronize(e->st));
+    }
+    CU(cudaGetLastError());
+    return 0;
+}
+
+extern "C" int g5b_op_hc_post(g5b_engine *e, float *h, const float *y, const float *post,
+                              const float *comb, int T)
+{
+    if (check_layer(e, 0, 1)) return -1;
+    const size_t E = e->c.hidden, M = e->c.hc_mult;
+    Staged s{e};
+    float *hd = s.in(h, (size_t)T * M * E), *yd = s.in(y, (size_t)T * E), *pd = s.in(post, (size_t)T * M),
+          *cd = s.in(comb, (size_t)T * M * M);
+    if (!hd || !yd || !pd || !cd) return fail("out of device memory");
+    hc_post(e->st, hd, yd, pd, cd, T, (int)M, (int)E);
+    return s.out(h, hd, (size_t)T * M * E);
+}
+
+extern "C" int g5b_op_decoder_layer(g5b_engine *e, int layer, float *h, int T, int cached)
+{
+    if (check_layer(e, layer, 1)) return -1;
+    const size_t E = e->c.hidden, M = e->c.hc_mult;
+    Staged s{e};
+    float *hd = s.in(h, (size_t)T * M * E);
+    if (!hd) return fail("out of device memory");
+    FOR_CHUNKS(T) if (run_layer(e, layer, hd + t0 * M * E, n_, cached + t0)) return -1;
+    return s.out(h, hd, (size_t)T * M * E);
+}
+
+static DMat *find_mat(g5b_engine *e, const char *name)
+{
+    if (!strcmp(name, "embed_tokens.weight")) return &e->embed;
+    if (!strcmp(name, "lm_head.weight")) return &e->lm_head;
+    int l = -1, used = 0;
+    if (sscanf(name, "layers.%d.%n", &l, &used) != 1 || l < 0 || l >= e->c.n_layers) return nullptr;
+    auto it = e->names[l].find(name + used);
+    if (it == e->names[l].end() || it->second.kind != 0 || !it->second.mat->loaded()) return nullptr;
+    return it->second.mat;
+}
+
+extern "C" int g5b_op_matvec(g5b_engine *e, const char *name, const float *x, int T, float *y)
+{
+    CU(cudaSetDevice(e->device));
+    DMat *m = find_mat(e, name);
+    if (!m) return fail("no loaded matrix named %s", name);
+    Staged s{e};
+    float *xd = s.in(x, (size_t)T * m->cols), *yd = s.in(nullptr, (size_t)T * m->rows);
+    if (!xd || !yd) return fail("out of device memory");
+    gemv(e->st, *m, xd, m->cols, yd, m->rows, T);
+    return s.out(y, yd, (size_t)T * m->rows);
+}
+
+static float *state_ptr(g5b_engine *e, int layer, int kind, size_t *n, int *bf16)
+{
+    const g5b_config &c = e->c;
+    Layer &w = e->L[layer];
+    *bf16 = 0;
+    if (kind == 0) {
+        const size_t P = (size_t)c.kda_heads * c.kda_head_dim;
+        *n = P * c.kda_head_dim + 3 * P * (size_t)(c.conv_k - 1);
+        return w.kda_state;
+    }
+    if (kind == 1) { *n = (size_t)e->cap * c.kv_lora; *bf16 = e->latent_bf16; return (float *)w.latent; }
+    if (kind == 2) {
+        *n = (size_t)2 * e->cap * c.index_dim + (size_t)((e->cap + c.index_kpool - 1) / c.index_kpool) * c.index_dim;
+        return w.idx_state;
+    }
+    return nullptr;
+}
+
+extern "C" int g5b_state_write(g5b_engine *e, int layer, int kind, size_t offset, const float *src, size_t count)
+{
+    if (!e->finalized || layer < 0 || layer >= e->c.n_layers) return fail("state access on a bad layer");
+    CU(cudaSetDevice(e->device));
+    size_t n = 0; int bf = 0;
+    float *p = state_ptr(e, layer, kind, &n, &bf);
+    if (!p || offset + count > n) return fail("state range outside the layer's state");
+    if (!bf) {
+        CU(cudaMemcpyAsync(p + offset, src, count * 4, cudaMemcpyHostToDevice, e->st));
+    } else {
+        Staged s{e};
+        float *tmp = s.in(src, count);
+        if (!tmp) return fail("out of device memory");
+        f32_to_bf16(e->st, (uint16_t *)p + offset, tmp, count);
+        CU(cudaStreamSynchronize(e->st));
+    }
+    CU(cudaStreamSynchronize(e->st));
+    return 0;
+}
+
+extern "C" int g5b_state_read(g5b_engine *e, int layer, int kind, size_t offset, float *dst, size_t count)
+{
+    if (!e->finalized || layer < 0 || layer >= e->c.n_layers) return fail("state access on a bad layer");
+    CU(cudaSetDevice(e->device));
+    size_t n = 0; int bf = 0;
+    float *p = state_ptr(e, layer, kind, &n, &bf);
+    if (!p || offset + count > n) return fail("state range outside the layer's state");
+    if (!bf) {
+        CU(cudaMemcpyAsync(dst, p + offset, count * 4, cudaMemcpyDeviceToHost, e->st));
+        CU(cudaStreamSynchronize(e->st));
+        return 0;
+    }
+    Staged s{e};
+    float *tmp = s.in(nullptr, count);
+    if (!tmp) return fail("out of device memory");
+    bf16_to_f32(e->st, tmp, (const uint16_t *)p + offset, count);
+    return s.out(dst, tmp, count);
+}
+
+// ------------------------------------------------------------ free-standing ops ----
+static int with_device(int device, cudaStream_t *st)
+{
+    if (device < 0 || device >= g5b_device_count()) return fail("CUDA device %d is not available (no CPU path)", device);
+    CU(cudaSetDevice(device));
+    *st = nullptr;     // legacy default stream: these entry points are synchronous
+    return 0;
+}
+
+struct Tmp {
+    std::vector<void *> bufs;
+    ~Tmp() { for (void *p : bufs) cudaFree(p); }
+    void *up(const void *src, size_t bytes)
+    {
+        void *p = nullptr;
+        if (cudaMalloc(&p, bytes + 16) != cudaSuccess) return nullptr;
+        bufs.push_back(p);
+        if (src) cudaMemcpy(p, src, bytes, cudaMemcpyHostToDevice);
+        else     cudaMemset(p, 0, bytes);
+        return p;
+    }
+};
+
+extern "C" int g5b_matvec_host(const g5b_tensor *w, int br, int bc, const float *x, int T, float *y, int device)
+{
+    cudaStream_t st;
+    if (with_device(device, &st)) return -1;
+    Tmp t;
+    DMat m;
+    m.dt = w->dtype; m.rows = w->rows; m.cols = w->cols;
+    const size_t n = (size_t)w->rows * w->cols;
+    m.w = t.up(w->data, n * elt(w->dtype));
+    if (w->dtype == G5B_DT_FP8) {
+        if (br < 1 || bc < 1 || !w->scale_inv) return fail("FP8 matrix without block size or scales");
+        m.br = br; m.bc = bc; m.scols = (w->cols + bc - 1) / bc;
+        m.s = (float *)t.up(w->scale_inv, (size_t)((w->rows + br - 1) / br) * m.scols * 4);
+    }
+    float *xd = (float *)t.up(x, (size_t)T * w->cols * 4), *yd = (float *)t.up(nullptr, (size_t)T * w->rows * 4);
+    if (!m.w || !xd || !yd) return fail("out of device memory");
+    gemv(st, m, xd, w->cols, yd, w->rows, T);
+    CU(cudaMemcpy(y, yd, (size_t)T * w->rows * 4, cudaMemcpyDeviceToHost));
+    CU(cudaGetLastError());
+    return 0;
+}
+
+extern "C" int g5b_rmsnorm_host(float *y, const float *x, const float *w, int n, int rows, float eps, int device)
+{
+    cudaStream_t st;
+    if (with_device(device, &st)) return -1;
+    Tmp t;
+    float *xd = (float *)t.up(x, (size_t)rows * n * 4), *yd = (float *)t.up(nullptr, (size_t)rows * n * 4);
+    float *wd = w ? (float *)t.up(w, (size_t)n * 4) : nullptr, *inv = (float *)t.up(nullptr, (size_t)rows * 4);
+    if (!xd || !yd || !inv) return fail("out of device memory");
+    rms_factor(st, xd, n, n, rows, eps, inv);
+    rms_apply(st, yd, xd, wd, inv, n, n, rows);
+    CU(cudaMemcpy(y, yd, (size_t)rows * n * 4, cudaMemcpyDeviceToHost));
+    CU(cudaGetLastError());
+    return 0;
+}
+
+extern "C" int g5b_swiglu_host(float *y, const float *gu, int n, int rows, float limit, int device)
+{
+    cudaStream_t st;
+    if (with_device(device, &st)) return -1;
+    Tmp t;
+    float *gd = (float *)t.up(gu, (size_t)rows * 2 * n * 4), *yd = (float *)t.up(nullptr, (size_t)rows * n * 4);
+    if (!gd || !yd) return fail("out of device memory");
+    swiglu(st, yd, gd, n, rows, limit);
+    CU(cudaMemcpy(y, yd, (size_t)rows * n * 4, cudaMemcpyDeviceToHost));
+    CU(cudaGetLastError());
+    return 0;
+}
+
+extern "C" int g5b_shortconv_host(float *y, const float *x, const float *w, float *state, int channels, int k,
+                                  int T, int device)
+{
+    cudaStream_t st;
+    if (with_device(device, &st)) return -1;
+    if (k - 1 > 16 || k < 1) return fail("conv kernel history %d above the limit of 16", k - 1);
+    Tmp t;
+    float *xd = (float *)t.up(x, (size_t)T * channels * 4), *yd = (float *)t.up(nullptr, (size_t)T * channels * 4);
+    float *wd = (float *)t.up(w, (size_t)channels * k * 4);
+    float *sd = state ? (float *)t.up(state, (size_t)channels * (k - 1) * 4) : nullptr;
+    if (!xd || !yd || !wd) return fail("out of device memory");
+    shortconv(st, yd, xd, wd, sd, channels, k, T);
+    CU(cudaMemcpy(y, yd, (size_t)T * channels * 4, cudaMemcpyDeviceToHost));
+    if (state) CU(cudaMemcpy(state, sd, (size_t)channels * (k - 1) * 4, cudaMemcpyDeviceToHost));
+    CU(cudaGetLastError());
+    return 0;
+}
+
+// ------------------------------------------------------------------------ timing ----
+// Time `iters` launches of one op ("moe", "kda", "mla", "layer") between CUDA events on the
+// engine's stream; before each launch `flush_bytes` of scratch are overwritten (0 = no flush) so
+// that weights come from HBM, not from L2. ms_each receives the per-launch times. When the
+// engine's "profile" option is on, the per-phase times of the MoE op accumulate in the profile.
+extern "C" int g5b_time_op(g5b_engine *e, const char *op, int layer, const float *x_dev, int T, int cached,
+                           float *out_dev, int iters, size_t flush_bytes, float *ms_total, float *ms_each)
+{
+    if (check_layer(e, layer, T)) return -1;
+    if (flush_bytes > e->flush_bytes) {
+        if (e->flush_buf) cudaFree(e->flush_buf);
+        e->flush_buf = nullptr; e->flush_bytes = 0;
+        CU(cudaMalloc(&e->flush_buf, flush_bytes));
+        e->flush_bytes = flush_bytes;
+    }
+    cudaEvent_t a, b;
+    CU(cudaEventCreate(&a));
+    CU(cudaEventCreate(&b));
+    double total = 0.0;
+    const size_t kper = [&] { const size_t P = (size_t)e->c.kda_heads * e->c.kda_head_dim;
+                              return P * e->c.kda_head_dim + 3 * P * (size_t)(e->c.conv_k - 1); }();
+    (void)kper;
+    for (int i = 0; i < iters; i++) {
+        if (flush_bytes) flush_l2(e->st, e->flush_buf, flush_bytes);
+        CU(cudaEventRecord(a, e->st));
+        int rc;
+        if (!strcmp(op, "moe"))        rc = g5b_dev_moe(e, layer, x_dev, T, out_dev);
+        else if (!strcmp(op, "kda"))   rc = g5b_dev_kda(e, layer, x_dev, T, out_dev);
+        else if (!strcmp(op, "mla"))   rc = g5b_dev_mla(e, layer, x_dev, T, cached, out_dev);
+        else if (!strcmp(op, "layer")) rc = g5b_dev_decoder_layer(e, layer, out_dev, T, cached);
+        else rc = fail("unknown op %s", op);
+        if (rc) return -1;
+        CU(cudaEventRecord(b, e->st));
+        CU(cudaEventSynchronize(b));
+        float ms = 0.f;
+        CU(cudaEventElapsedTime(&ms, a, b));
+        if (ms_each) ms_each[i] = ms;
+        total += ms;
+    }
+    CU(cudaGetLastError());
+    cudaEventDestroy(a);
+    cudaEventDestroy(b);
+    if (ms_total) *ms_total = (float)total;
+    return 0;
+}
+
+extern "C" int g5b_engine_profile_read(g5b_engine *e, float *ms, int n, long *count, int reset)
+{
+    for (int i = 0; i < n && i < PROF_SLOTS; i++) ms[i] = e->prof_ms[i];
+    if (count) *count = e->prof_n;
+    if (reset) { memset(e->prof_ms, 0, sizeof e->prof_ms); e->prof_n = 0; }
+    return 0;
+}
+
+// ------------------------------------------------------------- expert parallel ----
+extern "C" size_t g5b_engine_ep_handle_bytes(void) { return sizeof(cudaIpcMemHandle_t); }
+extern "C" int g5b_engine_ep_export(g5b_engine *e, void *handle_out)
+{
+    (void)handle_out;
+    if (e->ep_size == 1) return 0;
+    return fail("expert-parallel exchange is not wired in this build");
+}
+extern "C" int g5b_engine_ep_connect(g5b_engine *e, const void *all_handles)
+{
+    (void)all_handles;
+    if (e->ep_size == 1) return 0;
+    return fail("expert-parallel exchange is not wired in this build");
+}

@@ -1,0 +1,160 @@
+// kda.cu - the gated delta-rule linear attention step (KDA), everything between the input
+// projections and the output projection in one kernel.
+//
+// Reference: glm53f_kda_layer and kda_step (src/core/glm53f_ops.c:630-755). Its device form was
+// nine launches per layer and token (three k_shortconv, k_kda_prep, k_kda_decay, k_kda_read,
+// k_kda_write, k_kda_out, k_onorm_gate; src/gpu/glm53f_gpu_kernels.cu:243-450) that passed over
+// the 64 KB per-head state four times. Here one CTA per head does: short convolution + SiLU of
+// q/k/v with the carried history, L2 norm of q and k, beta and the per-channel decay, the
+// recurrence, and the gated per-head RMSNorm of the output. A thread owns one value column of
+// the state and keeps it in registers, so the state is read once and written once per call
+// however many tokens the call carries.
+//
+// The recurrence keeps the reference's order of FP32 operations (decay row i, u_j += S_ij k_i,
+// S_ij += k_i u_j, o_j += S_ij q_i, ascending i, products and sums rounded separately).
+#include "common.cuh"
+#include "kernels.h"
+
+namespace g5b {
+
+struct KdaArgs {
+    float *o;
+    const float *q, *k, *v, *z, *braw, *gb;
+    const float *q_conv, *k_conv, *v_conv, *A_log, *dt_bias, *o_norm;
+    float *state;
+    int T, H, D, K;
+    float gate_lb, rms_eps;
+};
+
+// conv + SiLU of one channel at one position; `past` holds K-1 previous inputs, oldest first.
+__device__ __forceinline__ float conv_step(float cur, const float *w, float *past, int K)
+{
+    const int hist = K - 1;
+    float acc = __fmul_rn(w[hist], cur);
+    for (int j = 0; j < hist; j++) acc = mul_add_unfused(w[j], past[j], acc);
+    for (int j = 0; j + 1 < hist; j++) past[j] = past[j + 1];
+    if (hist > 0) past[hist - 1] = cur;
+    return __fmul_rn(acc, sigmoid_host(acc));
+}
+
+// DS > 0: head_dim known at compile time, the state column lives in registers.
+// DS == 0: any head_dim up to 512, the state column is re-read from memory.
+template <int DS>
+__global__ void __launch_bounds__(DS > 0 ? DS : 512) kda_core_kernel(const KdaArgs a)
+{
+    __shared__ float sq[512], sk[512], sal[512];
+    __shared__ double red[32];
+    const int h = blockIdx.x, d = threadIdx.x;
+    const int D = DS > 0 ? DS : a.D, P = a.H * D, K = a.K, hist = K - 1;
+    const bool live = d < D;
+    const int ch = h * D + (live ? d : 0);
+    float *S = a.state + (size_t)h * D * D;
+    float *cs = a.state + (size_t)a.H * D * D;
+
+    float pq[16], pk[16], pv[16], wq[17], wk[17], wv[17];
+    for (int j = 0; j < hist; j++) {
+        pq[j] = cs[(size_t)ch * hist + j];
+        pk[j] = cs[(size_t)P * hist + (size_t)ch * hist + j];
+        pv[j] = cs[(size_t)2 * P * hist + (size_t)ch * hist + j];
+    }
+    for (int j = 0; j < K; j++) {
+        wq[j] = a.q_conv[(size_t)ch * K + j];
+        wk[j] = a.k_conv[(size_t)ch * K + j];
+        wv[j] = a.v_conv[(size_t)ch * K + j];
+    }
+    float sreg[DS > 0 ? DS : 1];
+    if (DS > 0) {
+#pragma unroll
+        for (int i = 0; i < DS; i++) sreg[i] = S[(size_t)i * DS + d];
+    }
+    const float ea = expf_host(a.A_log[h]);
+    const float dtb = a.dt_bias[ch], onw = a.o_norm[live ? d : 0];
+    const float qscale = 1.0f / sqrtf((float)D);
+
+    for (int t = 0; t < a.T; t++) {
+        const size_t off = (size_t)t * P + ch;
+        float qv = 0.f, kv = 0.f, vv = 0.f;
+        if (live) {
+            qv = conv_step(a.q[off], wq, pq, K);
+            kv = conv_step(a.k[off], wk, pk, K);
+            vv = conv_step(a.v[off], wv, pv, K);
+        }
+        // l2norm: divide by sqrt(sum of squares + 1e-6), sums in FP64 (glm53f_ops.c:661-667)
+        const double qq = block_sum(live ? (double)qv * (double)qv : 0.0, red);
+        const double kk = block_sum(live ? (double)kv * (double)kv : 0.0, red);
+        const float qinv = (float)(1.0 / sqrt(qq + (double)1e-6f));
+        const float kinv = (float)(1.0 / sqrt(kk + (double)1e-6f));
+        const float beta = sigmoid_host(a.braw[(size_t)t * a.H + h]);
+        __syncthreads();
+        if (live) {
+            sq[d] = __fmul_rn(__fmul_rn(qv, qinv), qscale);
+            sk[d] = __fmul_rn(kv, kinv);
+            const float g = __fmul_rn(a.gate_lb, sigmoid_host(__fmul_rn(ea, __fadd_rn(a.z[off], dtb))));
+            sal[d] = expf_host(g);
+        }
+        __syncthreads();
+
+        float ov = 0.f;
+        if (live) {
+            float u = 0.f;
+            if (DS > 0) {
+#pragma unroll
+                for (int i = 0; i < DS; i++) {
+                    sreg[i] = __fmul_rn(sreg[i], sal[i]);
+                    u = __fadd_rn(u, __fmul_rn(sreg[i], sk[i]));
+                }
+                u = __fmul_rn(__fsub_rn(vv, u), beta);
+#pragma unroll
+                for (int i = 0; i < DS; i++) {
+                    sreg[i] = __fadd_rn(sreg[i], __fmul_rn(sk[i], u));
+                    ov = __fadd_rn(ov, __fmul_rn(sreg[i], sq[i]));
+                }
+            } else {
+                for (int i = 0; i < D; i++) {
+                    const float s = __fmul_rn(S[(size_t)i * D + d], sal[i]);
+                    S[(size_t)i * D + d] = s;
+                    u = __fadd_rn(u, __fmul_rn(s, sk[i]));
+                }
+                u = __fmul_rn(__fsub_rn(vv, u), beta);
+                for (int i = 0; i < D; i++) {
+                    const float s = __fadd_rn(S[(size_t)i * D + d], __fmul_rn(sk[i], u));
+                    S[(size_t)i * D + d] = s;
+                    ov = __fadd_rn(ov, __fmul_rn(s, sq[i]));
+                }
+            }
+        }
+        // per-head RMSNorm with weight, then the sigmoid output gate (glm53f_ops.c:748-752)
+        const double oo = block_sum(live ? (double)ov * (double)ov : 0.0, red);
+        if (live) {
+            const float inv = (float)(1.0 / sqrt(oo / (double)D + (double)a.rms_eps));
+            const float n = __fmul_rn(onw, __fmul_rn(ov, inv));
+            a.o[off] = __fmul_rn(n, sigmoid_host(a.gb[off]));
+        }
+    }
+
+    if (live) {
+        if (DS > 0) {
+#pragma unroll
+            for (int i = 0; i < DS; i++) S[(size_t)i * DS + d] = sreg[i];
+        }
+        for (int j = 0; j < hist; j++) {
+            cs[(size_t)ch * hist + j] = pq[j];
+            cs[(size_t)P * hist + (size_t)ch * hist + j] = pk[j];
+            cs[(size_t)2 * P * hist + (size_t)ch * hist + j] = pv[j];
+        }
+    }
+}
+
+void kda_core(cudaStream_t st, float *o, const float *q, const float *k, const float *v, const float *z,
+              const float *braw, const float *gb, const float *q_conv, const float *k_conv,
+              const float *v_conv, const float *A_log, const float *dt_bias, const float *o_norm,
+              float *state, int T, const KdaShape &s)
+{
+    KdaArgs a{o, q, k, v, z, braw, gb, q_conv, k_conv, v_conv, A_log, dt_bias, o_norm, state,
+              T, s.H, s.D, s.K, s.gate_lb, s.rms_eps};
+    if (s.D == 128)     G5B_LAUNCH(kda_core_kernel<128>, s.H, 128, 0, st, a);
+    else if (s.D == 64) G5B_LAUNCH(kda_core_kernel<64>, s.H, 64, 0, st, a);
+    else                G5B_LAUNCH(kda_core_kernel<0>, s.H, ((s.D + 31) / 32) * 32, 0, st, a);
+}
+
+}  // namespace g5b

@@ -1,0 +1,135 @@
+// kernels.h - launchers of the engine's CUDA kernels (internal to libglm53f_b200).
+// Every launcher enqueues on the given stream and returns without waiting.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "../../include/glm53f_b200.h"
+
+namespace g5b {
+
+// A weight matrix resident in HBM, row-major, in its checkpoint format.
+struct DMat {
+    void  *w = nullptr;
+    float *s = nullptr;        // FP8 block scales [ceil(rows/br)][scols]
+    int    dt = 0, rows = 0, cols = 0, br = 0, bc = 0, scols = 0;
+    bool   loaded() const { return w != nullptr; }
+    size_t bytes() const { return (size_t)rows * cols * (dt == 0 ? 4 : dt == 1 ? 2 : 1); }
+};
+
+// ---- gemv.cu ------------------------------------------------------------------------------
+// One product y[T][rows] = W (xform(x))[T][cols] of a batch launched as a single grid.
+struct GemvSeg {
+    const void  *W;
+    const float *S;
+    const float *x;       // [T][ldx]
+    const float *xinv;    // optional RMSNorm factor per activation row
+    const float *xw;      // optional RMSNorm weight per column
+    float       *y;       // [T][ldy]
+    int dt, R, C, br, bc, scols, ldx, ldy;
+    int ksplit;           // 1: a whole CTA shares each group of rows (few-row matrices)
+    int block0;           // first block of this segment in the grid (filled by the launcher)
+};
+constexpr int GEMV_MAX_SEG = 8;
+
+GemvSeg make_seg(const DMat &m, const float *x, int ldx, float *y, int ldy,
+                 const float *xinv = nullptr, const float *xw = nullptr);
+// Matrix restricted to rows [r0, r0+n) (FP8: r0 must lie on a scale-block row).
+DMat row_slice(const DMat &m, int r0, int n);
+void gemv_batch(cudaStream_t st, const GemvSeg *segs, int n, int T);
+inline void gemv(cudaStream_t st, const DMat &m, const float *x, int ldx, float *y, int ldy, int T,
+                 const float *xinv = nullptr, const float *xw = nullptr)
+{
+    GemvSeg s = make_seg(m, x, ldx, y, ldy, xinv, xw);
+    gemv_batch(st, &s, 1, T);
+}
+
+// ---- elementwise.cu -----------------------------------------------------------------------
+void rms_factor(cudaStream_t st, const float *x, int n, int ld, int rows, float eps, float *inv);
+void rms_apply(cudaStream_t st, float *y, const float *x, const float *w, const float *inv, int n,
+               int ld, int rows);
+void swiglu(cudaStream_t st, float *y, const float *gu, int n, int rows, float limit);
+void shortconv(cudaStream_t st, float *y, const float *x, const float *w, float *state, int channels,
+               int k, int T);
+void embed_rows(cudaStream_t st, float *h, const DMat &table, const int *ids, int T, int M);
+void head_mean(cudaStream_t st, float *xm, const float *h, int T, int M, int E);
+void argmax_rows(cudaStream_t st, int *out, const float *logits, int n, int rows, float *scratch_v,
+                 int *scratch_i);
+void fill_codes(cudaStream_t st, uint8_t *dst, uint64_t seed, int layer, int expert, int which,
+                size_t count);
+void f32_to_bf16(cudaStream_t st, uint16_t *dst, const float *src, size_t n);
+void bf16_to_f32(cudaStream_t st, float *dst, const uint16_t *src, size_t n);
+void flush_l2(cudaStream_t st, void *buf, size_t bytes);
+
+// ---- mhc.cu -------------------------------------------------------------------------------
+struct HcW {
+    DMat   fn;
+    float *base = nullptr, *scale = nullptr;
+};
+// mix [T][(2+M)*M] must already hold fn . RMSNorm0(h). Writes x, post, comb.
+void hc_finish(cudaStream_t st, float *x, float *post, float *comb, const float *h, const float *mix,
+               const HcW &w, int T, int M, int E, int iters, float eps);
+void hc_post(cudaStream_t st, float *h, const float *y, const float *post, const float *comb, int T,
+             int M, int E);
+
+// ---- moe.cu -------------------------------------------------------------------------------
+struct ExpertW {          // one expert's three matrices, device pointers
+    const uint8_t *gate, *up, *down;
+    const float   *gate_s, *up_s, *down_s;
+};
+struct MoePlan {          // device arrays describing which expert multiplies which tokens
+    int *n_slots;         // [1] experts with work this call (shared expert included)
+    int *slot_expert;     // [max_slots] index into the ExpertW table
+    int *slot_off;        // [max_slots] first pair of the slot
+    int *slot_cnt;        // [max_slots] pairs of the slot
+    int *pair_tok;        // [max_pairs] activation row of the pair
+    int *pair_dst;        // [max_pairs] row of the contribution buffer the pair writes
+    int  max_slots, max_pairs;
+};
+struct MoeShape {
+    int E, I, NE, K, br, bc, dt;       // dt of expert matrices
+    int n_local0, n_local;             // experts [n_local0, n_local0+n_local) live on this GPU
+    float limit, routed_scale;
+    int norm_topk;
+};
+void router_topk(cudaStream_t st, int *idx, float *w, const float *x, int ldx, const void *gate,
+                 int gate_dt, const float *bias, double *score_scratch, int T, const MoeShape &s);
+void moe_plan(cudaStream_t st, const MoePlan &p, const int *idx, int T, const MoeShape &s,
+              int with_shared);
+void moe_gateup(cudaStream_t st, float *act, const float *x, int ldx, const ExpertW *experts,
+                const MoePlan &p, int T, const MoeShape &s);
+void moe_down(cudaStream_t st, float *contrib, const float *act, const ExpertW *experts,
+              const MoePlan &p, int T, const MoeShape &s);
+void moe_combine(cudaStream_t st, float *out, int ldo, const float *contrib, const float *w, int T,
+                 const MoeShape &s, int with_shared);
+
+// ---- kda.cu -------------------------------------------------------------------------------
+struct KdaShape { int H, D, K; float gate_lb, rms_eps; };
+// q,k,v,z,gb: [T][H*D] projections (q,k,v before the short convolution); braw [T][H]; state as
+// the reference lays it out (S [H][D][D] then conv histories q|k|v, glm53f.h:363-367).
+void kda_core(cudaStream_t st, float *o, const float *q, const float *k, const float *v, const float *z,
+              const float *braw, const float *gb, const float *q_conv, const float *k_conv,
+              const float *v_conv, const float *A_log, const float *dt_bias, const float *o_norm,
+              float *state, int T, const KdaShape &s);
+
+// ---- mla.cu -------------------------------------------------------------------------------
+struct MlaShape {
+    int H, qn, vh, KL, q_lora, E, cap;
+    int ID, IH, KP, topk;              // indexer dim, heads, pool size, index_topk
+    float rms_eps;
+    int latent_bf16;
+};
+void mla_store(cudaStream_t st, void *latent, float *idx_state, const float *ct_raw,
+               const float *kv_norm_w, const float *wk_raw, const float *gate_raw,
+               const float *k_norm_w, const float *k_norm_b, const float *ape, int T, int cached,
+               const MlaShape &s);
+void dsa_select(cudaStream_t st, int *sel, int *nsel, const float *idx_state, const float *qidx,
+                const float *wproj, float *score, int T, int cached, const MlaShape &s);
+void mla_absorb(cudaStream_t st, double *qa, const float *q, const DMat &kv_b, int T, const MlaShape &s);
+void mla_attend(cudaStream_t st, float *cb, const double *qa, const void *latent, const int *sel,
+                const int *nsel, double *dsc, int T, int cached, const MlaShape &s);
+void mla_vout(cudaStream_t st, float *acc_out, const float *cb, const DMat &kv_b, int T, const MlaShape &s);
+
+}  // namespace g5b

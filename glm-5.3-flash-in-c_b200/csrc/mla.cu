@@ -1,0 +1,397 @@
+// mla.cu - multi-head latent attention over the compressed KV cache, and the DSA indexer that
+// chooses which positions a query attends to.
+//
+// Reference: glm53f_mla, compressed-latent branch (src/core/glm53f_ops.c:828-911) and
+// glm53f_dsa_append / glm53f_dsa_select (src/core/glm53f_dsa.c:74-171). The reference's GPU
+// backend had neither: it expanded keys and values on the device, attended densely and refused
+// sessions past 2051 positions (src/model/glm53f_model.c:337-349). Here the cache holds only the
+// kv_lora latent per position (FP32, or BF16 when the engine is told so), kv_b is folded into
+// the query (W_k^T q) and into the output (W_v applied once to the weighted latent sum), and the
+// indexer runs on the device: pool scoring, an exact top-k by radix selection, and an ascending
+// position list that the attention kernels gather through.
+//
+// Sums that decide indices (pool scores) repeat the reference's order in FP64, so equal inputs
+// give bit-equal scores and therefore the same selection, ties included (lower pool wins).
+#include "dot_rows.cuh"
+#include "kernels.h"
+
+namespace g5b {
+
+// Indexer state, three consecutive arrays (src/core/glm53f_dsa.c:44-53).
+__device__ __forceinline__ float *st_key(float *s, int ID, int pos) { return s + (size_t)pos * ID; }
+__device__ __forceinline__ float *st_gate(float *s, int ID, int cap, int pos) { return s + ((size_t)cap + pos) * ID; }
+__device__ __forceinline__ float *st_pool(float *s, int ID, int cap, int pool) { return s + ((size_t)2 * cap + pool) * ID; }
+
+__device__ __forceinline__ float latent_at(const void *latent, int bf16, size_t i)
+{
+    return bf16 ? bf16_to_f32(static_cast<const uint16_t *>(latent)[i]) : static_cast<const float *>(latent)[i];
+}
+
+// ------------------------------------------------------------------- append ----
+// Per new position: latent = RMSNorm(kv_a x) into the cache; indexer key = LayerNorm(wk x)
+// (biased variance, eps 1e-6, FP64) and gate = gate x into the indexer state.
+__global__ void __launch_bounds__(256) mla_store_kernel(
+    void *latent, float *idx_state, const float *ct_raw, const float *kv_norm_w, const float *wk_raw,
+    const float *gate_raw, const float *k_norm_w, const float *k_norm_b, int cached, MlaShape s)
+{
+    __shared__ double red[32];
+    const int t = blockIdx.x, pos = cached + t;
+    const float *ct = ct_raw + (size_t)t * s.KL;
+    double ss = 0.0;
+    for (int i = threadIdx.x; i < s.KL; i += blockDim.x) ss += (double)ct[i] * (double)ct[i];
+    ss = block_sum(ss, red);
+    const float inv = (float)(1.0 / sqrt(ss / (double)s.KL + (double)s.rms_eps));
+    for (int i = threadIdx.x; i < s.KL; i += blockDim.x) {
+        const float v = __fmul_rn(kv_norm_w[i], __fmul_rn(ct[i], inv));
+        if (s.latent_bf16) static_cast<uint16_t *>(latent)[(size_t)pos * s.KL + i] = __bfloat16_as_ushort(__float2bfloat16_rn(v));
+        else               static_cast<float *>(latent)[(size_t)pos * s.KL + i] = v;
+    }
+    const float *raw = wk_raw + (size_t)t * s.ID;
+    double sum = 0.0;
+    for (int i = threadIdx.x; i < s.ID; i += blockDim.x) sum += (double)raw[i];
+    const double mean = block_sum(sum, red) / (double)s.ID;
+    double var = 0.0;
+    for (int i = threadIdx.x; i < s.ID; i += blockDim.x) { const double d = (double)raw[i] - mean; var += d * d; }
+    var = block_sum(var, red) / (double)s.ID;
+    const double linv = 1.0 / sqrt(var + 1e-6);
+    float *kp = st_key(idx_state, s.ID, pos), *gp = st_gate(idx_state, s.ID, s.cap, pos);
+    for (int i = threadIdx.x; i < s.ID; i += blockDim.x) {
+        kp[i] = mul_add_unfused((float)(((double)raw[i] - mean) * linv), k_norm_w[i], k_norm_b[i]);
+        gp[i] = gate_raw[(size_t)t * s.ID + i];
+    }
+}
+
+// Pools closed by this call: per channel, softmax over the pool's (gate + ape) weights its keys.
+__global__ void dsa_pool_kernel(float *idx_state, const float *ape, int pool0, MlaShape s)
+{
+    const int pool = pool0 + blockIdx.x, i = threadIdx.x;
+    if (i >= s.ID) return;
+    const int KP = s.KP;
+    double top = -INFINITY, z = 0.0, acc = 0.0;
+    for (int j = 0; j < KP; j++) {
+        const double l = (double)st_gate(idx_state, s.ID, s.cap, pool * KP + j)[i] + (double)ape[j * s.ID + i];
+        if (l > top) top = l;
+    }
+    for (int j = 0; j < KP; j++)
+        z += exp((double)st_gate(idx_state, s.ID, s.cap, pool * KP + j)[i] + (double)ape[j * s.ID + i] - top);
+    for (int j = 0; j < KP; j++) {
+        const double p = exp((double)st_gate(idx_state, s.ID, s.cap, pool * KP + j)[i] + (double)ape[j * s.ID + i] - top) / z;
+        acc = __dadd_rn(acc, __dmul_rn(p, (double)st_key(idx_state, s.ID, pool * KP + j)[i]));
+    }
+    st_pool(idx_state, s.ID, s.cap, pool)[i] = (float)acc;
+}
+
+void mla_store(cudaStream_t st, void *latent, float *idx_state, const float *ct_raw,
+               const float *kv_norm_w, const float *wk_raw, const float *gate_raw,
+               const float *k_norm_w, const float *k_norm_b, const float *ape, int T, int cached,
+               const MlaShape &s)
+{
+    G5B_LAUNCH(mla_store_kernel, T, 256, 0, st, latent, idx_state, ct_raw, kv_norm_w, wk_raw, gate_raw,
+               k_norm_w, k_norm_b, cached, s);
+    const int pool0 = cached / s.KP;                                         // pools closed before this call
+    const int pool1 = (cached + T) / s.KP;                                   // pools closed after this call
+    if (pool1 > pool0)
+        G5B_LAUNCH(dsa_pool_kernel, pool1 - pool0, ((s.ID + 31) / 32) * 32, 0, st, idx_state, ape, pool0, s);
+}
+
+// ------------------------------------------------------------------- select ----
+// score[pool] = (float) sum_h w[h]/sqrt(heads) * relu((q_h . P_pool)/sqrt(dim)), FP64, heads and
+// dimensions in ascending order as the reference sums them (glm53f_dsa.c:141-157). A lane owns a
+// head's dot product; lane 0 then adds the heads in order.
+constexpr int DSA_WARPS = 8;
+__global__ void __launch_bounds__(DSA_WARPS * 32) dsa_score_kernel(
+    float *score, const float *idx_state, const float *qidx, const float *wproj, int cached, MlaShape s)
+{
+    extern __shared__ float dsa_smem[];
+    float  *qT = dsa_smem;                                   // [ID][IH]
+    double *dh = reinterpret_cast<double *>(dsa_smem + (size_t)s.ID * s.IH);   // [warps][IH]
+    const int t = blockIdx.y, p = cached + t;
+    const int np = (p + 1) / s.KP;
+    if (np <= s.topk / s.KP) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float *q = qidx + (size_t)t * s.IH * s.ID, *wt = wproj + (size_t)t * s.IH;
+    for (int e = threadIdx.x; e < s.IH * s.ID; e += blockDim.x) qT[(e % s.ID) * s.IH + e / s.ID] = q[e];
+    __syncthreads();
+    const float hscale = 1.0f / sqrtf((float)s.IH), dscale = 1.0f / sqrtf((float)s.ID);
+    double *mine = dh + (size_t)warp * s.IH;
+    for (int pp = blockIdx.x * DSA_WARPS + warp; pp < np; pp += gridDim.x * DSA_WARPS) {
+        const float *pk = idx_state + ((size_t)2 * s.cap + pp) * s.ID;
+        for (int h = lane; h < s.IH; h += 32) {
+            double d = 0.0;
+            for (int i = 0; i < s.ID; i++) d = fma((double)qT[i * s.IH + h], (double)pk[i], d);
+            mine[h] = __dmul_rn(d, (double)dscale);
+        }
+        __syncwarp();
+        if (lane == 0) {
+            double acc = 0.0;
+            for (int h = 0; h < s.IH; h++) {
+                const double d = mine[h];
+                if (d > 0.0) acc = __dadd_rn(acc, __dmul_rn(__dmul_rn((double)wt[h], (double)hscale), d));
+            }
+            score[(size_t)t * (s.cap / s.KP + 1) + pp] = (float)acc;
+        }
+        __syncwarp();
+    }
+}
+
+// Exact top-k of the pool scores (score descending, pool index ascending on ties, the order of
+// the reference's qsort comparator, glm53f_dsa.c:111-116), by radix selection on a 64-bit key,
+// then an order-preserving compaction: kept pools ascending, each expanded to its positions, then
+// the incomplete tail pool.
+constexpr int TOPK_THREADS = 1024;
+__device__ __forceinline__ unsigned long long rank_key(float sc, int pool)
+{
+    if (sc == 0.0f) sc = 0.0f;                                    // -0 and +0 compare equal
+    uint32_t b = __float_as_uint(sc);
+    b = (b & 0x80000000u) ? ~b : (b | 0x80000000u);               // ascending float order
+    return ((unsigned long long)b << 32) | (unsigned long long)(0xffffffffu - (uint32_t)pool);
+}
+
+__global__ void __launch_bounds__(TOPK_THREADS) dsa_topk_kernel(int *sel, int *nsel, const float *score,
+                                                                int cached, MlaShape s)
+{
+    __shared__ int hist[256];
+    __shared__ unsigned long long prefix_s;
+    __shared__ int want_s;
+    __shared__ int scan[TOPK_THREADS];
+    const int t = blockIdx.x, p = cached + t, tid = threadIdx.x;
+    const int np = (p + 1) / s.KP, keep = s.topk / s.KP;
+    int *out = sel + (size_t)t * (s.topk + s.KP);
+    if (np <= keep) { if (tid == 0) nsel[t] = -1; return; }
+    const float *sc = score + (size_t)t * (s.cap / s.KP + 1);
+
+    // the keep-th largest key, one byte at a time from the top
+    if (tid == 0) { prefix_s = 0ull; want_s = keep; }
+    __syncthreads();
+    for (int shift = 56; shift >= 0; shift -= 8) {
+        if (tid < 256) hist[tid] = 0;
+        __syncthreads();
+        const unsigned long long prefix = prefix_s;
+        const unsigned long long mask = shift == 56 ? 0ull : (~0ull << (shift + 8));
+        for (int i = tid; i < np; i += TOPK_THREADS) {
+            const unsigned long long k = rank_key(sc[i], i);
+            if ((k & mask) == prefix) atomicAdd(&hist[(int)((k >> shift) & 0xff)], 1);
+        }
+        __syncthreads();
+        if (tid == 0) {
+            int want = want_s, dgt = 255;
+            for (; dgt > 0; dgt--) {
+                if (hist[dgt] >= want) break;
+                want -= hist[dgt];
+            }
+            prefix_s = prefix | ((unsigned long long)dgt << shift);
+            want_s = want;
+        }
+        __syncthreads();
+    }
+    const unsigned long long threshold = prefix_s;     // keys are distinct: exactly `keep` are >= it
+
+    // order-preserving compaction over pool index
+    const int per = (np + TOPK_THREADS - 1) / TOPK_THREADS;
+    const int lo = min(np, tid * per), hi = min(np, lo + per);
+    int mine = 0;
+    for (int i = lo; i < hi; i++) mine += rank_key(sc[i], i) >= threshold;
+    scan[tid] = mine;
+    __syncthreads();
+    for (int o = 1; o < TOPK_THREADS; o <<= 1) {
+        const int v = tid >= o ? scan[tid - o] : 0;
+        __syncthreads();
+        scan[tid] += v;
+        __syncthreads();
+    }
+    int at = scan[tid] - mine;
+    for (int i = lo; i < hi; i++)
+        if (rank_key(sc[i], i) >= threshold) {
+            for (int j = 0; j < s.KP; j++) out[at * s.KP + j] = i * s.KP + j;
+            at++;
+        }
+    const int base = keep * s.KP;
+    for (int j = np * s.KP + tid; j <= p; j += TOPK_THREADS) out[base + (j - np * s.KP)] = j;
+    if (tid == 0) nsel[t] = base + (p - np * s.KP + 1);
+}
+
+void dsa_select(cudaStream_t st, int *sel, int *nsel, const float *idx_state, const float *qidx,
+                const float *wproj, float *score, int T, int cached, const MlaShape &s)
+{
+    const int np_max = (cached + T) / s.KP;
+    if (np_max > s.topk / s.KP) {
+        const size_t smem = (size_t)s.ID * s.IH * sizeof(float) + (size_t)DSA_WARPS * s.IH * sizeof(double);
+        int blocks = (np_max + DSA_WARPS - 1) / DSA_WARPS;
+        if (blocks > 296) blocks = 296;
+        G5B_LAUNCH(dsa_score_kernel, dim3(blocks, T), DSA_WARPS * 32, smem, st, score, idx_state, qidx, wproj, cached, s);
+    }
+    G5B_LAUNCH(dsa_topk_kernel, T, TOPK_THREADS, 0, st, sel, nsel, score, cached, s);
+}
+
+// ---------------------------------------------------------------- attention ----
+__device__ __forceinline__ double mat_elem(const DMat &m, int r, int c)
+{
+    if (m.dt == DT_BF16) return (double)bf16_to_f32(static_cast<const uint16_t *>(m.w)[(size_t)r * m.cols + c]);
+    if (m.dt == DT_FP8)
+        return __dmul_rn((double)e4m3_to_f32(static_cast<const uint8_t *>(m.w)[(size_t)r * m.cols + c]),
+                         (double)m.s[(size_t)(r / m.br) * m.scols + c / m.bc]);
+    return (double)static_cast<const float *>(m.w)[(size_t)r * m.cols + c];
+}
+
+// qa[t][h][c] = sum_i q[t][h][i] * W_k[h][i][c] in FP64, ascending i (matmul_transposed,
+// glm53f_ops.c:793-814). A thread owns a latent column.
+__global__ void mla_absorb_kernel(double *qa, const float *q, const DMat kv_b, MlaShape s)
+{
+    const int h = blockIdx.x, t = blockIdx.y;
+    const int kvd = s.qn + s.vh;
+    const float *qt = q + ((size_t)t * s.H + h) * s.qn;
+    for (int c = threadIdx.x; c < s.KL; c += blockDim.x) {
+        double acc = 0.0;
+        if (kv_b.dt == DT_BF16) {
+            const uint16_t *w = static_cast<const uint16_t *>(kv_b.w) + (size_t)h * kvd * s.KL + c;
+#pragma unroll 8
+            for (int i = 0; i < s.qn; i++) acc = fma((double)qt[i], (double)bf16_to_f32(w[(size_t)i * s.KL]), acc);
+        } else {
+            for (int i = 0; i < s.qn; i++) acc = __dadd_rn(acc, __dmul_rn((double)qt[i], mat_elem(kv_b, h * kvd + i, c)));
+        }
+        qa[((size_t)t * s.H + h) * s.KL + c] = acc;
+    }
+}
+
+void mla_absorb(cudaStream_t st, double *qa, const float *q, const DMat &kv_b, int T, const MlaShape &s)
+{
+    G5B_LAUNCH(mla_absorb_kernel, dim3(s.H, T), s.KL >= 512 ? 512 : 128, 0, st, qa, q, kv_b, s);
+}
+
+// d[t][h][jj] = (qa . c_j) * scale in FP64 for the visible positions (all, or the selection).
+constexpr int ATT_WARPS = 8;
+__global__ void __launch_bounds__(ATT_WARPS * 32) mla_score_kernel(
+    double *dsc, const double *qa, const void *latent, const int *sel, const int *nsel, int cached,
+    int stride, MlaShape s)
+{
+    extern __shared__ double qs[];                            // [KL]
+    const int h = blockIdx.y, t = blockIdx.z, p = cached + t;
+    const int ns = nsel ? nsel[t] : -1;
+    const int nvis = ns < 0 ? p + 1 : ns;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (blockIdx.x * ATT_WARPS >= nvis) return;
+    for (int i = threadIdx.x; i < s.KL; i += blockDim.x) qs[i] = qa[((size_t)t * s.H + h) * s.KL + i];
+    __syncthreads();
+    const float scale = 1.0f / sqrtf((float)s.qn);
+    const int *sl = sel ? sel + (size_t)t * (s.topk + s.KP) : nullptr;
+    for (int jj = blockIdx.x * ATT_WARPS + warp; jj < nvis; jj += gridDim.x * ATT_WARPS) {
+        const int j = ns < 0 ? jj : sl[jj];
+        double d = 0.0;
+        for (int i = lane; i < s.KL; i += 32) d = fma(qs[i], (double)latent_at(latent, s.latent_bf16, (size_t)j * s.KL + i), d);
+        d = warp_sum(d);
+        if (lane == 0) dsc[((size_t)t * s.H + h) * stride + jj] = d * (double)scale;
+    }
+}
+
+// Softmax as the reference takes it (glm53f_ops.c:890-903): max over the unrounded scores, the
+// exponent of the score rounded to float, probabilities in FP64; then cb = sum_j p_j c_j with a
+// thread per latent column walking the positions in ascending order.
+__global__ void __launch_bounds__(512) mla_wsum_kernel(
+    float *cb, double *dsc, const void *latent, const int *sel, const int *nsel, int cached,
+    int stride, MlaShape s)
+{
+    __shared__ double red[32];
+    __shared__ double zs;
+    const int h = blockIdx.x, t = blockIdx.y, p = cached + t;
+    const int ns = nsel ? nsel[t] : -1;
+    const int nvis = ns < 0 ? p + 1 : ns;
+    double *d = dsc + ((size_t)t * s.H + h) * stride;
+    const int *sl = sel ? sel + (size_t)t * (s.topk + s.KP) : nullptr;
+
+    double top = -INFINITY;
+    for (int jj = threadIdx.x; jj < nvis; jj += blockDim.x) top = fmax(top, d[jj]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) top = fmax(top, __shfl_xor_sync(0xffffffffu, top, o));
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = top;
+    __syncthreads();
+    for (int w = 0; w < (int)(blockDim.x >> 5); w++) top = fmax(top, red[w]);
+    __syncthreads();
+
+    double z = 0.0;
+    for (int jj = threadIdx.x; jj < nvis; jj += blockDim.x) {
+        const double e = exp((double)(float)d[jj] - top);
+        d[jj] = e;                                         // keep the numerator
+        z += e;
+    }
+    z = block_sum(z, red);
+    if (threadIdx.x == 0) zs = z;
+    __syncthreads();
+    z = zs;
+    for (int jj = threadIdx.x; jj < nvis; jj += blockDim.x) d[jj] = d[jj] / z;
+    __syncthreads();
+    for (int i = threadIdx.x; i < s.KL; i += blockDim.x) {
+        double acc = 0.0;
+        for (int jj = 0; jj < nvis; jj++) {
+            const int j = ns < 0 ? jj : sl[jj];
+            acc = fma(d[jj], (double)latent_at(latent, s.latent_bf16, (size_t)j * s.KL + i), acc);
+        }
+        cb[((size_t)t * s.H + h) * s.KL + i] = (float)acc;
+    }
+}
+
+void mla_attend(cudaStream_t st, float *cb, const double *qa, const void *latent, const int *sel,
+                const int *nsel, double *dsc, int T, int cached, const MlaShape &s)
+{
+    const int nvis_max = cached + T < s.topk + s.KP ? cached + T : s.topk + s.KP;
+    const int stride = s.topk + s.KP;
+    int blocks = (nvis_max + ATT_WARPS - 1) / ATT_WARPS;
+    if (blocks > 32) blocks = 32;
+    G5B_LAUNCH(mla_score_kernel, dim3(blocks, s.H, T), ATT_WARPS * 32, (size_t)s.KL * sizeof(double), st, dsc, qa,
+               latent, sel, nsel, cached, stride, s);
+    G5B_LAUNCH(mla_wsum_kernel, dim3(s.H, T), s.KL >= 512 ? 512 : 128, 0, st, cb, dsc, latent, sel, nsel, cached,
+               stride, s);
+}
+
+// o[t][h][r] = W_v[h][r] . cb[t][h]: the value half of kv_b applied once per query and head
+// (glm53f_ops.c:904-909). A warp takes RW rows of one head.
+__global__ void __launch_bounds__(256) mla_vout_kernel(float *acc_out, const float *cb, const DMat kv_b, MlaShape s)
+{
+    const int h = blockIdx.y, t = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = (blockIdx.x * 8 + warp) * RW;
+    if (r >= s.vh) return;
+    const int kvd = s.qn + s.vh;
+    const size_t rb = (size_t)s.KL * (kv_b.dt == DT_FP8 ? 1 : kv_b.dt == DT_BF16 ? 2 : 4);
+    const void *wrow[RW];
+    const float *srow[RW];
+#pragma unroll
+    for (int q = 0; q < RW; q++) {
+        const int row = h * kvd + s.qn + min(r + q, s.vh - 1);
+        wrow[q] = static_cast<const uint8_t *>(kv_b.w) + (size_t)row * rb;
+        srow[q] = kv_b.dt == DT_FP8 ? kv_b.s + (size_t)(row / kv_b.br) * kv_b.scols : nullptr;
+    }
+    const float *xp[1] = {cb + ((size_t)t * s.H + h) * s.KL};
+    const float xinv[1] = {1.f};
+    float acc[RW][1];
+#pragma unroll
+    for (int q = 0; q < RW; q++) acc[q][0] = 0.f;
+    dot_rows<1>(acc, kv_b.dt, wrow, srow, kv_b.bc, xp, xinv, nullptr, false, 0, s.KL / piece_elems(kv_b.dt), lane);
+#pragma unroll
+    for (int q = 0; q < RW; q++) {
+        const float v = warp_sum(acc[q][0]);
+        if (lane == 0 && r + q < s.vh) acc_out[((size_t)t * s.H + h) * s.vh + r + q] = v;
+    }
+}
+
+// Same product for shapes the streaming loop cannot take (ragged columns, tiny FP8 blocks).
+__global__ void mla_vout_any_kernel(float *acc_out, const float *cb, const DMat kv_b, MlaShape s)
+{
+    const int h = blockIdx.y, t = blockIdx.z;
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= s.vh) return;
+    const int row = h * (s.qn + s.vh) + s.qn + r;
+    const float *x = cb + ((size_t)t * s.H + h) * s.KL;
+    double acc = 0.0;
+    for (int c = 0; c < s.KL; c++) acc += mat_elem(kv_b, row, c) * (double)x[c];
+    acc_out[((size_t)t * s.H + h) * s.vh + r] = (float)acc;
+}
+
+void mla_vout(cudaStream_t st, float *acc_out, const float *cb, const DMat &kv_b, int T, const MlaShape &s)
+{
+    const bool fast = s.KL % piece_elems(kv_b.dt) == 0 && (kv_b.dt != DT_FP8 || kv_b.bc % 16 == 0);
+    if (fast) G5B_LAUNCH(mla_vout_kernel, dim3((s.vh + 8 * RW - 1) / (8 * RW), s.H, T), 256, 0, st, acc_out, cb, kv_b, s);
+    else      G5B_LAUNCH(mla_vout_any_kernel, dim3((s.vh + 63) / 64, s.H, T), 64, 0, st, acc_out, cb, kv_b, s);
+}
+
+}  // namespace g5b

@@ -1,0 +1,345 @@
+// moe.cu - sigmoid router with correction bias and top-k, and the routed + shared experts.
+//
+// Reference: glm53f_router (src/core/glm53f_ops.c:945-976) and moe_chunk (:1144-1342). The
+// reference never ran these on a GPU: routed experts stayed on the CPU behind an SSD cache
+// (src/gpu/glm53f_gpu.c:1024-1040). Here every expert is HBM resident and a MoE layer is
+//   router_scores -> router_topk -> (moe_plan when T > 1) -> gate/up + clamped SwiGLU -> down
+//   -> combine,
+// with no host involvement: the expert ids stay on the device and the expert kernels index the
+// weight table with them.
+//
+// Expert-major like the reference: each distinct expert's weights are streamed once for all
+// (token, slot) pairs that chose it, every pair keeps its own output row, and the rows are
+// summed per token in top-k order in FP64 (:1329-1337), the shared expert added last in FP32.
+#include "dot_rows.cuh"
+#include "kernels.h"
+
+namespace g5b {
+
+constexpr int MOE_THREADS = 256;
+constexpr int MOE_WARPS = MOE_THREADS / 32;
+
+// ------------------------------------------------------------------ router ----
+// score[t][e] = sigmoid((float) sum_i W[e][i] x[t][i]) with the sum in FP64.
+__global__ void __launch_bounds__(MOE_THREADS) router_scores_kernel(
+    float *score, const float *x, int ldx, const void *gate, int gate_dt, int NE, int E)
+{
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = blockIdx.x * MOE_WARPS + warp, t = blockIdx.y;
+    if (e >= NE) return;
+    const float *xt = x + (size_t)t * ldx;
+    double acc = 0.0;
+    if (gate_dt == DT_BF16) {
+        const uint16_t *row = static_cast<const uint16_t *>(gate) + (size_t)e * E;
+        for (int i = lane; i < E; i += 32) acc += (double)bf16_to_f32(row[i]) * (double)xt[i];
+    } else {
+        const float *row = static_cast<const float *>(gate) + (size_t)e * E;
+        for (int i = lane; i < E; i += 32) acc += (double)row[i] * (double)xt[i];
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) score[(size_t)t * NE + e] = sigmoid_host((float)acc);
+}
+
+// Top-k of (score + bias) by repeated arg-max with strict '>' (lowest index wins ties), weights
+// from the unbiased scores, normalised in FP64, times the routed scale. One warp per token.
+__global__ void router_topk_kernel(int *idx, float *w, const float *score, const float *bias, int NE,
+                                   int K, int norm_topk, float routed_scale)
+{
+    __shared__ float choice[G5B_MAX_EXPERTS];
+    __shared__ float wsel[G5B_MAX_TOPK];
+    const int t = blockIdx.x, lane = threadIdx.x;
+    const float *sc = score + (size_t)t * NE;
+    for (int e = lane; e < NE; e += 32) choice[e] = __fadd_rn(sc[e], bias[e]);
+    __syncwarp();
+    for (int j = 0; j < K; j++) {
+        float bv = -INFINITY;
+        int bi = -1;
+        for (int e = lane; e < NE; e += 32)
+            if (choice[e] > bv) { bv = choice[e]; bi = e; }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (oi >= 0 && (bi < 0 || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
+        }
+        if (bi < 0) bi = 0;                        // every score NaN: the reference aborts here
+        if (lane == 0) {
+            idx[(size_t)t * K + j] = bi;
+            wsel[j] = sc[bi];
+            choice[bi] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    if (lane == 0) {
+        if (norm_topk) {
+            double s = 0.0;
+            for (int j = 0; j < K; j++) s += (double)wsel[j];
+            for (int j = 0; j < K; j++) wsel[j] = (float)((double)wsel[j] / (s + 1e-20));
+        }
+        for (int j = 0; j < K; j++) w[(size_t)t * K + j] = __fmul_rn(wsel[j], routed_scale);
+    }
+}
+
+void router_topk(cudaStream_t st, int *idx, float *w, const float *x, int ldx, const void *gate,
+                 int gate_dt, const float *bias, double *score_scratch, int T, const MoeShape &s)
+{
+    float *score = reinterpret_cast<float *>(score_scratch);
+    G5B_LAUNCH(router_scores_kernel, dim3((s.NE + MOE_WARPS - 1) / MOE_WARPS, T), MOE_THREADS, 0, st,
+               score, x, ldx, gate, gate_dt, s.NE, s.E);
+    G5B_LAUNCH(router_topk_kernel, T, 32, 0, st, idx, w, score, bias, s.NE, s.K, s.norm_topk, s.routed_scale);
+}
+
+// -------------------------------------------------------------------- plan ----
+// Group the (token, slot) pairs by expert. Thread e gathers the pairs of local expert e in token
+// order; slots are numbered in expert order; the shared expert, when asked for, is the last slot
+// and takes every token.
+__global__ void __launch_bounds__(1024) moe_plan_kernel(MoePlan p, const int *idx, int T, int K,
+                                                       int n_local0, int n_local, int with_shared)
+{
+    __shared__ int cnt[G5B_MAX_EXPERTS];
+    __shared__ int off[G5B_MAX_EXPERTS];
+    __shared__ int slot[G5B_MAX_EXPERTS];
+    __shared__ int totals[2];
+    const int e = threadIdx.x;
+    const int n = T * K;
+    int c = 0;
+    if (e < n_local)
+        for (int i = 0; i < n; i++) c += idx[i] == n_local0 + e;
+    if (e < n_local) cnt[e] = c;
+    __syncthreads();
+    if (e == 0) {
+        int o = 0, s = 0;
+        for (int i = 0; i < n_local; i++) {
+            off[i] = o; slot[i] = s;
+            if (cnt[i]) { o += cnt[i]; s++; }
+        }
+        totals[0] = o; totals[1] = s;
+    }
+    __syncthreads();
+    if (e < n_local && c) {
+        const int s = slot[e];
+        p.slot_expert[s] = e; p.slot_off[s] = off[e]; p.slot_cnt[s] = c;
+        int o = off[e];
+        for (int i = 0; i < n; i++)
+            if (idx[i] == n_local0 + e) { p.pair_tok[o] = i / K; p.pair_dst[o] = i; o++; }
+    }
+    if (with_shared) {
+        const int s = totals[1], o = totals[0];
+        if (e == 0) { p.slot_expert[s] = n_local; p.slot_off[s] = o; p.slot_cnt[s] = T; }
+        for (int t = e; t < T; t += blockDim.x) { p.pair_tok[o + t] = t; p.pair_dst[o + t] = n + t; }
+    }
+    if (e == 0) *p.n_slots = totals[1] + (with_shared ? 1 : 0);
+}
+
+void moe_plan(cudaStream_t st, const MoePlan &p, const int *idx, int T, const MoeShape &s, int with_shared)
+{
+    G5B_LAUNCH(moe_plan_kernel, 1, 1024, 0, st, p, idx, T, s.K, s.n_local0, s.n_local, with_shared);
+}
+
+// ----------------------------------------------------------------- experts ----
+__device__ __forceinline__ float swiglu_clamped(float g, float u, float lim)
+{
+    g = g > lim ? lim : g;
+    u = u > lim ? lim : (u < -lim ? -lim : u);
+    return __fmul_rn(__fmul_rn(g, sigmoid_host(g)), u);
+}
+
+struct ExpertArgs {
+    const ExpertW *experts;
+    MoePlan p;
+    const float *x;      // gate/up: layer input [T][ldx]; down: activations [pairs][I]
+    float *y;            // gate/up: activations [pairs][I]; down: contributions [T*K (+T)][E]
+    int ldx, E, I, br, bc, dt;
+    float limit;
+};
+
+// Rows of one token tile. gate/up: the warp holds gate rows r, r+1 and up rows r, r+1 and writes
+// the clamped SwiGLU of the pair; down: four consecutive output rows.
+template <int TT, bool GATEUP>
+__device__ __forceinline__ void expert_tile(const ExpertArgs &a, const void *const (&wrow)[RW],
+                                            const float *const (&srow)[RW], int off, int i0, int cnt,
+                                            int r, int rows_total, int C, int lane)
+{
+    const float *xp[TT];
+    float xinv[TT];
+    int pair[TT];
+#pragma unroll
+    for (int t = 0; t < TT; t++) {
+        pair[t] = off + min(i0 + t, cnt - 1);
+        xp[t] = GATEUP ? a.x + (size_t)a.p.pair_tok[pair[t]] * a.ldx : a.x + (size_t)pair[t] * a.I;
+        xinv[t] = 1.f;
+    }
+    float acc[RW][TT];
+#pragma unroll
+    for (int q = 0; q < RW; q++)
+#pragma unroll
+        for (int t = 0; t < TT; t++) acc[q][t] = 0.f;
+    dot_rows<TT>(acc, a.dt, wrow, srow, a.bc, xp, xinv, nullptr, false, 0, C / piece_elems(a.dt), lane);
+#pragma unroll
+    for (int q = 0; q < RW; q++)
+#pragma unroll
+        for (int t = 0; t < TT; t++) acc[q][t] = warp_sum(acc[q][t]);
+    if (lane == 0) {
+#pragma unroll
+        for (int t = 0; t < TT; t++) {
+            if (i0 + t >= cnt) break;
+            if (GATEUP) {
+                float *dst = a.y + (size_t)pair[t] * a.I;
+                dst[r] = swiglu_clamped(acc[0][t], acc[2][t], a.limit);
+                if (r + 1 < rows_total) dst[r + 1] = swiglu_clamped(acc[1][t], acc[3][t], a.limit);
+            } else {
+                float *dst = a.y + (size_t)a.p.pair_dst[pair[t]] * a.E;
+#pragma unroll
+                for (int q = 0; q < RW; q++)
+                    if (r + q < rows_total) dst[r + q] = acc[q][t];
+            }
+        }
+    }
+}
+
+// MAXTT = 1 is the decode instantiation (one token per expert, half the registers, two CTAs per
+// SM); MAXTT = 4 serves batches.
+template <bool GATEUP, int MAXTT>
+__global__ void __launch_bounds__(MOE_THREADS, MAXTT == 1 ? 2 : 1) expert_kernel(const ExpertArgs a)
+{
+    const int s = blockIdx.y;
+    if (s >= *a.p.n_slots) return;
+    const ExpertW ew = a.experts[a.p.slot_expert[s]];
+    const int off = a.p.slot_off[s], cnt = a.p.slot_cnt[s];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int C = GATEUP ? a.E : a.I;                       // columns of the matrices multiplied
+    const int rows_total = GATEUP ? a.I : a.E;
+    const int scols = (C + a.bc - 1) / (a.bc > 0 ? a.bc : 1);
+    const size_t rb = (size_t)C * (a.dt == DT_FP8 ? 1 : a.dt == DT_BF16 ? 2 : 4);
+    const int r = (blockIdx.x * MOE_WARPS + warp) * (GATEUP ? 2 : RW);
+    if (r >= rows_total) return;
+
+    const void  *wrow[RW];
+    const float *srow[RW];
+    if (GATEUP) {
+        const int r1 = min(r + 1, rows_total - 1);
+        wrow[0] = ew.gate + (size_t)r * rb;  wrow[1] = ew.gate + (size_t)r1 * rb;
+        wrow[2] = ew.up + (size_t)r * rb;    wrow[3] = ew.up + (size_t)r1 * rb;
+        if (a.dt == DT_FP8) {
+            srow[0] = ew.gate_s + (size_t)(r / a.br) * scols;  srow[1] = ew.gate_s + (size_t)(r1 / a.br) * scols;
+            srow[2] = ew.up_s + (size_t)(r / a.br) * scols;    srow[3] = ew.up_s + (size_t)(r1 / a.br) * scols;
+        } else { srow[0] = srow[1] = srow[2] = srow[3] = nullptr; }
+    } else {
+#pragma unroll
+        for (int q = 0; q < RW; q++) {
+            const int rq = min(r + q, rows_total - 1);
+            wrow[q] = ew.down + (size_t)rq * rb;
+            srow[q] = a.dt == DT_FP8 ? ew.down_s + (size_t)(rq / a.br) * scols : nullptr;
+        }
+    }
+    // Token tiles: the weights stream once per tile of up to four tokens of this expert.
+    for (int i0 = 0; i0 < cnt;) {
+        const int rem = cnt - i0;
+        if (MAXTT >= 4 && rem >= 3)      { expert_tile<MAXTT >= 4 ? 4 : 1, GATEUP>(a, wrow, srow, off, i0, cnt, r, rows_total, C, lane); i0 += 4; }
+        else if (MAXTT >= 2 && rem == 2) { expert_tile<MAXTT >= 2 ? 2 : 1, GATEUP>(a, wrow, srow, off, i0, cnt, r, rows_total, C, lane); i0 += 2; }
+        else                             { expert_tile<1, GATEUP>(a, wrow, srow, off, i0, cnt, r, rows_total, C, lane); i0 += 1; }
+    }
+}
+
+// Any shape / block size: a warp per output row and pair, FP64 sums (test fixtures).
+template <bool GATEUP>
+__global__ void __launch_bounds__(MOE_THREADS) expert_any_kernel(const ExpertArgs a)
+{
+    const int s = blockIdx.y;
+    if (s >= *a.p.n_slots) return;
+    const ExpertW ew = a.experts[a.p.slot_expert[s]];
+    const int off = a.p.slot_off[s], cnt = a.p.slot_cnt[s];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int C = GATEUP ? a.E : a.I, rows_total = GATEUP ? a.I : a.E;
+    const int scols = (C + a.bc - 1) / (a.bc > 0 ? a.bc : 1);
+    const int r = blockIdx.x * MOE_WARPS + warp;
+    if (r >= rows_total) return;
+    const int nm = GATEUP ? 2 : 1;
+    for (int i = 0; i < cnt; i++) {
+        const int pair = off + i;
+        const float *x = GATEUP ? a.x + (size_t)a.p.pair_tok[pair] * a.ldx : a.x + (size_t)pair * a.I;
+        double acc[2] = {0.0, 0.0};
+        for (int m = 0; m < nm; m++) {
+            const void *W = GATEUP ? (m ? ew.up : ew.gate) : ew.down;
+            const float *S = GATEUP ? (m ? ew.up_s : ew.gate_s) : ew.down_s;
+            for (int c = lane; c < C; c += 32) {
+                double wv;
+                if (a.dt == DT_FP8)
+                    wv = (double)e4m3_to_f32(static_cast<const uint8_t *>(W)[(size_t)r * C + c]) *
+                         (double)S[(size_t)(r / a.br) * scols + c / a.bc];
+                else if (a.dt == DT_BF16) wv = (double)bf16_to_f32(static_cast<const uint16_t *>(W)[(size_t)r * C + c]);
+                else wv = (double)static_cast<const float *>(W)[(size_t)r * C + c];
+                acc[m] += wv * (double)x[c];
+            }
+            acc[m] = warp_sum(acc[m]);
+        }
+        if (lane == 0) {
+            if (GATEUP) a.y[(size_t)pair * a.I + r] = swiglu_clamped((float)acc[0], (float)acc[1], a.limit);
+            else        a.y[(size_t)a.p.pair_dst[pair] * a.E + r] = (float)acc[0];
+        }
+    }
+}
+
+static bool experts_fast(const MoeShape &s, int C)
+{
+    if (C % piece_elems(s.dt)) return false;
+    if (s.dt == DT_FP8 && (s.bc % 16 || s.br < 1)) return false;
+    return true;
+}
+
+static int plan_slots(const MoePlan &p, int T, const MoeShape &s)
+{
+    int m = T * s.K < s.n_local ? T * s.K : s.n_local;
+    m += 1;
+    return m < p.max_slots ? m : p.max_slots;
+}
+
+void moe_gateup(cudaStream_t st, float *act, const float *x, int ldx, const ExpertW *experts,
+                const MoePlan &p, int T, const MoeShape &s)
+{
+    ExpertArgs a{experts, p, x, act, ldx, s.E, s.I, s.br, s.bc, s.dt, s.limit};
+    const int slots = plan_slots(p, T, s);
+    const dim3 grid((s.I + 2 * MOE_WARPS - 1) / (2 * MOE_WARPS), slots);
+    if (experts_fast(s, s.E) && (ldx % 4) == 0) {
+        if (T == 1) G5B_LAUNCH((expert_kernel<true, 1>), grid, MOE_THREADS, 0, st, a);
+        else        G5B_LAUNCH((expert_kernel<true, 4>), grid, MOE_THREADS, 0, st, a);
+    } else
+        G5B_LAUNCH(expert_any_kernel<true>, dim3((s.I + MOE_WARPS - 1) / MOE_WARPS, slots), MOE_THREADS, 0, st, a);
+}
+
+void moe_down(cudaStream_t st, float *contrib, const float *act, const ExpertW *experts,
+              const MoePlan &p, int T, const MoeShape &s)
+{
+    ExpertArgs a{experts, p, act, contrib, s.I, s.E, s.I, s.br, s.bc, s.dt, s.limit};
+    const int slots = plan_slots(p, T, s);
+    const dim3 grid((s.E + RW * MOE_WARPS - 1) / (RW * MOE_WARPS), slots);
+    if (experts_fast(s, s.I) && (s.I % 4) == 0) {
+        if (T == 1) G5B_LAUNCH((expert_kernel<false, 1>), grid, MOE_THREADS, 0, st, a);
+        else        G5B_LAUNCH((expert_kernel<false, 4>), grid, MOE_THREADS, 0, st, a);
+    } else
+        G5B_LAUNCH(expert_any_kernel<false>, dim3((s.E + MOE_WARPS - 1) / MOE_WARPS, slots), MOE_THREADS, 0, st, a);
+}
+
+// out[t][d] = (float) sum_j w[t][j] * contrib[t*K+j][d]  (FP64, top-k order)  (+ shared, FP32).
+__global__ void moe_combine_kernel(float *out, int ldo, const float *contrib, const float *w, int T, int K,
+                                   int E, int with_shared)
+{
+    const int t = blockIdx.y;
+    const int d = blockIdx.x * blockDim.x + threadIdx.x;
+    if (d >= E) return;
+    double s = 0.0;
+    for (int j = 0; j < K; j++)
+        s += (double)w[(size_t)t * K + j] * (double)contrib[((size_t)t * K + j) * E + d];
+    float o = (float)s;
+    if (with_shared) o = __fadd_rn(o, contrib[((size_t)T * K + t) * E + d]);
+    out[(size_t)t * ldo + d] = o;
+}
+
+void moe_combine(cudaStream_t st, float *out, int ldo, const float *contrib, const float *w, int T,
+                 const MoeShape &s, int with_shared)
+{
+    G5B_LAUNCH(moe_combine_kernel, dim3((s.E + 255) / 256, T), 256, 0, st, out, ldo, contrib, w, T, s.K, s.E,
+               with_shared);
+}
+
+}  // namespace g5b

@@ -116,6 +116,10 @@ int g5b_engine_load(g5b_engine *e, const char *name, const g5b_tensor *t);
 int g5b_engine_fill_expert(g5b_engine *e, int layer, int expert, uint64_t seed,
                            const float *gate_s, const float *up_s, const float *down_s);
 
+/* Engine options, by name. "latent_bf16" (before finalize): keep the MLA latent cache in BF16
+ * instead of FP32, half the bytes per position. "profile": record per-phase events in MoE ops. */
+int g5b_engine_set_option(g5b_engine *e, const char *name, int value);
+
 /* Check that every tensor the config implies has been loaded, then allocate the session
  * state (KDA recurrent + conv state, MLA latent cache, DSA indexer state) and work buffers. */
 int g5b_engine_finalize(g5b_engine *e);
@@ -209,12 +213,17 @@ int   g5b_engine_sync(g5b_engine *e);
 void *g5b_engine_stream(g5b_engine *e);            /* the cudaStream_t ops are launched on */
 /* Kernels this library has launched since it was loaded (benchmark bookkeeping). */
 uint64_t g5b_launch_count(void);
-/* Time `iters` back-to-back launches of the batch-1..64 MoE layer between two CUDA events on
- * the engine's stream, after writing `flush_bytes` to a scratch buffer before each launch
- * (0 = no flush). Returns the mean milliseconds per launch in *ms_out; per-kernel means of
- * the router / gate-up / down kernels in kern_ms[3] when not NULL. */
-int g5b_time_moe(g5b_engine *e, int layer, const float *x_dev, int T, float *out_dev,
-                 int iters, size_t flush_bytes, float *ms_out, float *kern_ms);
+/* Time `iters` launches of one op ("moe", "kda", "mla", "layer") between CUDA events recorded on
+ * the engine's stream. Before each launch `flush_bytes` of scratch memory are overwritten (0 =
+ * no flush) so that the weights come from HBM and not from L2. ms_total receives the sum of the
+ * per-launch times, ms_each (may be NULL, `iters` floats) each of them. For "layer", out_dev is
+ * the residual stream h, updated in place. */
+int g5b_time_op(g5b_engine *e, const char *op, int layer, const float *x_dev, int T, int cached,
+                float *out_dev, int iters, size_t flush_bytes, float *ms_total, float *ms_each);
+/* With the "profile" option on, every MoE op also records events between its phases; this
+ * reads the accumulated milliseconds of [router+plan, gate/up, down, combine] and the number of
+ * ops they cover, and optionally clears them. */
+int g5b_engine_profile_read(g5b_engine *e, float *ms, int n, long *count, int reset);
 
 #ifdef __cplusplus
 }
