@@ -36,7 +36,7 @@ sys.path.insert(0, os.path.join(ROOT, "tests"))
 SEED = 0
 EXPERT_BYTES = 3 * 2048 * 4096 + 3 * 16 * 32 * 4            # codes + block scales of one expert
 GATEUP_BYTES = 2 * 2048 * 4096 + 2 * 16 * 32 * 4            # what the gate/up kernel reads per expert
-ROUTER_BYTES = 288 * 4096 * 2
+ROUTER_BYTES = 288 * 4096 * 2                               # BF16 router matrix
 FLUSH_BYTES = 256 << 20                                     # > 126 MB of L2
 # dram__bytes_read.sum + dram__bytes_write.sum of one gate/up launch at batch 1 (profiles/), or None
 GATEUP_TRAFFIC_NCU = None
@@ -183,6 +183,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--experts", type=int, default=288,
+                    help="routed experts resident in the layer (288 = the stated config; fewer only to keep "
+                         "an ncu capture small: the batch-1 kernels touch 8 routed + 1 shared either way)")
+    ap.add_argument("--batches", default="8,64", help="extra batch sizes reported under 'extra'")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -204,7 +208,8 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
     warmup = max(3, args.warmup)
-    spec, trunk, eng = synth.build_moe_layer_engine(SEED, device=local, options={"profile": 1})
+    spec, trunk, eng = synth.build_moe_layer_engine(SEED, n_experts=args.experts, device=local,
+                                                    options={"profile": 1})
     sampler = ClockSampler(local)
 
     def barrier():
@@ -263,7 +268,7 @@ def main():
 
     extra = {"phase_ms_b1": {"router+plan": phases[0], "gate_up": phases[1], "down": phases[2], "combine": phases[3]}}
     if rank == 0:
-        for B in (8, 64):
+        for B in [int(b) for b in args.batches.split(",") if b]:
             eb, ph, _, _ = time_batch(pkg, eng, torch, B, max(10, args.steps // 10), 3)
             idx, _ = eng.op_router(0, synth.moe_inputs(spec.cfg, B, SEED))
             distinct = int(len(set(idx.ravel().tolist())))
@@ -274,7 +279,7 @@ def main():
     eng.close()
 
     cpu = None
-    if rank == 0 and not args.no_cpu_baseline:
+    if rank == 0 and not args.no_cpu_baseline and args.experts == 288:
         cpu = cpu_reference_moe(steps=60, warmup=2)
         one = cpu_reference_moe(steps=30, warmup=1, threads=1)
         cpu = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}

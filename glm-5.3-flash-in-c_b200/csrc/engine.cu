@@ -38,7 +38,7 @@ static int fail(const char *fmt, ...)
         if (e_ != cudaSuccess) return fail("%s: %s", #call, cudaGetErrorString(e_));       \
     } while (0)
 
-constexpr int CHUNK = 32;       // positions one pass of a layer works on (sizes the work buffers)
+constexpr int CHUNK = 64;       // positions one pass of a layer works on (the reference's MoE chunk, glm53f_ops.c:988)
 constexpr int PROF_SLOTS = 8;
 
 struct Layer {
@@ -78,7 +78,9 @@ struct g5b_engine {
     g5b_config c;
     int cap = 0, cached = 0, device = 0, ep_rank = 0, ep_size = 1, n_local0 = 0, n_local = 0;
     bool finalized = false;
-    int latent_bf16 = 0, profile = 0, partial = 0;
+    int latent_bf16 = 0, profile = 0, partial = 0, stream_experts = 1;
+    int *counter = nullptr, *tile_done = nullptr, *err_dev = nullptr;
+    volatile int *err_host = nullptr;   // mapped host memory: kernels record a timed-out wait here
     cudaStream_t st = nullptr;
     std::vector<Layer> L;
     std::vector<std::unordered_map<std::string, Target>> names;   // per layer
@@ -251,6 +253,7 @@ extern "C" int g5b_engine_set_option(g5b_engine *e, const char *name, int value)
     }
     if (!strcmp(name, "profile")) { e->profile = value; return 0; }
     if (!strcmp(name, "allow_partial")) { e->partial = value != 0; return 0; }
+    if (!strcmp(name, "stream_experts")) { e->stream_experts = value != 0; return 0; }
     return fail("unknown option %s", name);
 }
 
@@ -490,6 +493,14 @@ extern "C" int g5b_engine_finalize(g5b_engine *e)
     if (walloc(e, &e->plan.n_slots, 1) || walloc(e, &e->plan.slot_expert, e->plan.max_slots) ||
         walloc(e, &e->plan.slot_off, e->plan.max_slots) || walloc(e, &e->plan.slot_cnt, e->plan.max_slots) ||
         walloc(e, &e->plan.pair_tok, pairs) || walloc(e, &e->plan.pair_dst, pairs)) return -1;
+    if (walloc(e, &e->counter, 4) || walloc(e, &e->tile_done, E / 32 + 1)) return -1;
+    {
+        int *hp = nullptr;
+        CU(cudaHostAlloc((void **)&hp, 64, cudaHostAllocMapped));
+        *hp = 0;
+        e->err_host = hp;
+        CU(cudaHostGetDevicePointer((void **)&e->err_dev, hp, 0));
+    }
     if (walloc(e, &e->xm, N * E) || walloc(e, &e->inv_head, N) || walloc(e, &e->logits, N * (size_t)c.vocab) ||
         walloc(e, &e->am_v, N * 64) || walloc(e, &e->am_i, N * 64) || walloc(e, &e->am_out, (size_t)e->cap + N)) return -1;
     CU(cudaStreamSynchronize(e->st));
@@ -534,10 +545,19 @@ static int run_moe(g5b_engine *e, Layer &w, const float *x, int n, float *out, i
     const MoeShape s = moe_shape(e, w);
     const bool shared_in_plan = with_shared && c.n_shared == 1 && w.sh_gate.dt == s.dt;
     prof_mark(e, 0);
-    router_topk(e->st, e->ridx, e->rw, x, c.hidden, w.router.w, w.router.dt, w.bias,
-                reinterpret_cast<double *>(e->rscore), n, s);
-    moe_plan(e->st, e->plan, e->ridx, n, s, shared_in_plan ? 1 : 0);
+    router_plan(e->st, e->ridx, e->rw, e->rscore, x, c.hidden, w.router.w, w.router.dt, w.bias, n, s, e->plan,
+                shared_in_plan ? 1 : 0, e->counter);
     prof_mark(e, 1);
+    if (e->stream_experts && e->ep_size == 1 && (shared_in_plan || !with_shared) && moe_stream_supported(s, n)) {
+        moe_stream_gateup(e->st, e->act, x, w.table_dev, e->plan, s, e->err_dev);
+        prof_mark(e, 2);
+        moe_stream_down(e->st, out, e->contrib, e->act, e->rw, w.table_dev, e->plan, s, with_shared, e->tile_done,
+                        e->err_dev);
+        prof_mark(e, 3);
+        prof_mark(e, 4);
+        prof_collect(e, 4);
+        return 0;
+    }
     moe_gateup(e->st, e->act, x, c.hidden, w.table_dev, e->plan, n, s);
     prof_mark(e, 2);
     moe_down(e->st, e->contrib, e->act, w.table_dev, e->plan, n, s);
@@ -656,6 +676,17 @@ static int run_layer(g5b_engine *e, int l, float *h, int n, int cached)
     return 0;
 }
 
+// A kernel whose bounded wait ran out wrote its code here; the step's result is then invalid.
+static int check_device_error(g5b_engine *e)
+{
+    if (e->err_host && *e->err_host) {
+        const int code = *e->err_host;
+        *e->err_host = 0;
+        return fail("a device-side wait timed out (code %d); the result of this call is invalid", code);
+    }
+    return 0;
+}
+
 static int ensure_h(g5b_engine *e, size_t tokens)
 {
     if (tokens <= e->h_tokens) return 0;
@@ -724,6 +755,7 @@ extern "C" int g5b_engine_forward(g5b_engine *e, const int *ids, int T, float *l
     if (forward_device(e, e->ids_dev, T, argmax_all != nullptr, logits, argmax_all)) return -1;
     CU(cudaStreamSynchronize(e->st));
     CU(cudaGetLastError());
+    if (check_device_error(e)) return -1;
     e->cached += T;
     return 0;
 }
@@ -746,7 +778,7 @@ extern "C" int g5b_engine_decode_greedy(g5b_engine *e, int first, int n, int *ou
     CU(cudaMemcpyAsync(out, e->ids_dev + 1, (size_t)n * 4, cudaMemcpyDeviceToHost, e->st));
     CU(cudaStreamSynchronize(e->st));
     CU(cudaGetLastError());
-    return 0;
+    return check_device_error(e);
 }
 
 extern "C" void g5b_engine_reset(g5b_engine *e)
@@ -771,6 +803,7 @@ extern "C" void g5b_engine_free(g5b_engine *e)
     if (e->h) cudaFree(e->h);
     if (e->ids_dev) cudaFree(e->ids_dev);
     if (e->flush_buf) cudaFree(e->flush_buf);
+    if (e->err_host) cudaFreeHost((void *)e->err_host);
     for (int i = 0; i <= PROF_SLOTS; i++) cudaEventDestroy(e->prof_ev[i]);
     cudaStreamDestroy(e->st);
     delete e;
@@ -781,7 +814,7 @@ extern "C" int g5b_engine_sync(g5b_engine *e)
     CU(cudaSetDevice(e->device));
     CU(cudaStreamSynchronize(e->st));
     CU(cudaGetLastError());
-    return 0;
+    return check_device_error(e);
 }
 
 extern "C" void *g5b_engine_stream(g5b_engine *e) { return (void *)e->st; }
@@ -842,7 +875,7 @@ struct Staged {
         CU(cudaMemcpyAsync(dst, src, n * 4, cudaMemcpyDeviceToHost, e->st));
         CU(cudaStreamSynchronize(e->st));
         CU(cudaGetLastError());
-        return 0;
+        return check_device_error(e);
     }
 };
 
@@ -863,7 +896,7 @@ static int host_op(g5b_engine *e, const float *x, int T, float *out, F &&run)
     }
     CU(cudaStreamSynchronize(e->st));
     CU(cudaGetLastError());
-    return 0;
+    return check_device_error(e);
 }
 
 extern "C" int g5b_op_moe(g5b_engine *e, int layer, const float *x, int T, float *out, int with_shared)
@@ -886,8 +919,9 @@ extern "C" int g5b_op_router(g5b_engine *e, int layer, const float *x, int T, in
     if (!xd) return fail("out of device memory");
     const MoeShape ms = moe_shape(e, lw);
     FOR_CHUNKS(T) {
-        router_topk(e->st, e->ridx, e->rw, xd + t0 * E, (int)E, lw.router.w, lw.router.dt, lw.bias,
-                    reinterpret_cast<double *>(e->rscore), n_, ms);
+        MoePlan none{};
+        router_plan(e->st, e->ridx, e->rw, e->rscore, xd + t0 * E, (int)E, lw.router.w, lw.router.dt, lw.bias, n_, ms,
+                    none, 0, e->counter);
         CU(cudaMemcpyAsync(idx + t0 * K, e->ridx, n_ * K * 4, cudaMemcpyDeviceToHost, e->st));
         CU(cudaMemcpyAsync(w + t0 * K, e->rw, n_ * K * 4, cudaMemcpyDeviceToHost, e->st));
         CU(cudaStreamSynchronize(e->st));
@@ -1195,7 +1229,7 @@ extern "C" int g5b_time_op(g5b_engine *e, const char *op, int layer, const float
     cudaEventDestroy(a);
     cudaEventDestroy(b);
     if (ms_total) *ms_total = (float)total;
-    return 0;
+    return check_device_error(e);
 }
 
 extern "C" int g5b_engine_profile_read(g5b_engine *e, float *ms, int n, long *count, int reset)

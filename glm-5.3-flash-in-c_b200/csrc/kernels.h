@@ -94,10 +94,18 @@ struct MoeShape {
     float limit, routed_scale;
     int norm_topk;
 };
-void router_topk(cudaStream_t st, int *idx, float *w, const float *x, int ldx, const void *gate,
-                 int gate_dt, const float *bias, double *score_scratch, int T, const MoeShape &s);
-void moe_plan(cudaStream_t st, const MoePlan &p, const int *idx, int T, const MoeShape &s,
-              int with_shared);
+// Router scores, top-k and the expert-major plan in one launch. p.n_slots == nullptr: routing only.
+void router_plan(cudaStream_t st, int *idx, float *w, float *score, const float *x, int ldx, const void *gate,
+                 int gate_dt, const float *bias, int T, const MoeShape &s, const MoePlan &p, int with_shared,
+                 int *counter);
+// Batch-1 experts streamed through shared memory by the bulk-copy engine (moe_stream.cu).
+bool moe_stream_supported(const MoeShape &s, int T);
+void moe_stream_gateup(cudaStream_t st, float *act, const float *x, const ExpertW *experts, const MoePlan &p,
+                       const MoeShape &s, int *err);
+// out == nullptr: contributions only (the caller combines, e.g. after an expert-parallel exchange).
+void moe_stream_down(cudaStream_t st, float *out, float *contrib, const float *act, const float *w,
+                     const ExpertW *experts, const MoePlan &p, const MoeShape &s, int with_shared,
+                     int *tile_done, int *err);
 void moe_gateup(cudaStream_t st, float *act, const float *x, int ldx, const ExpertW *experts,
                 const MoePlan &p, int T, const MoeShape &s);
 void moe_down(cudaStream_t st, float *contrib, const float *act, const ExpertW *experts,

@@ -20,41 +20,37 @@ constexpr int MOE_THREADS = 256;
 constexpr int MOE_WARPS = MOE_THREADS / 32;
 
 // ------------------------------------------------------------------ router ----
-// score[t][e] = sigmoid((float) sum_i W[e][i] x[t][i]) with the sum in FP64.
-__global__ void __launch_bounds__(MOE_THREADS) router_scores_kernel(
-    float *score, const float *x, int ldx, const void *gate, int gate_dt, int NE, int E)
-{
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int e = blockIdx.x * MOE_WARPS + warp, t = blockIdx.y;
-    if (e >= NE) return;
-    const float *xt = x + (size_t)t * ldx;
-    double acc = 0.0;
-    if (gate_dt == DT_BF16) {
-        const uint16_t *row = static_cast<const uint16_t *>(gate) + (size_t)e * E;
-        for (int i = lane; i < E; i += 32) acc += (double)bf16_to_f32(row[i]) * (double)xt[i];
-    } else {
-        const float *row = static_cast<const float *>(gate) + (size_t)e * E;
-        for (int i = lane; i < E; i += 32) acc += (double)row[i] * (double)xt[i];
-    }
-    acc = warp_sum(acc);
-    if (lane == 0) score[(size_t)t * NE + e] = sigmoid_host((float)acc);
-}
+// One launch routes a chunk of tokens: every warp takes the FP64 dot product of one router row
+// with one token (16-byte loads of the BF16 or FP32 row), writes sigmoid((float) sum), and the
+// CTA that finishes last (a counter in device memory, no spinning) selects the top-k of every
+// token and groups the (token, slot) pairs by expert for the expert kernels.
+//
+// Selection: top-k of (score + bias) by repeated arg-max with strict '>' so that the lowest
+// index wins ties; weights from the unbiased scores, normalised in FP64, times the routed scale
+// (reference glm53f_router, src/core/glm53f_ops.c:945-976).
+constexpr int RT_WARPS = 4;
 
-// Top-k of (score + bias) by repeated arg-max with strict '>' (lowest index wins ties), weights
-// from the unbiased scores, normalised in FP64, times the routed scale. One warp per token.
-__global__ void router_topk_kernel(int *idx, float *w, const float *score, const float *bias, int NE,
-                                   int K, int norm_topk, float routed_scale)
+struct RouterArgs {
+    int *idx; float *w; float *score;
+    const float *x; int ldx;
+    const void *gate; int gate_dt;
+    const float *bias;
+    int NE, E, K, T, norm_topk;
+    float routed_scale;
+    MoePlan p;
+    int n_local0, n_local, with_shared;
+    int *counter;
+};
+
+__device__ void topk_one_token(const RouterArgs &a, int t, float *choice, float *wsel, int lane)
 {
-    __shared__ float choice[G5B_MAX_EXPERTS];
-    __shared__ float wsel[G5B_MAX_TOPK];
-    const int t = blockIdx.x, lane = threadIdx.x;
-    const float *sc = score + (size_t)t * NE;
-    for (int e = lane; e < NE; e += 32) choice[e] = __fadd_rn(sc[e], bias[e]);
+    const float *sc = a.score + (size_t)t * a.NE;
+    for (int e = lane; e < a.NE; e += 32) choice[e] = __fadd_rn(__ldcg(sc + e), a.bias[e]);
     __syncwarp();
-    for (int j = 0; j < K; j++) {
+    for (int j = 0; j < a.K; j++) {
         float bv = -INFINITY;
         int bi = -1;
-        for (int e = lane; e < NE; e += 32)
+        for (int e = lane; e < a.NE; e += 32)
             if (choice[e] > bv) { bv = choice[e]; bi = e; }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
@@ -64,76 +60,117 @@ __global__ void router_topk_kernel(int *idx, float *w, const float *score, const
         }
         if (bi < 0) bi = 0;                        // every score NaN: the reference aborts here
         if (lane == 0) {
-            idx[(size_t)t * K + j] = bi;
-            wsel[j] = sc[bi];
+            a.idx[(size_t)t * a.K + j] = bi;
+            wsel[j] = __ldcg(sc + bi);
             choice[bi] = -INFINITY;
         }
         __syncwarp();
     }
     if (lane == 0) {
-        if (norm_topk) {
+        if (a.norm_topk) {
             double s = 0.0;
-            for (int j = 0; j < K; j++) s += (double)wsel[j];
-            for (int j = 0; j < K; j++) wsel[j] = (float)((double)wsel[j] / (s + 1e-20));
+            for (int j = 0; j < a.K; j++) s += (double)wsel[j];
+            for (int j = 0; j < a.K; j++) wsel[j] = (float)((double)wsel[j] / (s + 1e-20));
         }
-        for (int j = 0; j < K; j++) w[(size_t)t * K + j] = __fmul_rn(wsel[j], routed_scale);
+        for (int j = 0; j < a.K; j++) a.w[(size_t)t * a.K + j] = __fmul_rn(wsel[j], a.routed_scale);
     }
+    __syncwarp();
 }
 
-void router_topk(cudaStream_t st, int *idx, float *w, const float *x, int ldx, const void *gate,
-                 int gate_dt, const float *bias, double *score_scratch, int T, const MoeShape &s)
+__global__ void __launch_bounds__(RT_WARPS * 32) router_kernel(const RouterArgs a)
 {
-    float *score = reinterpret_cast<float *>(score_scratch);
-    G5B_LAUNCH(router_scores_kernel, dim3((s.NE + MOE_WARPS - 1) / MOE_WARPS, T), MOE_THREADS, 0, st,
-               score, x, ldx, gate, gate_dt, s.NE, s.E);
-    G5B_LAUNCH(router_topk_kernel, T, 32, 0, st, idx, w, score, bias, s.NE, s.K, s.norm_topk, s.routed_scale);
-}
-
-// -------------------------------------------------------------------- plan ----
-// Group the (token, slot) pairs by expert. Thread e gathers the pairs of local expert e in token
-// order; slots are numbered in expert order; the shared expert, when asked for, is the last slot
-// and takes every token.
-__global__ void __launch_bounds__(1024) moe_plan_kernel(MoePlan p, const int *idx, int T, int K,
-                                                       int n_local0, int n_local, int with_shared)
-{
-    __shared__ int cnt[G5B_MAX_EXPERTS];
-    __shared__ int off[G5B_MAX_EXPERTS];
-    __shared__ int slot[G5B_MAX_EXPERTS];
+    __shared__ float choice[RT_WARPS][G5B_MAX_EXPERTS];
+    __shared__ float wsel[RT_WARPS][G5B_MAX_TOPK];
+    __shared__ int cnt[G5B_MAX_EXPERTS], off[G5B_MAX_EXPERTS], slot[G5B_MAX_EXPERTS];
     __shared__ int totals[2];
-    const int e = threadIdx.x;
-    const int n = T * K;
-    int c = 0;
-    if (e < n_local)
-        for (int i = 0; i < n; i++) c += idx[i] == n_local0 + e;
-    if (e < n_local) cnt[e] = c;
+    __shared__ int is_last;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = blockIdx.x * RT_WARPS + warp, t = blockIdx.y;
+    if (e < a.NE) {
+        const float *xt = a.x + (size_t)t * a.ldx;
+        double acc = 0.0;
+        if (a.gate_dt == DT_BF16 && (a.E & 7) == 0 && (a.ldx & 3) == 0) {
+            const uint16_t *row = static_cast<const uint16_t *>(a.gate) + (size_t)e * a.E;
+#pragma unroll 4
+            for (int c = lane * 8; c < a.E; c += 256) {
+                const uint4 wv = ld_stream16(row + c);
+                const float4 x0 = *reinterpret_cast<const float4 *>(xt + c), x1 = *reinterpret_cast<const float4 *>(xt + c + 4);
+                float w[8];
+                bf16x2_to_f32(wv.x, w[0], w[1]); bf16x2_to_f32(wv.y, w[2], w[3]);
+                bf16x2_to_f32(wv.z, w[4], w[5]); bf16x2_to_f32(wv.w, w[6], w[7]);
+                acc = fma((double)w[0], (double)x0.x, acc); acc = fma((double)w[1], (double)x0.y, acc);
+                acc = fma((double)w[2], (double)x0.z, acc); acc = fma((double)w[3], (double)x0.w, acc);
+                acc = fma((double)w[4], (double)x1.x, acc); acc = fma((double)w[5], (double)x1.y, acc);
+                acc = fma((double)w[6], (double)x1.z, acc); acc = fma((double)w[7], (double)x1.w, acc);
+            }
+        } else if (a.gate_dt == DT_BF16) {
+            const uint16_t *row = static_cast<const uint16_t *>(a.gate) + (size_t)e * a.E;
+            for (int i = lane; i < a.E; i += 32) acc = fma((double)bf16_to_f32(row[i]), (double)xt[i], acc);
+        } else {
+            const float *row = static_cast<const float *>(a.gate) + (size_t)e * a.E;
+            for (int i = lane; i < a.E; i += 32) acc = fma((double)row[i], (double)xt[i], acc);
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) a.score[(size_t)t * a.NE + e] = sigmoid_host((float)acc);
+    }
+    // last CTA to finish does the selection and the grouping
+    __threadfence();
     __syncthreads();
-    if (e == 0) {
+    if (threadIdx.x == 0) {
+        const int total = gridDim.x * gridDim.y;
+        const int prev = atomicAdd(a.counter, 1);
+        is_last = prev == total - 1;
+        if (is_last) *a.counter = 0;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int tt = warp; tt < a.T; tt += RT_WARPS) topk_one_token(a, tt, choice[warp], wsel[warp], lane);
+    __syncthreads();
+    if (!a.p.n_slots) return;
+
+    // Group the (token, slot) pairs by expert: pairs of a local expert in token order, slots in
+    // expert order; the shared expert, when asked for, is the last slot and takes every token.
+    const int n = a.T * a.K;
+    for (int le = threadIdx.x; le < a.n_local; le += blockDim.x) {
+        int c = 0;
+        for (int i = 0; i < n; i++) c += a.idx[i] == a.n_local0 + le;
+        cnt[le] = c;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
         int o = 0, s = 0;
-        for (int i = 0; i < n_local; i++) {
+        for (int i = 0; i < a.n_local; i++) {
             off[i] = o; slot[i] = s;
             if (cnt[i]) { o += cnt[i]; s++; }
         }
         totals[0] = o; totals[1] = s;
     }
     __syncthreads();
-    if (e < n_local && c) {
-        const int s = slot[e];
-        p.slot_expert[s] = e; p.slot_off[s] = off[e]; p.slot_cnt[s] = c;
-        int o = off[e];
+    for (int le = threadIdx.x; le < a.n_local; le += blockDim.x) {
+        if (!cnt[le]) continue;
+        const int s = slot[le];
+        a.p.slot_expert[s] = le; a.p.slot_off[s] = off[le]; a.p.slot_cnt[s] = cnt[le];
+        int o = off[le];
         for (int i = 0; i < n; i++)
-            if (idx[i] == n_local0 + e) { p.pair_tok[o] = i / K; p.pair_dst[o] = i; o++; }
+            if (a.idx[i] == a.n_local0 + le) { a.p.pair_tok[o] = i / a.K; a.p.pair_dst[o] = i; o++; }
     }
-    if (with_shared) {
+    if (a.with_shared) {
         const int s = totals[1], o = totals[0];
-        if (e == 0) { p.slot_expert[s] = n_local; p.slot_off[s] = o; p.slot_cnt[s] = T; }
-        for (int t = e; t < T; t += blockDim.x) { p.pair_tok[o + t] = t; p.pair_dst[o + t] = n + t; }
+        if (threadIdx.x == 0) { a.p.slot_expert[s] = a.n_local; a.p.slot_off[s] = o; a.p.slot_cnt[s] = a.T; }
+        for (int tt = threadIdx.x; tt < a.T; tt += blockDim.x) { a.p.pair_tok[o + tt] = tt; a.p.pair_dst[o + tt] = n + tt; }
     }
-    if (e == 0) *p.n_slots = totals[1] + (with_shared ? 1 : 0);
+    if (threadIdx.x == 0) *a.p.n_slots = totals[1] + (a.with_shared ? 1 : 0);
 }
 
-void moe_plan(cudaStream_t st, const MoePlan &p, const int *idx, int T, const MoeShape &s, int with_shared)
+// p may be null-planned (p.n_slots == nullptr) when only the routing is wanted.
+void router_plan(cudaStream_t st, int *idx, float *w, float *score, const float *x, int ldx, const void *gate,
+                 int gate_dt, const float *bias, int T, const MoeShape &s, const MoePlan &p, int with_shared,
+                 int *counter)
 {
-    G5B_LAUNCH(moe_plan_kernel, 1, 1024, 0, st, p, idx, T, s.K, s.n_local0, s.n_local, with_shared);
+    RouterArgs a{idx, w, score, x, ldx, gate, gate_dt, bias, s.NE, s.E, s.K, T, s.norm_topk, s.routed_scale,
+                 p, s.n_local0, s.n_local, with_shared, counter};
+    G5B_LAUNCH(router_kernel, dim3((s.NE + RT_WARPS - 1) / RT_WARPS, T), RT_WARPS * 32, 0, st, a);
 }
 
 // ----------------------------------------------------------------- experts ----

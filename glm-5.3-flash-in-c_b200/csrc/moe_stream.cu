@@ -1,0 +1,317 @@
+// moe_stream.cu - the batch-1 (decode) expert kernels: weights streamed HBM -> shared memory by
+// the bulk-copy engine (cp.async.bulk + mbarrier), multiplied out of shared memory.
+//
+// Why: at one token per expert a warp-per-rows kernel keeps at most ~64 KB of loads in flight per
+// SM (registers bound it) and measured 40 % of DRAM throughput on B200, stalled on the scoreboard.
+// Here one producer warp keeps two 64 KB stages in flight per SM with no register cost while eight
+// consumer warps decode and multiply the third, so the memory system stays saturated.
+//
+//   gate/up  stage = 16 gate rows + the same 16 up rows, 2048 columns of each (two stages cover the
+//            4096 columns); a consumer warp owns two row pairs and writes SwiGLU(gate, up).
+//   down     stage = 32 output rows x 2048 columns plus the expert's activation vector; the CTA that
+//            finishes the last expert of a row tile also combines the K routed contributions in
+//            top-k order in FP64 and adds the shared expert (reference: src/core/glm53f_ops.c:
+//            1329-1340), so no separate combine launch is needed.
+//
+// Persistent grid: one CTA per SM walks work items blockIdx.x, +gridDim.x, ... Every wait on an
+// mbarrier is bounded; a wait that runs out records an error code in device memory, the CTA drains
+// the copies it has in flight (again bounded) and returns, and the host reports failure.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace g5b {
+
+constexpr int ST_ROWS = 32;                  // weight rows per stage
+constexpr int ST_CB = 2048;                  // bytes of each row per stage
+constexpr int ST_NS = 3;                     // stages
+constexpr int ST_CONS = 8;                   // consumer warps
+constexpr int ST_THREADS = (ST_CONS + 1) * 32;
+constexpr int ST_WAIT_LIMIT = 1 << 22;       // try_wait attempts before giving up (~ a second)
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false (and an error code in *err) when the barrier never completes.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *err, int code)
+{
+    for (int i = 0; i < ST_WAIT_LIMIT; i++)
+        if (mbar_try_wait(bar, parity)) return true;
+    atomicExch(err, code);
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src, uint32_t bytes, uint64_t *bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst_smem)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+// Position of column c in the activation layout the consumers read without bank conflicts: the
+// 16 columns a lane multiplies with one 16-byte piece of codes are stored as four float4 that are
+// `pieces` float4 apart, so that the 32 lanes of a warp read 32 consecutive float4.
+__host__ __device__ inline int perm_index(int c, int pieces)
+{
+    return (((c & 15) >> 2) * pieces + (c >> 4)) * 4 + (c & 3);
+}
+
+struct StreamArgs {
+    const ExpertW *experts;
+    MoePlan p;
+    const float *x;        // gate/up: the token's activation [E]; down: activations [pairs][I] (permuted)
+    float *y;              // gate/up: activations [pairs][I] (permuted); down: contributions [K(+1)][E]
+    int E, I, br, bc;
+    float limit;
+    // combine (down only)
+    float *out;
+    const float *w;
+    int K, with_shared;
+    int *tile_done;        // [rows_total / ST_ROWS] arrivals per row tile, zeroed by the last arrival
+    int *err;
+};
+
+__device__ __forceinline__ float swiglu_clamped_s(float g, float u, float lim)
+{
+    g = g > lim ? lim : g;
+    u = u > lim ? lim : (u < -lim ? -lim : u);
+    return __fmul_rn(__fmul_rn(g, sigmoid_host(g)), u);
+}
+
+template <bool GATEUP>
+__global__ void __launch_bounds__(ST_THREADS, 1) moe_stream_kernel(const StreamArgs a)
+{
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int C = GATEUP ? a.E : a.I;                 // columns of the matrices
+    const int rows_total = GATEUP ? a.I : a.E;
+    const int KH = C / ST_CB;                         // stages per work item
+    const int pieces = C / 16;
+    const int scols = C / a.bc;
+    const int rows_per_item = GATEUP ? ST_ROWS / 2 : ST_ROWS;
+    const int tps = rows_total / rows_per_item;       // work items per expert
+    // stage layout: weights | scale rows (2 x 64 floats) | activation vector (down only)
+    const size_t scale_off = (size_t)ST_ROWS * ST_CB;
+    const size_t act_off = scale_off + 512;
+    const size_t stage_bytes = act_off + (GATEUP ? 0 : (size_t)a.I * 4);
+    uint8_t *stages = smem;
+    float *x_s = reinterpret_cast<float *>(smem + ST_NS * stage_bytes);          // gate/up only: [E] permuted
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + ST_NS * stage_bytes + (GATEUP ? (size_t)a.E * 4 : 0));
+    uint64_t *empty = full + ST_NS;
+    __shared__ int last_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < ST_NS; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], ST_CONS); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (GATEUP) {
+        for (int c = threadIdx.x; c < a.E; c += ST_THREADS) x_s[perm_index(c, pieces)] = a.x[c];
+    }
+    __syncthreads();
+
+    const int n_items = *a.p.n_slots * tps;
+    bool ok = true;
+
+    if (warp == ST_CONS) {
+        // ---------------------------------------------------------------- producer ----
+        int it = 0;
+        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+            const int slot = item / tps, rt = item % tps;
+            const ExpertW ew = a.experts[a.p.slot_expert[slot]];
+            const int pair = a.p.slot_off[slot];
+            for (int kh = 0; kh < KH && ok; kh++, it++) {
+                const int s = it % ST_NS;
+                if (it >= ST_NS) ok = mbar_wait(&empty[s], ((it / ST_NS) - 1) & 1, a.err, 1);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                uint8_t *st = stages + (size_t)s * stage_bytes;
+                const uint32_t bytes = ST_ROWS * ST_CB + (GATEUP ? 2 : 1) * scols * 4 + (GATEUP ? 0 : a.I * 4);
+                if (lane == 0) mbar_expect_tx(&full[s], bytes);
+                __syncwarp();
+                const uint8_t *src;
+                if (GATEUP) src = (lane < 16 ? ew.gate : ew.up) + (size_t)(rt * 16 + (lane & 15)) * C + (size_t)kh * ST_CB;
+                else        src = ew.down + (size_t)(rt * ST_ROWS + lane) * C + (size_t)kh * ST_CB;
+                bulk_g2s(st + (size_t)lane * ST_CB, src, ST_CB, &full[s]);
+                if (lane == 0) {
+                    const int r0 = rt * rows_per_item;
+                    if (GATEUP) {
+                        bulk_g2s(st + scale_off, ew.gate_s + (size_t)(r0 / a.br) * scols, scols * 4, &full[s]);
+                        bulk_g2s(st + scale_off + 256, ew.up_s + (size_t)(r0 / a.br) * scols, scols * 4, &full[s]);
+                    } else {
+                        bulk_g2s(st + scale_off, ew.down_s + (size_t)(r0 / a.br) * scols, scols * 4, &full[s]);
+                        bulk_g2s(st + act_off, a.x + (size_t)pair * a.I, a.I * 4, &full[s]);
+                    }
+                }
+            }
+        }
+        // copies in flight must land before the CTA's shared memory goes away
+        if (!ok) {
+            for (int k = 0; k < ST_NS && k < it; k++) {
+                const int j = it - 1 - k;
+                mbar_wait(&full[j % ST_NS], (j / ST_NS) & 1, a.err, 3);
+            }
+        }
+    } else {
+        // --------------------------------------------------------------- consumers ----
+        int it = 0;
+        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+            const int slot = item / tps, rt = item % tps;
+            const int pair = a.p.slot_off[slot];
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int kh = 0; kh < KH && ok; kh++, it++) {
+                const int s = it % ST_NS;
+                ok = mbar_wait(&full[s], (it / ST_NS) & 1, a.err, 2);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                const uint8_t *st = stages + (size_t)s * stage_bytes;
+                const float *sc = reinterpret_cast<const float *>(st + scale_off);
+                const float *xv = GATEUP ? x_s : reinterpret_cast<const float *>(st + act_off);
+                const uint8_t *w0, *w1, *w2, *w3;
+                if (GATEUP) {
+                    w0 = st + (size_t)(2 * warp) * ST_CB;      w1 = w0 + ST_CB;
+                    w2 = st + (size_t)(16 + 2 * warp) * ST_CB; w3 = w2 + ST_CB;
+                } else {
+                    w0 = st + (size_t)(4 * warp) * ST_CB; w1 = w0 + ST_CB; w2 = w1 + ST_CB; w3 = w2 + ST_CB;
+                }
+#pragma unroll
+                for (int j = 0; j < ST_CB / 16 / 32; j++) {
+                    const int piece = lane + 32 * j;                       // within this stage
+                    const int gpiece = kh * (ST_CB / 16) + piece;          // within the row
+                    float xr[16];
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        const float4 v = *reinterpret_cast<const float4 *>(xv + ((size_t)k * pieces + gpiece) * 4);
+                        xr[4 * k] = v.x; xr[4 * k + 1] = v.y; xr[4 * k + 2] = v.z; xr[4 * k + 3] = v.w;
+                    }
+                    const int cb = (gpiece * 16) / a.bc;
+                    const float s_a = sc[cb], s_b = GATEUP ? sc[64 + cb] : s_a;
+                    const uint8_t *wp[4] = {w0, w1, w2, w3};
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        const uint4 wv = *reinterpret_cast<const uint4 *>(wp[q] + (size_t)piece * 16);
+                        float w[16];
+                        e4m3x4_to_f32(wv.x, w[0], w[1], w[2], w[3]);
+                        e4m3x4_to_f32(wv.y, w[4], w[5], w[6], w[7]);
+                        e4m3x4_to_f32(wv.z, w[8], w[9], w[10], w[11]);
+                        e4m3x4_to_f32(wv.w, w[12], w[13], w[14], w[15]);
+                        float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+                        for (int e = 0; e < 16; e += 2) {
+                            s0 = fmaf(w[e], xr[e], s0);
+                            s1 = fmaf(w[e + 1], xr[e + 1], s1);
+                        }
+                        acc[q] = fmaf(s0 + s1, (GATEUP && q >= 2) ? s_b : s_a, acc[q]);
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[s]);
+            }
+            if (!ok) break;
+#pragma unroll
+            for (int q = 0; q < 4; q++) acc[q] = warp_sum(acc[q]);
+            if (GATEUP) {
+                if (lane == 0) {
+                    const int r = rt * 16 + 2 * warp;
+                    float *dst = a.y + (size_t)pair * a.I;
+                    const int ap = a.I / 16;
+                    dst[perm_index(r, ap)] = swiglu_clamped_s(acc[0], acc[2], a.limit);
+                    dst[perm_index(r + 1, ap)] = swiglu_clamped_s(acc[1], acc[3], a.limit);
+                }
+            } else {
+                const int r = rt * ST_ROWS + 4 * warp;
+                if (lane < 4) {
+                    const float v = lane == 0 ? acc[0] : lane == 1 ? acc[1] : lane == 2 ? acc[2] : acc[3];
+                    a.y[(size_t)a.p.pair_dst[pair] * a.E + r + lane] = v;
+                }
+                if (!a.out) continue;
+                // The CTA that finishes the last expert of this row tile combines the tile.
+                __threadfence();
+                asm volatile("bar.sync 1, %0;" ::"r"(ST_CONS * 32) : "memory");
+                if (threadIdx.x == 0) {
+                    const int n = *a.p.n_slots;
+                    const int prev = atomicAdd(&a.tile_done[rt], 1);
+                    last_flag = prev == n - 1;
+                    if (last_flag) a.tile_done[rt] = 0;
+                }
+                asm volatile("bar.sync 1, %0;" ::"r"(ST_CONS * 32) : "memory");
+                if (last_flag && threadIdx.x < ST_ROWS) {
+                    __threadfence();
+                    const int d = rt * ST_ROWS + threadIdx.x;
+                    double sum = 0.0;
+                    for (int j = 0; j < a.K; j++)
+                        sum += (double)a.w[j] * (double)__ldcg(a.y + (size_t)j * a.E + d);
+                    float o = (float)sum;
+                    if (a.with_shared) o = __fadd_rn(o, __ldcg(a.y + (size_t)a.K * a.E + d));
+                    a.out[d] = o;
+                }
+            }
+        }
+    }
+}
+
+size_t stream_smem_bytes(bool gateup, int E, int I)
+{
+    const size_t stage = (size_t)ST_ROWS * ST_CB + 512 + (gateup ? 0 : (size_t)I * 4);
+    return ST_NS * stage + (gateup ? (size_t)E * 4 : 0) + 2 * ST_NS * sizeof(uint64_t) + 64;
+}
+
+// The streamed path serves FP8 experts whose shapes tile evenly; everything else keeps the
+// register-streaming kernels of moe.cu.
+bool moe_stream_supported(const MoeShape &s, int T)
+{
+    if (T != 1 || s.dt != DT_FP8) return false;
+    if (s.E % ST_CB || s.I % ST_CB || s.I % 16 || s.E % ST_ROWS) return false;
+    if (s.bc < 16 || s.bc % 16 || s.br % ST_ROWS || s.E / s.bc > 64 || s.I / s.bc > 64) return false;
+    if ((s.E / s.bc) % 4 || (s.I / s.bc) % 4) return false;          // scale rows copied in 16-byte units
+    if (stream_smem_bytes(true, s.E, s.I) > 227 * 1024 || stream_smem_bytes(false, s.E, s.I) > 227 * 1024) return false;
+    return true;
+}
+
+static int g_sms = 0;
+static int sm_count()
+{
+    if (!g_sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev);
+        if (g_sms < 1) g_sms = 148;
+    }
+    return g_sms;
+}
+
+void moe_stream_gateup(cudaStream_t st, float *act, const float *x, const ExpertW *experts, const MoePlan &p,
+                       const MoeShape &s, int *err)
+{
+    StreamArgs a{experts, p, x, act, s.E, s.I, s.br, s.bc, s.limit, nullptr, nullptr, s.K, 0, nullptr, err};
+    const size_t smem = stream_smem_bytes(true, s.E, s.I);
+    static bool attr = false;
+    if (!attr) { cudaFuncSetAttribute(moe_stream_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); attr = true; }
+    G5B_LAUNCH(moe_stream_kernel<true>, sm_count(), ST_THREADS, smem, st, a);
+}
+
+void moe_stream_down(cudaStream_t st, float *out, float *contrib, const float *act, const float *w,
+                     const ExpertW *experts, const MoePlan &p, const MoeShape &s, int with_shared,
+                     int *tile_done, int *err)
+{
+    StreamArgs a{experts, p, act, contrib, s.E, s.I, s.br, s.bc, s.limit, out, w, s.K, with_shared, tile_done, err};
+    const size_t smem = stream_smem_bytes(false, s.E, s.I);
+    static bool attr = false;
+    if (!attr) { cudaFuncSetAttribute(moe_stream_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); attr = true; }
+    G5B_LAUNCH(moe_stream_kernel<false>, sm_count(), ST_THREADS, smem, st, a);
+}
+
+}  // namespace g5b

@@ -89,3 +89,18 @@ def test_full_size_mla_layer(gpu_lib, binding, latent_bf16):
             assert len(ws) in (2048, 2049, 2050, 2051) and np.array_equal(gs, ws), ctx
         assert common.rel_err(g, w) < (3e-3 if latent_bf16 else 1e-4), ctx
     eng.close(); orc.close()
+
+
+def test_streamed_and_register_expert_kernels_agree(moe_layer):
+    """Batch 1 runs the bulk-copy streamed kernels by default; the register-streaming kernels (the
+    path batches take) must give the same layer output to FP32 rounding."""
+    spec, trunk, eng = moe_layer
+    x = synth.moe_inputs(spec.cfg, 1, SEED + 3)
+    a = eng.op_moe(0, x)
+    eng.set_option("stream_experts", 0)
+    b = eng.op_moe(0, x)
+    eng.set_option("stream_experts", 1)
+    c = eng.op_moe(0, x)
+    assert np.array_equal(a, c)
+    assert common.rel_err(a, b) < 2e-6
+    assert common.rel_err(eng.op_moe(0, x, False), eng.op_moe(0, x, True)) > 1e-3   # the shared expert matters
