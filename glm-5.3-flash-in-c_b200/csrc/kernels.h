@@ -101,11 +101,11 @@ void router_plan(cudaStream_t st, int *idx, float *w, float *score, const float 
 // Batch-1 experts streamed through shared memory by the bulk-copy engine (moe_stream.cu).
 bool moe_stream_supported(const MoeShape &s, int T);
 void moe_stream_gateup(cudaStream_t st, float *act, const float *x, const ExpertW *experts, const MoePlan &p,
-                       const MoeShape &s, int *err);
+                       const MoeShape &s, int *err, int warps);
 // out == nullptr: contributions only (the caller combines, e.g. after an expert-parallel exchange).
 void moe_stream_down(cudaStream_t st, float *out, float *contrib, const float *act, const float *w,
                      const ExpertW *experts, const MoePlan &p, const MoeShape &s, int with_shared,
-                     int *tile_done, int *err);
+                     int *tile_done, int *err, int warps);
 void moe_gateup(cudaStream_t st, float *act, const float *x, int ldx, const ExpertW *experts,
                 const MoePlan &p, int T, const MoeShape &s);
 void moe_down(cudaStream_t st, float *contrib, const float *act, const ExpertW *experts,

@@ -132,9 +132,12 @@ __global__ void __launch_bounds__(RT_WARPS * 32) router_kernel(const RouterArgs 
     // Group the (token, slot) pairs by expert: pairs of a local expert in token order, slots in
     // expert order; the shared expert, when asked for, is the last slot and takes every token.
     const int n = a.T * a.K;
+    int *sidx = reinterpret_cast<int *>(&choice[0][0]);      // selection is done: reuse as [T*K] ids
+    for (int i = threadIdx.x; i < n; i += blockDim.x) sidx[i] = a.idx[i];
+    __syncthreads();
     for (int le = threadIdx.x; le < a.n_local; le += blockDim.x) {
         int c = 0;
-        for (int i = 0; i < n; i++) c += a.idx[i] == a.n_local0 + le;
+        for (int i = 0; i < n; i++) c += sidx[i] == a.n_local0 + le;
         cnt[le] = c;
     }
     __syncthreads();
@@ -153,7 +156,7 @@ __global__ void __launch_bounds__(RT_WARPS * 32) router_kernel(const RouterArgs 
         a.p.slot_expert[s] = le; a.p.slot_off[s] = off[le]; a.p.slot_cnt[s] = cnt[le];
         int o = off[le];
         for (int i = 0; i < n; i++)
-            if (a.idx[i] == a.n_local0 + le) { a.p.pair_tok[o] = i / a.K; a.p.pair_dst[o] = i; o++; }
+            if (sidx[i] == a.n_local0 + le) { a.p.pair_tok[o] = i / a.K; a.p.pair_dst[o] = i; o++; }
     }
     if (a.with_shared) {
         const int s = totals[1], o = totals[0];

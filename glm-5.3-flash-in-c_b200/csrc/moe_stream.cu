@@ -24,8 +24,7 @@ namespace g5b {
 constexpr int ST_ROWS = 32;                  // weight rows per stage
 constexpr int ST_CB = 2048;                  // bytes of each row per stage
 constexpr int ST_NS = 3;                     // stages
-constexpr int ST_CONS = 8;                   // consumer warps
-constexpr int ST_THREADS = (ST_CONS + 1) * 32;
+constexpr int ST_MAX_ITEMS = 32;             // work items one CTA may own (down: combine bookkeeping)
 constexpr int ST_WAIT_LIMIT = 1 << 22;       // try_wait attempts before giving up (~ a second)
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -92,9 +91,12 @@ __device__ __forceinline__ float swiglu_clamped_s(float g, float u, float lim)
     return __fmul_rn(__fmul_rn(g, sigmoid_host(g)), u);
 }
 
-template <bool GATEUP>
-__global__ void __launch_bounds__(ST_THREADS, 1) moe_stream_kernel(const StreamArgs a)
+// NW consumer warps share the 32 rows of a stage (4 rows each at NW = 8, 2 at NW = 16); warp NW is
+// the producer.
+template <bool GATEUP, int NW>
+__global__ void __launch_bounds__((NW + 1) * 32, 1) moe_stream_kernel(const StreamArgs a)
 {
+    constexpr int ST_CONS = NW, ST_THREADS = (NW + 1) * 32, RPW = ST_ROWS / NW;
     extern __shared__ __align__(128) uint8_t smem[];
     const int C = GATEUP ? a.E : a.I;                 // columns of the matrices
     const int rows_total = GATEUP ? a.I : a.E;
@@ -111,7 +113,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) moe_stream_kernel(const StreamA
     float *x_s = reinterpret_cast<float *>(smem + ST_NS * stage_bytes);          // gate/up only: [E] permuted
     uint64_t *full = reinterpret_cast<uint64_t *>(smem + ST_NS * stage_bytes + (GATEUP ? (size_t)a.E * 4 : 0));
     uint64_t *empty = full + ST_NS;
-    __shared__ int last_flag;
+    __shared__ int my_tiles[ST_MAX_ITEMS], my_last[ST_MAX_ITEMS];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -171,7 +173,9 @@ __global__ void __launch_bounds__(ST_THREADS, 1) moe_stream_kernel(const StreamA
         for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
             const int slot = item / tps, rt = item % tps;
             const int pair = a.p.slot_off[slot];
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            float acc[RPW];
+#pragma unroll
+            for (int q = 0; q < RPW; q++) acc[q] = 0.f;
             for (int kh = 0; kh < KH && ok; kh++, it++) {
                 const int s = it % ST_NS;
                 ok = mbar_wait(&full[s], (it / ST_NS) & 1, a.err, 2);
@@ -180,12 +184,13 @@ __global__ void __launch_bounds__(ST_THREADS, 1) moe_stream_kernel(const StreamA
                 const uint8_t *st = stages + (size_t)s * stage_bytes;
                 const float *sc = reinterpret_cast<const float *>(st + scale_off);
                 const float *xv = GATEUP ? x_s : reinterpret_cast<const float *>(st + act_off);
-                const uint8_t *w0, *w1, *w2, *w3;
-                if (GATEUP) {
-                    w0 = st + (size_t)(2 * warp) * ST_CB;      w1 = w0 + ST_CB;
-                    w2 = st + (size_t)(16 + 2 * warp) * ST_CB; w3 = w2 + ST_CB;
-                } else {
-                    w0 = st + (size_t)(4 * warp) * ST_CB; w1 = w0 + ST_CB; w2 = w1 + ST_CB; w3 = w2 + ST_CB;
+                // gate/up: the first RPW/2 rows of a warp are gate rows, the rest the same up rows
+                const uint8_t *wp[RPW];
+#pragma unroll
+                for (int q = 0; q < RPW; q++) {
+                    const int row = GATEUP ? (q < RPW / 2 ? (RPW / 2) * warp + q : 16 + (RPW / 2) * warp + (q - RPW / 2))
+                                           : RPW * warp + q;
+                    wp[q] = st + (size_t)row * ST_CB;
                 }
 #pragma unroll
                 for (int j = 0; j < ST_CB / 16 / 32; j++) {
@@ -199,9 +204,8 @@ __global__ void __launch_bounds__(ST_THREADS, 1) moe_stream_kernel(const StreamA
                     }
                     const int cb = (gpiece * 16) / a.bc;
                     const float s_a = sc[cb], s_b = GATEUP ? sc[64 + cb] : s_a;
-                    const uint8_t *wp[4] = {w0, w1, w2, w3};
 #pragma unroll
-                    for (int q = 0; q < 4; q++) {
+                    for (int q = 0; q < RPW; q++) {
                         const uint4 wv = *reinterpret_cast<const uint4 *>(wp[q] + (size_t)piece * 16);
                         float w[16];
                         e4m3x4_to_f32(wv.x, w[0], w[1], w[2], w[3]);
@@ -214,7 +218,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) moe_stream_kernel(const StreamA
                             s0 = fmaf(w[e], xr[e], s0);
                             s1 = fmaf(w[e + 1], xr[e + 1], s1);
                         }
-                        acc[q] = fmaf(s0 + s1, (GATEUP && q >= 2) ? s_b : s_a, acc[q]);
+                        acc[q] = fmaf(s0 + s1, (GATEUP && q >= RPW / 2) ? s_b : s_a, acc[q]);
                     }
                 }
                 __syncwarp();
@@ -222,42 +226,52 @@ __global__ void __launch_bounds__(ST_THREADS, 1) moe_stream_kernel(const StreamA
             }
             if (!ok) break;
 #pragma unroll
-            for (int q = 0; q < 4; q++) acc[q] = warp_sum(acc[q]);
+            for (int q = 0; q < RPW; q++) acc[q] = warp_sum(acc[q]);
             if (GATEUP) {
                 if (lane == 0) {
-                    const int r = rt * 16 + 2 * warp;
                     float *dst = a.y + (size_t)pair * a.I;
                     const int ap = a.I / 16;
-                    dst[perm_index(r, ap)] = swiglu_clamped_s(acc[0], acc[2], a.limit);
-                    dst[perm_index(r + 1, ap)] = swiglu_clamped_s(acc[1], acc[3], a.limit);
+#pragma unroll
+                    for (int q = 0; q < RPW / 2; q++) {
+                        const int r = rt * 16 + (RPW / 2) * warp + q;
+                        dst[perm_index(r, ap)] = swiglu_clamped_s(acc[q], acc[RPW / 2 + q], a.limit);
+                    }
                 }
             } else {
-                const int r = rt * ST_ROWS + 4 * warp;
-                if (lane < 4) {
-                    const float v = lane == 0 ? acc[0] : lane == 1 ? acc[1] : lane == 2 ? acc[2] : acc[3];
-                    a.y[(size_t)a.p.pair_dst[pair] * a.E + r + lane] = v;
+                const int r = rt * ST_ROWS + RPW * warp;
+                if (lane == 0) {
+#pragma unroll
+                    for (int q = 0; q < RPW; q++) a.y[(size_t)a.p.pair_dst[pair] * a.E + r + q] = acc[q];
                 }
-                if (!a.out) continue;
-                // The CTA that finishes the last expert of this row tile combines the tile.
-                __threadfence();
-                asm volatile("bar.sync 1, %0;" ::"r"(ST_CONS * 32) : "memory");
-                if (threadIdx.x == 0) {
-                    const int n = *a.p.n_slots;
-                    const int prev = atomicAdd(&a.tile_done[rt], 1);
-                    last_flag = prev == n - 1;
-                    if (last_flag) a.tile_done[rt] = 0;
-                }
-                asm volatile("bar.sync 1, %0;" ::"r"(ST_CONS * 32) : "memory");
-                if (last_flag && threadIdx.x < ST_ROWS) {
-                    __threadfence();
-                    const int d = rt * ST_ROWS + threadIdx.x;
-                    double sum = 0.0;
-                    for (int j = 0; j < a.K; j++)
-                        sum += (double)a.w[j] * (double)__ldcg(a.y + (size_t)j * a.E + d);
-                    float o = (float)sum;
-                    if (a.with_shared) o = __fadd_rn(o, __ldcg(a.y + (size_t)a.K * a.E + d));
-                    a.out[d] = o;
-                }
+            }
+        }
+        if (!GATEUP && a.out && ok) {
+            // Combine, once per CTA after all of its items: every item reports its row tile; the CTA
+            // whose report completes a tile (all experts of the token have written it) sums the K
+            // contributions of that tile in top-k order in FP64 and adds the shared expert.
+            __threadfence();
+            asm volatile("bar.sync 1, %0;" ::"r"(ST_CONS * 32) : "memory");
+            const int n = *a.p.n_slots;
+            int mine = 0;
+            for (int item = blockIdx.x; item < n_items; item += gridDim.x) mine++;
+            if (mine > ST_MAX_ITEMS) { if (threadIdx.x == 0) atomicExch(a.err, 4); mine = 0; }
+            if ((int)threadIdx.x < mine) {
+                const int rt = (blockIdx.x + threadIdx.x * gridDim.x) % tps;
+                const int prev = atomicAdd(&a.tile_done[rt], 1);
+                my_tiles[threadIdx.x] = rt;
+                my_last[threadIdx.x] = prev == n - 1;
+                if (prev == n - 1) a.tile_done[rt] = 0;
+            }
+            asm volatile("bar.sync 1, %0;" ::"r"(ST_CONS * 32) : "memory");
+            __threadfence();
+            for (int k = warp; k < mine; k += ST_CONS) {
+                if (!my_last[k]) continue;
+                const int d = my_tiles[k] * ST_ROWS + lane;
+                double sum = 0.0;
+                for (int j = 0; j < a.K; j++) sum += (double)a.w[j] * (double)__ldcg(a.y + (size_t)j * a.E + d);
+                float o = (float)sum;
+                if (a.with_shared) o = __fadd_rn(o, __ldcg(a.y + (size_t)a.K * a.E + d));
+                a.out[d] = o;
             }
         }
     }
@@ -293,25 +307,34 @@ static int sm_count()
     return g_sms;
 }
 
+template <bool GATEUP, int NW>
+static void launch_stream(cudaStream_t st, const StreamArgs &a, size_t smem)
+{
+    static bool attr = false;
+    if (!attr) {
+        cudaFuncSetAttribute(moe_stream_kernel<GATEUP, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attr = true;
+    }
+    G5B_LAUNCH((moe_stream_kernel<GATEUP, NW>), sm_count(), (NW + 1) * 32, smem, st, a);
+}
+
 void moe_stream_gateup(cudaStream_t st, float *act, const float *x, const ExpertW *experts, const MoePlan &p,
-                       const MoeShape &s, int *err)
+                       const MoeShape &s, int *err, int warps)
 {
     StreamArgs a{experts, p, x, act, s.E, s.I, s.br, s.bc, s.limit, nullptr, nullptr, s.K, 0, nullptr, err};
     const size_t smem = stream_smem_bytes(true, s.E, s.I);
-    static bool attr = false;
-    if (!attr) { cudaFuncSetAttribute(moe_stream_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); attr = true; }
-    G5B_LAUNCH(moe_stream_kernel<true>, sm_count(), ST_THREADS, smem, st, a);
+    if (warps == 8) launch_stream<true, 8>(st, a, smem);
+    else            launch_stream<true, 16>(st, a, smem);
 }
 
 void moe_stream_down(cudaStream_t st, float *out, float *contrib, const float *act, const float *w,
                      const ExpertW *experts, const MoePlan &p, const MoeShape &s, int with_shared,
-                     int *tile_done, int *err)
+                     int *tile_done, int *err, int warps)
 {
     StreamArgs a{experts, p, act, contrib, s.E, s.I, s.br, s.bc, s.limit, out, w, s.K, with_shared, tile_done, err};
     const size_t smem = stream_smem_bytes(false, s.E, s.I);
-    static bool attr = false;
-    if (!attr) { cudaFuncSetAttribute(moe_stream_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); attr = true; }
-    G5B_LAUNCH(moe_stream_kernel<false>, sm_count(), ST_THREADS, smem, st, a);
+    if (warps == 8) launch_stream<false, 8>(st, a, smem);
+    else            launch_stream<false, 16>(st, a, smem);
 }
 
 }  // namespace g5b
