@@ -187,7 +187,9 @@ def main():
                     help="routed experts resident in the layer (288 = the stated config; fewer only to keep "
                          "an ncu capture small: the batch-1 kernels touch 8 routed + 1 shared either way)")
     ap.add_argument("--batches", default="8,64", help="extra batch sizes reported under 'extra'")
-    ap.add_argument("--stream-warps", type=int, default=0, help="consumer warps of the streamed expert kernels (8/16)")
+    ap.add_argument("--stream-warps", type=int, default=0, help="consumer warps of the streamed CUDA-core kernels (8/16)")
+    ap.add_argument("--expert-path", type=int, default=-1,
+                    help="batch-1 expert kernels: 0 register-streaming, 1 bulk-copy + CUDA cores, 2 bulk-copy + tensor cores (default)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -212,6 +214,8 @@ def main():
     opts = {"profile": 1}
     if args.stream_warps:
         opts["stream_warps"] = args.stream_warps
+    if args.expert_path >= 0:
+        opts["stream_experts"] = args.expert_path
     spec, trunk, eng = synth.build_moe_layer_engine(SEED, n_experts=args.experts, device=local, options=opts)
     sampler = ClockSampler(local)
 
@@ -262,7 +266,7 @@ def main():
     peak, peak_kind = measured_peaks()
     gateup_ms = phases[1]
     achieved = 9 * GATEUP_BYTES / (gateup_ms * 1e-3) / 1e9 if gateup_ms > 0 else 0.0
-    roofline = {"bound": "hbm", "kernel": "moe_stream_kernel<gate/up> (8 routed + 1 shared expert, batch 1)",
+    roofline = {"bound": "hbm", "kernel": "moe_mma_kernel<gate/up> (8 routed + 1 shared expert, batch 1)",
                 "achieved": achieved, "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s",
                 "frac": achieved / peak, "traffic": GATEUP_TRAFFIC_NCU,
                 "algorithmic_bytes_per_launch": 9 * GATEUP_BYTES, "ms_per_launch": gateup_ms,

@@ -78,7 +78,7 @@ struct g5b_engine {
     g5b_config c;
     int cap = 0, cached = 0, device = 0, ep_rank = 0, ep_size = 1, n_local0 = 0, n_local = 0;
     bool finalized = false;
-    int latent_bf16 = 0, profile = 0, partial = 0, stream_experts = 1, stream_warps = 16;
+    int latent_bf16 = 0, profile = 0, partial = 0, stream_experts = 2, stream_warps = 8;
     int *counter = nullptr, *tile_done = nullptr, *err_dev = nullptr;
     volatile int *err_host = nullptr;   // mapped host memory: kernels record a timed-out wait here
     cudaStream_t st = nullptr;
@@ -253,7 +253,11 @@ extern "C" int g5b_engine_set_option(g5b_engine *e, const char *name, int value)
     }
     if (!strcmp(name, "profile")) { e->profile = value; return 0; }
     if (!strcmp(name, "allow_partial")) { e->partial = value != 0; return 0; }
-    if (!strcmp(name, "stream_experts")) { e->stream_experts = value != 0; return 0; }
+    if (!strcmp(name, "stream_experts")) {       // 0 register kernels, 1 streamed CUDA-core, 2 streamed tensor-core
+        if (value < 0 || value > 2) return fail("stream_experts is 0, 1 or 2");
+        e->stream_experts = value;
+        return 0;
+    }
     if (!strcmp(name, "stream_warps")) {
         if (value != 8 && value != 16) return fail("stream_warps is 8 or 16");
         e->stream_warps = value;
@@ -553,7 +557,17 @@ static int run_moe(g5b_engine *e, Layer &w, const float *x, int n, float *out, i
     router_plan(e->st, e->ridx, e->rw, e->rscore, x, c.hidden, w.router.w, w.router.dt, w.bias, n, s, e->plan,
                 shared_in_plan ? 1 : 0, e->counter);
     prof_mark(e, 1);
-    if (e->stream_experts && e->ep_size == 1 && (shared_in_plan || !with_shared) && moe_stream_supported(s, n)) {
+    const bool one_gpu_decode = e->ep_size == 1 && (shared_in_plan || !with_shared);
+    if (e->stream_experts == 2 && one_gpu_decode && moe_mma_supported(s, n)) {
+        moe_mma_gateup(e->st, e->act, x, w.table_dev, e->plan, s, e->err_dev);
+        prof_mark(e, 2);
+        moe_mma_down(e->st, out, e->contrib, e->act, e->rw, w.table_dev, e->plan, s, with_shared, e->tile_done, e->err_dev);
+        prof_mark(e, 3);
+        prof_mark(e, 4);
+        prof_collect(e, 4);
+        return 0;
+    }
+    if (e->stream_experts && one_gpu_decode && moe_stream_supported(s, n)) {
         moe_stream_gateup(e->st, e->act, x, w.table_dev, e->plan, s, e->err_dev, e->stream_warps);
         prof_mark(e, 2);
         moe_stream_down(e->st, out, e->contrib, e->act, e->rw, w.table_dev, e->plan, s, with_shared, e->tile_done,

@@ -102,6 +102,14 @@ void router_plan(cudaStream_t st, int *idx, float *w, float *score, const float 
 bool moe_stream_supported(const MoeShape &s, int T);
 void moe_stream_gateup(cudaStream_t st, float *act, const float *x, const ExpertW *experts, const MoePlan &p,
                        const MoeShape &s, int *err, int warps);
+// Batch-1 experts multiplied by the tensor cores from their FP8 codes (moe_mma.cu); act_terms holds
+// the SwiGLU output split into two F16 terms per element, [pairs][2][I].
+bool moe_mma_supported(const MoeShape &s, int T);
+void moe_mma_gateup(cudaStream_t st, void *act_terms, const float *x, const ExpertW *experts, const MoePlan &p,
+                    const MoeShape &s, int *err);
+void moe_mma_down(cudaStream_t st, float *out, float *contrib, const void *act_terms, const float *w,
+                  const ExpertW *experts, const MoePlan &p, const MoeShape &s, int with_shared, int *tile_done,
+                  int *err);
 // out == nullptr: contributions only (the caller combines, e.g. after an expert-parallel exchange).
 void moe_stream_down(cudaStream_t st, float *out, float *contrib, const float *act, const float *w,
                      const ExpertW *experts, const MoePlan &p, const MoeShape &s, int with_shared,

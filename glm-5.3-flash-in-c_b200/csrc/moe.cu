@@ -42,10 +42,14 @@ struct RouterArgs {
     int *counter;
 };
 
-__device__ void topk_one_token(const RouterArgs &a, int t, float *choice, float *wsel, int lane)
+__device__ void topk_one_token(const RouterArgs &a, int t, float *choice, float *scr, float *wsel, int lane)
 {
     const float *sc = a.score + (size_t)t * a.NE;
-    for (int e = lane; e < a.NE; e += 32) choice[e] = __fadd_rn(__ldcg(sc + e), a.bias[e]);
+    for (int e = lane; e < a.NE; e += 32) {
+        const float v = __ldcg(sc + e);
+        scr[e] = v;
+        choice[e] = __fadd_rn(v, a.bias[e]);
+    }
     __syncwarp();
     for (int j = 0; j < a.K; j++) {
         float bv = -INFINITY;
@@ -61,7 +65,7 @@ __device__ void topk_one_token(const RouterArgs &a, int t, float *choice, float 
         if (bi < 0) bi = 0;                        // every score NaN: the reference aborts here
         if (lane == 0) {
             a.idx[(size_t)t * a.K + j] = bi;
-            wsel[j] = __ldcg(sc + bi);
+            wsel[j] = scr[bi];
             choice[bi] = -INFINITY;
         }
         __syncwarp();
@@ -80,11 +84,12 @@ __device__ void topk_one_token(const RouterArgs &a, int t, float *choice, float 
 __global__ void __launch_bounds__(RT_WARPS * 32) router_kernel(const RouterArgs a)
 {
     __shared__ float choice[RT_WARPS][G5B_MAX_EXPERTS];
+    __shared__ float scr[RT_WARPS][G5B_MAX_EXPERTS];
     __shared__ float wsel[RT_WARPS][G5B_MAX_TOPK];
-    __shared__ int cnt[G5B_MAX_EXPERTS], off[G5B_MAX_EXPERTS], slot[G5B_MAX_EXPERTS];
-    __shared__ int totals[2];
+    __shared__ int cnt[G5B_MAX_EXPERTS], off[G5B_MAX_EXPERTS];
+    __shared__ int psum[RT_WARPS * 32], ssum[RT_WARPS * 32];
     __shared__ int is_last;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
     const int e = blockIdx.x * RT_WARPS + warp, t = blockIdx.y;
     if (e < a.NE) {
         const float *xt = a.x + (size_t)t * a.ldx;
@@ -116,7 +121,7 @@ __global__ void __launch_bounds__(RT_WARPS * 32) router_kernel(const RouterArgs 
     // last CTA to finish does the selection and the grouping
     __threadfence();
     __syncthreads();
-    if (threadIdx.x == 0) {
+    if (tid == 0) {
         const int total = gridDim.x * gridDim.y;
         const int prev = atomicAdd(a.counter, 1);
         is_last = prev == total - 1;
@@ -125,45 +130,63 @@ __global__ void __launch_bounds__(RT_WARPS * 32) router_kernel(const RouterArgs 
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    for (int tt = warp; tt < a.T; tt += RT_WARPS) topk_one_token(a, tt, choice[warp], wsel[warp], lane);
+    for (int tt = warp; tt < a.T; tt += RT_WARPS) topk_one_token(a, tt, choice[warp], scr[warp], wsel[warp], lane);
     __syncthreads();
     if (!a.p.n_slots) return;
 
-    // Group the (token, slot) pairs by expert: pairs of a local expert in token order, slots in
-    // expert order; the shared expert, when asked for, is the last slot and takes every token.
-    const int n = a.T * a.K;
-    int *sidx = reinterpret_cast<int *>(&choice[0][0]);      // selection is done: reuse as [T*K] ids
-    for (int i = threadIdx.x; i < n; i += blockDim.x) sidx[i] = a.idx[i];
+    // Group the (token, slot) pairs by expert. Slots are numbered in expert order; the shared
+    // expert, when asked for, is the last slot and takes every token. Which pair of an expert
+    // lands where inside its slot does not matter: every pair has its own output row.
+    const int n = a.T * a.K, nth = RT_WARPS * 32;
+    int *sidx = reinterpret_cast<int *>(&choice[0][0]);       // selection is done: reuse as [T*K] ids
+    for (int i = tid; i < n; i += nth) sidx[i] = a.idx[i];
+    for (int le = tid; le < a.n_local; le += nth) cnt[le] = 0;
     __syncthreads();
-    for (int le = threadIdx.x; le < a.n_local; le += blockDim.x) {
-        int c = 0;
-        for (int i = 0; i < n; i++) c += sidx[i] == a.n_local0 + le;
-        cnt[le] = c;
+    for (int i = tid; i < n; i += nth) {
+        const int le = sidx[i] - a.n_local0;
+        if (le >= 0 && le < a.n_local) atomicAdd(&cnt[le], 1);
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        int o = 0, s = 0;
-        for (int i = 0; i < a.n_local; i++) {
-            off[i] = o; slot[i] = s;
-            if (cnt[i]) { o += cnt[i]; s++; }
+    const int per = (a.n_local + nth - 1) / nth;              // consecutive experts per thread
+    int pairs = 0, slots = 0;
+    for (int k = 0; k < per; k++) {
+        const int le = tid * per + k;
+        if (le < a.n_local && cnt[le]) { pairs += cnt[le]; slots++; }
+    }
+    psum[tid] = pairs; ssum[tid] = slots;
+    __syncthreads();
+    for (int o = 1; o < nth; o <<= 1) {                       // inclusive scans over the threads
+        const int pv = tid >= o ? psum[tid - o] : 0, sv = tid >= o ? ssum[tid - o] : 0;
+        __syncthreads();
+        psum[tid] += pv; ssum[tid] += sv;
+        __syncthreads();
+    }
+    int pbase = psum[tid] - pairs, sbase = ssum[tid] - slots;
+    const int total_pairs = psum[nth - 1], total_slots = ssum[nth - 1];
+    for (int k = 0; k < per; k++) {
+        const int le = tid * per + k;
+        if (le >= a.n_local) break;
+        off[le] = pbase;
+        if (cnt[le]) {
+            a.p.slot_expert[sbase] = le; a.p.slot_off[sbase] = pbase; a.p.slot_cnt[sbase] = cnt[le];
+            pbase += cnt[le]; sbase++;
         }
-        totals[0] = o; totals[1] = s;
     }
     __syncthreads();
-    for (int le = threadIdx.x; le < a.n_local; le += blockDim.x) {
-        if (!cnt[le]) continue;
-        const int s = slot[le];
-        a.p.slot_expert[s] = le; a.p.slot_off[s] = off[le]; a.p.slot_cnt[s] = cnt[le];
-        int o = off[le];
-        for (int i = 0; i < n; i++)
-            if (sidx[i] == a.n_local0 + le) { a.p.pair_tok[o] = i / a.K; a.p.pair_dst[o] = i; o++; }
+    for (int le = tid; le < a.n_local; le += nth) cnt[le] = 0;    // reused as the write cursor of each expert
+    __syncthreads();
+    for (int i = tid; i < n; i += nth) {
+        const int le = sidx[i] - a.n_local0;
+        if (le < 0 || le >= a.n_local) continue;
+        const int pos = off[le] + atomicAdd(&cnt[le], 1);
+        a.p.pair_tok[pos] = i / a.K;
+        a.p.pair_dst[pos] = i;
     }
     if (a.with_shared) {
-        const int s = totals[1], o = totals[0];
-        if (threadIdx.x == 0) { a.p.slot_expert[s] = a.n_local; a.p.slot_off[s] = o; a.p.slot_cnt[s] = a.T; }
-        for (int tt = threadIdx.x; tt < a.T; tt += blockDim.x) { a.p.pair_tok[o + tt] = tt; a.p.pair_dst[o + tt] = n + tt; }
+        if (tid == 0) { a.p.slot_expert[total_slots] = a.n_local; a.p.slot_off[total_slots] = total_pairs; a.p.slot_cnt[total_slots] = a.T; }
+        for (int tt = tid; tt < a.T; tt += nth) { a.p.pair_tok[total_pairs + tt] = tt; a.p.pair_dst[total_pairs + tt] = n + tt; }
     }
-    if (threadIdx.x == 0) *a.p.n_slots = totals[1] + (a.with_shared ? 1 : 0);
+    if (tid == 0) *a.p.n_slots = total_slots + (a.with_shared ? 1 : 0);
 }
 
 // p may be null-planned (p.n_slots == nullptr) when only the routing is wanted.

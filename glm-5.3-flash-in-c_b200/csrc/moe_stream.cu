@@ -16,7 +16,7 @@
 // Persistent grid: one CTA per SM walks work items blockIdx.x, +gridDim.x, ... Every wait on an
 // mbarrier is bounded; a wait that runs out records an error code in device memory, the CTA drains
 // the copies it has in flight (again bounded) and returns, and the host reports failure.
-#include "common.cuh"
+#include "bulk.cuh"
 #include "kernels.h"
 
 namespace g5b {
@@ -25,41 +25,6 @@ constexpr int ST_ROWS = 32;                  // weight rows per stage
 constexpr int ST_CB = 2048;                  // bytes of each row per stage
 constexpr int ST_NS = 3;                     // stages
 constexpr int ST_MAX_ITEMS = 32;             // work items one CTA may own (down: combine bookkeeping)
-constexpr int ST_WAIT_LIMIT = 1 << 22;       // try_wait attempts before giving up (~ a second)
-
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t *bar)
-{
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
-{
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait: false (and an error code in *err) when the barrier never completes.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *err, int code)
-{
-    for (int i = 0; i < ST_WAIT_LIMIT; i++)
-        if (mbar_try_wait(bar, parity)) return true;
-    atomicExch(err, code);
-    return false;
-}
-__device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src, uint32_t bytes, uint64_t *bar)
-{
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(smem_u32(dst_smem)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
-}
 
 // Position of column c in the activation layout the consumers read without bank conflicts: the
 // 16 columns a lane multiplies with one 16-byte piece of codes are stored as four float4 that are

@@ -91,16 +91,24 @@ def test_full_size_mla_layer(gpu_lib, binding, latent_bf16):
     eng.close(); orc.close()
 
 
-def test_streamed_and_register_expert_kernels_agree(moe_layer):
-    """Batch 1 runs the bulk-copy streamed kernels by default; the register-streaming kernels (the
-    path batches take) must give the same layer output to FP32 rounding."""
+def test_expert_kernel_variants_agree(moe_layer, binding):
+    """Batch 1 has three expert implementations: register-streaming CUDA-core kernels (the path
+    batches take), bulk-copy streamed CUDA-core kernels, and bulk-copy streamed tensor-core kernels
+    (the default). All must give the layer output of the CPU path."""
     spec, trunk, eng = moe_layer
     x = synth.moe_inputs(spec.cfg, 1, SEED + 3)
-    a = eng.op_moe(0, x)
-    eng.set_option("stream_experts", 0)
-    b = eng.op_moe(0, x)
-    eng.set_option("stream_experts", 1)
-    c = eng.op_moe(0, x)
-    assert np.array_equal(a, c)
-    assert common.rel_err(a, b) < 2e-6
-    assert common.rel_err(eng.op_moe(0, x, False), eng.op_moe(0, x, True)) > 1e-3   # the shared expert matters
+    # a general FP32 activation too, not only BF16-representable values
+    x2 = (np.random.default_rng(5).standard_normal((1, spec.cfg.hidden)) * 3.7).astype(np.float32)
+    for xin in (x, x2):
+        idx, _ = eng.op_router(0, xin)
+        orc = synth.oracle_moe_layer(binding, spec, trunk, SEED, idx.ravel())
+        want = orc.op_moe(0, xin)
+        outs = []
+        for mode in (0, 1, 2):
+            eng.set_option("stream_experts", mode)
+            outs.append(eng.op_moe(0, xin))
+            assert common.rel_err(outs[-1], want) < 1e-5, mode
+            assert common.rel_err(eng.op_moe(0, xin, False), orc.op_moe(0, xin, False)) < 1e-5, mode
+        eng.set_option("stream_experts", 2)
+        assert np.array_equal(outs[2], eng.op_moe(0, xin))          # deterministic
+        orc.close()
