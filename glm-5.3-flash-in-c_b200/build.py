@@ -39,6 +39,7 @@ def build(verbose: bool = False) -> str:
     flags = list(FLAGS)
     if os.environ.get("G5B_PTXAS_V"):
         flags += ["-Xptxas", "-v"]
+    flags += os.environ.get("G5B_NVCC_FLAGS", "").split()      # e.g. -DG5B_STAGE_TIMERS for kernel timers
 
     def compile_one(src):
         obj = os.path.join(OBJ, os.path.basename(src)[:-3] + ".o")

@@ -24,6 +24,7 @@ namespace g5b {
 constexpr int MM_ROWS = 32, MM_CB = 2048, MM_PITCH = MM_CB + 64, MM_NS = 3, MM_CONS = 8;
 constexpr int MM_THREADS = (MM_CONS + 1) * 32;
 constexpr int MM_MAX_ITEMS = 32;
+constexpr int MM_MAX_SLOTS = 17;             // experts per token (top-k + shared) this path serves
 
 struct MmaArgs {
     const ExpertW *experts;
@@ -61,9 +62,20 @@ __device__ __forceinline__ void split_f16(float x, __half &hi, __half &mid)
     mid = __float2half_rn((x - __half2float(hi)) * 2048.0f);
 }
 
+#ifdef G5B_STAGE_TIMERS
+// Development aid (never in a normal build): per CTA, cycles spent in the prologue, by the producer
+// waiting for a free stage and issuing copies, and by consumer warp 0 waiting for data and computing.
+__device__ unsigned long long g_stage_timers[2][160][8];
+#define TIMER_NOW() clock64()
+#else
+#define TIMER_NOW() 0ll
+#endif
+
 template <bool GATEUP>
 __global__ void __launch_bounds__(MM_THREADS, 1) moe_mma_kernel(const MmaArgs a)
 {
+    const long long t_start = TIMER_NOW();
+    long long t_wait = 0, t_work = 0;
     extern __shared__ __align__(128) uint8_t smem[];
     const int C = GATEUP ? a.E : a.I;
     const int rows_total = GATEUP ? a.I : a.E;
@@ -82,6 +94,8 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_mma_kernel(const MmaArgs a)
     uint64_t *full = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(red) + MM_CONS * 16 * 4);
     uint64_t *empty = full + MM_NS;
     __shared__ int my_tiles[MM_MAX_ITEMS], my_last[MM_MAX_ITEMS];
+    __shared__ ExpertW s_ew[MM_MAX_SLOTS];
+    __shared__ int s_pair[MM_MAX_SLOTS], s_dst[MM_MAX_SLOTS], s_nslots;
     __shared__ float wmax[MM_THREADS / 32];
     __shared__ float x_scale[2];                                          // scale, 1/scale
 
@@ -89,6 +103,19 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_mma_kernel(const MmaArgs a)
     if (threadIdx.x == 0) {
         for (int s = 0; s < MM_NS; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], MM_CONS); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // The plan and the expert pointer table are read ONCE per CTA into shared memory: they sit
+    // behind two dependent loads, which per work item would stall the producer for microseconds.
+    if (warp == 0) {
+        int n = *a.p.n_slots;
+        n = n < 0 ? 0 : (n > MM_MAX_SLOTS ? MM_MAX_SLOTS : n);
+        for (int i = lane; i < n; i += 32) {
+            const int off = a.p.slot_off[i];
+            s_ew[i] = a.experts[a.p.slot_expert[i]];
+            s_pair[i] = off;
+            s_dst[i] = a.p.pair_dst[off];
+        }
+        if (lane == 0) s_nslots = n;
     }
     if (GATEUP) {
         // scale the activation by a power of two so that its largest element sits near 2^14, then
@@ -119,21 +146,25 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_mma_kernel(const MmaArgs a)
     }
     __syncthreads();
 
-    const int n_items = *a.p.n_slots * tps;
+    const int n_items = s_nslots * tps;
     bool ok = true;
+    const long long t_loop = TIMER_NOW();
 
     if (warp == MM_CONS) {
         // ---------------------------------------------------------------- producer ----
         int it = 0;
         for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
             const int slot = item / tps, rt = item % tps;
-            const ExpertW ew = a.experts[a.p.slot_expert[slot]];
-            const int pair = a.p.slot_off[slot];
+            const ExpertW ew = s_ew[slot];
+            const int pair = s_pair[slot];
             for (int kh = 0; kh < KH && ok; kh++, it++) {
                 const int s = it % MM_NS;
+                const long long t0 = TIMER_NOW();
                 if (it >= MM_NS) ok = mbar_wait(&empty[s], ((it / MM_NS) - 1) & 1, a.err, 1);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
+                const long long t1 = TIMER_NOW();
+                t_wait += t1 - t0;
                 uint8_t *st = stages + (size_t)s * stage_bytes;
                 const uint32_t bytes = MM_ROWS * MM_CB + (GATEUP ? 2 : 1) * scols * 4 + (GATEUP ? 0 : a.I * 4);
                 if (lane == 0) mbar_expect_tx(&full[s], bytes);
@@ -152,8 +183,15 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_mma_kernel(const MmaArgs a)
                         bulk_g2s(st + act_off, static_cast<const uint8_t *>(a.x) + (size_t)pair * a.I * 4, a.I * 4, &full[s]);
                     }
                 }
+                t_work += TIMER_NOW() - t1;
             }
         }
+#ifdef G5B_STAGE_TIMERS
+        if (lane == 0 && blockIdx.x < 160) {
+            unsigned long long *o = g_stage_timers[GATEUP ? 0 : 1][blockIdx.x];
+            o[0] = t_loop - t_start; o[1] = t_wait; o[2] = t_work; o[3] = TIMER_NOW() - t_loop;
+        }
+#endif
         if (!ok) {                       // copies in flight must land before shared memory goes away
             for (int k = 0; k < MM_NS && k < it; k++) {
                 const int j = it - 1 - k;
@@ -167,13 +205,16 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_mma_kernel(const MmaArgs a)
         int it = 0;
         for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
             const int slot = item / tps, rt = item % tps;
-            const int pair = a.p.slot_off[slot];
+            const int pair = s_pair[slot];
             float accf[4] = {0.f, 0.f, 0.f, 0.f};
             for (int kh = 0; kh < KH && ok; kh++, it++) {
                 const int s = it % MM_NS;
+                const long long t0 = TIMER_NOW();
                 ok = mbar_wait(&full[s], (it / MM_NS) & 1, a.err, 2);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
+                const long long t1 = TIMER_NOW();
+                t_wait += t1 - t0;
                 const uint8_t *st = stages + (size_t)s * stage_bytes;
                 const float *sc = reinterpret_cast<const float *>(st + scale_off) + ((GATEUP && mt) ? 64 : 0);
                 const uint8_t *w0p = st + (size_t)(mt * 16 + g) * MM_PITCH + kq * 512 + 16 * t;
@@ -204,6 +245,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_mma_kernel(const MmaArgs a)
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[s]);
+                t_work += TIMER_NOW() - t1;
             }
             if (!ok) break;
             // columns 0 (hi) and 1 (mid) of the accumulator tile live in the lanes with t == 0
@@ -234,17 +276,23 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_mma_kernel(const MmaArgs a)
                 float v = 0.f;
 #pragma unroll
                 for (int q = 0; q < 4; q++) v += red[(2 * q + m2) * 16 + rr];
-                static_cast<float *>(a.y)[(size_t)a.p.pair_dst[pair] * a.E + rt * MM_ROWS + r] = v;
+                static_cast<float *>(a.y)[(size_t)s_dst[slot] * a.E + rt * MM_ROWS + r] = v;
             }
             asm volatile("bar.sync 1, %0;" ::"r"(MM_CONS * 32) : "memory");
         }
+#ifdef G5B_STAGE_TIMERS
+        if (threadIdx.x == 0 && blockIdx.x < 160) {
+            unsigned long long *o = g_stage_timers[GATEUP ? 0 : 1][blockIdx.x];
+            o[4] = t_wait; o[5] = t_work; o[6] = TIMER_NOW() - t_loop;
+        }
+#endif
         if (!GATEUP && a.out && ok) {
             // Combine once per CTA: report every row tile this CTA wrote; whoever completes a tile
             // sums its K contributions in top-k order in FP64 and adds the shared expert
             // (reference: src/core/glm53f_ops.c:1329-1340).
             __threadfence();
             asm volatile("bar.sync 1, %0;" ::"r"(MM_CONS * 32) : "memory");
-            const int n = *a.p.n_slots;
+            const int n = s_nslots;
             int mine = 0;
             for (int item = blockIdx.x; item < n_items; item += gridDim.x) mine++;
             if (mine > MM_MAX_ITEMS) { if (threadIdx.x == 0) atomicExch(a.err, 4); mine = 0; }
@@ -279,7 +327,7 @@ static size_t mma_smem_bytes(bool gateup, int E, int I)
 
 bool moe_mma_supported(const MoeShape &s, int T)
 {
-    if (T != 1 || s.dt != DT_FP8) return false;
+    if (T != 1 || s.dt != DT_FP8 || s.K + 1 > MM_MAX_SLOTS) return false;
     if (s.E % MM_CB || s.I % MM_CB || s.I % 16 || s.E % MM_ROWS) return false;
     if (s.bc < 64 || 512 % s.bc || s.br % MM_ROWS || s.E / s.bc > 64 || s.I / s.bc > 64) return false;
     if ((s.E / s.bc) % 4 || (s.I / s.bc) % 4) return false;          // scale rows are copied in 16-byte units
@@ -325,5 +373,12 @@ void moe_mma_down(cudaStream_t st, float *out, float *contrib, const void *act_t
     MmaArgs a{experts, p, act_terms, contrib, s.E, s.I, s.br, s.bc, s.limit, out, w, s.K, with_shared, tile_done, err};
     launch_mma<false>(st, a, mma_smem_bytes(false, s.E, s.I));
 }
+
+#ifdef G5B_STAGE_TIMERS
+extern "C" int g5b_debug_stage_timers(unsigned long long *dst)
+{
+    return cudaMemcpyFromSymbol(dst, g_stage_timers, sizeof g_stage_timers) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 }  // namespace g5b

@@ -24,7 +24,9 @@ namespace g5b {
 constexpr int ST_ROWS = 32;                  // weight rows per stage
 constexpr int ST_CB = 2048;                  // bytes of each row per stage
 constexpr int ST_NS = 3;                     // stages
-constexpr int ST_MAX_ITEMS = 32;             // work items one CTA may own (down: combine bookkeeping)
+constexpr int ST_MAX_ITEMS = 32;
+constexpr int ST_MAX_SLOTS = 17;             // experts per token (top-k + shared) this path serves
+//             // work items one CTA may own (down: combine bookkeeping)
 
 // Position of column c in the activation layout the consumers read without bank conflicts: the
 // 16 columns a lane multiplies with one 16-byte piece of codes are stored as four float4 that are
@@ -79,18 +81,33 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) moe_stream_kernel(const Stre
     uint64_t *full = reinterpret_cast<uint64_t *>(smem + ST_NS * stage_bytes + (GATEUP ? (size_t)a.E * 4 : 0));
     uint64_t *empty = full + ST_NS;
     __shared__ int my_tiles[ST_MAX_ITEMS], my_last[ST_MAX_ITEMS];
+    __shared__ ExpertW s_ew[ST_MAX_SLOTS];
+    __shared__ int s_pair[ST_MAX_SLOTS], s_dst[ST_MAX_SLOTS], s_nslots;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         for (int s = 0; s < ST_NS; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], ST_CONS); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    // The plan and the expert pointer table are read ONCE per CTA into shared memory: they sit
+    // behind two dependent loads, which per work item would stall the producer for microseconds.
+    if (warp == 0) {
+        int n = *a.p.n_slots;
+        n = n < 0 ? 0 : (n > ST_MAX_SLOTS ? ST_MAX_SLOTS : n);
+        for (int i = lane; i < n; i += 32) {
+            const int off = a.p.slot_off[i];
+            s_ew[i] = a.experts[a.p.slot_expert[i]];
+            s_pair[i] = off;
+            s_dst[i] = a.p.pair_dst[off];
+        }
+        if (lane == 0) s_nslots = n;
+    }
     if (GATEUP) {
         for (int c = threadIdx.x; c < a.E; c += ST_THREADS) x_s[perm_index(c, pieces)] = a.x[c];
     }
     __syncthreads();
 
-    const int n_items = *a.p.n_slots * tps;
+    const int n_items = s_nslots * tps;
     bool ok = true;
 
     if (warp == ST_CONS) {
@@ -98,8 +115,8 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) moe_stream_kernel(const Stre
         int it = 0;
         for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
             const int slot = item / tps, rt = item % tps;
-            const ExpertW ew = a.experts[a.p.slot_expert[slot]];
-            const int pair = a.p.slot_off[slot];
+            const ExpertW ew = s_ew[slot];
+            const int pair = s_pair[slot];
             for (int kh = 0; kh < KH && ok; kh++, it++) {
                 const int s = it % ST_NS;
                 if (it >= ST_NS) ok = mbar_wait(&empty[s], ((it / ST_NS) - 1) & 1, a.err, 1);
@@ -137,7 +154,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) moe_stream_kernel(const Stre
         int it = 0;
         for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
             const int slot = item / tps, rt = item % tps;
-            const int pair = a.p.slot_off[slot];
+            const int pair = s_pair[slot];
             float acc[RPW];
 #pragma unroll
             for (int q = 0; q < RPW; q++) acc[q] = 0.f;
@@ -206,7 +223,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) moe_stream_kernel(const Stre
                 const int r = rt * ST_ROWS + RPW * warp;
                 if (lane == 0) {
 #pragma unroll
-                    for (int q = 0; q < RPW; q++) a.y[(size_t)a.p.pair_dst[pair] * a.E + r + q] = acc[q];
+                    for (int q = 0; q < RPW; q++) a.y[(size_t)s_dst[slot] * a.E + r + q] = acc[q];
                 }
             }
         }
@@ -216,7 +233,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) moe_stream_kernel(const Stre
             // contributions of that tile in top-k order in FP64 and adds the shared expert.
             __threadfence();
             asm volatile("bar.sync 1, %0;" ::"r"(ST_CONS * 32) : "memory");
-            const int n = *a.p.n_slots;
+            const int n = s_nslots;
             int mine = 0;
             for (int item = blockIdx.x; item < n_items; item += gridDim.x) mine++;
             if (mine > ST_MAX_ITEMS) { if (threadIdx.x == 0) atomicExch(a.err, 4); mine = 0; }
@@ -252,7 +269,7 @@ size_t stream_smem_bytes(bool gateup, int E, int I)
 // register-streaming kernels of moe.cu.
 bool moe_stream_supported(const MoeShape &s, int T)
 {
-    if (T != 1 || s.dt != DT_FP8) return false;
+    if (T != 1 || s.dt != DT_FP8 || s.K + 1 > ST_MAX_SLOTS) return false;
     if (s.E % ST_CB || s.I % ST_CB || s.I % 16 || s.E % ST_ROWS) return false;
     if (s.bc < 16 || s.bc % 16 || s.br % ST_ROWS || s.E / s.bc > 64 || s.I / s.bc > 64) return false;
     if ((s.E / s.bc) % 4 || (s.I / s.bc) % 4) return false;          // scale rows copied in 16-byte units
