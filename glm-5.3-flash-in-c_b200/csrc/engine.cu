@@ -77,7 +77,7 @@ using namespace g5b;
 struct g5b_engine {
     g5b_config c;
     int cap = 0, cached = 0, device = 0, ep_rank = 0, ep_size = 1, n_local0 = 0, n_local = 0;
-    bool finalized = false;
+    bool finalized = false, ep_connected = false;
     int latent_bf16 = 0, profile = 0, partial = 0, stream_experts = 2, stream_warps = 8;
     int *counter = nullptr, *tile_done = nullptr, *err_dev = nullptr;
     volatile int *err_host = nullptr;   // mapped host memory: kernels record a timed-out wait here
@@ -551,6 +551,8 @@ static int run_moe(g5b_engine *e, Layer &w, const float *x, int n, float *out, i
     const g5b_config &c = e->c;
     if (!w.table_dev || !w.router.loaded() || !w.bias || (with_shared && !w.sh_down.loaded()))
         return fail("this layer's MoE weights were not loaded");
+    if (e->ep_size > 1 && !e->ep_connected)
+        return fail("expert-parallel engine: connect the ranks (g5b_engine_ep_connect) before running a MoE layer");
     const MoeShape s = moe_shape(e, w);
     const bool shared_in_plan = with_shared && c.n_shared == 1 && w.sh_gate.dt == s.dt;
     prof_mark(e, 0);

@@ -22,7 +22,7 @@ def build(reference_tree: str = "/root/reference"):
     """Compile the oracle, and the reference objects when the reference tree is present."""
     subprocess.run(["make", "-C", HERE, "oracle"], check=True, stdout=subprocess.DEVNULL)
     if os.path.isdir(os.path.join(reference_tree, "src", "core")):
-        subprocess.run(["make", "-C", HERE, "ref", f"REF={reference_tree}"], check=True,
+        subprocess.run(["make", "-C", HERE, "ref", "ref-gpu-test", f"REF={reference_tree}"], check=True,
                        stdout=subprocess.DEVNULL)
 
 

@@ -54,3 +54,31 @@ def build_models(spec, tensors, cap, binding=None, engine=True, oracle=True, kv_
         orc.load_all(tensors)
         orc.finalize()
     return eng, orc
+
+
+def write_reference_tiny_checkpoint(directory):
+    """Re-create the reference's test checkpoint directory (config.json, model.safetensors,
+    ref.json) from the golden import, for programs that load it with the reference's own loader."""
+    import importlib
+    ck = importlib.import_module("glm53f_b200.checkpoint")
+    with open(os.path.join(GOLDEN, "reference_tiny.json")) as f:
+        meta = json.load(f)
+    z = np.load(os.path.join(GOLDEN, "reference_tiny.npz"))
+    st = {pkg.DT_F32: "F32", pkg.DT_BF16: "BF16", pkg.DT_FP8: "F8_E4M3"}
+    out = {}
+    for name, dt in meta["dtypes"].items():
+        full = name if name == "lm_head.weight" else ck.PREFIX + name
+        arr = z[name]
+        if "conv1d" in name:
+            arr = arr.reshape(arr.shape[0], 1, arr.shape[1])
+        elif arr.ndim == 2 and arr.shape[1] == 1 and not name.endswith("proj.weight"):
+            arr = arr.reshape(-1)
+        out[full] = (arr, st[dt])
+        if dt == pkg.DT_FP8:
+            out[full + "_scale_inv"] = (z[name + "_scale_inv"], "F32")
+    os.makedirs(directory, exist_ok=True)
+    ck.write_safetensors(os.path.join(directory, "model.safetensors"), out)
+    with open(os.path.join(directory, "config.json"), "w") as f:
+        json.dump(meta["config"], f)
+    with open(os.path.join(directory, "ref.json"), "w") as f:
+        json.dump(meta["golden"], f)

@@ -110,3 +110,22 @@ def test_latent_cache_in_bf16(gpu_lib, binding):
     # 20 attended positions
     assert common.rel_err(g, w) < 2e-3
     eng.close(); orc.close()
+
+
+def test_reference_unit_test_binary_on_this_backend(gpu_lib, tmp_path):
+    """The reference's own tests/unit/test_glm_tiny.c, compiled with -DGLM53F_CUDA against the
+    adapter in glm-5.3-flash-in-c_b200/adapter (reference driver + reference test + this engine):
+    its GPU gates G1-G3 must pass on the CUDA engine."""
+    import os
+    import subprocess
+    exe = os.path.join(common.GOLDEN, "..", "..", "oracle", "_ref", "test_glm_tiny_b200")
+    if not os.path.exists(exe):
+        pytest.skip("the reference test binary was not built (reference tree absent at build time)")
+    common.write_reference_tiny_checkpoint(str(tmp_path))
+    r = subprocess.run([exe, str(tmp_path)], capture_output=True, text=True, timeout=300)
+    out = r.stdout + r.stderr
+    assert "SKIP  GPU gates" not in out, out
+    for gate in ("GATE G1", "GATE G2", "GATE G3"):
+        line = [l for l in out.splitlines() if gate in l]
+        assert line and "PASS" in line[0], out
+    assert r.returncode == 0, out

@@ -166,3 +166,16 @@ def test_synthetic_codes_are_finite_and_spread(binding):
     assert counts[0x7f] == 0 and counts[0xff] == 0
     assert counts[counts > 0].min() > 150 and (counts > 0).sum() == 254
     assert not np.array_equal(c, binding.synth_codes(7, 3, 12, 1, 1 << 16))
+
+
+def test_reference_checkpoint_roundtrip(binding, tmp_path):
+    """The golden import written back as a checkpoint directory loads with the reference's own
+    safetensors reader and bind, and gives the golden logits."""
+    if not binding.have_ref():
+        pytest.skip("reference objects not built here")
+    cfg, is_mla, is_dense, tensors, g = common.load_reference_tiny()
+    common.write_reference_tiny_checkpoint(str(tmp_path))
+    m = binding.ref_open_dir(str(tmp_path), cfg, len(g["full_ids"]))
+    lg, _ = m.forward(g["prompt_ids"])
+    assert common.golden_tolerance_ratio(lg, g["logits_last"]) <= 1.0
+    m.close()
