@@ -32,6 +32,7 @@ static int fail(const char *fmt, ...)
     fprintf(stderr, "glm53f_b200: %s\n", g_err);
     return -1;
 }
+void set_last_error(const char *msg) { snprintf(g_err, sizeof g_err, "%s", msg); }
 #define CU(call)                                                                           \
     do {                                                                                   \
         cudaError_t e_ = (call);                                                           \

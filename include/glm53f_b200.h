@@ -201,6 +201,23 @@ int g5b_state_write(g5b_engine *e, int layer, int kind, size_t offset, const flo
 int g5b_state_read(g5b_engine *e, int layer, int kind, size_t offset, float *dst,
                    size_t count);
 
+/* RMSNorm of `rows` rows of n floats on DEVICE buffers of the current CUDA device, enqueued on
+ * `stream` (a cudaStream_t, NULL for the default stream) without waiting: y = w * x / sqrt(mean(x^2)
+ * + eps), w may be NULL. This entry point has no counterpart in the reference. It exists for
+ * callers that must not allocate: it calls no cudaMalloc / cudaFree and no allocating library
+ * routine, because its per-row scratch (the normalisation factors) is a fixed array built into
+ * the library. Limits and rules that follow from that:
+ *   - rows <= 4096; more is refused with -1 and a message (split the call);
+ *   - every GPU that loads the library holds the 16 KB array until the process exits;
+ *   - the first call on each device resolves the array's address (once per device, with that
+ *     device current): make that first call before any stream capture begins;
+ *   - all calls on a device share the array: two calls that may overlap on the GPU (different
+ *     streams, or different threads) race on it and must be ordered by the caller. Nothing in it
+ *     has to start at zero; each call overwrites every factor it reads.
+ * Same arithmetic and same kernels as g5b_rmsnorm_host. */
+int g5b_rmsnorm_noalloc(float *y_dev, const float *x_dev, const float *w_dev, int n, int rows,
+                        float eps, void *stream);
+
 /* --------------------------------------------------------------- DEVICE OPS ---- */
 /* Device pointers on the engine's GPU, launched on the engine's stream, no host copies and
  * no synchronisation (call g5b_engine_sync to wait). */
