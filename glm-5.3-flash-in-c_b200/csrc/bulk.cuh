@@ -37,6 +37,29 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *e
     atomicExch(err, code);
     return false;
 }
+// The same wait for a whole warp that has nothing else to do: one lane polls, with a pause
+// between polls, so that 32 lanes do not fill the shared-memory pipe with polls that the
+// producer warp's copies and shuffles would queue behind. Every lane then observes the
+// completed phase itself. The result is uniform over the warp.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t *bar, uint32_t parity, int *err, int code)
+{
+    bool ok = true;
+    if ((threadIdx.x & 31) == 0) {
+        ok = false;
+        for (int i = 0; i < ST_WAIT_LIMIT; i++) {
+            if (mbar_try_wait(bar, parity)) { ok = true; break; }
+            __nanosleep(20);
+        }
+        if (!ok) atomicExch(err, code);
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+        ok = false;
+        for (int i = 0; i < 1024 && !ok; i++) ok = mbar_try_wait(bar, parity);
+        ok = __all_sync(0xffffffffu, ok);
+    }
+    return ok;
+}
 __device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src, uint32_t bytes, uint64_t *bar)
 {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"

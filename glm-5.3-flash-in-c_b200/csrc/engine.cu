@@ -79,7 +79,8 @@ struct g5b_engine {
     g5b_config c;
     int cap = 0, cached = 0, device = 0, ep_rank = 0, ep_size = 1, n_local0 = 0, n_local = 0;
     bool finalized = false, ep_connected = false;
-    int latent_bf16 = 0, profile = 0, partial = 0, stream_experts = 2, stream_warps = 8;
+    int latent_bf16 = 0, profile = 0, partial = 0, stream_experts = 3, stream_warps = 8;
+    unsigned long long *grid_sync = nullptr, grid_launches = 0;
     int *counter = nullptr, *tile_done = nullptr, *err_dev = nullptr;
     volatile int *err_host = nullptr;   // mapped host memory: kernels record a timed-out wait here
     cudaStream_t st = nullptr;
@@ -254,8 +255,9 @@ extern "C" int g5b_engine_set_option(g5b_engine *e, const char *name, int value)
     }
     if (!strcmp(name, "profile")) { e->profile = value; return 0; }
     if (!strcmp(name, "allow_partial")) { e->partial = value != 0; return 0; }
-    if (!strcmp(name, "stream_experts")) {       // 0 register kernels, 1 streamed CUDA-core, 2 streamed tensor-core
-        if (value < 0 || value > 2) return fail("stream_experts is 0, 1 or 2");
+    if (!strcmp(name, "stream_experts")) {       // batch-1 experts: 0 register kernels, 1 streamed CUDA-core,
+                                                 // 2 streamed tensor-core, 3 the whole layer as one kernel
+        if (value < 0 || value > 3) return fail("stream_experts is 0, 1, 2 or 3");
         e->stream_experts = value;
         return 0;
     }
@@ -503,7 +505,7 @@ extern "C" int g5b_engine_finalize(g5b_engine *e)
     if (walloc(e, &e->plan.n_slots, 1) || walloc(e, &e->plan.slot_expert, e->plan.max_slots) ||
         walloc(e, &e->plan.slot_off, e->plan.max_slots) || walloc(e, &e->plan.slot_cnt, e->plan.max_slots) ||
         walloc(e, &e->plan.pair_tok, pairs) || walloc(e, &e->plan.pair_dst, pairs)) return -1;
-    if (walloc(e, &e->counter, 4) || walloc(e, &e->tile_done, E / 32 + 1)) return -1;
+    if (walloc(e, &e->counter, 4) || walloc(e, &e->tile_done, E / 32 + 1) || walloc(e, &e->grid_sync, 2)) return -1;
     {
         int *hp = nullptr;
         CU(cudaHostAlloc((void **)&hp, 64, cudaHostAllocMapped));
@@ -556,11 +558,19 @@ static int run_moe(g5b_engine *e, Layer &w, const float *x, int n, float *out, i
         return fail("expert-parallel engine: connect the ranks (g5b_engine_ep_connect) before running a MoE layer");
     const MoeShape s = moe_shape(e, w);
     const bool shared_in_plan = with_shared && c.n_shared == 1 && w.sh_gate.dt == s.dt;
+    const bool one_gpu_decode = e->ep_size == 1 && (shared_in_plan || !with_shared);
     prof_mark(e, 0);
+    if (e->stream_experts == 3 && one_gpu_decode && moe_decode_supported(s, n)) {
+        if (moe_decode(e->st, out, x, w.router.w, w.router.dt, w.bias, w.table_dev, e->rscore, e->ridx, e->rw, e->act,
+                       e->contrib, s, with_shared, e->grid_sync, &e->grid_launches, e->tile_done, e->err_dev) == 0) {
+            prof_mark(e, 1); prof_mark(e, 2); prof_mark(e, 3); prof_mark(e, 4);
+            prof_collect(e, 4);
+            return 0;
+        }
+    }
     router_plan(e->st, e->ridx, e->rw, e->rscore, x, c.hidden, w.router.w, w.router.dt, w.bias, n, s, e->plan,
                 shared_in_plan ? 1 : 0, e->counter);
     prof_mark(e, 1);
-    const bool one_gpu_decode = e->ep_size == 1 && (shared_in_plan || !with_shared);
     if (e->stream_experts == 2 && one_gpu_decode && moe_mma_supported(s, n)) {
         moe_mma_gateup(e->st, e->act, x, w.table_dev, e->plan, s, e->err_dev);
         prof_mark(e, 2);
@@ -704,6 +714,11 @@ static int check_device_error(g5b_engine *e)
     if (e->err_host && *e->err_host) {
         const int code = *e->err_host;
         *e->err_host = 0;
+        // the grid-wide counters and tile counters of the interrupted launch are unusable: start over
+        cudaMemsetAsync(e->grid_sync, 0, 2 * sizeof(unsigned long long), e->st);
+        cudaMemsetAsync(e->tile_done, 0, ((size_t)e->c.hidden / 32 + 1) * sizeof(int), e->st);
+        cudaStreamSynchronize(e->st);
+        e->grid_launches = 0;
         return fail("a device-side wait timed out (code %d); the result of this call is invalid", code);
     }
     return 0;

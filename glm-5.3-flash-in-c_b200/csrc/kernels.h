@@ -110,6 +110,14 @@ void moe_mma_gateup(cudaStream_t st, void *act_terms, const float *x, const Expe
 void moe_mma_down(cudaStream_t st, float *out, float *contrib, const void *act_terms, const float *w,
                   const ExpertW *experts, const MoePlan &p, const MoeShape &s, int with_shared, int *tile_done,
                   int *err);
+// The whole batch-1 layer (router, top-k, experts, combine) as one cooperative kernel
+// (moe_decode.cu). `sync` holds two device counters that only grow; `launches` is the host's count of
+// launches so far on them. Returns -1 when the cooperative launch is refused.
+bool moe_decode_supported(const MoeShape &s, int T);
+int moe_decode(cudaStream_t st, float *out, const float *x, const void *gate, int gate_dt, const float *bias,
+               const ExpertW *experts, float *score, int *idx, float *w, void *act, float *contrib,
+               const MoeShape &s, int with_shared, unsigned long long *sync, unsigned long long *launches,
+               int *tile_done, int *err);
 // out == nullptr: contributions only (the caller combines, e.g. after an expert-parallel exchange).
 void moe_stream_down(cudaStream_t st, float *out, float *contrib, const float *act, const float *w,
                      const ExpertW *experts, const MoePlan &p, const MoeShape &s, int with_shared,

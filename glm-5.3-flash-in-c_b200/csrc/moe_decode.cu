@@ -1,0 +1,558 @@
+// moe_decode.cu - one MoE layer for one token in ONE persistent kernel: router, top-k, gate/up
+// with clamped SwiGLU, down, and the combine.
+//
+// Why one kernel: as three launches (router, gate/up, down) the layer spent about a third of its
+// time outside the streaming loops - launch gaps, each kernel's prologue (barrier set-up, plan and
+// pointer loads, activation split), and a 20 us router whose tail ran on a single CTA. Here all
+// 148 SMs start streaming at once: the shared expert does not depend on routing, so its gate/up
+// rows are in flight while the router rows are being multiplied; every CTA then selects the top-k
+// itself from the 288 scores (identical everywhere), and the weight pipeline never drains between
+// gate/up and down because the down weights of a CTA's first row tiles are prefetched before the
+// grid-wide point where the activations become visible.
+//
+// Launched cooperatively (all CTAs co-resident, one per SM). The two grid-wide points are counters
+// in device memory that only ever grow (the host passes the value each launch starts from); every
+// wait - on them, on the shared-memory mbarriers - is bounded, and a wait that runs out records a
+// code in mapped host memory and unwinds the CTA after draining its copies.
+//
+// Work items: gate/up item = 16 gate rows + the same 16 up rows (two stages of 2048 columns);
+// down item = 32 output rows (one stage, plus the expert's activation terms). Items are numbered
+// shared expert first, then the routed experts in top-k order, and dealt round-robin to the CTAs.
+// Arithmetic is that of moe_mma.cu (tensor-core products of E4M3 codes with the activation split
+// into two F16 terms); selection and combine follow the reference (src/core/glm53f_ops.c:945-976,
+// 1329-1340).
+#include <stdlib.h>
+
+#include "kernels.h"
+#include "mma_stage.cuh"
+
+namespace g5b {
+
+constexpr int DEC_SPIN_LIMIT = 1 << 21;
+constexpr int DEC_PER = 16;                  // experts per lane of the selecting warp: NE <= 512
+
+struct DecodeArgs {
+    const ExpertW *experts;     // [NE + 1], shared expert last
+    const float *x;             // [E]
+    const void *gate; int gate_dt;
+    const float *bias;
+    float *score;               // [NE] scratch
+    int *idx; float *w;         // [K] outputs (also used by the combine)
+    __half *act;                // [K + 1][2][I] scratch
+    float *contrib;             // [K + 1][E] scratch
+    float *out;                 // [E]
+    int E, I, NE, K, br, bc, with_shared, norm_topk;
+    float limit, routed_scale;
+    unsigned long long *sync;   // [2] grid-wide counters
+    unsigned long long base;    // value of both counters when this launch starts
+    int *tile_done;
+    int *err;
+};
+
+__device__ __forceinline__ unsigned long long ld_acquire(const unsigned long long *p)
+{
+    unsigned long long v;
+    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Wait until every CTA of the grid has arrived at counter `which`; bounded. Called by a whole warp:
+// every lane polls the same word (one transaction), so the loop is uniform and the warp leaves
+// it converged - a single polling lane left the warp split for the code that follows, which
+// then ran several times slower.
+__device__ __forceinline__ bool grid_wait(const DecodeArgs &a, int which, int code)
+{
+    const unsigned long long target = a.base + gridDim.x;
+    bool seen = false;
+    for (int i = 0; i < DEC_SPIN_LIMIT && !seen; i++) {
+        seen = ld_acquire(a.sync + which) >= target;
+        if (!seen) __nanosleep(40);
+    }
+    seen = __all_sync(0xffffffffu, seen);
+    if (!seen && (threadIdx.x & 31) == 0) atomicExch(a.err, code);
+    __syncwarp();
+    return seen;
+}
+
+// Order-preserving key of a selection score; 0 = not selectable (NaN, -inf, already taken).
+__device__ __forceinline__ uint32_t choice_key(float v)
+{
+    if (!(v > -INFINITY)) return 0u;
+    const uint32_t u = __float_as_uint(__fadd_rn(v, 0.f));     // -0 -> +0
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+#ifdef G5B_STAGE_TIMERS
+__device__ unsigned long long g_decode_timers[160][16];
+#define DT_MARK(k) do { if (ctid == 0 && blockIdx.x < 160) g_decode_timers[blockIdx.x][k] = clock64() - t_begin; } while (0)
+#define DT_MARK_P(k) do { if (lane == 0 && blockIdx.x < 160) g_decode_timers[blockIdx.x][k] = clock64() - t_begin; } while (0)
+#else
+#define DT_MARK(k) do { } while (0)
+#define DT_MARK_P(k) do { } while (0)
+#endif
+
+__global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeArgs a)
+{
+#ifdef G5B_STAGE_TIMERS
+    const long long t_begin = clock64();
+    if (threadIdx.x == 0 && blockIdx.x < 160) {
+        unsigned long long gt;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+        g_decode_timers[blockIdx.x][10] = gt;
+    }
+#endif
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int tps_g = a.I / 16;                 // gate/up items per expert
+    const int tps_d = a.E / MM_ROWS;            // down items per expert
+    const int nsl = a.K + (a.with_shared ? 1 : 0);
+    const int n_gu = nsl * tps_g, n_dn = nsl * tps_d;
+    const int scols_g = a.E / a.bc, scols_d = a.I / a.bc;
+    const size_t scale_off = (size_t)MM_ROWS * MM_PITCH;
+    const size_t stage_bytes = scale_off + 512;
+    uint8_t *stages = smem;
+    uint8_t *actring = smem + MM_NS * stage_bytes;                  // [NS][2][I] F16; gate/up phase: x terms [2][E]
+    const size_t act_bytes = (size_t)a.I * 4;
+    __half *x_h = reinterpret_cast<__half *>(actring);
+    float *red = reinterpret_cast<float *>(actring + MM_NS * act_bytes);
+    uint64_t *full = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(red) + MM_CONS * 16 * 4);
+    uint64_t *empty = full + MM_NS;
+    uint64_t *plan_ready = empty + MM_NS;
+    __shared__ ExpertW s_ew[MM_MAX_SLOTS];       // slot j < K: j-th routed pick; slot K: shared expert
+    __shared__ float s_w[MM_MAX_SLOTS];
+    __shared__ int my_tiles[MM_MAX_ITEMS], my_last[MM_MAX_ITEMS];
+    __shared__ float wmax[MM_THREADS / 32];
+    __shared__ float x_scale[2];
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < MM_NS; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], MM_CONS); }
+        mbar_init(plan_ready, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (threadIdx.x == 32 && a.with_shared) s_ew[a.K] = a.experts[a.NE];
+    __syncthreads();
+
+    // item g of the gate/up list -> (slot, row tile); shared expert first
+    auto gu_slot = [&](int g, int &slot, int &rt) {
+        if (a.with_shared) {
+            if (g < tps_g) { slot = a.K; rt = g; }
+            else { slot = (g - tps_g) / tps_g; rt = (g - tps_g) % tps_g; }
+        } else { slot = g / tps_g; rt = g % tps_g; }
+    };
+    bool ok = true;
+
+    if (warp == MM_CONS) {
+        // ================================================================ producer ====
+        int it = 0;
+        bool have_plan = false;
+        float bias_r[DEC_PER];                       // the selection bias does not depend on the scores: fetch it now
+#pragma unroll
+        for (int i = 0; i < DEC_PER; i++) bias_r[i] = lane + 32 * i < a.NE ? a.bias[lane + 32 * i] : 0.f;
+        // The producer selects the experts (every CTA for itself; the result is the same everywhere)
+        // while the consumers multiply what is already in flight: wait for all router rows, then
+        // top-k of score + bias by repeated arg-max, lowest index on ties.
+        auto make_plan = [&]() -> bool {
+            if (!grid_wait(a, 0, 6)) return false;
+            DT_MARK_P(9);
+            // scores and choices stay in registers (expert lane + 32 i in slot i): one round of loads,
+            // no shared-memory traffic between the rounds
+            float sc[DEC_PER];
+            uint32_t key[DEC_PER];
+#pragma unroll
+            for (int i = 0; i < DEC_PER; i++) {
+                const int e = lane + 32 * i;
+                sc[i] = e < a.NE ? __ldcg(a.score + e) : 0.f;
+            }
+#pragma unroll
+            for (int i = 0; i < DEC_PER; i++) key[i] = lane + 32 * i < a.NE ? choice_key(__fadd_rn(sc[i], bias_r[i])) : 0u;
+            int my_pick = 0;
+            float my_w = 0.f;
+#ifdef G5B_STAGE_TIMERS
+            if (__shfl_xor_sync(0xffffffffu, key[0], 1) == 12345u) my_w = 1.f;
+            DT_MARK_P(12);
+#endif
+            // K rounds of arg-max: the largest key of the warp, then the lowest expert holding it
+            for (int j = 0; j < a.K; j++) {
+                uint32_t m = 0u;
+#pragma unroll
+                for (int i = 0; i < DEC_PER; i++) m = max(m, key[i]);
+                m = __reduce_max_sync(0xffffffffu, m);
+                uint32_t cand = 0xffffffffu;
+#pragma unroll
+                for (int i = 0; i < DEC_PER; i++) cand = min(cand, key[i] == m ? (uint32_t)(lane + 32 * i) : 0xffffffffu);
+                uint32_t bi = __reduce_min_sync(0xffffffffu, cand);
+                if (m == 0u) bi = 0u;                                  // nothing selectable is left
+                float wsel = 0.f;
+#pragma unroll
+                for (int i = 0; i < DEC_PER; i++)
+                    if (bi == (uint32_t)(lane + 32 * i)) { wsel = sc[i]; key[i] = 0u; }
+                wsel = __shfl_sync(0xffffffffu, wsel, bi & 31);
+                if (lane == j) { my_pick = (int)bi; my_w = wsel; }
+            }
+            DT_MARK_P(13);
+            if (lane < a.K) {                         // the K pointer records are fetched side by side
+                s_ew[lane] = a.experts[my_pick];
+                if (blockIdx.x == 0) a.idx[lane] = my_pick;
+            }
+            DT_MARK_P(14);
+            if (a.norm_topk) {
+                double tot = 0.0;
+                for (int j = 0; j < a.K; j++) tot += (double)__shfl_sync(0xffffffffu, my_w, j);
+                my_w = (float)((double)my_w / (tot + 1e-20));
+            }
+            my_w = __fmul_rn(my_w, a.routed_scale);
+            if (lane < a.K) {
+                s_w[lane] = my_w;
+                if (blockIdx.x == 0) a.w[lane] = my_w;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(plan_ready);
+            __syncwarp();
+            DT_MARK_P(1);
+            return true;
+        };
+        for (int g = blockIdx.x; g < n_gu && ok; g += gridDim.x) {
+            int slot, rt;
+            gu_slot(g, slot, rt);
+            if (slot != a.K && !have_plan) {
+                ok = make_plan();
+                if (!ok) break;
+                have_plan = true;
+            }
+            const ExpertW ew = s_ew[slot];
+            for (int kh = 0; kh < a.E / MM_CB && ok; kh++, it++) {
+                const int s = it % MM_NS;
+                if (it >= MM_NS) ok = mbar_wait(&empty[s], ((it / MM_NS) - 1) & 1, a.err, 1);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                uint8_t *st = stages + (size_t)s * stage_bytes;
+                if (lane == 0) mbar_expect_tx(&full[s], MM_ROWS * MM_CB + 2 * scols_g * 4);
+                __syncwarp();
+                const uint8_t *src = (lane < 16 ? ew.gate : ew.up) + (size_t)(rt * 16 + (lane & 15)) * a.E + (size_t)kh * MM_CB;
+                bulk_g2s(st + (size_t)lane * MM_PITCH, src, MM_CB, &full[s]);
+                if (lane == 0) {
+                    bulk_g2s(st + scale_off, ew.gate_s + (size_t)((rt * 16) / a.br) * scols_g, scols_g * 4, &full[s]);
+                    bulk_g2s(st + scale_off + 256, ew.up_s + (size_t)((rt * 16) / a.br) * scols_g, scols_g * 4, &full[s]);
+                }
+            }
+        }
+        if (ok && !have_plan && n_dn > 0) {          // a CTA with nothing but shared rows still needs the plan below
+            ok = make_plan();
+            have_plan = ok;
+        }
+        // down: weights are prefetched before the activations exist; their copy follows the grid point
+        bool acts_visible = false;
+        int pending = 0, pend_stage[MM_NS], pend_slot[MM_NS];
+        for (int g = blockIdx.x; g < n_dn && ok; g += gridDim.x, it++) {
+            const int slot = g / tps_d, rt = g % tps_d;
+            const ExpertW ew = s_ew[slot];
+            const int s = it % MM_NS;
+            if (it >= MM_NS) ok = mbar_wait(&empty[s], ((it / MM_NS) - 1) & 1, a.err, 1);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            uint8_t *st = stages + (size_t)s * stage_bytes;
+            if (lane == 0) mbar_expect_tx(&full[s], MM_ROWS * MM_CB + scols_d * 4 + (uint32_t)act_bytes);
+            __syncwarp();
+            bulk_g2s(st + (size_t)lane * MM_PITCH, ew.down + (size_t)(rt * MM_ROWS + lane) * a.I, MM_CB, &full[s]);
+            if (lane == 0)
+                bulk_g2s(st + scale_off, ew.down_s + (size_t)((rt * MM_ROWS) / a.br) * scols_d, scols_d * 4, &full[s]);
+            pend_stage[pending] = s; pend_slot[pending] = slot; pending++;
+            const bool last = g + (int)gridDim.x >= n_dn;
+            if (!acts_visible && (pending == MM_NS || last)) {
+                ok = grid_wait(a, 1, 7);
+                if (!ok) break;
+                acts_visible = true;
+            }
+            if (acts_visible) {
+                if (lane == 0)
+                    for (int k = 0; k < pending; k++)
+                        bulk_g2s(actring + (size_t)pend_stage[k] * act_bytes,
+                                 reinterpret_cast<const uint8_t *>(a.act) + (size_t)pend_slot[k] * act_bytes,
+                                 (uint32_t)act_bytes, &full[pend_stage[k]]);
+                pending = 0;
+            }
+        }
+        if (!ok) {
+            // Copies in flight must land before shared memory goes away. A stage whose activation
+            // copy was never issued cannot complete; give it its missing bytes from the buffer
+            // (whatever it holds) so that the barrier closes, then wait for every stage in flight.
+            if (lane == 0)
+                for (int k = 0; k < pending; k++)
+                    bulk_g2s(actring + (size_t)pend_stage[k] * act_bytes, reinterpret_cast<const uint8_t *>(a.act),
+                             (uint32_t)act_bytes, &full[pend_stage[k]]);
+            for (int k = 0; k < MM_NS && k < it; k++) {
+                const int j = it - 1 - k;
+                mbar_wait(&full[j % MM_NS], (j / MM_NS) & 1, a.err, 3);
+            }
+        }
+    } else {
+        // =============================================================== consumers ====
+        const int mt = warp & 1, kq = warp >> 1;
+        const int g8 = lane >> 2, t4 = lane & 3;
+        const int ctid = threadIdx.x;                     // 0..255
+        // ---- router rows first (every CTA waits for all of them): two rows per pass, each row split
+        // over four warps so that all of its loads are in flight at once; FP64 partial sums are
+        // added in a fixed order, then the float sigmoid
+        {
+            double *rsum = reinterpret_cast<double *>(red);           // [8] partial sums, red is idle here
+            const int quarter = warp & 3, which = warp >> 2, span = a.E / 4;
+            for (int e0 = blockIdx.x; e0 < a.NE; e0 += 2 * gridDim.x) {
+                const int e = e0 + which * gridDim.x;
+                double acc = 0.0;
+                if (e < a.NE) {
+                    if (a.gate_dt == DT_BF16) {
+                        const uint16_t *row = static_cast<const uint16_t *>(a.gate) + (size_t)e * a.E + (size_t)quarter * span;
+                        const float *xq = a.x + (size_t)quarter * span;
+#pragma unroll 4
+                        for (int c = lane * 8; c < span; c += 256) {
+                            const uint4 wv = ld_stream16(row + c);
+                            const float4 x0 = *reinterpret_cast<const float4 *>(xq + c), x1 = *reinterpret_cast<const float4 *>(xq + c + 4);
+                            float w[8];
+                            bf16x2_to_f32(wv.x, w[0], w[1]); bf16x2_to_f32(wv.y, w[2], w[3]);
+                            bf16x2_to_f32(wv.z, w[4], w[5]); bf16x2_to_f32(wv.w, w[6], w[7]);
+                            acc = fma((double)w[0], (double)x0.x, acc); acc = fma((double)w[1], (double)x0.y, acc);
+                            acc = fma((double)w[2], (double)x0.z, acc); acc = fma((double)w[3], (double)x0.w, acc);
+                            acc = fma((double)w[4], (double)x1.x, acc); acc = fma((double)w[5], (double)x1.y, acc);
+                            acc = fma((double)w[6], (double)x1.z, acc); acc = fma((double)w[7], (double)x1.w, acc);
+                        }
+                    } else {
+                        const float *row = static_cast<const float *>(a.gate) + (size_t)e * a.E + (size_t)quarter * span;
+                        const float *xq = a.x + (size_t)quarter * span;
+                        for (int i = lane; i < span; i += 32) acc = fma((double)row[i], (double)xq[i], acc);
+                    }
+                }
+                acc = warp_sum(acc);
+                if (lane == 0) rsum[warp] = acc;
+                asm volatile("bar.sync 1, %0;" ::"r"(MM_CONS * 32) : "memory");
+                if (ctid < 2 && e0 + ctid * (int)gridDim.x < a.NE) {
+                    const double t = ((rsum[4 * ctid] + rsum[4 * ctid + 1]) + rsum[4 * ctid + 2]) + rsum[4 * ctid + 3];
+                    a.score[e0 + ctid * gridDim.x] = sigmoid_host((float)t);
+                }
+                asm volatile("bar.sync 1, %0;" ::"r"(MM_CONS * 32) : "memory");
+            }
+            if (ctid == 0) { __threadfence(); atomicAdd(a.sync + 0, 1ull); }
+        }
+        DT_MARK(0);
+        // ---- activation split (power-of-two scale so that the largest element sits near 2^14)
+        {
+            float m = 0.f;
+            for (int c = ctid * 4; c < a.E; c += MM_CONS * 32 * 4) {
+                const float4 v = *reinterpret_cast<const float4 *>(a.x + c);
+                m = fmaxf(fmaxf(m, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+            if (lane == 0) wmax[warp] = m;
+            asm volatile("bar.sync 1, %0;" ::"r"(MM_CONS * 32) : "memory");
+            if (ctid == 0) {
+                float mm = 0.f;
+                for (int i = 0; i < MM_CONS; i++) mm = fmaxf(mm, wmax[i]);
+                int ex = 0;
+                if (mm > 0.f && mm < INFINITY) frexpf(mm, &ex);
+                x_scale[0] = ldexpf(1.0f, 14 - ex);
+                x_scale[1] = ldexpf(1.0f, ex - 14);
+            }
+            asm volatile("bar.sync 1, %0;" ::"r"(MM_CONS * 32) : "memory");
+            const float sc = x_scale[0];
+            for (int c = ctid; c < a.E; c += MM_CONS * 32) {
+                __half hi, mid;
+                split_f16(a.x[c] * sc, hi, mid);
+                x_h[c] = hi;
+                x_h[a.E + c] = mid;
+            }
+            asm volatile("bar.sync 1, %0;" ::"r"(MM_CONS * 32) : "memory");
+        }
+        DT_MARK(6);
+        int it = 0;
+#ifdef G5B_STAGE_TIMERS
+        bool seen_routed = false;
+#endif
+
+        // ---- gate/up items
+        for (int g = blockIdx.x; g < n_gu && ok; g += gridDim.x) {
+            int slot, rt;
+            gu_slot(g, slot, rt);
+            float accf[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int kh = 0; kh < a.E / MM_CB && ok; kh++, it++) {
+                const int s = it % MM_NS;
+                ok = mbar_wait_warp(&full[s], (it / MM_NS) & 1, a.err, 2);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+#ifdef G5B_STAGE_TIMERS
+                if (it == 0) DT_MARK(7);
+                if (slot != a.K && !seen_routed) { DT_MARK(8); seen_routed = true; }
+#endif
+                const uint8_t *st = stages + (size_t)s * stage_bytes;
+                const float *sc = reinterpret_cast<const float *>(st + scale_off) + (mt ? 64 : 0);
+                mma_consume_stage(accf, st, sc, x_h + (size_t)g8 * a.E, kh * MM_CB, a.bc, mt, kq, g8, t4);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[s]);
+            }
+            if (!ok) break;
+            if (t4 == 0) {
+                red[warp * 16 + g8] = accf[0] + accf[1] * (1.0f / 2048.0f);
+                red[warp * 16 + g8 + 8] = accf[2] + accf[3] * (1.0f / 2048.0f);
+            }
+            asm volatile("bar.sync 1, %0;" ::"r"(MM_CONS * 32) : "memory");
+            if (ctid < 16) {
+                const int r = ctid;
+                float gsum = 0.f, usum = 0.f;
+#pragma unroll
+                for (int q = 0; q < 4; q++) { gsum += red[(2 * q) * 16 + r]; usum += red[(2 * q + 1) * 16 + r]; }
+                const float inv = x_scale[1];
+                float gv = gsum * inv, uv = usum * inv;
+                gv = gv > a.limit ? a.limit : gv;
+                uv = uv > a.limit ? a.limit : (uv < -a.limit ? -a.limit : uv);
+                const float act = __fmul_rn(__fmul_rn(gv, sigmoid_host(gv)), uv);
+                __half hi, mid;
+                split_f16(act, hi, mid);
+                __half *dst = a.act + (size_t)slot * 2 * a.I;
+                dst[rt * 16 + r] = hi;
+                dst[a.I + rt * 16 + r] = mid;
+            }
+            asm volatile("bar.sync 1, %0;" ::"r"(MM_CONS * 32) : "memory");
+        }
+        // ---- grid point 1: this CTA's activations are written
+        __threadfence();
+        asm volatile("bar.sync 1, %0;" ::"r"(MM_CONS * 32) : "memory");
+        if (ctid == 0) atomicAdd(a.sync + 1, 1ull);
+        DT_MARK(2);
+        bool first_down = true;
+
+        // ---- down items (the stage's full barrier covers the activation terms too)
+        for (int g = blockIdx.x; g < n_dn && ok; g += gridDim.x, it++) {
+            const int slot = g / tps_d, rt = g % tps_d;
+            const int s = it % MM_NS;
+            ok = mbar_wait_warp(&full[s], (it / MM_NS) & 1, a.err, 2);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            if (first_down) { DT_MARK(3); first_down = false; }
+            const uint8_t *st = stages + (size_t)s * stage_bytes;
+            const float *sc = reinterpret_cast<const float *>(st + scale_off);
+            const __half *xt = reinterpret_cast<const __half *>(actring + (size_t)s * act_bytes) + (size_t)g8 * a.I;
+            float accf[4] = {0.f, 0.f, 0.f, 0.f};
+            mma_consume_stage(accf, st, sc, xt, 0, a.bc, mt, kq, g8, t4);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+            if (t4 == 0) {
+                red[warp * 16 + g8] = accf[0] + accf[1] * (1.0f / 2048.0f);
+                red[warp * 16 + g8 + 8] = accf[2] + accf[3] * (1.0f / 2048.0f);
+            }
+            asm volatile("bar.sync 1, %0;" ::"r"(MM_CONS * 32) : "memory");
+            if (ctid < 32) {
+                const int r = ctid, m2 = r >> 4, rr = r & 15;
+                float v = 0.f;
+#pragma unroll
+                for (int q = 0; q < 4; q++) v += red[(2 * q + m2) * 16 + rr];
+                a.contrib[(size_t)slot * a.E + rt * MM_ROWS + r] = v;
+            }
+            asm volatile("bar.sync 1, %0;" ::"r"(MM_CONS * 32) : "memory");
+        }
+        DT_MARK(4);
+        if (ok) {                                  // the combine needs the router weights of the plan
+            ok = mbar_wait_warp(plan_ready, 0, a.err, 8);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok) {
+            // ---- combine: report every row tile this CTA wrote; whoever completes a tile sums its K
+            // contributions in top-k order in FP64 and adds the shared expert in FP32
+            __threadfence();
+            asm volatile("bar.sync 1, %0;" ::"r"(MM_CONS * 32) : "memory");
+            int mine = 0;
+            for (int g = blockIdx.x; g < n_dn; g += gridDim.x) mine++;
+            if (mine > MM_MAX_ITEMS) { if (ctid == 0) atomicExch(a.err, 4); mine = 0; }
+            if (ctid < mine) {
+                const int rt = (blockIdx.x + ctid * gridDim.x) % tps_d;
+                const int prev = atomicAdd(&a.tile_done[rt], 1);
+                my_tiles[ctid] = rt;
+                my_last[ctid] = prev == nsl - 1;
+                if (prev == nsl - 1) a.tile_done[rt] = 0;
+            }
+            asm volatile("bar.sync 1, %0;" ::"r"(MM_CONS * 32) : "memory");
+            __threadfence();
+            for (int k = warp; k < mine; k += MM_CONS) {
+                if (!my_last[k]) continue;
+                const int d = my_tiles[k] * MM_ROWS + lane;
+                double sum = 0.0;
+                for (int j = 0; j < a.K; j++) sum += (double)s_w[j] * (double)__ldcg(a.contrib + (size_t)j * a.E + d);
+                float o = (float)sum;
+                if (a.with_shared) o = __fadd_rn(o, __ldcg(a.contrib + (size_t)a.K * a.E + d));
+                a.out[d] = o;
+            }
+        }
+        DT_MARK(5);
+    }
+#ifdef G5B_STAGE_TIMERS
+    __syncthreads();
+    if (threadIdx.x == 0 && blockIdx.x < 160) {
+        unsigned long long gt;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+        g_decode_timers[blockIdx.x][11] = gt;
+    }
+#endif
+}
+
+#ifdef G5B_STAGE_TIMERS
+extern "C" int g5b_debug_decode_timers(unsigned long long *dst)
+{
+    return cudaMemcpyFromSymbol(dst, g_decode_timers, sizeof g_decode_timers) == cudaSuccess ? 0 : -1;
+}
+#endif
+
+static size_t decode_smem_bytes(int I)
+{
+    return MM_NS * ((size_t)MM_ROWS * MM_PITCH + 512) + MM_NS * (size_t)I * 4 + MM_CONS * 16 * 4 + 8 * sizeof(uint64_t) + 64;
+}
+
+// Needs: the shapes of moe_mma_supported, two stages per gate/up item (so that the last stage is
+// idle while the plan is made), the activation terms of the gate/up phase fitting the down
+// phase's activation ring, all experts on this GPU, and a device that can launch cooperatively
+// with every SM available to this process.
+bool moe_decode_supported(const MoeShape &s, int T)
+{
+    if (!moe_mma_supported(s, T)) return false;
+    if (s.n_local != s.NE || s.NE > 32 * DEC_PER || s.K > 32 || s.K + 1 > MM_MAX_SLOTS) return false;
+    if (s.E / MM_CB > MM_NS - 1 || s.I != MM_CB) return false;
+    if ((size_t)s.E * 4 > MM_NS * (size_t)s.I * 4) return false;
+    if (decode_smem_bytes(s.I) > 226 * 1024) return false;
+    static int coop = -1, sms = 0, fits = 0;
+    if (coop < 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        cudaFuncSetAttribute(moe_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem_bytes(s.I));
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&fits, moe_decode_kernel, MM_THREADS, decode_smem_bytes(s.I));
+        cudaGetLastError();
+    }
+    return coop == 1 && fits >= 1 && sms >= 1;
+}
+
+int moe_decode(cudaStream_t st, float *out, const float *x, const void *gate, int gate_dt, const float *bias,
+               const ExpertW *experts, float *score, int *idx, float *w, void *act, float *contrib,
+               const MoeShape &s, int with_shared, unsigned long long *sync, unsigned long long *launches,
+               int *tile_done, int *err)
+{
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    DecodeArgs a{experts, x, gate, gate_dt, bias, score, idx, w, static_cast<__half *>(act), contrib, out,
+                 s.E, s.I, s.NE, s.K, s.br, s.bc, with_shared, s.norm_topk, s.limit, s.routed_scale,
+                 sync, (*launches) * (unsigned long long)sms, tile_done, err};
+    void *params[] = {&a};
+    cudaError_t rc;
+#ifdef G5B_STAGE_TIMERS
+    if (getenv("G5B_PLAIN_LAUNCH")) {            // development only: compare launch paths
+        moe_decode_kernel<<<sms, MM_THREADS, decode_smem_bytes(s.I), st>>>(a);
+        rc = cudaGetLastError();
+    } else
+#endif
+    rc = cudaLaunchCooperativeKernel((const void *)moe_decode_kernel, dim3(sms), dim3(MM_THREADS), params,
+                                     decode_smem_bytes(s.I), st);
+    if (rc != cudaSuccess) { cudaGetLastError(); return -1; }
+    ++(*launches);
+    ++g_launches;
+    return 0;
+}
+
+}  // namespace g5b

@@ -16,15 +16,10 @@
 // warp = (M tile of 16 rows) x (quarter of the stage's columns); the four column quarters of a
 // row are added at the end of a work item in a fixed order. Block scales are applied every 128
 // columns in FP32, as the reference factors its FP8 product (src/core/glm53f_ops.c:185-228).
-#include "bulk.cuh"
 #include "kernels.h"
+#include "mma_stage.cuh"
 
 namespace g5b {
-
-constexpr int MM_ROWS = 32, MM_CB = 2048, MM_PITCH = MM_CB + 64, MM_NS = 3, MM_CONS = 8;
-constexpr int MM_THREADS = (MM_CONS + 1) * 32;
-constexpr int MM_MAX_ITEMS = 32;
-constexpr int MM_MAX_SLOTS = 17;             // experts per token (top-k + shared) this path serves
 
 struct MmaArgs {
     const ExpertW *experts;
@@ -39,28 +34,6 @@ struct MmaArgs {
     int *tile_done;
     int *err;
 };
-
-__device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t two_codes)
-{
-    uint32_t r;
-    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(r) : "h"((unsigned short)two_codes));
-    return r;
-}
-
-__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                        uint32_t b0, uint32_t b1)
-{
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-// x = hi + mid / 2048 with hi, mid in F16: 22 significant bits of x (given |x| < 65504).
-__device__ __forceinline__ void split_f16(float x, __half &hi, __half &mid)
-{
-    hi = __float2half_rn(x);
-    mid = __float2half_rn((x - __half2float(hi)) * 2048.0f);
-}
 
 #ifdef G5B_STAGE_TIMERS
 // Development aid (never in a normal build): per CTA, cycles spent in the prologue, by the producer
@@ -210,39 +183,15 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_mma_kernel(const MmaArgs a)
             for (int kh = 0; kh < KH && ok; kh++, it++) {
                 const int s = it % MM_NS;
                 const long long t0 = TIMER_NOW();
-                ok = mbar_wait(&full[s], (it / MM_NS) & 1, a.err, 2);
+                ok = mbar_wait_warp(&full[s], (it / MM_NS) & 1, a.err, 2);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 const long long t1 = TIMER_NOW();
                 t_wait += t1 - t0;
                 const uint8_t *st = stages + (size_t)s * stage_bytes;
                 const float *sc = reinterpret_cast<const float *>(st + scale_off) + ((GATEUP && mt) ? 64 : 0);
-                const uint8_t *w0p = st + (size_t)(mt * 16 + g) * MM_PITCH + kq * 512 + 16 * t;
-                const uint8_t *w1p = w0p + 8 * MM_PITCH;
-                const int col0 = kh * MM_CB + kq * 512 + 16 * t;     // column of this lane's first piece in the row
                 const __half *xt = GATEUP ? x_h + (size_t)g * a.E : reinterpret_cast<const __half *>(st + act_off) + (size_t)g * a.I;
-                float c[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                for (int step = 0; step < 8; step++) {
-                    const uint4 w0 = *reinterpret_cast<const uint4 *>(w0p + step * 64);
-                    const uint4 w1 = *reinterpret_cast<const uint4 *>(w1p + step * 64);
-                    uint4 xa = make_uint4(0u, 0u, 0u, 0u), xb = xa;
-                    if (g < 2) {
-                        xa = *reinterpret_cast<const uint4 *>(xt + col0 + step * 64);
-                        xb = *reinterpret_cast<const uint4 *>(xt + col0 + step * 64 + 8);
-                    }
-                    const uint32_t wa[4] = {w0.x, w0.y, w0.z, w0.w}, wb[4] = {w1.x, w1.y, w1.z, w1.w};
-                    const uint32_t xr[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
-#pragma unroll
-                    for (int m = 0; m < 4; m++)
-                        mma_f16(c, e4m3x2_to_f16x2(wa[m]), e4m3x2_to_f16x2(wb[m]), e4m3x2_to_f16x2(wa[m] >> 16),
-                                e4m3x2_to_f16x2(wb[m] >> 16), xr[2 * m], xr[2 * m + 1]);
-                    if (((kq * 512 + (step + 1) * 64) % a.bc) == 0) {        // a scale block ends here
-                        const float sv = sc[(kh * MM_CB + kq * 512 + step * 64) / a.bc];
-#pragma unroll
-                        for (int i = 0; i < 4; i++) { accf[i] = fmaf(c[i], sv, accf[i]); c[i] = 0.f; }
-                    }
-                }
+                mma_consume_stage(accf, st, sc, xt, kh * MM_CB, a.bc, mt, kq, g, t);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[s]);
                 t_work += TIMER_NOW() - t1;

@@ -160,7 +160,7 @@ __global__ void __launch_bounds__((NW + 1) * 32, 1) moe_stream_kernel(const Stre
             for (int q = 0; q < RPW; q++) acc[q] = 0.f;
             for (int kh = 0; kh < KH && ok; kh++, it++) {
                 const int s = it % ST_NS;
-                ok = mbar_wait(&full[s], (it / ST_NS) & 1, a.err, 2);
+                ok = mbar_wait_warp(&full[s], (it / ST_NS) & 1, a.err, 2);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 const uint8_t *st = stages + (size_t)s * stage_bytes;
