@@ -39,7 +39,9 @@ GATEUP_BYTES = 2 * 2048 * 4096 + 2 * 16 * 32 * 4            # what the gate/up k
 ROUTER_BYTES = 288 * 4096 * 2                               # BF16 router matrix
 FLUSH_BYTES = 512 << 20                                     # two halves, each > 126 MB of L2: write one, read the other
 # dram__bytes_read.sum + dram__bytes_write.sum of one gate/up launch at batch 1 (profiles/), or None
+# DRAM bytes (read + write) per launch from the ncu captures summarised under profiles/
 GATEUP_TRAFFIC_NCU = None
+DECODE_TRAFFIC_NCU = 233.9e6      # moe_decode_kernel: 231.8 MB captured with 32 resident experts + 2.1 MB for 256 more router rows
 
 
 def measured_peaks():
@@ -66,6 +68,14 @@ class ClockSampler:
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
+
+    def wait_first(self, timeout=8.0):
+        """nvidia-smi takes a second or so to print its first line; the timed region is short, so wait
+        for the sampler to be running before the region starts and drop what it saw until then."""
+        t0 = time.time()
+        while self.proc and not self.rows and time.time() - t0 < timeout:
+            time.sleep(0.02)
+        self.rows.clear()
 
     def _read(self):
         for line in self.proc.stdout:
@@ -234,17 +244,18 @@ def main():
         torch.cuda.synchronize()
 
     # ---- headline: batch 1, device resident
-    barrier()
     sampler.start()
+    sampler.wait_first()
+    barrier()
     each, phases, launches, _ = time_batch(pkg, eng, torch, 1, args.steps, warmup)
     barrier()
-    total_ms = float(each.sum())
-    if world > 1:
-        t = torch.tensor([total_ms], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms = float(t.item())
-    ms_per_step = total_ms / args.steps
-    value = world * 1 * 1e3 / ms_per_step
+    import importlib
+    rep = importlib.import_module("glm53f_b200.replicas")
+    local_ms_per_step = float(each.sum()) / args.steps
+    job = rep.whole_job_rate(units_local=args.steps, seconds_local=float(each.sum()) * 1e-3,
+                             dist=dist if world > 1 else None, device="cuda")
+    ms_per_step = job["seconds"] * 1e3 / args.steps          # the slowest rank's
+    value = job["rate"]                                      # tokens of all ranks / slowest rank's time
 
     # ---- end to end: host buffers (pinned) through the C-ABI op, H2D and D2H inside the timing
     xh = torch.from_numpy(synth.moe_inputs(spec.cfg, 1, SEED)).pin_memory()
@@ -263,28 +274,37 @@ def main():
         t0 = time.perf_counter()
         assert L.g5b_op_moe(eng.handle, 0, xn.ctypes.data, 1, on.ctypes.data, 1) == 0
         e2e_s += time.perf_counter() - t0
-    if world > 1:
-        t = torch.tensor([e2e_s], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
+    e2e_job = rep.whole_job_rate(units_local=args.steps, seconds_local=e2e_s, dist=dist if world > 1 else None,
+                                 device="cuda")
+    e2e_s = e2e_job["seconds"]
     clocks = sampler.stop()       # sampled over the device-timed and the end-to-end regions
-    e2e = {"value": world * args.steps / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": int(xn.nbytes),
+    e2e = {"value": e2e_job["rate"], "unit": "tokens/s", "h2d_bytes_per_step": int(xn.nbytes),
            "d2h_bytes_per_step": int(on.nbytes), "ms_per_step": 1e3 * e2e_s / args.steps}
 
-    # ---- roofline of the dominant kernel (gate/up + SwiGLU of the 8 routed + 1 shared experts)
+    # ---- roofline of the dominant kernel
     router_bytes = args.experts * 4096 * 2
+    layer_bytes = 9 * EXPERT_BYTES + router_bytes
     peak, peak_kind = measured_peaks()
-    gateup_ms = phases[1]
-    achieved = 9 * GATEUP_BYTES / (gateup_ms * 1e-3) / 1e9 if gateup_ms > 0 else 0.0
-    roofline = {"bound": "hbm", "kernel": "moe_mma_kernel<gate/up> (8 routed + 1 shared expert, batch 1)",
-                "achieved": achieved, "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s",
-                "frac": achieved / peak, "traffic": GATEUP_TRAFFIC_NCU,
-                "algorithmic_bytes_per_launch": 9 * GATEUP_BYTES, "ms_per_launch": gateup_ms,
-                "layer": {"algorithmic_bytes_per_step": 9 * EXPERT_BYTES + router_bytes,
-                          "achieved": (9 * EXPERT_BYTES + router_bytes) / (ms_per_step * 1e-3) / 1e9,
-                          "frac": (9 * EXPERT_BYTES + router_bytes) / (ms_per_step * 1e-3) / 1e9 / peak}}
+    layer = {"algorithmic_bytes_per_step": layer_bytes, "achieved": layer_bytes / (local_ms_per_step * 1e-3) / 1e9,
+             "frac": layer_bytes / (local_ms_per_step * 1e-3) / 1e9 / peak}
+    if launches == args.steps:
+        # one launch per step: the whole layer (router matrix, 8 routed + 1 shared expert) in one kernel
+        roofline = {"bound": "hbm", "kernel": "moe_decode_kernel (router + top-8 + 8 routed and 1 shared expert + combine, batch 1)",
+                    "achieved": layer["achieved"], "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s",
+                    "frac": layer["frac"], "traffic": DECODE_TRAFFIC_NCU, "algorithmic_bytes_per_launch": layer_bytes,
+                    "ms_per_launch": local_ms_per_step, "layer": layer}
+    else:
+        gateup_ms = phases[1]
+        achieved = 9 * GATEUP_BYTES / (gateup_ms * 1e-3) / 1e9 if gateup_ms > 0 else 0.0
+        roofline = {"bound": "hbm", "kernel": "gate/up + SwiGLU kernel of the chosen expert path (8 routed + 1 shared expert, batch 1)",
+                    "achieved": achieved, "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s",
+                    "frac": achieved / peak, "traffic": GATEUP_TRAFFIC_NCU,
+                    "algorithmic_bytes_per_launch": 9 * GATEUP_BYTES, "ms_per_launch": gateup_ms, "layer": layer}
 
-    extra = {"phase_ms_b1": {"router+plan": phases[0], "gate_up": phases[1], "down": phases[2], "combine": phases[3]}}
+    if launches == args.steps:
+        extra = {"phase_ms_b1": {"moe_decode_kernel": phases[0]}}
+    else:
+        extra = {"phase_ms_b1": {"router+plan": phases[0], "gate_up": phases[1], "down": phases[2], "combine": phases[3]}}
     if rank == 0:
         for B in [int(b) for b in args.batches.split(",") if b]:
             eb, ph, _, _ = time_batch(pkg, eng, torch, B, max(10, args.steps // 10), 3)
