@@ -194,6 +194,64 @@ def time_batch(pkg, eng, torch, B, steps, warmup, flush=FLUSH_BYTES):
     return timed, phases, int(launches), out
 
 
+def time_attention_layers(pkg, torch, steps: int, peak: float, device: int = 0):
+    """The third benchmark configuration: one full-size KDA layer (32 and 64 heads) and one MLA layer
+    with the indexer at contexts 2048 / 8192 / 32768, one new token, device-resident, L2 flushed
+    before every call. Bytes = the layer's weights as stored + recurrent state read and written
+    (KDA) or the latent rows and pooled keys read (MLA)."""
+    import synth
+    L = pkg.lib()
+    out = {}
+
+    def weight_bytes(tensors):
+        return int(sum(a.nbytes + (0 if sc is None else sc.nbytes) for a, _, sc in tensors.values()))
+
+    def run(eng, op, x, cached, n):
+        xd = torch.from_numpy(x).cuda(); od = torch.empty_like(xd)
+        each = np.zeros(max(n, 3), np.float32); tot = C.c_float(0)
+        for k in (3, n):
+            assert L.g5b_time_op(eng.handle, op, 0, xd.data_ptr(), 1, cached, od.data_ptr(), k, FLUSH_BYTES,
+                                 C.byref(tot), each.ctypes.data) == 0, L.g5b_last_error()
+        return float(np.mean(each[:n]))
+
+    rng = np.random.default_rng(SEED)
+    for H in (32, 64):
+        spec = synth.layer_spec("kda", kda_heads=H)
+        tensors = synth.make_model(spec, seed=4, recipe="baseline")
+        eng = pkg.Engine(spec.cfg, spec.is_mla, spec.is_dense, 8, device)
+        eng.set_option("allow_partial", 1)
+        eng.load_all(tensors); eng.finalize()
+        D = spec.cfg.kda_head_dim
+        state_bytes = 4 * (H * D * D + 3 * H * D * (spec.cfg.conv_k - 1))
+        x = synth.bf16_round(rng.standard_normal((1, spec.cfg.hidden)).astype(np.float32))
+        ms = run(eng, b"kda", x, 0, steps)
+        nbytes = weight_bytes(tensors) + 2 * state_bytes
+        out[f"kda_H{H}"] = {"ms": ms, "algorithmic_bytes": nbytes, "achieved_GBps": nbytes / (ms * 1e-3) / 1e9,
+                            "frac": nbytes / (ms * 1e-3) / 1e9 / peak}
+        eng.close()
+    spec = synth.layer_spec("mla")
+    c = spec.cfg
+    cap = 32768
+    tensors = synth.make_model(spec, seed=5, recipe="spread")
+    eng = pkg.Engine(c, spec.is_mla, spec.is_dense, cap, device)
+    eng.set_option("allow_partial", 1)
+    eng.set_option("latent_bf16", 1)
+    eng.load_all(tensors); eng.finalize()
+    lat = synth.bf16_round(rng.standard_normal((cap, c.kv_lora)).astype(np.float32))
+    idx = rng.standard_normal(2 * cap * c.index_dim + (cap // c.index_kpool) * c.index_dim).astype(np.float32)
+    eng.state_write(0, 1, 0, lat)
+    eng.state_write(0, 2, 0, idx)
+    x = synth.bf16_round(rng.standard_normal((1, c.hidden)).astype(np.float32))
+    for ctx in (2048, 8192, 32768):
+        ms = run(eng, b"mla", x, ctx - 1, steps)
+        visible = min(ctx, c.index_topk + c.index_kpool - 1)
+        nbytes = weight_bytes(tensors) + visible * c.kv_lora * 2 + (ctx // c.index_kpool) * c.index_dim * 4
+        out[f"mla_ctx{ctx}"] = {"ms": ms, "algorithmic_bytes": nbytes, "achieved_GBps": nbytes / (ms * 1e-3) / 1e9,
+                                "frac": nbytes / (ms * 1e-3) / 1e9 / peak, "latent": "bf16"}
+    eng.close()
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -205,6 +263,8 @@ def main():
                     help="routed experts resident in the layer (288 = the stated config; fewer only to keep "
                          "an ncu capture small: the batch-1 kernels touch 8 routed + 1 shared either way)")
     ap.add_argument("--batches", default="8,64", help="extra batch sizes reported under 'extra'")
+    ap.add_argument("--no-attention-layers", action="store_true",
+                    help="skip the KDA / MLA single-layer timings reported under 'extra'")
     ap.add_argument("--stream-warps", type=int, default=0, help="consumer warps of the streamed CUDA-core kernels (8/16)")
     ap.add_argument("--expert-path", type=int, default=-1,
                     help="batch-1 expert kernels: 0 register-streaming, 1 bulk-copy + CUDA cores, 2 bulk-copy + tensor cores, 3 whole layer in one kernel (default)")
@@ -315,6 +375,8 @@ def main():
                                   "achieved_GBps": ((distinct + 1) * EXPERT_BYTES + ROUTER_BYTES) / (ms * 1e-3) / 1e9,
                                   "phase_ms": ph}
     eng.close()
+    if rank == 0 and not args.no_attention_layers and args.experts == 288:
+        extra["config3"] = time_attention_layers(pkg, torch, max(10, args.steps // 10), peak, local)
 
     cpu = None
     if rank == 0 and not args.no_cpu_baseline and args.experts == 288:

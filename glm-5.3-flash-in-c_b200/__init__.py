@@ -317,6 +317,19 @@ class Engine(FlatModel):
                                          d.ctypes.data) != 0:
             self._err("fill_expert")
 
+    def ep_export(self) -> bytes:
+        """This rank's exchange-region handle (g5b_engine_ep_export), to be gathered from all ranks."""
+        buf = C.create_string_buffer(self.L.g5b_engine_ep_handle_bytes())
+        if self.L.g5b_engine_ep_export(self.handle, buf) != 0:
+            self._err("ep_export")
+        return buf.raw
+
+    def ep_connect(self, handles):
+        """Map every rank's exchange region (handles in rank order, this rank's own included)."""
+        blob = b"".join(handles)
+        if self.L.g5b_engine_ep_connect(self.handle, blob) != 0:
+            self._err("ep_connect")
+
     def decode_greedy(self, first: int, n: int):
         out = np.zeros(n, np.int32)
         if self.L.g5b_engine_decode_greedy(self.handle, first, n, out.ctypes.data) != 0:

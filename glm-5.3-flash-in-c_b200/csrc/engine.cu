@@ -39,6 +39,7 @@ void set_last_error(const char *msg) { snprintf(g_err, sizeof g_err, "%s", msg);
         if (e_ != cudaSuccess) return fail("%s: %s", #call, cudaGetErrorString(e_));       \
     } while (0)
 
+constexpr size_t EP_FLAG_BYTES = 1024;   // exchange region: the ranks' step words, then the row buffers
 constexpr int CHUNK = 64;       // positions one pass of a layer works on (the reference's MoE chunk, glm53f_ops.c:988)
 constexpr int PROF_SLOTS = 8;
 
@@ -79,6 +80,14 @@ struct g5b_engine {
     g5b_config c;
     int cap = 0, cached = 0, device = 0, ep_rank = 0, ep_size = 1, n_local0 = 0, n_local = 0;
     bool finalized = false, ep_connected = false;
+    // expert-parallel exchange region of this rank: ep_size 64-bit words, then two row buffers
+    uint8_t *ep_region = nullptr;
+    size_t ep_rows_bytes = 0;
+    void **ep_peers_dev = nullptr;
+    std::vector<void *> ep_opened;               // peer mappings to close
+    std::vector<void *> ep_standins;             // local stand-ins for peers (option ep_loopback)
+    unsigned long long ep_step = 0;
+    int *ep_arrive = nullptr;
     int latent_bf16 = 0, profile = 0, partial = 0, stream_experts = 3, stream_warps = 8;
     unsigned long long *grid_sync = nullptr, grid_launches = 0;
     int *counter = nullptr, *tile_done = nullptr, *err_dev = nullptr;
@@ -246,6 +255,7 @@ extern "C" g5b_engine *g5b_engine_create(const g5b_config *cfg, const uint8_t *i
     return e;
 }
 
+static int ep_loopback(g5b_engine *e);
 extern "C" int g5b_engine_set_option(g5b_engine *e, const char *name, int value)
 {
     if (!strcmp(name, "latent_bf16")) {
@@ -255,6 +265,7 @@ extern "C" int g5b_engine_set_option(g5b_engine *e, const char *name, int value)
     }
     if (!strcmp(name, "profile")) { e->profile = value; return 0; }
     if (!strcmp(name, "allow_partial")) { e->partial = value != 0; return 0; }
+    if (!strcmp(name, "ep_loopback")) return value ? ep_loopback(e) : 0;
     if (!strcmp(name, "stream_experts")) {       // batch-1 experts: 0 register kernels, 1 streamed CUDA-core,
                                                  // 2 streamed tensor-core, 3 the whole layer as one kernel
         if (value < 0 || value > 3) return fail("stream_experts is 0, 1, 2 or 3");
@@ -602,7 +613,17 @@ static int run_moe(g5b_engine *e, Layer &w, const float *x, int n, float *out, i
         swiglu(e->st, e->dact, e->gu, SI, n, c.swiglu_limit);
         gemv(e->st, w.sh_down, e->dact, SI, e->contrib + (size_t)n * c.topk * c.hidden, c.hidden, n);
     }
-    moe_combine(e->st, out, c.hidden, e->contrib, e->rw, n, s, with_shared);
+    if (e->ep_size > 1) {
+        // every rank computed the rows of the picks it owns: gather all rows everywhere and combine
+        ++e->ep_step;
+        EpExchange x{e->contrib, e->plan, e->ep_peers_dev, e->ep_rank, e->ep_size, n, c.topk, c.hidden, with_shared,
+                     EP_FLAG_BYTES + (size_t)(e->ep_step & 1) * e->ep_rows_bytes, e->ep_step, e->ep_arrive, e->rw,
+                     out, c.hidden, e->err_dev};
+        const int want = (int)(((size_t)n * c.hidden + 255) / 256);
+        ep_exchange_combine(e->st, x, want < 8 ? 8 : want > 148 ? 148 : want);
+    } else {
+        moe_combine(e->st, out, c.hidden, e->contrib, e->rw, n, s, with_shared);
+    }
     prof_mark(e, 4);
     prof_collect(e, 4);
     return 0;
@@ -717,6 +738,7 @@ static int check_device_error(g5b_engine *e)
         // the grid-wide counters and tile counters of the interrupted launch are unusable: start over
         cudaMemsetAsync(e->grid_sync, 0, 2 * sizeof(unsigned long long), e->st);
         cudaMemsetAsync(e->tile_done, 0, ((size_t)e->c.hidden / 32 + 1) * sizeof(int), e->st);
+        if (e->ep_arrive) cudaMemsetAsync(e->ep_arrive, 0, sizeof(int), e->st);
         cudaStreamSynchronize(e->st);
         e->grid_launches = 0;
         return fail("a device-side wait timed out (code %d); the result of this call is invalid", code);
@@ -837,6 +859,9 @@ extern "C" void g5b_engine_free(g5b_engine *e)
     cudaSetDevice(e->device);
     cudaStreamSynchronize(e->st);
     for (void *p : e->owned) cudaFree(p);
+    for (void *p : e->ep_opened) cudaIpcCloseMemHandle(p);
+    for (void *p : e->ep_standins) cudaFree(p);
+    if (e->ep_region) cudaFree(e->ep_region);
     if (e->h) cudaFree(e->h);
     if (e->ids_dev) cudaFree(e->ids_dev);
     if (e->flush_buf) cudaFree(e->flush_buf);
@@ -1278,16 +1303,83 @@ extern "C" int g5b_engine_profile_read(g5b_engine *e, float *ms, int n, long *co
 }
 
 // ------------------------------------------------------------- expert parallel ----
+
+static int ep_alloc(g5b_engine *e)
+{
+    if (e->ep_region) return 0;
+    e->ep_rows_bytes = (size_t)CHUNK * e->c.topk * e->c.hidden * 4;
+    const size_t bytes = EP_FLAG_BYTES + 2 * e->ep_rows_bytes;
+    CU(cudaMalloc((void **)&e->ep_region, bytes));       // an allocation of its own: it is what peers map
+    CU(cudaMemset(e->ep_region, 0, bytes));
+    if (e->dalloc((void **)&e->ep_peers_dev, sizeof(void *) * (size_t)e->ep_size)) return -1;
+    if (e->dalloc((void **)&e->ep_arrive, sizeof(int))) return -1;
+    CU(cudaStreamSynchronize(e->st));
+    return 0;
+}
+
+static int ep_publish_peers(g5b_engine *e, const std::vector<void *> &peers)
+{
+    CU(cudaMemcpy(e->ep_peers_dev, peers.data(), sizeof(void *) * peers.size(), cudaMemcpyHostToDevice));
+    e->ep_connected = true;
+    e->ep_step = 0;
+    return 0;
+}
+
 extern "C" size_t g5b_engine_ep_handle_bytes(void) { return sizeof(cudaIpcMemHandle_t); }
+
 extern "C" int g5b_engine_ep_export(g5b_engine *e, void *handle_out)
 {
-    (void)handle_out;
-    if (e->ep_size == 1) return 0;
-    return fail("expert-parallel exchange is not wired in this build");
+    if (!e || !handle_out) return fail("null argument");
+    if (e->ep_size == 1) { memset(handle_out, 0, sizeof(cudaIpcMemHandle_t)); return 0; }
+    if (!e->finalized) return fail("export the exchange handle after finalize");
+    CU(cudaSetDevice(e->device));
+    if (ep_alloc(e)) return -1;
+    CU(cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t *>(handle_out), e->ep_region));
+    return 0;
 }
+
 extern "C" int g5b_engine_ep_connect(g5b_engine *e, const void *all_handles)
 {
-    (void)all_handles;
+    if (!e) return fail("null engine");
     if (e->ep_size == 1) return 0;
-    return fail("expert-parallel exchange is not wired in this build");
+    if (!all_handles) return fail("null handle array");
+    if (!e->finalized) return fail("connect after finalize");
+    if (e->ep_connected) return fail("the ranks are already connected");
+    CU(cudaSetDevice(e->device));
+    if (ep_alloc(e)) return -1;
+    const cudaIpcMemHandle_t *h = static_cast<const cudaIpcMemHandle_t *>(all_handles);
+    std::vector<void *> peers((size_t)e->ep_size, nullptr);
+    for (int r = 0; r < e->ep_size; r++) {
+        if (r == e->ep_rank) { peers[r] = e->ep_region; continue; }
+        void *p = nullptr;
+        const cudaError_t rc = cudaIpcOpenMemHandle(&p, h[r], cudaIpcMemLazyEnablePeerAccess);
+        if (rc != cudaSuccess) {
+            cudaGetLastError();
+            return fail("rank %d cannot map rank %d's exchange region: %s", e->ep_rank, r, cudaGetErrorString(rc));
+        }
+        e->ep_opened.push_back(p);
+        peers[r] = p;
+    }
+    return ep_publish_peers(e, peers);
 }
+
+// Stand-in peers in this GPU's own memory that nobody ever writes: lets one GPU exercise the
+// delivery code and the bounded wait (which then runs out and is reported), nothing else.
+static int ep_loopback(g5b_engine *e)
+{
+    if (e->ep_size == 1) return 0;
+    if (!e->finalized) return fail("ep_loopback after finalize");
+    if (e->ep_connected) return fail("the ranks are already connected");
+    if (ep_alloc(e)) return -1;
+    std::vector<void *> peers((size_t)e->ep_size, nullptr);
+    for (int r = 0; r < e->ep_size; r++) {
+        if (r == e->ep_rank) { peers[r] = e->ep_region; continue; }
+        void *p = nullptr;
+        CU(cudaMalloc(&p, EP_FLAG_BYTES + 2 * e->ep_rows_bytes));
+        CU(cudaMemset(p, 0, EP_FLAG_BYTES + 2 * e->ep_rows_bytes));
+        e->ep_standins.push_back(p);
+        peers[r] = p;
+    }
+    return ep_publish_peers(e, peers);
+}
+

@@ -1,0 +1,105 @@
+// ep_exchange.cu - the exchange step of an expert-parallel MoE layer, fused with the combine.
+//
+// Every rank (one process per GPU) holds the replicated activations and 1/ep_size of the routed
+// experts, routes every token itself (same inputs, same picks on every rank) and computes the
+// contribution rows of the picks whose experts it owns. This kernel then
+//   1. stores each of those rows into the exchange buffer of EVERY rank (its own included) with
+//      plain 16-byte stores over NVLink peer mappings - an all-gather of contribution rows with no
+//      library call and no staging copy,
+//   2. publishes "rank r has delivered step s" as one 64-bit word in every rank's flag array
+//      (system-scope fence, then the store, by the last CTA to finish its rows),
+//   3. waits - bounded - until every rank's word for this step has arrived here, and
+//   4. combines: out[t][d] = (float) sum_j w[t][j] * row[t*K+j][d] in FP64 in top-k order, plus the
+//      shared expert's row (computed on every rank) in FP32: the arithmetic of the one-GPU combine
+//      and of the reference (src/core/glm53f_ops.c:1329-1340), so the result does not depend on
+//      the number of ranks.
+//
+// Two exchange buffers alternate by step parity: a rank can be at most one step ahead of a peer
+// (its next combine needs that peer's next word), so rows of step s+1 never land in a buffer
+// that a slower peer still reads for step s. A wait that runs out sets the error word in mapped
+// host memory and the CTA returns without combining; nothing is left in flight.
+#include "kernels.h"
+#include "common.cuh"
+
+namespace g5b {
+
+constexpr int EP_SPIN_LIMIT = 1 << 21;         // about a second at the poll interval below
+
+__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long *p)
+{
+    unsigned long long v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned long long *p, unsigned long long v)
+{
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+
+__global__ void __launch_bounds__(256) ep_exchange_combine_kernel(const EpExchange a)
+{
+    __shared__ int s_flag;                                      // this CTA finished last
+    const int tid = threadIdx.x;
+    const size_t row_f4 = (size_t)a.E / 4;
+    const int routed_rows = a.T * a.K;
+    const int ns = *a.plan.n_slots;
+    const int total = ns > 0 ? a.plan.slot_off[ns - 1] + a.plan.slot_cnt[ns - 1] : 0;
+
+    // ---- 1. deliver this rank's rows to every rank
+    for (int p = blockIdx.x; p < total; p += gridDim.x) {
+        const int row = a.plan.pair_dst[p];
+        if (row >= routed_rows) continue;                       // the shared expert's rows stay local
+        const float4 *src = reinterpret_cast<const float4 *>(a.contrib + (size_t)row * a.E);
+        for (int r = 0; r < a.size; r++) {
+            float4 *dst = reinterpret_cast<float4 *>(static_cast<uint8_t *>(a.peers[r]) + a.rows_off) + (size_t)row * row_f4;
+            for (size_t i = tid; i < row_f4; i += blockDim.x) dst[i] = src[i];
+        }
+    }
+    // ---- 2. the last CTA to finish publishes this rank's word on every rank
+    __threadfence_system();
+    __syncthreads();
+    if (tid == 0) {
+        const int prev = atomicAdd(a.arrive, 1);
+        s_flag = prev == (int)gridDim.x - 1;
+    }
+    __syncthreads();
+    if (s_flag) {
+        if (tid == 0) *a.arrive = 0;
+        __threadfence_system();
+        if (tid < a.size) {
+            unsigned long long *flags = reinterpret_cast<unsigned long long *>(a.peers[tid]);
+            st_release_sys(flags + a.rank, a.step);
+        }
+    }
+    // ---- 3. wait for every rank's word (bounded); thread r watches rank r
+    bool seen = true;
+    if (tid < a.size) {
+        const unsigned long long *mine = reinterpret_cast<const unsigned long long *>(a.peers[a.rank]);
+        seen = false;
+        for (int i = 0; i < EP_SPIN_LIMIT && !seen; i++) {
+            seen = ld_acquire_sys(mine + tid) >= a.step;
+            if (!seen) __nanosleep(100);
+        }
+        if (!seen) atomicExch(a.err, 20 + tid);                 // which rank never delivered
+    }
+    if (!__syncthreads_and(seen)) return;
+    // ---- 4. combine from the local exchange buffer
+    const float *rows = reinterpret_cast<const float *>(static_cast<const uint8_t *>(a.peers[a.rank]) + a.rows_off);
+    const size_t n = (size_t)a.T * a.E;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + tid; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const int t = (int)(i / a.E), d = (int)(i % a.E);
+        double s = 0.0;
+        for (int j = 0; j < a.K; j++)
+            s += (double)a.w[(size_t)t * a.K + j] * (double)__ldcg(rows + ((size_t)t * a.K + j) * a.E + d);
+        float o = (float)s;
+        if (a.with_shared) o = __fadd_rn(o, a.contrib[((size_t)routed_rows + t) * a.E + d]);
+        a.out[(size_t)t * a.ldo + d] = o;
+    }
+}
+
+void ep_exchange_combine(cudaStream_t st, const EpExchange &a, int ctas)
+{
+    G5B_LAUNCH(ep_exchange_combine_kernel, dim3(ctas), 256, 0, st, a);
+}
+
+}  // namespace g5b

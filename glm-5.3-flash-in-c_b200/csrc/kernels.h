@@ -129,6 +129,24 @@ void moe_down(cudaStream_t st, float *contrib, const float *act, const ExpertW *
 void moe_combine(cudaStream_t st, float *out, int ldo, const float *contrib, const float *w, int T,
                  const MoeShape &s, int with_shared);
 
+// ---- ep_exchange.cu ------------------------------------------------------------------------
+// Expert-parallel exchange + combine. peers[r] is rank r's exchange region as mapped in this
+// process: ep_size 64-bit words (word q = last step rank q delivered), then at rows_off the
+// buffer of this step's parity, [T*K][E] floats.
+struct EpExchange {
+    const float *contrib;          // local contribution rows [T*K + T][E] (shared expert's rows last)
+    MoePlan plan;                  // local slots; pair_dst < T*K are the rows to deliver
+    void *const *peers;            // device array [size]
+    int rank, size, T, K, E, with_shared;
+    size_t rows_off;
+    unsigned long long step;       // this call's number, the same on every rank, starting at 1
+    int *arrive;                   // local counter, zero between launches
+    const float *w;                // router weights [T][K]
+    float *out; int ldo;
+    int *err;
+};
+void ep_exchange_combine(cudaStream_t st, const EpExchange &a, int ctas);
+
 // ---- kda.cu -------------------------------------------------------------------------------
 struct KdaShape { int H, D, K; float gate_lb, rms_eps; };
 // q,k,v,z,gb: [T][H*D] projections (q,k,v before the short convolution); braw [T][H]; state as

@@ -1,0 +1,111 @@
+"""Expert-parallel MoE layers: the exchange of contribution rows between ranks.
+
+One GPU: the delivery code runs against stand-in peers that never answer, so the bounded wait
+runs out and the call reports it (the failure is made by a flag that nothing sets; no fault, no
+hang). Two GPUs (skipped when the box has one): two processes, one engine each, own halves of the
+experts, exchange over peer mappings, results against the one-GPU CPU path.
+"""
+import os
+
+import numpy as np
+import pytest
+
+import common
+import synth
+
+pkg = synth.pkg
+pytestmark = pytest.mark.gpu
+
+
+def _tiny():
+    spec = synth.tiny_spec()
+    return spec, synth.make_model(spec, seed=11, recipe="baseline")
+
+
+def test_unanswered_exchange_times_out_and_is_reported(gpu_lib, binding):
+    spec, tensors = _tiny()
+    eng = pkg.Engine(spec.cfg, spec.is_mla, spec.is_dense, 32, 0, 0, 2)     # rank 0 of 2
+    eng.load_all(tensors); eng.finalize()
+    moe_layer = next(l for l in range(spec.cfg.n_layers) if not spec.is_dense[l])
+    x = synth.moe_inputs(spec.cfg, 2, 3)
+    with pytest.raises(RuntimeError, match="connect the ranks"):
+        eng.op_moe(moe_layer, x)
+    eng.set_option("ep_loopback", 1)
+    with pytest.raises(RuntimeError, match="timed out"):
+        eng.op_moe(moe_layer, x)
+    eng.close()
+    # the context is still usable: a one-GPU engine on the same device gives the CPU path's output
+    one, orc = common.build_models(spec, tensors, 32, binding)
+    assert common.rel_err(one.op_moe(moe_layer, x), orc.op_moe(moe_layer, x)) < 1e-5
+    one.close(); orc.close()
+
+
+def _rank_main(rank, world, conn, peers_conn):
+    """Child process: one rank of an expert-parallel pair. Results go back through `conn`."""
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    sys.path.insert(0, os.path.dirname(here)); sys.path.insert(0, here)
+    import numpy as np
+    import synth as sy
+    import common as cm
+    from oracle import binding
+    try:
+        spec = sy.tiny_spec()
+        tensors = sy.make_model(spec, seed=11, recipe="baseline")
+        eng = sy.pkg.Engine(spec.cfg, spec.is_mla, spec.is_dense, 32, rank, rank, world)
+        eng.load_all(tensors); eng.finalize()
+        conn.send(("handle", eng.ep_export()))
+        handles = conn.recv()
+        eng.ep_connect(handles)
+        orc = binding.OracleModel(spec.cfg, spec.is_mla, spec.is_dense, 32, 2)
+        orc.load_all(tensors); orc.finalize()
+        moe_layer = next(l for l in range(spec.cfg.n_layers) if not spec.is_dense[l])
+        worst = 0.0
+        for T, seed in ((1, 1), (4, 2), (1, 3), (7, 4), (32, 5)):
+            x = sy.moe_inputs(spec.cfg, T, seed)
+            worst = max(worst, cm.rel_err(eng.op_moe(moe_layer, x), orc.op_moe(moe_layer, x)))
+        ids = np.random.default_rng(0).integers(0, spec.cfg.vocab, 18).tolist()
+        lg, _ = eng.forward(ids)
+        lw, _ = orc.forward(ids)
+        fw = cm.rel_err(lg, lw)
+        steps = []
+        for _ in range(4):
+            tok = int(np.argmax(lg)); assert tok == int(np.argmax(lw))
+            lg, _ = eng.forward([tok]); lw, _ = orc.forward([tok])
+            steps.append(cm.rel_err(lg, lw))
+        eng.close(); orc.close()
+        conn.send(("ok", worst, fw, max(steps)))
+    except Exception as exc:                                   # report instead of dying silently
+        conn.send(("error", repr(exc)))
+
+
+def test_two_ranks_exchange_and_match_the_cpu_path(gpu_lib):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    world = 2
+    pipes = [ctx.Pipe() for _ in range(world)]
+    procs = [ctx.Process(target=_rank_main, args=(r, world, pipes[r][1], None)) for r in range(world)]
+    for p in procs:
+        p.start()
+    try:
+        handles = []
+        for r in range(world):
+            assert pipes[r][0].poll(300), "rank did not export its handle"
+            msg = pipes[r][0].recv()
+            assert msg[0] == "handle", msg
+            handles.append(msg[1])
+        for r in range(world):
+            pipes[r][0].send(handles)
+        for r in range(world):
+            assert pipes[r][0].poll(300), "rank did not finish"
+            msg = pipes[r][0].recv()
+            assert msg[0] == "ok", msg
+            assert msg[1] < 1e-5 and msg[2] < 1e-3 and msg[3] < 1e-3, msg
+    finally:
+        for p in procs:
+            p.join(timeout=60)
+            if p.is_alive():
+                p.kill()
