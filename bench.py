@@ -163,7 +163,7 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
-def time_batch(pkg, eng, torch, B, steps, warmup, flush=FLUSH_BYTES):
+def time_batch(pkg, eng, torch, B, steps, warmup, flush=FLUSH_BYTES, phases=True):
     """Device-resident timing of the MoE layer at batch B: (ms per step list, phase ms, launches)."""
     import synth
     L = pkg.lib()
@@ -181,6 +181,8 @@ def time_batch(pkg, eng, torch, B, steps, warmup, flush=FLUSH_BYTES):
                          C.byref(tot), each.ctypes.data) == 0, L.g5b_last_error()
     launches = L.g5b_launch_count() - n0 - (2 * steps if flush else 0)
     timed = each[:steps].astype(float)
+    if not phases:
+        return timed, [0.0] * 4, int(launches), out
     # per-phase times in a separate short pass: the phase events make the host wait inside every
     # step, which would inflate the step time measured above
     eng.set_option("profile", 1)
@@ -263,6 +265,8 @@ def main():
                     help="routed experts resident in the layer (288 = the stated config; fewer only to keep "
                          "an ncu capture small: the batch-1 kernels touch 8 routed + 1 shared either way)")
     ap.add_argument("--batches", default="8,64", help="extra batch sizes reported under 'extra'")
+    ap.add_argument("--no-expert-parallel", action="store_true",
+                    help="N > 1: skip the expert-parallel timing of the layer reported under 'extra'")
     ap.add_argument("--no-attention-layers", action="store_true",
                     help="skip the KDA / MLA single-layer timings reported under 'extra'")
     ap.add_argument("--stream-warps", type=int, default=0, help="consumer warps of the streamed CUDA-core kernels (8/16)")
@@ -377,6 +381,29 @@ def main():
     eng.close()
     if rank == 0 and not args.no_attention_layers and args.experts == 288:
         extra["config3"] = time_attention_layers(pkg, torch, max(10, args.steps // 10), peak, local)
+
+    # ---- N > 1: the same layer expert-parallel (288 / N routed experts per rank, activations and the
+    # shared expert replicated, contribution rows exchanged over peer mappings): one token stream
+    # served by all ranks together, i.e. the latency side of the N-GPU trade-off
+    if world > 1 and 288 % world == 0 and not args.no_expert_parallel:
+        spec_ep = synth.layer_spec("moe", n_experts=args.experts)
+        trunk_ep = synth.moe_layer_trunk(spec_ep, SEED)
+        ep = pkg.Engine(spec_ep.cfg, spec_ep.is_mla, spec_ep.is_dense, 8, local, rank, world)
+        ep.set_option("allow_partial", 1)
+        ep.load_all(trunk_ep)
+        for ex in range(args.experts):
+            ep.fill_expert(0, ex, SEED, *synth.expert_scales(spec_ep.cfg, 0, ex, SEED))
+        ep.finalize()
+        handles = [None] * world
+        dist.all_gather_object(handles, ep.ep_export())
+        ep.ep_connect(handles)
+        barrier()
+        ep_each, _, _, _ = time_batch(pkg, ep, torch, 1, args.steps, warmup, phases=False)
+        barrier()
+        ep_ms = rep.max_over_ranks(float(ep_each.mean()), dist, "cuda")
+        ep.close()
+        extra["expert_parallel_b1"] = {"ranks": world, "ms_per_step": ep_ms, "tokens_per_s": 1e3 / ep_ms,
+                                       "routed_experts_per_rank": args.experts // world}
 
     cpu = None
     if rank == 0 and not args.no_cpu_baseline and args.experts == 288:

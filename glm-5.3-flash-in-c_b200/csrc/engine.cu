@@ -582,6 +582,26 @@ static int run_moe(g5b_engine *e, Layer &w, const float *x, int n, float *out, i
     router_plan(e->st, e->ridx, e->rw, e->rscore, x, c.hidden, w.router.w, w.router.dt, w.bias, n, s, e->plan,
                 shared_in_plan ? 1 : 0, e->counter);
     prof_mark(e, 1);
+    auto exchange_and_combine = [&]() {
+        // every rank computed the rows of the picks it owns: gather all rows everywhere and combine
+        ++e->ep_step;
+        EpExchange x{e->contrib, e->plan, e->ep_peers_dev, e->ep_rank, e->ep_size, n, c.topk, c.hidden, with_shared,
+                     EP_FLAG_BYTES + (size_t)(e->ep_step & 1) * e->ep_rows_bytes, e->ep_step, e->ep_arrive, e->rw,
+                     out, c.hidden, e->err_dev};
+        const int want = (int)(((size_t)n * c.hidden + 255) / 256);
+        ep_exchange_combine(e->st, x, want < 8 ? 8 : want > 148 ? 148 : want);
+    };
+    if (e->ep_size > 1 && e->stream_experts >= 2 && (shared_in_plan || !with_shared) && moe_mma_supported(s, n)) {
+        // batch 1 across ranks: the tensor-core kernels on this rank's picks, contributions only
+        moe_mma_gateup(e->st, e->act, x, w.table_dev, e->plan, s, e->err_dev);
+        prof_mark(e, 2);
+        moe_mma_down(e->st, nullptr, e->contrib, e->act, e->rw, w.table_dev, e->plan, s, with_shared, e->tile_done, e->err_dev);
+        prof_mark(e, 3);
+        exchange_and_combine();
+        prof_mark(e, 4);
+        prof_collect(e, 4);
+        return 0;
+    }
     if (e->stream_experts == 2 && one_gpu_decode && moe_mma_supported(s, n)) {
         moe_mma_gateup(e->st, e->act, x, w.table_dev, e->plan, s, e->err_dev);
         prof_mark(e, 2);
@@ -614,13 +634,7 @@ static int run_moe(g5b_engine *e, Layer &w, const float *x, int n, float *out, i
         gemv(e->st, w.sh_down, e->dact, SI, e->contrib + (size_t)n * c.topk * c.hidden, c.hidden, n);
     }
     if (e->ep_size > 1) {
-        // every rank computed the rows of the picks it owns: gather all rows everywhere and combine
-        ++e->ep_step;
-        EpExchange x{e->contrib, e->plan, e->ep_peers_dev, e->ep_rank, e->ep_size, n, c.topk, c.hidden, with_shared,
-                     EP_FLAG_BYTES + (size_t)(e->ep_step & 1) * e->ep_rows_bytes, e->ep_step, e->ep_arrive, e->rw,
-                     out, c.hidden, e->err_dev};
-        const int want = (int)(((size_t)n * c.hidden + 255) / 256);
-        ep_exchange_combine(e->st, x, want < 8 ? 8 : want > 148 ? 148 : want);
+        exchange_and_combine();
     } else {
         moe_combine(e->st, out, c.hidden, e->contrib, e->rw, n, s, with_shared);
     }
