@@ -140,8 +140,15 @@ int  g5b_engine_cached(const g5b_engine *e);  /* positions consumed so far */
  * logits to the host and takes the argmax there). out receives n token ids. */
 int g5b_engine_decode_greedy(g5b_engine *e, int first, int n, int *out);
 
-/* Expert-parallel wiring for ep_size > 1: every rank exports a handle to its exchange buffer,
- * the caller gathers all handles (any transport) and gives each rank the full table. */
+/* Expert-parallel wiring for ep_size > 1 (no counterpart in the reference, whose device list is a
+ * layer pipeline, src/gpu/glm53f_gpu.c:758-790): after finalize every rank exports a handle to its
+ * exchange region (ep_handle_bytes() bytes, a CUDA IPC handle), the caller gathers all handles in
+ * rank order over any transport and gives each rank the full table. From then on every MoE layer
+ * ends in one kernel that stores this rank's contribution rows into every rank's region through
+ * the peer mappings, waits (bounded; a wait that runs out makes the call return -1) for the other
+ * ranks' rows and combines in top-k order. All ranks must make the same sequence of calls.
+ * Option "ep_loopback" (g5b_engine_set_option) wires stand-in peers in local memory that never
+ * answer: it exists to exercise the time-out report on one GPU. */
 size_t g5b_engine_ep_handle_bytes(void);
 int    g5b_engine_ep_export(g5b_engine *e, void *handle_out);
 int    g5b_engine_ep_connect(g5b_engine *e, const void *all_handles /* ep_size entries */);
