@@ -267,6 +267,8 @@ def main():
     ap.add_argument("--batches", default="8,64", help="extra batch sizes reported under 'extra'")
     ap.add_argument("--no-expert-parallel", action="store_true",
                     help="N > 1: skip the expert-parallel timing of the layer reported under 'extra'")
+    ap.add_argument("--only-attention-layers", action="store_true",
+                    help="run only the KDA / MLA single-layer timings and print them (a small case for ncu)")
     ap.add_argument("--no-attention-layers", action="store_true",
                     help="skip the KDA / MLA single-layer timings reported under 'extra'")
     ap.add_argument("--stream-warps", type=int, default=0, help="consumer warps of the streamed CUDA-core kernels (8/16)")
@@ -293,6 +295,10 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
     warmup = max(3, args.warmup)
+    if args.only_attention_layers:
+        peak, _ = measured_peaks()
+        print(json.dumps({"config3": time_attention_layers(pkg, torch, max(3, args.steps), peak, local)}), flush=True)
+        return
     opts = {}
     if args.stream_warps:
         opts["stream_warps"] = args.stream_warps

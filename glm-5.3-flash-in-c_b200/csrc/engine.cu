@@ -40,6 +40,7 @@ void set_last_error(const char *msg) { snprintf(g_err, sizeof g_err, "%s", msg);
     } while (0)
 
 constexpr size_t EP_FLAG_BYTES = 1024;   // exchange region: the ranks' step words, then the row buffers
+constexpr int MLA_PART_TOKENS = 4;     // tokens whose attention partial sums are held at once
 constexpr int CHUNK = 64;       // positions one pass of a layer works on (the reference's MoE chunk, glm53f_ops.c:988)
 constexpr int PROF_SLOTS = 8;
 
@@ -105,7 +106,7 @@ struct g5b_engine {
     float *inv0, *inv1, *mix, *xc, *xn, *y, *post, *comb;
     float *kq, *kk, *kv, *kz, *kgb, *ko, *kbraw, *klr;
     float *mq_raw, *mct, *mwk, *mgate, *mwp, *mq, *mqidx, *mcb, *macc, *mscore, *minvq;
-    double *mqa, *mdsc;
+    double *mqa, *mdsc, *mpart = nullptr, *mstats = nullptr;
     int   *msel, *mnsel;
     float *rscore, *rw, *act, *contrib, *gu, *dact;
     int   *ridx;
@@ -506,7 +507,9 @@ extern "C" int g5b_engine_finalize(g5b_engine *e)
         walloc(e, &e->mcb, N * H * KL) || walloc(e, &e->macc, N * H * c.v_head) ||
         walloc(e, &e->mscore, N * ((size_t)e->cap / c.index_kpool + 1)) || walloc(e, &e->minvq, N) ||
         walloc(e, &e->mqa, N * H * KL) || walloc(e, &e->mdsc, N * H * stride) ||
-        walloc(e, &e->msel, N * stride) || walloc(e, &e->mnsel, N)) return -1;
+        walloc(e, &e->msel, N * stride) || walloc(e, &e->mnsel, N) ||
+        walloc(e, &e->mstats, N * H * 2) ||
+        walloc(e, &e->mpart, (size_t)MLA_PART_TOKENS * H * ((stride + 63) / 64) * KL)) return -1;
     const size_t pairs = N * K + N;
     if (walloc(e, &e->rscore, N * c.n_experts) || walloc(e, &e->rw, N * K) || walloc(e, &e->ridx, N * K) ||
         walloc(e, &e->act, pairs * (I > SI ? I : SI)) || walloc(e, &e->contrib, pairs * E) ||
@@ -705,7 +708,7 @@ static int run_mla(g5b_engine *e, Layer &w, const float *x, int n, int cached, f
     gemv_batch(e->st, b, 2, n);
     dsa_select(e->st, e->msel, e->mnsel, w.idx_state, e->mqidx, e->mwp, e->mscore, n, cached, s);
     mla_absorb(e->st, e->mqa, e->mq, w.kv_b, n, s);
-    mla_attend(e->st, e->mcb, e->mqa, w.latent, e->msel, e->mnsel, e->mdsc, n, cached, s);
+    mla_attend(e->st, e->mcb, e->mqa, w.latent, e->msel, e->mnsel, e->mdsc, e->mpart, e->mstats, MLA_PART_TOKENS, n, cached, s);
     mla_vout(e->st, e->macc, e->mcb, w.kv_b, n, s);
     gemv(e->st, w.mo, e->macc, c.mla_heads * c.v_head, out, E, n);
     return 0;

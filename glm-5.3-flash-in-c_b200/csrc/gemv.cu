@@ -22,7 +22,7 @@ constexpr int GEMV_WARPS = GEMV_THREADS / 32;
 
 // Fast path: columns a multiple of the 16-byte piece, FP8 column blocks a multiple of 16.
 template <int TT>
-__global__ void __launch_bounds__(GEMV_THREADS) gemv_fast_kernel(const GemvBatch b)
+__global__ void __launch_bounds__(GEMV_THREADS, TT == 1 ? 3 : 2) gemv_fast_kernel(const GemvBatch b)
 {
     int si = 0;
 #pragma unroll 1
@@ -181,9 +181,14 @@ void gemv_batch(cudaStream_t st, const GemvSeg *segs, int n, int T)
     for (int i = 0; i < n; i++) {
         GemvSeg s = segs[i];
         if (seg_is_fast(s)) {
-            // few-row matrices: one CTA per RW rows so that the whole GPU takes part
+            // Matrices whose whole-row grid would not even give every SM a CTA take one CTA per RW
+            // rows, the eight warps splitting the columns, provided a row gives every lane a piece
+            // (measured: with 256 whole-row CTAs available the split is the slower of the two).
             const long bytes = (long)s.R * s.C;
-            s.ksplit = (s.R <= 1024 && bytes >= 32768 && s.C / piece_elems(s.dt) >= 64) ? 1 : 0;
+            const int pieces = s.C / piece_elems(s.dt);
+            const int whole_row_blocks = (s.R + RW * GEMV_WARPS - 1) / (RW * GEMV_WARPS);
+            s.ksplit = (bytes >= 32768 && pieces >= 64 &&
+                        (s.R <= 1024 || (pieces >= GEMV_THREADS && whole_row_blocks < 148))) ? 1 : 0;
             s.block0 = fb;
             fb += s.ksplit ? (s.R + RW - 1) / RW : (s.R + RW * GEMV_WARPS - 1) / (RW * GEMV_WARPS);
             fast.s[fast.n++] = s;

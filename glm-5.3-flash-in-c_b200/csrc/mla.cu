@@ -253,8 +253,36 @@ __global__ void mla_absorb_kernel(double *qa, const float *q, const DMat kv_b, M
     }
 }
 
+// The same sums with the GPU filled: a CTA takes 128 latent columns of one head, its four row
+// groups (64 rows each at qk_nope = 256) accumulate in FP64 and are added in ascending order.
+constexpr int AB_COLS = 128, AB_GROUPS = 4;
+__global__ void __launch_bounds__(AB_COLS * AB_GROUPS) mla_absorb_split_kernel(double *qa, const float *q, const DMat kv_b,
+                                                                              MlaShape s)
+{
+    __shared__ double part[AB_GROUPS][AB_COLS];
+    const int h = blockIdx.x, t = blockIdx.y, c = blockIdx.z * AB_COLS + (threadIdx.x % AB_COLS), grp = threadIdx.x / AB_COLS;
+    const int kvd = s.qn + s.vh, per = s.qn / AB_GROUPS;
+    const float *qt = q + ((size_t)t * s.H + h) * s.qn + grp * per;
+    const uint16_t *w = static_cast<const uint16_t *>(kv_b.w) + ((size_t)h * kvd + (size_t)grp * per) * s.KL + c;
+    double acc = 0.0;
+#pragma unroll 8
+    for (int i = 0; i < per; i++) acc = fma((double)qt[i], (double)bf16_to_f32(w[(size_t)i * s.KL]), acc);
+    part[grp][threadIdx.x % AB_COLS] = acc;
+    __syncthreads();
+    if (grp == 0) {
+        double sum = part[0][threadIdx.x];
+#pragma unroll
+        for (int g = 1; g < AB_GROUPS; g++) sum += part[g][threadIdx.x];
+        qa[((size_t)t * s.H + h) * s.KL + c] = sum;
+    }
+}
+
 void mla_absorb(cudaStream_t st, double *qa, const float *q, const DMat &kv_b, int T, const MlaShape &s)
 {
+    if (kv_b.dt == DT_BF16 && s.KL % AB_COLS == 0 && s.qn % (AB_GROUPS * 8) == 0) {
+        G5B_LAUNCH(mla_absorb_split_kernel, dim3(s.H, T, s.KL / AB_COLS), AB_COLS * AB_GROUPS, 0, st, qa, q, kv_b, s);
+        return;
+    }
     G5B_LAUNCH(mla_absorb_kernel, dim3(s.H, T), s.KL >= 512 ? 512 : 128, 0, st, qa, q, kv_b, s);
 }
 
@@ -280,6 +308,65 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) mla_score_kernel(
         for (int i = lane; i < s.KL; i += 32) d = fma(qs[i], (double)latent_at(latent, s.latent_bf16, (size_t)j * s.KL + i), d);
         d = warp_sum(d);
         if (lane == 0) dsc[((size_t)t * s.H + h) * stride + jj] = d * (double)scale;
+    }
+}
+
+// The same scores for kv_lora = 512 with four heads per CTA: the absorbed queries of the four
+// heads stay in registers (lane l holds elements 2l, 2l+1 of every 64), a latent row is loaded
+// once for the four of them, and the four sums cross the warp in six exchanges instead of twenty.
+constexpr int SC_HEADS = 4, SC_CHUNK = 64;
+__global__ void __launch_bounds__(256) mla_score4_kernel(double *dsc, const double *qa, const void *latent, const int *sel,
+                                                         const int *nsel, int cached, int stride, MlaShape s)
+{
+    const int h0 = blockIdx.y * SC_HEADS, t = blockIdx.z, p = cached + t;
+    const int ns = nsel ? nsel[t] : -1;
+    const int nvis = ns < 0 ? p + 1 : ns;
+    const int j0 = blockIdx.x * SC_CHUNK;
+    if (j0 >= nvis) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    double q[SC_HEADS][16];
+#pragma unroll
+    for (int hh = 0; hh < SC_HEADS; hh++)
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            const double2 v = *reinterpret_cast<const double2 *>(qa + ((size_t)t * s.H + h0 + hh) * s.KL + 64 * k + 2 * lane);
+            q[hh][2 * k] = v.x;
+            q[hh][2 * k + 1] = v.y;
+        }
+    const double scale = (double)(1.0f / sqrtf((float)s.qn));
+    const int *sl = sel ? sel + (size_t)t * (s.topk + s.KP) : nullptr;
+    const int jend = min(j0 + SC_CHUNK, nvis);
+    for (int jj = j0 + warp; jj < jend; jj += 8) {
+        const int j = ns < 0 ? jj : sl[jj];
+        float c[16];
+        if (s.latent_bf16) {
+            const uint32_t *row = reinterpret_cast<const uint32_t *>(static_cast<const uint16_t *>(latent) + (size_t)j * s.KL);
+#pragma unroll
+            for (int k = 0; k < 8; k++) bf16x2_to_f32(row[32 * k + lane], c[2 * k], c[2 * k + 1]);
+        } else {
+            const float2 *row = reinterpret_cast<const float2 *>(static_cast<const float *>(latent) + (size_t)j * s.KL);
+#pragma unroll
+            for (int k = 0; k < 8; k++) { const float2 v = row[32 * k + lane]; c[2 * k] = v.x; c[2 * k + 1] = v.y; }
+        }
+        double a[SC_HEADS] = {0.0, 0.0, 0.0, 0.0};
+#pragma unroll
+        for (int k = 0; k < 16; k++) {
+            const double cd = (double)c[k];
+#pragma unroll
+            for (int hh = 0; hh < SC_HEADS; hh++) a[hh] = fma(q[hh][k], cd, a[hh]);
+        }
+        // four sums across 32 lanes: halve the values a lane carries, twice, then a plain butterfly
+        const bool up16 = lane & 16, up8 = lane & 8;
+        const double r0 = (up16 ? a[2] : a[0]) + __shfl_xor_sync(0xffffffffu, up16 ? a[0] : a[2], 16);
+        const double r1 = (up16 ? a[3] : a[1]) + __shfl_xor_sync(0xffffffffu, up16 ? a[1] : a[3], 16);
+        double v = (up8 ? r1 : r0) + __shfl_xor_sync(0xffffffffu, up8 ? r0 : r1, 8);
+        v += __shfl_xor_sync(0xffffffffu, v, 4);
+        v += __shfl_xor_sync(0xffffffffu, v, 2);
+        v += __shfl_xor_sync(0xffffffffu, v, 1);
+        if ((lane & 7) == 0) {
+            const int hh = ((lane >> 4) << 1) | ((lane >> 3) & 1);
+            dsc[((size_t)t * s.H + h0 + hh) * stride + jj] = v * scale;
+        }
     }
 }
 
@@ -330,17 +417,133 @@ __global__ void __launch_bounds__(512) mla_wsum_kernel(
     }
 }
 
+// The same softmax and weighted sum spread over the whole GPU (the kernel above walks all positions
+// with one CTA per head: 0.44 ms at 2051 positions). Three small launches:
+//   stats   per (head, token): max of the unrounded scores and z = sum exp((double)(float)s - max)
+//   chunk   per (64 positions, 8 heads, token): p_j = exp(.) / z, partial sums of p_j c_j in FP64,
+//           positions ascending; the eight heads share every latent row they load
+//   reduce  per (head, token, column): the chunks' partial sums added in ascending order
+// The association of the FP64 sum differs from the reference's single ascending walk by the chunk
+// boundaries only; the result is rounded to float once, at the end, like the reference's.
+constexpr int WS_CHUNK = 64, WS_HEADS = 8, WS_THREADS = 256;
+
+__global__ void __launch_bounds__(256) mla_softmax_stats_kernel(double *stats, const double *dsc, const int *nsel,
+                                                                int cached, int stride, MlaShape s)
+{
+    __shared__ double red[32];
+    const int h = blockIdx.x, t = blockIdx.y, p = cached + t;
+    const int ns = nsel ? nsel[t] : -1;
+    const int nvis = ns < 0 ? p + 1 : ns;
+    const double *d = dsc + ((size_t)t * s.H + h) * stride;
+    double top = -INFINITY;
+    for (int jj = threadIdx.x; jj < nvis; jj += blockDim.x) top = fmax(top, d[jj]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) top = fmax(top, __shfl_xor_sync(0xffffffffu, top, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = top;
+    __syncthreads();
+    for (int w = 0; w < (int)(blockDim.x >> 5); w++) top = fmax(top, red[w]);
+    __syncthreads();
+    double z = 0.0;
+    for (int jj = threadIdx.x; jj < nvis; jj += blockDim.x) z += exp((double)(float)d[jj] - top);
+    z = block_sum(z, red);
+    if (threadIdx.x == 0) {
+        stats[((size_t)t * s.H + h) * 2] = top;
+        stats[((size_t)t * s.H + h) * 2 + 1] = z;
+    }
+}
+
+__global__ void __launch_bounds__(WS_THREADS) mla_wsum_chunk_kernel(
+    double *part, const double *dsc, const double *stats, const void *latent, const int *sel, const int *nsel,
+    int cached, int stride, int nchunks, MlaShape s)
+{
+    __shared__ double pj[WS_HEADS][WS_CHUNK];
+    __shared__ int idx[WS_CHUNK];
+    const int chunk = blockIdx.x, h0 = blockIdx.y * WS_HEADS, t = blockIdx.z, p = cached + t;
+    const int ns = nsel ? nsel[t] : -1;
+    const int nvis = ns < 0 ? p + 1 : ns;
+    const int j0 = chunk * WS_CHUNK;
+    const int cnt = min(WS_CHUNK, nvis - j0);
+    const int i0 = threadIdx.x, i1 = threadIdx.x + WS_THREADS;         // this thread's two latent columns
+    double acc0[WS_HEADS], acc1[WS_HEADS];
+#pragma unroll
+    for (int q = 0; q < WS_HEADS; q++) { acc0[q] = 0.0; acc1[q] = 0.0; }
+    if (cnt > 0) {
+        const int *sl = sel ? sel + (size_t)t * (s.topk + s.KP) : nullptr;
+        for (int k = threadIdx.x; k < WS_HEADS * WS_CHUNK; k += WS_THREADS) {
+            const int q = k / WS_CHUNK, jj = k % WS_CHUNK;
+            double v = 0.0;
+            if (jj < cnt) {
+                const size_t hs = (size_t)t * s.H + h0 + q;
+                v = exp((double)(float)dsc[hs * stride + j0 + jj] - stats[hs * 2]) / stats[hs * 2 + 1];
+            }
+            pj[q][jj] = v;
+        }
+        for (int jj = threadIdx.x; jj < WS_CHUNK; jj += WS_THREADS) idx[jj] = jj < cnt ? (ns < 0 ? j0 + jj : sl[j0 + jj]) : 0;
+        __syncthreads();
+#pragma unroll 4
+        for (int jj = 0; jj < cnt; jj++) {
+            const size_t row = (size_t)idx[jj] * s.KL;
+            const double c0 = (double)latent_at(latent, s.latent_bf16, row + i0);
+            const double c1 = (double)latent_at(latent, s.latent_bf16, row + i1);
+#pragma unroll
+            for (int q = 0; q < WS_HEADS; q++) {
+                const double pv = pj[q][jj];
+                acc0[q] = fma(pv, c0, acc0[q]);
+                acc1[q] = fma(pv, c1, acc1[q]);
+            }
+        }
+    }
+#pragma unroll
+    for (int q = 0; q < WS_HEADS; q++) {
+        double *dst = part + (((size_t)t * s.H + h0 + q) * nchunks + chunk) * s.KL;
+        dst[i0] = acc0[q];
+        dst[i1] = acc1[q];
+    }
+}
+
+__global__ void __launch_bounds__(256) mla_wsum_reduce_kernel(float *cb, const double *part, int nchunks, int used,
+                                                              int n, int KL)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;                // (t, h, column)
+    if (i >= n) return;
+    const int th = i / KL, col = i % KL;
+    const double *src = part + (size_t)th * nchunks * KL + col;
+    double acc = 0.0;
+    for (int c = 0; c < used; c++) acc += src[(size_t)c * KL];
+    cb[i] = (float)acc;
+}
+
 void mla_attend(cudaStream_t st, float *cb, const double *qa, const void *latent, const int *sel,
-                const int *nsel, double *dsc, int T, int cached, const MlaShape &s)
+                const int *nsel, double *dsc, double *part, double *stats, int part_tokens, int T, int cached,
+                const MlaShape &s)
 {
     const int nvis_max = cached + T < s.topk + s.KP ? cached + T : s.topk + s.KP;
     const int stride = s.topk + s.KP;
     int blocks = (nvis_max + ATT_WARPS - 1) / ATT_WARPS;
     if (blocks > 32) blocks = 32;
-    G5B_LAUNCH(mla_score_kernel, dim3(blocks, s.H, T), ATT_WARPS * 32, (size_t)s.KL * sizeof(double), st, dsc, qa,
-               latent, sel, nsel, cached, stride, s);
-    G5B_LAUNCH(mla_wsum_kernel, dim3(s.H, T), s.KL >= 512 ? 512 : 128, 0, st, cb, dsc, latent, sel, nsel, cached,
-               stride, s);
+    if (s.KL == 512 && s.H % SC_HEADS == 0)
+        G5B_LAUNCH(mla_score4_kernel, dim3((nvis_max + SC_CHUNK - 1) / SC_CHUNK, s.H / SC_HEADS, T), 256, 0, st, dsc, qa,
+                   latent, sel, nsel, cached, stride, s);
+    else
+        G5B_LAUNCH(mla_score_kernel, dim3(blocks, s.H, T), ATT_WARPS * 32, (size_t)s.KL * sizeof(double), st, dsc, qa,
+                   latent, sel, nsel, cached, stride, s);
+    if (s.KL != 2 * WS_THREADS || s.H % WS_HEADS != 0 || !part || part_tokens < 1) {
+        G5B_LAUNCH(mla_wsum_kernel, dim3(s.H, T), s.KL >= 512 ? 512 : 128, 0, st, cb, dsc, latent, sel, nsel, cached,
+                   stride, s);
+        return;
+    }
+    const int nchunks = (stride + WS_CHUNK - 1) / WS_CHUNK;             // the partial buffer is laid out for this many
+    G5B_LAUNCH(mla_softmax_stats_kernel, dim3(s.H, T), 256, 0, st, stats, dsc, nsel, cached, stride, s);
+    for (int t0 = 0; t0 < T; t0 += part_tokens) {
+        const int n = T - t0 < part_tokens ? T - t0 : part_tokens;
+        const int used = (((cached + t0 + n < stride) ? cached + t0 + n : stride) + WS_CHUNK - 1) / WS_CHUNK;
+        G5B_LAUNCH(mla_wsum_chunk_kernel, dim3(used, s.H / WS_HEADS, n), WS_THREADS, 0, st, part,
+                   dsc + (size_t)t0 * s.H * stride, stats + (size_t)t0 * s.H * 2, latent,
+                   sel ? sel + (size_t)t0 * stride : nullptr, nsel ? nsel + t0 : nullptr, cached + t0, stride, nchunks, s);
+        // chunks beyond `used` were not written: reduce over the used ones only
+        G5B_LAUNCH(mla_wsum_reduce_kernel, dim3((n * s.H * s.KL + 255) / 256), 256, 0, st,
+                   cb + (size_t)t0 * s.H * s.KL, part, nchunks, used, n * s.H * s.KL, s.KL);
+    }
 }
 
 // o[t][h][r] = W_v[h][r] . cb[t][h]: the value half of kv_b applied once per query and head
