@@ -107,6 +107,7 @@ struct g5b_engine {
     float *kq, *kk, *kv, *kz, *kgb, *ko, *kbraw, *klr;
     float *mq_raw, *mct, *mwk, *mgate, *mwp, *mq, *mqidx, *mcb, *macc, *mscore, *minvq;
     double *mqa, *mdsc, *mpart = nullptr, *mstats = nullptr;
+    void *xterms = nullptr; float *xinv = nullptr;      // batched expert kernels: F16 terms of the activations
     int   *msel, *mnsel;
     float *rscore, *rw, *act, *contrib, *gu, *dact;
     int   *ridx;
@@ -513,7 +514,8 @@ extern "C" int g5b_engine_finalize(g5b_engine *e)
     const size_t pairs = N * K + N;
     if (walloc(e, &e->rscore, N * c.n_experts) || walloc(e, &e->rw, N * K) || walloc(e, &e->ridx, N * K) ||
         walloc(e, &e->act, pairs * (I > SI ? I : SI)) || walloc(e, &e->contrib, pairs * E) ||
-        walloc(e, &e->gu, N * 2 * DI) || walloc(e, &e->dact, N * DI)) return -1;
+        walloc(e, &e->gu, N * 2 * DI) || walloc(e, &e->dact, N * DI) || walloc(e, &e->xinv, N) ||
+        e->dalloc(&e->xterms, N * 2 * E * 2)) return -1;
     e->plan.max_slots = (int)((N * K < (size_t)e->n_local ? N * K : (size_t)e->n_local) + 1);
     e->plan.max_pairs = (int)pairs;
     if (walloc(e, &e->plan.n_slots, 1) || walloc(e, &e->plan.slot_expert, e->plan.max_slots) ||
@@ -624,10 +626,18 @@ static int run_moe(g5b_engine *e, Layer &w, const float *x, int n, float *out, i
         prof_collect(e, 4);
         return 0;
     }
-    moe_gateup(e->st, e->act, x, c.hidden, w.table_dev, e->plan, n, s);
-    prof_mark(e, 2);
-    moe_down(e->st, e->contrib, e->act, w.table_dev, e->plan, n, s);
-    prof_mark(e, 3);
+    if (e->stream_experts >= 2 && (shared_in_plan || !with_shared) && moe_mma_batch_supported(s, n)) {
+        // batches: the tensor-core pipeline with four tokens per weight stage
+        moe_mma_batch_gateup(e->st, e->act, e->xterms, e->xinv, x, c.hidden, w.table_dev, e->plan, n, s, e->err_dev);
+        prof_mark(e, 2);
+        moe_mma_batch_down(e->st, e->contrib, e->act, w.table_dev, e->plan, n, s, e->err_dev);
+        prof_mark(e, 3);
+    } else {
+        moe_gateup(e->st, e->act, x, c.hidden, w.table_dev, e->plan, n, s);
+        prof_mark(e, 2);
+        moe_down(e->st, e->contrib, e->act, w.table_dev, e->plan, n, s);
+        prof_mark(e, 3);
+    }
     if (with_shared && !shared_in_plan) {
         // a shared expert of another width or format goes through the plain MLP path
         const int SI = c.moe_inter * c.n_shared;

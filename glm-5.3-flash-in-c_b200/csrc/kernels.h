@@ -110,6 +110,13 @@ void moe_mma_gateup(cudaStream_t st, void *act_terms, const float *x, const Expe
 void moe_mma_down(cudaStream_t st, float *out, float *contrib, const void *act_terms, const float *w,
                   const ExpertW *experts, const MoePlan &p, const MoeShape &s, int with_shared, int *tile_done,
                   int *err);
+// Batches of 2..64 tokens on the same pipeline, four tokens per weight stage (moe_mma_batch.cu).
+// xterms: scratch for [T][2][E] F16, xinv: [T] floats. Contributions only; the caller combines.
+bool moe_mma_batch_supported(const MoeShape &s, int T);
+void moe_mma_batch_gateup(cudaStream_t st, void *act_terms, void *xterms, float *xinv, const float *x, int ldx,
+                          const ExpertW *experts, const MoePlan &p, int T, const MoeShape &s, int *err);
+void moe_mma_batch_down(cudaStream_t st, float *contrib, const void *act_terms, const ExpertW *experts,
+                        const MoePlan &p, int T, const MoeShape &s, int *err);
 // The whole batch-1 layer (router, top-k, experts, combine) as one cooperative kernel
 // (moe_decode.cu). `sync` holds two device counters that only grow; `launches` is the host's count of
 // launches so far on them. Returns -1 when the cooperative launch is refused.

@@ -78,4 +78,38 @@ __device__ __forceinline__ void mma_consume_stage(float (&accf)[4], const uint8_
     }
 }
 
+// The same stage against FOUR activation vectors: B column 2p is the hi term of vector p, column
+// 2p + 1 its mid term, so all eight columns carry data and every lane loads a B fragment (row g of
+// the activation tile; rows are XT_PITCH bytes apart: a lane reads two 16-byte pieces 32 bytes
+// apart from its neighbour's, so the two rows of a quarter warp must sit 16 bytes off each other
+// modulo 32 to use all banks once). The tile holds the columns of this stage only.
+// accf[0..1]: row g, vector t (hi, mid); accf[2..3]: row g + 8 - meaningful in every lane.
+constexpr int XT_PITCH = MM_CB * 2 + 16;
+__device__ __forceinline__ void mma_consume_stage_x4(float (&accf)[4], const uint8_t *st, const float *sc,
+                                                     const uint8_t *xtile, int col0, int bc, int mt, int kq, int g, int t)
+{
+    const uint8_t *w0p = st + (size_t)(mt * 16 + g) * MM_PITCH + kq * 512 + 16 * t;
+    const uint8_t *w1p = w0p + 8 * MM_PITCH;
+    const uint8_t *xp = xtile + (size_t)g * XT_PITCH + (size_t)(kq * 512 + 16 * t) * 2;
+    float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int step = 0; step < 8; step++) {
+        const uint4 w0 = *reinterpret_cast<const uint4 *>(w0p + step * 64);
+        const uint4 w1 = *reinterpret_cast<const uint4 *>(w1p + step * 64);
+        const uint4 xa = *reinterpret_cast<const uint4 *>(xp + step * 128);
+        const uint4 xb = *reinterpret_cast<const uint4 *>(xp + step * 128 + 16);
+        const uint32_t wa[4] = {w0.x, w0.y, w0.z, w0.w}, wb[4] = {w1.x, w1.y, w1.z, w1.w};
+        const uint32_t xr[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+        mma_f16(c0, e4m3x2_to_f16x2(wa[0]), e4m3x2_to_f16x2(wb[0]), e4m3x2_to_f16x2(wa[0] >> 16), e4m3x2_to_f16x2(wb[0] >> 16), xr[0], xr[1]);
+        mma_f16(c1, e4m3x2_to_f16x2(wa[1]), e4m3x2_to_f16x2(wb[1]), e4m3x2_to_f16x2(wa[1] >> 16), e4m3x2_to_f16x2(wb[1] >> 16), xr[2], xr[3]);
+        mma_f16(c0, e4m3x2_to_f16x2(wa[2]), e4m3x2_to_f16x2(wb[2]), e4m3x2_to_f16x2(wa[2] >> 16), e4m3x2_to_f16x2(wb[2] >> 16), xr[4], xr[5]);
+        mma_f16(c1, e4m3x2_to_f16x2(wa[3]), e4m3x2_to_f16x2(wb[3]), e4m3x2_to_f16x2(wa[3] >> 16), e4m3x2_to_f16x2(wb[3] >> 16), xr[6], xr[7]);
+        if (((kq * 512 + (step + 1) * 64) % bc) == 0) {        // a scale block ends here
+            const float sv = sc[(col0 + kq * 512 + step * 64) / bc];
+#pragma unroll
+            for (int i = 0; i < 4; i++) { accf[i] = fmaf(c0[i] + c1[i], sv, accf[i]); c0[i] = 0.f; c1[i] = 0.f; }
+        }
+    }
+}
+
 }  // namespace g5b
