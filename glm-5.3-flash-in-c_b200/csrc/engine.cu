@@ -521,7 +521,7 @@ extern "C" int g5b_engine_finalize(g5b_engine *e)
     if (walloc(e, &e->plan.n_slots, 1) || walloc(e, &e->plan.slot_expert, e->plan.max_slots) ||
         walloc(e, &e->plan.slot_off, e->plan.max_slots) || walloc(e, &e->plan.slot_cnt, e->plan.max_slots) ||
         walloc(e, &e->plan.pair_tok, pairs) || walloc(e, &e->plan.pair_dst, pairs)) return -1;
-    if (walloc(e, &e->counter, 4) || walloc(e, &e->tile_done, E / 32 + 1) || walloc(e, &e->grid_sync, 2)) return -1;
+    if (walloc(e, &e->counter, CHUNK + 4) || walloc(e, &e->tile_done, E / 32 + 1) || walloc(e, &e->grid_sync, 2)) return -1;
     {
         int *hp = nullptr;
         CU(cudaHostAlloc((void **)&hp, 64, cudaHostAllocMapped));

@@ -29,6 +29,7 @@ constexpr int MOE_WARPS = MOE_THREADS / 32;
 // index wins ties; weights from the unbiased scores, normalised in FP64, times the routed scale
 // (reference glm53f_router, src/core/glm53f_ops.c:945-976).
 constexpr int RT_WARPS = 4;
+constexpr int RT_MAX_TOKENS = 64;            // tokens per launch (the engine's pass size)
 
 struct RouterArgs {
     int *idx; float *w; float *score;
@@ -42,50 +43,68 @@ struct RouterArgs {
     int *counter;
 };
 
-__device__ void topk_one_token(const RouterArgs &a, int t, float *choice, float *scr, float *wsel, int lane)
+// Order-preserving key of a selection score; 0 = not selectable (NaN, -inf, already taken).
+__device__ __forceinline__ uint32_t choice_key(float v)
 {
-    const float *sc = a.score + (size_t)t * a.NE;
-    for (int e = lane; e < a.NE; e += 32) {
-        const float v = __ldcg(sc + e);
-        scr[e] = v;
-        choice[e] = __fadd_rn(v, a.bias[e]);
-    }
-    __syncwarp();
-    for (int j = 0; j < a.K; j++) {
-        float bv = -INFINITY;
-        int bi = -1;
-        for (int e = lane; e < a.NE; e += 32)
-            if (choice[e] > bv) { bv = choice[e]; bi = e; }
+    if (!(v > -INFINITY)) return 0u;
+    const uint32_t u = __float_as_uint(__fadd_rn(v, 0.f));     // -0 -> +0
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// Top-k of one token by one warp, scores and keys in registers (expert lane + 32 i in slot i): K
+// rounds of "largest key of the warp, then the lowest expert holding it" with warp reductions.
+template <int PER>
+__device__ void topk_one_token(const RouterArgs &a, int t, int lane)
+{
+    const float *scp = a.score + (size_t)t * a.NE;
+    float sc[PER];
+    uint32_t key[PER];
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (oi >= 0 && (bi < 0 || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
-        }
-        if (bi < 0) bi = 0;                        // every score NaN: the reference aborts here
-        if (lane == 0) {
-            a.idx[(size_t)t * a.K + j] = bi;
-            wsel[j] = scr[bi];
-            choice[bi] = -INFINITY;
-        }
-        __syncwarp();
+    for (int i = 0; i < PER; i++) {
+        const int e = lane + 32 * i;
+        sc[i] = e < a.NE ? __ldcg(scp + e) : 0.f;
+        key[i] = e < a.NE ? choice_key(__fadd_rn(sc[i], a.bias[e])) : 0u;
     }
-    if (lane == 0) {
-        if (a.norm_topk) {
-            double s = 0.0;
-            for (int j = 0; j < a.K; j++) s += (double)wsel[j];
-            for (int j = 0; j < a.K; j++) wsel[j] = (float)((double)wsel[j] / (s + 1e-20));
+    int pick0 = 0, pick1 = 0;                      // lane l keeps picks l and l + 32 (K <= 64)
+    float w0 = 0.f, w1 = 0.f;
+    for (int j = 0; j < a.K; j++) {
+        uint32_t m = 0u;
+#pragma unroll
+        for (int i = 0; i < PER; i++) m = max(m, key[i]);
+        m = __reduce_max_sync(0xffffffffu, m);
+        uint32_t cand = 0xffffffffu;
+#pragma unroll
+        for (int i = 0; i < PER; i++) cand = min(cand, key[i] == m ? (uint32_t)(lane + 32 * i) : 0xffffffffu);
+        uint32_t bi = __reduce_min_sync(0xffffffffu, cand);
+        if (m == 0u) bi = 0u;                      // nothing selectable is left (the reference aborts here)
+        float wsel = 0.f;
+#pragma unroll
+        for (int i = 0; i < PER; i++)
+            if (bi == (uint32_t)(lane + 32 * i)) { wsel = sc[i]; key[i] = 0u; }
+        wsel = __shfl_sync(0xffffffffu, wsel, bi & 31);
+        if (lane == (j & 31)) {
+            if (j < 32) { pick0 = (int)bi; w0 = wsel; } else { pick1 = (int)bi; w1 = wsel; }
         }
-        for (int j = 0; j < a.K; j++) a.w[(size_t)t * a.K + j] = __fmul_rn(wsel[j], a.routed_scale);
     }
-    __syncwarp();
+    if (a.norm_topk) {
+        double tot = 0.0;
+        for (int j = 0; j < a.K; j++) tot += (double)__shfl_sync(0xffffffffu, j < 32 ? w0 : w1, j & 31);
+        w0 = (float)((double)w0 / (tot + 1e-20));
+        w1 = (float)((double)w1 / (tot + 1e-20));
+    }
+    if (lane < a.K) {
+        a.idx[(size_t)t * a.K + lane] = pick0;
+        a.w[(size_t)t * a.K + lane] = __fmul_rn(w0, a.routed_scale);
+    }
+    if (lane + 32 < a.K) {
+        a.idx[(size_t)t * a.K + lane + 32] = pick1;
+        a.w[(size_t)t * a.K + lane + 32] = __fmul_rn(w1, a.routed_scale);
+    }
 }
 
 __global__ void __launch_bounds__(RT_WARPS * 32) router_kernel(const RouterArgs a)
 {
-    __shared__ float choice[RT_WARPS][G5B_MAX_EXPERTS];
-    __shared__ float scr[RT_WARPS][G5B_MAX_EXPERTS];
-    __shared__ float wsel[RT_WARPS][G5B_MAX_TOPK];
+    __shared__ int sidx_buf[RT_MAX_TOKENS * G5B_MAX_TOPK];
     __shared__ int cnt[G5B_MAX_EXPERTS], off[G5B_MAX_EXPERTS];
     __shared__ int psum[RT_WARPS * 32], ssum[RT_WARPS * 32];
     __shared__ int is_last;
@@ -118,28 +137,41 @@ __global__ void __launch_bounds__(RT_WARPS * 32) router_kernel(const RouterArgs 
         acc = warp_sum(acc);
         if (lane == 0) a.score[(size_t)t * a.NE + e] = sigmoid_host((float)acc);
     }
-    // last CTA to finish does the selection and the grouping
+    // The CTA that finishes a token's rows last (one counter per token, no spinning) selects that
+    // token's experts, so the tokens of a batch are selected in parallel; the CTA that finishes
+    // the last selection then groups the pairs.
     __threadfence();
     __syncthreads();
     if (tid == 0) {
-        const int total = gridDim.x * gridDim.y;
+        const int prev = atomicAdd(a.counter + 1 + t, 1);
+        is_last = prev == (int)gridDim.x - 1;
+        if (is_last) a.counter[1 + t] = 0;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    if (warp == 0) {
+        if (a.NE <= 512) topk_one_token<16>(a, t, lane);
+        else             topk_one_token<32>(a, t, lane);
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
         const int prev = atomicAdd(a.counter, 1);
-        is_last = prev == total - 1;
+        is_last = prev == (int)gridDim.y - 1;
         if (is_last) *a.counter = 0;
     }
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    for (int tt = warp; tt < a.T; tt += RT_WARPS) topk_one_token(a, tt, choice[warp], scr[warp], wsel[warp], lane);
-    __syncthreads();
     if (!a.p.n_slots) return;
 
     // Group the (token, slot) pairs by expert. Slots are numbered in expert order; the shared
     // expert, when asked for, is the last slot and takes every token. Which pair of an expert
     // lands where inside its slot does not matter: every pair has its own output row.
     const int n = a.T * a.K, nth = RT_WARPS * 32;
-    int *sidx = reinterpret_cast<int *>(&choice[0][0]);       // selection is done: reuse as [T*K] ids
-    for (int i = tid; i < n; i += nth) sidx[i] = a.idx[i];
+    int *sidx = sidx_buf;                                     // [T*K] ids
+    for (int i = tid; i < n; i += nth) sidx[i] = __ldcg(a.idx + i);
     for (int le = tid; le < a.n_local; le += nth) cnt[le] = 0;
     __syncthreads();
     for (int i = tid; i < n; i += nth) {
