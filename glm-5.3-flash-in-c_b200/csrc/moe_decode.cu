@@ -116,7 +116,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
     float *red = reinterpret_cast<float *>(actring + MM_NS * act_bytes);
     uint64_t *full = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(red) + MM_CONS * 16 * 4);
     uint64_t *empty = full + MM_NS;
-    uint64_t *plan_ready = empty + MM_NS;
+    uint64_t *plan_ready = empty + MM_NS;       // the router weights of the picks are in s_w
     __shared__ ExpertW s_ew[MM_MAX_SLOTS];       // slot j < K: j-th routed pick; slot K: shared expert
     __shared__ float s_w[MM_MAX_SLOTS];
     __shared__ int my_tiles[MM_MAX_ITEMS], my_last[MM_MAX_ITEMS];
@@ -145,9 +145,11 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
         // ================================================================ producer ====
         int it = 0;
         bool have_plan = false;
+        float plan_w = 0.f;                          // lane j < K: router score of the j-th pick
         float bias_r[DEC_PER];                       // the selection bias does not depend on the scores: fetch it now
 #pragma unroll
         for (int i = 0; i < DEC_PER; i++) bias_r[i] = lane + 32 * i < a.NE ? a.bias[lane + 32 * i] : 0.f;
+        asm volatile("bar.sync 2, %0;" ::"r"((MM_CONS + 1) * 32) : "memory");   // the consumers' router loads are issued
         // The producer selects the experts (every CTA for itself; the result is the same everywhere)
         // while the consumers multiply what is already in flight: wait for all router rows, then
         // top-k of score + bias by repeated arg-max, lowest index on ties.
@@ -195,21 +197,27 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
                 if (blockIdx.x == 0) a.idx[lane] = my_pick;
             }
             DT_MARK_P(14);
-            if (a.norm_topk) {
-                double tot = 0.0;
-                for (int j = 0; j < a.K; j++) tot += (double)__shfl_sync(0xffffffffu, my_w, j);
-                my_w = (float)((double)my_w / (tot + 1e-20));
-            }
-            my_w = __fmul_rn(my_w, a.routed_scale);
-            if (lane < a.K) {
-                s_w[lane] = my_w;
-                if (blockIdx.x == 0) a.w[lane] = my_w;
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(plan_ready);
+            plan_w = my_w;                            // normalised after the last copy is issued (below)
             __syncwarp();
             DT_MARK_P(1);
             return true;
+        };
+        // Router weights of the picks (reference: normalise in FP64, scale). Only the combine needs
+        // them, so the FP64 division stays off the path to the first routed copy.
+        auto finish_weights = [&]() {
+            float w = plan_w;
+            if (a.norm_topk) {
+                double tot = 0.0;
+                for (int j = 0; j < a.K; j++) tot += (double)__shfl_sync(0xffffffffu, w, j);
+                w = (float)((double)w / (tot + 1e-20));
+            }
+            w = __fmul_rn(w, a.routed_scale);
+            if (lane < a.K) {
+                s_w[lane] = w;
+                if (blockIdx.x == 0) a.w[lane] = w;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(plan_ready);
         };
         for (int g = blockIdx.x; g < n_gu && ok; g += gridDim.x) {
             int slot, rt;
@@ -272,6 +280,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
                 pending = 0;
             }
         }
+        if (ok) finish_weights();
         if (!ok) {
             // Copies in flight must land before shared memory goes away. A stage whose activation
             // copy was never issued cannot complete; give it its missing bytes from the buffer
@@ -296,25 +305,43 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
         {
             double *rsum = reinterpret_cast<double *>(red);           // [8] partial sums, red is idle here
             const int quarter = warp & 3, which = warp >> 2, span = a.E / 4;
+            bool released = false;                                // the producer may start copying
             for (int e0 = blockIdx.x; e0 < a.NE; e0 += 2 * gridDim.x) {
                 const int e = e0 + which * gridDim.x;
                 double acc = 0.0;
-                if (e < a.NE) {
+                if (a.gate_dt == DT_BF16 && span == 1024) {
+                    // all loads of the row quarter first, then the hand-over to the producer, then the
+                    // arithmetic: the router's few loads enter the memory queues ahead of the 200 KB
+                    // of bulk copies each SM is about to issue instead of behind them
+                    const int ee = e < a.NE ? e : a.NE - 1;
+                    const uint16_t *row = static_cast<const uint16_t *>(a.gate) + (size_t)ee * a.E + (size_t)quarter * span;
+                    const float *xq = a.x + (size_t)quarter * span;
+                    uint4 wv[4];
+                    float4 x0[4], x1[4];
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        const int c = lane * 8 + k * 256;
+                        wv[k] = ld_stream16(row + c);
+                        x0[k] = *reinterpret_cast<const float4 *>(xq + c);
+                        x1[k] = *reinterpret_cast<const float4 *>(xq + c + 4);
+                    }
+                    if (!released) { asm volatile("bar.arrive 2, %0;" ::"r"((MM_CONS + 1) * 32) : "memory"); released = true; }
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        float w[8];
+                        bf16x2_to_f32(wv[k].x, w[0], w[1]); bf16x2_to_f32(wv[k].y, w[2], w[3]);
+                        bf16x2_to_f32(wv[k].z, w[4], w[5]); bf16x2_to_f32(wv[k].w, w[6], w[7]);
+                        acc = fma((double)w[0], (double)x0[k].x, acc); acc = fma((double)w[1], (double)x0[k].y, acc);
+                        acc = fma((double)w[2], (double)x0[k].z, acc); acc = fma((double)w[3], (double)x0[k].w, acc);
+                        acc = fma((double)w[4], (double)x1[k].x, acc); acc = fma((double)w[5], (double)x1[k].y, acc);
+                        acc = fma((double)w[6], (double)x1[k].z, acc); acc = fma((double)w[7], (double)x1[k].w, acc);
+                    }
+                } else if (e < a.NE) {
+                    if (!released) { asm volatile("bar.arrive 2, %0;" ::"r"((MM_CONS + 1) * 32) : "memory"); released = true; }
                     if (a.gate_dt == DT_BF16) {
                         const uint16_t *row = static_cast<const uint16_t *>(a.gate) + (size_t)e * a.E + (size_t)quarter * span;
                         const float *xq = a.x + (size_t)quarter * span;
-#pragma unroll 4
-                        for (int c = lane * 8; c < span; c += 256) {
-                            const uint4 wv = ld_stream16(row + c);
-                            const float4 x0 = *reinterpret_cast<const float4 *>(xq + c), x1 = *reinterpret_cast<const float4 *>(xq + c + 4);
-                            float w[8];
-                            bf16x2_to_f32(wv.x, w[0], w[1]); bf16x2_to_f32(wv.y, w[2], w[3]);
-                            bf16x2_to_f32(wv.z, w[4], w[5]); bf16x2_to_f32(wv.w, w[6], w[7]);
-                            acc = fma((double)w[0], (double)x0.x, acc); acc = fma((double)w[1], (double)x0.y, acc);
-                            acc = fma((double)w[2], (double)x0.z, acc); acc = fma((double)w[3], (double)x0.w, acc);
-                            acc = fma((double)w[4], (double)x1.x, acc); acc = fma((double)w[5], (double)x1.y, acc);
-                            acc = fma((double)w[6], (double)x1.z, acc); acc = fma((double)w[7], (double)x1.w, acc);
-                        }
+                        for (int i = lane; i < span; i += 32) acc = fma((double)bf16_to_f32(row[i]), (double)xq[i], acc);
                     } else {
                         const float *row = static_cast<const float *>(a.gate) + (size_t)e * a.E + (size_t)quarter * span;
                         const float *xq = a.x + (size_t)quarter * span;
@@ -330,6 +357,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
                 }
                 asm volatile("bar.sync 1, %0;" ::"r"(MM_CONS * 32) : "memory");
             }
+            if (!released) asm volatile("bar.arrive 2, %0;" ::"r"((MM_CONS + 1) * 32) : "memory");
             if (ctid == 0) { __threadfence(); atomicAdd(a.sync + 0, 1ull); }
         }
         DT_MARK(0);
