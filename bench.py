@@ -254,6 +254,50 @@ def time_attention_layers(pkg, torch, steps: int, peak: float, device: int = 0):
     return out
 
 
+def time_decoder_layers(pkg, torch, steps: int, device: int = 0):
+    """Two whole full-size decoder layers, one new token: layer 0 = KDA + MoE, layer 1 = MLA (8192
+    cached positions, indexer selecting) + MoE, each with its two mHC sites and norms. From the two
+    times the full model's batch-1 token time on ONE GPU's worth of bandwidth is extrapolated
+    (34 KDA layers + 11 MLA layers + the 1.27 GB head at the KDA layer's measured GB/s) - the
+    306 GB model itself needs 8 GPUs."""
+    import synth
+    L = pkg.lib()
+    c = pkg.full_size_config()
+    c.n_layers = 2
+    spec = synth.Spec(c, [0, 1], [0, 0], with_head=False)
+    tensors = synth.make_model(spec, seed=6, recipe="baseline", experts=False)
+    cap = 8192
+    eng = pkg.Engine(c, spec.is_mla, spec.is_dense, cap, device)
+    eng.set_option("allow_partial", 1)
+    eng.set_option("latent_bf16", 1)
+    eng.load_all(tensors)
+    for layer in range(2):
+        for ex in range(c.n_experts):
+            eng.fill_expert(layer, ex, SEED, *synth.expert_scales(c, layer, ex, SEED))
+    eng.finalize()
+    rng = np.random.default_rng(SEED)
+    h = torch.from_numpy(rng.standard_normal((1, c.hc_mult, c.hidden)).astype(np.float32)).cuda()
+    out = {}
+    for layer, cached, name in ((0, 0, "kda_moe_layer"), (1, cap - 1, "mla_moe_layer_ctx8192")):
+        hd = h.clone()
+        each = np.zeros(max(steps, 3), np.float32); tot = C.c_float(0)
+        for k in (3, steps):
+            hd.copy_(h)
+            assert L.g5b_time_op(eng.handle, b"layer", layer, hd.data_ptr(), 1, cached, hd.data_ptr(), k, FLUSH_BYTES,
+                                 C.byref(tot), each.ctypes.data) == 0, L.g5b_last_error()
+        out[name] = {"ms": float(np.mean(each[:steps])), "finite": bool(torch.isfinite(hd).all().item())}
+    eng.close()
+    kda_bytes = 286048984 + 228907008 + 2 * 786432
+    rate = kda_bytes / (out["kda_moe_layer"]["ms"] * 1e-3)
+    head_ms = 154880 * 4096 * 2 / rate * 1e3
+    token_ms = 34 * out["kda_moe_layer"]["ms"] + 11 * out["mla_moe_layer_ctx8192"]["ms"] + head_ms
+    out["full_model_token_ms_extrapolated"] = token_ms
+    out["full_model_tokens_per_s_extrapolated"] = 1e3 / token_ms
+    out["note"] = ("extrapolated: 34 x KDA+MoE layer + 11 x MLA+MoE layer + lm_head at the KDA+MoE layer's measured "
+                   "rate; the three dense-MLP layers counted as MoE layers; one GPU's bandwidth, weights of 8 GPUs")
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -297,7 +341,8 @@ def main():
     warmup = max(3, args.warmup)
     if args.only_attention_layers:
         peak, _ = measured_peaks()
-        print(json.dumps({"config3": time_attention_layers(pkg, torch, max(3, args.steps), peak, local)}), flush=True)
+        print(json.dumps({"config3": time_attention_layers(pkg, torch, max(3, args.steps), peak, local),
+                          "decoder_layers": time_decoder_layers(pkg, torch, max(3, args.steps), local)}), flush=True)
         return
     opts = {}
     if args.stream_warps:
@@ -387,6 +432,7 @@ def main():
     eng.close()
     if rank == 0 and not args.no_attention_layers and args.experts == 288:
         extra["config3"] = time_attention_layers(pkg, torch, max(10, args.steps // 10), peak, local)
+        extra["decoder_layers"] = time_decoder_layers(pkg, torch, max(10, args.steps // 10), local)
 
     # ---- N > 1: the same layer expert-parallel (288 / N routed experts per rank, activations and the
     # shared expert replicated, contribution rows exchanged over peer mappings): one token stream

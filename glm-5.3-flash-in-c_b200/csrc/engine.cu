@@ -107,6 +107,7 @@ struct g5b_engine {
     float *kq, *kk, *kv, *kz, *kgb, *ko, *kbraw, *klr;
     float *mq_raw, *mct, *mwk, *mgate, *mwp, *mq, *mqidx, *mcb, *macc, *mscore, *minvq;
     double *mqa, *mdsc, *mpart = nullptr, *mstats = nullptr;
+    double *hc_part = nullptr; int *hc_count = nullptr;  // fused mHC site: partial sums and per-token counters
     void *xterms = nullptr; float *xinv = nullptr;      // batched expert kernels: F16 terms of the activations
     int   *msel, *mnsel;
     float *rscore, *rw, *act, *contrib, *gu, *dact;
@@ -515,6 +516,7 @@ extern "C" int g5b_engine_finalize(g5b_engine *e)
     if (walloc(e, &e->rscore, N * c.n_experts) || walloc(e, &e->rw, N * K) || walloc(e, &e->ridx, N * K) ||
         walloc(e, &e->act, pairs * (I > SI ? I : SI)) || walloc(e, &e->contrib, pairs * E) ||
         walloc(e, &e->gu, N * 2 * DI) || walloc(e, &e->dact, N * DI) || walloc(e, &e->xinv, N) ||
+        walloc(e, &e->hc_part, N * 32 * (MIX + 1)) || walloc(e, &e->hc_count, N) ||
         e->dalloc(&e->xterms, N * 2 * E * 2)) return -1;
     e->plan.max_slots = (int)((N * K < (size_t)e->n_local ? N * K : (size_t)e->n_local) + 1);
     e->plan.max_pairs = (int)pairs;
@@ -743,10 +745,16 @@ static int run_layer(g5b_engine *e, int l, float *h, int n, int cached)
     Layer &w = e->L[l];
     const int M = c.hc_mult, E = c.hidden;
     for (int site = 0; site < 2; site++) {
-        if (run_hc_pre(e, w.hc[site], h, n)) return -1;
         if (!w.in_norm || !w.post_norm) return fail("this layer's norms were not loaded");
-        rms_factor(e->st, e->xc, E, E, n, c.rms_eps, e->inv1);
-        rms_apply(e->st, e->xn, e->xc, site ? w.post_norm : w.in_norm, e->inv1, E, E, n);
+        const HcW &hw = w.hc[site];
+        if (hw.fn.loaded() && hw.base && hw.scale && hc_pre_fused_supported(hw, M, E)) {
+            hc_pre_fused(e->st, e->xn, e->post, e->comb, h, hw, site ? w.post_norm : w.in_norm, e->hc_part, e->hc_count,
+                         n, M, E, c.hc_iters, c.hc_eps, c.rms_eps);
+        } else {
+            if (run_hc_pre(e, hw, h, n)) return -1;
+            rms_factor(e->st, e->xc, E, E, n, c.rms_eps, e->inv1);
+            rms_apply(e->st, e->xn, e->xc, site ? w.post_norm : w.in_norm, e->inv1, E, E, n);
+        }
         int rc;
         if (site == 0) rc = w.is_mla ? run_mla(e, w, e->xn, n, cached, e->y) : run_kda(e, w, e->xn, n, e->y);
         else           rc = w.is_dense ? run_mlp(e, w, e->xn, n, e->y) : run_moe(e, w, e->xn, n, e->y, 1);

@@ -85,6 +85,207 @@ void hc_finish(cudaStream_t st, float *x, float *post, float *comb, const float 
     G5B_LAUNCH(hc_finish_kernel, T, HC_THREADS, 0, st, x, post, comb, h, mix, w.base, w.scale, M, E, iters, eps);
 }
 
+// ---- one launch per site for the decoder layer: RMSNorm0 factor + mixer product + gates + Sinkhorn
+// + collapse + the sub-block's input RMSNorm.
+// As separate launches these were six kernels of one to six CTAs each, about 60 us per site and
+// two sites per layer - more than the attention or the MoE block they wrap. Here HCF_SLICES CTAs
+// per token each take a slice of the flattened streams: the slice's sum of squares and its part
+// of the (2+M)M mixer dot products, in FP64. The CTA that finishes a token last (a counter, no
+// spinning) adds the parts in slice order, applies the norm factor to the dots (the mixer's input
+// is RMSNorm0(h) = h * inv without a weight, src/core/glm53f_ops.c:563-569), then runs the code of
+// hc_finish_kernel above and finally normalises the collapsed vector with the layer's norm weight
+// (glm53f_rmsnorm, src/core/glm53f_ops.c:473-480), so the sub-block reads its input directly.
+constexpr int HCF_SLICES = 32, HCF_MAX_E = 8192, HCF_MAX_MIX = (2 + G5B_MAX_HC) * G5B_MAX_HC;
+
+struct HcFused {
+    float *xn, *post, *comb;
+    const float *h;
+    const uint16_t *fn;             // BF16 [(2+M)M][M*E]
+    const float *base, *scale, *norm_w;
+    double *part;                   // [T][HCF_SLICES][(2+M)M + 1]
+    int *counters;                  // [T], zero between launches
+    int M, E, iters;
+    float hc_eps, rms_eps;
+};
+
+__global__ void __launch_bounds__(HC_THREADS) hc_pre_fused_kernel(const HcFused a)
+{
+    __shared__ float hs[HCF_MAX_E * G5B_MAX_HC / HCF_SLICES];   // this CTA's slice of the streams; later reused
+    __shared__ float xs[HCF_MAX_E];                              // collapsed vector (last CTA)
+    __shared__ double red[32];
+    __shared__ double dots[HCF_MAX_MIX + 1];
+    __shared__ float mx[HCF_MAX_MIX];
+    __shared__ double pre[G5B_MAX_HC];
+    __shared__ double cm[G5B_MAX_HC * G5B_MAX_HC];
+    __shared__ int is_last;
+    const int t = blockIdx.y, cta = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int M = a.M, E = a.E, ME = M * E, MIX = (2 + M) * M;
+    const int width = ME / HCF_SLICES, c0 = cta * width;
+    const float *ht = a.h + (size_t)t * ME;
+
+    // ---- every CTA: its slice
+    double ss = 0.0;
+    for (int i = tid; i < width; i += HC_THREADS) {
+        const float v = ht[c0 + i];
+        hs[i] = v;
+        ss += (double)v * (double)v;
+    }
+    ss = block_sum(ss, red);                                   // also orders the writes of hs
+    double *mine = a.part + ((size_t)t * HCF_SLICES + cta) * (MIX + 1);
+    if (tid == 0) mine[MIX] = ss;
+    for (int k = warp; k < MIX; k += HC_THREADS / 32) {
+        const uint16_t *row = a.fn + (size_t)k * ME + c0;
+        double acc = 0.0;
+        for (int i = lane * 8; i < width; i += 256) {
+            const uint4 wv = ld_stream16(row + i);
+            float w[8];
+            bf16x2_to_f32(wv.x, w[0], w[1]); bf16x2_to_f32(wv.y, w[2], w[3]);
+            bf16x2_to_f32(wv.z, w[4], w[5]); bf16x2_to_f32(wv.w, w[6], w[7]);
+#pragma unroll
+            for (int j = 0; j < 8; j++) acc = fma((double)w[j], (double)hs[i + j], acc);
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) mine[k] = acc;
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const int prev = atomicAdd(a.counters + t, 1);
+        is_last = prev == HCF_SLICES - 1;
+        if (is_last) a.counters[t] = 0;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+
+    // ---- the token's last CTA: parts in slice order, factor, gates
+    if (tid <= MIX) {
+        double s = 0.0;
+        for (int cc = 0; cc < HCF_SLICES; cc++) s += __ldcg(a.part + ((size_t)t * HCF_SLICES + cc) * (MIX + 1) + tid);
+        dots[tid] = s;
+    }
+    __syncthreads();
+    if (tid < MIX) {
+        const float inv = (float)(1.0 / sqrt(dots[MIX] / (double)ME + (double)a.rms_eps));
+        mx[tid] = (float)(dots[tid] * (double)inv);
+    }
+    __syncthreads();
+    const double eps = (double)a.hc_eps;
+    if (tid >= 32 && tid < 32 + M) {
+        const int i = tid - 32;
+        pre[i] = (double)sigmoid_host(mul_add_unfused(mx[i], a.scale[0], a.base[i])) + eps;
+        a.post[(size_t)t * M + i] = __fmul_rn(2.0f, sigmoid_host(mul_add_unfused(mx[M + i], a.scale[1], a.base[M + i])));
+    }
+    __syncthreads();
+    if (tid < 32) {
+        // row softmax + eps, then column / row normalisations (src/core/glm53f_ops.c:577-598)
+        const int MM = M * M;
+        for (int e = tid; e < MM; e += 32) {
+            const int i = e / M, j = e % M;
+            double top = -INFINITY, z = 0.0, own = 0.0;
+            for (int jj = 0; jj < M; jj++) {
+                const int k = 2 * M + i * M + jj;
+                const double l = (double)mul_add_unfused(mx[k], a.scale[2], a.base[k]);
+                if (l > top) top = l;
+            }
+            for (int jj = 0; jj < M; jj++) {
+                const int k = 2 * M + i * M + jj;
+                const double l = (double)mul_add_unfused(mx[k], a.scale[2], a.base[k]);
+                const double ex = exp(l - top);
+                z += ex;
+                if (jj == j) own = ex;
+            }
+            cm[e] = own / z + eps;
+        }
+        __syncwarp();
+        if (MM <= 32) {
+            // a lane per matrix element, sums gathered with shuffles in the reference's index order
+            const int i = tid / M, j = tid % M;
+            double v = tid < MM ? cm[tid] : 0.0;
+            for (int pass = 0; pass < 2 * a.iters - 1; pass++) {
+                const bool by_col = (pass & 1) == 0;
+                double sum = 0.0;
+                for (int b = 0; b < M; b++) {
+                    const int src = by_col ? b * M + j : i * M + b;
+                    sum += __shfl_sync(0xffffffffu, v, src < 32 ? src : 0);
+                }
+                if (tid < MM) v = v / (sum + eps);
+            }
+            if (tid < MM) a.comb[(size_t)t * MM + tid] = (float)v;
+        } else {
+            for (int pass = 0; pass < 2 * a.iters - 1; pass++) {
+                const bool by_col = (pass & 1) == 0;
+                double nv[2];
+                int n = 0;
+                for (int e = tid; e < MM; e += 32, n++) {
+                    const int i = e / M, j = e % M;
+                    double s = 0.0;
+                    for (int b = 0; b < M; b++) s += by_col ? cm[b * M + j] : cm[i * M + b];
+                    nv[n] = cm[e] / (s + eps);
+                }
+                __syncwarp();
+                n = 0;
+                for (int e = tid; e < MM; e += 32, n++) cm[e] = nv[n];
+                __syncwarp();
+            }
+            for (int e = tid; e < MM; e += 32) a.comb[(size_t)t * MM + e] = (float)cm[e];
+        }
+    } else {
+        // x[d] = sum_i pre[i] * h[i][d] in FP64 (src/core/glm53f_ops.c:603-607), kept in shared memory.
+        // Four columns per thread and all of a thread's loads issued before the sums: one CTA walks
+        // the whole token here, so the loads must overlap (they hit L2: the slices were just read).
+        for (int d0 = (tid - 32) * 4; d0 < E; d0 += (HC_THREADS - 32) * 4 * 2) {
+            const int d1 = d0 + (HC_THREADS - 32) * 4;
+            float4 va[G5B_MAX_HC], vb[G5B_MAX_HC];
+#pragma unroll
+            for (int i = 0; i < G5B_MAX_HC; i++)
+                if (i < M) {
+                    va[i] = *reinterpret_cast<const float4 *>(ht + (size_t)i * E + d0);
+                    if (d1 < E) vb[i] = *reinterpret_cast<const float4 *>(ht + (size_t)i * E + d1);
+                }
+            double sa[4] = {0.0, 0.0, 0.0, 0.0}, sb[4] = {0.0, 0.0, 0.0, 0.0};
+#pragma unroll
+            for (int i = 0; i < G5B_MAX_HC; i++)
+                if (i < M) {
+                    const double p = pre[i];
+                    sa[0] += p * (double)va[i].x; sa[1] += p * (double)va[i].y; sa[2] += p * (double)va[i].z; sa[3] += p * (double)va[i].w;
+                    if (d1 < E) { sb[0] += p * (double)vb[i].x; sb[1] += p * (double)vb[i].y; sb[2] += p * (double)vb[i].z; sb[3] += p * (double)vb[i].w; }
+                }
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                xs[d0 + q] = (float)sa[q];
+                if (d1 < E) xs[d1 + q] = (float)sb[q];
+            }
+        }
+    }
+    __syncthreads();
+    // ---- the sub-block's input: RMSNorm(x) * w
+    double s2 = 0.0;
+    for (int d = tid; d < E; d += HC_THREADS) s2 += (double)xs[d] * (double)xs[d];
+    s2 = block_sum(s2, red);
+    __shared__ float inv2;
+    if (tid == 0) inv2 = (float)(1.0 / sqrt(s2 / (double)E + (double)a.rms_eps));
+    __syncthreads();
+    const float f = inv2;
+    for (int d = tid; d < E; d += HC_THREADS) a.xn[(size_t)t * E + d] = __fmul_rn(a.norm_w[d], __fmul_rn(xs[d], f));
+}
+
+bool hc_pre_fused_supported(const HcW &w, int M, int E)
+{
+    const int ME = M * E;
+    return w.fn.dt == DT_BF16 && E <= HCF_MAX_E && E % 4 == 0 && M <= G5B_MAX_HC && ME % (HCF_SLICES * 256) == 0 &&
+           ME / HCF_SLICES <= HCF_MAX_E * G5B_MAX_HC / HCF_SLICES;
+}
+
+void hc_pre_fused(cudaStream_t st, float *xn, float *post, float *comb, const float *h, const HcW &w,
+                  const float *norm_w, double *part, int *counters, int T, int M, int E, int iters, float hc_eps,
+                  float rms_eps)
+{
+    HcFused a{xn, post, comb, h, static_cast<const uint16_t *>(w.fn.w), w.base, w.scale, norm_w, part, counters,
+              M, E, iters, hc_eps, rms_eps};
+    G5B_LAUNCH(hc_pre_fused_kernel, dim3(HCF_SLICES, T), HC_THREADS, 0, st, a);
+}
+
 // h'[j][d] = post[j]*y[d] + sum_i comb[i][j]*h[i][d] in FP64, in place: a thread owns column d of
 // every stream (src/core/glm53f_ops.c:612-625; note comb is used transposed).
 __global__ void hc_post_kernel(float *h, const float *y, const float *post, const float *comb, int M, int E)

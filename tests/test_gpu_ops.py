@@ -192,3 +192,26 @@ def test_engine_fails_loudly_on_bad_input(pair):
         eng.forward([spec.cfg.vocab + 5])
     with pytest.raises(RuntimeError):
         eng.load("layers.0.no_such_tensor", np.zeros((1, 1), np.float32), pkg.DT_F32)
+
+
+def test_decoder_layer_with_fused_mhc_site(gpu_lib, binding):
+    """Hidden 2048 with 4 streams is the smallest shape whose mHC site takes the one-launch path
+    (norm factor + mixer product + gates + Sinkhorn + collapse + input RMSNorm in one kernel);
+    the tiny model above takes the separate kernels. Both must give the CPU path's layer output."""
+    c = pkg.Config(hidden=2048, n_layers=2, vocab=64, rms_eps=1e-5, hc_mult=4, hc_iters=20, hc_eps=1e-6,
+                   kda_heads=4, kda_head_dim=64, conv_k=4, gate_lb=-5.0, mla_heads=4, q_lora=192, kv_lora=128,
+                   qk_nope=64, v_head=64, index_topk=16, index_kpool=4, index_heads=4, index_dim=32,
+                   n_experts=8, topk=2, n_shared=1, moe_inter=128, dense_inter=256, routed_scale=2.5,
+                   norm_topk=1, swiglu_limit=10.0, fp8_block_r=128, fp8_block_c=128)
+    spec = synth.Spec(c, [0, 1], [1, 0], with_head=False)
+    for recipe in ("baseline", "spread"):
+        tensors = synth.make_model(spec, seed=23, recipe=recipe)
+        eng, orc = common.build_models(spec, tensors, 32, binding, options={"allow_partial": 1})
+        rng = np.random.default_rng(29)
+        for T in (1, 5):
+            h = rng.standard_normal((T, c.hc_mult, c.hidden)).astype(np.float32)
+            for layer in range(c.n_layers):
+                g, w = eng.op_decoder_layer(layer, h, 0), orc.op_decoder_layer(layer, h, 0)
+                assert common.rel_err(g, w) < 2e-5, (recipe, T, layer)
+                h = w
+        eng.close(); orc.close()
