@@ -511,7 +511,7 @@ extern "C" int g5b_engine_finalize(g5b_engine *e)
         walloc(e, &e->mqa, N * H * KL) || walloc(e, &e->mdsc, N * H * stride) ||
         walloc(e, &e->msel, N * stride) || walloc(e, &e->mnsel, N) ||
         walloc(e, &e->mstats, N * H * 2) ||
-        walloc(e, &e->mpart, (size_t)MLA_PART_TOKENS * H * ((stride + 63) / 64) * KL)) return -1;
+        walloc(e, &e->mpart, (size_t)MLA_PART_TOKENS * H * ((stride + 31) / 32) * KL)) return -1;
     const size_t pairs = N * K + N;
     if (walloc(e, &e->rscore, N * c.n_experts) || walloc(e, &e->rw, N * K) || walloc(e, &e->ridx, N * K) ||
         walloc(e, &e->act, pairs * (I > SI ? I : SI)) || walloc(e, &e->contrib, pairs * E) ||

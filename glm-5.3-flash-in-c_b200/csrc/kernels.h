@@ -183,7 +183,7 @@ void mla_store(cudaStream_t st, void *latent, float *idx_state, const float *ct_
 void dsa_select(cudaStream_t st, int *sel, int *nsel, const float *idx_state, const float *qidx,
                 const float *wproj, float *score, int T, int cached, const MlaShape &s);
 void mla_absorb(cudaStream_t st, double *qa, const float *q, const DMat &kv_b, int T, const MlaShape &s);
-// part: FP64 partial sums [part_tokens][H][ceil((topk+KP)/64)][KL], stats [T][H][2]; part == nullptr
+// part: FP64 partial sums [part_tokens][H][ceil((topk+KP)/32)][KL], stats [T][H][2]; part == nullptr
 // falls back to one CTA per head.
 void mla_attend(cudaStream_t st, float *cb, const double *qa, const void *latent, const int *sel,
                 const int *nsel, double *dsc, double *part, double *stats, int part_tokens, int T, int cached,

@@ -173,14 +173,32 @@ __global__ void __launch_bounds__(TOPK_THREADS) dsa_topk_kernel(int *sel, int *n
             if ((k & mask) == prefix) atomicAdd(&hist[(int)((k >> shift) & 0xff)], 1);
         }
         __syncthreads();
-        if (tid == 0) {
-            int want = want_s, dgt = 255;
-            for (; dgt > 0; dgt--) {
-                if (hist[dgt] >= want) break;
-                want -= hist[dgt];
+        if (tid < 32) {
+            // the digit holding the want-th largest key: lane l owns digits 255 - 8l .. 248 - 8l; a warp
+            // scan over the lanes' totals, then a walk over the owning lane's eight bins
+            int c[8], tot = 0;
+#pragma unroll
+            for (int k = 0; k < 8; k++) { c[k] = hist[255 - (8 * tid + k)]; tot += c[k]; }
+            int incl = tot;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, incl, o);
+                if (tid >= o) incl += v;
             }
-            prefix_s = prefix | ((unsigned long long)dgt << shift);
-            want_s = want;
+            const int excl = incl - tot, want = want_s;
+            __syncwarp();
+            if (excl < want && want <= incl) {
+                int w = want - excl, dgt = 255 - 8 * tid;
+#pragma unroll
+                for (int k = 0; k < 8; k++) {
+                    if (c[k] >= w) { dgt = 255 - (8 * tid + k); break; }
+                    w -= c[k];
+                    dgt = 255 - (8 * tid + k) - 1;
+                }
+                if (dgt < 0) dgt = 0;
+                prefix_s = prefix | ((unsigned long long)dgt << shift);
+                want_s = w;
+            }
         }
         __syncthreads();
     }
@@ -336,9 +354,14 @@ __global__ void __launch_bounds__(256) mla_score4_kernel(double *dsc, const doub
     const double scale = (double)(1.0f / sqrtf((float)s.qn));
     const int *sl = sel ? sel + (size_t)t * (s.topk + s.KP) : nullptr;
     const int jend = min(j0 + SC_CHUNK, nvis);
-    for (int jj = j0 + warp; jj < jend; jj += 8) {
-        const int j = ns < 0 ? jj : sl[jj];
-        float c[16];
+    // this warp's positions are j0 + warp + 8k; their cache rows are looked up first (lane k holds
+    // row k), and two positions' latent rows are in flight at a time
+    int myrow = 0;
+    {
+        const int jj = j0 + warp + 8 * lane;
+        if (lane < SC_CHUNK / 8 && jj < jend) myrow = ns < 0 ? jj : sl[jj];
+    }
+    auto load_row = [&](float (&c)[16], int j) {
         if (s.latent_bf16) {
             const uint32_t *row = reinterpret_cast<const uint32_t *>(static_cast<const uint16_t *>(latent) + (size_t)j * s.KL);
 #pragma unroll
@@ -348,6 +371,8 @@ __global__ void __launch_bounds__(256) mla_score4_kernel(double *dsc, const doub
 #pragma unroll
             for (int k = 0; k < 8; k++) { const float2 v = row[32 * k + lane]; c[2 * k] = v.x; c[2 * k + 1] = v.y; }
         }
+    };
+    auto finish = [&](const float (&c)[16], int jj) {
         double a[SC_HEADS] = {0.0, 0.0, 0.0, 0.0};
 #pragma unroll
         for (int k = 0; k < 16; k++) {
@@ -367,6 +392,16 @@ __global__ void __launch_bounds__(256) mla_score4_kernel(double *dsc, const doub
             const int hh = ((lane >> 4) << 1) | ((lane >> 3) & 1);
             dsc[((size_t)t * s.H + h0 + hh) * stride + jj] = v * scale;
         }
+    };
+    for (int k = 0; k < SC_CHUNK / 8; k += 2) {
+        const int jj0 = j0 + warp + 8 * k, jj1 = jj0 + 8;
+        if (jj0 >= jend) break;
+        const int row0 = __shfl_sync(0xffffffffu, myrow, k), row1 = __shfl_sync(0xffffffffu, myrow, k + 1);
+        float c0[16], c1[16];
+        load_row(c0, row0);
+        if (jj1 < jend) load_row(c1, row1);
+        finish(c0, jj0);
+        if (jj1 < jend) finish(c1, jj1);
     }
 }
 
@@ -420,12 +455,12 @@ __global__ void __launch_bounds__(512) mla_wsum_kernel(
 // The same softmax and weighted sum spread over the whole GPU (the kernel above walks all positions
 // with one CTA per head: 0.44 ms at 2051 positions). Three small launches:
 //   stats   per (head, token): max of the unrounded scores and z = sum exp((double)(float)s - max)
-//   chunk   per (64 positions, 8 heads, token): p_j = exp(.) / z, partial sums of p_j c_j in FP64,
+//   chunk   per (32 positions, 8 heads, token): p_j = exp(.) / z, partial sums of p_j c_j in FP64,
 //           positions ascending; the eight heads share every latent row they load
 //   reduce  per (head, token, column): the chunks' partial sums added in ascending order
 // The association of the FP64 sum differs from the reference's single ascending walk by the chunk
 // boundaries only; the result is rounded to float once, at the end, like the reference's.
-constexpr int WS_CHUNK = 64, WS_HEADS = 8, WS_THREADS = 256;
+constexpr int WS_CHUNK = 32, WS_HEADS = 8, WS_THREADS = 256;
 
 __global__ void __launch_bounds__(256) mla_softmax_stats_kernel(double *stats, const double *dsc, const int *nsel,
                                                                 int cached, int stride, MlaShape s)
@@ -480,7 +515,7 @@ __global__ void __launch_bounds__(WS_THREADS) mla_wsum_chunk_kernel(
         }
         for (int jj = threadIdx.x; jj < WS_CHUNK; jj += WS_THREADS) idx[jj] = jj < cnt ? (ns < 0 ? j0 + jj : sl[j0 + jj]) : 0;
         __syncthreads();
-#pragma unroll 4
+#pragma unroll 8
         for (int jj = 0; jj < cnt; jj++) {
             const size_t row = (size_t)idx[jj] * s.KL;
             const double c0 = (double)latent_at(latent, s.latent_bf16, row + i0);
