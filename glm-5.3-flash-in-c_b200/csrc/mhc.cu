@@ -95,6 +95,18 @@ void hc_finish(cudaStream_t st, float *x, float *post, float *comb, const float 
 // is RMSNorm0(h) = h * inv without a weight, src/core/glm53f_ops.c:563-569), then runs the code of
 // hc_finish_kernel above and finally normalises the collapsed vector with the layer's norm weight
 // (glm53f_rmsnorm, src/core/glm53f_ops.c:473-480), so the sub-block reads its input directly.
+// 1 / d for d > 0 to within an ulp or two: the hardware's 20-bit estimate and two Newton steps.
+// The Sinkhorn passes below are a chain of 39 dependent divisions per site; the exact division
+// sequence made that chain 7 us long, and the mixer is rounded to float at the end anyway.
+__device__ __forceinline__ double recip_newton(double d)
+{
+    double r;
+    asm("rcp.approx.ftz.f64 %0, %1;" : "=d"(r) : "d"(d));
+    r = fma(r, fma(-d, r, 1.0), r);
+    r = fma(r, fma(-d, r, 1.0), r);
+    return r;
+}
+
 constexpr int HCF_SLICES = 32, HCF_MAX_E = 8192, HCF_MAX_MIX = (2 + G5B_MAX_HC) * G5B_MAX_HC;
 
 struct HcFused {
@@ -209,7 +221,7 @@ __global__ void __launch_bounds__(HC_THREADS) hc_pre_fused_kernel(const HcFused 
                     const int src = by_col ? b * M + j : i * M + b;
                     sum += __shfl_sync(0xffffffffu, v, src < 32 ? src : 0);
                 }
-                if (tid < MM) v = v / (sum + eps);
+                if (tid < MM) v = v * recip_newton(sum + eps);
             }
             if (tid < MM) a.comb[(size_t)t * MM + tid] = (float)v;
         } else {
