@@ -106,4 +106,16 @@ __device__ __forceinline__ double block_sum(double v, double *red)
     return t;
 }
 
+// System-scope acquire / release on 64-bit words that another GPU writes or reads.
+__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long *p)
+{
+    unsigned long long v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned long long *p, unsigned long long v)
+{
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+
 }  // namespace g5b

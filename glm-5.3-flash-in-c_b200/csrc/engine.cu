@@ -578,9 +578,14 @@ static int run_moe(g5b_engine *e, Layer &w, const float *x, int n, float *out, i
     const bool shared_in_plan = with_shared && c.n_shared == 1 && w.sh_gate.dt == s.dt;
     const bool one_gpu_decode = e->ep_size == 1 && (shared_in_plan || !with_shared);
     prof_mark(e, 0);
-    if (e->stream_experts == 3 && one_gpu_decode && moe_decode_supported(s, n)) {
+    const bool ep_decode = e->ep_size > 1 && (shared_in_plan || !with_shared);
+    if (e->stream_experts == 3 && (one_gpu_decode || ep_decode) && moe_decode_supported(s, n)) {
+        DecodeEp ep{e->ep_rank, e->ep_size, e->ep_peers_dev, EP_FLAG_BYTES + (size_t)((e->ep_step + 1) & 1) * e->ep_rows_bytes,
+                    e->ep_step + 1, e->ep_arrive};
         if (moe_decode(e->st, out, x, w.router.w, w.router.dt, w.bias, w.table_dev, e->rscore, e->ridx, e->rw, e->act,
-                       e->contrib, s, with_shared, e->grid_sync, &e->grid_launches, e->tile_done, e->err_dev) == 0) {
+                       e->contrib, s, with_shared, e->grid_sync, &e->grid_launches, e->tile_done, e->err_dev,
+                       ep_decode ? &ep : nullptr) == 0) {
+            if (ep_decode) ++e->ep_step;
             prof_mark(e, 1); prof_mark(e, 2); prof_mark(e, 3); prof_mark(e, 4);
             prof_collect(e, 4);
             return 0;

@@ -25,17 +25,6 @@ namespace g5b {
 
 constexpr int EP_SPIN_LIMIT = 1 << 21;         // about a second at the poll interval below
 
-__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long *p)
-{
-    unsigned long long v;
-    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void st_release_sys(unsigned long long *p, unsigned long long v)
-{
-    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
-}
-
 __global__ void __launch_bounds__(256) ep_exchange_combine_kernel(const EpExchange a)
 {
     __shared__ int s_flag;                                      // this CTA finished last

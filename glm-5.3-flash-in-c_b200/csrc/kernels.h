@@ -127,10 +127,20 @@ void moe_mma_batch_down(cudaStream_t st, float *contrib, const void *act_terms, 
 // (moe_decode.cu). `sync` holds two device counters that only grow; `launches` is the host's count of
 // launches so far on them. Returns -1 when the cooperative launch is refused.
 bool moe_decode_supported(const MoeShape &s, int T);
+// ep != nullptr: expert parallel - this rank computes the picks it owns (and the shared expert),
+// stores their rows into every rank's exchange region from the down epilogue and combines after
+// every rank's step word has arrived (see ep_exchange.cu for the region's layout).
+struct DecodeEp {
+    int rank, size;
+    void *const *peers;
+    size_t rows_off;
+    unsigned long long step;
+    int *arrive;
+};
 int moe_decode(cudaStream_t st, float *out, const float *x, const void *gate, int gate_dt, const float *bias,
                const ExpertW *experts, float *score, int *idx, float *w, void *act, float *contrib,
                const MoeShape &s, int with_shared, unsigned long long *sync, unsigned long long *launches,
-               int *tile_done, int *err);
+               int *tile_done, int *err, const DecodeEp *ep = nullptr);
 // out == nullptr: contributions only (the caller combines, e.g. after an expert-parallel exchange).
 void moe_stream_down(cudaStream_t st, float *out, float *contrib, const float *act, const float *w,
                      const ExpertW *experts, const MoePlan &p, const MoeShape &s, int with_shared,

@@ -47,6 +47,14 @@ struct DecodeArgs {
     unsigned long long base;    // value of both counters when this launch starts
     int *tile_done;
     int *err;
+    // expert parallel (ep_size > 1): this rank owns experts [n_local0, n_local0 + n_local); experts[]
+    // is indexed by local expert, shared expert last; peers[r] is rank r's exchange region (ep_size
+    // step words, then at rows_off this step's row buffer [K][E])
+    int ep_rank, ep_size, n_local0, n_local;
+    void *const *peers;
+    size_t rows_off;
+    unsigned long long ep_step;
+    int *ep_arrive;
 };
 
 __device__ __forceinline__ unsigned long long ld_acquire(const unsigned long long *p)
@@ -117,8 +125,11 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
     uint64_t *full = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(red) + MM_CONS * 16 * 4);
     uint64_t *empty = full + MM_NS;
     uint64_t *plan_ready = empty + MM_NS;       // the router weights of the picks are in s_w
+    uint64_t *sel_ready = plan_ready + 1;        // the picks' expert pointers and s_local are written
     __shared__ ExpertW s_ew[MM_MAX_SLOTS];       // slot j < K: j-th routed pick; slot K: shared expert
     __shared__ float s_w[MM_MAX_SLOTS];
+    __shared__ int s_local[MM_MAX_SLOTS];        // the slot's expert lives on this rank
+    __shared__ int s_flag;
     __shared__ int my_tiles[MM_MAX_ITEMS], my_last[MM_MAX_ITEMS];
     __shared__ float wmax[MM_THREADS / 32];
     __shared__ float x_scale[2];
@@ -127,9 +138,10 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
     if (threadIdx.x == 0) {
         for (int s = 0; s < MM_NS; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], MM_CONS); }
         mbar_init(plan_ready, 1);
+        mbar_init(sel_ready, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (threadIdx.x == 32 && a.with_shared) s_ew[a.K] = a.experts[a.NE];
+    if (threadIdx.x == 32 && a.with_shared) { s_ew[a.K] = a.experts[a.n_local]; s_local[a.K] = 1; }
     __syncthreads();
 
     // item g of the gate/up list -> (slot, row tile); shared expert first
@@ -193,9 +205,14 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
             }
             DT_MARK_P(13);
             if (lane < a.K) {                         // the K pointer records are fetched side by side
-                s_ew[lane] = a.experts[my_pick];
+                const int le = my_pick - a.n_local0;
+                const bool local = le >= 0 && le < a.n_local;
+                s_local[lane] = local;
+                if (local) s_ew[lane] = a.experts[le];
                 if (blockIdx.x == 0) a.idx[lane] = my_pick;
             }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(sel_ready);
             DT_MARK_P(14);
             plan_w = my_w;                            // normalised after the last copy is issued (below)
             __syncwarp();
@@ -227,6 +244,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
                 if (!ok) break;
                 have_plan = true;
             }
+            if (!s_local[slot]) continue;             // another rank's expert
             const ExpertW ew = s_ew[slot];
             for (int kh = 0; kh < a.E / MM_CB && ok; kh++, it++) {
                 const int s = it % MM_NS;
@@ -251,8 +269,12 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
         // down: weights are prefetched before the activations exist; their copy follows the grid point
         bool acts_visible = false;
         int pending = 0, pend_stage[MM_NS], pend_slot[MM_NS];
-        for (int g = blockIdx.x; g < n_dn && ok; g += gridDim.x, it++) {
+        int last_g = -1;                               // this CTA's last down item on this rank
+        for (int g = blockIdx.x; g < n_dn; g += gridDim.x)
+            if (s_local[g / tps_d]) last_g = g;
+        for (int g = blockIdx.x; g < n_dn && ok; g += gridDim.x) {
             const int slot = g / tps_d, rt = g % tps_d;
+            if (!s_local[slot]) continue;
             const ExpertW ew = s_ew[slot];
             const int s = it % MM_NS;
             if (it >= MM_NS) ok = mbar_wait(&empty[s], ((it / MM_NS) - 1) & 1, a.err, 1);
@@ -265,7 +287,8 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
             if (lane == 0)
                 bulk_g2s(st + scale_off, ew.down_s + (size_t)((rt * MM_ROWS) / a.br) * scols_d, scols_d * 4, &full[s]);
             pend_stage[pending] = s; pend_slot[pending] = slot; pending++;
-            const bool last = g + (int)gridDim.x >= n_dn;
+            const bool last = g == last_g;
+            it++;
             if (!acts_visible && (pending == MM_NS || last)) {
                 ok = grid_wait(a, 1, 7);
                 if (!ok) break;
@@ -397,9 +420,16 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
 #endif
 
         // ---- gate/up items
+        bool have_sel = false;
         for (int g = blockIdx.x; g < n_gu && ok; g += gridDim.x) {
             int slot, rt;
             gu_slot(g, slot, rt);
+            if (slot != a.K && !have_sel) {            // which of the picks are this rank's
+                ok = mbar_wait_warp(sel_ready, 0, a.err, 10);
+                if (!ok) break;
+                have_sel = true;
+            }
+            if (!s_local[slot]) continue;
             float accf[4] = {0.f, 0.f, 0.f, 0.f};
             for (int kh = 0; kh < a.E / MM_CB && ok; kh++, it++) {
                 const int s = it % MM_NS;
@@ -448,12 +478,15 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
         bool first_down = true;
 
         // ---- down items (the stage's full barrier covers the activation terms too)
-        for (int g = blockIdx.x; g < n_dn && ok; g += gridDim.x, it++) {
+        if (ok && !have_sel) { ok = mbar_wait_warp(sel_ready, 0, a.err, 10); have_sel = ok; }
+        for (int g = blockIdx.x; g < n_dn && ok; g += gridDim.x) {
             const int slot = g / tps_d, rt = g % tps_d;
+            if (!s_local[slot]) continue;
             const int s = it % MM_NS;
             ok = mbar_wait_warp(&full[s], (it / MM_NS) & 1, a.err, 2);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
+            it++;
             if (first_down) { DT_MARK(3); first_down = false; }
             const uint8_t *st = stages + (size_t)s * stage_bytes;
             const float *sc = reinterpret_cast<const float *>(st + scale_off);
@@ -472,7 +505,14 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
                 float v = 0.f;
 #pragma unroll
                 for (int q = 0; q < 4; q++) v += red[(2 * q + m2) * 16 + rr];
-                a.contrib[(size_t)slot * a.E + rt * MM_ROWS + r] = v;
+                const size_t at = (size_t)slot * a.E + rt * MM_ROWS + r;
+                if (a.ep_size > 1 && slot != a.K) {
+                    // a routed pick's row goes straight into every rank's exchange buffer (peer stores)
+                    for (int q = 0; q < a.ep_size; q++)
+                        reinterpret_cast<float *>(static_cast<uint8_t *>(a.peers[q]) + a.rows_off)[at] = v;
+                } else {
+                    a.contrib[at] = v;
+                }
             }
             asm volatile("bar.sync 1, %0;" ::"r"(MM_CONS * 32) : "memory");
         }
@@ -481,7 +521,47 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
             ok = mbar_wait_warp(plan_ready, 0, a.err, 8);
             ok = __all_sync(0xffffffffu, ok);
         }
-        if (ok) {
+        if (ok && a.ep_size > 1) {
+            // ---- expert parallel: every rank's rows are on their way into every rank's buffer. The
+            // last CTA of this rank to get here publishes this rank's step word everywhere; then all
+            // CTAs wait (bounded) for every rank's word and combine a share of the output rows.
+            __threadfence_system();
+            asm volatile("bar.sync 1, %0;" ::"r"(MM_CONS * 32) : "memory");
+            if (ctid == 0) {
+                const int prev = atomicAdd(a.ep_arrive, 1);
+                s_flag = prev == (int)gridDim.x - 1;
+                if (s_flag) *a.ep_arrive = 0;
+            }
+            asm volatile("bar.sync 1, %0;" ::"r"(MM_CONS * 32) : "memory");
+            if (s_flag) {
+                __threadfence_system();
+                if (ctid < a.ep_size)
+                    st_release_sys(reinterpret_cast<unsigned long long *>(a.peers[ctid]) + a.ep_rank, a.ep_step);
+            }
+            asm volatile("bar.sync 1, %0;" ::"r"(MM_CONS * 32) : "memory");
+            if (ctid == 0) s_flag = 1;
+            asm volatile("bar.sync 1, %0;" ::"r"(MM_CONS * 32) : "memory");
+            if (ctid < a.ep_size) {
+                const unsigned long long *mine = reinterpret_cast<const unsigned long long *>(a.peers[a.ep_rank]) + ctid;
+                bool seen = false;
+                for (int i = 0; i < DEC_SPIN_LIMIT && !seen; i++) {
+                    seen = ld_acquire_sys(mine) >= a.ep_step;
+                    if (!seen) __nanosleep(100);
+                }
+                if (!seen) { atomicExch(a.err, 20 + ctid); s_flag = 0; }
+            }
+            asm volatile("bar.sync 1, %0;" ::"r"(MM_CONS * 32) : "memory");
+            if (s_flag) {
+                const float *rows = reinterpret_cast<const float *>(static_cast<const uint8_t *>(a.peers[a.ep_rank]) + a.rows_off);
+                for (int d = blockIdx.x * MM_CONS * 32 + ctid; d < a.E; d += gridDim.x * MM_CONS * 32) {
+                    double sum = 0.0;
+                    for (int j = 0; j < a.K; j++) sum += (double)s_w[j] * (double)__ldcg(rows + (size_t)j * a.E + d);
+                    float o = (float)sum;
+                    if (a.with_shared) o = __fadd_rn(o, __ldcg(a.contrib + (size_t)a.K * a.E + d));
+                    a.out[d] = o;
+                }
+            }
+        } else if (ok) {
             // ---- combine: report every row tile this CTA wrote; whoever completes a tile sums its K
             // contributions in top-k order in FP64 and adds the shared expert in FP32
             __threadfence();
@@ -539,7 +619,7 @@ static size_t decode_smem_bytes(int I)
 bool moe_decode_supported(const MoeShape &s, int T)
 {
     if (!moe_mma_supported(s, T)) return false;
-    if (s.n_local != s.NE || s.NE > 32 * DEC_PER || s.K > 32 || s.K + 1 > MM_MAX_SLOTS) return false;
+    if (s.NE > 32 * DEC_PER || s.K > 32 || s.K + 1 > MM_MAX_SLOTS) return false;
     if (s.E / MM_CB > MM_NS - 1 || s.I != MM_CB) return false;
     if ((size_t)s.E * 4 > MM_NS * (size_t)s.I * 4) return false;
     if (decode_smem_bytes(s.I) > 226 * 1024) return false;
@@ -559,14 +639,16 @@ bool moe_decode_supported(const MoeShape &s, int T)
 int moe_decode(cudaStream_t st, float *out, const float *x, const void *gate, int gate_dt, const float *bias,
                const ExpertW *experts, float *score, int *idx, float *w, void *act, float *contrib,
                const MoeShape &s, int with_shared, unsigned long long *sync, unsigned long long *launches,
-               int *tile_done, int *err)
+               int *tile_done, int *err, const DecodeEp *ep)
 {
     int dev = 0, sms = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     DecodeArgs a{experts, x, gate, gate_dt, bias, score, idx, w, static_cast<__half *>(act), contrib, out,
                  s.E, s.I, s.NE, s.K, s.br, s.bc, with_shared, s.norm_topk, s.limit, s.routed_scale,
-                 sync, (*launches) * (unsigned long long)sms, tile_done, err};
+                 sync, (*launches) * (unsigned long long)sms, tile_done, err,
+                 ep ? ep->rank : 0, ep ? ep->size : 1, s.n_local0, s.n_local, ep ? ep->peers : nullptr,
+                 ep ? ep->rows_off : 0, ep ? ep->step : 0ull, ep ? ep->arrive : nullptr};
     void *params[] = {&a};
     cudaError_t rc;
 #ifdef G5B_STAGE_TIMERS
