@@ -107,6 +107,7 @@ struct g5b_engine {
     float *kq, *kk, *kv, *kz, *kgb, *ko, *kbraw, *klr;
     float *mq_raw, *mct, *mwk, *mgate, *mwp, *mq, *mqidx, *mcb, *macc, *mscore, *minvq;
     double *mqa, *mdsc, *mpart = nullptr, *mstats = nullptr;
+    float *post_h = nullptr; int post_n = 0;             // positions whose hc_post is still owed (run_layer)
     double *hc_part = nullptr; int *hc_count = nullptr;  // fused mHC site: partial sums and per-token counters
     void *xterms = nullptr; float *xinv = nullptr;      // batched expert kernels: F16 terms of the activations
     int   *msel, *mnsel;
@@ -742,6 +743,14 @@ static int run_hc_pre(g5b_engine *e, const HcW &hw, const float *h, int n)
     return 0;
 }
 
+// The stream expansion a decoder-layer site still owes (see run_layer).
+static void flush_hc_post(g5b_engine *e)
+{
+    if (!e->post_h) return;
+    hc_post(e->st, e->post_h, e->y, e->post, e->comb, e->post_n, e->c.hc_mult, e->c.hidden);
+    e->post_h = nullptr;
+}
+
 // One decoder layer over n <= CHUNK positions (reference: glm53f_decoder_layer,
 // src/core/glm53f_ops.c:1400-1433).
 static int run_layer(g5b_engine *e, int l, float *h, int n, int cached)
@@ -753,9 +762,14 @@ static int run_layer(g5b_engine *e, int l, float *h, int n, int cached)
         if (!w.in_norm || !w.post_norm) return fail("this layer's norms were not loaded");
         const HcW &hw = w.hc[site];
         if (hw.fn.loaded() && hw.base && hw.scale && hc_pre_fused_supported(hw, M, E)) {
-            hc_pre_fused(e->st, e->xn, e->post, e->comb, h, hw, site ? w.post_norm : w.in_norm, e->hc_part, e->hc_count,
-                         n, M, E, c.hc_iters, c.hc_eps, c.rms_eps);
+            // the previous site's stream expansion, if still owed to these positions, rides along
+            const bool ride = e->post_h == h && e->post_n == n;
+            if (!ride) flush_hc_post(e);
+            hc_pre_fused(e->st, e->xn, e->post, e->comb, h, ride ? e->y : nullptr, hw, site ? w.post_norm : w.in_norm,
+                         e->hc_part, e->hc_count, n, M, E, c.hc_iters, c.hc_eps, c.rms_eps);
+            e->post_h = nullptr;
         } else {
+            flush_hc_post(e);
             if (run_hc_pre(e, hw, h, n)) return -1;
             rms_factor(e->st, e->xc, E, E, n, c.rms_eps, e->inv1);
             rms_apply(e->st, e->xn, e->xc, site ? w.post_norm : w.in_norm, e->inv1, E, E, n);
@@ -764,7 +778,9 @@ static int run_layer(g5b_engine *e, int l, float *h, int n, int cached)
         if (site == 0) rc = w.is_mla ? run_mla(e, w, e->xn, n, cached, e->y) : run_kda(e, w, e->xn, n, e->y);
         else           rc = w.is_dense ? run_mlp(e, w, e->xn, n, e->y) : run_moe(e, w, e->xn, n, e->y, 1);
         if (rc) return rc;
-        hc_post(e->st, h, e->y, e->post, e->comb, n, M, E);
+        // owed: h' = hc_post(h, y). The next site on these positions applies it inside its own launch;
+        // anything else that touches h calls flush_hc_post first.
+        e->post_h = h; e->post_n = n;
     }
     return 0;
 }
@@ -818,12 +834,14 @@ static int forward_device(g5b_engine *e, const int *ids_dev, int T, bool all_pos
     if (!e->embed.loaded() || !e->lm_head.loaded() || !e->norm)
         return fail("forward needs embed_tokens, norm and lm_head");
     if (ensure_h(e, (size_t)T)) return -1;
+    e->post_h = nullptr;                              // nothing is owed from a call that failed half-way
     embed_rows(e->st, e->h, e->embed, ids_dev, T, M);
     for (int l = 0; l < c.n_layers; l++)
         for (int t0 = 0; t0 < T; t0 += CHUNK) {
             const int n = T - t0 < CHUNK ? T - t0 : CHUNK;
             if (run_layer(e, l, e->h + (size_t)t0 * M * E, n, e->cached + t0)) return -1;
         }
+    flush_hc_post(e);
     const int first = all_positions ? 0 : T - 1;
     for (int t0 = first; t0 < T; t0 += CHUNK) {
         const int n = T - t0 < CHUNK ? T - t0 : CHUNK;
@@ -955,7 +973,11 @@ extern "C" int g5b_dev_mla(g5b_engine *e, int layer, const float *x_dev, int T, 
 extern "C" int g5b_dev_decoder_layer(g5b_engine *e, int layer, float *h_dev, int T, int cached)
 {
     if (check_layer(e, layer, T)) return -1;
-    return run_layer(e, layer, h_dev, T, cached);
+    e->post_h = nullptr;
+    const int rc = run_layer(e, layer, h_dev, T, cached);
+    if (rc) e->post_h = nullptr;
+    flush_hc_post(e);
+    return rc;
 }
 
 // ------------------------------------------------------------------ host-buffer ops ----
@@ -1113,7 +1135,12 @@ extern "C" int g5b_op_decoder_layer(g5b_engine *e, int layer, float *h, int T, i
     Staged s{e};
     float *hd = s.in(h, (size_t)T * M * E);
     if (!hd) return fail("out of device memory");
-    FOR_CHUNKS(T) if (run_layer(e, layer, hd + t0 * M * E, n_, cached + t0)) return -1;
+    FOR_CHUNKS(T) {
+        e->post_h = nullptr;
+        const int rc = run_layer(e, layer, hd + t0 * M * E, n_, cached + t0);
+        if (rc) { e->post_h = nullptr; return -1; }
+        flush_hc_post(e);
+    }
     return s.out(h, hd, (size_t)T * M * E);
 }
 

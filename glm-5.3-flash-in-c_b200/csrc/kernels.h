@@ -74,9 +74,11 @@ void hc_finish(cudaStream_t st, float *x, float *post, float *comb, const float 
 // The whole pre side of a site in one launch, ending in the sub-block's normalised input xn
 // (RMSNorm with norm_w). part: [T][32][(2+M)M + 1] doubles, counters: [T] zeroed ints.
 bool hc_pre_fused_supported(const HcW &w, int M, int E);
-void hc_pre_fused(cudaStream_t st, float *xn, float *post, float *comb, const float *h, const HcW &w,
-                  const float *norm_w, double *part, int *counters, int T, int M, int E, int iters, float hc_eps,
-                  float rms_eps);
+// y_pending != nullptr: the previous site's hc_post (y_pending with the post / comb still in the
+// arrays) is applied to h first, in the same launch.
+void hc_pre_fused(cudaStream_t st, float *xn, float *post, float *comb, float *h, const float *y_pending,
+                  const HcW &w, const float *norm_w, double *part, int *counters, int T, int M, int E, int iters,
+                  float hc_eps, float rms_eps);
 void hc_post(cudaStream_t st, float *h, const float *y, const float *post, const float *comb, int T,
              int M, int E);
 

@@ -111,7 +111,9 @@ constexpr int HCF_SLICES = 32, HCF_MAX_E = 8192, HCF_MAX_MIX = (2 + G5B_MAX_HC) 
 
 struct HcFused {
     float *xn, *post, *comb;
-    const float *h;
+    float *h;                       // [T][M][E]; rewritten in place when y is given
+    const float *y;                 // optional: the previous sub-block's output [T][E] - its hc_post
+                                    // (with the post / comb still in the arrays above) is applied first
     const uint16_t *fn;             // BF16 [(2+M)M][M*E]
     const float *base, *scale, *norm_w;
     double *part;                   // [T][HCF_SLICES][(2+M)M + 1]
@@ -132,29 +134,50 @@ __global__ void __launch_bounds__(HC_THREADS) hc_pre_fused_kernel(const HcFused 
     __shared__ int is_last;
     const int t = blockIdx.y, cta = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int M = a.M, E = a.E, ME = M * E, MIX = (2 + M) * M;
-    const int width = ME / HCF_SLICES, c0 = cta * width;
-    const float *ht = a.h + (size_t)t * ME;
+    const int W = E / HCF_SLICES, d0 = cta * W;                 // this CTA's columns, of every stream
+    float *ht = a.h + (size_t)t * ME;
 
-    // ---- every CTA: its slice
-    double ss = 0.0;
-    for (int i = tid; i < width; i += HC_THREADS) {
-        const float v = ht[c0 + i];
-        hs[i] = v;
-        ss += (double)v * (double)v;
+    // ---- every CTA: its columns of the M streams
+    for (int i = tid; i < M * W; i += HC_THREADS) hs[i] = ht[(size_t)(i / W) * E + d0 + (i % W)];
+    __syncthreads();
+    if (a.y) {
+        // the pending hc_post of the previous site: h'[j][d] = post[j] y[d] + sum_i comb[i][j] h[i][d]
+        // in FP64 (src/core/glm53f_ops.c:612-625), written back and used below
+        float nv[G5B_MAX_HC];
+        if (tid < W) {
+            const double yv = (double)a.y[(size_t)t * E + d0 + tid];
+            const float *cb = a.comb + (size_t)t * M * M, *po = a.post + (size_t)t * M;
+            for (int j = 0; j < M; j++) {
+                double sj = (double)po[j] * yv;
+                for (int i = 0; i < M; i++) sj += (double)cb[i * M + j] * (double)hs[i * W + tid];
+                nv[j] = (float)sj;
+            }
+        }
+        __syncthreads();
+        if (tid < W)
+            for (int j = 0; j < M; j++) {
+                hs[j * W + tid] = nv[j];
+                ht[(size_t)j * E + d0 + tid] = nv[j];
+            }
+        __syncthreads();
     }
-    ss = block_sum(ss, red);                                   // also orders the writes of hs
+    double ss = 0.0;
+    for (int i = tid; i < M * W; i += HC_THREADS) ss += (double)hs[i] * (double)hs[i];
+    ss = block_sum(ss, red);
     double *mine = a.part + ((size_t)t * HCF_SLICES + cta) * (MIX + 1);
     if (tid == 0) mine[MIX] = ss;
+    const int per_seg = W / 8;                                     // 16-byte pieces per stream segment
     for (int k = warp; k < MIX; k += HC_THREADS / 32) {
-        const uint16_t *row = a.fn + (size_t)k * ME + c0;
+        const uint16_t *row = a.fn + (size_t)k * ME + d0;
         double acc = 0.0;
-        for (int i = lane * 8; i < width; i += 256) {
-            const uint4 wv = ld_stream16(row + i);
+        for (int piece = lane; piece < M * per_seg; piece += 32) {
+            const int i = piece / per_seg, off = (piece % per_seg) * 8;
+            const uint4 wv = ld_stream16(row + (size_t)i * E + off);
             float w[8];
             bf16x2_to_f32(wv.x, w[0], w[1]); bf16x2_to_f32(wv.y, w[2], w[3]);
             bf16x2_to_f32(wv.z, w[4], w[5]); bf16x2_to_f32(wv.w, w[6], w[7]);
 #pragma unroll
-            for (int j = 0; j < 8; j++) acc = fma((double)w[j], (double)hs[i + j], acc);
+            for (int j = 0; j < 8; j++) acc = fma((double)w[j], (double)hs[i * W + off + j], acc);
         }
         acc = warp_sum(acc);
         if (lane == 0) mine[k] = acc;
@@ -284,17 +307,16 @@ __global__ void __launch_bounds__(HC_THREADS) hc_pre_fused_kernel(const HcFused 
 
 bool hc_pre_fused_supported(const HcW &w, int M, int E)
 {
-    const int ME = M * E;
-    return w.fn.dt == DT_BF16 && E <= HCF_MAX_E && E % 4 == 0 && M <= G5B_MAX_HC && ME % (HCF_SLICES * 256) == 0 &&
-           ME / HCF_SLICES <= HCF_MAX_E * G5B_MAX_HC / HCF_SLICES;
+    return w.fn.dt == DT_BF16 && E <= HCF_MAX_E && E % (HCF_SLICES * 8) == 0 && M <= G5B_MAX_HC &&
+           M * (E / HCF_SLICES) <= HCF_MAX_E * G5B_MAX_HC / HCF_SLICES && E / HCF_SLICES <= HC_THREADS;
 }
 
-void hc_pre_fused(cudaStream_t st, float *xn, float *post, float *comb, const float *h, const HcW &w,
-                  const float *norm_w, double *part, int *counters, int T, int M, int E, int iters, float hc_eps,
-                  float rms_eps)
+void hc_pre_fused(cudaStream_t st, float *xn, float *post, float *comb, float *h, const float *y_pending,
+                  const HcW &w, const float *norm_w, double *part, int *counters, int T, int M, int E, int iters,
+                  float hc_eps, float rms_eps)
 {
-    HcFused a{xn, post, comb, h, static_cast<const uint16_t *>(w.fn.w), w.base, w.scale, norm_w, part, counters,
-              M, E, iters, hc_eps, rms_eps};
+    HcFused a{xn, post, comb, h, y_pending, static_cast<const uint16_t *>(w.fn.w), w.base, w.scale, norm_w, part,
+              counters, M, E, iters, hc_eps, rms_eps};
     G5B_LAUNCH(hc_pre_fused_kernel, dim3(HCF_SLICES, T), HC_THREADS, 0, st, a);
 }
 
