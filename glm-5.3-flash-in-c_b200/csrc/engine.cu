@@ -107,6 +107,7 @@ struct g5b_engine {
     float *kq, *kk, *kv, *kz, *kgb, *ko, *kbraw, *klr;
     float *mq_raw, *mct, *mwk, *mgate, *mwp, *mq, *mqidx, *mcb, *macc, *mscore, *minvq;
     double *mqa, *mdsc, *mpart = nullptr, *mstats = nullptr;
+    int *mcount = nullptr;
     float *post_h = nullptr; int post_n = 0;             // positions whose hc_post is still owed (run_layer)
     double *hc_part = nullptr; int *hc_count = nullptr;  // fused mHC site: partial sums and per-token counters
     void *xterms = nullptr; float *xinv = nullptr;      // batched expert kernels: F16 terms of the activations
@@ -511,7 +512,7 @@ extern "C" int g5b_engine_finalize(g5b_engine *e)
         walloc(e, &e->mscore, N * ((size_t)e->cap / c.index_kpool + 1)) || walloc(e, &e->minvq, N) ||
         walloc(e, &e->mqa, N * H * KL) || walloc(e, &e->mdsc, N * H * stride) ||
         walloc(e, &e->msel, N * stride) || walloc(e, &e->mnsel, N) ||
-        walloc(e, &e->mstats, N * H * 2) ||
+        walloc(e, &e->mstats, N * H * 2) || walloc(e, &e->mcount, N * H) ||
         walloc(e, &e->mpart, (size_t)MLA_PART_TOKENS * H * ((stride + 31) / 32) * KL)) return -1;
     const size_t pairs = N * K + N;
     if (walloc(e, &e->rscore, N * c.n_experts) || walloc(e, &e->rw, N * K) || walloc(e, &e->ridx, N * K) ||
@@ -717,16 +718,15 @@ static int run_mla(g5b_engine *e, Layer &w, const float *x, int n, int cached, f
                     make_seg(w.wk, x, E, e->mwk, c.index_dim), make_seg(w.igate, x, E, e->mgate, c.index_dim),
                     make_seg(w.wproj, x, E, e->mwp, c.index_heads)};
     gemv_batch(e->st, a, 5, n);
-    rms_factor(e->st, e->mq_raw, c.q_lora, c.q_lora, n, c.rms_eps, e->minvq);
     mla_store(e->st, w.latent, w.idx_state, e->mct, w.kv_a_norm, e->mwk, e->mgate, w.k_norm_w, w.k_norm_b,
-              w.ape, n, cached, s);
+              w.ape, e->mq_raw, e->minvq, n, cached, s);
     // q = q_b(RMSNorm(q_a x)) and the indexer query, the norm applied on the way into the product
     GemvSeg b[2] = {make_seg(w.q_b, e->mq_raw, c.q_lora, e->mq, c.mla_heads * c.qk_nope, e->minvq, w.q_a_norm),
                     make_seg(w.wq_b, e->mq_raw, c.q_lora, e->mqidx, c.index_heads * c.index_dim, e->minvq, w.q_a_norm)};
     gemv_batch(e->st, b, 2, n);
     dsa_select(e->st, e->msel, e->mnsel, w.idx_state, e->mqidx, e->mwp, e->mscore, n, cached, s);
     mla_absorb(e->st, e->mqa, e->mq, w.kv_b, n, s);
-    mla_attend(e->st, e->mcb, e->mqa, w.latent, e->msel, e->mnsel, e->mdsc, e->mpart, e->mstats, MLA_PART_TOKENS, n, cached, s);
+    mla_attend(e->st, e->mcb, e->mqa, w.latent, e->msel, e->mnsel, e->mdsc, e->mpart, e->mstats, e->mcount, MLA_PART_TOKENS, n, cached, s);
     mla_vout(e->st, e->macc, e->mcb, w.kv_b, n, s);
     gemv(e->st, w.mo, e->macc, c.mla_heads * c.v_head, out, E, n);
     return 0;

@@ -188,18 +188,20 @@ struct MlaShape {
     float rms_eps;
     int latent_bf16;
 };
+// Also writes q_inv[t] = RMSNorm factor of q_raw[t][q_lora] (the q_a output of the same positions).
 void mla_store(cudaStream_t st, void *latent, float *idx_state, const float *ct_raw,
                const float *kv_norm_w, const float *wk_raw, const float *gate_raw,
-               const float *k_norm_w, const float *k_norm_b, const float *ape, int T, int cached,
-               const MlaShape &s);
+               const float *k_norm_w, const float *k_norm_b, const float *ape, const float *q_raw, float *q_inv,
+               int T, int cached, const MlaShape &s);
 void dsa_select(cudaStream_t st, int *sel, int *nsel, const float *idx_state, const float *qidx,
                 const float *wproj, float *score, int T, int cached, const MlaShape &s);
 void mla_absorb(cudaStream_t st, double *qa, const float *q, const DMat &kv_b, int T, const MlaShape &s);
 // part: FP64 partial sums [part_tokens][H][ceil((topk+KP)/32)][KL], stats [T][H][2]; part == nullptr
 // falls back to one CTA per head.
+// counters: [T][H / 4] zeroed ints (the score kernel's per head-group arrival counts).
 void mla_attend(cudaStream_t st, float *cb, const double *qa, const void *latent, const int *sel,
-                const int *nsel, double *dsc, double *part, double *stats, int part_tokens, int T, int cached,
-                const MlaShape &s);
+                const int *nsel, double *dsc, double *part, double *stats, int *counters, int part_tokens, int T,
+                int cached, const MlaShape &s);
 void mla_vout(cudaStream_t st, float *acc_out, const float *cb, const DMat &kv_b, int T, const MlaShape &s);
 
 }  // namespace g5b

@@ -30,11 +30,26 @@ __device__ __forceinline__ float latent_at(const void *latent, int bf16, size_t 
 // ------------------------------------------------------------------- append ----
 // Per new position: latent = RMSNorm(kv_a x) into the cache; indexer key = LayerNorm(wk x)
 // (biased variance, eps 1e-6, FP64) and gate = gate x into the indexer state.
+__device__ void dsa_pool_one(float *idx_state, const float *ape, int pool, int i, const MlaShape &s);
+
+// Blocks [0, T) do the above; blocks [T, 2T) compute the RMSNorm factor of q_a's output for the same
+// positions (it used to be a launch of its own). With one new position, the block also closes the
+// pool that position completes (otherwise dsa_pool_kernel follows).
 __global__ void __launch_bounds__(256) mla_store_kernel(
     void *latent, float *idx_state, const float *ct_raw, const float *kv_norm_w, const float *wk_raw,
-    const float *gate_raw, const float *k_norm_w, const float *k_norm_b, int cached, MlaShape s)
+    const float *gate_raw, const float *k_norm_w, const float *k_norm_b, int cached, MlaShape s,
+    const float *q_raw, float *q_inv, int T, const float *ape, int pool_here)
 {
     __shared__ double red[32];
+    if ((int)blockIdx.x >= T) {
+        const int tq = blockIdx.x - T;
+        const float *row = q_raw + (size_t)tq * s.q_lora;
+        double ssq = 0.0;
+        for (int i = threadIdx.x; i < s.q_lora; i += blockDim.x) ssq += (double)row[i] * (double)row[i];
+        ssq = block_sum(ssq, red);
+        if (threadIdx.x == 0) q_inv[tq] = (float)(1.0 / sqrt(ssq / (double)s.q_lora + (double)s.rms_eps));
+        return;
+    }
     const int t = blockIdx.x, pos = cached + t;
     const float *ct = ct_raw + (size_t)t * s.KL;
     double ss = 0.0;
@@ -59,13 +74,15 @@ __global__ void __launch_bounds__(256) mla_store_kernel(
         kp[i] = mul_add_unfused((float)(((double)raw[i] - mean) * linv), k_norm_w[i], k_norm_b[i]);
         gp[i] = gate_raw[(size_t)t * s.ID + i];
     }
+    if (pool_here >= 0) {                                     // this position completes a pool
+        __syncthreads();                                      // its key and gate are written (same block)
+        for (int i = threadIdx.x; i < s.ID; i += blockDim.x) dsa_pool_one(idx_state, ape, pool_here, i, s);
+    }
 }
 
 // Pools closed by this call: per channel, softmax over the pool's (gate + ape) weights its keys.
-__global__ void dsa_pool_kernel(float *idx_state, const float *ape, int pool0, MlaShape s)
+__device__ void dsa_pool_one(float *idx_state, const float *ape, int pool, int i, const MlaShape &s)
 {
-    const int pool = pool0 + blockIdx.x, i = threadIdx.x;
-    if (i >= s.ID) return;
     const int KP = s.KP;
     double top = -INFINITY, z = 0.0, acc = 0.0;
     for (int j = 0; j < KP; j++) {
@@ -81,16 +98,24 @@ __global__ void dsa_pool_kernel(float *idx_state, const float *ape, int pool0, M
     st_pool(idx_state, s.ID, s.cap, pool)[i] = (float)acc;
 }
 
+__global__ void dsa_pool_kernel(float *idx_state, const float *ape, int pool0, MlaShape s)
+{
+    const int pool = pool0 + blockIdx.x, i = threadIdx.x;
+    if (i >= s.ID) return;
+    dsa_pool_one(idx_state, ape, pool, i, s);
+}
+
 void mla_store(cudaStream_t st, void *latent, float *idx_state, const float *ct_raw,
                const float *kv_norm_w, const float *wk_raw, const float *gate_raw,
-               const float *k_norm_w, const float *k_norm_b, const float *ape, int T, int cached,
-               const MlaShape &s)
+               const float *k_norm_w, const float *k_norm_b, const float *ape, const float *q_raw, float *q_inv,
+               int T, int cached, const MlaShape &s)
 {
-    G5B_LAUNCH(mla_store_kernel, T, 256, 0, st, latent, idx_state, ct_raw, kv_norm_w, wk_raw, gate_raw,
-               k_norm_w, k_norm_b, cached, s);
     const int pool0 = cached / s.KP;                                         // pools closed before this call
     const int pool1 = (cached + T) / s.KP;                                   // pools closed after this call
-    if (pool1 > pool0)
+    const int pool_here = (T == 1 && pool1 > pool0) ? pool0 : -1;
+    G5B_LAUNCH(mla_store_kernel, 2 * T, 256, 0, st, latent, idx_state, ct_raw, kv_norm_w, wk_raw, gate_raw,
+               k_norm_w, k_norm_b, cached, s, q_raw, q_inv, T, ape, pool_here);
+    if (pool1 > pool0 && pool_here < 0)
         G5B_LAUNCH(dsa_pool_kernel, pool1 - pool0, ((s.ID + 31) / 32) * 32, 0, st, idx_state, ape, pool0, s);
 }
 
@@ -333,9 +358,15 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) mla_score_kernel(
 // heads stay in registers (lane l holds elements 2l, 2l+1 of every 64), a latent row is loaded
 // once for the four of them, and the four sums cross the warp in six exchanges instead of twenty.
 constexpr int SC_HEADS = 4, SC_CHUNK = 64;
+// The chunk CTA that finishes a (token, head group) last - a counter, no spinning - also takes the
+// softmax statistics of its four heads (max of the unrounded scores, z of the float-rounded ones:
+// src/core/glm53f_ops.c:890-903), which saves the launch that did only that.
 __global__ void __launch_bounds__(256) mla_score4_kernel(double *dsc, const double *qa, const void *latent, const int *sel,
-                                                         const int *nsel, int cached, int stride, MlaShape s)
+                                                         const int *nsel, int cached, int stride, MlaShape s,
+                                                         double *stats, int *counters)
 {
+    __shared__ double ptop[8], pz[8];
+    __shared__ int is_last;
     const int h0 = blockIdx.y * SC_HEADS, t = blockIdx.z, p = cached + t;
     const int ns = nsel ? nsel[t] : -1;
     const int nvis = ns < 0 ? p + 1 : ns;
@@ -402,6 +433,37 @@ __global__ void __launch_bounds__(256) mla_score4_kernel(double *dsc, const doub
         if (jj1 < jend) load_row(c1, row1);
         finish(c0, jj0);
         if (jj1 < jend) finish(c1, jj1);
+    }
+    // ---- statistics by the last chunk of this (token, head group)
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int *cnt = counters + (size_t)t * gridDim.y + blockIdx.y;
+        const int active = (nvis + SC_CHUNK - 1) / SC_CHUNK;
+        const int prev = atomicAdd(cnt, 1);
+        is_last = prev == active - 1;
+        if (is_last) *cnt = 0;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    const int hh = warp >> 1, half = warp & 1;                 // two warps per head
+    const double *d = dsc + ((size_t)t * s.H + h0 + hh) * stride;
+    double top = -INFINITY;
+    for (int jj = half * 32 + lane; jj < nvis; jj += 64) top = fmax(top, __ldcg(d + jj));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) top = fmax(top, __shfl_xor_sync(0xffffffffu, top, o));
+    if (lane == 0) ptop[warp] = top;
+    __syncthreads();
+    top = fmax(ptop[2 * hh], ptop[2 * hh + 1]);
+    double z = 0.0;
+    for (int jj = half * 32 + lane; jj < nvis; jj += 64) z += exp((double)(float)__ldcg(d + jj) - top);
+    z = warp_sum(z);
+    if (lane == 0) pz[warp] = z;
+    __syncthreads();
+    if (half == 0 && lane == 0) {
+        stats[((size_t)t * s.H + h0 + hh) * 2] = top;
+        stats[((size_t)t * s.H + h0 + hh) * 2 + 1] = pz[2 * hh] + pz[2 * hh + 1];
     }
 }
 
@@ -549,16 +611,17 @@ __global__ void __launch_bounds__(256) mla_wsum_reduce_kernel(float *cb, const d
 }
 
 void mla_attend(cudaStream_t st, float *cb, const double *qa, const void *latent, const int *sel,
-                const int *nsel, double *dsc, double *part, double *stats, int part_tokens, int T, int cached,
-                const MlaShape &s)
+                const int *nsel, double *dsc, double *part, double *stats, int *counters, int part_tokens, int T,
+                int cached, const MlaShape &s)
 {
     const int nvis_max = cached + T < s.topk + s.KP ? cached + T : s.topk + s.KP;
     const int stride = s.topk + s.KP;
     int blocks = (nvis_max + ATT_WARPS - 1) / ATT_WARPS;
     if (blocks > 32) blocks = 32;
-    if (s.KL == 512 && s.H % SC_HEADS == 0)
+    const bool fast_score = s.KL == 512 && s.H % SC_HEADS == 0 && stats && counters;
+    if (fast_score)
         G5B_LAUNCH(mla_score4_kernel, dim3((nvis_max + SC_CHUNK - 1) / SC_CHUNK, s.H / SC_HEADS, T), 256, 0, st, dsc, qa,
-                   latent, sel, nsel, cached, stride, s);
+                   latent, sel, nsel, cached, stride, s, stats, counters);
     else
         G5B_LAUNCH(mla_score_kernel, dim3(blocks, s.H, T), ATT_WARPS * 32, (size_t)s.KL * sizeof(double), st, dsc, qa,
                    latent, sel, nsel, cached, stride, s);
@@ -568,7 +631,7 @@ void mla_attend(cudaStream_t st, float *cb, const double *qa, const void *latent
         return;
     }
     const int nchunks = (stride + WS_CHUNK - 1) / WS_CHUNK;             // the partial buffer is laid out for this many
-    G5B_LAUNCH(mla_softmax_stats_kernel, dim3(s.H, T), 256, 0, st, stats, dsc, nsel, cached, stride, s);
+    if (!fast_score) G5B_LAUNCH(mla_softmax_stats_kernel, dim3(s.H, T), 256, 0, st, stats, dsc, nsel, cached, stride, s);
     for (int t0 = 0; t0 < T; t0 += part_tokens) {
         const int n = T - t0 < part_tokens ? T - t0 : part_tokens;
         const int used = (((cached + t0 + n < stride) ? cached + t0 + n : stride) + WS_CHUNK - 1) / WS_CHUNK;
