@@ -98,6 +98,8 @@ def lib() -> C.CDLL:
     L.g5b_engine_ep_handle_bytes.restype = C.c_size_t
     L.g5b_engine_ep_export.argtypes = [C.c_void_p, C.c_void_p]
     L.g5b_engine_ep_connect.argtypes = [C.c_void_p, C.c_void_p]
+    L.g5b_engine_use_sequence.argtypes = [C.c_void_p, C.c_int]
+    L.g5b_engine_decode_batch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
     L.g5b_engine_set_option.argtypes = [C.c_void_p, C.c_char_p, C.c_int]
     for fn in ("g5b_dev_moe", "g5b_dev_kda"):
         getattr(L, fn).argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p]
@@ -316,6 +318,21 @@ class Engine(FlatModel):
         if self.L.g5b_engine_fill_expert(self.handle, layer, expert, seed, g.ctypes.data, u.ctypes.data,
                                          d.ctypes.data) != 0:
             self._err("fill_expert")
+
+    def use_sequence(self, seq: int):
+        if self.L.g5b_engine_use_sequence(self.handle, seq) != 0:
+            self._err("use_sequence")
+
+    def decode_batch(self, ids, want_logits=True):
+        """One new token per sequence (option "sequences"): returns (logits [S][vocab] or None, argmax [S])."""
+        ids = np.ascontiguousarray(ids, dtype=np.int32)
+        S = ids.size
+        lg = np.zeros((S, self.cfg.vocab), np.float32) if want_logits else None
+        am = np.zeros(S, np.int32)
+        if self.L.g5b_engine_decode_batch(self.handle, ids.ctypes.data, lg.ctypes.data if want_logits else None,
+                                          am.ctypes.data) != 0:
+            self._err("decode_batch")
+        return lg, am
 
     def ep_export(self) -> bytes:
         """This rank's exchange-region handle (g5b_engine_ep_export), to be gathered from all ranks."""

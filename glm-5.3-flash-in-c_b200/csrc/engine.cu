@@ -81,6 +81,11 @@ struct g5b_engine {
     g5b_config c;
     int cap = 0, cached = 0, device = 0, ep_rank = 0, ep_size = 1, n_local0 = 0, n_local = 0;
     bool finalized = false, ep_connected = false;
+    // independent sequences (option "sequences", default 1): every layer's session state exists once
+    // per sequence; single-sequence calls address sequence `cur_seq`
+    int n_seq = 1, cur_seq = 0;
+    std::vector<int> cached_seq;
+    size_t kda_seq = 0, lat_seq = 0, idx_seq = 0;          // elements between consecutive sequences' states
     // expert-parallel exchange region of this rank: ep_size 64-bit words, then two row buffers
     uint8_t *ep_region = nullptr;
     size_t ep_rows_bytes = 0;
@@ -270,6 +275,12 @@ extern "C" int g5b_engine_set_option(g5b_engine *e, const char *name, int value)
     }
     if (!strcmp(name, "profile")) { e->profile = value; return 0; }
     if (!strcmp(name, "allow_partial")) { e->partial = value != 0; return 0; }
+    if (!strcmp(name, "sequences")) {
+        if (e->finalized) return fail("set the number of sequences before finalize");
+        if (value < 1 || value > CHUNK) return fail("sequences is 1..%d", CHUNK);
+        e->n_seq = value;
+        return 0;
+    }
     if (!strcmp(name, "ep_loopback")) return value ? ep_loopback(e) : 0;
     if (!strcmp(name, "stream_experts")) {       // batch-1 experts: 0 register kernels, 1 streamed CUDA-core,
                                                  // 2 streamed tensor-core, 3 the whole layer as one kernel
@@ -485,13 +496,15 @@ extern "C" int g5b_engine_finalize(g5b_engine *e)
         }
         // session state (reference: src/model/glm53f_model.c:194-228, always the latent form here)
         if (w.is_mla) {
-            if (e->dalloc(&w.latent, (size_t)e->cap * c.kv_lora * (e->latent_bf16 ? 2 : 4))) return -1;
-            const size_t ni = (size_t)2 * e->cap * c.index_dim +
-                              (size_t)((e->cap + c.index_kpool - 1) / c.index_kpool) * c.index_dim;
-            if (walloc(e, &w.idx_state, ni)) return -1;
+            e->lat_seq = (size_t)e->cap * c.kv_lora;
+            e->idx_seq = (size_t)2 * e->cap * c.index_dim +
+                         (size_t)((e->cap + c.index_kpool - 1) / c.index_kpool) * c.index_dim;
+            if (e->dalloc(&w.latent, e->n_seq * e->lat_seq * (e->latent_bf16 ? 2 : 4))) return -1;
+            if (walloc(e, &w.idx_state, e->n_seq * e->idx_seq)) return -1;
         } else {
             const size_t P = (size_t)c.kda_heads * c.kda_head_dim;
-            if (walloc(e, &w.kda_state, P * c.kda_head_dim + 3 * P * (size_t)(c.conv_k - 1))) return -1;
+            e->kda_seq = P * c.kda_head_dim + 3 * P * (size_t)(c.conv_k - 1);
+            if (walloc(e, &w.kda_state, e->n_seq * e->kda_seq)) return -1;
         }
     }
     const size_t N = CHUNK, E = c.hidden, M = c.hc_mult, MIX = (2 + M) * M;
@@ -536,6 +549,7 @@ extern "C" int g5b_engine_finalize(g5b_engine *e)
     if (walloc(e, &e->xm, N * E) || walloc(e, &e->inv_head, N) || walloc(e, &e->logits, N * (size_t)c.vocab) ||
         walloc(e, &e->am_v, N * 64) || walloc(e, &e->am_i, N * 64) || walloc(e, &e->am_out, (size_t)e->cap + N)) return -1;
     CU(cudaStreamSynchronize(e->st));
+    e->cached_seq.assign((size_t)e->n_seq, 0);
     e->finalized = true;
     return 0;
 }
@@ -677,7 +691,9 @@ static int run_mlp(g5b_engine *e, Layer &w, const float *x, int n, float *out)
     return 0;
 }
 
-static int run_kda(g5b_engine *e, Layer &w, const float *x, int n, float *out)
+// batch: the n rows are one new position of n different sequences (sequences 0..n-1), otherwise n
+// consecutive positions of the current sequence.
+static int run_kda(g5b_engine *e, Layer &w, const float *x, int n, float *out, bool batch = false)
 {
     const g5b_config &c = e->c;
     const int E = c.hidden, H = c.kda_heads, D = c.kda_head_dim, P = H * D;
@@ -690,8 +706,12 @@ static int run_kda(g5b_engine *e, Layer &w, const float *x, int n, float *out)
     GemvSeg b[2] = {make_seg(w.f_b, lrf, D, e->kz, P), make_seg(w.g_b, lrg, D, e->kgb, P)};
     gemv_batch(e->st, b, 2, n);
     KdaShape ks{H, D, c.conv_k, c.gate_lb, c.rms_eps};
-    kda_core(e->st, e->ko, e->kq, e->kk, e->kv, e->kz, e->kbraw, e->kgb, w.q_conv, w.k_conv, w.v_conv,
-             w.A_log, w.dt_bias, w.o_norm, w.kda_state, n, ks);
+    if (batch)
+        kda_core(e->st, e->ko, e->kq, e->kk, e->kv, e->kz, e->kbraw, e->kgb, w.q_conv, w.k_conv, w.v_conv,
+                 w.A_log, w.dt_bias, w.o_norm, w.kda_state, 1, ks, n, e->kda_seq);
+    else
+        kda_core(e->st, e->ko, e->kq, e->kk, e->kv, e->kz, e->kbraw, e->kgb, w.q_conv, w.k_conv, w.v_conv,
+                 w.A_log, w.dt_bias, w.o_norm, w.kda_state + (size_t)e->cur_seq * e->kda_seq, n, ks);
     gemv(e->st, w.ko, e->ko, P, out, E, n);
     return 0;
 }
@@ -706,27 +726,31 @@ static MlaShape mla_shape(const g5b_engine *e)
     return s;
 }
 
-static int run_mla(g5b_engine *e, Layer &w, const float *x, int n, int cached, float *out)
+static int run_mla(g5b_engine *e, Layer &w, const float *x, int n, int cached, float *out, bool batch = false)
 {
     const g5b_config &c = e->c;
     const int E = c.hidden;
-    const MlaShape s = mla_shape(e);
+    MlaShape s = mla_shape(e);
+    // the caches of the sequence(s) this call works on
+    void *lat = static_cast<uint8_t *>(w.latent) + (batch ? 0 : (size_t)e->cur_seq * e->lat_seq * (e->latent_bf16 ? 2 : 4));
+    float *ist = w.idx_state + (batch ? 0 : (size_t)e->cur_seq * e->idx_seq);
+    if (batch) { s.batch = 1; s.lat_seq = e->lat_seq; s.idx_seq = e->idx_seq; }
     if (!w.q_a.loaded() || !w.kv_b.loaded() || !w.mo.loaded() || !w.wq_b.loaded() || !w.ape || !w.latent)
         return fail("this layer's MLA weights were not loaded");
-    if (cached + n > e->cap) return fail("MLA cache position %d beyond capacity %d", cached + n - 1, e->cap);
+    if (cached + (batch ? 1 : n) > e->cap) return fail("MLA cache position %d beyond capacity %d", cached + (batch ? 1 : n) - 1, e->cap);
     GemvSeg a[5] = {make_seg(w.q_a, x, E, e->mq_raw, c.q_lora), make_seg(w.kv_a, x, E, e->mct, c.kv_lora),
                     make_seg(w.wk, x, E, e->mwk, c.index_dim), make_seg(w.igate, x, E, e->mgate, c.index_dim),
                     make_seg(w.wproj, x, E, e->mwp, c.index_heads)};
     gemv_batch(e->st, a, 5, n);
-    mla_store(e->st, w.latent, w.idx_state, e->mct, w.kv_a_norm, e->mwk, e->mgate, w.k_norm_w, w.k_norm_b,
+    mla_store(e->st, lat, ist, e->mct, w.kv_a_norm, e->mwk, e->mgate, w.k_norm_w, w.k_norm_b,
               w.ape, e->mq_raw, e->minvq, n, cached, s);
     // q = q_b(RMSNorm(q_a x)) and the indexer query, the norm applied on the way into the product
     GemvSeg b[2] = {make_seg(w.q_b, e->mq_raw, c.q_lora, e->mq, c.mla_heads * c.qk_nope, e->minvq, w.q_a_norm),
                     make_seg(w.wq_b, e->mq_raw, c.q_lora, e->mqidx, c.index_heads * c.index_dim, e->minvq, w.q_a_norm)};
     gemv_batch(e->st, b, 2, n);
-    dsa_select(e->st, e->msel, e->mnsel, w.idx_state, e->mqidx, e->mwp, e->mscore, n, cached, s);
+    dsa_select(e->st, e->msel, e->mnsel, ist, e->mqidx, e->mwp, e->mscore, n, cached, s);
     mla_absorb(e->st, e->mqa, e->mq, w.kv_b, n, s);
-    mla_attend(e->st, e->mcb, e->mqa, w.latent, e->msel, e->mnsel, e->mdsc, e->mpart, e->mstats, e->mcount, MLA_PART_TOKENS, n, cached, s);
+    mla_attend(e->st, e->mcb, e->mqa, lat, e->msel, e->mnsel, e->mdsc, e->mpart, e->mstats, e->mcount, MLA_PART_TOKENS, n, cached, s);
     mla_vout(e->st, e->macc, e->mcb, w.kv_b, n, s);
     gemv(e->st, w.mo, e->macc, c.mla_heads * c.v_head, out, E, n);
     return 0;
@@ -753,7 +777,7 @@ static void flush_hc_post(g5b_engine *e)
 
 // One decoder layer over n <= CHUNK positions (reference: glm53f_decoder_layer,
 // src/core/glm53f_ops.c:1400-1433).
-static int run_layer(g5b_engine *e, int l, float *h, int n, int cached)
+static int run_layer(g5b_engine *e, int l, float *h, int n, int cached, bool batch = false)
 {
     const g5b_config &c = e->c;
     Layer &w = e->L[l];
@@ -775,7 +799,7 @@ static int run_layer(g5b_engine *e, int l, float *h, int n, int cached)
             rms_apply(e->st, e->xn, e->xc, site ? w.post_norm : w.in_norm, e->inv1, E, E, n);
         }
         int rc;
-        if (site == 0) rc = w.is_mla ? run_mla(e, w, e->xn, n, cached, e->y) : run_kda(e, w, e->xn, n, e->y);
+        if (site == 0) rc = w.is_mla ? run_mla(e, w, e->xn, n, cached, e->y, batch) : run_kda(e, w, e->xn, n, e->y, batch);
         else           rc = w.is_dense ? run_mlp(e, w, e->xn, n, e->y) : run_moe(e, w, e->xn, n, e->y, 1);
         if (rc) return rc;
         // owed: h' = hc_post(h, y). The next site on these positions applies it inside its own launch;
@@ -826,8 +850,10 @@ static int ensure_ids(g5b_engine *e, size_t n)
 // Layers over T positions whose ids are already on the device, then the head for positions
 // [first, T): logits of position t land in e->logits row (t - first) % CHUNK, arg-max in
 // e->am_out[t].
+// batch: the T ids are one new token for each of sequences 0..T-1 (T <= CHUNK), all at position
+// e->cached; logits_host then receives all T rows.
 static int forward_device(g5b_engine *e, const int *ids_dev, int T, bool all_positions, float *logits_host,
-                          int *argmax_host)
+                          int *argmax_host, bool batch = false)
 {
     const g5b_config &c = e->c;
     const int M = c.hc_mult, E = c.hidden;
@@ -839,7 +865,7 @@ static int forward_device(g5b_engine *e, const int *ids_dev, int T, bool all_pos
     for (int l = 0; l < c.n_layers; l++)
         for (int t0 = 0; t0 < T; t0 += CHUNK) {
             const int n = T - t0 < CHUNK ? T - t0 : CHUNK;
-            if (run_layer(e, l, e->h + (size_t)t0 * M * E, n, e->cached + t0)) return -1;
+            if (run_layer(e, l, e->h + (size_t)t0 * M * E, n, batch ? e->cached : e->cached + t0, batch)) return -1;
         }
     flush_hc_post(e);
     const int first = all_positions ? 0 : T - 1;
@@ -849,7 +875,9 @@ static int forward_device(g5b_engine *e, const int *ids_dev, int T, bool all_pos
         rms_factor(e->st, e->xm, E, E, n, c.rms_eps, e->inv_head);
         gemv(e->st, e->lm_head, e->xm, E, e->logits, c.vocab, n, e->inv_head, e->norm);
         argmax_rows(e->st, e->am_out + t0, e->logits, c.vocab, n, e->am_v, e->am_i);
-        if (logits_host && t0 + n == T)
+        if (logits_host && batch)
+            CU(cudaMemcpyAsync(logits_host, e->logits, (size_t)n * c.vocab * 4, cudaMemcpyDeviceToHost, e->st));
+        else if (logits_host && t0 + n == T)
             CU(cudaMemcpyAsync(logits_host, e->logits + (size_t)(n - 1) * c.vocab, (size_t)c.vocab * 4,
                                cudaMemcpyDeviceToHost, e->st));
     }
@@ -903,10 +931,56 @@ extern "C" void g5b_engine_reset(g5b_engine *e)
     cudaSetDevice(e->device);
     const g5b_config &c = e->c;
     const size_t P = (size_t)c.kda_heads * c.kda_head_dim;
+    (void)P;
     for (auto &w : e->L)
-        if (w.kda_state) cudaMemsetAsync(w.kda_state, 0, (P * c.kda_head_dim + 3 * P * (size_t)(c.conv_k - 1)) * 4, e->st);
+        if (w.kda_state) cudaMemsetAsync(w.kda_state, 0, (size_t)e->n_seq * e->kda_seq * 4, e->st);
     cudaStreamSynchronize(e->st);
     e->cached = 0;
+    for (auto &v : e->cached_seq) v = 0;
+}
+
+// Which sequence the single-sequence calls (forward, decode_greedy, layer ops, state access) address.
+extern "C" int g5b_engine_use_sequence(g5b_engine *e, int seq)
+{
+    if (!e || !e->finalized) return fail("use_sequence before finalize");
+    if (seq < 0 || seq >= e->n_seq) return fail("sequence %d of %d", seq, e->n_seq);
+    e->cached_seq[(size_t)e->cur_seq] = e->cached;
+    e->cur_seq = seq;
+    e->cached = e->cached_seq[(size_t)seq];
+    return 0;
+}
+
+// One new token for every sequence at once (lockstep decode): ids[s] continues sequence s; all
+// sequences must hold the same number of positions. logits: [n_seq][vocab] or NULL; argmax:
+// [n_seq] or NULL. Attention state and caches are per sequence, every weight is read once for
+// the whole batch.
+extern "C" int g5b_engine_decode_batch(g5b_engine *e, const int *ids, float *logits, int *argmax)
+{
+    if (!e || !e->finalized) return fail("decode_batch before finalize");
+    CU(cudaSetDevice(e->device));
+    const int S = e->n_seq;
+    e->cached_seq[(size_t)e->cur_seq] = e->cached;
+    for (int q = 1; q < S; q++)
+        if (e->cached_seq[(size_t)q] != e->cached_seq[0])
+            return fail("decode_batch needs sequences of equal length (sequence %d holds %d positions, sequence 0 %d)", q,
+                        e->cached_seq[(size_t)q], e->cached_seq[0]);
+    const int pos = e->cached_seq[0];
+    if (pos + 1 > e->cap) return fail("%d cached + 1 new position exceed the session capacity %d", pos, e->cap);
+    for (int q = 0; q < S; q++)
+        if (ids[q] < 0 || ids[q] >= e->c.vocab) return fail("token id %d outside the vocabulary", ids[q]);
+    if (ensure_ids(e, (size_t)S)) return -1;
+    CU(cudaMemcpyAsync(e->ids_dev, ids, (size_t)S * 4, cudaMemcpyHostToDevice, e->st));
+    const int keep = e->cached;
+    e->cached = pos;
+    const int rc = forward_device(e, e->ids_dev, S, true, logits, argmax, true);
+    e->cached = keep;
+    if (rc) return -1;
+    CU(cudaStreamSynchronize(e->st));
+    CU(cudaGetLastError());
+    if (check_device_error(e)) return -1;
+    for (auto &v : e->cached_seq) v = pos + 1;
+    e->cached = pos + 1;
+    return 0;
 }
 
 extern "C" int g5b_engine_cached(const g5b_engine *e) { return e->cached; }
@@ -1175,12 +1249,16 @@ static float *state_ptr(g5b_engine *e, int layer, int kind, size_t *n, int *bf16
     if (kind == 0) {
         const size_t P = (size_t)c.kda_heads * c.kda_head_dim;
         *n = P * c.kda_head_dim + 3 * P * (size_t)(c.conv_k - 1);
-        return w.kda_state;
+        return w.kda_state ? w.kda_state + (size_t)e->cur_seq * e->kda_seq : nullptr;
     }
-    if (kind == 1) { *n = (size_t)e->cap * c.kv_lora; *bf16 = e->latent_bf16; return (float *)w.latent; }
+    if (kind == 1) {
+        *n = (size_t)e->cap * c.kv_lora; *bf16 = e->latent_bf16;
+        if (!w.latent) return nullptr;
+        return (float *)(static_cast<uint8_t *>(w.latent) + (size_t)e->cur_seq * e->lat_seq * (e->latent_bf16 ? 2 : 4));
+    }
     if (kind == 2) {
         *n = (size_t)2 * e->cap * c.index_dim + (size_t)((e->cap + c.index_kpool - 1) / c.index_kpool) * c.index_dim;
-        return w.idx_state;
+        return w.idx_state ? w.idx_state + (size_t)e->cur_seq * e->idx_seq : nullptr;
     }
     return nullptr;
 }

@@ -24,6 +24,8 @@ struct KdaArgs {
     float *state;
     int T, H, D, K;
     float gate_lb, rms_eps;
+    size_t seq_stride;            // floats between the states of consecutive sequences (grid.y > 1:
+                                  // CTA (h, s) advances sequence s by the T positions at rows s*T ...)
 };
 
 // conv + SiLU of one channel at one position; `past` holds K-1 previous inputs, oldest first.
@@ -48,8 +50,10 @@ __global__ void __launch_bounds__(DS > 0 ? DS : 512) kda_core_kernel(const KdaAr
     const int D = DS > 0 ? DS : a.D, P = a.H * D, K = a.K, hist = K - 1;
     const bool live = d < D;
     const int ch = h * D + (live ? d : 0);
-    float *S = a.state + (size_t)h * D * D;
-    float *cs = a.state + (size_t)a.H * D * D;
+    float *state = a.state + (size_t)blockIdx.y * a.seq_stride;
+    float *S = state + (size_t)h * D * D;
+    float *cs = state + (size_t)a.H * D * D;
+    const int row0 = blockIdx.y * a.T;                       // first activation row of this sequence
 
     float pq[16], pk[16], pv[16], wq[17], wk[17], wv[17];
     for (int j = 0; j < hist; j++) {
@@ -72,7 +76,7 @@ __global__ void __launch_bounds__(DS > 0 ? DS : 512) kda_core_kernel(const KdaAr
     const float qscale = 1.0f / sqrtf((float)D);
 
     for (int t = 0; t < a.T; t++) {
-        const size_t off = (size_t)t * P + ch;
+        const size_t off = (size_t)(row0 + t) * P + ch;
         float qv = 0.f, kv = 0.f, vv = 0.f;
         if (live) {
             qv = conv_step(a.q[off], wq, pq, K);
@@ -84,7 +88,7 @@ __global__ void __launch_bounds__(DS > 0 ? DS : 512) kda_core_kernel(const KdaAr
         const double kk = block_sum(live ? (double)kv * (double)kv : 0.0, red);
         const float qinv = (float)(1.0 / sqrt(qq + (double)1e-6f));
         const float kinv = (float)(1.0 / sqrt(kk + (double)1e-6f));
-        const float beta = sigmoid_host(a.braw[(size_t)t * a.H + h]);
+        const float beta = sigmoid_host(a.braw[(size_t)(row0 + t) * a.H + h]);
         __syncthreads();
         if (live) {
             sq[d] = __fmul_rn(__fmul_rn(qv, qinv), qscale);
@@ -148,13 +152,14 @@ __global__ void __launch_bounds__(DS > 0 ? DS : 512) kda_core_kernel(const KdaAr
 void kda_core(cudaStream_t st, float *o, const float *q, const float *k, const float *v, const float *z,
               const float *braw, const float *gb, const float *q_conv, const float *k_conv,
               const float *v_conv, const float *A_log, const float *dt_bias, const float *o_norm,
-              float *state, int T, const KdaShape &s)
+              float *state, int T, const KdaShape &s, int n_seq, size_t seq_stride)
 {
     KdaArgs a{o, q, k, v, z, braw, gb, q_conv, k_conv, v_conv, A_log, dt_bias, o_norm, state,
-              T, s.H, s.D, s.K, s.gate_lb, s.rms_eps};
-    if (s.D == 128)     G5B_LAUNCH(kda_core_kernel<128>, s.H, 128, 0, st, a);
-    else if (s.D == 64) G5B_LAUNCH(kda_core_kernel<64>, s.H, 64, 0, st, a);
-    else                G5B_LAUNCH(kda_core_kernel<0>, s.H, ((s.D + 31) / 32) * 32, 0, st, a);
+              T, s.H, s.D, s.K, s.gate_lb, s.rms_eps, seq_stride};
+    const dim3 grid(s.H, n_seq < 1 ? 1 : n_seq);
+    if (s.D == 128)     G5B_LAUNCH(kda_core_kernel<128>, grid, 128, 0, st, a);
+    else if (s.D == 64) G5B_LAUNCH(kda_core_kernel<64>, grid, 64, 0, st, a);
+    else                G5B_LAUNCH(kda_core_kernel<0>, grid, ((s.D + 31) / 32) * 32, 0, st, a);
 }
 
 }  // namespace g5b

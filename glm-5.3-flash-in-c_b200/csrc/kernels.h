@@ -179,7 +179,7 @@ struct KdaShape { int H, D, K; float gate_lb, rms_eps; };
 void kda_core(cudaStream_t st, float *o, const float *q, const float *k, const float *v, const float *z,
               const float *braw, const float *gb, const float *q_conv, const float *k_conv,
               const float *v_conv, const float *A_log, const float *dt_bias, const float *o_norm,
-              float *state, int T, const KdaShape &s);
+              float *state, int T, const KdaShape &s, int n_seq = 1, size_t seq_stride = 0);
 
 // ---- mla.cu -------------------------------------------------------------------------------
 struct MlaShape {
@@ -187,6 +187,11 @@ struct MlaShape {
     int ID, IH, KP, topk;              // indexer dim, heads, pool size, index_topk
     float rms_eps;
     int latent_bf16;
+    // batch of sequences: token t of a call belongs to sequence t, all at the same position; the
+    // caches of consecutive sequences lie lat_seq / idx_seq elements apart (0 = one sequence, token
+    // t at position cached + t)
+    int batch = 0;
+    size_t lat_seq = 0, idx_seq = 0;
 };
 // Also writes q_inv[t] = RMSNorm factor of q_raw[t][q_lora] (the q_a output of the same positions).
 void mla_store(cudaStream_t st, void *latent, float *idx_state, const float *ct_raw,

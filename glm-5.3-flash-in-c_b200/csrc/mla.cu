@@ -27,6 +27,19 @@ __device__ __forceinline__ float latent_at(const void *latent, int bf16, size_t 
     return bf16 ? bf16_to_f32(static_cast<const uint16_t *>(latent)[i]) : static_cast<const float *>(latent)[i];
 }
 
+// Batch of sequences (MlaShape::batch): token t works on sequence t's caches, at position `cached`.
+__device__ __forceinline__ int pos_of(const MlaShape &s, int cached, int t) { return s.batch ? cached : cached + t; }
+__device__ __forceinline__ const void *seq_latent(const void *latent, const MlaShape &s, int t)
+{
+    if (!s.batch) return latent;
+    return s.latent_bf16 ? static_cast<const void *>(static_cast<const uint16_t *>(latent) + (size_t)t * s.lat_seq)
+                         : static_cast<const void *>(static_cast<const float *>(latent) + (size_t)t * s.lat_seq);
+}
+__device__ __forceinline__ float *seq_idx(float *idx_state, const MlaShape &s, int t)
+{
+    return s.batch ? idx_state + (size_t)t * s.idx_seq : idx_state;
+}
+
 // ------------------------------------------------------------------- append ----
 // Per new position: latent = RMSNorm(kv_a x) into the cache; indexer key = LayerNorm(wk x)
 // (biased variance, eps 1e-6, FP64) and gate = gate x into the indexer state.
@@ -50,7 +63,9 @@ __global__ void __launch_bounds__(256) mla_store_kernel(
         if (threadIdx.x == 0) q_inv[tq] = (float)(1.0 / sqrt(ssq / (double)s.q_lora + (double)s.rms_eps));
         return;
     }
-    const int t = blockIdx.x, pos = cached + t;
+    const int t = blockIdx.x, pos = pos_of(s, cached, t);
+    latent = const_cast<void *>(seq_latent(latent, s, t));
+    idx_state = seq_idx(idx_state, s, t);
     const float *ct = ct_raw + (size_t)t * s.KL;
     double ss = 0.0;
     for (int i = threadIdx.x; i < s.KL; i += blockDim.x) ss += (double)ct[i] * (double)ct[i];
@@ -111,8 +126,8 @@ void mla_store(cudaStream_t st, void *latent, float *idx_state, const float *ct_
                int T, int cached, const MlaShape &s)
 {
     const int pool0 = cached / s.KP;                                         // pools closed before this call
-    const int pool1 = (cached + T) / s.KP;                                   // pools closed after this call
-    const int pool_here = (T == 1 && pool1 > pool0) ? pool0 : -1;
+    const int pool1 = (cached + (s.batch ? 1 : T)) / s.KP;                   // pools closed after this call
+    const int pool_here = ((T == 1 || s.batch) && pool1 > pool0) ? pool0 : -1;
     G5B_LAUNCH(mla_store_kernel, 2 * T, 256, 0, st, latent, idx_state, ct_raw, kv_norm_w, wk_raw, gate_raw,
                k_norm_w, k_norm_b, cached, s, q_raw, q_inv, T, ape, pool_here);
     if (pool1 > pool0 && pool_here < 0)
@@ -130,7 +145,8 @@ __global__ void __launch_bounds__(DSA_WARPS * 32) dsa_score_kernel(
     extern __shared__ float dsa_smem[];
     float  *qT = dsa_smem;                                   // [ID][IH]
     double *dh = reinterpret_cast<double *>(dsa_smem + (size_t)s.ID * s.IH);   // [warps][IH]
-    const int t = blockIdx.y, p = cached + t;
+    const int t = blockIdx.y, p = pos_of(s, cached, t);
+    idx_state = seq_idx(const_cast<float *>(idx_state), s, t);
     const int np = (p + 1) / s.KP;
     if (np <= s.topk / s.KP) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -179,7 +195,7 @@ __global__ void __launch_bounds__(TOPK_THREADS) dsa_topk_kernel(int *sel, int *n
     __shared__ unsigned long long prefix_s;
     __shared__ int want_s;
     __shared__ int scan[TOPK_THREADS];
-    const int t = blockIdx.x, p = cached + t, tid = threadIdx.x;
+    const int t = blockIdx.x, p = pos_of(s, cached, t), tid = threadIdx.x;
     const int np = (p + 1) / s.KP, keep = s.topk / s.KP;
     int *out = sel + (size_t)t * (s.topk + s.KP);
     if (np <= keep) { if (tid == 0) nsel[t] = -1; return; }
@@ -256,7 +272,7 @@ __global__ void __launch_bounds__(TOPK_THREADS) dsa_topk_kernel(int *sel, int *n
 void dsa_select(cudaStream_t st, int *sel, int *nsel, const float *idx_state, const float *qidx,
                 const float *wproj, float *score, int T, int cached, const MlaShape &s)
 {
-    const int np_max = (cached + T) / s.KP;
+    const int np_max = (cached + (s.batch ? 1 : T)) / s.KP;
     if (np_max > s.topk / s.KP) {
         const size_t smem = (size_t)s.ID * s.IH * sizeof(float) + (size_t)DSA_WARPS * s.IH * sizeof(double);
         int blocks = (np_max + DSA_WARPS - 1) / DSA_WARPS;
@@ -336,7 +352,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) mla_score_kernel(
     int stride, MlaShape s)
 {
     extern __shared__ double qs[];                            // [KL]
-    const int h = blockIdx.y, t = blockIdx.z, p = cached + t;
+    const int h = blockIdx.y, t = blockIdx.z, p = pos_of(s, cached, t);
+    latent = seq_latent(latent, s, t);
     const int ns = nsel ? nsel[t] : -1;
     const int nvis = ns < 0 ? p + 1 : ns;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -367,7 +384,8 @@ __global__ void __launch_bounds__(256) mla_score4_kernel(double *dsc, const doub
 {
     __shared__ double ptop[8], pz[8];
     __shared__ int is_last;
-    const int h0 = blockIdx.y * SC_HEADS, t = blockIdx.z, p = cached + t;
+    const int h0 = blockIdx.y * SC_HEADS, t = blockIdx.z, p = pos_of(s, cached, t);
+    latent = seq_latent(latent, s, t);
     const int ns = nsel ? nsel[t] : -1;
     const int nvis = ns < 0 ? p + 1 : ns;
     const int j0 = blockIdx.x * SC_CHUNK;
@@ -476,7 +494,8 @@ __global__ void __launch_bounds__(512) mla_wsum_kernel(
 {
     __shared__ double red[32];
     __shared__ double zs;
-    const int h = blockIdx.x, t = blockIdx.y, p = cached + t;
+    const int h = blockIdx.x, t = blockIdx.y, p = pos_of(s, cached, t);
+    latent = seq_latent(latent, s, t);
     const int ns = nsel ? nsel[t] : -1;
     const int nvis = ns < 0 ? p + 1 : ns;
     double *d = dsc + ((size_t)t * s.H + h) * stride;
@@ -528,7 +547,7 @@ __global__ void __launch_bounds__(256) mla_softmax_stats_kernel(double *stats, c
                                                                 int cached, int stride, MlaShape s)
 {
     __shared__ double red[32];
-    const int h = blockIdx.x, t = blockIdx.y, p = cached + t;
+    const int h = blockIdx.x, t = blockIdx.y, p = pos_of(s, cached, t);
     const int ns = nsel ? nsel[t] : -1;
     const int nvis = ns < 0 ? p + 1 : ns;
     const double *d = dsc + ((size_t)t * s.H + h) * stride;
@@ -555,7 +574,8 @@ __global__ void __launch_bounds__(WS_THREADS) mla_wsum_chunk_kernel(
 {
     __shared__ double pj[WS_HEADS][WS_CHUNK];
     __shared__ int idx[WS_CHUNK];
-    const int chunk = blockIdx.x, h0 = blockIdx.y * WS_HEADS, t = blockIdx.z, p = cached + t;
+    const int chunk = blockIdx.x, h0 = blockIdx.y * WS_HEADS, t = blockIdx.z, p = pos_of(s, cached, t);
+    latent = seq_latent(latent, s, t);
     const int ns = nsel ? nsel[t] : -1;
     const int nvis = ns < 0 ? p + 1 : ns;
     const int j0 = chunk * WS_CHUNK;
@@ -614,7 +634,8 @@ void mla_attend(cudaStream_t st, float *cb, const double *qa, const void *latent
                 const int *nsel, double *dsc, double *part, double *stats, int *counters, int part_tokens, int T,
                 int cached, const MlaShape &s)
 {
-    const int nvis_max = cached + T < s.topk + s.KP ? cached + T : s.topk + s.KP;
+    const int span = s.batch ? 1 : T;                                      // positions this call adds to a sequence
+    const int nvis_max = cached + span < s.topk + s.KP ? cached + span : s.topk + s.KP;
     const int stride = s.topk + s.KP;
     int blocks = (nvis_max + ATT_WARPS - 1) / ATT_WARPS;
     if (blocks > 32) blocks = 32;
@@ -634,10 +655,16 @@ void mla_attend(cudaStream_t st, float *cb, const double *qa, const void *latent
     if (!fast_score) G5B_LAUNCH(mla_softmax_stats_kernel, dim3(s.H, T), 256, 0, st, stats, dsc, nsel, cached, stride, s);
     for (int t0 = 0; t0 < T; t0 += part_tokens) {
         const int n = T - t0 < part_tokens ? T - t0 : part_tokens;
-        const int used = (((cached + t0 + n < stride) ? cached + t0 + n : stride) + WS_CHUNK - 1) / WS_CHUNK;
+        const int reach = s.batch ? cached + 1 : cached + t0 + n;
+        const void *lat0 = latent;                                 // the kernel's token 0 is sequence t0 of a batch
+        if (s.batch)
+            lat0 = s.latent_bf16 ? static_cast<const void *>(static_cast<const uint16_t *>(latent) + (size_t)t0 * s.lat_seq)
+                                 : static_cast<const void *>(static_cast<const float *>(latent) + (size_t)t0 * s.lat_seq);
+        const int used = (((reach < stride) ? reach : stride) + WS_CHUNK - 1) / WS_CHUNK;
         G5B_LAUNCH(mla_wsum_chunk_kernel, dim3(used, s.H / WS_HEADS, n), WS_THREADS, 0, st, part,
-                   dsc + (size_t)t0 * s.H * stride, stats + (size_t)t0 * s.H * 2, latent,
-                   sel ? sel + (size_t)t0 * stride : nullptr, nsel ? nsel + t0 : nullptr, cached + t0, stride, nchunks, s);
+                   dsc + (size_t)t0 * s.H * stride, stats + (size_t)t0 * s.H * 2, lat0,
+                   sel ? sel + (size_t)t0 * stride : nullptr, nsel ? nsel + t0 : nullptr, s.batch ? cached : cached + t0, stride, nchunks,
+                   s);
         // chunks beyond `used` were not written: reduce over the used ones only
         G5B_LAUNCH(mla_wsum_reduce_kernel, dim3((n * s.H * s.KL + 255) / 256), 256, 0, st,
                    cb + (size_t)t0 * s.H * s.KL, part, nchunks, used, n * s.H * s.KL, s.KL);

@@ -140,6 +140,18 @@ int  g5b_engine_cached(const g5b_engine *e);  /* positions consumed so far */
  * logits to the host and takes the argmax there). out receives n token ids. */
 int g5b_engine_decode_greedy(g5b_engine *e, int first, int n, int *out);
 
+/* Several independent sequences on one engine (no counterpart in the reference, which holds one
+ * session per model, src/model/glm53f_model.h:53-75; the benchmark's batch-64 decode needs it).
+ * Option "sequences" = S (g5b_engine_set_option before finalize, 1..64) gives every layer S copies
+ * of its session state. g5b_engine_use_sequence picks the sequence that forward / decode_greedy /
+ * the layer ops / g5b_state_* address (each sequence keeps its own position count), e.g. to
+ * prefill S prompts one after the other. g5b_engine_decode_batch then advances all S sequences by
+ * one token in a single pass: ids[s] continues sequence s, every weight is read once for the
+ * batch, attention state and caches are per sequence. All sequences must hold the same number of
+ * positions. logits: [S][vocab] or NULL, argmax: [S] or NULL. */
+int g5b_engine_use_sequence(g5b_engine *e, int seq);
+int g5b_engine_decode_batch(g5b_engine *e, const int *ids, float *logits, int *argmax);
+
 /* Expert-parallel wiring for ep_size > 1 (no counterpart in the reference, whose device list is a
  * layer pipeline, src/gpu/glm53f_gpu.c:758-790): after finalize every rank exports a handle to its
  * exchange region (ep_handle_bytes() bytes, a CUDA IPC handle), the caller gathers all handles in
