@@ -270,6 +270,7 @@ def time_decoder_layers(pkg, torch, steps: int, device: int = 0):
     eng = pkg.Engine(c, spec.is_mla, spec.is_dense, cap, device)
     eng.set_option("allow_partial", 1)
     eng.set_option("latent_bf16", 1)
+    eng.set_option("sequences", 64)
     eng.load_all(tensors)
     for layer in range(2):
         for ex in range(c.n_experts):
@@ -286,7 +287,21 @@ def time_decoder_layers(pkg, torch, steps: int, device: int = 0):
             assert L.g5b_time_op(eng.handle, b"layer", layer, hd.data_ptr(), 1, cached, hd.data_ptr(), k, FLUSH_BYTES,
                                  C.byref(tot), each.ctypes.data) == 0, L.g5b_last_error()
         out[name] = {"ms": float(np.mean(each[:steps])), "finite": bool(torch.isfinite(hd).all().item())}
+    # the same two layers advancing 64 sequences by one token each (state and caches per sequence,
+    # weights read once per batch)
+    h64 = torch.from_numpy(rng.standard_normal((64, c.hc_mult, c.hidden)).astype(np.float32)).cuda()
+    for layer, cached, name in ((0, 0, "kda_moe_layer_batch64"), (1, cap - 1, "mla_moe_layer_ctx8192_batch64")):
+        hd = h64.clone()
+        n = max(3, steps // 2)
+        each = np.zeros(max(n, 3), np.float32); tot = C.c_float(0)
+        for k in (2, n):
+            hd.copy_(h64)
+            assert L.g5b_time_op(eng.handle, b"layer_batch", layer, hd.data_ptr(), 64, cached, hd.data_ptr(), k, FLUSH_BYTES,
+                                 C.byref(tot), each.ctypes.data) == 0, L.g5b_last_error()
+        out[name] = {"ms": float(np.mean(each[:n])), "finite": bool(torch.isfinite(hd).all().item())}
     eng.close()
+    b64_ms = 34 * out["kda_moe_layer_batch64"]["ms"] + 11 * out["mla_moe_layer_ctx8192_batch64"]["ms"]
+    out["full_model_batch64_tokens_per_s_extrapolated"] = 64e3 / b64_ms
     kda_bytes = 286048984 + 228907008 + 2 * 786432
     rate = kda_bytes / (out["kda_moe_layer"]["ms"] * 1e-3)
     head_ms = 154880 * 4096 * 2 / rate * 1e3
