@@ -113,6 +113,7 @@ struct g5b_engine {
     float *mq_raw, *mct, *mwk, *mgate, *mwp, *mq, *mqidx, *mcb, *macc, *mscore, *minvq;
     double *mqa, *mdsc, *mpart = nullptr, *mstats = nullptr;
     int *mcount = nullptr;
+    GemmTokens *gemm = nullptr;                          // BF16 projections of 8+ tokens (cuBLAS)
     float *post_h = nullptr; int post_n = 0;             // positions whose hc_post is still owed (run_layer)
     double *hc_part = nullptr; int *hc_count = nullptr;  // fused mHC site: partial sums and per-token counters
     void *xterms = nullptr; float *xinv = nullptr;      // batched expert kernels: F16 terms of the activations
@@ -549,6 +550,13 @@ extern "C" int g5b_engine_finalize(g5b_engine *e)
     if (walloc(e, &e->xm, N * E) || walloc(e, &e->inv_head, N) || walloc(e, &e->logits, N * (size_t)c.vocab) ||
         walloc(e, &e->am_v, N * 64) || walloc(e, &e->am_i, N * 64) || walloc(e, &e->am_out, (size_t)e->cap + N)) return -1;
     CU(cudaStreamSynchronize(e->st));
+    {
+        const int P = c.kda_heads * c.kda_head_dim;
+        int max_c = c.hidden;
+        for (int v : {P, c.q_lora, c.kv_lora, c.kda_head_dim, c.mla_heads * c.v_head}) max_c = v > max_c ? v : max_c;
+        e->gemm = gemm_tokens_create(e->st, CHUNK, max_c);
+        if (!e->gemm) return fail("cuBLAS context or its scratch could not be created");
+    }
     e->cached_seq.assign((size_t)e->n_seq, 0);
     e->finalized = true;
     return 0;
@@ -691,6 +699,29 @@ static int run_mlp(g5b_engine *e, Layer &w, const float *x, int n, float *out)
     return 0;
 }
 
+// Several products sharing (some of) their inputs: BF16 matrices with 8 or more tokens go to the
+// GEMM path, the rest to the GEMV kernel in one launch.
+static int proj_batch(g5b_engine *e, const GemvSeg *segs, int n, int T)
+{
+    if (T < 8 || !e->gemm) { gemv_batch(e->st, segs, n, T); return 0; }
+    gemm_tokens_new_input(e->gemm);
+    GemvSeg rest[GEMV_MAX_SEG];
+    int nr = 0;
+    for (int i = 0; i < n; i++) {
+        if (gemm_tokens_takes(e->gemm, segs[i], T)) {
+            if (gemm_tokens_run(e->gemm, e->st, segs[i], T)) return fail("the cuBLAS GEMM of a projection failed");
+        } else rest[nr++] = segs[i];
+    }
+    if (nr) gemv_batch(e->st, rest, nr, T);
+    return 0;
+}
+static int proj(g5b_engine *e, const DMat &m, const float *x, int ldx, float *y, int ldy, int T,
+                const float *xinv = nullptr, const float *xw = nullptr)
+{
+    GemvSeg s = make_seg(m, x, ldx, y, ldy, xinv, xw);
+    return proj_batch(e, &s, 1, T);
+}
+
 // batch: the n rows are one new position of n different sequences (sequences 0..n-1), otherwise n
 // consecutive positions of the current sequence.
 static int run_kda(g5b_engine *e, Layer &w, const float *x, int n, float *out, bool batch = false)
@@ -702,9 +733,9 @@ static int run_kda(g5b_engine *e, Layer &w, const float *x, int n, float *out, b
     float *lrf = e->klr, *lrg = e->klr + (size_t)CHUNK * D;
     GemvSeg a[6] = {make_seg(w.kq, x, E, e->kq, P), make_seg(w.kk, x, E, e->kk, P), make_seg(w.kv, x, E, e->kv, P),
                     make_seg(w.kb, x, E, e->kbraw, H), make_seg(w.f_a, x, E, lrf, D), make_seg(w.g_a, x, E, lrg, D)};
-    gemv_batch(e->st, a, 6, n);
+    if (proj_batch(e, a, 6, n)) return -1;
     GemvSeg b[2] = {make_seg(w.f_b, lrf, D, e->kz, P), make_seg(w.g_b, lrg, D, e->kgb, P)};
-    gemv_batch(e->st, b, 2, n);
+    if (proj_batch(e, b, 2, n)) return -1;
     KdaShape ks{H, D, c.conv_k, c.gate_lb, c.rms_eps};
     if (batch)
         kda_core(e->st, e->ko, e->kq, e->kk, e->kv, e->kz, e->kbraw, e->kgb, w.q_conv, w.k_conv, w.v_conv,
@@ -712,8 +743,7 @@ static int run_kda(g5b_engine *e, Layer &w, const float *x, int n, float *out, b
     else
         kda_core(e->st, e->ko, e->kq, e->kk, e->kv, e->kz, e->kbraw, e->kgb, w.q_conv, w.k_conv, w.v_conv,
                  w.A_log, w.dt_bias, w.o_norm, w.kda_state + (size_t)e->cur_seq * e->kda_seq, n, ks);
-    gemv(e->st, w.ko, e->ko, P, out, E, n);
-    return 0;
+    return proj(e, w.ko, e->ko, P, out, E, n);
 }
 
 static MlaShape mla_shape(const g5b_engine *e)
@@ -741,13 +771,13 @@ static int run_mla(g5b_engine *e, Layer &w, const float *x, int n, int cached, f
     GemvSeg a[5] = {make_seg(w.q_a, x, E, e->mq_raw, c.q_lora), make_seg(w.kv_a, x, E, e->mct, c.kv_lora),
                     make_seg(w.wk, x, E, e->mwk, c.index_dim), make_seg(w.igate, x, E, e->mgate, c.index_dim),
                     make_seg(w.wproj, x, E, e->mwp, c.index_heads)};
-    gemv_batch(e->st, a, 5, n);
+    if (proj_batch(e, a, 5, n)) return -1;
     mla_store(e->st, lat, ist, e->mct, w.kv_a_norm, e->mwk, e->mgate, w.k_norm_w, w.k_norm_b,
               w.ape, e->mq_raw, e->minvq, n, cached, s);
     // q = q_b(RMSNorm(q_a x)) and the indexer query, the norm applied on the way into the product
     GemvSeg b[2] = {make_seg(w.q_b, e->mq_raw, c.q_lora, e->mq, c.mla_heads * c.qk_nope, e->minvq, w.q_a_norm),
                     make_seg(w.wq_b, e->mq_raw, c.q_lora, e->mqidx, c.index_heads * c.index_dim, e->minvq, w.q_a_norm)};
-    gemv_batch(e->st, b, 2, n);
+    if (proj_batch(e, b, 2, n)) return -1;
     dsa_select(e->st, e->msel, e->mnsel, ist, e->mqidx, e->mwp, e->mscore, n, cached, s);
     mla_absorb(e->st, e->mqa, e->mq, w.kv_b, n, s);
     mla_attend(e->st, e->mcb, e->mqa, lat, e->msel, e->mnsel, e->mdsc, e->mpart, e->mstats, e->mcount, MLA_PART_TOKENS, n, cached, s);
@@ -873,7 +903,7 @@ static int forward_device(g5b_engine *e, const int *ids_dev, int T, bool all_pos
         const int n = T - t0 < CHUNK ? T - t0 : CHUNK;
         head_mean(e->st, e->xm, e->h + (size_t)t0 * M * E, n, M, E);
         rms_factor(e->st, e->xm, E, E, n, c.rms_eps, e->inv_head);
-        gemv(e->st, e->lm_head, e->xm, E, e->logits, c.vocab, n, e->inv_head, e->norm);
+        if (proj(e, e->lm_head, e->xm, E, e->logits, c.vocab, n, e->inv_head, e->norm)) return -1;
         argmax_rows(e->st, e->am_out + t0, e->logits, c.vocab, n, e->am_v, e->am_i);
         if (logits_host && batch)
             CU(cudaMemcpyAsync(logits_host, e->logits, (size_t)n * c.vocab * 4, cudaMemcpyDeviceToHost, e->st));
@@ -990,6 +1020,7 @@ extern "C" void g5b_engine_free(g5b_engine *e)
     if (!e) return;
     cudaSetDevice(e->device);
     cudaStreamSynchronize(e->st);
+    gemm_tokens_free(e->gemm);
     for (void *p : e->owned) cudaFree(p);
     for (void *p : e->ep_opened) cudaIpcCloseMemHandle(p);
     for (void *p : e->ep_standins) cudaFree(p);
