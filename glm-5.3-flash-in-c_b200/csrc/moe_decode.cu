@@ -244,7 +244,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
                 if (!ok) break;
                 have_plan = true;
             }
-            if (!s_local[slot]) continue;             // another rank's expert
+            if (a.ep_size > 1 && !s_local[slot]) continue;             // another rank's expert
             const ExpertW ew = s_ew[slot];
             for (int kh = 0; kh < a.E / MM_CB && ok; kh++, it++) {
                 const int s = it % MM_NS;
@@ -271,10 +271,10 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
         int pending = 0, pend_stage[MM_NS], pend_slot[MM_NS];
         int last_g = -1;                               // this CTA's last down item on this rank
         for (int g = blockIdx.x; g < n_dn; g += gridDim.x)
-            if (s_local[g / tps_d]) last_g = g;
+            if (a.ep_size == 1 || s_local[g / tps_d]) last_g = g;
         for (int g = blockIdx.x; g < n_dn && ok; g += gridDim.x) {
             const int slot = g / tps_d, rt = g % tps_d;
-            if (!s_local[slot]) continue;
+            if (a.ep_size > 1 && !s_local[slot]) continue;
             const ExpertW ew = s_ew[slot];
             const int s = it % MM_NS;
             if (it >= MM_NS) ok = mbar_wait(&empty[s], ((it / MM_NS) - 1) & 1, a.err, 1);
@@ -424,12 +424,12 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
         for (int g = blockIdx.x; g < n_gu && ok; g += gridDim.x) {
             int slot, rt;
             gu_slot(g, slot, rt);
-            if (slot != a.K && !have_sel) {            // which of the picks are this rank's
+            if (a.ep_size > 1 && slot != a.K && !have_sel) {   // which of the picks are this rank's
                 ok = mbar_wait_warp(sel_ready, 0, a.err, 10);
                 if (!ok) break;
                 have_sel = true;
             }
-            if (!s_local[slot]) continue;
+            if (a.ep_size > 1 && !s_local[slot]) continue;
             float accf[4] = {0.f, 0.f, 0.f, 0.f};
             for (int kh = 0; kh < a.E / MM_CB && ok; kh++, it++) {
                 const int s = it % MM_NS;
@@ -478,10 +478,10 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
         bool first_down = true;
 
         // ---- down items (the stage's full barrier covers the activation terms too)
-        if (ok && !have_sel) { ok = mbar_wait_warp(sel_ready, 0, a.err, 10); have_sel = ok; }
+        if (ok && a.ep_size > 1 && !have_sel) { ok = mbar_wait_warp(sel_ready, 0, a.err, 10); have_sel = ok; }
         for (int g = blockIdx.x; g < n_dn && ok; g += gridDim.x) {
             const int slot = g / tps_d, rt = g % tps_d;
-            if (!s_local[slot]) continue;
+            if (a.ep_size > 1 && !s_local[slot]) continue;
             const int s = it % MM_NS;
             ok = mbar_wait_warp(&full[s], (it / MM_NS) & 1, a.err, 2);
             ok = __all_sync(0xffffffffu, ok);
