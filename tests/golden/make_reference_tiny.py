@@ -9,7 +9,7 @@ so it pins both the CPU oracle and the GPU engine to something that neither of t
 Writes reference_tiny.npz (every tensor by engine name, raw storage: uint8 codes, uint16 BF16
 bits, float32) and reference_tiny.json (config + the golden vectors).
 
-    python tests/golden/make_reference_tiny.py [/root/reference]
+    python tests/golden/make_reference_tiny.py [path of the reference tree]
 """
 import json
 import os
