@@ -260,4 +260,27 @@ void flush_l2(cudaStream_t st, void *buf, size_t bytes)
     G5B_LAUNCH(flush_read_kernel, 1184, 256, 0, st, p + half16, half16 - 1, reinterpret_cast<uint32_t *>(p + 2 * half16 - 1));
 }
 
+// ---------------------------------------------------------------- L2 prefetch ----
+// Ask the memory system to bring [p, p + bytes) into L2 (no data reaches the SM, nothing waits):
+// one bulk prefetch per 32 KB piece. Launched on a side stream while a latency-bound kernel runs,
+// so that the weights of the product that follows it are already in L2.
+__global__ void l2_prefetch_kernel(const uint8_t *p, size_t bytes)
+{
+    constexpr size_t PIECE = 32768;
+    const size_t pieces = (bytes + PIECE - 1) / PIECE;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < pieces; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t off = i * PIECE;
+        const unsigned n = (unsigned)(((bytes - off < PIECE ? bytes - off : PIECE)) & ~(size_t)15);
+        if (n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p + off), "r"(n) : "memory");
+    }
+}
+
+void l2_prefetch(cudaStream_t st, const void *p, size_t bytes)
+{
+    if (!p || bytes < 16 || (reinterpret_cast<uintptr_t>(p) & 15)) return;
+    const size_t pieces = (bytes + 32767) / 32768;
+    const int blocks = (int)((pieces + 127) / 128);
+    G5B_LAUNCH(l2_prefetch_kernel, blocks < 1 ? 1 : blocks, 128, 0, st, static_cast<const uint8_t *>(p), bytes);
+}
+
 }  // namespace g5b

@@ -99,6 +99,8 @@ struct g5b_engine {
     int *counter = nullptr, *tile_done = nullptr, *err_dev = nullptr;
     volatile int *err_host = nullptr;   // mapped host memory: kernels record a timed-out wait here
     cudaStream_t st = nullptr;
+    cudaStream_t side = nullptr;                         // L2 prefetches that run beside latency-bound kernels
+    cudaEvent_t side_ev = nullptr;
     std::vector<Layer> L;
     std::vector<std::unordered_map<std::string, Target>> names;   // per layer
     DMat embed, lm_head;
@@ -251,6 +253,8 @@ extern "C" g5b_engine *g5b_engine_create(const g5b_config *cfg, const uint8_t *i
     e->ep_rank = ep_rank; e->ep_size = ep_size;
     e->n_local = c.n_experts / ep_size;
     e->n_local0 = ep_rank * e->n_local;
+    cudaStreamCreateWithFlags(&e->side, cudaStreamNonBlocking);
+    cudaEventCreateWithFlags(&e->side_ev, cudaEventDisableTiming);
     if (cudaStreamCreateWithFlags(&e->st, cudaStreamNonBlocking) != cudaSuccess) {
         fail("cannot create a stream"); delete e; return nullptr;
     }
@@ -699,6 +703,17 @@ static int run_mlp(g5b_engine *e, Layer &w, const float *x, int n, float *out)
     return 0;
 }
 
+// From this point of the main stream on, fetch a matrix into L2 on the side stream: the kernels
+// launched next on the main stream (latency-bound, few CTAs) run while the weights of the product
+// after them arrive. Only worth it when the matrix fits L2 and is read once (one token).
+static void prefetch_beside(g5b_engine *e, const DMat &m)
+{
+    if (!e->side || !e->side_ev || !m.loaded() || m.bytes() > ((size_t)96 << 20)) return;
+    if (cudaEventRecord(e->side_ev, e->st) != cudaSuccess) return;
+    if (cudaStreamWaitEvent(e->side, e->side_ev, 0) != cudaSuccess) return;
+    l2_prefetch(e->side, m.w, m.bytes());
+}
+
 // Several products sharing (some of) their inputs: BF16 matrices with 8 or more tokens go to the
 // GEMM path, the rest to the GEMV kernel in one launch.
 static int proj_batch(g5b_engine *e, const GemvSeg *segs, int n, int T)
@@ -737,6 +752,7 @@ static int run_kda(g5b_engine *e, Layer &w, const float *x, int n, float *out, b
     GemvSeg b[2] = {make_seg(w.f_b, lrf, D, e->kz, P), make_seg(w.g_b, lrg, D, e->kgb, P)};
     if (proj_batch(e, b, 2, n)) return -1;
     KdaShape ks{H, D, c.conv_k, c.gate_lb, c.rms_eps};
+    if (n == 1) prefetch_beside(e, w.ko);               // the recurrence below leaves half the SMs and all of HBM idle
     if (batch)
         kda_core(e->st, e->ko, e->kq, e->kk, e->kv, e->kz, e->kbraw, e->kgb, w.q_conv, w.k_conv, w.v_conv,
                  w.A_log, w.dt_bias, w.o_norm, w.kda_state, 1, ks, n, e->kda_seq);
@@ -1030,6 +1046,8 @@ extern "C" void g5b_engine_free(g5b_engine *e)
     if (e->flush_buf) cudaFree(e->flush_buf);
     if (e->err_host) cudaFreeHost((void *)e->err_host);
     for (int i = 0; i <= PROF_SLOTS; i++) cudaEventDestroy(e->prof_ev[i]);
+    if (e->side) { cudaStreamSynchronize(e->side); cudaStreamDestroy(e->side); }
+    if (e->side_ev) cudaEventDestroy(e->side_ev);
     cudaStreamDestroy(e->st);
     delete e;
 }

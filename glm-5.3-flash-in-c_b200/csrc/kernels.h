@@ -73,6 +73,8 @@ void fill_codes(cudaStream_t st, uint8_t *dst, uint64_t seed, int layer, int exp
 void f32_to_bf16(cudaStream_t st, uint16_t *dst, const float *src, size_t n);
 void bf16_to_f32(cudaStream_t st, float *dst, const uint16_t *src, size_t n);
 void flush_l2(cudaStream_t st, void *buf, size_t bytes);
+// Hint: bring [p, p + bytes) into L2 (16-byte aligned p; nothing waits for it).
+void l2_prefetch(cudaStream_t st, const void *p, size_t bytes);
 
 // ---- mhc.cu -------------------------------------------------------------------------------
 struct HcW {
