@@ -312,9 +312,9 @@ __global__ void mla_absorb_kernel(double *qa, const float *q, const DMat kv_b, M
     }
 }
 
-// The same sums with the GPU filled: a CTA takes 128 latent columns of one head, its four row
-// groups (64 rows each at qk_nope = 256) accumulate in FP64 and are added in ascending order.
-constexpr int AB_COLS = 128, AB_GROUPS = 4;
+// The same sums with the GPU filled: a CTA takes 128 latent columns of one head, its eight row
+// groups (32 rows each at qk_nope = 256) accumulate in FP64 and are added in ascending order.
+constexpr int AB_COLS = 128, AB_GROUPS = 8;
 __global__ void __launch_bounds__(AB_COLS * AB_GROUPS) mla_absorb_split_kernel(double *qa, const float *q, const DMat kv_b,
                                                                               MlaShape s)
 {
@@ -404,7 +404,7 @@ __global__ void __launch_bounds__(256) mla_score4_kernel(double *dsc, const doub
     const int *sl = sel ? sel + (size_t)t * (s.topk + s.KP) : nullptr;
     const int jend = min(j0 + SC_CHUNK, nvis);
     // this warp's positions are j0 + warp + 8k; their cache rows are looked up first (lane k holds
-    // row k), and two positions' latent rows are in flight at a time
+    // row k), and four positions' latent rows are in flight at a time
     int myrow = 0;
     {
         const int jj = j0 + warp + 8 * lane;
@@ -442,15 +442,20 @@ __global__ void __launch_bounds__(256) mla_score4_kernel(double *dsc, const doub
             dsc[((size_t)t * s.H + h0 + hh) * stride + jj] = v * scale;
         }
     };
-    for (int k = 0; k < SC_CHUNK / 8; k += 2) {
-        const int jj0 = j0 + warp + 8 * k, jj1 = jj0 + 8;
+    for (int k = 0; k < SC_CHUNK / 8; k += 4) {                  // four latent rows in flight per warp
+        const int jj0 = j0 + warp + 8 * k, jj1 = jj0 + 8, jj2 = jj0 + 16, jj3 = jj0 + 24;
         if (jj0 >= jend) break;
         const int row0 = __shfl_sync(0xffffffffu, myrow, k), row1 = __shfl_sync(0xffffffffu, myrow, k + 1);
-        float c0[16], c1[16];
+        const int row2 = __shfl_sync(0xffffffffu, myrow, k + 2), row3 = __shfl_sync(0xffffffffu, myrow, k + 3);
+        float c0[16], c1[16], c2[16], c3[16];
         load_row(c0, row0);
         if (jj1 < jend) load_row(c1, row1);
+        if (jj2 < jend) load_row(c2, row2);
+        if (jj3 < jend) load_row(c3, row3);
         finish(c0, jj0);
         if (jj1 < jend) finish(c1, jj1);
+        if (jj2 < jend) finish(c2, jj2);
+        if (jj3 < jend) finish(c3, jj3);
     }
     // ---- statistics by the last chunk of this (token, head group)
     __threadfence();
