@@ -155,11 +155,17 @@ __global__ void __launch_bounds__(DSA_WARPS * 32) dsa_score_kernel(
     __syncthreads();
     const float hscale = 1.0f / sqrtf((float)s.IH), dscale = 1.0f / sqrtf((float)s.ID);
     double *mine = dh + (size_t)warp * s.IH;
+    float *pks = reinterpret_cast<float *>(dh + (size_t)DSA_WARPS * s.IH) + (size_t)warp * s.ID;   // this warp's pooled key
     for (int pp = blockIdx.x * DSA_WARPS + warp; pp < np; pp += gridDim.x * DSA_WARPS) {
         const float *pk = idx_state + ((size_t)2 * s.cap + pp) * s.ID;
+        // the key goes to shared memory in one coalesced load: read from global inside the dot
+        // product, every one of its ID dependent steps waited for a load
+        for (int i = lane; i < s.ID; i += 32) pks[i] = pk[i];
+        __syncwarp();
         for (int h = lane; h < s.IH; h += 32) {
             double d = 0.0;
-            for (int i = 0; i < s.ID; i++) d = fma((double)qT[i * s.IH + h], (double)pk[i], d);
+#pragma unroll 8
+            for (int i = 0; i < s.ID; i++) d = fma((double)qT[i * s.IH + h], (double)pks[i], d);
             mine[h] = __dmul_rn(d, (double)dscale);
         }
         __syncwarp();
@@ -274,7 +280,8 @@ void dsa_select(cudaStream_t st, int *sel, int *nsel, const float *idx_state, co
 {
     const int np_max = (cached + (s.batch ? 1 : T)) / s.KP;
     if (np_max > s.topk / s.KP) {
-        const size_t smem = (size_t)s.ID * s.IH * sizeof(float) + (size_t)DSA_WARPS * s.IH * sizeof(double);
+        const size_t smem = (size_t)s.ID * s.IH * sizeof(float) + (size_t)DSA_WARPS * s.IH * sizeof(double) +
+                            (size_t)DSA_WARPS * s.ID * sizeof(float);
         int blocks = (np_max + DSA_WARPS - 1) / DSA_WARPS;
         if (blocks > 296) blocks = 296;
         G5B_LAUNCH(dsa_score_kernel, dim3(blocks, T), DSA_WARPS * 32, smem, st, score, idx_state, qidx, wproj, cached, s);
