@@ -186,23 +186,20 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
             DT_MARK_P(12);
 #endif
             // K rounds of arg-max: the largest key of the warp, then the lowest expert holding it
-            // (only the first `per` of a lane's slots can hold an expert)
-            const int per = (a.NE + 31) >> 5;
             for (int j = 0; j < a.K; j++) {
                 uint32_t m = 0u;
 #pragma unroll
-                for (int i = 0; i < DEC_PER; i++) if (i < per) m = max(m, key[i]);
+                for (int i = 0; i < DEC_PER; i++) m = max(m, key[i]);
                 m = __reduce_max_sync(0xffffffffu, m);
                 uint32_t cand = 0xffffffffu;
 #pragma unroll
-                for (int i = 0; i < DEC_PER; i++)
-                    if (i < per) cand = min(cand, key[i] == m ? (uint32_t)(lane + 32 * i) : 0xffffffffu);
+                for (int i = 0; i < DEC_PER; i++) cand = min(cand, key[i] == m ? (uint32_t)(lane + 32 * i) : 0xffffffffu);
                 uint32_t bi = __reduce_min_sync(0xffffffffu, cand);
                 if (m == 0u) bi = 0u;                                  // nothing selectable is left
                 float wsel = 0.f;
 #pragma unroll
                 for (int i = 0; i < DEC_PER; i++)
-                    if (i < per && bi == (uint32_t)(lane + 32 * i)) { wsel = sc[i]; key[i] = 0u; }
+                    if (bi == (uint32_t)(lane + 32 * i)) { wsel = sc[i]; key[i] = 0u; }
                 wsel = __shfl_sync(0xffffffffu, wsel, bi & 31);
                 if (lane == j) { my_pick = (int)bi; my_w = wsel; }
             }
