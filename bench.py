@@ -328,6 +328,9 @@ def main():
                     help="N > 1: skip the expert-parallel timing of the layer reported under 'extra'")
     ap.add_argument("--only-attention-layers", action="store_true",
                     help="run only the KDA / MLA single-layer timings and print them (a small case for ncu)")
+    ap.add_argument("--no-decoder-layers", action="store_true",
+                    help="with --only-attention-layers: skip the two whole decoder layers (15 GB of experts), "
+                         "which keeps an ncu capture of the KDA / MLA kernels small")
     ap.add_argument("--no-attention-layers", action="store_true",
                     help="skip the KDA / MLA single-layer timings reported under 'extra'")
     ap.add_argument("--stream-warps", type=int, default=0, help="consumer warps of the streamed CUDA-core kernels (8/16)")
@@ -356,8 +359,10 @@ def main():
     warmup = max(3, args.warmup)
     if args.only_attention_layers:
         peak, _ = measured_peaks()
-        print(json.dumps({"config3": time_attention_layers(pkg, torch, max(3, args.steps), peak, local),
-                          "decoder_layers": time_decoder_layers(pkg, torch, max(3, args.steps), local)}), flush=True)
+        res = {"config3": time_attention_layers(pkg, torch, max(3, args.steps), peak, local)}
+        if not args.no_decoder_layers:
+            res["decoder_layers"] = time_decoder_layers(pkg, torch, max(3, args.steps), local)
+        print(json.dumps(res), flush=True)
         return
     opts = {}
     if args.stream_warps:
