@@ -387,7 +387,7 @@ constexpr int SC_HEADS = 4, SC_CHUNK = 64;
 // src/core/glm53f_ops.c:890-903), which saves the launch that did only that.
 __global__ void __launch_bounds__(256) mla_score4_kernel(double *dsc, const double *qa, const void *latent, const int *sel,
                                                          const int *nsel, int cached, int stride, MlaShape s,
-                                                         double *stats, int *counters)
+                                                         double *stats, int *counters, int chunk)
 {
     __shared__ double ptop[8], pz[8];
     __shared__ int is_last;
@@ -395,7 +395,7 @@ __global__ void __launch_bounds__(256) mla_score4_kernel(double *dsc, const doub
     latent = seq_latent(latent, s, t);
     const int ns = nsel ? nsel[t] : -1;
     const int nvis = ns < 0 ? p + 1 : ns;
-    const int j0 = blockIdx.x * SC_CHUNK;
+    const int j0 = blockIdx.x * chunk;                         // chunk = 64 or 256 positions (<= 32 per warp)
     if (j0 >= nvis) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     double q[SC_HEADS][16];
@@ -409,13 +409,13 @@ __global__ void __launch_bounds__(256) mla_score4_kernel(double *dsc, const doub
         }
     const double scale = (double)(1.0f / sqrtf((float)s.qn));
     const int *sl = sel ? sel + (size_t)t * (s.topk + s.KP) : nullptr;
-    const int jend = min(j0 + SC_CHUNK, nvis);
+    const int jend = min(j0 + chunk, nvis);
     // this warp's positions are j0 + warp + 8k; their cache rows are looked up first (lane k holds
     // row k), and four positions' latent rows are in flight at a time
     int myrow = 0;
     {
         const int jj = j0 + warp + 8 * lane;
-        if (lane < SC_CHUNK / 8 && jj < jend) myrow = ns < 0 ? jj : sl[jj];
+        if (lane < chunk / 8 && jj < jend) myrow = ns < 0 ? jj : sl[jj];
     }
     auto load_row = [&](float (&c)[16], int j) {
         if (s.latent_bf16) {
@@ -449,7 +449,7 @@ __global__ void __launch_bounds__(256) mla_score4_kernel(double *dsc, const doub
             dsc[((size_t)t * s.H + h0 + hh) * stride + jj] = v * scale;
         }
     };
-    for (int k = 0; k < SC_CHUNK / 8; k += 4) {                  // four latent rows in flight per warp
+    for (int k = 0; k < chunk / 8; k += 4) {                     // four latent rows in flight per warp
         const int jj0 = j0 + warp + 8 * k, jj1 = jj0 + 8, jj2 = jj0 + 16, jj3 = jj0 + 24;
         if (jj0 >= jend) break;
         const int row0 = __shfl_sync(0xffffffffu, myrow, k), row1 = __shfl_sync(0xffffffffu, myrow, k + 1);
@@ -469,7 +469,7 @@ __global__ void __launch_bounds__(256) mla_score4_kernel(double *dsc, const doub
     __syncthreads();
     if (threadIdx.x == 0) {
         int *cnt = counters + (size_t)t * gridDim.y + blockIdx.y;
-        const int active = (nvis + SC_CHUNK - 1) / SC_CHUNK;
+        const int active = (nvis + chunk - 1) / chunk;
         const int prev = atomicAdd(cnt, 1);
         is_last = prev == active - 1;
         if (is_last) *cnt = 0;
@@ -652,9 +652,13 @@ void mla_attend(cudaStream_t st, float *cb, const double *qa, const void *latent
     int blocks = (nvis_max + ATT_WARPS - 1) / ATT_WARPS;
     if (blocks > 32) blocks = 32;
     const bool fast_score = s.KL == 512 && s.H % SC_HEADS == 0 && stats && counters;
-    if (fast_score)
-        G5B_LAUNCH(mla_score4_kernel, dim3((nvis_max + SC_CHUNK - 1) / SC_CHUNK, s.H / SC_HEADS, T), 256, 0, st, dsc, qa,
-                   latent, sel, nsel, cached, stride, s, stats, counters);
+    if (fast_score) {
+        // many tokens: fewer, longer CTAs, so that loading the four absorbed queries (16 KB) is a small
+        // part of a CTA's work; one token: many short CTAs, for the latency
+        const int chunk = T >= 8 ? 4 * SC_CHUNK : SC_CHUNK;
+        G5B_LAUNCH(mla_score4_kernel, dim3((nvis_max + chunk - 1) / chunk, s.H / SC_HEADS, T), 256, 0, st, dsc, qa,
+                   latent, sel, nsel, cached, stride, s, stats, counters, chunk);
+    }
     else
         G5B_LAUNCH(mla_score_kernel, dim3(blocks, s.H, T), ATT_WARPS * 32, (size_t)s.KL * sizeof(double), st, dsc, qa,
                    latent, sel, nsel, cached, stride, s);
