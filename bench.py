@@ -313,6 +313,54 @@ def time_decoder_layers(pkg, torch, steps: int, device: int = 0):
     return out
 
 
+def time_expert_parallel(pkg, torch, dist, synth, rep, args, local, rank, world, warmup):
+    """N > 1: the same layer expert-parallel (288 / N routed experts per rank, activations and the
+    shared expert replicated, contribution rows exchanged over peer mappings inside the decode
+    kernel): one token stream served by all ranks together, i.e. the latency side of the N-GPU
+    trade-off. Returns the entry for `extra`. Every rank takes part in every collective here
+    whatever happens on it, and the ranks agree on each stage's outcome before the next."""
+    def all_ok(flag: bool) -> bool:
+        t = torch.tensor([1.0 if flag else 0.0], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return bool(t.item() > 0.5)
+
+    ep, err, handle = None, "", b""
+    try:
+        spec_ep = synth.layer_spec("moe", n_experts=args.experts)
+        trunk_ep = synth.moe_layer_trunk(spec_ep, SEED)
+        ep = pkg.Engine(spec_ep.cfg, spec_ep.is_mla, spec_ep.is_dense, 8, local, rank, world)
+        ep.set_option("allow_partial", 1)
+        ep.load_all(trunk_ep)
+        for ex in range(args.experts):
+            ep.fill_expert(0, ex, SEED, *synth.expert_scales(spec_ep.cfg, 0, ex, SEED))
+        ep.finalize()
+        handle = ep.ep_export()
+    except Exception as exc:                                   # noqa: BLE001
+        err = repr(exc)[:300]
+    handles = [None] * world
+    dist.all_gather_object(handles, handle)
+    if not err:
+        try:
+            ep.ep_connect(handles)
+        except Exception as exc:                               # noqa: BLE001
+            err = repr(exc)[:300]
+    ep_ms = 0.0
+    if all_ok(not err):
+        try:
+            ep_each, _, _, _ = time_batch(pkg, ep, torch, 1, args.steps, warmup, phases=False)
+            ep_ms = float(ep_each.mean())
+        except Exception as exc:                               # noqa: BLE001
+            err = repr(exc)[:300]
+    ok = all_ok(not err)
+    ep_ms = rep.max_over_ranks(ep_ms, dist, "cuda")
+    if ep is not None:
+        ep.close()
+    if not ok or ep_ms <= 0:
+        return {"ranks": world, "error": err or "another rank failed"}
+    return {"ranks": world, "ms_per_step": ep_ms, "tokens_per_s": 1e3 / ep_ms,
+            "routed_experts_per_rank": args.experts // world}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -458,24 +506,12 @@ def main():
     # shared expert replicated, contribution rows exchanged over peer mappings): one token stream
     # served by all ranks together, i.e. the latency side of the N-GPU trade-off
     if world > 1 and 288 % world == 0 and not args.no_expert_parallel:
-        spec_ep = synth.layer_spec("moe", n_experts=args.experts)
-        trunk_ep = synth.moe_layer_trunk(spec_ep, SEED)
-        ep = pkg.Engine(spec_ep.cfg, spec_ep.is_mla, spec_ep.is_dense, 8, local, rank, world)
-        ep.set_option("allow_partial", 1)
-        ep.load_all(trunk_ep)
-        for ex in range(args.experts):
-            ep.fill_expert(0, ex, SEED, *synth.expert_scales(spec_ep.cfg, 0, ex, SEED))
-        ep.finalize()
-        handles = [None] * world
-        dist.all_gather_object(handles, ep.ep_export())
-        ep.ep_connect(handles)
-        barrier()
-        ep_each, _, _, _ = time_batch(pkg, ep, torch, 1, args.steps, warmup, phases=False)
-        barrier()
-        ep_ms = rep.max_over_ranks(float(ep_each.mean()), dist, "cuda")
-        ep.close()
-        extra["expert_parallel_b1"] = {"ranks": world, "ms_per_step": ep_ms, "tokens_per_s": 1e3 / ep_ms,
-                                       "routed_experts_per_rank": args.experts // world}
+        # the headline above does not depend on this extra: a failure here is reported, not fatal
+        try:
+            extra["expert_parallel_b1"] = time_expert_parallel(pkg, torch, dist, synth, rep, args, local, rank, world,
+                                                               warmup)
+        except Exception as exc:                               # noqa: BLE001
+            extra["expert_parallel_b1"] = {"ranks": world, "error": repr(exc)[:300]}
 
     cpu = None
     if rank == 0 and not args.no_cpu_baseline and args.experts == 288:
