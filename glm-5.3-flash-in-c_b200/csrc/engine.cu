@@ -1443,7 +1443,7 @@ extern "C" int g5b_shortconv_host(float *y, const float *x, const float *w, floa
 }
 
 // ------------------------------------------------------------------------ timing ----
-// Time `iters` launches of one op ("moe", "kda", "mla", "layer", "layer_batch") between CUDA events on the
+// Time `iters` launches of one op ("moe", "kda", "mla", "layer", "layer_batch", "hc_site", "hc_site_post") between CUDA events on the
 // engine's stream; before each launch `flush_bytes` of scratch are overwritten (0 = no flush) so
 // that weights come from HBM, not from L2. ms_each receives the per-launch times. When the
 // engine's "profile" option is on, the per-phase times of the MoE op accumulate in the profile.
@@ -1479,6 +1479,17 @@ extern "C" int g5b_time_op(g5b_engine *e, const char *op, int layer, const float
                 rc = run_layer(e, layer, out_dev, T, cached, true);
                 if (rc) e->post_h = nullptr;
                 flush_hc_post(e);
+            }
+        }
+        else if (!strcmp(op, "hc_site") || !strcmp(op, "hc_site_post")) {
+            // one mHC site of the layer on its own: gates, Sinkhorn, collapse and the sub-block's
+            // RMSNorm, without / with the previous sub-block's stream expansion riding along
+            const HcW &hw = e->L[layer].hc[0];
+            if (!hw.fn.loaded() || !hc_pre_fused_supported(hw, e->c.hc_mult, e->c.hidden)) rc = fail("no fused mHC site for this layer");
+            else {
+                hc_pre_fused(e->st, e->xn, e->post, e->comb, out_dev, op[7] ? e->y : nullptr, hw, e->L[layer].in_norm,
+                             e->hc_part, e->hc_count, T, e->c.hc_mult, e->c.hidden, e->c.hc_iters, e->c.hc_eps, e->c.rms_eps);
+                rc = 0;
             }
         }
         else rc = fail("unknown op %s", op);

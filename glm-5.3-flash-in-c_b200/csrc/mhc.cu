@@ -5,6 +5,7 @@
 // thread per token ran the whole Sinkhorn normalisation and two more launches collapsed and
 // expanded the streams. Here one launch per site does gates, Sinkhorn and the collapse: warp 0
 // normalises the mixer while the other warps collapse the streams, which only need `pre`.
+#include "acc2.cuh"
 #include "common.cuh"
 #include "kernels.h"
 
@@ -305,9 +306,272 @@ __global__ void __launch_bounds__(HC_THREADS) hc_pre_fused_kernel(const HcFused 
     for (int d = tid; d < E; d += HC_THREADS) a.xn[(size_t)t * E + d] = __fmul_rn(a.norm_w[d], __fmul_rn(xs[d], f));
 }
 
+// ---- the same site as one thread-block cluster per token.
+// The kernel above hands a token to whichever CTA finishes last: a fence, an atomic, a reload of
+// 32 x 25 partial sums and then ONE CTA walking the whole token for the collapse and the norm
+// (about 21 us per site, two sites per layer: a quarter of a batch-1 decoder layer). Here the
+// HCC_CTAS CTAs of a cluster each keep their columns of the streams in shared memory from the
+// first load to the last store; the partial sums (mixer dots, then the collapsed vector's sum of
+// squares) are exchanged through distributed shared memory at two cluster barriers, every CTA
+// derives the gates for itself and collapses and normalises its own columns. The Sinkhorn chain
+// (39 dependent normalisations, needed only for the NEXT stream expansion) runs in warp 0 of CTA 0
+// beside all that: warp 0 arrives at the second barrier before it starts and waits after.
+constexpr int HCC_CTAS = 8, HCC_THREADS = 512, HCC_WARPS = HCC_THREADS / 32, HCC_MAX_W = 1024, HCC_MAX_HS = 4096;
+constexpr int HCC_ROWS = 3, HCC_PIECES = 4, HCC_ROW_WARPS = 8, HCC_SPLITS = HCC_WARPS / HCC_ROW_WARPS;
+
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+__device__ __forceinline__ uint32_t cluster_cta_rank()
+{
+    uint32_t r;
+    asm("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// the shared variable `p` of CTA `rank` of this cluster
+__device__ __forceinline__ double ld_cluster_f64(const double *p, uint32_t rank)
+{
+    const uint32_t mine = (uint32_t)__cvta_generic_to_shared(p);
+    uint32_t theirs;
+    double v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(theirs) : "r"(mine), "r"(rank));
+    asm volatile("ld.shared::cluster.f64 %0, [%1];" : "=d"(v) : "r"(theirs) : "memory");
+    return v;
+}
+
+// v / d for d > 0 to a relative 2^-40: the hardware's reciprocal estimate r (20 bits), its error
+// e = 1 - d r, and v r (1 + e). An FP64 instruction occupies its pipe for 32 cycles per warp here
+// and a Sinkhorn pass is a chain of nothing else, so every instruction less is 0.6 us per site; the
+// mixer is rounded to float (2^-24) after the last pass.
+__device__ __forceinline__ double div_chain(double v, double d)
+{
+    double r;
+    asm("rcp.approx.ftz.f64 %0, %1;" : "=d"(r) : "d"(d));
+    const double q = v * r;
+    return fma(q, fma(-d, r, 1.0), q);
+}
+
+// The 2 iters - 1 alternating column / row normalisations v <- v / (sum + eps) of the mixer
+// (src/core/glm53f_ops.c:583-598) for the lane that holds element (i, j); all 32 lanes call it. One
+// warp runs this chain while the rest of the cluster waits for nothing else, so the M = 4 case is
+// written without a loop or a branch inside a pass: four shuffles, the members' sum as a two-level
+// tree (the reference keeps a running sum: a few ulps of FP64 apart), one division.
+template <int MT>
+__device__ __forceinline__ double sinkhorn_passes(double v, int M, int i, int j, int passes, double eps)
+{
+    if constexpr (MT == 4) {
+        for (int pass = 0; pass < passes; pass++) {
+            const bool by_col = (pass & 1) == 0;
+            const int s0 = by_col ? j : i * 4, st = by_col ? 4 : 1;
+            const double p0 = __shfl_sync(0xffffffffu, v, s0), p1 = __shfl_sync(0xffffffffu, v, s0 + st);
+            const double p2 = __shfl_sync(0xffffffffu, v, s0 + 2 * st), p3 = __shfl_sync(0xffffffffu, v, s0 + 3 * st);
+            v = div_chain(v, ((p0 + p1) + (p2 + p3)) + eps);
+        }
+    } else {
+        for (int pass = 0; pass < passes; pass++) {
+            const bool by_col = (pass & 1) == 0;
+            double sum = 0.0;
+            for (int m = 0; m < M; m++) sum += __shfl_sync(0xffffffffu, v, by_col ? m * M + j : i * M + m);
+            v = div_chain(v, sum + eps);
+        }
+    }
+    return v;
+}
+
+__global__ void __cluster_dims__(HCC_CTAS, 1, 1) __launch_bounds__(HCC_THREADS) hc_pre_cluster_kernel(const HcFused a)
+{
+    __shared__ __align__(16) float hs[HCC_MAX_HS];     // this CTA's columns of the M streams
+    __shared__ float xs[HCC_MAX_W];                     // its columns of the collapsed vector
+    __shared__ double red[32];
+    __shared__ double mine[HCC_SPLITS][HCF_MAX_MIX + 1];   // this CTA's parts of the dots; [0][MIX] = sum h^2
+    __shared__ double mine_s2;                          // its part of sum x^2
+    __shared__ double dots[HCF_MAX_MIX + 1];
+    __shared__ float mx[HCF_MAX_MIX];
+    __shared__ double pre[G5B_MAX_HC];
+    const int t = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t rank = cluster_cta_rank();
+    const int M = a.M, E = a.E, ME = M * E, MIX = (2 + M) * M, MM = M * M;
+    const int W = E / HCC_CTAS, d0 = (int)rank * W;
+    float *ht = a.h + (size_t)t * ME;
+    const double eps = (double)a.hc_eps;
+
+    // The mixer rows depend on nothing computed here: this warp's first batch of them is requested
+    // before anything else, so it arrives while the streams are loaded, expanded and squared. (All
+    // CTAs of a cluster sit in one GPC, and its share of the L2 bandwidth makes these 0.8 MB per
+    // token take about 2 us.) Warp (q, b) takes rows b, b + 8, ... HCC_ROWS at a time and every
+    // HCC_SPLITS-th group of 32 16-byte pieces of each.
+    const int per_seg = W / 8, n_pieces = M * per_seg;            // pieces per stream segment / per row
+    const int q = warp / HCC_ROW_WARPS, b = warp % HCC_ROW_WARPS;
+    uint4 wv[HCC_ROWS][HCC_PIECES];
+    auto load_rows = [&](int k0, int p0) {
+#pragma unroll
+        for (int r = 0; r < HCC_ROWS; r++) {
+            const int k = k0 + r * HCC_ROW_WARPS;
+#pragma unroll
+            for (int u = 0; u < HCC_PIECES; u++) {
+                const int piece = p0 + u * 32 * HCC_SPLITS;
+                if (k < MIX && piece < n_pieces)
+                    wv[r][u] = ld_stream16(a.fn + (size_t)k * ME + (size_t)(piece / per_seg) * E + d0 + (piece % per_seg) * 8);
+            }
+        }
+    };
+    load_rows(b, lane + 32 * q);
+
+    for (int i = tid * 4; i < M * W; i += HCC_THREADS * 4)
+        *reinterpret_cast<float4 *>(hs + i) = *reinterpret_cast<const float4 *>(ht + (size_t)(i / W) * E + d0 + (i % W));
+    __syncthreads();
+    if (a.y) {
+        // the pending hc_post of the previous site: h'[j][d] = post[j] y[d] + sum_i comb[i][j] h[i][d]
+        // (src/core/glm53f_ops.c:612-625, FP64 there, compensated FP32 here); a thread owns a column,
+        // so no barrier inside
+        const float *cb = a.comb + (size_t)t * MM, *po = a.post + (size_t)t * M;
+        for (int d = tid; d < W; d += HCC_THREADS) {
+            const float yv = a.y[(size_t)t * E + d0 + d];
+            float nv[G5B_MAX_HC];
+#pragma unroll
+            for (int j = 0; j < G5B_MAX_HC; j++)
+                if (j < M) {
+                    Acc2 sj;
+                    acc2_fma(sj, po[j], yv);
+                    for (int i = 0; i < M; i++) acc2_fma(sj, cb[i * M + j], hs[i * W + d]);
+                    nv[j] = acc2_f32(sj);
+                }
+#pragma unroll
+            for (int j = 0; j < G5B_MAX_HC; j++)
+                if (j < M) {
+                    hs[j * W + d] = nv[j];
+                    ht[(size_t)j * E + d0 + d] = nv[j];
+                }
+        }
+        __syncthreads();
+    }
+    Acc2 sq;
+    for (int i = tid; i < M * W; i += HCC_THREADS) acc2_fma(sq, hs[i], hs[i]);
+    const double ss = block_sum(acc2_f64(sq), red);
+    if (tid == 0) mine[0][MIX] = ss;
+
+    // mixer rows (compensated FP32 sums; the reference's are FP64)
+    for (int k0 = b; k0 < MIX; k0 += HCC_ROW_WARPS * HCC_ROWS) {
+        Acc2 acc[HCC_ROWS];
+        for (int p0 = lane + 32 * q; p0 < n_pieces; p0 += 32 * HCC_SPLITS * HCC_PIECES) {
+            if (k0 != b || p0 != lane + 32 * q) load_rows(k0, p0);
+#pragma unroll
+            for (int u = 0; u < HCC_PIECES; u++) {
+                const int piece = p0 + u * 32 * HCC_SPLITS;
+                if (piece >= n_pieces) continue;
+                const float *hv = hs + (piece / per_seg) * W + (piece % per_seg) * 8;
+                const float4 h0 = *reinterpret_cast<const float4 *>(hv), h1 = *reinterpret_cast<const float4 *>(hv + 4);
+                const float hd[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+#pragma unroll
+                for (int r = 0; r < HCC_ROWS; r++) {
+                    if (k0 + r * HCC_ROW_WARPS >= MIX) continue;
+                    const uint32_t wr[4] = {wv[r][u].x, wv[r][u].y, wv[r][u].z, wv[r][u].w};
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        acc2_fma(acc[r], __uint_as_float(wr[j] << 16), hd[2 * j]);
+                        acc2_fma(acc[r], __uint_as_float(wr[j] & 0xffff0000u), hd[2 * j + 1]);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < HCC_ROWS; r++) {
+            const int k = k0 + r * HCC_ROW_WARPS;
+            const double s = warp_sum(acc2_f64(acc[r]));
+            if (lane == 0 && k < MIX) mine[q][k] = s;
+        }
+    }
+    __syncthreads();
+    cluster_arrive();
+    cluster_wait();
+
+    // ---- every CTA: the token's sums in CTA order, the norm factor, the gates
+    if (tid <= MIX) {
+        double s = 0.0;
+        for (uint32_t r = 0; r < HCC_CTAS; r++) {
+            double part = ld_cluster_f64(&mine[0][tid], r);
+            if (tid < MIX)
+                for (int qq = 1; qq < HCC_SPLITS; qq++) part += ld_cluster_f64(&mine[qq][tid], r);
+            s += part;
+        }
+        dots[tid] = s;
+    }
+    __syncthreads();
+    if (tid < MIX) {
+        const float inv = (float)(1.0 / sqrt(dots[MIX] / (double)ME + (double)a.rms_eps));
+        mx[tid] = (float)(dots[tid] * (double)inv);
+    }
+    __syncthreads();
+    if (tid >= 32 && tid < 32 + M) {
+        const int i = tid - 32;
+        pre[i] = (double)sigmoid_host(mul_add_unfused(mx[i], a.scale[0], a.base[i])) + eps;
+        if (rank == 0)
+            a.post[(size_t)t * M + i] = __fmul_rn(2.0f, sigmoid_host(mul_add_unfused(mx[M + i], a.scale[1], a.base[M + i])));
+    }
+    if (warp == 0) {
+        cluster_arrive();                                // nothing of this warp goes into sum x^2
+        if (rank == 0) {
+            // row softmax + eps, then column / row normalisations (src/core/glm53f_ops.c:577-598): a
+            // lane per matrix element, the row's / column's members gathered with shuffles
+            const int el = lane < MM ? lane : 0, i = el / M, j = el % M;
+            const int k = 2 * M + el;
+            const double l = (double)mul_add_unfused(mx[k], a.scale[2], a.base[k]);
+            double top = -INFINITY;
+            for (int jj = 0; jj < M; jj++) top = fmax(top, __shfl_sync(0xffffffffu, l, i * M + jj));
+            const double ex = exp(l - top);
+            double z = 0.0;
+            for (int jj = 0; jj < M; jj++) z += __shfl_sync(0xffffffffu, ex, i * M + jj);
+            double v = ex / z + eps;
+            v = M == 4 ? sinkhorn_passes<4>(v, M, i, j, 2 * a.iters - 1, eps) : sinkhorn_passes<0>(v, M, i, j, 2 * a.iters - 1, eps);
+            if (lane < MM) a.comb[(size_t)t * MM + lane] = (float)v;
+            __syncwarp();
+        }
+        cluster_wait();
+    } else {
+        // x[d] = sum_i pre[i] * h[i][d] in FP64 (src/core/glm53f_ops.c:603-607) for this CTA's columns
+        constexpr int NW = HCC_THREADS - 32;
+        const int wt = tid - 32;
+        asm volatile("bar.sync 1, %0;" ::"n"(NW) : "memory");     // `pre` comes from threads of these warps
+        double s2 = 0.0;
+        for (int d = wt; d < W; d += NW) {
+            double s = 0.0;
+            for (int i = 0; i < M; i++) s += pre[i] * (double)hs[i * W + d];
+            const float xv = (float)s;
+            xs[d] = xv;
+            s2 += (double)xv * (double)xv;
+        }
+        s2 = warp_sum(s2);
+        if (lane == 0) red[warp] = s2;
+        asm volatile("bar.sync 1, %0;" ::"n"(NW) : "memory");
+        if (wt == 0) {
+            double s = 0.0;
+            for (int w = 1; w < HCC_WARPS; w++) s += red[w];
+            mine_s2 = s;
+        }
+        cluster_arrive();
+        cluster_wait();
+        // ---- the sub-block's input: RMSNorm(x) * w (glm53f_rmsnorm, src/core/glm53f_ops.c:473-480)
+        double tot = 0.0;
+        for (uint32_t r = 0; r < HCC_CTAS; r++) tot += ld_cluster_f64(&mine_s2, r);
+        const float f = (float)(1.0 / sqrt(tot / (double)E + (double)a.rms_eps));
+        for (int d = wt; d < W; d += NW)
+            a.xn[(size_t)t * E + d0 + d] = __fmul_rn(a.norm_w[d0 + d], __fmul_rn(xs[d], f));
+    }
+    // no CTA leaves while another may still read its shared memory
+    cluster_arrive();
+    cluster_wait();
+}
+
+static bool hc_pre_cluster_takes(int M, int E)
+{
+    const int W = E / HCC_CTAS;
+    return E % (HCC_CTAS * 8) == 0 && W <= HCC_MAX_W && M * W <= HCC_MAX_HS && M * M <= 32 && M <= G5B_MAX_HC;
+}
+
 bool hc_pre_fused_supported(const HcW &w, int M, int E)
 {
-    return w.fn.dt == DT_BF16 && E <= HCF_MAX_E && E % (HCF_SLICES * 8) == 0 && M <= G5B_MAX_HC &&
+    if (w.fn.dt != DT_BF16) return false;
+    if (hc_pre_cluster_takes(M, E)) return true;
+    return E <= HCF_MAX_E && E % (HCF_SLICES * 8) == 0 && M <= G5B_MAX_HC &&
            M * (E / HCF_SLICES) <= HCF_MAX_E * G5B_MAX_HC / HCF_SLICES && E / HCF_SLICES <= HC_THREADS;
 }
 
@@ -317,7 +581,8 @@ void hc_pre_fused(cudaStream_t st, float *xn, float *post, float *comb, float *h
 {
     HcFused a{xn, post, comb, h, y_pending, static_cast<const uint16_t *>(w.fn.w), w.base, w.scale, norm_w, part,
               counters, M, E, iters, hc_eps, rms_eps};
-    G5B_LAUNCH(hc_pre_fused_kernel, dim3(HCF_SLICES, T), HC_THREADS, 0, st, a);
+    if (hc_pre_cluster_takes(M, E)) G5B_LAUNCH(hc_pre_cluster_kernel, dim3(HCC_CTAS, T), HCC_THREADS, 0, st, a);
+    else                            G5B_LAUNCH(hc_pre_fused_kernel, dim3(HCF_SLICES, T), HC_THREADS, 0, st, a);
 }
 
 // h'[j][d] = post[j]*y[d] + sum_i comb[i][j]*h[i][d] in FP64, in place: a thread owns column d of

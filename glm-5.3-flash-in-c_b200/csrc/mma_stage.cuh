@@ -42,6 +42,20 @@ __device__ __forceinline__ void split_f16(float x, __half &hi, __half &mid)
     mid = __float2half_rn((x - __half2float(hi)) * 2048.0f);
 }
 
+// The SwiGLU clamp bounds |silu(g) * u| by limit^2, so the activation terms of the down projection
+// are stored times the largest power of two that keeps limit^2 below 2^15 (2^8 for a clamp at 10):
+// small activations keep their bits in F16 and the factor comes off exactly in the down epilogue.
+// Products below 2^-24 / factor still flush to zero - an absolute error far below the FP32 rounding
+// of any output the layer produces from normalised activations.
+__device__ __forceinline__ float act_term_scale(float limit)
+{
+    const float b = limit * limit;
+    if (!(b > 0.f) || !(b < 32768.f)) return 1.0f;
+    int ex;
+    frexpf(32768.0f / b, &ex);                        // 32768 / b = m * 2^ex, 0.5 <= m < 1
+    return ldexpf(1.0f, ex - 1 > 14 ? 14 : ex - 1);
+}
+
 // accf[0..1]: row g (hi, mid columns), accf[2..3]: row g + 8, meaningful in lanes with t == 0.
 //   st     stage base (weights at offset 0)
 //   sc     the scale row of this warp's M tile

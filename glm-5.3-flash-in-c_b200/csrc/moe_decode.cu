@@ -101,6 +101,7 @@ __device__ unsigned long long g_decode_timers[160][16];
 
 __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeArgs a)
 {
+    const float act_sc = act_term_scale(a.limit), act_inv = 1.0f / act_sc;   // powers of two
 #ifdef G5B_STAGE_TIMERS
     const long long t_begin = clock64();
     if (threadIdx.x == 0 && blockIdx.x < 160) {
@@ -463,7 +464,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
                 uv = uv > a.limit ? a.limit : (uv < -a.limit ? -a.limit : uv);
                 const float act = __fmul_rn(__fmul_rn(gv, sigmoid_host(gv)), uv);
                 __half hi, mid;
-                split_f16(act, hi, mid);
+                split_f16(act * act_sc, hi, mid);
                 __half *dst = a.act + (size_t)slot * 2 * a.I;
                 dst[rt * 16 + r] = hi;
                 dst[a.I + rt * 16 + r] = mid;
@@ -505,6 +506,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
                 float v = 0.f;
 #pragma unroll
                 for (int q = 0; q < 4; q++) v += red[(2 * q + m2) * 16 + rr];
+                v *= act_inv;
                 const size_t at = (size_t)slot * a.E + rt * MM_ROWS + r;
                 if (a.ep_size > 1 && slot != a.K) {
                     // a routed pick's row goes straight into every rank's exchange buffer (peer stores)

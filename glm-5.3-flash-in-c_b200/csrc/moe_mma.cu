@@ -52,6 +52,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_mma_kernel(const MmaArgs a)
     extern __shared__ __align__(128) uint8_t smem[];
     const int C = GATEUP ? a.E : a.I;
     const int rows_total = GATEUP ? a.I : a.E;
+    const float act_sc = act_term_scale(a.limit), act_inv = 1.0f / act_sc;   // powers of two
     const int KH = C / MM_CB;
     const int scols = C / a.bc;
     const int rows_per_item = GATEUP ? MM_ROWS / 2 : MM_ROWS;
@@ -215,7 +216,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_mma_kernel(const MmaArgs a)
                     uv = uv > a.limit ? a.limit : (uv < -a.limit ? -a.limit : uv);
                     const float act = __fmul_rn(__fmul_rn(gv, sigmoid_host(gv)), uv);
                     __half hi, mid;
-                    split_f16(act, hi, mid);
+                    split_f16(act * act_sc, hi, mid);
                     __half *dst = static_cast<__half *>(a.y) + (size_t)pair * 2 * a.I;
                     dst[rt * 16 + r] = hi;
                     dst[a.I + rt * 16 + r] = mid;
@@ -225,7 +226,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_mma_kernel(const MmaArgs a)
                 float v = 0.f;
 #pragma unroll
                 for (int q = 0; q < 4; q++) v += red[(2 * q + m2) * 16 + rr];
-                static_cast<float *>(a.y)[(size_t)s_dst[slot] * a.E + rt * MM_ROWS + r] = v;
+                static_cast<float *>(a.y)[(size_t)s_dst[slot] * a.E + rt * MM_ROWS + r] = v * act_inv;
             }
             asm volatile("bar.sync 1, %0;" ::"r"(MM_CONS * 32) : "memory");
         }

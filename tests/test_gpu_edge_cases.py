@@ -1,0 +1,93 @@
+"""Edge cases of the MoE layer at full-size shapes (hidden 4096, inter 2048; 32 resident experts keep
+it small): activations that stress the exact two-term F16 split of the tensor-core kernels (all
+zero, huge, tiny, one element dominating), and exact ties in the router, where the reference takes
+the lowest expert index (src/core/glm53f_ops.c:955-966). Batch 1 runs the single decode kernel,
+batch 5 the batched kernels; both must give the CPU path's output."""
+import numpy as np
+import pytest
+
+import common
+import synth
+
+pkg = synth.pkg
+pytestmark = pytest.mark.gpu
+SEED = 5
+
+
+@pytest.fixture(scope="module")
+def small_layer(gpu_lib, binding):
+    spec, trunk, eng = synth.build_moe_layer_engine(SEED, n_experts=32)
+    yield spec, trunk, eng
+    eng.close()
+
+
+def _inputs(cfg):
+    rng = np.random.default_rng(77)
+    E = cfg.hidden
+    base = rng.standard_normal(E).astype(np.float32)
+    spike = (base * 1e-3).astype(np.float32); spike[123] = 3.0e4
+    return {
+        "zeros": np.zeros(E, np.float32),
+        "huge": (base * 1.0e4).astype(np.float32),
+        "small": (base * 1.0e-3).astype(np.float32),
+        "tiny": (base * 1.0e-12).astype(np.float32),
+        "one element dominates": spike,
+        "not bf16-representable": (base * np.float32(np.pi)).astype(np.float32),
+    }
+
+
+@pytest.mark.parametrize("T", [1, 5])
+def test_extreme_activations(small_layer, binding, T):
+    spec, trunk, eng = small_layer
+    for name, v in _inputs(spec.cfg).items():
+        x = np.tile(v, (T, 1)).astype(np.float32)
+        if T > 1:
+            x[1:] *= np.float32(0.5)                         # rows differ, same kind of extreme
+        idx, _ = eng.op_router(0, x)
+        orc = synth.oracle_moe_layer(binding, spec, trunk, SEED, idx.ravel())
+        want_idx, want_w = orc.op_router(0, x)
+        assert np.array_equal(idx, want_idx), name
+        got, want = eng.op_moe(0, x), orc.op_moe(0, x)
+        if not np.any(want):
+            assert not np.any(got), name
+        elif name == "tiny":
+            # The tensor-core kernels keep silu(g) * u as two F16 terms times 2^8: products below
+            # 2^-32 flush to zero. That is an absolute error (here the whole output, about 1e-20);
+            # normalised activations never come near it.
+            assert np.all(np.isfinite(got)) and np.abs(got - want).max() < 1e-12, name
+        else:
+            assert np.all(np.isfinite(got)), name
+            assert common.rel_err(got, want) < 1e-5, name
+        orc.close()
+
+
+def test_router_ties_take_the_lowest_index(gpu_lib, binding):
+    """Experts 2i and 2i+1 share their router row and bias, so every score ties exactly in pairs."""
+    spec = synth.layer_spec("moe", n_experts=32)
+    trunk = synth.moe_layer_trunk(spec, SEED)
+    gate, dt, _ = trunk["layers.0.mlp.gate.weight"]
+    gate = gate.copy(); gate[1::2] = gate[0::2]
+    trunk["layers.0.mlp.gate.weight"] = (gate, dt, None)
+    bias, bdt, _ = trunk["layers.0.mlp.gate.e_score_correction_bias"]
+    bias = bias.copy(); bias[1::2] = bias[0::2]
+    trunk["layers.0.mlp.gate.e_score_correction_bias"] = (bias, bdt, None)
+    eng = pkg.Engine(spec.cfg, spec.is_mla, spec.is_dense, 8)
+    eng.set_option("allow_partial", 1)
+    eng.load_all(trunk)
+    for ex in range(32):
+        eng.fill_expert(0, ex, SEED, *synth.expert_scales(spec.cfg, 0, ex, SEED))
+    eng.finalize()
+    for T in (1, 3):
+        x = synth.moe_inputs(spec.cfg, T, 11)
+        idx, w = eng.op_router(0, x)
+        orc = synth.oracle_moe_layer(binding, spec, trunk, SEED, idx.ravel())
+        widx, ww = orc.op_router(0, x)
+        assert np.array_equal(idx, widx)
+        # the top-8 of 16 tied pairs: both members of the four best pairs, the even one first
+        for t in range(T):
+            picks = idx[t].tolist()
+            assert all(picks[i + 1] == picks[i] + 1 and picks[i] % 2 == 0 for i in range(0, 8, 2)), picks
+        assert common.rel_err(w, ww) < 1e-6
+        assert common.rel_err(eng.op_moe(0, x), orc.op_moe(0, x)) < 1e-5      # the decode kernel selects for itself
+        orc.close()
+    eng.close()
