@@ -254,6 +254,41 @@ def time_attention_layers(pkg, torch, steps: int, peak: float, device: int = 0):
     return out
 
 
+def time_mhc_site(pkg, torch, steps: int, device: int = 0):
+    """One mHC site of a full-size layer on its own (gates, Sinkhorn, collapse, the sub-block's
+    RMSNorm in one launch), without and with the previous sub-block's stream expansion riding along,
+    for 1 and 64 tokens. The engine holds one KDA + MoE layer with 16 routed experts (0.5 GB): small
+    enough for a profiler capture."""
+    import synth
+    L = pkg.lib()
+    c = pkg.full_size_config()
+    c.n_layers = 1
+    c.n_experts = 16
+    spec = synth.Spec(c, [0], [0], with_head=False)
+    tensors = synth.make_model(spec, seed=6, recipe="baseline", experts=False)
+    eng = pkg.Engine(c, spec.is_mla, spec.is_dense, 8, device)
+    eng.set_option("allow_partial", 1)
+    eng.set_option("sequences", 64)
+    eng.load_all(tensors)
+    for ex in range(c.n_experts):
+        eng.fill_expert(0, ex, SEED, *synth.expert_scales(c, 0, ex, SEED))
+    eng.finalize()
+    rng = np.random.default_rng(SEED)
+    out = {}
+    for T in (1, 64):
+        h = torch.from_numpy(rng.standard_normal((T, c.hc_mult, c.hidden)).astype(np.float32)).cuda()
+        for op in (b"hc_site", b"hc_site_post"):
+            hd = h.clone()
+            each = np.zeros(max(steps, 3), np.float32); tot = C.c_float(0)
+            for k in (3, steps):
+                hd.copy_(h)
+                assert L.g5b_time_op(eng.handle, op, 0, hd.data_ptr(), T, 0, hd.data_ptr(), k, FLUSH_BYTES,
+                                     C.byref(tot), each.ctypes.data) == 0, L.g5b_last_error()
+            out[f"{op.decode()}_T{T}_us"] = float(np.mean(each[:steps])) * 1e3
+    eng.close()
+    return out
+
+
 def time_decoder_layers(pkg, torch, steps: int, device: int = 0):
     """Two whole full-size decoder layers, one new token: layer 0 = KDA + MoE, layer 1 = MLA (8192
     cached positions, indexer selecting) + MoE, each with its two mHC sites and norms. From the two
@@ -379,6 +414,8 @@ def main():
     ap.add_argument("--no-decoder-layers", action="store_true",
                     help="with --only-attention-layers: skip the two whole decoder layers (15 GB of experts), "
                          "which keeps an ncu capture of the KDA / MLA kernels small")
+    ap.add_argument("--only-mhc-site", action="store_true",
+                    help="run only the timing of one mHC site of a full-size layer and print it (a small case for ncu)")
     ap.add_argument("--no-attention-layers", action="store_true",
                     help="skip the KDA / MLA single-layer timings reported under 'extra'")
     ap.add_argument("--stream-warps", type=int, default=0, help="consumer warps of the streamed CUDA-core kernels (8/16)")
@@ -405,6 +442,9 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
     warmup = max(3, args.warmup)
+    if args.only_mhc_site:
+        print(json.dumps({"mhc_site": time_mhc_site(pkg, torch, max(3, args.steps), local)}), flush=True)
+        return
     if args.only_attention_layers:
         peak, _ = measured_peaks()
         res = {"config3": time_attention_layers(pkg, torch, max(3, args.steps), peak, local)}
@@ -501,6 +541,7 @@ def main():
     if rank == 0 and not args.no_attention_layers and args.experts == 288:
         extra["config3"] = time_attention_layers(pkg, torch, max(10, args.steps // 10), peak, local)
         extra["decoder_layers"] = time_decoder_layers(pkg, torch, max(10, args.steps // 10), local)
+        extra["mhc_site"] = time_mhc_site(pkg, torch, max(10, args.steps // 10), local)
 
     # ---- N > 1: the same layer expert-parallel (288 / N routed experts per rank, activations and the
     # shared expert replicated, contribution rows exchanged over peer mappings): one token stream

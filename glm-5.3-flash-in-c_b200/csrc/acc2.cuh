@@ -1,13 +1,15 @@
 // acc2.cuh - running sums in two floats (sum, carry) instead of one double.
 //
 // The reference accumulates its dot products in FP64 (src/core/glm53f_ops.c:101-154 and every
-// caller). On this GPU an FP64 instruction issues for one lane per clock per SM sub-partition -
-// a thirty-second of the FP32 rate, measured: 4 FMA per clock per SM - so a kernel that follows
-// the reference literally is bound by that pipe long before it is bound by memory. A compensated
-// FP32 sum (Knuth's TwoSum for the addition, the FMA's exact product error for the product) costs
-// ten FP32 instructions per term, a third of the FP64 FMA's issue time, and carries the sum to
-// about 2^-46 relative: after the final rounding to float it equals the FP64 result except where
-// that result sits within 2^-22 ulp of a rounding boundary.
+// caller). On this GPU the FP64 pipe issues about 16 FMA per clock per SM (an eighth of the FP32
+// rate; the MLA score kernel sustains 14.5), and a float -> double conversion costs about twice
+// an FP64 FMA, so a loop that converts both factors of every product spends four fifths of its
+// time converting. A compensated FP32 sum (Knuth's TwoSum for the addition, the FMA's exact
+// product error for the product) costs ten FP32 instructions per term - less than half of
+// convert + convert + FMA - and carries the sum to about 2^-46 relative: after the final rounding
+// to float it equals the FP64 result except where that result sits within 2^-22 ulp of a
+// rounding boundary. Used where the factors arrive as floats or BF16 (mHC mixer rows, router
+// rows); kernels whose factors already sit in shared memory as doubles keep the FP64 FMA.
 #pragma once
 
 namespace g5b {

@@ -23,6 +23,7 @@
 // 1329-1340).
 #include <stdlib.h>
 
+#include "acc2.cuh"
 #include "kernels.h"
 #include "mma_stage.cuh"
 
@@ -342,6 +343,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
                     const float *xq = a.x + (size_t)quarter * span;
                     uint4 wv[4];
                     float4 x0[4], x1[4];
+                    Acc2 lo[2];          // compensated FP32 sums: the FP64 pipe is an eighth of the FP32 rate
 #pragma unroll
                     for (int k = 0; k < 4; k++) {
                         const int c = lane * 8 + k * 256;
@@ -355,11 +357,12 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
                         float w[8];
                         bf16x2_to_f32(wv[k].x, w[0], w[1]); bf16x2_to_f32(wv[k].y, w[2], w[3]);
                         bf16x2_to_f32(wv[k].z, w[4], w[5]); bf16x2_to_f32(wv[k].w, w[6], w[7]);
-                        acc = fma((double)w[0], (double)x0[k].x, acc); acc = fma((double)w[1], (double)x0[k].y, acc);
-                        acc = fma((double)w[2], (double)x0[k].z, acc); acc = fma((double)w[3], (double)x0[k].w, acc);
-                        acc = fma((double)w[4], (double)x1[k].x, acc); acc = fma((double)w[5], (double)x1[k].y, acc);
-                        acc = fma((double)w[6], (double)x1[k].z, acc); acc = fma((double)w[7], (double)x1[k].w, acc);
+                        acc2_fma(lo[0], w[0], x0[k].x); acc2_fma(lo[1], w[1], x0[k].y);
+                        acc2_fma(lo[0], w[2], x0[k].z); acc2_fma(lo[1], w[3], x0[k].w);
+                        acc2_fma(lo[0], w[4], x1[k].x); acc2_fma(lo[1], w[5], x1[k].y);
+                        acc2_fma(lo[0], w[6], x1[k].z); acc2_fma(lo[1], w[7], x1[k].w);
                     }
+                    acc = acc2_f64(lo[0]) + acc2_f64(lo[1]);
                 } else if (e < a.NE) {
                     if (!released) { asm volatile("bar.arrive 2, %0;" ::"r"((MM_CONS + 1) * 32) : "memory"); released = true; }
                     if (a.gate_dt == DT_BF16) {
