@@ -1132,14 +1132,26 @@ struct Staged {
 // Host buffers through the engine's own staging rows (no allocation per call): copy a piece in,
 // run, copy the result out; one wait at the end. With pinned host memory the copies overlap the
 // kernels of the neighbouring pieces.
+// `direct_out`: the op's last kernel writes every output element exactly once with plain stores.
+// If the caller's buffer is pinned and mapped, that kernel then writes straight into it (16 KB per
+// token over PCIe as posted writes, visible once the stream has drained) and the copy engine's
+// turn after the kernel - about 6 us of a 90 us call at batch 1 - is saved.
 template <typename F>
-static int host_op(g5b_engine *e, const float *x, int T, float *out, F &&run)
+static int host_op(g5b_engine *e, const float *x, int T, float *out, F &&run, bool direct_out = false)
 {
     const size_t E = e->c.hidden;
+    float *out_dev = nullptr;
+    if (direct_out) {
+        cudaPointerAttributes at{};
+        if (cudaPointerGetAttributes(&at, out) == cudaSuccess && at.type == cudaMemoryTypeHost && at.devicePointer)
+            out_dev = static_cast<float *>(at.devicePointer);
+        else
+            cudaGetLastError();
+    }
     FOR_CHUNKS(T) {
         CU(cudaMemcpyAsync(e->xn, x + t0 * E, n_ * E * 4, cudaMemcpyHostToDevice, e->st));
-        if (run(e->xn, n_, e->y, t0)) return -1;
-        CU(cudaMemcpyAsync(out + t0 * E, e->y, n_ * E * 4, cudaMemcpyDeviceToHost, e->st));
+        if (run(e->xn, n_, out_dev ? out_dev + t0 * E : e->y, t0)) return -1;
+        if (!out_dev) CU(cudaMemcpyAsync(out + t0 * E, e->y, n_ * E * 4, cudaMemcpyDeviceToHost, e->st));
     }
     CU(cudaStreamSynchronize(e->st));
     CU(cudaGetLastError());
@@ -1152,7 +1164,7 @@ extern "C" int g5b_op_moe(g5b_engine *e, int layer, const float *x, int T, float
     if (e->L[layer].is_dense) return fail("layer %d has a dense MLP", layer);
     return host_op(e, x, T, out, [&](const float *xd, int n, float *od, int) {
         return run_moe(e, e->L[layer], xd, n, od, with_shared);
-    });
+    }, e->ep_size <= 1);
 }
 
 extern "C" int g5b_op_router(g5b_engine *e, int layer, const float *x, int T, int *idx, float *w)

@@ -317,7 +317,7 @@ __global__ void __launch_bounds__(HC_THREADS) hc_pre_fused_kernel(const HcFused 
 // (39 dependent normalisations, needed only for the NEXT stream expansion) runs in warp 0 of CTA 0
 // beside all that: warp 0 arrives at the second barrier before it starts and waits after.
 constexpr int HCC_CTAS = 8, HCC_THREADS = 512, HCC_WARPS = HCC_THREADS / 32, HCC_MAX_W = 1024, HCC_MAX_HS = 4096;
-constexpr int HCC_ROWS = 3, HCC_PIECES = 4, HCC_ROW_WARPS = 8, HCC_SPLITS = HCC_WARPS / HCC_ROW_WARPS;
+constexpr int HCC_ROWS = 3, HCC_ROW_WARPS = 8, HCC_SPLITS = HCC_WARPS / HCC_ROW_WARPS;
 
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
@@ -394,27 +394,25 @@ __global__ void __cluster_dims__(HCC_CTAS, 1, 1) __launch_bounds__(HCC_THREADS) 
     float *ht = a.h + (size_t)t * ME;
     const double eps = (double)a.hc_eps;
 
-    // The mixer rows depend on nothing computed here: this warp's first batch of them is requested
-    // before anything else, so it arrives while the streams are loaded, expanded and squared. (All
-    // CTAs of a cluster sit in one GPC, and its share of the L2 bandwidth makes these 0.8 MB per
-    // token take about 2 us.) Warp (q, b) takes rows b, b + 8, ... HCC_ROWS at a time and every
-    // HCC_SPLITS-th group of 32 16-byte pieces of each.
+    // Warp (q, b) takes the mixer rows b, b + 8, ... HCC_ROWS at a time and every HCC_SPLITS-th group of
+    // 32 16-byte pieces of each. The rows depend on nothing computed here: the first piece is
+    // requested before anything else; after that the piece for the next turn of the loop is
+    // requested before the current one is summed. (The loop is kept rolled on purpose: this kernel
+    // runs once per site with a cold instruction cache, and with the twelve pieces of a warp
+    // unrolled - 17 KB of straight-line code - it waited for instruction fetch more than for data.)
     const int per_seg = W / 8, n_pieces = M * per_seg;            // pieces per stream segment / per row
     const int q = warp / HCC_ROW_WARPS, b = warp % HCC_ROW_WARPS;
-    uint4 wv[HCC_ROWS][HCC_PIECES];
-    auto load_rows = [&](int k0, int p0) {
+    const int p_first = lane + 32 * q, p_step = 32 * HCC_SPLITS;
+    uint4 wnext[HCC_ROWS];
+    auto load_piece = [&](int k0, int piece) {
 #pragma unroll
         for (int r = 0; r < HCC_ROWS; r++) {
             const int k = k0 + r * HCC_ROW_WARPS;
-#pragma unroll
-            for (int u = 0; u < HCC_PIECES; u++) {
-                const int piece = p0 + u * 32 * HCC_SPLITS;
-                if (k < MIX && piece < n_pieces)
-                    wv[r][u] = ld_stream16(a.fn + (size_t)k * ME + (size_t)(piece / per_seg) * E + d0 + (piece % per_seg) * 8);
-            }
+            if (k < MIX && piece < n_pieces)
+                wnext[r] = ld_stream16(a.fn + (size_t)k * ME + (size_t)(piece / per_seg) * E + d0 + (piece % per_seg) * 8);
         }
     };
-    load_rows(b, lane + 32 * q);
+    load_piece(b, p_first);
 
     for (int i = tid * 4; i < M * W; i += HCC_THREADS * 4)
         *reinterpret_cast<float4 *>(hs + i) = *reinterpret_cast<const float4 *>(ht + (size_t)(i / W) * E + d0 + (i % W));
@@ -452,24 +450,24 @@ __global__ void __cluster_dims__(HCC_CTAS, 1, 1) __launch_bounds__(HCC_THREADS) 
     // mixer rows (compensated FP32 sums; the reference's are FP64)
     for (int k0 = b; k0 < MIX; k0 += HCC_ROW_WARPS * HCC_ROWS) {
         Acc2 acc[HCC_ROWS];
-        for (int p0 = lane + 32 * q; p0 < n_pieces; p0 += 32 * HCC_SPLITS * HCC_PIECES) {
-            if (k0 != b || p0 != lane + 32 * q) load_rows(k0, p0);
+        if (k0 != b) load_piece(k0, p_first);
+#pragma unroll 1
+        for (int piece = p_first; piece < n_pieces; piece += p_step) {
+            uint4 wv[HCC_ROWS];
 #pragma unroll
-            for (int u = 0; u < HCC_PIECES; u++) {
-                const int piece = p0 + u * 32 * HCC_SPLITS;
-                if (piece >= n_pieces) continue;
-                const float *hv = hs + (piece / per_seg) * W + (piece % per_seg) * 8;
-                const float4 h0 = *reinterpret_cast<const float4 *>(hv), h1 = *reinterpret_cast<const float4 *>(hv + 4);
-                const float hd[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+            for (int r = 0; r < HCC_ROWS; r++) wv[r] = wnext[r];
+            load_piece(k0, piece + p_step);
+            const float *hv = hs + (piece / per_seg) * W + (piece % per_seg) * 8;
+            const float4 h0 = *reinterpret_cast<const float4 *>(hv), h1 = *reinterpret_cast<const float4 *>(hv + 4);
+            const float hd[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
 #pragma unroll
-                for (int r = 0; r < HCC_ROWS; r++) {
-                    if (k0 + r * HCC_ROW_WARPS >= MIX) continue;
-                    const uint32_t wr[4] = {wv[r][u].x, wv[r][u].y, wv[r][u].z, wv[r][u].w};
+            for (int r = 0; r < HCC_ROWS; r++) {
+                if (k0 + r * HCC_ROW_WARPS >= MIX) continue;
+                const uint32_t wr[4] = {wv[r].x, wv[r].y, wv[r].z, wv[r].w};
 #pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        acc2_fma(acc[r], __uint_as_float(wr[j] << 16), hd[2 * j]);
-                        acc2_fma(acc[r], __uint_as_float(wr[j] & 0xffff0000u), hd[2 * j + 1]);
-                    }
+                for (int j = 0; j < 4; j++) {
+                    acc2_fma(acc[r], __uint_as_float(wr[j] << 16), hd[2 * j]);
+                    acc2_fma(acc[r], __uint_as_float(wr[j] & 0xffff0000u), hd[2 * j + 1]);
                 }
             }
         }

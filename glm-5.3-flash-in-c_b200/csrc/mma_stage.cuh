@@ -47,7 +47,7 @@ __device__ __forceinline__ void split_f16(float x, __half &hi, __half &mid)
 // small activations keep their bits in F16 and the factor comes off exactly in the down epilogue.
 // Products below 2^-24 / factor still flush to zero - an absolute error far below the FP32 rounding
 // of any output the layer produces from normalised activations.
-__device__ __forceinline__ float act_term_scale(float limit)
+__host__ __device__ __forceinline__ float act_term_scale(float limit)
 {
     const float b = limit * limit;
     if (!(b > 0.f) || !(b < 32768.f)) return 1.0f;

@@ -91,3 +91,42 @@ def test_router_ties_take_the_lowest_index(gpu_lib, binding):
         assert common.rel_err(eng.op_moe(0, x), orc.op_moe(0, x)) < 1e-5      # the decode kernel selects for itself
         orc.close()
     eng.close()
+
+
+def test_forward_refuses_what_the_reference_refuses(gpu_lib, binding):
+    """Error behaviour of the forward pass: an empty call, a token outside the vocabulary and a call
+    that would overrun the session's positions are refused with a message and leave the session
+    where it was (the reference returns an error from glm53f_model_forward for the same inputs,
+    src/model/glm53f_model.c:366-381); the next valid call continues from the same state."""
+    spec = synth.tiny_spec()
+    tensors = synth.make_model(spec, seed=0, recipe="baseline")
+    eng, orc = common.build_models(spec, tensors, 8, binding)
+    ids = np.random.default_rng(3).integers(0, spec.cfg.vocab, 6)
+    lg = eng.forward(ids)[0]
+    assert eng.cached == 6
+    for bad, word in (([], "at least one"), ([spec.cfg.vocab], "vocabulary"), ([-1], "vocabulary"),
+                      ([1, 2, 3], "capacity")):
+        with pytest.raises(RuntimeError, match=word):
+            eng.forward(bad)
+        assert eng.cached == 6
+    lo = orc.forward(ids)[0]
+    assert common.rel_err(lg, lo) < 1e-3
+    nxt = [int(np.argmax(lo))]
+    assert common.rel_err(eng.forward(nxt)[0], orc.forward(nxt)[0]) < 1e-3     # state intact after the refusals
+    assert eng.cached == 7
+    eng.close(); orc.close()
+
+
+@pytest.mark.parametrize("T", [1, 5])
+def test_moe_op_with_pinned_host_buffers(small_layer, T):
+    """With a pinned, mapped output buffer the layer's last kernel writes the result straight into host
+    memory (no device-to-host copy); the values are those of the staged path, bit for bit."""
+    import torch
+    spec, _, eng = small_layer
+    L = pkg.lib()
+    x = synth.moe_inputs(spec.cfg, T, 21)
+    want = eng.op_moe(0, x)                                   # pageable numpy buffers: staged copies
+    xp = torch.from_numpy(x).pin_memory()
+    op = torch.full((T, spec.cfg.hidden), float("nan")).pin_memory()
+    assert L.g5b_op_moe(eng.handle, 0, xp.numpy().ctypes.data, T, op.numpy().ctypes.data, 1) == 0, L.g5b_last_error()
+    assert np.array_equal(op.numpy(), want)
