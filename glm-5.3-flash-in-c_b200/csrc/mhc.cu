@@ -424,21 +424,20 @@ __global__ void __cluster_dims__(HCC_CTAS, 1, 1) __launch_bounds__(HCC_THREADS) 
         const float *cb = a.comb + (size_t)t * MM, *po = a.post + (size_t)t * M;
         for (int d = tid; d < W; d += HCC_THREADS) {
             const float yv = a.y[(size_t)t * E + d0 + d];
-            float nv[G5B_MAX_HC];
+            float hv[G5B_MAX_HC];
 #pragma unroll
-            for (int j = 0; j < G5B_MAX_HC; j++)
-                if (j < M) {
-                    Acc2 sj;
-                    acc2_fma(sj, po[j], yv);
-                    for (int i = 0; i < M; i++) acc2_fma(sj, cb[i * M + j], hs[i * W + d]);
-                    nv[j] = acc2_f32(sj);
-                }
+            for (int i = 0; i < G5B_MAX_HC; i++) hv[i] = i < M ? hs[i * W + d] : 0.f;
+#pragma unroll 1
+            for (int j = 0; j < M; j++) {                // rolled: cold instruction cache, see above
+                Acc2 sj;
+                acc2_fma(sj, po[j], yv);
 #pragma unroll
-            for (int j = 0; j < G5B_MAX_HC; j++)
-                if (j < M) {
-                    hs[j * W + d] = nv[j];
-                    ht[(size_t)j * E + d0 + d] = nv[j];
-                }
+                for (int i = 0; i < G5B_MAX_HC; i++)
+                    if (i < M) acc2_fma(sj, cb[i * M + j], hv[i]);
+                const float nv = acc2_f32(sj);
+                hs[j * W + d] = nv;
+                ht[(size_t)j * E + d0 + d] = nv;
+            }
         }
         __syncthreads();
     }
