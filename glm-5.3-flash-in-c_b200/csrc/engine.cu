@@ -749,8 +749,13 @@ static int run_kda(g5b_engine *e, Layer &w, const float *x, int n, float *out, b
     GemvSeg a[6] = {make_seg(w.kq, x, E, e->kq, P), make_seg(w.kk, x, E, e->kk, P), make_seg(w.kv, x, E, e->kv, P),
                     make_seg(w.kb, x, E, e->kbraw, H), make_seg(w.f_a, x, E, lrf, D), make_seg(w.g_a, x, E, lrg, D)};
     if (proj_batch(e, a, 6, n)) return -1;
-    GemvSeg b[2] = {make_seg(w.f_b, lrf, D, e->kz, P), make_seg(w.g_b, lrg, D, e->kgb, P)};
-    if (proj_batch(e, b, 2, n)) return -1;
+    // one new token: the recurrence kernel takes the two low-rank up-projections itself
+    const bool lr_inside = n == 1 && !batch && w.f_b.dt == G5B_DT_BF16 && w.g_b.dt == G5B_DT_BF16 && (D == 64 || D == 128);
+    const KdaLowRank lr{w.f_b.w, w.g_b.w, lrf, lrg};
+    if (!lr_inside) {
+        GemvSeg b[2] = {make_seg(w.f_b, lrf, D, e->kz, P), make_seg(w.g_b, lrg, D, e->kgb, P)};
+        if (proj_batch(e, b, 2, n)) return -1;
+    }
     KdaShape ks{H, D, c.conv_k, c.gate_lb, c.rms_eps};
     if (n == 1) prefetch_beside(e, w.ko);               // the recurrence below leaves half the SMs and all of HBM idle
     if (batch)
@@ -758,7 +763,8 @@ static int run_kda(g5b_engine *e, Layer &w, const float *x, int n, float *out, b
                  w.A_log, w.dt_bias, w.o_norm, w.kda_state, 1, ks, n, e->kda_seq);
     else
         kda_core(e->st, e->ko, e->kq, e->kk, e->kv, e->kz, e->kbraw, e->kgb, w.q_conv, w.k_conv, w.v_conv,
-                 w.A_log, w.dt_bias, w.o_norm, w.kda_state + (size_t)e->cur_seq * e->kda_seq, n, ks);
+                 w.A_log, w.dt_bias, w.o_norm, w.kda_state + (size_t)e->cur_seq * e->kda_seq, n, ks, 1, 0,
+                 lr_inside ? &lr : nullptr);
     return proj(e, w.ko, e->ko, P, out, E, n);
 }
 

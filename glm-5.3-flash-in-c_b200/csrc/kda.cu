@@ -26,6 +26,8 @@ struct KdaArgs {
     float gate_lb, rms_eps;
     size_t seq_stride;            // floats between the states of consecutive sequences (grid.y > 1:
                                   // CTA (h, s) advances sequence s by the T positions at rows s*T ...)
+    const uint16_t *f_b, *g_b;    // optional (T == 1): z and gb are computed here from lrf / lrg
+    const float *lrf, *lrg;
 };
 
 // conv + SiLU of one channel at one position; `past` holds K-1 previous inputs, oldest first.
@@ -55,6 +57,23 @@ __global__ void __launch_bounds__(DS > 0 ? DS : 512) kda_core_kernel(const KdaAr
     float *cs = state + (size_t)a.H * D * D;
     const int row0 = blockIdx.y * a.T;                       // first activation row of this sequence
 
+    // One new token: the two low-rank up-projections z = f_b lrf, gb = g_b lrg of this head's channels
+    // are taken here. Their 2 x D rows of D BF16 are copied to shared memory asynchronously first
+    // thing (16-byte pieces, a warp reads consecutive pieces of consecutive rows), so they travel
+    // beside the state; each thread later multiplies the two rows of its own channel.
+    extern __shared__ __align__(16) uint8_t lrw[];               // [2 D][pitch]: f_b rows, then g_b rows
+    const int pitch = 2 * D + 16;                                // 16 bytes of padding: rows fall on different banks
+    if (a.f_b) {
+        const int per_row = D / 8;
+        for (int i = d; i < 2 * D * per_row; i += (int)blockDim.x) {
+            const int row = i / per_row, piece = i % per_row;
+            const uint16_t *src = (row < D ? a.f_b : a.g_b) + ((size_t)h * D + (row < D ? row : row - D)) * D + piece * 8;
+            const uint32_t dst = (uint32_t)__cvta_generic_to_shared(lrw + (size_t)row * pitch + piece * 16);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+
     float pq[16], pk[16], pv[16], wq[17], wk[17], wv[17];
     for (int j = 0; j < hist; j++) {
         pq[j] = cs[(size_t)ch * hist + j];
@@ -70,6 +89,32 @@ __global__ void __launch_bounds__(DS > 0 ? DS : 512) kda_core_kernel(const KdaAr
     if (DS > 0) {
 #pragma unroll
         for (int i = 0; i < DS; i++) sreg[i] = S[(size_t)i * DS + d];
+    }
+    // (the low-rank rows requested above have landed by now, under the state's and the histories' loads)
+    float z_own = 0.f, gb_own = 0.f;
+    if (a.f_b) {
+        if (live) { sq[d] = a.lrf[d]; sk[d] = a.lrg[d]; }
+        asm volatile("cp.async.wait_all;" ::: "memory");
+        __syncthreads();
+        if (live) {
+            const uint8_t *fr = lrw + (size_t)d * pitch, *gr = lrw + (size_t)(D + d) * pitch;
+            float z0 = 0.f, z1 = 0.f, g0 = 0.f, g1 = 0.f;
+#pragma unroll 4
+            for (int c = 0; c < D; c += 8) {
+                const uint4 fw = *reinterpret_cast<const uint4 *>(fr + 2 * c), gw = *reinterpret_cast<const uint4 *>(gr + 2 * c);
+                const uint32_t fu[4] = {fw.x, fw.y, fw.z, fw.w}, gu[4] = {gw.x, gw.y, gw.z, gw.w};
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    float lo, hi;
+                    bf16x2_to_f32(fu[j], lo, hi);
+                    z0 = fmaf(lo, sq[c + 2 * j], z0); z1 = fmaf(hi, sq[c + 2 * j + 1], z1);
+                    bf16x2_to_f32(gu[j], lo, hi);
+                    g0 = fmaf(lo, sk[c + 2 * j], g0); g1 = fmaf(hi, sk[c + 2 * j + 1], g1);
+                }
+            }
+            z_own = z0 + z1; gb_own = g0 + g1;
+        }
+        __syncthreads();
     }
     const float ea = expf_host(a.A_log[h]);
     const float dtb = a.dt_bias[ch], onw = a.o_norm[live ? d : 0];
@@ -93,7 +138,7 @@ __global__ void __launch_bounds__(DS > 0 ? DS : 512) kda_core_kernel(const KdaAr
         if (live) {
             sq[d] = __fmul_rn(__fmul_rn(qv, qinv), qscale);
             sk[d] = __fmul_rn(kv, kinv);
-            const float g = __fmul_rn(a.gate_lb, sigmoid_host(__fmul_rn(ea, __fadd_rn(a.z[off], dtb))));
+            const float g = __fmul_rn(a.gate_lb, sigmoid_host(__fmul_rn(ea, __fadd_rn(a.f_b ? z_own : a.z[off], dtb))));
             sal[d] = expf_host(g);
         }
         __syncthreads();
@@ -132,7 +177,7 @@ __global__ void __launch_bounds__(DS > 0 ? DS : 512) kda_core_kernel(const KdaAr
         if (live) {
             const float inv = (float)(1.0 / sqrt(oo / (double)D + (double)a.rms_eps));
             const float n = __fmul_rn(onw, __fmul_rn(ov, inv));
-            a.o[off] = __fmul_rn(n, sigmoid_host(a.gb[off]));
+            a.o[off] = __fmul_rn(n, sigmoid_host(a.f_b ? gb_own : a.gb[off]));
         }
     }
 
@@ -152,13 +197,21 @@ __global__ void __launch_bounds__(DS > 0 ? DS : 512) kda_core_kernel(const KdaAr
 void kda_core(cudaStream_t st, float *o, const float *q, const float *k, const float *v, const float *z,
               const float *braw, const float *gb, const float *q_conv, const float *k_conv,
               const float *v_conv, const float *A_log, const float *dt_bias, const float *o_norm,
-              float *state, int T, const KdaShape &s, int n_seq, size_t seq_stride)
+              float *state, int T, const KdaShape &s, int n_seq, size_t seq_stride, const KdaLowRank *lr)
 {
+    const bool fused = lr && T == 1 && n_seq <= 1 && (s.D == 64 || s.D == 128);
     KdaArgs a{o, q, k, v, z, braw, gb, q_conv, k_conv, v_conv, A_log, dt_bias, o_norm, state,
-              T, s.H, s.D, s.K, s.gate_lb, s.rms_eps, seq_stride};
+              T, s.H, s.D, s.K, s.gate_lb, s.rms_eps, seq_stride,
+              fused ? static_cast<const uint16_t *>(lr->f_b) : nullptr, fused ? static_cast<const uint16_t *>(lr->g_b) : nullptr,
+              fused ? lr->lrf : nullptr, fused ? lr->lrg : nullptr};
     const dim3 grid(s.H, n_seq < 1 ? 1 : n_seq);
-    if (s.D == 128)     G5B_LAUNCH(kda_core_kernel<128>, grid, 128, 0, st, a);
-    else if (s.D == 64) G5B_LAUNCH(kda_core_kernel<64>, grid, 64, 0, st, a);
+    const size_t smem = fused ? (size_t)2 * s.D * (2 * s.D + 16) : 0;
+    if (s.D == 128) {
+        static bool attr = false;
+        if (!attr) { cudaFuncSetAttribute(kda_core_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 128 * (2 * 128 + 16)); attr = true; }
+        G5B_LAUNCH(kda_core_kernel<128>, grid, 128, smem, st, a);
+    }
+    else if (s.D == 64) G5B_LAUNCH(kda_core_kernel<64>, grid, 64, smem, st, a);
     else                G5B_LAUNCH(kda_core_kernel<0>, grid, ((s.D + 31) / 32) * 32, 0, st, a);
 }
 

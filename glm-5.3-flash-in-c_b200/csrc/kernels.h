@@ -187,12 +187,21 @@ void ep_exchange_combine(cudaStream_t st, const EpExchange &a, int ctas);
 
 // ---- kda.cu -------------------------------------------------------------------------------
 struct KdaShape { int H, D, K; float gate_lb, rms_eps; };
+// One new token only: the two low-rank up-projections z = f_b lrf and gb = g_b lrg (BF16 [H*D][D],
+// inputs of D floats) are taken inside the kernel, each thread the two rows of its own channel,
+// instead of by a launch of their own between the input projections and this kernel.
+struct KdaLowRank {
+    const void *f_b, *g_b;
+    const float *lrf, *lrg;
+};
+
 // q,k,v,z,gb: [T][H*D] projections (q,k,v before the short convolution); braw [T][H]; state as
 // the reference lays it out (S [H][D][D] then conv histories q|k|v, glm53f.h:363-367).
 void kda_core(cudaStream_t st, float *o, const float *q, const float *k, const float *v, const float *z,
               const float *braw, const float *gb, const float *q_conv, const float *k_conv,
               const float *v_conv, const float *A_log, const float *dt_bias, const float *o_norm,
-              float *state, int T, const KdaShape &s, int n_seq = 1, size_t seq_stride = 0);
+              float *state, int T, const KdaShape &s, int n_seq = 1, size_t seq_stride = 0,
+              const KdaLowRank *lr = nullptr);
 
 // ---- mla.cu -------------------------------------------------------------------------------
 struct MlaShape {

@@ -68,7 +68,9 @@ __device__ __forceinline__ void mma_consume_stage(float (&accf)[4], const uint8_
     const uint8_t *w1p = w0p + 8 * MM_PITCH;
     const int c_lane = col0 + kq * 512 + 16 * t;
     float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
+    // unrolled by four, not eight: as fast with a warm instruction cache and about 1 us faster when
+    // the kernel runs after other kernels (cold code costs about 0.2 us per KB on the critical path)
+#pragma unroll 4
     for (int step = 0; step < 8; step++) {
         const uint4 w0 = *reinterpret_cast<const uint4 *>(w0p + step * 64);
         const uint4 w1 = *reinterpret_cast<const uint4 *>(w1p + step * 64);
