@@ -100,7 +100,7 @@ struct g5b_engine {
     volatile int *err_host = nullptr;   // mapped host memory: kernels record a timed-out wait here
     cudaStream_t st = nullptr;
     cudaStream_t side = nullptr;                         // L2 prefetches that run beside latency-bound kernels
-    cudaEvent_t side_ev = nullptr;
+    cudaEvent_t side_ev = nullptr, side_done = nullptr;  // fork from / join into the main stream
     std::vector<Layer> L;
     std::vector<std::unordered_map<std::string, Target>> names;   // per layer
     DMat embed, lm_head;
@@ -255,6 +255,7 @@ extern "C" g5b_engine *g5b_engine_create(const g5b_config *cfg, const uint8_t *i
     e->n_local0 = ep_rank * e->n_local;
     cudaStreamCreateWithFlags(&e->side, cudaStreamNonBlocking);
     cudaEventCreateWithFlags(&e->side_ev, cudaEventDisableTiming);
+    cudaEventCreateWithFlags(&e->side_done, cudaEventDisableTiming);
     if (cudaStreamCreateWithFlags(&e->st, cudaStreamNonBlocking) != cudaSuccess) {
         fail("cannot create a stream"); delete e; return nullptr;
     }
@@ -800,8 +801,20 @@ static int run_mla(g5b_engine *e, Layer &w, const float *x, int n, int cached, f
     GemvSeg b[2] = {make_seg(w.q_b, e->mq_raw, c.q_lora, e->mq, c.mla_heads * c.qk_nope, e->minvq, w.q_a_norm),
                     make_seg(w.wq_b, e->mq_raw, c.q_lora, e->mqidx, c.index_heads * c.index_dim, e->minvq, w.q_a_norm)};
     if (proj_batch(e, b, 2, n)) return -1;
+    // The indexer (pool scores, top-k, expansion: two latency-bound kernels) and the absorption of
+    // W_k into the query need nothing from each other: the absorption runs on the side stream
+    // meanwhile and the main stream takes it back before the scores.
+    bool forked = false, join = false;
+    if (e->side && e->side_ev && e->side_done && cudaEventRecord(e->side_ev, e->st) == cudaSuccess &&
+        cudaStreamWaitEvent(e->side, e->side_ev, 0) == cudaSuccess) {
+        mla_absorb(e->side, e->mqa, e->mq, w.kv_b, n, s);
+        forked = true;
+        join = cudaEventRecord(e->side_done, e->side) == cudaSuccess;
+        if (!join) cudaStreamSynchronize(e->side);
+    }
     dsa_select(e->st, e->msel, e->mnsel, ist, e->mqidx, e->mwp, e->mscore, n, cached, s);
-    mla_absorb(e->st, e->mqa, e->mq, w.kv_b, n, s);
+    if (!forked) mla_absorb(e->st, e->mqa, e->mq, w.kv_b, n, s);
+    else if (join && cudaStreamWaitEvent(e->st, e->side_done, 0) != cudaSuccess) cudaStreamSynchronize(e->side);
     mla_attend(e->st, e->mcb, e->mqa, lat, e->msel, e->mnsel, e->mdsc, e->mpart, e->mstats, e->mcount, MLA_PART_TOKENS, n, cached, s);
     mla_vout(e->st, e->macc, e->mcb, w.kv_b, n, s);
     gemv(e->st, w.mo, e->macc, c.mla_heads * c.v_head, out, E, n);
@@ -1054,6 +1067,7 @@ extern "C" void g5b_engine_free(g5b_engine *e)
     for (int i = 0; i <= PROF_SLOTS; i++) cudaEventDestroy(e->prof_ev[i]);
     if (e->side) { cudaStreamSynchronize(e->side); cudaStreamDestroy(e->side); }
     if (e->side_ev) cudaEventDestroy(e->side_ev);
+    if (e->side_done) cudaEventDestroy(e->side_done);
     cudaStreamDestroy(e->st);
     delete e;
 }
