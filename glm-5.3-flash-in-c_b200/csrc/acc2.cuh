@@ -8,8 +8,8 @@
 // product error for the product) costs ten FP32 instructions per term - less than half of
 // convert + convert + FMA - and carries the sum to about 2^-46 relative: after the final rounding
 // to float it equals the FP64 result except where that result sits within 2^-22 ulp of a
-// rounding boundary. Used where the factors arrive as floats or BF16 (mHC mixer rows, router
-// rows); kernels whose factors already sit in shared memory as doubles keep the FP64 FMA.
+// rounding boundary. Used where the factors arrive as floats or BF16 (mHC mixer rows and
+// stream expansion); kernels whose factors already sit in shared memory as doubles keep the FP64 FMA.
 #pragma once
 
 namespace g5b {
