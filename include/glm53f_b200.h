@@ -204,7 +204,9 @@ int g5b_op_mla(g5b_engine *e, int layer, const float *x, int T, int cached, floa
                int *sel_out, int *n_sel_out);
 /* glm53f_router (glm53f.h:340): idx/w [T][topk]. */
 int g5b_op_router(g5b_engine *e, int layer, const float *x, int T, int *idx, float *w);
-/* glm53f_moe (glm53f.h:348); with_shared = 0 gives glm53f_moe_routed (glm53f.h:344). */
+/* glm53f_moe (glm53f.h:348); with_shared = 0 gives glm53f_moe_routed (glm53f.h:344). Any host
+ * memory is accepted; when `out` is pinned and mapped (cudaHostAlloc / cudaHostRegister) the layer's
+ * last kernel writes it directly and the device-to-host copy is skipped. */
 int g5b_op_moe(g5b_engine *e, int layer, const float *x, int T, float *out, int with_shared);
 /* glm53f_mlp on a dense layer's gate/up/down (glm53f.h:352). */
 int g5b_op_mlp(g5b_engine *e, int layer, const float *x, int T, float *out);
