@@ -25,6 +25,30 @@ extern unsigned long long g_launches;
         ++::g5b::g_launches;                                                   \
     } while (0)
 
+// The same launch with programmatic stream serialization: the grid may be scheduled while the
+// kernel before it in the stream is still draining (once all of that kernel's CTAs have passed
+// pdl_trigger() or exited), so its launch latency and whatever it does before pdl_wait() overlap
+// that kernel's tail. Only for kernels that call pdl_wait() before they read anything an earlier
+// kernel wrote. (A kernel launched the ordinary way may call both: they do nothing then.)
+#define G5B_LAUNCH_PDL(kernel, grid, block, smem, strm_, ...)                                      \
+    do {                                                                                        \
+        cudaLaunchConfig_t cfg_{};                                                              \
+        cfg_.gridDim = (grid); cfg_.blockDim = (block);                                         \
+        cfg_.dynamicSmemBytes = (smem); cfg_.stream = (strm_);                                  \
+        cudaLaunchAttribute at_[1];                                                             \
+        at_[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                         \
+        at_[0].val.programmaticStreamSerializationAllowed = 1;                                  \
+        cfg_.attrs = at_; cfg_.numAttrs = 1;                                                    \
+        if (cudaLaunchKernelEx(&cfg_, kernel, __VA_ARGS__) != cudaSuccess) {                    \
+            cudaGetLastError();                                                                 \
+            kernel<<<(grid), (block), (smem), (strm_)>>>(__VA_ARGS__);                          \
+        }                                                                                       \
+        ++::g5b::g_launches;                                                                    \
+    } while (0)
+
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // 16-byte streaming load: weights are read once per token, so they bypass L1 allocation and
 // leave it to the activations that every row re-reads.
 __device__ __forceinline__ uint4 ld_stream16(const void *p)

@@ -24,6 +24,7 @@ constexpr int GEMV_WARPS = GEMV_THREADS / 32;
 template <int TT>
 __global__ void __launch_bounds__(GEMV_THREADS, TT == 1 ? 3 : 2) gemv_fast_kernel(const GemvBatch b)
 {
+    pdl_trigger();      // the KDA recurrence behind the input projections is launched early and waits inside
     int si = 0;
 #pragma unroll 1
     for (int i = 1; i < b.n; i++)

@@ -90,6 +90,10 @@ __global__ void __launch_bounds__(DS > 0 ? DS : 512) kda_core_kernel(const KdaAr
 #pragma unroll
         for (int i = 0; i < DS; i++) sreg[i] = S[(size_t)i * DS + d];
     }
+    // Everything above reads weights and this layer's own state. From here on the projections of the
+    // kernel before this one are read: when this grid was launched early (programmatic stream
+    // serialization), wait until that grid has completed and its results are visible.
+    pdl_wait();
     // (the low-rank rows requested above have landed by now, under the state's and the histories' loads)
     float z_own = 0.f, gb_own = 0.f;
     if (a.f_b) {
@@ -209,7 +213,9 @@ void kda_core(cudaStream_t st, float *o, const float *q, const float *k, const f
     if (s.D == 128) {
         static bool attr = false;
         if (!attr) { cudaFuncSetAttribute(kda_core_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 128 * (2 * 128 + 16)); attr = true; }
-        G5B_LAUNCH(kda_core_kernel<128>, grid, 128, smem, st, a);
+        // launched early: its CTAs load the 64 KB state and the histories while the projection kernel
+        // before it drains, and wait for that kernel inside (griddepcontrol.wait above)
+        G5B_LAUNCH_PDL(kda_core_kernel<128>, grid, dim3(128), smem, st, a);
     }
     else if (s.D == 64) G5B_LAUNCH(kda_core_kernel<64>, grid, 64, smem, st, a);
     else                G5B_LAUNCH(kda_core_kernel<0>, grid, ((s.D + 31) / 32) * 32, 0, st, a);
