@@ -413,6 +413,7 @@ __global__ void __cluster_dims__(HCC_CTAS, 1, 1) __launch_bounds__(HCC_THREADS) 
         }
     };
     load_piece(b, p_first);
+    pdl_wait();                  // the streams and y come from earlier kernels; the mixer rows do not
 
     for (int i = tid * 4; i < M * W; i += HCC_THREADS * 4)
         *reinterpret_cast<float4 *>(hs + i) = *reinterpret_cast<const float4 *>(ht + (size_t)(i / W) * E + d0 + (i % W));
@@ -578,7 +579,7 @@ void hc_pre_fused(cudaStream_t st, float *xn, float *post, float *comb, float *h
 {
     HcFused a{xn, post, comb, h, y_pending, static_cast<const uint16_t *>(w.fn.w), w.base, w.scale, norm_w, part,
               counters, M, E, iters, hc_eps, rms_eps};
-    if (hc_pre_cluster_takes(M, E)) G5B_LAUNCH(hc_pre_cluster_kernel, dim3(HCC_CTAS, T), HCC_THREADS, 0, st, a);
+    if (hc_pre_cluster_takes(M, E)) G5B_LAUNCH_PDL(hc_pre_cluster_kernel, dim3(HCC_CTAS, T), dim3(HCC_THREADS), 0, st, a);
     else                            G5B_LAUNCH(hc_pre_fused_kernel, dim3(HCF_SLICES, T), HC_THREADS, 0, st, a);
 }
 
