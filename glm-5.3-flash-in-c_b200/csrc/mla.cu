@@ -53,6 +53,8 @@ __global__ void __launch_bounds__(256) mla_store_kernel(
     const float *gate_raw, const float *k_norm_w, const float *k_norm_b, int cached, MlaShape s,
     const float *q_raw, float *q_inv, int T, const float *ape, int pool_here)
 {
+    pdl_trigger();
+    pdl_wait();
     __shared__ double red[32];
     if ((int)blockIdx.x >= T) {
         const int tq = blockIdx.x - T;
@@ -128,7 +130,7 @@ void mla_store(cudaStream_t st, void *latent, float *idx_state, const float *ct_
     const int pool0 = cached / s.KP;                                         // pools closed before this call
     const int pool1 = (cached + (s.batch ? 1 : T)) / s.KP;                   // pools closed after this call
     const int pool_here = ((T == 1 || s.batch) && pool1 > pool0) ? pool0 : -1;
-    G5B_LAUNCH(mla_store_kernel, 2 * T, 256, 0, st, latent, idx_state, ct_raw, kv_norm_w, wk_raw, gate_raw,
+    G5B_LAUNCH_PDL(mla_store_kernel, 2 * T, 256, 0, st, latent, idx_state, ct_raw, kv_norm_w, wk_raw, gate_raw,
                k_norm_w, k_norm_b, cached, s, q_raw, q_inv, T, ape, pool_here);
     if (pool1 > pool0 && pool_here < 0)
         G5B_LAUNCH(dsa_pool_kernel, pool1 - pool0, ((s.ID + 31) / 32) * 32, 0, st, idx_state, ape, pool0, s);
@@ -389,6 +391,8 @@ __global__ void __launch_bounds__(256) mla_score4_kernel(double *dsc, const doub
                                                          const int *nsel, int cached, int stride, MlaShape s,
                                                          double *stats, int *counters, int chunk)
 {
+    pdl_trigger();
+    pdl_wait();
     __shared__ double ptop[8], pz[8];
     __shared__ int is_last;
     const int h0 = blockIdx.y * SC_HEADS, t = blockIdx.z, p = pos_of(s, cached, t);
@@ -584,6 +588,8 @@ __global__ void __launch_bounds__(WS_THREADS) mla_wsum_chunk_kernel(
     double *part, const double *dsc, const double *stats, const void *latent, const int *sel, const int *nsel,
     int cached, int stride, int nchunks, MlaShape s)
 {
+    pdl_trigger();
+    pdl_wait();
     __shared__ double pj[WS_HEADS][WS_CHUNK];
     __shared__ int idx[WS_CHUNK];
     const int chunk = blockIdx.x, h0 = blockIdx.y * WS_HEADS, t = blockIdx.z, p = pos_of(s, cached, t);
@@ -633,6 +639,8 @@ __global__ void __launch_bounds__(WS_THREADS) mla_wsum_chunk_kernel(
 __global__ void __launch_bounds__(256) mla_wsum_reduce_kernel(float *cb, const double *part, int nchunks, int used,
                                                               int n, int KL)
 {
+    pdl_trigger();
+    pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;                // (t, h, column)
     if (i >= n) return;
     const int th = i / KL, col = i % KL;
@@ -656,7 +664,7 @@ void mla_attend(cudaStream_t st, float *cb, const double *qa, const void *latent
         // many tokens: fewer, longer CTAs, so that loading the four absorbed queries (16 KB) is a small
         // part of a CTA's work; one token: many short CTAs, for the latency
         const int chunk = T >= 8 ? 4 * SC_CHUNK : SC_CHUNK;
-        G5B_LAUNCH(mla_score4_kernel, dim3((nvis_max + chunk - 1) / chunk, s.H / SC_HEADS, T), 256, 0, st, dsc, qa,
+        G5B_LAUNCH_PDL(mla_score4_kernel, dim3((nvis_max + chunk - 1) / chunk, s.H / SC_HEADS, T), 256, 0, st, dsc, qa,
                    latent, sel, nsel, cached, stride, s, stats, counters, chunk);
     }
     else
@@ -677,12 +685,12 @@ void mla_attend(cudaStream_t st, float *cb, const double *qa, const void *latent
             lat0 = s.latent_bf16 ? static_cast<const void *>(static_cast<const uint16_t *>(latent) + (size_t)t0 * s.lat_seq)
                                  : static_cast<const void *>(static_cast<const float *>(latent) + (size_t)t0 * s.lat_seq);
         const int used = (((reach < stride) ? reach : stride) + WS_CHUNK - 1) / WS_CHUNK;
-        G5B_LAUNCH(mla_wsum_chunk_kernel, dim3(used, s.H / WS_HEADS, n), WS_THREADS, 0, st, part,
+        G5B_LAUNCH_PDL(mla_wsum_chunk_kernel, dim3(used, s.H / WS_HEADS, n), WS_THREADS, 0, st, part,
                    dsc + (size_t)t0 * s.H * stride, stats + (size_t)t0 * s.H * 2, lat0,
                    sel ? sel + (size_t)t0 * stride : nullptr, nsel ? nsel + t0 : nullptr, s.batch ? cached : cached + t0, stride, nchunks,
                    s);
         // chunks beyond `used` were not written: reduce over the used ones only
-        G5B_LAUNCH(mla_wsum_reduce_kernel, dim3((n * s.H * s.KL + 255) / 256), 256, 0, st,
+        G5B_LAUNCH_PDL(mla_wsum_reduce_kernel, dim3((n * s.H * s.KL + 255) / 256), 256, 0, st,
                    cb + (size_t)t0 * s.H * s.KL, part, nchunks, used, n * s.H * s.KL, s.KL);
     }
 }
@@ -691,6 +699,8 @@ void mla_attend(cudaStream_t st, float *cb, const double *qa, const void *latent
 // (glm53f_ops.c:904-909). A warp takes RW rows of one head.
 __global__ void __launch_bounds__(256) mla_vout_kernel(float *acc_out, const float *cb, const DMat kv_b, MlaShape s)
 {
+    pdl_trigger();
+    pdl_wait();
     const int h = blockIdx.y, t = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = (blockIdx.x * 8 + warp) * RW;
@@ -734,7 +744,7 @@ __global__ void mla_vout_any_kernel(float *acc_out, const float *cb, const DMat 
 void mla_vout(cudaStream_t st, float *acc_out, const float *cb, const DMat &kv_b, int T, const MlaShape &s)
 {
     const bool fast = s.KL % piece_elems(kv_b.dt) == 0 && (kv_b.dt != DT_FP8 || kv_b.bc % 16 == 0);
-    if (fast) G5B_LAUNCH(mla_vout_kernel, dim3((s.vh + 8 * RW - 1) / (8 * RW), s.H, T), 256, 0, st, acc_out, cb, kv_b, s);
+    if (fast) G5B_LAUNCH_PDL(mla_vout_kernel, dim3((s.vh + 8 * RW - 1) / (8 * RW), s.H, T), 256, 0, st, acc_out, cb, kv_b, s);
     else      G5B_LAUNCH(mla_vout_any_kernel, dim3((s.vh + 63) / 64, s.H, T), 64, 0, st, acc_out, cb, kv_b, s);
 }
 
