@@ -717,9 +717,9 @@ static void prefetch_beside(g5b_engine *e, const DMat &m)
 
 // Several products sharing (some of) their inputs: BF16 matrices with 8 or more tokens go to the
 // GEMM path, the rest to the GEMV kernel in one launch.
-static int proj_batch(g5b_engine *e, const GemvSeg *segs, int n, int T)
+static int proj_batch(g5b_engine *e, const GemvSeg *segs, int n, int T, bool early = false)
 {
-    if (T < 8 || !e->gemm) { gemv_batch(e->st, segs, n, T); return 0; }
+    if (T < 8 || !e->gemm) { gemv_batch(e->st, segs, n, T, early); return 0; }
     gemm_tokens_new_input(e->gemm);
     GemvSeg rest[GEMV_MAX_SEG];
     int nr = 0;
@@ -749,7 +749,7 @@ static int run_kda(g5b_engine *e, Layer &w, const float *x, int n, float *out, b
     float *lrf = e->klr, *lrg = e->klr + (size_t)CHUNK * D;
     GemvSeg a[6] = {make_seg(w.kq, x, E, e->kq, P), make_seg(w.kk, x, E, e->kk, P), make_seg(w.kv, x, E, e->kv, P),
                     make_seg(w.kb, x, E, e->kbraw, H), make_seg(w.f_a, x, E, lrf, D), make_seg(w.g_a, x, E, lrg, D)};
-    if (proj_batch(e, a, 6, n)) return -1;
+    if (proj_batch(e, a, 6, n, true)) return -1;
     // one new token: the recurrence kernel takes the two low-rank up-projections itself
     const bool lr_inside = n == 1 && !batch && w.f_b.dt == G5B_DT_BF16 && w.g_b.dt == G5B_DT_BF16 && (D == 64 || D == 128);
     const KdaLowRank lr{w.f_b.w, w.g_b.w, lrf, lrg};
@@ -794,13 +794,13 @@ static int run_mla(g5b_engine *e, Layer &w, const float *x, int n, int cached, f
     GemvSeg a[5] = {make_seg(w.q_a, x, E, e->mq_raw, c.q_lora), make_seg(w.kv_a, x, E, e->mct, c.kv_lora),
                     make_seg(w.wk, x, E, e->mwk, c.index_dim), make_seg(w.igate, x, E, e->mgate, c.index_dim),
                     make_seg(w.wproj, x, E, e->mwp, c.index_heads)};
-    if (proj_batch(e, a, 5, n)) return -1;
+    if (proj_batch(e, a, 5, n, true)) return -1;
     mla_store(e->st, lat, ist, e->mct, w.kv_a_norm, e->mwk, e->mgate, w.k_norm_w, w.k_norm_b,
               w.ape, e->mq_raw, e->minvq, n, cached, s);
     // q = q_b(RMSNorm(q_a x)) and the indexer query, the norm applied on the way into the product
     GemvSeg b[2] = {make_seg(w.q_b, e->mq_raw, c.q_lora, e->mq, c.mla_heads * c.qk_nope, e->minvq, w.q_a_norm),
                     make_seg(w.wq_b, e->mq_raw, c.q_lora, e->mqidx, c.index_heads * c.index_dim, e->minvq, w.q_a_norm)};
-    if (proj_batch(e, b, 2, n)) return -1;
+    if (proj_batch(e, b, 2, n, true)) return -1;
     // The indexer (pool scores, top-k, expansion: two latency-bound kernels) and the absorption of
     // W_k into the query need nothing from each other: the absorption runs on the side stream
     // meanwhile and the main stream takes it back before the scores.
@@ -817,7 +817,10 @@ static int run_mla(g5b_engine *e, Layer &w, const float *x, int n, int cached, f
     else if (join && cudaStreamWaitEvent(e->st, e->side_done, 0) != cudaSuccess) cudaStreamSynchronize(e->side);
     mla_attend(e->st, e->mcb, e->mqa, lat, e->msel, e->mnsel, e->mdsc, e->mpart, e->mstats, e->mcount, MLA_PART_TOKENS, n, cached, s);
     mla_vout(e->st, e->macc, e->mcb, w.kv_b, n, s);
-    gemv(e->st, w.mo, e->macc, c.mla_heads * c.v_head, out, E, n);
+    {
+        GemvSeg o = make_seg(w.mo, e->macc, c.mla_heads * c.v_head, out, E);
+        gemv_batch(e->st, &o, 1, n, true);
+    }
     return 0;
 }
 

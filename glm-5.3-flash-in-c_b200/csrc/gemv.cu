@@ -24,7 +24,8 @@ constexpr int GEMV_WARPS = GEMV_THREADS / 32;
 template <int TT>
 __global__ void __launch_bounds__(GEMV_THREADS, TT == 1 ? 3 : 2) gemv_fast_kernel(const GemvBatch b)
 {
-    pdl_trigger();      // the KDA recurrence behind the input projections is launched early and waits inside
+    pdl_trigger();      // a kernel launched early behind this one waits for this grid inside
+    pdl_wait();         // and so does this one when it was launched early itself
     int si = 0;
 #pragma unroll 1
     for (int i = 1; i < b.n; i++)
@@ -173,7 +174,7 @@ static bool seg_is_fast(const GemvSeg &s)
     return true;
 }
 
-void gemv_batch(cudaStream_t st, const GemvSeg *segs, int n, int T)
+void gemv_batch(cudaStream_t st, const GemvSeg *segs, int n, int T, bool early)
 {
     GemvBatch fast, any;
     fast.n = any.n = 0;
@@ -200,7 +201,8 @@ void gemv_batch(cudaStream_t st, const GemvSeg *segs, int n, int T)
         }
     }
     if (fast.n) {
-        if (T == 1)      G5B_LAUNCH(gemv_fast_kernel<1>, fb, GEMV_THREADS, 0, st, fast);
+        if (T == 1 && early) G5B_LAUNCH_PDL(gemv_fast_kernel<1>, fb, GEMV_THREADS, 0, st, fast);
+        else if (T == 1) G5B_LAUNCH(gemv_fast_kernel<1>, fb, GEMV_THREADS, 0, st, fast);
         else if (T == 2) G5B_LAUNCH(gemv_fast_kernel<2>, fb, GEMV_THREADS, 0, st, fast);
         else             G5B_LAUNCH(gemv_fast_kernel<4>, fb, GEMV_THREADS, 0, st, fast);
     }

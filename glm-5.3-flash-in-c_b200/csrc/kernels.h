@@ -38,7 +38,9 @@ GemvSeg make_seg(const DMat &m, const float *x, int ldx, float *y, int ldy,
                  const float *xinv = nullptr, const float *xw = nullptr);
 // Matrix restricted to rows [r0, r0+n) (FP8: r0 must lie on a scale-block row).
 DMat row_slice(const DMat &m, int r0, int n);
-void gemv_batch(cudaStream_t st, const GemvSeg *segs, int n, int T);
+// early: one token, launched with programmatic stream serialization (the grid may be scheduled while
+// the kernel before it drains; it waits for that kernel before it reads anything)
+void gemv_batch(cudaStream_t st, const GemvSeg *segs, int n, int T, bool early = false);
 inline void gemv(cudaStream_t st, const DMat &m, const float *x, int ldx, float *y, int ldy, int T,
                  const float *xinv = nullptr, const float *xw = nullptr)
 {
