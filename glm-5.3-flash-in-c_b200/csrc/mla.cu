@@ -199,6 +199,8 @@ __device__ __forceinline__ unsigned long long rank_key(float sc, int pool)
 __global__ void __launch_bounds__(TOPK_THREADS) dsa_topk_kernel(int *sel, int *nsel, const float *score,
                                                                 int cached, MlaShape s)
 {
+    pdl_trigger();
+    pdl_wait();
     __shared__ int hist[256];
     __shared__ unsigned long long prefix_s;
     __shared__ int want_s;
@@ -288,7 +290,7 @@ void dsa_select(cudaStream_t st, int *sel, int *nsel, const float *idx_state, co
         if (blocks > 296) blocks = 296;
         G5B_LAUNCH(dsa_score_kernel, dim3(blocks, T), DSA_WARPS * 32, smem, st, score, idx_state, qidx, wproj, cached, s);
     }
-    G5B_LAUNCH(dsa_topk_kernel, T, TOPK_THREADS, 0, st, sel, nsel, score, cached, s);
+    G5B_LAUNCH_PDL(dsa_topk_kernel, T, TOPK_THREADS, 0, st, sel, nsel, score, cached, s);
 }
 
 // ---------------------------------------------------------------- attention ----
