@@ -322,6 +322,15 @@ def time_decoder_layers(pkg, torch, steps: int, device: int = 0):
             assert L.g5b_time_op(eng.handle, b"layer", layer, hd.data_ptr(), 1, cached, hd.data_ptr(), k, FLUSH_BYTES,
                                  C.byref(tot), each.ctypes.data) == 0, L.g5b_last_error()
         out[name] = {"ms": float(np.mean(each[:steps])), "finite": bool(torch.isfinite(hd).all().item())}
+    # both layers in one pass (the second layer's first mHC site applies the first layer's pending
+    # stream expansion inside its own launch, as in the whole model)
+    hd = h.clone()
+    each = np.zeros(max(steps, 3), np.float32); tot = C.c_float(0)
+    for k in (3, steps):
+        hd.copy_(h)
+        assert L.g5b_time_op(eng.handle, b"layers", 0, hd.data_ptr(), 1, cap - 1, hd.data_ptr(), k, FLUSH_BYTES,
+                             C.byref(tot), each.ctypes.data) == 0, L.g5b_last_error()
+    out["kda_moe_then_mla_moe_layers"] = {"ms": float(np.mean(each[:steps])), "finite": bool(torch.isfinite(hd).all().item())}
     # the same two layers advancing 64 sequences by one token each (state and caches per sequence,
     # weights read once per batch)
     h64 = torch.from_numpy(rng.standard_normal((64, c.hc_mult, c.hidden)).astype(np.float32)).cuda()

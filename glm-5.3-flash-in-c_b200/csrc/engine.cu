@@ -1478,7 +1478,7 @@ extern "C" int g5b_shortconv_host(float *y, const float *x, const float *w, floa
 }
 
 // ------------------------------------------------------------------------ timing ----
-// Time `iters` launches of one op ("moe", "kda", "mla", "layer", "layer_batch", "hc_site", "hc_site_post") between CUDA events on the
+// Time `iters` launches of one op ("moe", "kda", "mla", "layer", "layers", "layer_batch", "hc_site", "hc_site_post") between CUDA events on the
 // engine's stream; before each launch `flush_bytes` of scratch are overwritten (0 = no flush) so
 // that weights come from HBM, not from L2. ms_each receives the per-launch times. When the
 // engine's "profile" option is on, the per-phase times of the MoE op accumulate in the profile.
@@ -1507,6 +1507,12 @@ extern "C" int g5b_time_op(g5b_engine *e, const char *op, int layer, const float
         else if (!strcmp(op, "kda"))   rc = g5b_dev_kda(e, layer, x_dev, T, out_dev);
         else if (!strcmp(op, "mla"))   rc = g5b_dev_mla(e, layer, x_dev, T, cached, out_dev);
         else if (!strcmp(op, "layer")) rc = g5b_dev_decoder_layer(e, layer, out_dev, T, cached);
+        else if (!strcmp(op, "layers")) {                  // every layer of the engine in order, one pass
+            rc = 0;
+            for (int l = 0; l < e->c.n_layers && !rc; l++) rc = run_layer(e, l, out_dev, T, cached);
+            if (rc) e->post_h = nullptr;
+            flush_hc_post(e);
+        }
         else if (!strcmp(op, "layer_batch")) {             // T sequences, one new position each
             if (T > e->n_seq || T > CHUNK) rc = fail("layer_batch takes at most %d sequences", e->n_seq < CHUNK ? e->n_seq : CHUNK);
             else {
