@@ -427,9 +427,8 @@ def main():
                     help="run only the timing of one mHC site of a full-size layer and print it (a small case for ncu)")
     ap.add_argument("--no-attention-layers", action="store_true",
                     help="skip the KDA / MLA single-layer timings reported under 'extra'")
-    ap.add_argument("--stream-warps", type=int, default=0, help="consumer warps of the streamed CUDA-core kernels (8/16)")
     ap.add_argument("--expert-path", type=int, default=-1,
-                    help="batch-1 expert kernels: 0 register-streaming, 1 bulk-copy + CUDA cores, 2 bulk-copy + tensor cores, 3 whole layer in one kernel (default)")
+                    help="batch-1 expert kernels: 0 register-streaming, 1 tensor-core kernels as three launches, 2 whole layer in one kernel (default)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -462,10 +461,8 @@ def main():
         print(json.dumps(res), flush=True)
         return
     opts = {}
-    if args.stream_warps:
-        opts["stream_warps"] = args.stream_warps
     if args.expert_path >= 0:
-        opts["stream_experts"] = args.expert_path
+        opts["expert_path"] = args.expert_path
     spec, trunk, eng = synth.build_moe_layer_engine(SEED, n_experts=args.experts, device=local, options=opts)
     sampler = ClockSampler(local)
 

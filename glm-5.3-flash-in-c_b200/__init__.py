@@ -98,6 +98,7 @@ def lib() -> C.CDLL:
     L.g5b_engine_ep_handle_bytes.restype = C.c_size_t
     L.g5b_engine_ep_export.argtypes = [C.c_void_p, C.c_void_p]
     L.g5b_engine_ep_connect.argtypes = [C.c_void_p, C.c_void_p]
+    L.g5b_engine_ep_resync.argtypes = [C.c_void_p]
     L.g5b_engine_use_sequence.argtypes = [C.c_void_p, C.c_int]
     L.g5b_engine_decode_batch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
     L.g5b_engine_set_option.argtypes = [C.c_void_p, C.c_char_p, C.c_int]
@@ -346,6 +347,11 @@ class Engine(FlatModel):
         blob = b"".join(handles)
         if self.L.g5b_engine_ep_connect(self.handle, blob) != 0:
             self._err("ep_connect")
+
+    def ep_resync(self):
+        """Re-align the ranks' step count after a failed step (collective; barriers are the caller's)."""
+        if self.L.g5b_engine_ep_resync(self.handle) != 0:
+            self._err("ep_resync")
 
     def decode_greedy(self, first: int, n: int):
         out = np.zeros(n, np.int32)

@@ -142,4 +142,28 @@ __device__ __forceinline__ void st_release_sys(unsigned long long *p, unsigned l
     asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 
+
+__device__ __forceinline__ unsigned long long global_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Wait until the 64-bit word another GPU publishes reaches `want`. The limit is wall-clock time
+// (the ranks are separate host processes: ordinary host skew must not look like a lost peer), with
+// an iteration cap behind it in case the timer does not advance. False when the wait ran out.
+__device__ __forceinline__ bool wait_word_sys(const unsigned long long *p, unsigned long long want,
+                                              unsigned long long limit_ns)
+{
+    if (ld_acquire_sys(p) >= want) return true;
+    const unsigned long long t0 = global_ns();
+    for (long long i = 0; i < (1ll << 28); i++) {
+        if (ld_acquire_sys(p) >= want) return true;
+        if (global_ns() - t0 > limit_ns) return false;
+        __nanosleep(100);
+    }
+    return false;
+}
+
 }  // namespace g5b

@@ -94,7 +94,9 @@ struct g5b_engine {
     std::vector<void *> ep_standins;             // local stand-ins for peers (option ep_loopback)
     unsigned long long ep_step = 0;
     int *ep_arrive = nullptr;
-    int latent_bf16 = 0, profile = 0, partial = 0, stream_experts = 3, stream_warps = 8;
+    int ep_wait_ms = 5000;                       // wall-clock limit of a wait for the other ranks (option "ep_wait_ms")
+    bool dirty = false;                          // a call failed half-way: session state is undefined until reset
+    int latent_bf16 = 0, profile = 0, partial = 0, expert_path = 2;
     unsigned long long *grid_sync = nullptr, grid_launches = 0;
     int *counter = nullptr, *tile_done = nullptr, *err_dev = nullptr;
     volatile int *err_host = nullptr;   // mapped host memory: kernels record a timed-out wait here
@@ -288,15 +290,15 @@ extern "C" int g5b_engine_set_option(g5b_engine *e, const char *name, int value)
         return 0;
     }
     if (!strcmp(name, "ep_loopback")) return value ? ep_loopback(e) : 0;
-    if (!strcmp(name, "stream_experts")) {       // batch-1 experts: 0 register kernels, 1 streamed CUDA-core,
-                                                 // 2 streamed tensor-core, 3 the whole layer as one kernel
-        if (value < 0 || value > 3) return fail("stream_experts is 0, 1, 2 or 3");
-        e->stream_experts = value;
+    if (!strcmp(name, "ep_wait_ms")) {
+        if (value < 1 || value > 600000) return fail("ep_wait_ms is 1..600000");
+        e->ep_wait_ms = value;
         return 0;
     }
-    if (!strcmp(name, "stream_warps")) {
-        if (value != 8 && value != 16) return fail("stream_warps is 8 or 16");
-        e->stream_warps = value;
+    if (!strcmp(name, "expert_path")) {          // batch-1 experts: 0 register kernels, 1 tensor-core kernels (router,
+                                                 // gate/up, down as three launches), 2 the whole layer as one kernel
+        if (value < 0 || value > 2) return fail("expert_path is 0, 1 or 2");
+        e->expert_path = value;
         return 0;
     }
     return fail("unknown option %s", name);
@@ -608,9 +610,9 @@ static int run_moe(g5b_engine *e, Layer &w, const float *x, int n, float *out, i
     const bool one_gpu_decode = e->ep_size == 1 && (shared_in_plan || !with_shared);
     prof_mark(e, 0);
     const bool ep_decode = e->ep_size > 1 && (shared_in_plan || !with_shared);
-    if (e->stream_experts == 3 && (one_gpu_decode || ep_decode) && moe_decode_supported(s, n)) {
+    if (e->expert_path == 2 && (one_gpu_decode || ep_decode) && moe_decode_supported(s, n)) {
         DecodeEp ep{e->ep_rank, e->ep_size, e->ep_peers_dev, EP_FLAG_BYTES + (size_t)((e->ep_step + 1) & 1) * e->ep_rows_bytes,
-                    e->ep_step + 1, e->ep_arrive};
+                    e->ep_step + 1, e->ep_arrive, (unsigned long long)e->ep_wait_ms * 1000000ull};
         if (moe_decode(e->st, out, x, w.router.w, w.router.dt, w.bias, w.table_dev, e->rscore, e->ridx, e->rw, e->act,
                        e->contrib, s, with_shared, e->grid_sync, &e->grid_launches, e->tile_done, e->err_dev,
                        ep_decode ? &ep : nullptr) == 0) {
@@ -628,11 +630,11 @@ static int run_moe(g5b_engine *e, Layer &w, const float *x, int n, float *out, i
         ++e->ep_step;
         EpExchange x{e->contrib, e->plan, e->ep_peers_dev, e->ep_rank, e->ep_size, n, c.topk, c.hidden, with_shared,
                      EP_FLAG_BYTES + (size_t)(e->ep_step & 1) * e->ep_rows_bytes, e->ep_step, e->ep_arrive, e->rw,
-                     out, c.hidden, e->err_dev};
+                     out, c.hidden, e->err_dev, (unsigned long long)e->ep_wait_ms * 1000000ull};
         const int want = (int)(((size_t)n * c.hidden + 255) / 256);
         ep_exchange_combine(e->st, x, want < 8 ? 8 : want > 148 ? 148 : want);
     };
-    if (e->ep_size > 1 && e->stream_experts >= 2 && (shared_in_plan || !with_shared) && moe_mma_supported(s, n)) {
+    if (e->ep_size > 1 && e->expert_path >= 1 && (shared_in_plan || !with_shared) && moe_mma_supported(s, n)) {
         // batch 1 across ranks: the tensor-core kernels on this rank's picks, contributions only
         moe_mma_gateup(e->st, e->act, x, w.table_dev, e->plan, s, e->err_dev);
         prof_mark(e, 2);
@@ -643,7 +645,7 @@ static int run_moe(g5b_engine *e, Layer &w, const float *x, int n, float *out, i
         prof_collect(e, 4);
         return 0;
     }
-    if (e->stream_experts == 2 && one_gpu_decode && moe_mma_supported(s, n)) {
+    if (e->expert_path == 1 && one_gpu_decode && moe_mma_supported(s, n)) {
         moe_mma_gateup(e->st, e->act, x, w.table_dev, e->plan, s, e->err_dev);
         prof_mark(e, 2);
         moe_mma_down(e->st, out, e->contrib, e->act, e->rw, w.table_dev, e->plan, s, with_shared, e->tile_done, e->err_dev);
@@ -652,17 +654,7 @@ static int run_moe(g5b_engine *e, Layer &w, const float *x, int n, float *out, i
         prof_collect(e, 4);
         return 0;
     }
-    if (e->stream_experts && one_gpu_decode && moe_stream_supported(s, n)) {
-        moe_stream_gateup(e->st, e->act, x, w.table_dev, e->plan, s, e->err_dev, e->stream_warps);
-        prof_mark(e, 2);
-        moe_stream_down(e->st, out, e->contrib, e->act, e->rw, w.table_dev, e->plan, s, with_shared, e->tile_done,
-                        e->err_dev, e->stream_warps);
-        prof_mark(e, 3);
-        prof_mark(e, 4);
-        prof_collect(e, 4);
-        return 0;
-    }
-    if (e->stream_experts >= 2 && (shared_in_plan || !with_shared) && moe_mma_batch_supported(s, n)) {
+    if (e->expert_path >= 1 && (shared_in_plan || !with_shared) && moe_mma_batch_supported(s, n)) {
         // batches: the tensor-core pipeline with four tokens per weight stage
         moe_mma_batch_gateup(e->st, e->act, e->xterms, e->xinv, x, c.hidden, w.table_dev, e->plan, n, s, e->err_dev);
         prof_mark(e, 2);
@@ -958,6 +950,7 @@ extern "C" int g5b_engine_forward(g5b_engine *e, const int *ids, int T, float *l
 {
     if (!e->finalized) return fail("forward before finalize");
     CU(cudaSetDevice(e->device));
+    if (e->dirty) return fail("an earlier call failed half-way: reset the engine (g5b_engine_reset) first");
     if (T < 1) return fail("forward needs at least one token");
     if (e->cached + T > e->cap)
         return fail("%d cached + %d new positions exceed the session capacity %d", e->cached, T, e->cap);
@@ -965,10 +958,13 @@ extern "C" int g5b_engine_forward(g5b_engine *e, const int *ids, int T, float *l
         if (ids[t] < 0 || ids[t] >= e->c.vocab) return fail("token id %d outside the vocabulary", ids[t]);
     if (ensure_ids(e, (size_t)T)) return -1;
     CU(cudaMemcpyAsync(e->ids_dev, ids, (size_t)T * 4, cudaMemcpyHostToDevice, e->st));
+    // from here on the session state is being advanced: any failure leaves it undefined
+    e->dirty = true;
     if (forward_device(e, e->ids_dev, T, argmax_all != nullptr, logits, argmax_all)) return -1;
     CU(cudaStreamSynchronize(e->st));
     CU(cudaGetLastError());
     if (check_device_error(e)) return -1;
+    e->dirty = false;
     e->cached += T;
     return 0;
 }
@@ -979,19 +975,29 @@ extern "C" int g5b_engine_decode_greedy(g5b_engine *e, int first, int n, int *ou
 {
     if (!e->finalized) return fail("decode before finalize");
     CU(cudaSetDevice(e->device));
+    if (e->dirty) return fail("an earlier call failed half-way: reset the engine (g5b_engine_reset) first");
     if (n < 1 || e->cached + n > e->cap) return fail("decode of %d tokens exceeds the session capacity", n);
     if (first < 0 || first >= e->c.vocab) return fail("token id %d outside the vocabulary", first);
     if (ensure_ids(e, (size_t)n + 1)) return -1;
     CU(cudaMemcpyAsync(e->ids_dev, &first, 4, cudaMemcpyHostToDevice, e->st));
+    // The position count is committed only once every step is known to have succeeded; until then
+    // the session is marked undefined, so that a failed call cannot be continued by accident.
+    const int start = e->cached;
+    e->dirty = true;
     for (int i = 0; i < n; i++) {
-        if (forward_device(e, e->ids_dev + i, 1, false, nullptr, nullptr)) return -1;
+        e->cached = start + i;
+        const int rc = forward_device(e, e->ids_dev + i, 1, false, nullptr, nullptr);
+        if (rc) { e->cached = start; return -1; }
         CU(cudaMemcpyAsync(e->ids_dev + i + 1, e->am_out, 4, cudaMemcpyDeviceToDevice, e->st));
-        e->cached += 1;
     }
+    e->cached = start;
     CU(cudaMemcpyAsync(out, e->ids_dev + 1, (size_t)n * 4, cudaMemcpyDeviceToHost, e->st));
     CU(cudaStreamSynchronize(e->st));
     CU(cudaGetLastError());
-    return check_device_error(e);
+    if (check_device_error(e)) return -1;
+    e->dirty = false;
+    e->cached = start + n;
+    return 0;
 }
 
 extern "C" void g5b_engine_reset(g5b_engine *e)
@@ -1004,6 +1010,8 @@ extern "C" void g5b_engine_reset(g5b_engine *e)
         if (w.kda_state) cudaMemsetAsync(w.kda_state, 0, (size_t)e->n_seq * e->kda_seq * 4, e->st);
     cudaStreamSynchronize(e->st);
     e->cached = 0;
+    e->dirty = false;
+    e->post_h = nullptr;
     for (auto &v : e->cached_seq) v = 0;
 }
 
@@ -1026,6 +1034,7 @@ extern "C" int g5b_engine_decode_batch(g5b_engine *e, const int *ids, float *log
 {
     if (!e || !e->finalized) return fail("decode_batch before finalize");
     CU(cudaSetDevice(e->device));
+    if (e->dirty) return fail("an earlier call failed half-way: reset the engine (g5b_engine_reset) first");
     const int S = e->n_seq;
     e->cached_seq[(size_t)e->cur_seq] = e->cached;
     for (int q = 1; q < S; q++)
@@ -1040,12 +1049,14 @@ extern "C" int g5b_engine_decode_batch(g5b_engine *e, const int *ids, float *log
     CU(cudaMemcpyAsync(e->ids_dev, ids, (size_t)S * 4, cudaMemcpyHostToDevice, e->st));
     const int keep = e->cached;
     e->cached = pos;
+    e->dirty = true;
     const int rc = forward_device(e, e->ids_dev, S, true, logits, argmax, true);
     e->cached = keep;
     if (rc) return -1;
     CU(cudaStreamSynchronize(e->st));
     CU(cudaGetLastError());
     if (check_device_error(e)) return -1;
+    e->dirty = false;
     for (auto &v : e->cached_seq) v = pos + 1;
     e->cached = pos + 1;
     return 0;
@@ -1149,7 +1160,13 @@ struct Staged {
     }
 };
 
-// Ops accept any T: the host entry points walk it in CHUNK-sized pieces.
+// Ops accept any T >= 1: the host entry points walk it in CHUNK-sized pieces.
+static int check_op(g5b_engine *e, int layer, int T)
+{
+    if (T < 1) return fail("ops take at least one position, got %d", T);
+    return check_layer(e, layer, 1);
+}
+
 #define FOR_CHUNKS(T) for (int t0 = 0, n_ = 0; (n_ = (T) - t0 < CHUNK ? (T) - t0 : CHUNK), t0 < (T); t0 += CHUNK)
 
 // Host buffers through the engine's own staging rows (no allocation per call): copy a piece in,
@@ -1173,7 +1190,10 @@ static int host_op(g5b_engine *e, const float *x, int T, float *out, F &&run, bo
     }
     FOR_CHUNKS(T) {
         CU(cudaMemcpyAsync(e->xn, x + t0 * E, n_ * E * 4, cudaMemcpyHostToDevice, e->st));
-        if (run(e->xn, n_, out_dev ? out_dev + t0 * E : e->y, t0)) return -1;
+        if (run(e->xn, n_, out_dev ? out_dev + t0 * E : e->y, t0)) {
+            cudaStreamSynchronize(e->st);            // copies on the caller's buffers must not outlive the call
+            return -1;
+        }
         if (!out_dev) CU(cudaMemcpyAsync(out + t0 * E, e->y, n_ * E * 4, cudaMemcpyDeviceToHost, e->st));
     }
     CU(cudaStreamSynchronize(e->st));
@@ -1183,7 +1203,7 @@ static int host_op(g5b_engine *e, const float *x, int T, float *out, F &&run, bo
 
 extern "C" int g5b_op_moe(g5b_engine *e, int layer, const float *x, int T, float *out, int with_shared)
 {
-    if (check_layer(e, layer, 1)) return -1;
+    if (check_op(e, layer, T)) return -1;
     if (e->L[layer].is_dense) return fail("layer %d has a dense MLP", layer);
     return host_op(e, x, T, out, [&](const float *xd, int n, float *od, int) {
         return run_moe(e, e->L[layer], xd, n, od, with_shared);
@@ -1192,7 +1212,7 @@ extern "C" int g5b_op_moe(g5b_engine *e, int layer, const float *x, int T, float
 
 extern "C" int g5b_op_router(g5b_engine *e, int layer, const float *x, int T, int *idx, float *w)
 {
-    if (check_layer(e, layer, 1)) return -1;
+    if (check_op(e, layer, T)) return -1;
     if (e->L[layer].is_dense) return fail("layer %d has a dense MLP", layer);
     const size_t E = e->c.hidden, K = e->c.topk;
     Layer &lw = e->L[layer];
@@ -1214,7 +1234,7 @@ extern "C" int g5b_op_router(g5b_engine *e, int layer, const float *x, int T, in
 
 extern "C" int g5b_op_mlp(g5b_engine *e, int layer, const float *x, int T, float *out)
 {
-    if (check_layer(e, layer, 1)) return -1;
+    if (check_op(e, layer, T)) return -1;
     if (!e->L[layer].is_dense) return fail("layer %d is a MoE layer", layer);
     return host_op(e, x, T, out, [&](const float *xd, int n, float *od, int) {
         return run_mlp(e, e->L[layer], xd, n, od);
@@ -1223,7 +1243,7 @@ extern "C" int g5b_op_mlp(g5b_engine *e, int layer, const float *x, int T, float
 
 extern "C" int g5b_op_kda(g5b_engine *e, int layer, const float *x, int T, float *out)
 {
-    if (check_layer(e, layer, 1)) return -1;
+    if (check_op(e, layer, T)) return -1;
     if (e->L[layer].is_mla) return fail("layer %d is an MLA layer", layer);
     return host_op(e, x, T, out, [&](const float *xd, int n, float *od, int) {
         return run_kda(e, e->L[layer], xd, n, od);
@@ -1233,7 +1253,7 @@ extern "C" int g5b_op_kda(g5b_engine *e, int layer, const float *x, int T, float
 extern "C" int g5b_op_mla(g5b_engine *e, int layer, const float *x, int T, int cached, float *out,
                           int *sel_out, int *n_sel_out)
 {
-    if (check_layer(e, layer, 1)) return -1;
+    if (check_op(e, layer, T)) return -1;
     if (!e->L[layer].is_mla) return fail("layer %d is a KDA layer", layer);
     int last_n = 0;
     if (host_op(e, x, T, out, [&](const float *xd, int n, float *od, int t0) {
@@ -1257,7 +1277,7 @@ extern "C" int g5b_op_mla(g5b_engine *e, int layer, const float *x, int T, int c
 extern "C" int g5b_op_hc_pre(g5b_engine *e, int layer, int site, const float *h, int T, float *x,
                              float *post, float *comb)
 {
-    if (check_layer(e, layer, 1)) return -1;
+    if (check_op(e, layer, T)) return -1;
     const size_t E = e->c.hidden, M = e->c.hc_mult;
     Staged s{e};
     float *hd = s.in(h, (size_t)T * M * E);
@@ -1276,7 +1296,7 @@ extern "C" int g5b_op_hc_pre(g5b_engine *e, int layer, int site, const float *h,
 extern "C" int g5b_op_hc_post(g5b_engine *e, float *h, const float *y, const float *post,
                               const float *comb, int T)
 {
-    if (check_layer(e, 0, 1)) return -1;
+    if (check_op(e, 0, T)) return -1;
     const size_t E = e->c.hidden, M = e->c.hc_mult;
     Staged s{e};
     float *hd = s.in(h, (size_t)T * M * E), *yd = s.in(y, (size_t)T * E), *pd = s.in(post, (size_t)T * M),
@@ -1288,7 +1308,7 @@ extern "C" int g5b_op_hc_post(g5b_engine *e, float *h, const float *y, const flo
 
 extern "C" int g5b_op_decoder_layer(g5b_engine *e, int layer, float *h, int T, int cached)
 {
-    if (check_layer(e, layer, 1)) return -1;
+    if (check_op(e, layer, T)) return -1;
     const size_t E = e->c.hidden, M = e->c.hc_mult;
     Staged s{e};
     float *hd = s.in(h, (size_t)T * M * E);
@@ -1316,6 +1336,7 @@ static DMat *find_mat(g5b_engine *e, const char *name)
 extern "C" int g5b_op_matvec(g5b_engine *e, const char *name, const float *x, int T, float *y)
 {
     CU(cudaSetDevice(e->device));
+    if (T < 1) return fail("ops take at least one position, got %d", T);
     DMat *m = find_mat(e, name);
     if (!m) return fail("no loaded matrix named %s", name);
     Staged s{e};
@@ -1616,6 +1637,25 @@ extern "C" int g5b_engine_ep_connect(g5b_engine *e, const void *all_handles)
         peers[r] = p;
     }
     return ep_publish_peers(e, peers);
+}
+
+// Re-align the ranks after a step that failed on some of them. Host-side and collective: every rank
+// calls it, and the caller's own transport must order the calls so that no rank has a MoE kernel in
+// flight and none starts one before all have returned (a barrier before and one after). It forgets
+// every published step word of this rank's region and restarts the step count at zero.
+extern "C" int g5b_engine_ep_resync(g5b_engine *e)
+{
+    if (!e) return fail("null engine");
+    if (e->ep_size == 1) return 0;
+    if (!e->ep_connected) return fail("resync before the ranks are connected");
+    CU(cudaSetDevice(e->device));
+    CU(cudaStreamSynchronize(e->st));
+    CU(cudaMemsetAsync(e->ep_region, 0, EP_FLAG_BYTES, e->st));
+    CU(cudaMemsetAsync(e->ep_arrive, 0, sizeof(int), e->st));
+    CU(cudaStreamSynchronize(e->st));
+    if (e->err_host) *e->err_host = 0;
+    e->ep_step = 0;
+    return 0;
 }
 
 // Stand-in peers in this GPU's own memory that nobody ever writes: lets one GPU exercise the

@@ -16,14 +16,15 @@
 //
 // Two exchange buffers alternate by step parity: a rank can be at most one step ahead of a peer
 // (its next combine needs that peer's next word), so rows of step s+1 never land in a buffer
-// that a slower peer still reads for step s. A wait that runs out sets the error word in mapped
-// host memory and the CTA returns without combining; nothing is left in flight.
+// that a slower peer still reads for step s. The wait is limited in wall-clock time (engine option
+// "ep_wait_ms", default 5 s): a wait that runs out sets the error word in mapped host memory and
+// the CTA returns without combining; nothing is left in flight. After such a failure the ranks
+// no longer agree on the step number (this rank counted the step, a slower peer may still
+// complete it), so the group must be re-aligned with g5b_engine_ep_resync before its next step.
 #include "kernels.h"
 #include "common.cuh"
 
 namespace g5b {
-
-constexpr int EP_SPIN_LIMIT = 1 << 21;         // about a second at the poll interval below
 
 __global__ void __launch_bounds__(256) ep_exchange_combine_kernel(const EpExchange a)
 {
@@ -64,11 +65,7 @@ __global__ void __launch_bounds__(256) ep_exchange_combine_kernel(const EpExchan
     bool seen = true;
     if (tid < a.size) {
         const unsigned long long *mine = reinterpret_cast<const unsigned long long *>(a.peers[a.rank]);
-        seen = false;
-        for (int i = 0; i < EP_SPIN_LIMIT && !seen; i++) {
-            seen = ld_acquire_sys(mine + tid) >= a.step;
-            if (!seen) __nanosleep(100);
-        }
+        seen = wait_word_sys(mine + tid, a.step, a.wait_ns);
         if (!seen) atomicExch(a.err, 20 + tid);                 // which rank never delivered
     }
     if (!__syncthreads_and(seen)) return;

@@ -211,8 +211,8 @@ void kda_core(cudaStream_t st, float *o, const float *q, const float *k, const f
     const dim3 grid(s.H, n_seq < 1 ? 1 : n_seq);
     const size_t smem = fused ? (size_t)2 * s.D * (2 * s.D + 16) : 0;
     if (s.D == 128) {
-        static bool attr = false;
-        if (!attr) { cudaFuncSetAttribute(kda_core_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 128 * (2 * 128 + 16)); attr = true; }
+        static SmemGrant grant;
+        if (!dev_opt_in_smem((const void *)kda_core_kernel<128>, 2 * 128 * (2 * 128 + 16), grant)) return;
         // launched early: its CTAs load the 64 KB state and the histories while the projection kernel
         // before it drains, and wait for that kernel inside (griddepcontrol.wait above)
         G5B_LAUNCH_PDL(kda_core_kernel<128>, grid, dim3(128), smem, st, a);

@@ -19,6 +19,19 @@ struct DMat {
     size_t bytes() const { return (size_t)rows * cols * (dt == 0 ? 4 : dt == 1 ? 2 : 1); }
 };
 
+// ---- device_info.cu -----------------------------------------------------------------------
+// Facts about, and one-time kernel set-up on, the device that is current at the call. Nothing is
+// cached across devices: a process may hold engines on several GPUs.
+constexpr int G5B_MAX_DEVICES = 64;
+struct SmemGrant { size_t bytes[G5B_MAX_DEVICES] = {}; };   // per kernel: what each device has granted
+int  dev_now();
+int  dev_sms();
+bool dev_cooperative();
+// Opt `kernel` into `bytes` of dynamic shared memory on the current device (again if a later call
+// asks for more). False, with the message kept for g5b_last_error, when the device refuses.
+bool dev_opt_in_smem(const void *kernel, size_t bytes, SmemGrant &grant);
+void set_last_error(const char *msg);
+
 // ---- gemv.cu ------------------------------------------------------------------------------
 // One product y[T][rows] = W (xform(x))[T][cols] of a batch launched as a single grid.
 struct GemvSeg {
@@ -121,10 +134,6 @@ struct MoeShape {
 void router_plan(cudaStream_t st, int *idx, float *w, float *score, const float *x, int ldx, const void *gate,
                  int gate_dt, const float *bias, int T, const MoeShape &s, const MoePlan &p, int with_shared,
                  int *counter);
-// Batch-1 experts streamed through shared memory by the bulk-copy engine (moe_stream.cu).
-bool moe_stream_supported(const MoeShape &s, int T);
-void moe_stream_gateup(cudaStream_t st, float *act, const float *x, const ExpertW *experts, const MoePlan &p,
-                       const MoeShape &s, int *err, int warps);
 // Batch-1 experts multiplied by the tensor cores from their FP8 codes (moe_mma.cu); act_terms holds
 // the SwiGLU output split into two F16 terms per element, [pairs][2][I].
 bool moe_mma_supported(const MoeShape &s, int T);
@@ -153,15 +162,12 @@ struct DecodeEp {
     size_t rows_off;
     unsigned long long step;
     int *arrive;
+    unsigned long long wait_ns;    // wall-clock limit of the wait for the other ranks' step words
 };
 int moe_decode(cudaStream_t st, float *out, const float *x, const void *gate, int gate_dt, const float *bias,
                const ExpertW *experts, float *score, int *idx, float *w, void *act, float *contrib,
                const MoeShape &s, int with_shared, unsigned long long *sync, unsigned long long *launches,
                int *tile_done, int *err, const DecodeEp *ep = nullptr);
-// out == nullptr: contributions only (the caller combines, e.g. after an expert-parallel exchange).
-void moe_stream_down(cudaStream_t st, float *out, float *contrib, const float *act, const float *w,
-                     const ExpertW *experts, const MoePlan &p, const MoeShape &s, int with_shared,
-                     int *tile_done, int *err, int warps);
 void moe_gateup(cudaStream_t st, float *act, const float *x, int ldx, const ExpertW *experts,
                 const MoePlan &p, int T, const MoeShape &s);
 void moe_down(cudaStream_t st, float *contrib, const float *act, const ExpertW *experts,
@@ -184,6 +190,7 @@ struct EpExchange {
     const float *w;                // router weights [T][K]
     float *out; int ldo;
     int *err;
+    unsigned long long wait_ns;    // wall-clock limit of the wait for the other ranks' step words
 };
 void ep_exchange_combine(cudaStream_t st, const EpExchange &a, int ctas);
 

@@ -21,10 +21,9 @@
 // Arithmetic is that of moe_mma.cu (tensor-core products of E4M3 codes with the activation split
 // into two F16 terms); selection and combine follow the reference (src/core/glm53f_ops.c:945-976,
 // 1329-1340).
-#include <stdlib.h>
-
 #include "kernels.h"
 #include "mma_stage.cuh"
+#include "stage_timers.cuh"
 
 namespace g5b {
 
@@ -55,6 +54,7 @@ struct DecodeArgs {
     size_t rows_off;
     unsigned long long ep_step;
     int *ep_arrive;
+    unsigned long long ep_wait_ns;
 };
 
 __device__ __forceinline__ unsigned long long ld_acquire(const unsigned long long *p)
@@ -90,26 +90,10 @@ __device__ __forceinline__ uint32_t choice_key(float v)
     return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
-#ifdef G5B_STAGE_TIMERS
-__device__ unsigned long long g_decode_timers[160][16];
-#define DT_MARK(k) do { if (ctid == 0 && blockIdx.x < 160) g_decode_timers[blockIdx.x][k] = clock64() - t_begin; } while (0)
-#define DT_MARK_P(k) do { if (lane == 0 && blockIdx.x < 160) g_decode_timers[blockIdx.x][k] = clock64() - t_begin; } while (0)
-#else
-#define DT_MARK(k) do { } while (0)
-#define DT_MARK_P(k) do { } while (0)
-#endif
-
 __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeArgs a)
 {
     const float act_sc = act_term_scale(a.limit), act_inv = 1.0f / act_sc;   // powers of two
-#ifdef G5B_STAGE_TIMERS
-    const long long t_begin = clock64();
-    if (threadIdx.x == 0 && blockIdx.x < 160) {
-        unsigned long long gt;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
-        g_decode_timers[blockIdx.x][10] = gt;
-    }
-#endif
+    DT_BEGIN();
     extern __shared__ __align__(128) uint8_t smem[];
     const int tps_g = a.I / 16;                 // gate/up items per expert
     const int tps_d = a.E / MM_ROWS;            // down items per expert
@@ -182,10 +166,6 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
             for (int i = 0; i < DEC_PER; i++) key[i] = lane + 32 * i < a.NE ? choice_key(__fadd_rn(sc[i], bias_r[i])) : 0u;
             int my_pick = 0;
             float my_w = 0.f;
-#ifdef G5B_STAGE_TIMERS
-            if (__shfl_xor_sync(0xffffffffu, key[0], 1) == 12345u) my_w = 1.f;
-            DT_MARK_P(12);
-#endif
             // K rounds of arg-max: the largest key of the warp, then the lowest expert holding it
             for (int j = 0; j < a.K; j++) {
                 uint32_t m = 0u;
@@ -417,9 +397,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
         }
         DT_MARK(6);
         int it = 0;
-#ifdef G5B_STAGE_TIMERS
         bool seen_routed = false;
-#endif
 
         // ---- gate/up items
         bool have_sel = false;
@@ -438,10 +416,8 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
                 ok = mbar_wait_warp(&full[s], (it / MM_NS) & 1, a.err, 2);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
-#ifdef G5B_STAGE_TIMERS
                 if (it == 0) DT_MARK(7);
                 if (slot != a.K && !seen_routed) { DT_MARK(8); seen_routed = true; }
-#endif
                 const uint8_t *st = stages + (size_t)s * stage_bytes;
                 const float *sc = reinterpret_cast<const float *>(st + scale_off) + (mt ? 64 : 0);
                 mma_consume_stage(accf, st, sc, x_h + (size_t)g8 * a.E, kh * MM_CB, a.bc, mt, kq, g8, t4);
@@ -546,11 +522,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
             asm volatile("bar.sync 1, %0;" ::"r"(MM_CONS * 32) : "memory");
             if (ctid < a.ep_size) {
                 const unsigned long long *mine = reinterpret_cast<const unsigned long long *>(a.peers[a.ep_rank]) + ctid;
-                bool seen = false;
-                for (int i = 0; i < DEC_SPIN_LIMIT && !seen; i++) {
-                    seen = ld_acquire_sys(mine) >= a.ep_step;
-                    if (!seen) __nanosleep(100);
-                }
+                const bool seen = wait_word_sys(mine, a.ep_step, a.ep_wait_ns);
                 if (!seen) { atomicExch(a.err, 20 + ctid); s_flag = 0; }
             }
             asm volatile("bar.sync 1, %0;" ::"r"(MM_CONS * 32) : "memory");
@@ -593,22 +565,10 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
         }
         DT_MARK(5);
     }
-#ifdef G5B_STAGE_TIMERS
-    __syncthreads();
-    if (threadIdx.x == 0 && blockIdx.x < 160) {
-        unsigned long long gt;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
-        g_decode_timers[blockIdx.x][11] = gt;
-    }
-#endif
+    DT_END();
 }
 
-#ifdef G5B_STAGE_TIMERS
-extern "C" int g5b_debug_decode_timers(unsigned long long *dst)
-{
-    return cudaMemcpyFromSymbol(dst, g_decode_timers, sizeof g_decode_timers) == cudaSuccess ? 0 : -1;
-}
-#endif
+DT_EXPORT()
 
 static size_t decode_smem_bytes(int I)
 {
@@ -626,17 +586,21 @@ bool moe_decode_supported(const MoeShape &s, int T)
     if (s.E / MM_CB > MM_NS - 1 || s.I != MM_CB) return false;
     if ((size_t)s.E * 4 > MM_NS * (size_t)s.I * 4) return false;
     if (decode_smem_bytes(s.I) > 226 * 1024) return false;
-    static int coop = -1, sms = 0, fits = 0;
-    if (coop < 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        cudaFuncSetAttribute(moe_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem_bytes(s.I));
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&fits, moe_decode_kernel, MM_THREADS, decode_smem_bytes(s.I));
-        cudaGetLastError();
+    // per device: the opt-in to this much shared memory, and whether one CTA per SM is resident
+    static SmemGrant grant;
+    static int fits[G5B_MAX_DEVICES];                       // 0 not asked yet, 1 yes, -1 no
+    const int dev = dev_now();
+    if (!dev_cooperative()) return false;
+    if (!dev_opt_in_smem((const void *)moe_decode_kernel, decode_smem_bytes(s.I), grant)) return false;
+    if (fits[dev] == 0) {
+        int n = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, moe_decode_kernel, MM_THREADS, decode_smem_bytes(s.I)) != cudaSuccess) {
+            cudaGetLastError();
+            n = 0;
+        }
+        fits[dev] = n >= 1 ? 1 : -1;
     }
-    return coop == 1 && fits >= 1 && sms >= 1;
+    return fits[dev] == 1;
 }
 
 int moe_decode(cudaStream_t st, float *out, const float *x, const void *gate, int gate_dt, const float *bias,
@@ -644,22 +608,14 @@ int moe_decode(cudaStream_t st, float *out, const float *x, const void *gate, in
                const MoeShape &s, int with_shared, unsigned long long *sync, unsigned long long *launches,
                int *tile_done, int *err, const DecodeEp *ep)
 {
-    int dev = 0, sms = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int sms = dev_sms();
     DecodeArgs a{experts, x, gate, gate_dt, bias, score, idx, w, static_cast<__half *>(act), contrib, out,
                  s.E, s.I, s.NE, s.K, s.br, s.bc, with_shared, s.norm_topk, s.limit, s.routed_scale,
                  sync, (*launches) * (unsigned long long)sms, tile_done, err,
                  ep ? ep->rank : 0, ep ? ep->size : 1, s.n_local0, s.n_local, ep ? ep->peers : nullptr,
-                 ep ? ep->rows_off : 0, ep ? ep->step : 0ull, ep ? ep->arrive : nullptr};
+                 ep ? ep->rows_off : 0, ep ? ep->step : 0ull, ep ? ep->arrive : nullptr, ep ? ep->wait_ns : 0ull};
     void *params[] = {&a};
     cudaError_t rc;
-#ifdef G5B_STAGE_TIMERS
-    if (getenv("G5B_PLAIN_LAUNCH")) {            // development only: compare launch paths
-        moe_decode_kernel<<<sms, MM_THREADS, decode_smem_bytes(s.I), st>>>(a);
-        rc = cudaGetLastError();
-    } else
-#endif
     rc = cudaLaunchCooperativeKernel((const void *)moe_decode_kernel, dim3(sms), dim3(MM_THREADS), params,
                                      decode_smem_bytes(s.I), st);
     if (rc != cudaSuccess) { cudaGetLastError(); return -1; }

@@ -35,20 +35,9 @@ struct MmaArgs {
     int *err;
 };
 
-#ifdef G5B_STAGE_TIMERS
-// Development aid (never in a normal build): per CTA, cycles spent in the prologue, by the producer
-// waiting for a free stage and issuing copies, and by consumer warp 0 waiting for data and computing.
-__device__ unsigned long long g_stage_timers[2][160][8];
-#define TIMER_NOW() clock64()
-#else
-#define TIMER_NOW() 0ll
-#endif
-
 template <bool GATEUP>
 __global__ void __launch_bounds__(MM_THREADS, 1) moe_mma_kernel(const MmaArgs a)
 {
-    const long long t_start = TIMER_NOW();
-    long long t_wait = 0, t_work = 0;
     extern __shared__ __align__(128) uint8_t smem[];
     const int C = GATEUP ? a.E : a.I;
     const int rows_total = GATEUP ? a.I : a.E;
@@ -122,7 +111,6 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_mma_kernel(const MmaArgs a)
 
     const int n_items = s_nslots * tps;
     bool ok = true;
-    const long long t_loop = TIMER_NOW();
 
     if (warp == MM_CONS) {
         // ---------------------------------------------------------------- producer ----
@@ -133,12 +121,9 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_mma_kernel(const MmaArgs a)
             const int pair = s_pair[slot];
             for (int kh = 0; kh < KH && ok; kh++, it++) {
                 const int s = it % MM_NS;
-                const long long t0 = TIMER_NOW();
                 if (it >= MM_NS) ok = mbar_wait(&empty[s], ((it / MM_NS) - 1) & 1, a.err, 1);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
-                const long long t1 = TIMER_NOW();
-                t_wait += t1 - t0;
                 uint8_t *st = stages + (size_t)s * stage_bytes;
                 const uint32_t bytes = MM_ROWS * MM_CB + (GATEUP ? 2 : 1) * scols * 4 + (GATEUP ? 0 : a.I * 4);
                 if (lane == 0) mbar_expect_tx(&full[s], bytes);
@@ -157,15 +142,8 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_mma_kernel(const MmaArgs a)
                         bulk_g2s(st + act_off, static_cast<const uint8_t *>(a.x) + (size_t)pair * a.I * 4, a.I * 4, &full[s]);
                     }
                 }
-                t_work += TIMER_NOW() - t1;
             }
         }
-#ifdef G5B_STAGE_TIMERS
-        if (lane == 0 && blockIdx.x < 160) {
-            unsigned long long *o = g_stage_timers[GATEUP ? 0 : 1][blockIdx.x];
-            o[0] = t_loop - t_start; o[1] = t_wait; o[2] = t_work; o[3] = TIMER_NOW() - t_loop;
-        }
-#endif
         if (!ok) {                       // copies in flight must land before shared memory goes away
             for (int k = 0; k < MM_NS && k < it; k++) {
                 const int j = it - 1 - k;
@@ -183,19 +161,15 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_mma_kernel(const MmaArgs a)
             float accf[4] = {0.f, 0.f, 0.f, 0.f};
             for (int kh = 0; kh < KH && ok; kh++, it++) {
                 const int s = it % MM_NS;
-                const long long t0 = TIMER_NOW();
                 ok = mbar_wait_warp(&full[s], (it / MM_NS) & 1, a.err, 2);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
-                const long long t1 = TIMER_NOW();
-                t_wait += t1 - t0;
                 const uint8_t *st = stages + (size_t)s * stage_bytes;
                 const float *sc = reinterpret_cast<const float *>(st + scale_off) + ((GATEUP && mt) ? 64 : 0);
                 const __half *xt = GATEUP ? x_h + (size_t)g * a.E : reinterpret_cast<const __half *>(st + act_off) + (size_t)g * a.I;
                 mma_consume_stage(accf, st, sc, xt, kh * MM_CB, a.bc, mt, kq, g, t);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[s]);
-                t_work += TIMER_NOW() - t1;
             }
             if (!ok) break;
             // columns 0 (hi) and 1 (mid) of the accumulator tile live in the lanes with t == 0
@@ -230,12 +204,6 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_mma_kernel(const MmaArgs a)
             }
             asm volatile("bar.sync 1, %0;" ::"r"(MM_CONS * 32) : "memory");
         }
-#ifdef G5B_STAGE_TIMERS
-        if (threadIdx.x == 0 && blockIdx.x < 160) {
-            unsigned long long *o = g_stage_timers[GATEUP ? 0 : 1][blockIdx.x];
-            o[4] = t_wait; o[5] = t_work; o[6] = TIMER_NOW() - t_loop;
-        }
-#endif
         if (!GATEUP && a.out && ok) {
             // Combine once per CTA: report every row tile this CTA wrote; whoever completes a tile
             // sums its K contributions in top-k order in FP64 and adds the shared expert
@@ -286,27 +254,12 @@ bool moe_mma_supported(const MoeShape &s, int T)
     return true;
 }
 
-static int mma_sm_count()
-{
-    static int sms = 0;
-    if (!sms) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        if (sms < 1) sms = 148;
-    }
-    return sms;
-}
-
 template <bool GATEUP>
 static void launch_mma(cudaStream_t st, const MmaArgs &a, size_t smem)
 {
-    static bool attr = false;
-    if (!attr) {
-        cudaFuncSetAttribute(moe_mma_kernel<GATEUP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attr = true;
-    }
-    G5B_LAUNCH(moe_mma_kernel<GATEUP>, mma_sm_count(), MM_THREADS, smem, st, a);
+    static SmemGrant grant;
+    if (!dev_opt_in_smem((const void *)moe_mma_kernel<GATEUP>, smem, grant)) return;
+    G5B_LAUNCH(moe_mma_kernel<GATEUP>, dev_sms(), MM_THREADS, smem, st, a);
 }
 
 void moe_mma_gateup(cudaStream_t st, void *act_terms, const float *x, const ExpertW *experts, const MoePlan &p,
@@ -323,12 +276,5 @@ void moe_mma_down(cudaStream_t st, float *out, float *contrib, const void *act_t
     MmaArgs a{experts, p, act_terms, contrib, s.E, s.I, s.br, s.bc, s.limit, out, w, s.K, with_shared, tile_done, err};
     launch_mma<false>(st, a, mma_smem_bytes(false, s.E, s.I));
 }
-
-#ifdef G5B_STAGE_TIMERS
-extern "C" int g5b_debug_stage_timers(unsigned long long *dst)
-{
-    return cudaMemcpyFromSymbol(dst, g_stage_timers, sizeof g_stage_timers) == cudaSuccess ? 0 : -1;
-}
-#endif
 
 }  // namespace g5b

@@ -241,27 +241,12 @@ bool moe_mma_batch_supported(const MoeShape &s, int T)
     return mmab_smem_bytes() <= 226 * 1024;
 }
 
-static int mmab_sm_count()
-{
-    static int sms = 0;
-    if (!sms) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        if (sms < 1) sms = 148;
-    }
-    return sms;
-}
-
 template <bool GATEUP>
 static void launch_mmab(cudaStream_t st, const MmaBatchArgs &a)
 {
-    static bool attr = false;
-    if (!attr) {
-        cudaFuncSetAttribute(moe_mma_batch_kernel<GATEUP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mmab_smem_bytes());
-        attr = true;
-    }
-    G5B_LAUNCH(moe_mma_batch_kernel<GATEUP>, mmab_sm_count(), MM_THREADS, mmab_smem_bytes(), st, a);
+    static SmemGrant grant;
+    if (!dev_opt_in_smem((const void *)moe_mma_batch_kernel<GATEUP>, mmab_smem_bytes(), grant)) return;
+    G5B_LAUNCH(moe_mma_batch_kernel<GATEUP>, dev_sms(), MM_THREADS, mmab_smem_bytes(), st, a);
 }
 
 void moe_mma_batch_gateup(cudaStream_t st, void *act_terms, void *xterms, float *xinv, const float *x, int ldx,

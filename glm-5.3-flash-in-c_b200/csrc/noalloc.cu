@@ -29,7 +29,11 @@ constexpr int NOALLOC_MAX_DEVICES = 64;
 // symbol table, not a device address; the address is resolved once per device below.
 static __device__ __align__(256) float g_noalloc_rms_factor[NOALLOC_MAX_ROWS];
 
-float *g_factor_addr[NOALLOC_MAX_DEVICES];   // resolved device address, per device ordinal
+// Resolved device address, per device ordinal. Filled by the first call on a device and never
+// locked: the library's contract is one caller thread at a time, and two first calls that did race
+// would both store the same value. It is not refreshed: after cudaDeviceReset the process has to
+// reload the library before it calls this entry point again.
+float *g_factor_addr[NOALLOC_MAX_DEVICES];
 
 }  // namespace
 

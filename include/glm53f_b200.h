@@ -117,7 +117,11 @@ int g5b_engine_fill_expert(g5b_engine *e, int layer, int expert, uint64_t seed,
                            const float *gate_s, const float *up_s, const float *down_s);
 
 /* Engine options, by name. "latent_bf16" (before finalize): keep the MLA latent cache in BF16
- * instead of FP32, half the bytes per position. "profile": record per-phase events in MoE ops. */
+ * instead of FP32, half the bytes per position. "profile": record per-phase events in MoE ops.
+ * "sequences" (before finalize), "ep_wait_ms", "ep_loopback": see below. "expert_path": which
+ * batch-1 expert kernels run (0 register kernels, 1 tensor-core kernels as three launches, 2 the
+ * whole layer as one kernel, the default); "allow_partial": finalize accepts missing tensors
+ * (single-layer harnesses). */
 int g5b_engine_set_option(g5b_engine *e, const char *name, int value);
 
 /* Check that every tensor the config implies has been loaded, then allocate the session
@@ -130,7 +134,11 @@ int g5b_engine_finalize(g5b_engine *e);
  * (glm53f_model.h:59-64, glm53f_gpu.h:49-50). */
 int g5b_engine_forward(g5b_engine *e, const int *ids, int T, float *logits, int *argmax_all);
 
-/* Forget every carried position (glm53f_gpu_reset, glm53f_gpu.h:53). */
+/* A forward / decode call that fails after it began to advance the session (a launch error, a
+ * device-side wait that ran out) leaves the KDA state, the caches and the position count out of
+ * step with each other: the engine then refuses further forward / decode calls until
+ * g5b_engine_reset (the reference: "session must be reset", glm53f_model.h:61-64).
+ * Forget every carried position (glm53f_gpu_reset, glm53f_gpu.h:53). */
 void g5b_engine_reset(g5b_engine *e);
 void g5b_engine_free(g5b_engine *e);       /* glm53f_gpu_free, glm53f_gpu.h:47 */
 int  g5b_engine_cached(const g5b_engine *e);  /* positions consumed so far */
@@ -160,10 +168,17 @@ int g5b_engine_decode_batch(g5b_engine *e, const int *ids, float *logits, int *a
  * the peer mappings, waits (bounded; a wait that runs out makes the call return -1) for the other
  * ranks' rows and combines in top-k order. All ranks must make the same sequence of calls.
  * Option "ep_loopback" (g5b_engine_set_option) wires stand-in peers in local memory that never
- * answer: it exists to exercise the time-out report on one GPU. */
+ * answer: it exists to exercise the time-out report on one GPU.
+ * The wait is limited in wall-clock time (option "ep_wait_ms", default 5000): the ranks are separate
+ * host processes, so ordinary host skew must not look like a lost peer. A wait that does run out
+ * poisons the group: the rank that gave up has counted the step while a slower peer may still
+ * finish it, so from then on the ranks would pair different steps. After a failed call, bring all
+ * ranks to a barrier of your own, call g5b_engine_ep_resync on every rank (it forgets the step
+ * words and restarts the count), reset the engines, and pass another barrier before the next step. */
 size_t g5b_engine_ep_handle_bytes(void);
 int    g5b_engine_ep_export(g5b_engine *e, void *handle_out);
 int    g5b_engine_ep_connect(g5b_engine *e, const void *all_handles /* ep_size entries */);
+int    g5b_engine_ep_resync(g5b_engine *e);
 
 /* ---------------------------------------------------------------- LAYER OPS ---- */
 /* Host buffers in and out. Activations are FP32 like the reference's. `layer` indexes the
@@ -231,7 +246,8 @@ int g5b_state_read(g5b_engine *e, int layer, int kind, size_t offset, float *dst
  *   - rows <= 4096; more is refused with -1 and a message (split the call);
  *   - every GPU that loads the library holds the 16 KB array until the process exits;
  *   - the first call on each device resolves the array's address (once per device, with that
- *     device current): make that first call before any stream capture begins;
+ *     device current): make that first call before any stream capture begins, from one thread
+ *     (two first calls must not race), and not across a cudaDeviceReset (the address is kept);
  *   - all calls on a device share the array: two calls that may overlap on the GPU (different
  *     streams, or different threads) race on it and must be ordered by the caller. Nothing in it
  *     has to start at zero; each call overwrites every factor it reads.

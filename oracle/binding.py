@@ -18,8 +18,15 @@ ORACLE_SO = os.path.join(HERE, "_build", "libglm53f_oracle.so")
 REF_SO = os.path.join(HERE, "_ref", "libglm53f_ref.so")
 
 
-def build(reference_tree: str = "/root/reference"):
+def reference_tree() -> str:
+    """Where the unmodified reference project lies: $GLM53F_REFERENCE, else a directory named
+    `reference` beside this repository. It only has to exist where the checker is built."""
+    return os.environ.get("GLM53F_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
+def build(reference_tree: str | None = None):
     """Compile the oracle, and the reference objects when the reference tree is present."""
+    reference_tree = reference_tree or globals()["reference_tree"]()
     subprocess.run(["make", "-C", HERE, "oracle"], check=True, stdout=subprocess.DEVNULL)
     if os.path.isdir(os.path.join(reference_tree, "src", "core")):
         subprocess.run(["make", "-C", HERE, "ref", "ref-gpu-test", f"REF={reference_tree}"], check=True,

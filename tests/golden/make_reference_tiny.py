@@ -28,7 +28,8 @@ ck = importlib.import_module("glm53f_b200.checkpoint")
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    from oracle import binding
+    ref = sys.argv[1] if len(sys.argv) > 1 else binding.reference_tree()
     d = os.path.join(ref, "tests", "fixtures", "glm_tiny")
     tensors = ck.read_checkpoint(d)
     arrays, meta = {}, {}

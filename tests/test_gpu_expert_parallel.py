@@ -31,8 +31,22 @@ def test_unanswered_exchange_times_out_and_is_reported(gpu_lib, binding):
     with pytest.raises(RuntimeError, match="connect the ranks"):
         eng.op_moe(moe_layer, x)
     eng.set_option("ep_loopback", 1)
+    eng.set_option("ep_wait_ms", 300)                  # the stand-in peers never answer: do not wait 5 s for them
     with pytest.raises(RuntimeError, match="timed out"):
         eng.op_moe(moe_layer, x)
+    # a failed step poisons the step count; resync restarts it, and the next step fails the same clean way
+    eng.ep_resync()
+    with pytest.raises(RuntimeError, match="timed out"):
+        eng.op_moe(moe_layer, x[:1])
+    # a forward pass that fails half-way leaves the session undefined: refused until reset
+    eng.ep_resync()
+    ids = [1, 2, 3]
+    with pytest.raises(RuntimeError, match="timed out"):
+        eng.forward(ids)
+    with pytest.raises(RuntimeError, match="reset the engine"):
+        eng.forward(ids)
+    eng.reset()
+    assert eng.cached == 0
     eng.close()
     # the context is still usable: a one-GPU engine on the same device gives the CPU path's output
     one, orc = common.build_models(spec, tensors, 32, binding)

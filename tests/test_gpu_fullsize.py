@@ -92,9 +92,9 @@ def test_full_size_mla_layer(gpu_lib, binding, latent_bf16):
 
 
 def test_expert_kernel_variants_agree(moe_layer, binding):
-    """Batch 1 has four implementations: register-streaming CUDA-core kernels (the path batches
-    take), bulk-copy streamed CUDA-core kernels, bulk-copy streamed tensor-core kernels, and the
-    whole layer as one cooperative kernel (the default). All must give the CPU path's output."""
+    """Batch 1 has three implementations: register-streaming CUDA-core kernels (the path odd shapes
+    take), bulk-copy streamed tensor-core kernels as three launches, and the whole layer as one
+    cooperative kernel (the default). All must give the CPU path's output."""
     spec, trunk, eng = moe_layer
     x = synth.moe_inputs(spec.cfg, 1, SEED + 3)
     # a general FP32 activation too, not only BF16-representable values
@@ -104,12 +104,12 @@ def test_expert_kernel_variants_agree(moe_layer, binding):
         orc = synth.oracle_moe_layer(binding, spec, trunk, SEED, idx.ravel())
         want = orc.op_moe(0, xin)
         outs = []
-        for mode in (0, 1, 2, 3):
-            eng.set_option("stream_experts", mode)
+        for mode in (0, 1, 2):
+            eng.set_option("expert_path", mode)
             outs.append(eng.op_moe(0, xin))
             assert common.rel_err(outs[-1], want) < 1e-5, mode
             assert common.rel_err(eng.op_moe(0, xin, False), orc.op_moe(0, xin, False)) < 1e-5, mode
-        eng.set_option("stream_experts", 3)
+        eng.set_option("expert_path", 2)
         for _ in range(3):
-            assert np.array_equal(outs[3], eng.op_moe(0, xin))      # deterministic, counters carry over
+            assert np.array_equal(outs[2], eng.op_moe(0, xin))      # deterministic, counters carry over
         orc.close()
