@@ -4,17 +4,20 @@ with 128x128 block scales), batch 1 - the configuration the expert-GEMV roofline
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-A step is one pass of the layer over one batch. Prints ONE JSON line:
+A step is one pass of the layer over one token. Prints ONE JSON line:
   value        decode tokens/s through the layer with inputs resident in HBM (CUDA events on the
-               engine's stream around each step, L2 flushed before each step), all GPUs summed
+               engine's stream around each step, L2 flushed before each step)
   e2e          the same through the host-buffer C-ABI call (pinned host memory in and out)
-  roofline     the gate/up expert kernel: algorithmic bytes / its event-timed duration against
-               the measured HBM copy bandwidth
-  cpu_baseline the reference's own CPU implementation (glm53f_moe) on this box's host cores
-  extra        batch 8 and 64 of the same layer, and per-phase times
-With N > 1 (launched by torchrun, one rank per GPU) every rank serves its own stream of tokens
-through its own replica of the layer (weak scaling, no data-path collective: sequences are
-independent); the time is the maximum over ranks.
+  roofline     the layer's kernel: algorithmic bytes / its event-timed duration against the
+               measured HBM copy bandwidth; in_layer = the same inside a whole decoder layer
+  cpu_baseline the reference's own CPU implementation (glm53f_moe) on this box's host cores (N = 1)
+  extra        batch 8 / 64, the attention layers, whole decoder layers, and the full-size
+               random-init model (as many of its 45 layers as the GPUs hold) decoded greedily
+With N > 1 (launched by torchrun, one rank per GPU) the N GPUs serve ONE token stream together:
+the layer is expert parallel (288 / N routed experts per rank, rows exchanged over NVLink peer
+mappings inside the layer's kernel), so the scaling is strong; the time is the maximum over ranks.
+Before timing, the expert-parallel output is compared with the one-GPU engine's on the same inputs
+(extra.expert_parallel.parity). N independent replicas are reported under extra.replicas.
 """
 from __future__ import annotations
 
@@ -148,16 +151,28 @@ def cpu_reference_moe(steps: int, warmup: int, batch: int = 1, threads: int | No
                       f"{len(set(chosen.tolist()))} distinct routed experts + shared resident in RAM"}
 
 
+METRIC = "decode tokens/s through one full-size MoE layer, batch 1"
+DTYPE = "fp8_e4m3 weights, f32 activations and accumulation"
+
+
+def bench_config(world: int) -> dict:
+    """The `config` object of the JSON line: the same for this repo's arm and the reference arm."""
+    return {"workload": "config 2: single MoE layer decode, hidden 4096, inter 2048, 288+1 experts, top-8, batch 1",
+            "l2": f"GPU arm: flushed before every step ({FLUSH_BYTES >> 21} MiB written, then {FLUSH_BYTES >> 21} MiB "
+                  "read so that no dirty line is left); CPU arm: 4 rotating inputs, 226 MB of weights per step",
+            "parallelism": "one GPU" if world == 1 else
+                           f"expert parallel over {world} GPUs: one token stream, {288 // world} routed experts per rank"}
+
+
 def run_reference(args, rank, world):
     if rank != 0:
         return
-    steps = max(3, min(args.steps, 40))
-    r = cpu_reference_moe(steps, max(1, min(args.warmup, 3)))
-    line = {"impl": "reference", "metric": "decode tokens/s through one full-size MoE layer, batch 1",
-            "value": r["value"], "unit": "tokens/s", "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 3),
-            "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "fp8_e4m3 weights, f32 activations", "data": "synthetic",
-            "config": {"workload": "config 2: single MoE layer decode, hidden 4096, inter 2048, 288+1 experts, top-8, batch 1"},
+    warmup = max(3, args.warmup)
+    r = cpu_reference_moe(args.steps, warmup)
+    line = {"impl": "reference", "metric": METRIC,
+            "value": r["value"], "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": warmup,
+            "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": DTYPE, "data": "synthetic", "config": bench_config(max(1, args.gpus)),
             "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
             "e2e": {"value": r["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)

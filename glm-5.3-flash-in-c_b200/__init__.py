@@ -94,6 +94,8 @@ def lib() -> C.CDLL:
     L.g5b_engine_create.restype = C.c_void_p
     L.g5b_engine_create.argtypes = [C.POINTER(Config), C.c_char_p, C.c_char_p, C.c_int, C.c_int, C.c_int, C.c_int]
     L.g5b_engine_fill_expert.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_uint64, C.c_void_p, C.c_void_p, C.c_void_p]
+    L.g5b_engine_fill_matrix.argtypes = [C.c_void_p, C.c_char_p, C.c_int, C.c_uint64, C.c_float, C.c_void_p]
+    L.g5b_engine_last_picks.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
     L.g5b_engine_decode_greedy.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p]
     L.g5b_engine_ep_handle_bytes.restype = C.c_size_t
     L.g5b_engine_ep_export.argtypes = [C.c_void_p, C.c_void_p]
@@ -319,6 +321,21 @@ class Engine(FlatModel):
         if self.L.g5b_engine_fill_expert(self.handle, layer, expert, seed, g.ctypes.data, u.ctypes.data,
                                          d.ctypes.data) != 0:
             self._err("fill_expert")
+
+    def fill_matrix(self, name: str, dtype: int, seed: int, rows: int, mul: float = 0.0, scale_inv=None):
+        """A named matrix generated on the GPU (g5b_engine_fill_matrix); `rows` is recorded for op_matvec."""
+        sc = _f32(scale_inv) if scale_inv is not None else None
+        if self.L.g5b_engine_fill_matrix(self.handle, name.encode(), dtype, seed, C.c_float(mul),
+                                         sc.ctypes.data if sc is not None else None) != 0:
+            self._err(f"fill_matrix({name})")
+        self._rows[name] = rows
+
+    def last_picks(self, T: int = 1):
+        """(idx [T][topk], w [T][topk]) of the most recent MoE pass (g5b_engine_last_picks)."""
+        idx = np.zeros((T, self.cfg.topk), np.int32); w = np.zeros((T, self.cfg.topk), np.float32)
+        if self.L.g5b_engine_last_picks(self.handle, T, idx.ctypes.data, w.ctypes.data) != 0:
+            self._err("last_picks")
+        return idx, w
 
     def use_sequence(self, seq: int):
         if self.L.g5b_engine_use_sequence(self.handle, seq) != 0:

@@ -214,6 +214,36 @@ void fill_codes(cudaStream_t st, uint8_t *dst, uint64_t seed, int layer, int exp
     G5B_LAUNCH(fill_codes_kernel, 1184, 256, 0, st, reinterpret_cast<uint32_t *>(dst), key, groups);
 }
 
+// Synthetic matrices by tensor name: the key mixes the seed with an FNV-1a hash of the name, so that
+// the CPU can regenerate any single tensor bit for bit (orc_synth_matrix_* in the checker).
+uint64_t synth_key(uint64_t seed, const char *name)
+{
+    uint64_t h = 0xcbf29ce484222325ull;
+    for (const unsigned char *p = reinterpret_cast<const unsigned char *>(name); *p; p++) { h ^= *p; h *= 0x100000001b3ull; }
+    return mix64(seed ^ mix64(h));
+}
+
+void fill_codes_key(cudaStream_t st, uint8_t *dst, uint64_t key, size_t count)
+{
+    G5B_LAUNCH(fill_codes_kernel, 1184, 256, 0, st, reinterpret_cast<uint32_t *>(dst), key, count / 4);
+}
+
+// BF16 values with a bell-shaped distribution made of integer arithmetic only: the sum of the four
+// 16-bit fields of the element's hash, centred, times `mul` (one float rounding), rounded to BF16 -
+// every step is exact or a single IEEE rounding, so host and device agree to the bit.
+__global__ void fill_bf16_kernel(uint16_t *dst, uint64_t key, float mul, size_t n)
+{
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const uint64_t h = mix64(key + i);
+        const int c = (int)((h & 0xffffu) + ((h >> 16) & 0xffffu) + ((h >> 32) & 0xffffu) + (h >> 48)) - 131070;
+        dst[i] = __bfloat16_as_ushort(__float2bfloat16_rn(__fmul_rn((float)c, mul)));
+    }
+}
+void fill_bf16_key(cudaStream_t st, uint16_t *dst, uint64_t key, float mul, size_t count)
+{
+    G5B_LAUNCH(fill_bf16_kernel, 1184, 256, 0, st, dst, key, mul, count);
+}
+
 __global__ void f32_to_bf16_kernel(uint16_t *dst, const float *src, size_t n)
 {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)

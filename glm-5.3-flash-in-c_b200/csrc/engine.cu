@@ -468,6 +468,47 @@ extern "C" int g5b_engine_fill_expert(g5b_engine *e, int layer, int expert, uint
     return 0;
 }
 
+// A whole named matrix filled with synthetic values on the GPU (no host copy of the weights ever
+// exists): FP8 = uniform finite codes with the given scale grid, BF16 = bell-shaped values of
+// standard deviation ~ 37837 * mul. The full-size model's 12.6 GB trunk is built this way.
+extern "C" int g5b_engine_fill_matrix(g5b_engine *e, const char *name, int dtype, uint64_t seed, float mul,
+                                      const float *scale_inv)
+{
+    if (e->finalized) return fail("fill after finalize");
+    CU(cudaSetDevice(e->device));
+    const g5b_config &c = e->c;
+    DMat *m = nullptr;
+    int rows = 0, cols = 0;
+    if (!strcmp(name, "embed_tokens.weight")) { m = &e->embed; rows = c.vocab; cols = c.hidden; }
+    else if (!strcmp(name, "lm_head.weight")) { m = &e->lm_head; rows = c.vocab; cols = c.hidden; }
+    else {
+        int l = -1, used = 0;
+        if (sscanf(name, "layers.%d.%n", &l, &used) != 1 || l < 0 || l >= c.n_layers) return fail("unknown tensor %s", name);
+        auto it = e->names[l].find(name + used);
+        if (it == e->names[l].end() || it->second.kind != 0) return fail("%s is not a matrix of layer %d", name, l);
+        m = it->second.mat; rows = it->second.rows; cols = it->second.cols;
+    }
+    if (m->loaded()) return fail("%s is already loaded", name);
+    const size_t n = (size_t)rows * cols;
+    if (dtype == G5B_DT_BF16) {
+        m->dt = dtype; m->rows = rows; m->cols = cols;
+        if (e->dalloc(&m->w, n * 2)) return -1;
+        fill_bf16_key(e->st, static_cast<uint16_t *>(m->w), synth_key(seed, name), mul, n);
+    } else if (dtype == G5B_DT_FP8) {
+        if (!scale_inv || c.fp8_block_r < 1 || c.fp8_block_c < 1) return fail("%s: FP8 needs a scale grid and the config's block size", name);
+        if (n % 4) return fail("%s: synthetic FP8 matrices need a multiple of 4 elements", name);
+        m->dt = dtype; m->rows = rows; m->cols = cols;
+        m->br = c.fp8_block_r; m->bc = c.fp8_block_c; m->scols = (cols + m->bc - 1) / m->bc;
+        const size_t ns = (size_t)((rows + m->br - 1) / m->br) * m->scols;
+        if (e->dalloc(&m->w, n) || e->dalloc((void **)&m->s, ns * 4)) return -1;
+        fill_codes_key(e->st, static_cast<uint8_t *>(m->w), synth_key(seed, name), n);
+        if (copy_in(e, m->s, scale_inv, ns * 4, 0)) return -1;
+    } else return fail("%s: synthetic matrices are BF16 or FP8", name);
+    CU(cudaStreamSynchronize(e->st));
+    CU(cudaGetLastError());
+    return 0;
+}
+
 template <typename T>
 static int walloc(g5b_engine *e, T **p, size_t count) { return e->dalloc((void **)p, count * sizeof(T)); }
 
@@ -1232,6 +1273,20 @@ extern "C" int g5b_op_router(g5b_engine *e, int layer, const float *x, int T, in
     return 0;
 }
 
+// The expert picks and weights of the most recent MoE pass (its last chunk of T <= 64 positions),
+// whatever entry point ran it - how a caller learns which experts a whole-layer op routed to.
+extern "C" int g5b_engine_last_picks(g5b_engine *e, int T, int *idx, float *w)
+{
+    if (!e || !e->finalized) return fail("last_picks before finalize");
+    if (T < 1 || T > CHUNK) return fail("last_picks covers 1..%d positions", CHUNK);
+    CU(cudaSetDevice(e->device));
+    const size_t n = (size_t)T * e->c.topk;
+    if (idx) CU(cudaMemcpyAsync(idx, e->ridx, n * 4, cudaMemcpyDeviceToHost, e->st));
+    if (w)   CU(cudaMemcpyAsync(w, e->rw, n * 4, cudaMemcpyDeviceToHost, e->st));
+    CU(cudaStreamSynchronize(e->st));
+    return 0;
+}
+
 extern "C" int g5b_op_mlp(g5b_engine *e, int layer, const float *x, int T, float *out)
 {
     if (check_op(e, layer, T)) return -1;
@@ -1342,7 +1397,10 @@ extern "C" int g5b_op_matvec(g5b_engine *e, const char *name, const float *x, in
     Staged s{e};
     float *xd = s.in(x, (size_t)T * m->cols), *yd = s.in(nullptr, (size_t)T * m->rows);
     if (!xd || !yd) return fail("out of device memory");
-    gemv(e->st, *m, xd, m->cols, yd, m->rows, T);
+    // the path the forward pass takes for this many positions (one-token kernels below 8, the
+    // multi-token projection path from 8 on), a chunk at a time
+    FOR_CHUNKS(T)
+        if (proj(e, *m, xd + (size_t)t0 * m->cols, m->cols, yd + (size_t)t0 * m->rows, m->rows, n_)) return -1;
     return s.out(y, yd, (size_t)T * m->rows);
 }
 
@@ -1499,7 +1557,7 @@ extern "C" int g5b_shortconv_host(float *y, const float *x, const float *w, floa
 }
 
 // ------------------------------------------------------------------------ timing ----
-// Time `iters` launches of one op ("moe", "kda", "mla", "layer", "layers", "layer_batch", "hc_site", "hc_site_post") between CUDA events on the
+// Time `iters` launches of one op ("moe", "kda", "mla", "mlp", "head", "layer", "layers", "layer_batch", "hc_site", "hc_site_post") between CUDA events on the
 // engine's stream; before each launch `flush_bytes` of scratch are overwritten (0 = no flush) so
 // that weights come from HBM, not from L2. ms_each receives the per-launch times. When the
 // engine's "profile" option is on, the per-phase times of the MoE op accumulate in the profile.
@@ -1513,16 +1571,18 @@ extern "C" int g5b_time_op(g5b_engine *e, const char *op, int layer, const float
         CU(cudaMalloc(&e->flush_buf, flush_bytes));
         e->flush_bytes = flush_bytes;
     }
-    cudaEvent_t a, b;
-    CU(cudaEventCreate(&a));
-    CU(cudaEventCreate(&b));
+    // Every iteration is enqueued before the host waits for any of them: [flush, event, op, event]
+    // repeated, then one wait. The events bracket the op alone, the flush runs between the timed
+    // regions, and no host round trip sits between a step's end and the next step's launch - which
+    // is how a decode loop runs, and what keeps expert-parallel ranks (separate host processes) from
+    // timing each other's host wake-up jitter inside the op's wait for its peers.
+    std::vector<cudaEvent_t> ev((size_t)2 * iters, nullptr);
+    struct EvGuard { std::vector<cudaEvent_t> &v; ~EvGuard() { for (cudaEvent_t x : v) if (x) cudaEventDestroy(x); } } guard{ev};
+    for (auto &x : ev) CU(cudaEventCreate(&x));
     double total = 0.0;
-    const size_t kper = [&] { const size_t P = (size_t)e->c.kda_heads * e->c.kda_head_dim;
-                              return P * e->c.kda_head_dim + 3 * P * (size_t)(e->c.conv_k - 1); }();
-    (void)kper;
     for (int i = 0; i < iters; i++) {
         if (flush_bytes) flush_l2(e->st, e->flush_buf, flush_bytes);
-        CU(cudaEventRecord(a, e->st));
+        CU(cudaEventRecord(ev[2 * i], e->st));
         int rc;
         if (!strcmp(op, "moe"))        rc = g5b_dev_moe(e, layer, x_dev, T, out_dev);
         else if (!strcmp(op, "kda"))   rc = g5b_dev_kda(e, layer, x_dev, T, out_dev);
@@ -1554,18 +1614,30 @@ extern "C" int g5b_time_op(g5b_engine *e, const char *op, int layer, const float
                 rc = 0;
             }
         }
+        else if (!strcmp(op, "head")) {                    // mean of the streams, final norm, lm_head, arg-max
+            if (!e->lm_head.loaded() || !e->norm) rc = fail("the head was not loaded");
+            else {
+                head_mean(e->st, e->xm, out_dev, T, e->c.hc_mult, e->c.hidden);
+                rms_factor(e->st, e->xm, e->c.hidden, e->c.hidden, T, e->c.rms_eps, e->inv_head);
+                rc = proj(e, e->lm_head, e->xm, e->c.hidden, e->logits, e->c.vocab, T, e->inv_head, e->norm);
+                if (!rc) argmax_rows(e->st, e->am_out, e->logits, e->c.vocab, T, e->am_v, e->am_i);
+            }
+        }
+        else if (!strcmp(op, "mlp")) {
+            rc = e->L[layer].is_dense ? run_mlp(e, e->L[layer], x_dev, T, out_dev) : fail("layer %d is a MoE layer", layer);
+        }
         else rc = fail("unknown op %s", op);
-        if (rc) return -1;
-        CU(cudaEventRecord(b, e->st));
-        CU(cudaEventSynchronize(b));
+        if (rc) { cudaStreamSynchronize(e->st); return -1; }
+        CU(cudaEventRecord(ev[2 * i + 1], e->st));
+    }
+    CU(cudaStreamSynchronize(e->st));
+    for (int i = 0; i < iters; i++) {
         float ms = 0.f;
-        CU(cudaEventElapsedTime(&ms, a, b));
+        CU(cudaEventElapsedTime(&ms, ev[2 * i], ev[2 * i + 1]));
         if (ms_each) ms_each[i] = ms;
         total += ms;
     }
     CU(cudaGetLastError());
-    cudaEventDestroy(a);
-    cudaEventDestroy(b);
     if (ms_total) *ms_total = (float)total;
     return check_device_error(e);
 }

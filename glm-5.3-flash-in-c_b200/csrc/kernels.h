@@ -85,6 +85,9 @@ void argmax_rows(cudaStream_t st, int *out, const float *logits, int n, int rows
                  int *scratch_i);
 void fill_codes(cudaStream_t st, uint8_t *dst, uint64_t seed, int layer, int expert, int which,
                 size_t count);
+uint64_t synth_key(uint64_t seed, const char *name);
+void fill_codes_key(cudaStream_t st, uint8_t *dst, uint64_t key, size_t count);      // count a multiple of 4
+void fill_bf16_key(cudaStream_t st, uint16_t *dst, uint64_t key, float mul, size_t count);
 void f32_to_bf16(cudaStream_t st, uint16_t *dst, const float *src, size_t n);
 void bf16_to_f32(cudaStream_t st, float *dst, const uint16_t *src, size_t n);
 void flush_l2(cudaStream_t st, void *buf, size_t bytes);

@@ -116,6 +116,16 @@ int g5b_engine_load(g5b_engine *e, const char *name, const g5b_tensor *t);
 int g5b_engine_fill_expert(g5b_engine *e, int layer, int expert, uint64_t seed,
                            const float *gate_s, const float *up_s, const float *down_s);
 
+/* Fill one whole named matrix (any matrix g5b_engine_load accepts except a routed expert's) with
+ * synthetic weights generated on the GPU from a hash of (seed, tensor name, element index), so that
+ * no host copy of the weights ever exists and the CPU can still regenerate any single tensor bit
+ * for bit: FP8 = E4M3 codes uniform over the 254 finite codes with the given scale grid (host
+ * memory); BF16 = a bell-shaped distribution (sum of four uniform 16-bit fields, centred) times
+ * `mul`, i.e. standard deviation 37837.2 * mul. This is how the full-size random-init model's
+ * trunk is built without a checkpoint (no counterpart in the reference, which loads safetensors). */
+int g5b_engine_fill_matrix(g5b_engine *e, const char *name, int dtype, uint64_t seed, float mul,
+                           const float *scale_inv);
+
 /* Engine options, by name. "latent_bf16" (before finalize): keep the MLA latent cache in BF16
  * instead of FP32, half the bytes per position. "profile": record per-phase events in MoE ops.
  * "sequences" (before finalize), "ep_wait_ms", "ep_loopback": see below. "expert_path": which
@@ -219,6 +229,10 @@ int g5b_op_mla(g5b_engine *e, int layer, const float *x, int T, int cached, floa
                int *sel_out, int *n_sel_out);
 /* glm53f_router (glm53f.h:340): idx/w [T][topk]. */
 int g5b_op_router(g5b_engine *e, int layer, const float *x, int T, int *idx, float *w);
+/* Expert indices and weights [T][topk] of the most recent MoE pass on this engine (the last chunk of
+ * T <= 64 positions), whichever entry point ran it: lets a caller of a whole-layer op see the
+ * routing the reference exposes through glm53f_router. Either output may be NULL. */
+int g5b_engine_last_picks(g5b_engine *e, int T, int *idx, float *w);
 /* glm53f_moe (glm53f.h:348); with_shared = 0 gives glm53f_moe_routed (glm53f.h:344). Any host
  * memory is accepted; when `out` is pinned and mapped (cudaHostAlloc / cudaHostRegister) the layer's
  * last kernel writes it directly and the device-to-host copy is skipped. */

@@ -62,6 +62,10 @@ def oracle_lib():
         L = _open(ORACLE_SO, "orc")
         L.orc_synth_codes.argtypes = [C.c_void_p, C.c_uint64, C.c_int, C.c_int, C.c_int, C.c_size_t]
         L.orc_synth_codes.restype = None
+        L.orc_synth_matrix_codes.argtypes = [C.c_void_p, C.c_uint64, C.c_char_p, C.c_size_t]
+        L.orc_synth_matrix_codes.restype = None
+        L.orc_synth_matrix_bf16.argtypes = [C.c_void_p, C.c_uint64, C.c_char_p, C.c_float, C.c_size_t]
+        L.orc_synth_matrix_bf16.restype = None
         _libs["orc"] = L
     return _libs["orc"]
 
@@ -152,3 +156,31 @@ def synth_codes(seed, layer, expert, which, count) -> np.ndarray:
     out = np.zeros(count, np.uint8)
     oracle_lib().orc_synth_codes(out.ctypes.data, seed, layer, expert, which, count)
     return out
+
+
+def synth_matrix_codes(seed, name: str, count) -> np.ndarray:
+    """E4M3 codes of the named matrix as g5b_engine_fill_matrix generates them on the GPU."""
+    out = np.zeros(count, np.uint8)
+    oracle_lib().orc_synth_matrix_codes(out.ctypes.data, seed, name.encode(), count)
+    return out
+
+
+def synth_matrix_bf16(seed, name: str, mul: float, count) -> np.ndarray:
+    """BF16 bits of the named matrix as g5b_engine_fill_matrix generates them on the GPU."""
+    out = np.zeros(count, np.uint16)
+    oracle_lib().orc_synth_matrix_bf16(out.ctypes.data, seed, name.encode(), C.c_float(mul), count)
+    return out
+
+
+def rmsnorm_host(prefix, x, w, eps) -> np.ndarray:
+    """glm53f_rmsnorm over the rows of x through the oracle or the reference; w may be None."""
+    L = oracle_lib() if prefix == "orc" else ref_lib()
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    rows, n = (x.shape[0], x.shape[1]) if x.ndim == 2 else (1, x.size)
+    wv = None if w is None else np.ascontiguousarray(w, dtype=np.float32)
+    y = np.zeros_like(x)
+    rc = getattr(L, f"{prefix}_rmsnorm_host")(y.ctypes.data, x.ctypes.data, None if wv is None else wv.ctypes.data,
+                                             n, rows, C.c_float(eps))
+    if rc != 0:
+        raise RuntimeError(f"{prefix}_rmsnorm_host failed")
+    return y

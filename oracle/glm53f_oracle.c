@@ -1134,6 +1134,40 @@ static uint64_t mix64(uint64_t z)
     return z ^ (z >> 31);
 }
 
+/* The generators of g5b_engine_fill_matrix, restated: key = mix64(seed ^ mix64(FNV-1a(name))). */
+static uint64_t synth_key(uint64_t seed, const char *name)
+{
+    uint64_t h = 0xcbf29ce484222325ull;
+    for (const unsigned char *p = (const unsigned char *)name; *p; p++) { h ^= *p; h *= 0x100000001b3ull; }
+    return mix64(seed ^ mix64(h));
+}
+
+void orc_synth_matrix_codes(uint8_t *dst, uint64_t seed, const char *name, size_t count)
+{
+    const uint64_t key = synth_key(seed, name);
+    for (size_t g = 0; g * 4 < count; g++) {
+        const uint64_t h = mix64(key + g);
+        for (int j = 0; j < 4 && g * 4 + j < count; j++) {
+            const uint32_t v = (uint32_t)(((h >> (16 * j)) & 0xffffu) * 254u) >> 16;
+            dst[g * 4 + j] = (uint8_t)(v + (v >= 127u));
+        }
+    }
+}
+
+void orc_synth_matrix_bf16(uint16_t *dst, uint64_t seed, const char *name, float mul, size_t count)
+{
+    const uint64_t key = synth_key(seed, name);
+    for (size_t i = 0; i < count; i++) {
+        const uint64_t h = mix64(key + i);
+        const int c = (int)((h & 0xffffu) + ((h >> 16) & 0xffffu) + ((h >> 32) & 0xffffu) + (h >> 48)) - 131070;
+        const float v = (float)c * mul;
+        uint32_t u;
+        memcpy(&u, &v, 4);
+        u += 0x7fffu + ((u >> 16) & 1u);               /* round to nearest even; values are finite */
+        dst[i] = (uint16_t)(u >> 16);
+    }
+}
+
 void orc_synth_codes(uint8_t *dst, uint64_t seed, int layer, int expert, int which, size_t count)
 {
     const uint64_t key = mix64(seed ^ mix64(((uint64_t)layer << 40) ^ ((uint64_t)expert << 8) ^ (uint64_t)which));

@@ -66,6 +66,10 @@ int orc_state_read(orc_model *m, int layer, int kind, size_t offset, float *dst,
 void orc_synth_codes(uint8_t *dst, uint64_t seed, int layer, int expert, int which,
                      size_t count);
 
+/* The named-matrix generators of g5b_engine_fill_matrix, on the CPU. */
+void orc_synth_matrix_codes(uint8_t *dst, uint64_t seed, const char *name, size_t count);
+void orc_synth_matrix_bf16(uint16_t *dst, uint64_t seed, const char *name, float mul, size_t count);
+
 #ifdef __cplusplus
 }
 #endif

@@ -282,3 +282,161 @@ def oracle_moe_layer(binding, spec: Spec, trunk: dict, seed: int, experts):
             codes = binding.synth_codes(seed, 0, ex, which, n).reshape(shape)
             orc.load(f"layers.0.mlp.experts.{ex}.{nm}_proj.weight", codes, DT_FP8, sc)
     return orc
+
+
+# ------------------------------------------- full-size model (configs 4 and 5) ----
+BF16_UNIT = 37837.2       # standard deviation of the device generator's BF16 values at mul = 1
+
+
+def full_model_spec(n_layers: int = 45) -> Spec:
+    """The released architecture (45 layers: MLA at 3, 7, ..., 43, KDA elsewhere; dense MLP in
+    layers 0-2, MoE from 3 on), optionally cut to its first `n_layers` layers the way the
+    reference's --layers option does (src/model/glm53f_model.c:77)."""
+    c = pkg.full_size_config()
+    c.n_layers = n_layers
+    is_mla = [1 if l % 4 == 3 else 0 for l in range(n_layers)]
+    is_dense = [1 if l < 3 else 0 for l in range(n_layers)]
+    return Spec(c, is_mla, is_dense)
+
+
+def layer_tensor_table(c, is_mla: bool, is_dense: bool):
+    """[(name below 'layers.L.', 'mat' | 'vec', rows, cols, dtype, what)] of one decoder layer, routed
+    experts excluded: names and shapes as the reference binds them (src/model/glm53f_bind.c:139-206).
+    `what` tells the generators which distribution a vector gets."""
+    E, M = c.hidden, c.hc_mult
+    MIX = (2 + M) * M
+    t = [("input_layernorm.weight", "vec", E, 1, DT_BF16, "norm"),
+         ("post_attention_layernorm.weight", "vec", E, 1, DT_BF16, "norm")]
+    for site in ("attn", "ffn"):
+        t += [(f"hc_{site}_fn", "mat", MIX, M * E, DT_BF16, ""), (f"hc_{site}_base", "vec", MIX, 1, DT_F32, "small"),
+              (f"hc_{site}_scale", "vec", 3, 1, DT_F32, "one")]
+    a = "self_attn."
+    if is_mla:
+        H, IH, ID = c.mla_heads, c.index_heads, c.index_dim
+        t += [(a + "q_a_proj.weight", "mat", c.q_lora, E, DT_FP8, ""), (a + "q_a_layernorm.weight", "vec", c.q_lora, 1, DT_BF16, "norm"),
+              (a + "q_b_proj.weight", "mat", H * c.qk_nope, c.q_lora, DT_FP8, ""),
+              (a + "kv_a_proj_with_mqa.weight", "mat", c.kv_lora, E, DT_FP8, ""),
+              (a + "kv_a_layernorm.weight", "vec", c.kv_lora, 1, DT_BF16, "norm"),
+              (a + "kv_b_proj.weight", "mat", H * (c.qk_nope + c.v_head), c.kv_lora, DT_BF16, ""),
+              (a + "o_proj.weight", "mat", E, H * c.v_head, DT_FP8, ""),
+              (a + "indexer.wq_b.weight", "mat", IH * ID, c.q_lora, DT_BF16, ""),
+              (a + "indexer.wk.weight", "mat", ID, E, DT_BF16, ""),
+              (a + "indexer.k_norm.weight", "vec", ID, 1, DT_BF16, "norm"), (a + "indexer.k_norm.bias", "vec", ID, 1, DT_BF16, "small"),
+              (a + "indexer.weights_proj.weight", "mat", IH, E, DT_BF16, ""),
+              (a + "indexer.index_kpool_compress_gate", "mat", ID, E, DT_BF16, ""),
+              (a + "indexer.index_kpool_compress_ape", "vec", c.index_kpool * ID, 1, DT_BF16, "small")]
+    else:
+        H, D = c.kda_heads, c.kda_head_dim
+        P = H * D
+        for n in ("q", "k", "v"):
+            t += [(a + f"{n}_proj.weight", "mat", P, E, DT_BF16, ""), (a + f"{n}_conv1d.weight", "vec", P * c.conv_k, 1, DT_BF16, "small")]
+        t += [(a + "f_a_proj.weight", "mat", D, E, DT_BF16, ""), (a + "f_b_proj.weight", "mat", P, D, DT_BF16, ""),
+              (a + "A_log", "vec", H, 1, DT_F32, "small"), (a + "dt_bias", "vec", P, 1, DT_F32, "small"),
+              (a + "b_proj.weight", "mat", H, E, DT_BF16, ""), (a + "g_a_proj.weight", "mat", D, E, DT_BF16, ""),
+              (a + "g_b_proj.weight", "mat", P, D, DT_BF16, ""), (a + "o_norm.weight", "vec", D, 1, DT_BF16, "norm"),
+              (a + "o_proj.weight", "mat", E, P, DT_BF16, "")]
+    if is_dense:
+        t += [("mlp.gate_proj.weight", "mat", c.dense_inter, E, DT_FP8, ""), ("mlp.up_proj.weight", "mat", c.dense_inter, E, DT_FP8, ""),
+              ("mlp.down_proj.weight", "mat", E, c.dense_inter, DT_FP8, "")]
+    else:
+        SI = c.moe_inter * c.n_shared
+        t += [("mlp.gate.weight", "mat", c.n_experts, E, DT_BF16, ""), ("mlp.gate.e_score_correction_bias", "vec", c.n_experts, 1, DT_F32, "bias"),
+              ("mlp.shared_experts.gate_proj.weight", "mat", SI, E, DT_FP8, ""), ("mlp.shared_experts.up_proj.weight", "mat", SI, E, DT_FP8, ""),
+              ("mlp.shared_experts.down_proj.weight", "mat", E, SI, DT_FP8, "")]
+    return t
+
+
+def synth_vector(seed: int, name: str, n: int, dtype: int, what: str):
+    """A small vector of the full-size synthetic model, made on the host: norm weights 1 + N(0, 0.02),
+    correction bias N(0, 0.1), mHC scale 1, everything else N(0, 0.02). Seeded by (seed, name)."""
+    import zlib
+    rng = np.random.default_rng([seed, zlib.crc32(name.encode())])
+    v = {"norm": lambda: 1.0 + 0.02 * rng.standard_normal(n), "bias": lambda: 0.1 * rng.standard_normal(n),
+         "one": lambda: np.ones(n), "small": lambda: 0.02 * rng.standard_normal(n)}[what]().astype(np.float32)
+    if dtype == DT_BF16:
+        return to_bf16_bits(v).reshape(n, 1), DT_BF16
+    return v.reshape(n, 1), DT_F32
+
+
+E4M3_UNIFORM_RMS = 100.058      # root mean square of the 254 finite E4M3 values, each equally likely
+
+
+def synth_scale_grid(c, seed: int, name: str, rows: int, cols: int) -> np.ndarray:
+    """FP32 block scales of a synthetic FP8 matrix of the full-size model: log-uniform over a factor
+    of four around 0.02 / (RMS of uniform codes), so that the matrix as a whole has the N(0, 0.02)
+    magnitude of the other random-init weights and every sub-block's output stays O(1)."""
+    import zlib
+    rng = np.random.default_rng([seed, zlib.crc32(name.encode()), 5])
+    sr, sc = (rows + c.fp8_block_r - 1) // c.fp8_block_r, (cols + c.fp8_block_c - 1) // c.fp8_block_c
+    return (0.02 / E4M3_UNIFORM_RMS * np.exp2(-1.0 + 2.0 * rng.random((sr, sc)))).astype(np.float32)
+
+
+def full_expert_scales(c, layer: int, expert: int, seed: int):
+    """The three scale grids (gate, up, down) of a routed expert of the full-size synthetic model."""
+    p = f"layers.{layer}.mlp.experts.{expert}."
+    return (synth_scale_grid(c, seed, p + "gate_proj.weight", c.moe_inter, c.hidden),
+            synth_scale_grid(c, seed, p + "up_proj.weight", c.moe_inter, c.hidden),
+            synth_scale_grid(c, seed, p + "down_proj.weight", c.hidden, c.moe_inter))
+
+
+def model_level_tensors(c):
+    return [("embed_tokens.weight", "mat", c.vocab, c.hidden, DT_BF16, ""), ("norm.weight", "vec", c.hidden, 1, DT_BF16, "norm"),
+            ("lm_head.weight", "mat", c.vocab, c.hidden, DT_BF16, "")]
+
+
+def fill_full_model(eng, spec: Spec, seed: int, ep_rank: int = 0, ep_size: int = 1, head: bool = True):
+    """Random-init weights of the full-size architecture straight into HBM: matrices are generated on
+    the GPU (g5b_engine_fill_matrix / fill_expert), vectors and scale grids on the host. BF16
+    matrices ~ N(0, 0.02); FP8 matrices uniform finite codes with block scales that give them the
+    same overall magnitude."""
+    c = spec.cfg
+    mul = np.float32(0.02 / BF16_UNIT)
+
+    def put(name, kind, rows, cols, dt, what):
+        if kind == "vec":
+            arr, vdt = synth_vector(seed, name, rows, dt, what)
+            eng.load(name, arr, vdt)
+        elif dt == DT_BF16:
+            eng.fill_matrix(name, DT_BF16, seed, rows, mul=float(mul))
+        else:
+            eng.fill_matrix(name, DT_FP8, seed, rows, scale_inv=synth_scale_grid(c, seed, name, rows, cols))
+
+    if head:
+        for row in model_level_tensors(c):
+            put(*row)
+    per = c.n_experts // ep_size
+    for L in range(c.n_layers):
+        for name, kind, rows, cols, dt, what in layer_tensor_table(c, bool(spec.is_mla[L]), bool(spec.is_dense[L])):
+            put(f"layers.{L}." + name, kind, rows, cols, dt, what)
+        if not spec.is_dense[L]:
+            for ex in range(ep_rank * per, (ep_rank + 1) * per):
+                eng.fill_expert(L, ex, seed, *full_expert_scales(c, L, ex, seed))
+
+
+def oracle_full_layer(binding, spec: Spec, seed: int, layer: int, experts, cap: int, kv_mode: int = 2):
+    """Layer `layer` of the synthetic full-size model on the CPU, as a one-layer model: every trunk
+    tensor of the layer is regenerated from the same hashes the GPU used, and of the routed experts
+    only those in `experts` (the ones the GPU's router picked) are materialised."""
+    c = spec.cfg.copy()
+    c.n_layers = 1
+    mul = np.float32(0.02 / BF16_UNIT)
+    orc = binding.OracleModel(c, [spec.is_mla[layer]], [spec.is_dense[layer]], cap, kv_mode)
+    for name, kind, rows, cols, dt, what in layer_tensor_table(c, bool(spec.is_mla[layer]), bool(spec.is_dense[layer])):
+        src = f"layers.{layer}." + name
+        if kind == "vec":
+            arr, vdt = synth_vector(seed, src, rows, dt, what)
+            orc.load("layers.0." + name, arr, vdt)
+        elif dt == DT_BF16:
+            orc.load("layers.0." + name, binding.synth_matrix_bf16(seed, src, float(mul), rows * cols).reshape(rows, cols), DT_BF16)
+        else:
+            orc.load("layers.0." + name, binding.synth_matrix_codes(seed, src, rows * cols).reshape(rows, cols), DT_FP8,
+                     synth_scale_grid(spec.cfg, seed, src, rows, cols))
+    if not spec.is_dense[layer]:
+        n = c.moe_inter * c.hidden
+        for ex in sorted(set(int(e) for e in experts)):
+            gs, us, ds = full_expert_scales(c, layer, ex, seed)
+            for which, (nm, shape, sc) in enumerate((("gate", (c.moe_inter, c.hidden), gs), ("up", (c.moe_inter, c.hidden), us),
+                                                     ("down", (c.hidden, c.moe_inter), ds))):
+                codes = binding.synth_codes(seed, layer, ex, which, n).reshape(shape)
+                orc.load(f"layers.0.mlp.experts.{ex}.{nm}_proj.weight", codes, DT_FP8, sc)
+    return orc
