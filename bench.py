@@ -305,119 +305,223 @@ def time_mhc_site(pkg, torch, steps: int, device: int = 0):
 
 
 def time_decoder_layers(pkg, torch, steps: int, device: int = 0):
-    """Two whole full-size decoder layers, one new token: layer 0 = KDA + MoE, layer 1 = MLA (8192
-    cached positions, indexer selecting) + MoE, each with its two mHC sites and norms. From the two
-    times the full model's batch-1 token time on ONE GPU's worth of bandwidth is extrapolated
-    (34 KDA layers + 11 MLA layers + the 1.27 GB head at the KDA layer's measured GB/s) - the
-    306 GB model itself needs 8 GPUs."""
-    import synth
+    """Two whole full-size decoder layers, one new token: layer 0 = KDA + MoE, layer 1 = MLA (8191
+    cached positions, indexer selecting) + MoE, each with its two mHC sites and norms; weights
+    generated in HBM. Before anything is timed each layer's output is compared with the CPU path's
+    stored result for the same seeded input and state (tests/golden/fullsize_layers.npz)."""
+    import fullmodel
     L = pkg.lib()
-    c = pkg.full_size_config()
-    c.n_layers = 2
-    spec = synth.Spec(c, [0, 1], [0, 0], with_head=False)
-    tensors = synth.make_model(spec, seed=6, recipe="baseline", experts=False)
-    cap = 8192
-    eng = pkg.Engine(c, spec.is_mla, spec.is_dense, cap, device)
-    eng.set_option("allow_partial", 1)
-    eng.set_option("latent_bf16", 1)
-    eng.set_option("sequences", 64)
-    eng.load_all(tensors)
-    for layer in range(2):
-        for ex in range(c.n_experts):
-            eng.fill_expert(layer, ex, SEED, *synth.expert_scales(c, layer, ex, SEED))
-    eng.finalize()
+    golden = fullmodel.load_layer_case_golden()
+    spec, eng, inputs = fullmodel.build_layer_case_engine(device, sequences=64)
+    c, cap = spec.cfg, fullmodel.LAYER_CASE_CAP
+    out = {"parity_vs_stored_cpu_result": {name: fullmodel.check_layer_case(eng, inputs, golden, layer)
+                                           for layer, name in ((0, "kda_moe_layer"), (1, "mla_moe_layer_ctx8192"))}}
     rng = np.random.default_rng(SEED)
     h = torch.from_numpy(rng.standard_normal((1, c.hc_mult, c.hidden)).astype(np.float32)).cuda()
-    out = {}
-    for layer, cached, name in ((0, 0, "kda_moe_layer"), (1, cap - 1, "mla_moe_layer_ctx8192")):
-        hd = h.clone()
-        each = np.zeros(max(steps, 3), np.float32); tot = C.c_float(0)
-        for k in (3, steps):
-            hd.copy_(h)
-            assert L.g5b_time_op(eng.handle, b"layer", layer, hd.data_ptr(), 1, cached, hd.data_ptr(), k, FLUSH_BYTES,
+
+    def timed(op, layer, hsrc, T, cached, n):
+        hd = hsrc.clone()
+        each = np.zeros(max(n, 3), np.float32); tot = C.c_float(0)
+        for k in (3, n):
+            hd.copy_(hsrc)
+            assert L.g5b_time_op(eng.handle, op, layer, hd.data_ptr(), T, cached, hd.data_ptr(), k, FLUSH_BYTES,
                                  C.byref(tot), each.ctypes.data) == 0, L.g5b_last_error()
-        out[name] = {"ms": float(np.mean(each[:steps])), "finite": bool(torch.isfinite(hd).all().item())}
+        return {"ms": float(np.mean(each[:n])), "finite": bool(torch.isfinite(hd).all().item())}
+
+    out["kda_moe_layer"] = timed(b"layer", 0, h, 1, 0, steps)
+    out["mla_moe_layer_ctx8192"] = timed(b"layer", 1, h, 1, cap - 1, steps)
     # both layers in one pass (the second layer's first mHC site applies the first layer's pending
     # stream expansion inside its own launch, as in the whole model)
-    hd = h.clone()
-    each = np.zeros(max(steps, 3), np.float32); tot = C.c_float(0)
-    for k in (3, steps):
-        hd.copy_(h)
-        assert L.g5b_time_op(eng.handle, b"layers", 0, hd.data_ptr(), 1, cap - 1, hd.data_ptr(), k, FLUSH_BYTES,
-                             C.byref(tot), each.ctypes.data) == 0, L.g5b_last_error()
-    out["kda_moe_then_mla_moe_layers"] = {"ms": float(np.mean(each[:steps])), "finite": bool(torch.isfinite(hd).all().item())}
+    out["kda_moe_then_mla_moe_layers"] = timed(b"layers", 0, h, 1, cap - 1, steps)
     # the same two layers advancing 64 sequences by one token each (state and caches per sequence,
     # weights read once per batch)
     h64 = torch.from_numpy(rng.standard_normal((64, c.hc_mult, c.hidden)).astype(np.float32)).cuda()
-    for layer, cached, name in ((0, 0, "kda_moe_layer_batch64"), (1, cap - 1, "mla_moe_layer_ctx8192_batch64")):
-        hd = h64.clone()
-        n = max(3, steps // 2)
-        each = np.zeros(max(n, 3), np.float32); tot = C.c_float(0)
-        for k in (2, n):
-            hd.copy_(h64)
-            assert L.g5b_time_op(eng.handle, b"layer_batch", layer, hd.data_ptr(), 64, cached, hd.data_ptr(), k, FLUSH_BYTES,
-                                 C.byref(tot), each.ctypes.data) == 0, L.g5b_last_error()
-        out[name] = {"ms": float(np.mean(each[:n])), "finite": bool(torch.isfinite(hd).all().item())}
+    out["kda_moe_layer_batch64"] = timed(b"layer_batch", 0, h64, 64, 0, max(3, steps // 2))
+    out["mla_moe_layer_ctx8192_batch64"] = timed(b"layer_batch", 1, h64, 64, cap - 1, max(3, steps // 2))
     eng.close()
-    b64_ms = 34 * out["kda_moe_layer_batch64"]["ms"] + 11 * out["mla_moe_layer_ctx8192_batch64"]["ms"]
-    out["full_model_batch64_tokens_per_s_extrapolated"] = 64e3 / b64_ms
-    kda_bytes = 286048984 + 228907008 + 2 * 786432
-    rate = kda_bytes / (out["kda_moe_layer"]["ms"] * 1e-3)
-    head_ms = 154880 * 4096 * 2 / rate * 1e3
-    token_ms = 34 * out["kda_moe_layer"]["ms"] + 11 * out["mla_moe_layer_ctx8192"]["ms"] + head_ms
-    out["full_model_token_ms_extrapolated"] = token_ms
-    out["full_model_tokens_per_s_extrapolated"] = 1e3 / token_ms
-    out["note"] = ("extrapolated: 34 x KDA+MoE layer + 11 x MLA+MoE layer + lm_head at the KDA+MoE layer's measured "
-                   "rate; the three dense-MLP layers counted as MoE layers; one GPU's bandwidth, weights of 8 GPUs")
     return out
 
 
-def time_expert_parallel(pkg, torch, dist, synth, rep, args, local, rank, world, warmup):
-    """N > 1: the same layer expert-parallel (288 / N routed experts per rank, activations and the
-    shared expert replicated, contribution rows exchanged over peer mappings inside the decode
-    kernel): one token stream served by all ranks together, i.e. the latency side of the N-GPU
-    trade-off. Returns the entry for `extra`. Every rank takes part in every collective here
-    whatever happens on it, and the ranks agree on each stage's outcome before the next."""
-    def all_ok(flag: bool) -> bool:
-        t = torch.tensor([1.0 if flag else 0.0], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MIN)
-        return bool(t.item() > 0.5)
+def time_head_and_dense(pkg, torch, steps: int, device: int = 0):
+    """The vocabulary-sized head (mean of the streams, final norm, lm_head 154880 x 4096 BF16, arg-max)
+    and one dense MLP (inter 12288, FP8) of the full-size model, one token, L2 flushed."""
+    import fullmodel
+    L = pkg.lib()
+    spec = synth_mod().full_model_spec(1)                         # layer 0: KDA + dense MLP
+    eng = fullmodel.build_engine(spec, SEED, 8, device)
+    c = spec.cfg
+    rng = np.random.default_rng(SEED)
+    h = torch.from_numpy(rng.standard_normal((1, c.hc_mult, c.hidden)).astype(np.float32)).cuda()
+    x = torch.from_numpy(rng.standard_normal((1, c.hidden)).astype(np.float32)).cuda()
+    y = torch.empty_like(x)
+    out = {}
+    for op, src, dst, nbytes in ((b"head", h, h, c.vocab * c.hidden * 2),
+                                 (b"mlp", x, y, 3 * c.dense_inter * c.hidden + 3 * (c.dense_inter // 128) * (c.hidden // 128) * 4)):
+        each = np.zeros(max(steps, 3), np.float32); tot = C.c_float(0)
+        for k in (3, steps):
+            assert L.g5b_time_op(eng.handle, op, 0, src.data_ptr(), 1, 0, dst.data_ptr(), k, FLUSH_BYTES,
+                                 C.byref(tot), each.ctypes.data) == 0, L.g5b_last_error()
+        ms = float(np.mean(each[:steps]))
+        out[op.decode()] = {"ms": ms, "algorithmic_bytes": nbytes, "achieved_GBps": nbytes / (ms * 1e-3) / 1e9}
+    eng.close()
+    return out
 
-    ep, err, handle = None, "", b""
+
+def synth_mod():
+    import synth
+    return synth
+
+
+def expert_parallel_parity(pkg, one, ep, ranks, rank: int):
+    """The expert-parallel layer against the one-GPU engine of the same rank on the same seeded
+    inputs (batch 1 four times, batch 8 once): outputs must be bit-equal, because the contribution
+    rows and the top-k-ordered FP64 combine are the same arithmetic wherever the rows were computed.
+    Returns the `parity` object; every rank makes the same calls."""
+    import synth
+    worst, bit_equal, idx_equal = 0.0, True, True
+    err = ""
     try:
-        spec_ep = synth.layer_spec("moe", n_experts=args.experts)
-        trunk_ep = synth.moe_layer_trunk(spec_ep, SEED)
-        ep = pkg.Engine(spec_ep.cfg, spec_ep.is_mla, spec_ep.is_dense, 8, local, rank, world)
-        ep.set_option("allow_partial", 1)
-        ep.load_all(trunk_ep)
-        for ex in range(args.experts):
-            ep.fill_expert(0, ex, SEED, *synth.expert_scales(spec_ep.cfg, 0, ex, SEED))
-        ep.finalize()
-        handle = ep.ep_export()
-    except Exception as exc:                                   # noqa: BLE001
+        for B, seed in ((1, SEED), (1, SEED + 1), (1, SEED + 2), (1, SEED + 3), (8, SEED + 4)):
+            x = synth.moe_inputs(one.cfg, B, seed)
+            a, b = one.op_moe(0, x), ep.op_moe(0, x)
+            ia, _ = one.op_router(0, x)
+            ib, _ = ep.op_router(0, x)
+            bit_equal = bit_equal and bool(np.array_equal(a, b))
+            idx_equal = idx_equal and bool(np.array_equal(ia, ib))
+            worst = max(worst, float(np.max(np.abs(a.astype(np.float64) - b)) / (np.max(np.abs(a)) + 1e-300)))
+    except Exception as exc:                                       # noqa: BLE001
         err = repr(exc)[:300]
-    handles = [None] * world
-    dist.all_gather_object(handles, handle)
-    if not err:
+    ok = ranks.all_ok(not err)
+    res = {"max_rel_err": ranks.reduce(worst, "max"), "bit_equal": ranks.all_ok(bit_equal),
+           "router_idx_equal": ranks.all_ok(idx_equal), "cases": "batch 1 x 4 seeds, batch 8 x 1 seed, against the one-GPU engine on every rank"}
+    if not ok:
+        res["error"] = err or "another rank failed"
+    return res
+
+
+def time_e2e(L, eng, torch, ranks, steps: int, warmup: int):
+    """The layer through the host-buffer C-ABI call: pinned host memory in and out, copies inside the
+    timed region, L2 flushed before every step. Returns (seconds of the slowest rank, bytes in, bytes out)."""
+    import synth
+    xh = torch.from_numpy(synth.moe_inputs(eng.cfg, 1, SEED)).pin_memory()
+    oh = torch.empty_like(xh).pin_memory()
+    xn, on = xh.numpy(), oh.numpy()
+    for _ in range(warmup):
+        assert L.g5b_op_moe(eng.handle, 0, xn.ctypes.data, 1, on.ctypes.data, 1) == 0, L.g5b_last_error()
+    flush = torch.empty(FLUSH_BYTES // 8, dtype=torch.float32, device="cuda")
+    clean = torch.zeros(FLUSH_BYTES // 8, dtype=torch.float32, device="cuda")
+    total = 0.0
+    ranks.barrier()
+    for _ in range(steps):
+        flush.zero_()
+        clean.sum()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        assert L.g5b_op_moe(eng.handle, 0, xn.ctypes.data, 1, on.ctypes.data, 1) == 0, L.g5b_last_error()
+        total += time.perf_counter() - t0
+    return ranks.reduce(total, "max"), int(xn.nbytes), int(on.nbytes)
+
+
+def run_full_model(pkg, torch, ranks, local: int, rank: int, world: int, peak: float, layers_cap: int,
+                   new_tokens: int = 256):
+    """Benchmark configuration 4: the full-size random-init model (45 layers, 288 experts per MoE
+    layer, vocabulary 154880) resident across the ranks, expert parallel (trunk replicated): prefill
+    an 18-token random-id prompt, then decode `new_tokens` tokens greedily at batch 1 without
+    returning to the host between steps. With fewer GPUs than the 306 GB need, the first layers that
+    fit are run (the reference's --layers cut). Then layers 0, 3 and the last one are compared with
+    the CPU path on the GPU's own state (rank 0 checks; every rank makes the same engine calls)."""
+    import fullmodel
+    import synth
+    res, err, eng = {}, "", None
+    free = torch.cuda.mem_get_info()[0]
+    n_layers = 0
+    for n in range(min(45, layers_cap), 0, -1):
+        resident, _, _ = fullmodel.model_bytes(synth.full_model_spec(n), world)
+        if resident + (6 << 30) <= free * 0.94:
+            n_layers = n
+            break
+    n_layers = int(ranks.reduce(n_layers, "min"))
+    if n_layers < 4:
+        return {"error": "not enough free device memory for four layers"}
+    spec = synth.full_model_spec(n_layers)
+    c = spec.cfg
+    cap = 18 + new_tokens + 30
+    resident, token_rank, token_all = fullmodel.model_bytes(spec, world)
+    t0 = time.perf_counter()
+    try:
+        eng = fullmodel.build_engine(spec, SEED, cap, local, rank, world, options={"latent_bf16": 1})
+    except Exception as exc:                                       # noqa: BLE001
+        err = repr(exc)[:300]
+    build_s = time.perf_counter() - t0
+    if not ranks.all_ok(not err):
+        if eng is not None:
+            eng.close()
+        return {"error": err or "another rank could not build the model"}
+    handles = ranks.gather(eng.ep_export() if world > 1 else b"")
+    toks = None
+    try:
+        if world > 1:
+            eng.ep_connect(handles)
+    except Exception as exc:                                       # noqa: BLE001
+        err = repr(exc)[:300]
+    if not ranks.all_ok(not err):
+        eng.close()
+        return {"error": err or "another rank could not connect"}
+    ids = np.random.default_rng(SEED).integers(0, c.vocab, 18).astype(np.int32)
+    prefill_s = decode_s = 0.0
+    try:
+        # warm-up: the same prefill and a few decode steps, then forget them
+        lg, _ = eng.forward(ids)
+        eng.decode_greedy(int(np.argmax(lg)), 8)
+        eng.reset()
+        ranks.barrier()
+        t0 = time.perf_counter()
+        lg, _ = eng.forward(ids)
+        prefill_s = time.perf_counter() - t0
+        first = int(np.argmax(lg))
+        ranks.barrier()
+        t0 = time.perf_counter()
+        toks = eng.decode_greedy(first, new_tokens)
+        decode_s = time.perf_counter() - t0
+    except Exception as exc:                                       # noqa: BLE001
+        err = repr(exc)[:300]
+    ok = ranks.all_ok(not err)
+    decode_s = ranks.reduce(decode_s, "max")
+    prefill_s = ranks.reduce(prefill_s, "max")
+    all_toks = ranks.gather(None if toks is None else toks.tolist())
+    if not ok:
+        eng.close()
+        return {"error": err or "another rank failed while decoding"}
+    ms = 1e3 * decode_s / new_tokens
+    res = {"layers": n_layers, "of_layers": 45, "n_gpus": world, "new_tokens": new_tokens, "prompt_tokens": 18,
+           "trunk": "replicated on every rank", "experts_per_rank": c.n_experts // world,
+           "resident_bytes_per_rank": resident, "build_s": build_s, "prefill_ms": 1e3 * prefill_s,
+           "ms_per_token": ms, "tokens_per_s": 1e3 / ms,
+           "algorithmic_bytes_per_token": token_all, "bytes_read_per_token_per_rank": token_rank,
+           "frac_of_aggregate_roofline": token_all / (ms * 1e-3) / 1e9 / (world * peak),
+           "frac_of_one_rank_roofline_for_its_own_reads": token_rank / (ms * 1e-3) / 1e9 / peak,
+           "tokens_equal_on_all_ranks": all(t == all_toks[0] for t in all_toks),
+           "first_tokens": all_toks[0][:8]}
+    # per-layer parity at the position reached (rank 0 holds the CPU side)
+    parity, perr = {}, ""
+    rng = np.random.default_rng(SEED + 11)
+    for layer in sorted({0, 3, n_layers - 1}):
+        h = rng.standard_normal((1, c.hc_mult, c.hidden)).astype(np.float32)
         try:
-            ep.ep_connect(handles)
-        except Exception as exc:                               # noqa: BLE001
-            err = repr(exc)[:300]
-    ep_ms = 0.0
-    if all_ok(not err):
-        try:
-            ep_each, _, _, _ = time_batch(pkg, ep, torch, 1, args.steps, warmup, phases=False)
-            ep_ms = float(ep_each.mean())
-        except Exception as exc:                               # noqa: BLE001
-            err = repr(exc)[:300]
-    ok = all_ok(not err)
-    ep_ms = rep.max_over_ranks(ep_ms, dist, "cuda")
-    if ep is not None:
-        ep.close()
-    if not ok or ep_ms <= 0:
-        return {"ranks": world, "error": err or "another rank failed"}
-    return {"ranks": world, "ms_per_step": ep_ms, "tokens_per_s": 1e3 / ep_ms,
-            "routed_experts_per_rank": args.experts // world}
+            if rank == 0:
+                from oracle import binding
+                r = fullmodel.layer_parity(eng, binding, spec, SEED, layer, h, eng.cached, cap)
+                parity[f"layer{layer}"] = {"rel_err": r["rel_err"], "picks": None if r["picks"] is None else r["picks"].ravel().tolist()}
+            else:
+                fullmodel.layer_parity(eng, None, spec, SEED, layer, h, eng.cached, cap, check=False)
+        except Exception as exc:                                   # noqa: BLE001
+            perr = repr(exc)[:300]
+        if not ranks.all_ok(not perr):
+            parity["error"] = perr or "another rank failed"
+            break
+    res["layer_parity_vs_cpu"] = parity
+    eng.close()
+    return res
 
 
 def main():
@@ -432,7 +536,7 @@ def main():
                          "an ncu capture small: the batch-1 kernels touch 8 routed + 1 shared either way)")
     ap.add_argument("--batches", default="8,64", help="extra batch sizes reported under 'extra'")
     ap.add_argument("--no-expert-parallel", action="store_true",
-                    help="N > 1: skip the expert-parallel timing of the layer reported under 'extra'")
+                    help="N > 1: run N independent replicas only (no expert-parallel engine)")
     ap.add_argument("--only-attention-layers", action="store_true",
                     help="run only the KDA / MLA single-layer timings and print them (a small case for ncu)")
     ap.add_argument("--no-decoder-layers", action="store_true",
@@ -441,7 +545,11 @@ def main():
     ap.add_argument("--only-mhc-site", action="store_true",
                     help="run only the timing of one mHC site of a full-size layer and print it (a small case for ncu)")
     ap.add_argument("--no-attention-layers", action="store_true",
-                    help="skip the KDA / MLA single-layer timings reported under 'extra'")
+                    help="skip the KDA / MLA single-layer and decoder-layer timings reported under 'extra'")
+    ap.add_argument("--no-full-model", action="store_true", help="skip the full-size model's greedy decode")
+    ap.add_argument("--only-full-model", action="store_true", help="run only the full-size model's greedy decode and print it")
+    ap.add_argument("--full-model-layers", type=int, default=45, help="upper limit on the layers of the full-size model")
+    ap.add_argument("--full-model-tokens", type=int, default=256)
     ap.add_argument("--expert-path", type=int, default=-1,
                     help="batch-1 expert kernels: 0 register-streaming, 1 tensor-core kernels as three launches, 2 whole layer in one kernel (default)")
     args = ap.parse_args()
@@ -461,135 +569,173 @@ def main():
     if not torch.cuda.is_available() or L.g5b_device_count() < 1:
         raise SystemExit("bench.py needs a CUDA device: the engine has no CPU path")
     torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
-    warmup = max(3, args.warmup)
-    if args.only_mhc_site:
-        print(json.dumps({"mhc_site": time_mhc_site(pkg, torch, max(3, args.steps), local)}), flush=True)
-        return
-    if args.only_attention_layers:
-        peak, _ = measured_peaks()
-        res = {"config3": time_attention_layers(pkg, torch, max(3, args.steps), peak, local)}
-        if not args.no_decoder_layers:
-            res["decoder_layers"] = time_decoder_layers(pkg, torch, max(3, args.steps), local)
-        print(json.dumps(res), flush=True)
-        return
-    opts = {}
-    if args.expert_path >= 0:
-        opts["expert_path"] = args.expert_path
-    spec, trunk, eng = synth.build_moe_layer_engine(SEED, n_experts=args.experts, device=local, options=opts)
-    sampler = ClockSampler(local)
-
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    # ---- headline: batch 1, device resident
-    sampler.start()
-    sampler.wait_first()
-    barrier()
-    each, phases, launches, _ = time_batch(pkg, eng, torch, 1, args.steps, warmup)
-    barrier()
-    import importlib
-    rep = importlib.import_module("glm53f_b200.replicas")
-    local_ms_per_step = float(each.sum()) / args.steps
-    job = rep.whole_job_rate(units_local=args.steps, seconds_local=float(each.sum()) * 1e-3,
-                             dist=dist if world > 1 else None, device="cuda")
-    ms_per_step = job["seconds"] * 1e3 / args.steps          # the slowest rank's
-    value = job["rate"]                                      # tokens of all ranks / slowest rank's time
-
-    # ---- end to end: host buffers (pinned) through the C-ABI op, H2D and D2H inside the timing
-    xh = torch.from_numpy(synth.moe_inputs(spec.cfg, 1, SEED)).pin_memory()
-    oh = torch.empty_like(xh).pin_memory()
-    xn, on = xh.numpy(), oh.numpy()
-    for _ in range(warmup):
-        assert L.g5b_op_moe(eng.handle, 0, xn.ctypes.data, 1, on.ctypes.data, 1) == 0
-    flush = torch.empty(FLUSH_BYTES // 8, dtype=torch.float32, device="cuda")
-    clean = torch.zeros(FLUSH_BYTES // 8, dtype=torch.float32, device="cuda")
-    e2e_s = 0.0
-    barrier()
-    for _ in range(args.steps):
-        flush.zero_()
-        clean.sum()
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        assert L.g5b_op_moe(eng.handle, 0, xn.ctypes.data, 1, on.ctypes.data, 1) == 0
-        e2e_s += time.perf_counter() - t0
-    e2e_job = rep.whole_job_rate(units_local=args.steps, seconds_local=e2e_s, dist=dist if world > 1 else None,
-                                 device="cuda")
-    e2e_s = e2e_job["seconds"]
-    clocks = sampler.stop()       # sampled over the device-timed and the end-to-end regions
-    e2e = {"value": e2e_job["rate"], "unit": "tokens/s", "h2d_bytes_per_step": int(xn.nbytes),
-           "d2h_bytes_per_step": int(on.nbytes), "ms_per_step": 1e3 * e2e_s / args.steps}
-
-    # ---- roofline of the dominant kernel
-    router_bytes = args.experts * 4096 * 2
-    layer_bytes = 9 * EXPERT_BYTES + router_bytes
-    peak, peak_kind = measured_peaks()
-    layer = {"algorithmic_bytes_per_step": layer_bytes, "achieved": layer_bytes / (local_ms_per_step * 1e-3) / 1e9,
-             "frac": layer_bytes / (local_ms_per_step * 1e-3) / 1e9 / peak}
-    if launches == args.steps:
-        # one launch per step: the whole layer (router matrix, 8 routed + 1 shared expert) in one kernel
-        roofline = {"bound": "hbm", "kernel": "moe_decode_kernel (router + top-8 + 8 routed and 1 shared expert + combine, batch 1)",
-                    "achieved": layer["achieved"], "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s",
-                    "frac": layer["frac"], "traffic": DECODE_TRAFFIC_NCU, "algorithmic_bytes_per_launch": layer_bytes,
-                    "ms_per_launch": local_ms_per_step, "layer": layer}
-    else:
-        gateup_ms = phases[1]
-        achieved = 9 * GATEUP_BYTES / (gateup_ms * 1e-3) / 1e9 if gateup_ms > 0 else 0.0
-        roofline = {"bound": "hbm", "kernel": "gate/up + SwiGLU kernel of the chosen expert path (8 routed + 1 shared expert, batch 1)",
-                    "achieved": achieved, "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s",
-                    "frac": achieved / peak, "traffic": GATEUP_TRAFFIC_NCU,
-                    "algorithmic_bytes_per_launch": 9 * GATEUP_BYTES, "ms_per_launch": gateup_ms, "layer": layer}
-
-    if launches == args.steps:
-        extra = {"phase_ms_b1": {"moe_decode_kernel": phases[0]}}
-    else:
-        extra = {"phase_ms_b1": {"router+plan": phases[0], "gate_up": phases[1], "down": phases[2], "combine": phases[3]}}
-    if rank == 0:
-        for B in [int(b) for b in args.batches.split(",") if b]:
-            eb, ph, _, _ = time_batch(pkg, eng, torch, B, max(10, args.steps // 10), 3)
-            idx, _ = eng.op_router(0, synth.moe_inputs(spec.cfg, B, SEED))
-            distinct = int(len(set(idx.ravel().tolist())))
-            ms = float(eb.mean())
-            extra[f"batch{B}"] = {"tokens_per_s": B * 1e3 / ms, "ms_per_step": ms, "distinct_experts": distinct,
-                                  "achieved_GBps": ((distinct + 1) * EXPERT_BYTES + ROUTER_BYTES) / (ms * 1e-3) / 1e9,
-                                  "phase_ms": ph}
-    eng.close()
-    if rank == 0 and not args.no_attention_layers and args.experts == 288:
-        extra["config3"] = time_attention_layers(pkg, torch, max(10, args.steps // 10), peak, local)
-        extra["decoder_layers"] = time_decoder_layers(pkg, torch, max(10, args.steps // 10), local)
-        extra["mhc_site"] = time_mhc_site(pkg, torch, max(10, args.steps // 10), local)
-
-    # ---- N > 1: the same layer expert-parallel (288 / N routed experts per rank, activations and the
-    # shared expert replicated, contribution rows exchanged over peer mappings): one token stream
-    # served by all ranks together, i.e. the latency side of the N-GPU trade-off
-    if world > 1 and 288 % world == 0 and not args.no_expert_parallel:
-        # the headline above does not depend on this extra: a failure here is reported, not fatal
-        try:
-            extra["expert_parallel_b1"] = time_expert_parallel(pkg, torch, dist, synth, rep, args, local, rank, world,
-                                                               warmup)
-        except Exception as exc:                               # noqa: BLE001
-            extra["expert_parallel_b1"] = {"ranks": world, "error": repr(exc)[:300]}
-
+    # the CPU baseline first: one rank, before any other rank's process competes for the host cores
     cpu = None
-    if rank == 0 and not args.no_cpu_baseline and args.experts == 288:
+    if world == 1 and not args.no_cpu_baseline and args.experts == 288 and not (
+            args.only_mhc_site or args.only_attention_layers or args.only_full_model):
         cpu = cpu_reference_moe(steps=60, warmup=2)
         one = cpu_reference_moe(steps=30, warmup=1, threads=1)
         cpu = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
         cpu["one_thread_value"] = one["value"]
 
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    import importlib
+    ranks = importlib.import_module("glm53f_b200.ranks").Ranks(dist if world > 1 else None, "cuda")
+    peak, peak_kind = measured_peaks()
+    warmup = max(3, args.warmup)
+
+    if args.only_mhc_site:
+        print(json.dumps({"mhc_site": time_mhc_site(pkg, torch, max(3, args.steps), local)}), flush=True)
+        return
+    if args.only_attention_layers:
+        res = {"config3": time_attention_layers(pkg, torch, max(3, args.steps), peak, local)}
+        if not args.no_decoder_layers:
+            res["decoder_layers"] = time_decoder_layers(pkg, torch, max(3, args.steps), local)
+        print(json.dumps(res), flush=True)
+        return
+    if args.only_full_model:
+        res = run_full_model(pkg, torch, ranks, local, rank, world, peak, args.full_model_layers, args.full_model_tokens)
+        if rank == 0:
+            print(json.dumps({"full_model": res}), flush=True)
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
+    opts = {}
+    if args.expert_path >= 0:
+        opts["expert_path"] = args.expert_path
+    # every rank holds a whole copy of the layer (the one-GPU engine): the headline at N = 1, the
+    # reference for the expert-parallel parity check and the replica figure at N > 1
+    spec, trunk, one_eng = synth.build_moe_layer_engine(SEED, n_experts=args.experts, device=local, options=opts)
+    use_ep = world > 1 and args.experts % world == 0 and not args.no_expert_parallel
+    extra = {}
+    ep_eng, ep_err = None, ""
+    if use_ep:
+        try:
+            ep_eng = pkg.Engine(spec.cfg, spec.is_mla, spec.is_dense, 8, local, rank, world)
+            ep_eng.set_option("allow_partial", 1)
+            for k, v in opts.items():
+                ep_eng.set_option(k, v)
+            ep_eng.load_all(trunk)
+            for ex in range(args.experts):
+                ep_eng.fill_expert(0, ex, SEED, *synth.expert_scales(spec.cfg, 0, ex, SEED))
+            ep_eng.finalize()
+        except Exception as exc:                               # noqa: BLE001
+            ep_err = repr(exc)[:300]
+        handles = ranks.gather(ep_eng.ep_export() if not ep_err else b"")
+        if not ep_err:
+            try:
+                ep_eng.ep_connect(handles)
+            except Exception as exc:                           # noqa: BLE001
+                ep_err = repr(exc)[:300]
+        if not ranks.all_ok(not ep_err):
+            raise SystemExit(f"expert-parallel engine could not be set up: {ep_err or 'another rank failed'}")
+        extra["expert_parallel"] = {"ranks": world, "routed_experts_per_rank": args.experts // world,
+                                    "parity": expert_parallel_parity(pkg, one_eng, ep_eng, ranks, rank)}
+    eng = ep_eng if use_ep else one_eng
+    sampler = ClockSampler(local)
+
+    # ---- headline: batch 1, device resident
+    sampler.start()
+    sampler.wait_first()
+    ranks.barrier()
+    each, phases, launches, _ = time_batch(pkg, eng, torch, 1, args.steps, warmup, phases=not use_ep)
+    ranks.barrier()
+    local_ms_per_step = float(each.sum()) / args.steps
+    ms_per_step = ranks.reduce(local_ms_per_step, "max")        # the slowest rank's
+    # expert parallel: all ranks serve the same token; replicas only when asked for: one stream per rank
+    streams = 1 if (use_ep or world == 1) else world
+    value = streams * 1e3 / ms_per_step
+
+    # ---- end to end: host buffers (pinned) through the C-ABI op, H2D and D2H inside the timing
+    e2e_s, h2d, d2h = time_e2e(L, eng, torch, ranks, args.steps, warmup)
+    clocks = sampler.stop()       # sampled over the device-timed and the end-to-end regions
+    e2e = {"value": streams * args.steps / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+           "d2h_bytes_per_step": d2h, "ms_per_step": 1e3 * e2e_s / args.steps}
+
+    # ---- roofline of the dominant kernel
+    router_bytes = args.experts * 4096 * 2
+    layer_bytes = 9 * EXPERT_BYTES + router_bytes
+    one_launch = launches == args.steps
+    if use_ep:
+        # every rank reads the router matrix and the shared expert, and the routed picks it owns
+        all_bytes = world * (EXPERT_BYTES + router_bytes) + 8 * EXPERT_BYTES
+        roofline = {"bound": "hbm", "kernel": "moe_decode_kernel, expert parallel (router + top-8 + own picks + shared expert + "
+                                              "row exchange over peer mappings + combine, batch 1)",
+                    "achieved": all_bytes / (ms_per_step * 1e-3) / 1e9, "peak": world * peak,
+                    "peak_kind": f"{world} x the {peak_kind} copy bandwidth", "unit": "GB/s",
+                    "frac": all_bytes / (ms_per_step * 1e-3) / 1e9 / (world * peak), "traffic": None,
+                    "algorithmic_bytes_per_launch": all_bytes, "ms_per_launch": ms_per_step,
+                    "note": "bytes all ranks read per step (each rank: router + shared expert; the 8 picks once), "
+                            "against the ranks' combined bandwidth"}
+    else:
+        layer = {"algorithmic_bytes_per_step": layer_bytes, "achieved": layer_bytes / (local_ms_per_step * 1e-3) / 1e9,
+                 "frac": layer_bytes / (local_ms_per_step * 1e-3) / 1e9 / peak}
+        if one_launch:
+            roofline = {"bound": "hbm", "kernel": "moe_decode_kernel (router + top-8 + 8 routed and 1 shared expert + combine, batch 1)",
+                        "achieved": layer["achieved"], "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s",
+                        "frac": layer["frac"], "traffic": DECODE_TRAFFIC_NCU, "algorithmic_bytes_per_launch": layer_bytes,
+                        "ms_per_launch": local_ms_per_step, "layer": layer}
+        else:
+            gateup_ms = phases[1]
+            achieved = 9 * GATEUP_BYTES / (gateup_ms * 1e-3) / 1e9 if gateup_ms > 0 else 0.0
+            roofline = {"bound": "hbm", "kernel": "gate/up + SwiGLU kernel of the chosen expert path (8 routed + 1 shared expert, batch 1)",
+                        "achieved": achieved, "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s",
+                        "frac": achieved / peak, "traffic": GATEUP_TRAFFIC_NCU,
+                        "algorithmic_bytes_per_launch": 9 * GATEUP_BYTES, "ms_per_launch": gateup_ms, "layer": layer}
+
+    if not use_ep:
+        extra["phase_ms_b1"] = ({"moe_decode_kernel": phases[0]} if one_launch else
+                                {"router+plan": phases[0], "gate_up": phases[1], "down": phases[2], "combine": phases[3]})
+    if use_ep:
+        # N independent replicas of the layer, one token stream each (no data-path collective)
+        ranks.barrier()
+        r_each, _, _, _ = time_batch(pkg, one_eng, torch, 1, args.steps, warmup, phases=False)
+        r_ms = ranks.reduce(float(r_each.sum()) / args.steps, "max")
+        extra["replicas"] = {"ranks": world, "tokens_per_s": world * 1e3 / r_ms, "ms_per_step": r_ms,
+                             "note": "one whole copy of the layer and one token stream per rank"}
+        ep_eng.close()
+    if rank == 0 and world == 1:
+        for B in [int(b) for b in args.batches.split(",") if b]:
+            eb, ph, _, _ = time_batch(pkg, one_eng, torch, B, max(10, args.steps // 10), 3)
+            idx, _ = one_eng.op_router(0, synth.moe_inputs(spec.cfg, B, SEED))
+            distinct = int(len(set(idx.ravel().tolist())))
+            ms = float(eb.mean())
+            extra[f"batch{B}"] = {"tokens_per_s": B * 1e3 / ms, "ms_per_step": ms, "distinct_experts": distinct,
+                                  "achieved_GBps": ((distinct + 1) * EXPERT_BYTES + ROUTER_BYTES) / (ms * 1e-3) / 1e9,
+                                  "phase_ms": ph}
+    one_eng.close()
+    if world == 1 and not args.no_attention_layers and args.experts == 288:
+        n = max(10, args.steps // 10)
+        extra["config3"] = time_attention_layers(pkg, torch, n, peak, local)
+        extra["decoder_layers"] = time_decoder_layers(pkg, torch, n, local)
+        extra["head_and_dense_mlp"] = time_head_and_dense(pkg, torch, n, local)
+        extra["mhc_site"] = time_mhc_site(pkg, torch, n, local)
+        if not use_ep and one_launch:
+            # the same kernel inside a whole decoder layer (after other kernels, cold instruction cache)
+            kda_layer_bytes = 286048984 + layer_bytes + 2 * 786432
+            ms = extra["decoder_layers"]["kda_moe_layer"]["ms"]
+            roofline["in_layer"] = {"what": "whole KDA + MoE decoder layer, one token: weights + state read and written",
+                                    "ms": ms, "algorithmic_bytes": kda_layer_bytes,
+                                    "frac": kda_layer_bytes / (ms * 1e-3) / 1e9 / peak}
+
+    # ---- the full-size model, as many layers as the GPUs hold (all 45 from four GPUs on)
+    if not args.no_full_model and args.experts == 288:
+        try:
+            extra["full_model"] = run_full_model(pkg, torch, ranks, local, rank, world, peak, args.full_model_layers,
+                                                 args.full_model_tokens)
+        except Exception as exc:                                   # noqa: BLE001
+            extra["full_model"] = {"error": repr(exc)[:300]}
+
     if rank == 0:
-        line = {"metric": "decode tokens/s through one full-size MoE layer, batch 1", "value": value, "unit": "tokens/s",
+        line = {"metric": METRIC, "value": value, "unit": "tokens/s",
                 "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms_per_step,
-                "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-                "dtype": "fp8_e4m3 weights, f32 activations and accumulation", "data": "synthetic",
-                "config": {"workload": "config 2: single MoE layer decode, hidden 4096, inter 2048, 288+1 experts, "
-                                       "top-8, batch 1", "l2": f"flushed before every step ({FLUSH_BYTES >> 21} MiB written, then {FLUSH_BYTES >> 21} MiB read so that no dirty line is left)",
-                           "parallelism": f"{world} independent replica(s), one token stream each"},
+                "higher_is_better": True, "scaling": "strong" if (use_ep or world == 1) else "weak", "vs_baseline": None,
+                "dtype": DTYPE, "data": "synthetic", "config": bench_config(world) if (use_ep or world == 1) else
+                dict(bench_config(1), parallelism=f"{world} independent replicas, one token stream each"),
                 "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
                 "extra": extra}
         print(json.dumps(line), flush=True)

@@ -130,3 +130,29 @@ def test_moe_op_with_pinned_host_buffers(small_layer, T):
     op = torch.full((T, spec.cfg.hidden), float("nan")).pin_memory()
     assert L.g5b_op_moe(eng.handle, 0, xp.numpy().ctypes.data, T, op.numpy().ctypes.data, 1) == 0, L.g5b_last_error()
     assert np.array_equal(op.numpy(), want)
+
+
+def test_two_engines_on_two_devices_in_one_process(gpu_lib, binding):
+    """Kernel set-up (the opt-in to large shared memory, SM counts, cooperative-launch support) is
+    kept per device: a second engine on another GPU of the same process must give the CPU path's
+    output too, in whichever order the two are used."""
+    if gpu_lib.g5b_device_count() < 2:
+        pytest.skip("needs two GPUs")
+    spec = synth.tiny_spec()
+    tensors = synth.make_model(spec, seed=21, recipe="baseline")
+    orc = binding.OracleModel(spec.cfg, spec.is_mla, spec.is_dense, 32, 2)
+    orc.load_all(tensors); orc.finalize()
+    engines = []
+    for dev in (0, 1):
+        e = pkg.Engine(spec.cfg, spec.is_mla, spec.is_dense, 32, dev)
+        e.load_all(tensors); e.finalize()
+        engines.append(e)
+    ids = np.random.default_rng(2).integers(0, spec.cfg.vocab, 12).tolist()
+    want, _ = orc.forward(ids)
+    for e in (engines[1], engines[0], engines[1]):
+        e.reset()
+        got, _ = e.forward(ids)
+        assert common.rel_err(got, want) < 1e-3 and int(np.argmax(got)) == int(np.argmax(want))
+    for e in engines:
+        e.close()
+    orc.close()
