@@ -143,6 +143,12 @@ __device__ __forceinline__ void st_release_sys(unsigned long long *p, unsigned l
 }
 
 
+// One more on a 64-bit counter another GPU waits on, with release semantics at system scope.
+__device__ __forceinline__ void red_release_sys_add(unsigned long long *p, unsigned long long v)
+{
+    asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+
 __device__ __forceinline__ unsigned long long global_ns()
 {
     unsigned long long t;

@@ -92,7 +92,8 @@ struct g5b_engine {
     void **ep_peers_dev = nullptr;
     std::vector<void *> ep_opened;               // peer mappings to close
     std::vector<void *> ep_standins;             // local stand-ins for peers (option ep_loopback)
-    unsigned long long ep_step = 0;
+    unsigned long long ep_step = 0;              // exchanges so far (both kernels): picks the row buffer
+    unsigned long long ep_decode_launches = 0;   // of them, by the one-token kernel (its arrival counters count CTAs)
     int *ep_arrive = nullptr;
     int ep_wait_ms = 5000;                       // wall-clock limit of a wait for the other ranks (option "ep_wait_ms")
     bool dirty = false;                          // a call failed half-way: session state is undefined until reset
@@ -653,11 +654,11 @@ static int run_moe(g5b_engine *e, Layer &w, const float *x, int n, float *out, i
     const bool ep_decode = e->ep_size > 1 && (shared_in_plan || !with_shared);
     if (e->expert_path == 2 && (one_gpu_decode || ep_decode) && moe_decode_supported(s, n)) {
         DecodeEp ep{e->ep_rank, e->ep_size, e->ep_peers_dev, EP_FLAG_BYTES + (size_t)((e->ep_step + 1) & 1) * e->ep_rows_bytes,
-                    e->ep_step + 1, e->ep_arrive, (unsigned long long)e->ep_wait_ms * 1000000ull};
+                    e->ep_decode_launches + 1, (unsigned long long)e->ep_wait_ms * 1000000ull};
         if (moe_decode(e->st, out, x, w.router.w, w.router.dt, w.bias, w.table_dev, e->rscore, e->ridx, e->rw, e->act,
                        e->contrib, s, with_shared, e->grid_sync, &e->grid_launches, e->tile_done, e->err_dev,
                        ep_decode ? &ep : nullptr) == 0) {
-            if (ep_decode) ++e->ep_step;
+            if (ep_decode) { ++e->ep_step; ++e->ep_decode_launches; }
             prof_mark(e, 1); prof_mark(e, 2); prof_mark(e, 3); prof_mark(e, 4);
             prof_collect(e, 4);
             return 0;
@@ -1670,6 +1671,7 @@ static int ep_publish_peers(g5b_engine *e, const std::vector<void *> &peers)
     CU(cudaMemcpy(e->ep_peers_dev, peers.data(), sizeof(void *) * peers.size(), cudaMemcpyHostToDevice));
     e->ep_connected = true;
     e->ep_step = 0;
+    e->ep_decode_launches = 0;
     return 0;
 }
 
@@ -1727,6 +1729,7 @@ extern "C" int g5b_engine_ep_resync(g5b_engine *e)
     CU(cudaStreamSynchronize(e->st));
     if (e->err_host) *e->err_host = 0;
     e->ep_step = 0;
+    e->ep_decode_launches = 0;
     return 0;
 }
 

@@ -163,9 +163,8 @@ struct DecodeEp {
     int rank, size;
     void *const *peers;
     size_t rows_off;
-    unsigned long long step;
-    int *arrive;
-    unsigned long long wait_ns;    // wall-clock limit of the wait for the other ranks' step words
+    unsigned long long launch;     // expert-parallel launches of the decode kernel so far, this one included
+    unsigned long long wait_ns;    // wall-clock limit of the wait for the other ranks' arrival counters
 };
 int moe_decode(cudaStream_t st, float *out, const float *x, const void *gate, int gate_dt, const float *bias,
                const ExpertW *experts, float *score, int *idx, float *w, void *act, float *contrib,

@@ -47,13 +47,14 @@ struct DecodeArgs {
     int *tile_done;
     int *err;
     // expert parallel (ep_size > 1): this rank owns experts [n_local0, n_local0 + n_local); experts[]
-    // is indexed by local expert, shared expert last; peers[r] is rank r's exchange region (ep_size
-    // step words, then at rows_off this step's row buffer [K][E])
+    // is indexed by local expert, shared expert last; peers[r] is rank r's exchange region: ep_size
+    // step words (the multi-token exchange kernel's), ep_size arrival counters (this kernel's: word
+    // ep_size + q counts the CTAs of rank q that have delivered, over all launches), then at rows_off
+    // this step's row buffer [K][E]
     int ep_rank, ep_size, n_local0, n_local;
     void *const *peers;
     size_t rows_off;
-    unsigned long long ep_step;
-    int *ep_arrive;
+    unsigned long long ep_launch;      // expert-parallel launches of this kernel so far, this one included
     unsigned long long ep_wait_ns;
 };
 
@@ -98,7 +99,8 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
     const int tps_g = a.I / 16;                 // gate/up items per expert
     const int tps_d = a.E / MM_ROWS;            // down items per expert
     const int nsl = a.K + (a.with_shared ? 1 : 0);
-    const int n_gu = nsl * tps_g, n_dn = nsl * tps_d;
+    const int sh_g = a.with_shared ? tps_g : 0;   // gate/up items of the shared expert: known before the plan
+    const int n_dn_all = nsl * tps_d;             // down items when every pick is this GPU's
     const int scols_g = a.E / a.bc, scols_d = a.I / a.bc;
     const size_t scale_off = (size_t)MM_ROWS * MM_PITCH;
     const size_t stage_bytes = scale_off + 512;
@@ -113,7 +115,8 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
     uint64_t *sel_ready = plan_ready + 1;        // the picks' expert pointers and s_local are written
     __shared__ ExpertW s_ew[MM_MAX_SLOTS];       // slot j < K: j-th routed pick; slot K: shared expert
     __shared__ float s_w[MM_MAX_SLOTS];
-    __shared__ int s_local[MM_MAX_SLOTS];        // the slot's expert lives on this rank
+    __shared__ int s_lslot[MM_MAX_SLOTS];        // the picks whose experts live on this rank, in top-k order
+    __shared__ int s_nloc;                       // how many (K on a single GPU)
     __shared__ int s_flag;
     __shared__ int my_tiles[MM_MAX_ITEMS], my_last[MM_MAX_ITEMS];
     __shared__ float wmax[MM_THREADS / 32];
@@ -126,15 +129,25 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
         mbar_init(sel_ready, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (threadIdx.x == 32 && a.with_shared) { s_ew[a.K] = a.experts[a.n_local]; s_local[a.K] = 1; }
+    if (threadIdx.x == 32 && a.with_shared) s_ew[a.K] = a.experts[a.n_local];
     __syncthreads();
 
-    // item g of the gate/up list -> (slot, row tile); shared expert first
+    // Work items are numbered over the picks this rank owns only, so that the round-robin deal stays
+    // even when other ranks own some of the picks. Gate/up: the shared expert's row tiles first (they
+    // need no plan), then the local picks in top-k order. Down: the local picks, then the shared
+    // expert. (s_lslot / s_nloc are valid once the plan is made; on one GPU they are the identity.)
     auto gu_slot = [&](int g, int &slot, int &rt) {
-        if (a.with_shared) {
-            if (g < tps_g) { slot = a.K; rt = g; }
-            else { slot = (g - tps_g) / tps_g; rt = (g - tps_g) % tps_g; }
-        } else { slot = g / tps_g; rt = g % tps_g; }
+        if (g < sh_g) { slot = a.K; rt = g; }
+        else {
+            const int j = (g - sh_g) / tps_g;
+            slot = a.ep_size > 1 ? s_lslot[j] : j;
+            rt = (g - sh_g) % tps_g;
+        }
+    };
+    auto dn_slot = [&](int g, int nloc, int &slot, int &rt) {
+        const int j = g / tps_d;
+        rt = g % tps_d;
+        slot = j < nloc ? (a.ep_size > 1 ? s_lslot[j] : j) : a.K;
     };
     bool ok = true;
 
@@ -185,12 +198,14 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
                 if (lane == j) { my_pick = (int)bi; my_w = wsel; }
             }
             DT_MARK_P(13);
-            if (lane < a.K) {                         // the K pointer records are fetched side by side
+            {                                         // the K pointer records are fetched side by side
                 const int le = my_pick - a.n_local0;
-                const bool local = le >= 0 && le < a.n_local;
-                s_local[lane] = local;
+                const bool local = lane < a.K && le >= 0 && le < a.n_local;
                 if (local) s_ew[lane] = a.experts[le];
-                if (blockIdx.x == 0) a.idx[lane] = my_pick;
+                if (lane < a.K && blockIdx.x == 0) a.idx[lane] = my_pick;
+                const unsigned lm = __ballot_sync(0xffffffffu, local);
+                if (local) s_lslot[__popc(lm & ((1u << lane) - 1u))] = lane;
+                if (lane == 0) s_nloc = __popc(lm);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(sel_ready);
@@ -217,15 +232,17 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
             __syncwarp();
             if (lane == 0) mbar_arrive(plan_ready);
         };
-        for (int g = blockIdx.x; g < n_gu && ok; g += gridDim.x) {
-            int slot, rt;
-            gu_slot(g, slot, rt);
-            if (slot != a.K && !have_plan) {
+        int n_gu = sh_g;                               // until the plan is made only the shared expert's items exist
+        for (int g = blockIdx.x; ok; g += gridDim.x) {
+            if (g >= sh_g && !have_plan) {
                 ok = make_plan();
                 if (!ok) break;
                 have_plan = true;
+                n_gu = sh_g + s_nloc * tps_g;
             }
-            if (a.ep_size > 1 && !s_local[slot]) continue;             // another rank's expert
+            if (g >= n_gu) break;
+            int slot, rt;
+            gu_slot(g, slot, rt);
             const ExpertW ew = s_ew[slot];
             for (int kh = 0; kh < a.E / MM_CB && ok; kh++, it++) {
                 const int s = it % MM_NS;
@@ -243,19 +260,16 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
                 }
             }
         }
-        if (ok && !have_plan && n_dn > 0) {          // a CTA with nothing but shared rows still needs the plan below
-            ok = make_plan();
-            have_plan = ok;
-        }
         // down: weights are prefetched before the activations exist; their copy follows the grid point
         bool acts_visible = false;
         int pending = 0, pend_stage[MM_NS], pend_slot[MM_NS];
-        int last_g = -1;                               // this CTA's last down item on this rank
-        for (int g = blockIdx.x; g < n_dn; g += gridDim.x)
-            if (a.ep_size == 1 || s_local[g / tps_d]) last_g = g;
+        const int nloc_p = ok ? s_nloc : 0;
+        const int n_dn = ok ? (nloc_p + (a.with_shared ? 1 : 0)) * tps_d : 0;
+        // this CTA's last down item
+        const int last_g = (int)blockIdx.x < n_dn ? (int)blockIdx.x + ((n_dn - 1 - (int)blockIdx.x) / (int)gridDim.x) * (int)gridDim.x : -1;
         for (int g = blockIdx.x; g < n_dn && ok; g += gridDim.x) {
-            const int slot = g / tps_d, rt = g % tps_d;
-            if (a.ep_size > 1 && !s_local[slot]) continue;
+            int slot, rt;
+            dn_slot(g, nloc_p, slot, rt);
             const ExpertW ew = s_ew[slot];
             const int s = it % MM_NS;
             if (it >= MM_NS) ok = mbar_wait(&empty[s], ((it / MM_NS) - 1) & 1, a.err, 1);
@@ -401,15 +415,17 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
 
         // ---- gate/up items
         bool have_sel = false;
-        for (int g = blockIdx.x; g < n_gu && ok; g += gridDim.x) {
-            int slot, rt;
-            gu_slot(g, slot, rt);
-            if (a.ep_size > 1 && slot != a.K && !have_sel) {   // which of the picks are this rank's
+        int n_gu = a.ep_size > 1 ? sh_g : sh_g + a.K * tps_g;     // expert parallel: the local picks are not known yet
+        for (int g = blockIdx.x; ok; g += gridDim.x) {
+            if (a.ep_size > 1 && g >= sh_g && !have_sel) {       // which of the picks are this rank's
                 ok = mbar_wait_warp(sel_ready, 0, a.err, 10);
                 if (!ok) break;
                 have_sel = true;
+                n_gu = sh_g + s_nloc * tps_g;
             }
-            if (a.ep_size > 1 && !s_local[slot]) continue;
+            if (g >= n_gu) break;
+            int slot, rt;
+            gu_slot(g, slot, rt);
             float accf[4] = {0.f, 0.f, 0.f, 0.f};
             for (int kh = 0; kh < a.E / MM_CB && ok; kh++, it++) {
                 const int s = it % MM_NS;
@@ -457,9 +473,11 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
 
         // ---- down items (the stage's full barrier covers the activation terms too)
         if (ok && a.ep_size > 1 && !have_sel) { ok = mbar_wait_warp(sel_ready, 0, a.err, 10); have_sel = ok; }
+        const int nloc_c = a.ep_size > 1 ? (ok ? s_nloc : 0) : a.K;
+        const int n_dn = ok ? (nloc_c + (a.with_shared ? 1 : 0)) * tps_d : 0;
         for (int g = blockIdx.x; g < n_dn && ok; g += gridDim.x) {
-            const int slot = g / tps_d, rt = g % tps_d;
-            if (a.ep_size > 1 && !s_local[slot]) continue;
+            int slot, rt;
+            dn_slot(g, nloc_c, slot, rt);
             const int s = it % MM_NS;
             ok = mbar_wait_warp(&full[s], (it / MM_NS) & 1, a.err, 2);
             ok = __all_sync(0xffffffffu, ok);
@@ -501,39 +519,35 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
             ok = __all_sync(0xffffffffu, ok);
         }
         if (ok && a.ep_size > 1) {
-            // ---- expert parallel: every rank's rows are on their way into every rank's buffer. The
-            // last CTA of this rank to get here publishes this rank's step word everywhere; then all
-            // CTAs wait (bounded) for every rank's word and combine a share of the output rows.
-            __threadfence_system();
+            // ---- expert parallel: this CTA's rows are on their way into every rank's buffer. One
+            // release-add per rank (system scope; through the barrier before it, it covers the stores
+            // of every thread of the CTA) counts this CTA as done on that rank - no election of a last
+            // CTA and no second fence. A rank is complete on a peer when its counter there has grown
+            // by one per CTA; only the CTAs that hold a share of the combine wait for that.
             asm volatile("bar.sync 1, %0;" ::"r"(MM_CONS * 32) : "memory");
-            if (ctid == 0) {
-                const int prev = atomicAdd(a.ep_arrive, 1);
-                s_flag = prev == (int)gridDim.x - 1;
-                if (s_flag) *a.ep_arrive = 0;
-            }
-            asm volatile("bar.sync 1, %0;" ::"r"(MM_CONS * 32) : "memory");
-            if (s_flag) {
-                __threadfence_system();
-                if (ctid < a.ep_size)
-                    st_release_sys(reinterpret_cast<unsigned long long *>(a.peers[ctid]) + a.ep_rank, a.ep_step);
-            }
-            asm volatile("bar.sync 1, %0;" ::"r"(MM_CONS * 32) : "memory");
-            if (ctid == 0) s_flag = 1;
-            asm volatile("bar.sync 1, %0;" ::"r"(MM_CONS * 32) : "memory");
-            if (ctid < a.ep_size) {
-                const unsigned long long *mine = reinterpret_cast<const unsigned long long *>(a.peers[a.ep_rank]) + ctid;
-                const bool seen = wait_word_sys(mine, a.ep_step, a.ep_wait_ns);
-                if (!seen) { atomicExch(a.err, 20 + ctid); s_flag = 0; }
-            }
-            asm volatile("bar.sync 1, %0;" ::"r"(MM_CONS * 32) : "memory");
-            if (s_flag) {
-                const float *rows = reinterpret_cast<const float *>(static_cast<const uint8_t *>(a.peers[a.ep_rank]) + a.rows_off);
-                for (int d = blockIdx.x * MM_CONS * 32 + ctid; d < a.E; d += gridDim.x * MM_CONS * 32) {
-                    double sum = 0.0;
-                    for (int j = 0; j < a.K; j++) sum += (double)s_w[j] * (double)__ldcg(rows + (size_t)j * a.E + d);
-                    float o = (float)sum;
-                    if (a.with_shared) o = __fadd_rn(o, __ldcg(a.contrib + (size_t)a.K * a.E + d));
-                    a.out[d] = o;
+            const int cnt0 = a.ep_size;                             // the counters follow the step words
+            if (ctid < a.ep_size)
+                red_release_sys_add(reinterpret_cast<unsigned long long *>(a.peers[ctid]) + cnt0 + a.ep_rank, 1ull);
+            DT_MARK(15);
+            if ((int)blockIdx.x * MM_CONS * 32 < a.E) {
+                if (ctid == 0) s_flag = 1;
+                asm volatile("bar.sync 1, %0;" ::"r"(MM_CONS * 32) : "memory");
+                if (ctid < a.ep_size) {
+                    const unsigned long long *mine = reinterpret_cast<const unsigned long long *>(a.peers[a.ep_rank]) + cnt0 + ctid;
+                    const bool seen = wait_word_sys(mine, a.ep_launch * gridDim.x, a.ep_wait_ns);
+                    if (!seen) { atomicExch(a.err, 20 + ctid); s_flag = 0; }
+                }
+                asm volatile("bar.sync 1, %0;" ::"r"(MM_CONS * 32) : "memory");
+                DT_MARK(12);
+                if (s_flag) {
+                    const float *rows = reinterpret_cast<const float *>(static_cast<const uint8_t *>(a.peers[a.ep_rank]) + a.rows_off);
+                    for (int d = blockIdx.x * MM_CONS * 32 + ctid; d < a.E; d += gridDim.x * MM_CONS * 32) {
+                        double sum = 0.0;
+                        for (int j = 0; j < a.K; j++) sum += (double)s_w[j] * (double)__ldcg(rows + (size_t)j * a.E + d);
+                        float o = (float)sum;
+                        if (a.with_shared) o = __fadd_rn(o, __ldcg(a.contrib + (size_t)a.K * a.E + d));
+                        a.out[d] = o;
+                    }
                 }
             }
         } else if (ok) {
@@ -542,7 +556,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) moe_decode_kernel(const DecodeA
             __threadfence();
             asm volatile("bar.sync 1, %0;" ::"r"(MM_CONS * 32) : "memory");
             int mine = 0;
-            for (int g = blockIdx.x; g < n_dn; g += gridDim.x) mine++;
+            for (int g = blockIdx.x; g < n_dn_all; g += gridDim.x) mine++;
             if (mine > MM_MAX_ITEMS) { if (ctid == 0) atomicExch(a.err, 4); mine = 0; }
             if (ctid < mine) {
                 const int rt = (blockIdx.x + ctid * gridDim.x) % tps_d;
@@ -613,7 +627,7 @@ int moe_decode(cudaStream_t st, float *out, const float *x, const void *gate, in
                  s.E, s.I, s.NE, s.K, s.br, s.bc, with_shared, s.norm_topk, s.limit, s.routed_scale,
                  sync, (*launches) * (unsigned long long)sms, tile_done, err,
                  ep ? ep->rank : 0, ep ? ep->size : 1, s.n_local0, s.n_local, ep ? ep->peers : nullptr,
-                 ep ? ep->rows_off : 0, ep ? ep->step : 0ull, ep ? ep->arrive : nullptr, ep ? ep->wait_ns : 0ull};
+                 ep ? ep->rows_off : 0, ep ? ep->launch : 0ull, ep ? ep->wait_ns : 0ull};
     void *params[] = {&a};
     cudaError_t rc;
     rc = cudaLaunchCooperativeKernel((const void *)moe_decode_kernel, dim3(sms), dim3(MM_THREADS), params,
