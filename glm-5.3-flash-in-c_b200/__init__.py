@@ -115,6 +115,7 @@ def lib() -> C.CDLL:
     L.g5b_rmsnorm_noalloc.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_float, C.c_void_p]
     L.g5b_time_op.argtypes = [C.c_void_p, C.c_char_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_void_p,
                               C.c_int, C.c_size_t, C.c_void_p, C.c_void_p]
+    L.g5b_time_matvec.argtypes = [C.c_void_p, C.c_char_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_size_t, C.c_void_p]
     _lib = L
     return L
 

@@ -55,7 +55,7 @@ def build(verbose: bool = False) -> str:
     with cf.ThreadPoolExecutor(max_workers=min(8, len(sources))) as pool:
         objs = list(pool.map(compile_one, sources))
     if _stale(OUT, objs):
-        cmd = [NVCC, "-shared", "-ccbin", HOST_CXX, "-o", OUT] + objs + ["-lcudart", "-lcublas"]
+        cmd = [NVCC, "-shared", "-ccbin", HOST_CXX, "-o", OUT] + objs + ["-lcudart"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")

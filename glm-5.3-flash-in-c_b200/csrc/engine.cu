@@ -118,7 +118,8 @@ struct g5b_engine {
     float *mq_raw, *mct, *mwk, *mgate, *mwp, *mq, *mqidx, *mcb, *macc, *mscore, *minvq;
     double *mqa, *mdsc, *mpart = nullptr, *mstats = nullptr;
     int *mcount = nullptr;
-    GemmTokens *gemm = nullptr;                          // BF16 projections of 8+ tokens (cuBLAS)
+    TcGemm *tc = nullptr;                                // FP8 / BF16 projections of 8+ positions on tcgen05
+    int tensor_gemm = 1;                                 // option "tensor_gemm": 0 keeps 8+ positions on the one-token kernels
     float *post_h = nullptr; int post_n = 0;             // positions whose hc_post is still owed (run_layer)
     double *hc_part = nullptr; int *hc_count = nullptr;  // fused mHC site: partial sums and per-token counters
     void *xterms = nullptr; float *xinv = nullptr;      // batched expert kernels: F16 terms of the activations
@@ -290,6 +291,7 @@ extern "C" int g5b_engine_set_option(g5b_engine *e, const char *name, int value)
         e->n_seq = value;
         return 0;
     }
+    if (!strcmp(name, "tensor_gemm")) { e->tensor_gemm = value; return 0; }
     if (!strcmp(name, "ep_loopback")) return value ? ep_loopback(e) : 0;
     if (!strcmp(name, "ep_wait_ms")) {
         if (value < 1 || value > 600000) return fail("ep_wait_ms is 1..600000");
@@ -603,8 +605,9 @@ extern "C" int g5b_engine_finalize(g5b_engine *e)
         const int P = c.kda_heads * c.kda_head_dim;
         int max_c = c.hidden;
         for (int v : {P, c.q_lora, c.kv_lora, c.kda_head_dim, c.mla_heads * c.v_head}) max_c = v > max_c ? v : max_c;
-        e->gemm = gemm_tokens_create(e->st, CHUNK, max_c);
-        if (!e->gemm) return fail("cuBLAS context or its scratch could not be created");
+        for (int v : {c.dense_inter, c.moe_inter * c.n_shared}) max_c = v > max_c ? v : max_c;
+        e->tc = tc_gemm_create(max_c, e->err_dev);
+        if (!e->tc) return fail("the tensor-core projection path could not be set up (tensor-map encoder or scratch)");
     }
     e->cached_seq.assign((size_t)e->n_seq, 0);
     e->finalized = true;
@@ -726,16 +729,19 @@ static int run_moe(g5b_engine *e, Layer &w, const float *x, int n, float *out, i
     return 0;
 }
 
+static int proj_batch(g5b_engine *e, const GemvSeg *segs, int n, int T, bool early = false);
+static int proj(g5b_engine *e, const DMat &m, const float *x, int ldx, float *y, int ldy, int T,
+                const float *xinv = nullptr, const float *xw = nullptr);
+
 static int run_mlp(g5b_engine *e, Layer &w, const float *x, int n, float *out)
 {
     const g5b_config &c = e->c;
     const int DI = c.dense_inter;
     if (!w.d_gate.loaded() || !w.d_up.loaded() || !w.d_down.loaded()) return fail("this layer's dense MLP was not loaded");
     GemvSeg g[2] = {make_seg(w.d_gate, x, c.hidden, e->gu, 2 * DI), make_seg(w.d_up, x, c.hidden, e->gu + DI, 2 * DI)};
-    gemv_batch(e->st, g, 2, n);
+    if (proj_batch(e, g, 2, n)) return -1;
     swiglu(e->st, e->dact, e->gu, DI, n, c.swiglu_limit);
-    gemv(e->st, w.d_down, e->dact, DI, out, c.hidden, n);
-    return 0;
+    return proj(e, w.d_down, e->dact, DI, out, c.hidden, n);
 }
 
 // From this point of the main stream on, fetch a matrix into L2 on the side stream: the kernels
@@ -749,24 +755,25 @@ static void prefetch_beside(g5b_engine *e, const DMat &m)
     l2_prefetch(e->side, m.w, m.bytes());
 }
 
-// Several products sharing (some of) their inputs: BF16 matrices with 8 or more tokens go to the
-// GEMM path, the rest to the GEMV kernel in one launch.
-static int proj_batch(g5b_engine *e, const GemvSeg *segs, int n, int T, bool early = false)
+// Several products sharing (some of) their inputs: with 8 or more positions, FP8 (128 x 128 blocks)
+// and BF16 matrices whose rows fill 128-row tiles go to the tcgen05 kernel, which reads the weights
+// once; the rest (few rows, odd shapes) to the one-token kernel in one launch.
+static int proj_batch(g5b_engine *e, const GemvSeg *segs, int n, int T, bool early)
 {
-    if (T < 8 || !e->gemm) { gemv_batch(e->st, segs, n, T, early); return 0; }
-    gemm_tokens_new_input(e->gemm);
+    if (T < 8 || !e->tc || e->tensor_gemm == 0) { gemv_batch(e->st, segs, n, T, early); return 0; }
+    tc_gemm_new_input(e->tc);
     GemvSeg rest[GEMV_MAX_SEG];
     int nr = 0;
     for (int i = 0; i < n; i++) {
-        if (gemm_tokens_takes(e->gemm, segs[i], T)) {
-            if (gemm_tokens_run(e->gemm, e->st, segs[i], T)) return fail("the cuBLAS GEMM of a projection failed");
+        if (tc_gemm_takes(e->tc, segs[i], T)) {
+            if (tc_gemm_run(e->tc, e->st, segs[i], T)) return fail("the tensor-core projection could not be launched");
         } else rest[nr++] = segs[i];
     }
     if (nr) gemv_batch(e->st, rest, nr, T);
     return 0;
 }
 static int proj(g5b_engine *e, const DMat &m, const float *x, int ldx, float *y, int ldy, int T,
-                const float *xinv = nullptr, const float *xw = nullptr)
+                const float *xinv, const float *xw)
 {
     GemvSeg s = make_seg(m, x, ldx, y, ldy, xinv, xw);
     return proj_batch(e, &s, 1, T);
@@ -853,7 +860,7 @@ static int run_mla(g5b_engine *e, Layer &w, const float *x, int n, int cached, f
     mla_vout(e->st, e->macc, e->mcb, w.kv_b, n, s);
     {
         GemvSeg o = make_seg(w.mo, e->macc, c.mla_heads * c.v_head, out, E);
-        gemv_batch(e->st, &o, 1, n, true);
+        if (proj_batch(e, &o, 1, n, true)) return -1;
     }
     return 0;
 }
@@ -1111,7 +1118,7 @@ extern "C" void g5b_engine_free(g5b_engine *e)
     if (!e) return;
     cudaSetDevice(e->device);
     cudaStreamSynchronize(e->st);
-    gemm_tokens_free(e->gemm);
+    tc_gemm_free(e->tc);
     for (void *p : e->owned) cudaFree(p);
     for (void *p : e->ep_opened) cudaIpcCloseMemHandle(p);
     for (void *p : e->ep_standins) cudaFree(p);
@@ -1640,6 +1647,37 @@ extern "C" int g5b_time_op(g5b_engine *e, const char *op, int layer, const float
     }
     CU(cudaGetLastError());
     if (ms_total) *ms_total = (float)total;
+    return check_device_error(e);
+}
+
+// Time `iters` products of one loaded matrix with T positions (the path the forward pass takes for
+// that many positions), events around each product, L2 flushed before each.
+extern "C" int g5b_time_matvec(g5b_engine *e, const char *name, const float *x_dev, int T, float *y_dev, int iters,
+                               size_t flush_bytes, float *ms_each)
+{
+    if (!e || !e->finalized) return fail("time_matvec before finalize");
+    CU(cudaSetDevice(e->device));
+    if (T < 1 || T > CHUNK) return fail("time_matvec takes 1..%d positions", CHUNK);
+    DMat *m = find_mat(e, name);
+    if (!m) return fail("no loaded matrix named %s", name);
+    if (flush_bytes > e->flush_bytes) {
+        if (e->flush_buf) cudaFree(e->flush_buf);
+        e->flush_buf = nullptr; e->flush_bytes = 0;
+        CU(cudaMalloc(&e->flush_buf, flush_bytes));
+        e->flush_bytes = flush_bytes;
+    }
+    std::vector<cudaEvent_t> ev((size_t)2 * iters, nullptr);
+    struct EvGuard { std::vector<cudaEvent_t> &v; ~EvGuard() { for (cudaEvent_t x : v) if (x) cudaEventDestroy(x); } } guard{ev};
+    for (auto &x : ev) CU(cudaEventCreate(&x));
+    for (int i = 0; i < iters; i++) {
+        if (flush_bytes) flush_l2(e->st, e->flush_buf, flush_bytes);
+        CU(cudaEventRecord(ev[2 * i], e->st));
+        if (proj(e, *m, x_dev, m->cols, y_dev, m->rows, T)) { cudaStreamSynchronize(e->st); return -1; }
+        CU(cudaEventRecord(ev[2 * i + 1], e->st));
+    }
+    CU(cudaStreamSynchronize(e->st));
+    for (int i = 0; i < iters; i++) CU(cudaEventElapsedTime(&ms_each[i], ev[2 * i], ev[2 * i + 1]));
+    CU(cudaGetLastError());
     return check_device_error(e);
 }
 

@@ -61,16 +61,17 @@ inline void gemv(cudaStream_t st, const DMat &m, const float *x, int ldx, float 
     gemv_batch(st, &s, 1, T);
 }
 
-// ---- gemm_tokens.cu -----------------------------------------------------------------------
-// BF16 matrices times 8..max_t tokens as a cuBLAS GEMM on exact three-term BF16 splits of the FP32
-// activations. Segments that share an input reuse its split within one burst of calls;
-// gemm_tokens_new_input forgets it (call it whenever the input buffers get new contents).
-struct GemmTokens;
-GemmTokens *gemm_tokens_create(cudaStream_t st, int max_t, int max_c);
-void gemm_tokens_free(GemmTokens *g);
-void gemm_tokens_new_input(GemmTokens *g);
-bool gemm_tokens_takes(const GemmTokens *g, const GemvSeg &s, int T);
-int  gemm_tokens_run(GemmTokens *g, cudaStream_t st, const GemvSeg &s, int T);
+// ---- tc_gemm.cu ---------------------------------------------------------------------------
+// FP8 block-scaled (128 x 128 blocks) and BF16 matrices times 8..64 positions on tcgen05 tensor
+// cores, weights streamed once by TMA; activations as exact 16-bit term sums. Segments that share
+// an input reuse its terms within one burst of calls; tc_gemm_new_input forgets them (call it
+// whenever the input buffers get new contents). err: where a bounded wait that ran out is recorded.
+struct TcGemm;
+TcGemm *tc_gemm_create(int max_c, int *err);
+void tc_gemm_free(TcGemm *g);
+void tc_gemm_new_input(TcGemm *g);
+bool tc_gemm_takes(const TcGemm *g, const GemvSeg &s, int T);
+int  tc_gemm_run(TcGemm *g, cudaStream_t st, const GemvSeg &s, int T);
 
 // ---- elementwise.cu -----------------------------------------------------------------------
 void rms_factor(cudaStream_t st, const float *x, int n, int ld, int rows, float eps, float *inv);

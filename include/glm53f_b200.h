@@ -288,6 +288,10 @@ uint64_t g5b_launch_count(void);
  * the residual stream h, updated in place. */
 int g5b_time_op(g5b_engine *e, const char *op, int layer, const float *x_dev, int T, int cached,
                 float *out_dev, int iters, size_t flush_bytes, float *ms_total, float *ms_each);
+/* The same for one product y[T][rows] = W x[T][cols] of a loaded matrix, on the path the forward pass
+ * takes for T positions (x_dev, y_dev: device buffers of T * cols and T * rows floats). */
+int g5b_time_matvec(g5b_engine *e, const char *name, const float *x_dev, int T, float *y_dev, int iters,
+                    size_t flush_bytes, float *ms_each);
 /* With the "profile" option on, every MoE op also records events between its phases; this
  * reads the accumulated milliseconds of [router+plan, gate/up, down, combine] and the number of
  * ops they cover, and optionally clears them. */
