@@ -115,6 +115,8 @@ def lib() -> C.CDLL:
     L.g5b_rmsnorm_noalloc.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_float, C.c_void_p]
     L.g5b_time_op.argtypes = [C.c_void_p, C.c_char_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_void_p,
                               C.c_int, C.c_size_t, C.c_void_p, C.c_void_p]
+    L.g5b_engine_decode_sampled.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_float, C.c_float, C.c_uint64, C.c_void_p]
+    L.g5b_sample_host.argtypes = [C.c_void_p, C.c_int, C.c_float, C.c_float, C.c_uint64, C.c_uint64, C.c_void_p, C.c_int]
     L.g5b_time_matvec.argtypes = [C.c_void_p, C.c_char_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_size_t, C.c_void_p]
     _lib = L
     return L
@@ -377,6 +379,13 @@ class Engine(FlatModel):
             self._err("decode_greedy")
         return out
 
+    def decode_sampled(self, first: int, n: int, temperature: float, top_p: float, seed: int):
+        out = np.zeros(n, np.int32)
+        if self.L.g5b_engine_decode_sampled(self.handle, first, n, C.c_float(temperature), C.c_float(top_p), seed,
+                                            out.ctypes.data) != 0:
+            self._err("decode_sampled")
+        return out
+
     def sync(self):
         if self.L.g5b_engine_sync(self.handle) != 0:
             self._err("sync")
@@ -391,3 +400,13 @@ class Engine(FlatModel):
             self.close()
         except Exception:
             pass
+
+
+def sample_host(logits, temperature: float, top_p: float, seed: int, step: int, device: int = 0) -> int:
+    """One draw of the device sampler from host logits (g5b_sample_host)."""
+    lg = _f32(logits).ravel()
+    tok = C.c_int(-1)
+    if lib().g5b_sample_host(lg.ctypes.data, lg.size, C.c_float(temperature), C.c_float(top_p), seed, step,
+                             C.addressof(tok), device) != 0:
+        raise RuntimeError("g5b_sample_host failed: " + (lib().g5b_last_error() or b"").decode())
+    return tok.value

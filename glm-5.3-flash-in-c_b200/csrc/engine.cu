@@ -1049,6 +1049,40 @@ extern "C" int g5b_engine_decode_greedy(g5b_engine *e, int first, int n, int *ou
     return 0;
 }
 
+// Sampled decode without host round trips: each step's token is drawn on the device from that
+// step's logits (sample.cu) and is the next step's input. temperature <= 0 decodes greedily.
+extern "C" int g5b_engine_decode_sampled(g5b_engine *e, int first, int n, float temperature, float top_p,
+                                         uint64_t seed, int *out)
+{
+    if (!e->finalized) return fail("decode before finalize");
+    if (!(temperature > 0.f)) return g5b_engine_decode_greedy(e, first, n, out);
+    if (!(top_p > 0.f)) return fail("top_p must be positive (1 keeps every token)");
+    CU(cudaSetDevice(e->device));
+    if (e->dirty) return fail("an earlier call failed half-way: reset the engine (g5b_engine_reset) first");
+    if (n < 1 || e->cached + n > e->cap) return fail("decode of %d tokens exceeds the session capacity", n);
+    if (first < 0 || first >= e->c.vocab) return fail("token id %d outside the vocabulary", first);
+    if (ensure_ids(e, (size_t)n + 1)) return -1;
+    CU(cudaMemcpyAsync(e->ids_dev, &first, 4, cudaMemcpyHostToDevice, e->st));
+    const int start = e->cached;
+    e->dirty = true;
+    for (int i = 0; i < n; i++) {
+        e->cached = start + i;
+        const int rc = forward_device(e, e->ids_dev + i, 1, false, nullptr, nullptr);
+        if (rc) { e->cached = start; return -1; }
+        // the step counter of the draw is the position the token will occupy
+        sample_token(e->st, e->ids_dev + i + 1, e->logits, e->logits + e->c.vocab, e->c.vocab, temperature, top_p, seed,
+                     (uint64_t)(start + i + 1));
+    }
+    e->cached = start;
+    CU(cudaMemcpyAsync(out, e->ids_dev + 1, (size_t)n * 4, cudaMemcpyDeviceToHost, e->st));
+    CU(cudaStreamSynchronize(e->st));
+    CU(cudaGetLastError());
+    if (check_device_error(e)) return -1;
+    e->dirty = false;
+    e->cached = start + n;
+    return 0;
+}
+
 extern "C" void g5b_engine_reset(g5b_engine *e)
 {
     cudaSetDevice(e->device);
@@ -1529,6 +1563,23 @@ extern "C" int g5b_rmsnorm_host(float *y, const float *x, const float *w, int n,
     rms_factor(st, xd, n, n, rows, eps, inv);
     rms_apply(st, yd, xd, wd, inv, n, n, rows);
     CU(cudaMemcpy(y, yd, (size_t)rows * n * 4, cudaMemcpyDeviceToHost));
+    CU(cudaGetLastError());
+    return 0;
+}
+
+// One draw from host logits: the sampler of g5b_engine_decode_sampled on its own.
+extern "C" int g5b_sample_host(const float *logits, int V, float temperature, float top_p, uint64_t seed, uint64_t step,
+                               int *token, int device)
+{
+    cudaStream_t st;
+    if (with_device(device, &st)) return -1;
+    if (V < 1 || !(temperature > 0.f) || !(top_p > 0.f)) return fail("sampling needs a vocabulary, temperature > 0 and top_p > 0");
+    Tmp t;
+    float *ld = (float *)t.up(logits, (size_t)V * 4), *pd = (float *)t.up(nullptr, (size_t)V * 4);
+    int *od = (int *)t.up(nullptr, 4);
+    if (!ld || !pd || !od) return fail("out of device memory");
+    sample_token(st, od, ld, pd, V, temperature, top_p, seed, step);
+    CU(cudaMemcpy(token, od, 4, cudaMemcpyDeviceToHost));
     CU(cudaGetLastError());
     return 0;
 }

@@ -95,6 +95,11 @@ void flush_l2(cudaStream_t st, void *buf, size_t bytes);
 // Hint: bring [p, p + bytes) into L2 (16-byte aligned p; nothing waits for it).
 void l2_prefetch(cudaStream_t st, const void *p, size_t bytes);
 
+// ---- sample.cu ----------------------------------------------------------------------------
+// One token drawn from logits[V] (temperature, nucleus truncation, counter-based draw); prob: V floats of scratch.
+void sample_token(cudaStream_t st, int *out, const float *logits, float *prob, int V, float temperature, float top_p,
+                  uint64_t seed, uint64_t step);
+
 // ---- mhc.cu -------------------------------------------------------------------------------
 struct HcW {
     DMat   fn;

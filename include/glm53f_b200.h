@@ -158,6 +158,18 @@ int  g5b_engine_cached(const g5b_engine *e);  /* positions consumed so far */
  * logits to the host and takes the argmax there). out receives n token ids. */
 int g5b_engine_decode_greedy(g5b_engine *e, int first, int n, int *out);
 
+/* Sampled decode on the device (no counterpart in the reference, which is greedy only,
+ * src/cli/glm53f_run.c:492-494): as g5b_engine_decode_greedy, but each token is drawn from the
+ * step's logits: p = softmax(logits / temperature), truncated to the nucleus (every token at least
+ * as probable as the least probable one needed to reach top_p of the mass; top_p >= 1 keeps all),
+ * one draw per step from a counter-based generator of (seed, position), so a run is reproducible
+ * and independent of how it is split into calls. temperature <= 0 decodes greedily. */
+int g5b_engine_decode_sampled(g5b_engine *e, int first, int n, float temperature, float top_p,
+                              uint64_t seed, int *out);
+/* The sampler on its own: one draw from V host logits; `step` is the generator's counter. */
+int g5b_sample_host(const float *logits, int V, float temperature, float top_p, uint64_t seed,
+                    uint64_t step, int *token, int device);
+
 /* Several independent sequences on one engine (no counterpart in the reference, which holds one
  * session per model, src/model/glm53f_model.h:53-75; the benchmark's batch-64 decode needs it).
  * Option "sequences" = S (g5b_engine_set_option before finalize, 1..64) gives every layer S copies
