@@ -119,6 +119,8 @@ struct g5b_engine {
     double *mqa, *mdsc, *mpart = nullptr, *mstats = nullptr;
     int *mcount = nullptr;
     TcGemm *tc = nullptr;                                // FP8 / BF16 projections of 8+ positions on tcgen05
+    int mla_tensor = 1;                                  // option "mla_tensor": 0 keeps the attention core on the FP64 kernels
+    size_t mpart_bytes = 0;
     int tensor_gemm = 1;                                 // option "tensor_gemm": 0 keeps 8+ positions on the one-token kernels
     float *post_h = nullptr; int post_n = 0;             // positions whose hc_post is still owed (run_layer)
     double *hc_part = nullptr; int *hc_count = nullptr;  // fused mHC site: partial sums and per-token counters
@@ -292,6 +294,7 @@ extern "C" int g5b_engine_set_option(g5b_engine *e, const char *name, int value)
         return 0;
     }
     if (!strcmp(name, "tensor_gemm")) { e->tensor_gemm = value; return 0; }
+    if (!strcmp(name, "mla_tensor")) { e->mla_tensor = value; return 0; }
     if (!strcmp(name, "ep_loopback")) return value ? ep_loopback(e) : 0;
     if (!strcmp(name, "ep_wait_ms")) {
         if (value < 1 || value > 600000) return fail("ep_wait_ms is 1..600000");
@@ -579,6 +582,7 @@ extern "C" int g5b_engine_finalize(g5b_engine *e)
         walloc(e, &e->msel, N * stride) || walloc(e, &e->mnsel, N) ||
         walloc(e, &e->mstats, N * H * 2) || walloc(e, &e->mcount, N * H) ||
         walloc(e, &e->mpart, (size_t)MLA_PART_TOKENS * H * ((stride + 31) / 32) * KL)) return -1;
+    e->mpart_bytes = (size_t)MLA_PART_TOKENS * H * ((stride + 31) / 32) * KL * sizeof(double);
     const size_t pairs = N * K + N;
     if (walloc(e, &e->rscore, N * c.n_experts) || walloc(e, &e->rw, N * K) || walloc(e, &e->ridx, N * K) ||
         walloc(e, &e->act, pairs * (I > SI ? I : SI)) || walloc(e, &e->contrib, pairs * E) ||
@@ -856,7 +860,10 @@ static int run_mla(g5b_engine *e, Layer &w, const float *x, int n, int cached, f
     dsa_select(e->st, e->msel, e->mnsel, ist, e->mqidx, e->mwp, e->mscore, n, cached, s);
     if (!forked) mla_absorb(e->st, e->mqa, e->mq, w.kv_b, n, s);
     else if (join && cudaStreamWaitEvent(e->st, e->side_done, 0) != cudaSuccess) cudaStreamSynchronize(e->side);
-    mla_attend(e->st, e->mcb, e->mqa, lat, e->msel, e->mnsel, e->mdsc, e->mpart, e->mstats, e->mcount, MLA_PART_TOKENS, n, cached, s);
+    if (e->mla_tensor && mla_flash_takes(s))
+        mla_attend_flash(e->st, e->mcb, e->mqa, lat, e->msel, e->mnsel, e->mpart, e->mpart_bytes, e->mdsc, n, cached, s);
+    else
+        mla_attend(e->st, e->mcb, e->mqa, lat, e->msel, e->mnsel, e->mdsc, e->mpart, e->mstats, e->mcount, MLA_PART_TOKENS, n, cached, s);
     mla_vout(e->st, e->macc, e->mcb, w.kv_b, n, s);
     {
         GemvSeg o = make_seg(w.mo, e->macc, c.mla_heads * c.v_head, out, E);

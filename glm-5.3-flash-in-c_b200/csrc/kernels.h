@@ -246,6 +246,13 @@ void mla_absorb(cudaStream_t st, double *qa, const float *q, const DMat &kv_b, i
 void mla_attend(cudaStream_t st, float *cb, const double *qa, const void *latent, const int *sel,
                 const int *nsel, double *dsc, double *part, double *stats, int *counters, int part_tokens, int T,
                 int cached, const MlaShape &s);
+// The same attention core on the tensor cores (BF16 latent cache, kv_lora 512): scores and weighted
+// sums as mma.sync products on exact BF16 term splits, softmax per chunk of 64 positions and a
+// rescaling reduction. part / part_bytes: scratch for the chunks' partial rows; cstat: room for
+// [T][H][ceil((topk + KP) / 64)][2] doubles.
+bool mla_flash_takes(const MlaShape &s);
+void mla_attend_flash(cudaStream_t st, float *cb, const double *qa, const void *latent, const int *sel, const int *nsel,
+                      void *part, size_t part_bytes, double *cstat, int T, int cached, const MlaShape &s);
 void mla_vout(cudaStream_t st, float *acc_out, const float *cb, const DMat &kv_b, int T, const MlaShape &s);
 
 }  // namespace g5b

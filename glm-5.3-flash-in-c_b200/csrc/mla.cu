@@ -697,6 +697,248 @@ void mla_attend(cudaStream_t st, float *cb, const double *qa, const void *latent
     }
 }
 
+// ------------------------------------------------- attention core on the tensor cores ----
+// With the latent cache in BF16 the two contractions of the attention core - scores q~ . c_j over
+// the 512 latent columns, and the weighted sum of the latent rows - are small GEMMs whose one
+// operand (the cache) is already exact in BF16. The other operand is split into three BF16 terms
+// (24 significant bits: the absorbed query after the 1/sqrt(d) scaling, the probabilities), so the
+// products are exact and only the FP32 accumulation of mma.sync rounds (about 1e-6 relative; the
+// reference, src/core/glm53f_ops.c:879-911, accumulates in FP64 and rounds the score to float).
+// A CTA takes FL_POS visible positions and FL_HEADS heads of one query: it gathers the latent rows
+// into shared memory once (the DSA selection is a list of row numbers), multiplies scores, takes the
+// chunk's own maximum and exponentials, multiplies the weighted sum and leaves (max, sum, partial
+// rows) for the reduction kernel, which rescales the chunks to the common maximum the way a
+// two-pass softmax would have (the reference's max over all scores first, then the exponentials).
+constexpr int FL_POS = 64, FL_HEADS = 16, FL_KL = 512, FL_PITCH = FL_KL + 8, FL_PPITCH = FL_POS + 8;
+constexpr int FL_THREADS = 256;
+constexpr size_t FL_SMEM = (size_t)3 * FL_HEADS * FL_PITCH * 2 + (size_t)FL_POS * FL_PITCH * 2 +
+                           (size_t)FL_HEADS * FL_POS * 4 + (size_t)3 * FL_HEADS * FL_PPITCH * 2;
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void *p)
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+}
+__device__ __forceinline__ void ldsm_x2(uint32_t (&r)[2], const void *p)
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];"
+                 : "=r"(r[0]), "=r"(r[1]) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+}
+__device__ __forceinline__ void ldsm_x2_trans(uint32_t (&r)[2], const void *p)
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0, %1}, [%2];"
+                 : "=r"(r[0]), "=r"(r[1]) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2])
+{
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+// v = hi + mid + lo exactly enough (24 bits), each a BF16
+__device__ __forceinline__ void split3_bf16(float v, __nv_bfloat16 &hi, __nv_bfloat16 &mid, __nv_bfloat16 &lo)
+{
+    hi = __float2bfloat16_rn(v);
+    const float e1 = v - __bfloat162float(hi);
+    mid = __float2bfloat16_rn(e1);
+    lo = __float2bfloat16_rn(e1 - __bfloat162float(mid));
+}
+
+// part: [T][H][nchunks][KL] floats (unnormalised partial rows); cstat: [T][H][nchunks][2] doubles
+// (chunk maximum, sum of exponentials).
+__global__ void __launch_bounds__(FL_THREADS) mla_flash_kernel(float *part, double *cstat, const double *qa, const void *latent,
+                                                               const int *sel, const int *nsel, int cached, int nchunks, MlaShape s)
+{
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ __align__(16) uint8_t fl_smem[];
+    __nv_bfloat16 *qs = reinterpret_cast<__nv_bfloat16 *>(fl_smem);                          // [3][16][FL_PITCH]
+    __nv_bfloat16 *cs = qs + 3 * FL_HEADS * FL_PITCH;                                       // [64][FL_PITCH]
+    float *ss = reinterpret_cast<float *>(cs + FL_POS * FL_PITCH);                          // [16][64]
+    __nv_bfloat16 *ps = reinterpret_cast<__nv_bfloat16 *>(ss + FL_HEADS * FL_POS);          // [3][16][FL_PPITCH]
+    const int chunk = blockIdx.x, h0 = blockIdx.y * FL_HEADS, t = blockIdx.z, p = pos_of(s, cached, t);
+    const uint16_t *lat = static_cast<const uint16_t *>(seq_latent(latent, s, t));
+    const int ns = nsel ? nsel[t] : -1;
+    const int nvis = ns < 0 ? p + 1 : ns;
+    const int j0 = chunk * FL_POS;
+    if (j0 >= nvis) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+    const int *sl = sel ? sel + (size_t)t * (s.topk + s.KP) : nullptr;
+
+    // ---- the chunk's latent rows (16-byte pieces, four threads per row); rows past the last visible
+    // position are zero so that nothing undefined enters a product
+    for (int i = tid; i < FL_POS * (FL_KL / 8); i += FL_THREADS) {
+        const int r = i / (FL_KL / 8), c8 = i % (FL_KL / 8);
+        const int jj = j0 + r;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (jj < nvis) {
+            const int j = ns < 0 ? jj : sl[jj];
+            v = *reinterpret_cast<const uint4 *>(lat + (size_t)j * FL_KL + c8 * 8);
+        }
+        *reinterpret_cast<uint4 *>(cs + (size_t)r * FL_PITCH + c8 * 8) = v;
+    }
+    // ---- the absorbed queries of the 16 heads, scaled, as three BF16 terms
+    const double scale = (double)(1.0f / sqrtf((float)s.qn));
+    for (int i = tid; i < FL_HEADS * FL_KL; i += FL_THREADS) {
+        const int hh = i / FL_KL, c = i % FL_KL;
+        const float v = (float)(qa[((size_t)t * s.H + h0 + hh) * FL_KL + c] * scale);
+        __nv_bfloat16 a, b, d;
+        split3_bf16(v, a, b, d);
+        qs[(0 * FL_HEADS + hh) * FL_PITCH + c] = a;
+        qs[(1 * FL_HEADS + hh) * FL_PITCH + c] = b;
+        qs[(2 * FL_HEADS + hh) * FL_PITCH + c] = d;
+    }
+    __syncthreads();
+
+    // ---- scores: warp w takes positions 8w..8w+7 of the chunk, all 16 heads, all 512 columns
+    {
+        float c[4] = {0.f, 0.f, 0.f, 0.f};
+        const __nv_bfloat16 *brow = cs + (size_t)(warp * 8 + (lane & 7)) * FL_PITCH + 8 * ((lane >> 3) & 1);
+        const __nv_bfloat16 *arow = qs + (size_t)((lane & 7) + 8 * ((lane >> 3) & 1)) * FL_PITCH + 8 * (lane >> 4);
+#pragma unroll 4
+        for (int k0 = 0; k0 < FL_KL; k0 += 16) {
+            uint32_t b[2];
+            ldsm_x2(b, brow + k0);
+#pragma unroll
+            for (int term = 0; term < 3; term++) {
+                uint32_t a[4];
+                ldsm_x4(a, arow + (size_t)term * FL_HEADS * FL_PITCH + k0);
+                mma_bf16(c, a, b);
+            }
+        }
+        const int r = lane >> 2, col = warp * 8 + 2 * (lane & 3);
+        ss[r * FL_POS + col] = c[0]; ss[r * FL_POS + col + 1] = c[1];
+        ss[(r + 8) * FL_POS + col] = c[2]; ss[(r + 8) * FL_POS + col + 1] = c[3];
+    }
+    __syncthreads();
+
+    // ---- the chunk's maximum and exponentials: a warp takes two heads, a lane two positions
+    for (int hh = warp * 2; hh < warp * 2 + 2; hh++) {
+        const int ja = lane, jb = lane + 32;
+        const float sa = j0 + ja < nvis ? ss[hh * FL_POS + ja] : -INFINITY;
+        const float sb = j0 + jb < nvis ? ss[hh * FL_POS + jb] : -INFINITY;
+        float m = fmaxf(sa, sb);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        const double ea = j0 + ja < nvis ? exp((double)sa - (double)m) : 0.0;
+        const double eb = j0 + jb < nvis ? exp((double)sb - (double)m) : 0.0;
+        const double z = warp_sum(ea + eb);
+        __nv_bfloat16 a, b, d;
+        split3_bf16((float)ea, a, b, d);
+        ps[(0 * FL_HEADS + hh) * FL_PPITCH + ja] = a; ps[(1 * FL_HEADS + hh) * FL_PPITCH + ja] = b; ps[(2 * FL_HEADS + hh) * FL_PPITCH + ja] = d;
+        split3_bf16((float)eb, a, b, d);
+        ps[(0 * FL_HEADS + hh) * FL_PPITCH + jb] = a; ps[(1 * FL_HEADS + hh) * FL_PPITCH + jb] = b; ps[(2 * FL_HEADS + hh) * FL_PPITCH + jb] = d;
+        if (lane == 0) {
+            double *st = cstat + (((size_t)t * s.H + h0 + hh) * nchunks + chunk) * 2;
+            st[0] = (double)m;
+            st[1] = z;
+        }
+    }
+    __syncthreads();
+
+    // ---- weighted sum of the rows: warp w takes latent columns 64w..64w+63 for the 16 heads
+    {
+        float acc[8][4];
+#pragma unroll
+        for (int n = 0; n < 8; n++) { acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f; }
+        const __nv_bfloat16 *arow = ps + (size_t)((lane & 7) + 8 * ((lane >> 3) & 1)) * FL_PPITCH + 8 * (lane >> 4);
+#pragma unroll
+        for (int k0 = 0; k0 < FL_POS; k0 += 16) {
+            uint32_t a[3][4];
+#pragma unroll
+            for (int term = 0; term < 3; term++) ldsm_x4(a[term], arow + (size_t)term * FL_HEADS * FL_PPITCH + k0);
+            const __nv_bfloat16 *brow = cs + (size_t)(k0 + (lane & 15)) * FL_PITCH + warp * 64;
+#pragma unroll
+            for (int n = 0; n < 8; n++) {
+                uint32_t b[2];
+                ldsm_x2_trans(b, brow + n * 8);
+#pragma unroll
+                for (int term = 0; term < 3; term++) mma_bf16(acc[n], a[term], b);
+            }
+        }
+        const int r = lane >> 2;
+        float *o0 = part + (((size_t)t * s.H + h0 + r) * nchunks + chunk) * FL_KL + warp * 64 + 2 * (lane & 3);
+        float *o1 = part + (((size_t)t * s.H + h0 + r + 8) * nchunks + chunk) * FL_KL + warp * 64 + 2 * (lane & 3);
+#pragma unroll
+        for (int n = 0; n < 8; n++) {
+            *reinterpret_cast<float2 *>(o0 + n * 8) = make_float2(acc[n][0], acc[n][1]);
+            *reinterpret_cast<float2 *>(o1 + n * 8) = make_float2(acc[n][2], acc[n][3]);
+        }
+    }
+}
+
+// cb[t][h][c] = sum_chunks e^(m_c - M) part_c[c] / sum_chunks e^(m_c - M) z_c, chunks ascending, FP64.
+// The chunk weights are computed once per (query, head) - one exponential per chunk, by as many
+// threads - and shared; a thread then owns latent columns.
+constexpr int FL_MAX_CHUNKS = 64;
+__global__ void __launch_bounds__(256) mla_flash_reduce_kernel(float *cb, const float *part, const double *cstat, const int *nsel,
+                                                               int cached, int nchunks, MlaShape s)
+{
+    pdl_trigger();
+    pdl_wait();
+    __shared__ double s_m[FL_MAX_CHUNKS], s_w[FL_MAX_CHUNKS];
+    __shared__ double s_z;
+    const int h = blockIdx.x, t = blockIdx.y, p = pos_of(s, cached, t);
+    const int ns = nsel ? nsel[t] : -1;
+    const int nvis = ns < 0 ? p + 1 : ns;
+    const int used = (nvis + FL_POS - 1) / FL_POS;
+    const double *st = cstat + ((size_t)t * s.H + h) * nchunks * 2;
+    double zc = 0.0;
+    if ((int)threadIdx.x < used) { s_m[threadIdx.x] = st[2 * threadIdx.x]; zc = st[2 * threadIdx.x + 1]; }
+    __syncthreads();
+    double M = -INFINITY;
+    for (int c = 0; c < used; c++) M = fmax(M, s_m[c]);
+    if ((int)threadIdx.x < used) s_w[threadIdx.x] = exp(s_m[threadIdx.x] - M);
+    __syncthreads();
+    if ((int)threadIdx.x < used) s_m[threadIdx.x] = s_w[threadIdx.x] * zc;       // reuse: the chunk's share of the denominator
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double Z = 0.0;
+        for (int c = 0; c < used; c++) Z += s_m[c];
+        s_z = Z;
+    }
+    __syncthreads();
+    const double Z = s_z;
+    const float *pr = part + ((size_t)t * s.H + h) * nchunks * FL_KL;
+    for (int col = threadIdx.x; col < FL_KL; col += blockDim.x) {
+        double acc = 0.0;
+#pragma unroll 4
+        for (int c = 0; c < used; c++) acc = fma(s_w[c], (double)__ldcg(pr + (size_t)c * FL_KL + col), acc);
+        cb[((size_t)t * s.H + h) * FL_KL + col] = (float)(acc / Z);
+    }
+}
+
+bool mla_flash_takes(const MlaShape &s)
+{
+    return s.latent_bf16 && s.KL == FL_KL && s.H % FL_HEADS == 0 && (s.topk + s.KP + FL_POS - 1) / FL_POS <= FL_MAX_CHUNKS;
+}
+
+// scratch: `part_bytes` bytes for the partial rows; `cstat` room for [T][H][nchunks][2] doubles.
+void mla_attend_flash(cudaStream_t st, float *cb, const double *qa, const void *latent, const int *sel, const int *nsel,
+                      void *part, size_t part_bytes, double *cstat, int T, int cached, const MlaShape &s)
+{
+    static SmemGrant grant;
+    if (!dev_opt_in_smem((const void *)mla_flash_kernel, FL_SMEM, grant)) return;
+    const int stride = s.topk + s.KP;
+    const int nchunks = (stride + FL_POS - 1) / FL_POS;
+    const size_t per_token = (size_t)s.H * nchunks * FL_KL * sizeof(float);
+    int group = (int)(part_bytes / per_token);
+    if (group < 1) group = 1;
+    for (int t0 = 0; t0 < T; t0 += group) {
+        const int n = T - t0 < group ? T - t0 : group;
+        const int reach = s.batch ? cached + 1 : cached + t0 + n;
+        const int used = (((reach < stride) ? reach : stride) + FL_POS - 1) / FL_POS;
+        const void *lat0 = latent;                                 // the kernel's token 0 is sequence t0 of a batch
+        if (s.batch) lat0 = static_cast<const void *>(static_cast<const uint16_t *>(latent) + (size_t)t0 * s.lat_seq);
+        G5B_LAUNCH_PDL(mla_flash_kernel, dim3(used, s.H / FL_HEADS, n), FL_THREADS, FL_SMEM, st, static_cast<float *>(part), cstat,
+                       qa + (size_t)t0 * s.H * s.KL, lat0, sel ? sel + (size_t)t0 * stride : nullptr, nsel ? nsel + t0 : nullptr,
+                       s.batch ? cached : cached + t0, nchunks, s);
+        G5B_LAUNCH_PDL(mla_flash_reduce_kernel, dim3(s.H, n), 256, 0, st, cb + (size_t)t0 * s.H * s.KL, static_cast<const float *>(part),
+                       cstat, nsel ? nsel + t0 : nullptr, s.batch ? cached : cached + t0, nchunks, s);
+    }
+}
+
+
 // o[t][h][r] = W_v[h][r] . cb[t][h]: the value half of kv_b applied once per query and head
 // (glm53f_ops.c:904-909). A warp takes RW rows of one head.
 __global__ void __launch_bounds__(256) mla_vout_kernel(float *acc_out, const float *cb, const DMat kv_b, MlaShape s)

@@ -88,6 +88,14 @@ def test_full_size_mla_layer(gpu_lib, binding, latent_bf16):
         else:
             assert len(ws) in (2048, 2049, 2050, 2051) and np.array_equal(gs, ws), ctx
         assert common.rel_err(g, w) < (3e-3 if latent_bf16 else 1e-4), ctx
+        if latent_bf16:
+            # the attention core on the tensor cores (the default with a BF16 cache) against the FP64
+            # kernels on the same cache: same selection, output within the FP32 accumulation's reach
+            eng.set_option("mla_tensor", 0)
+            g64, gs64 = eng.op_mla(0, x, ctx - 1)
+            eng.set_option("mla_tensor", 1)
+            assert (gs is None and gs64 is None) or np.array_equal(gs, gs64)
+            assert common.rel_err(g, g64) < 2e-5, ctx
     eng.close(); orc.close()
 
 
