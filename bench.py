@@ -367,6 +367,35 @@ def time_head_and_dense(pkg, torch, steps: int, device: int = 0):
     return out
 
 
+def time_projection(pkg, torch, name: str, T: int, steps: int, device: int = 0):
+    """One matrix of the full-size model times T positions (the path the forward pass takes for that
+    many positions: one-token kernels below 8, the tcgen05 kernel from 8 on), L2 flushed before every
+    launch. The engine holds layer 0 (KDA + dense MLP) and, for lm_head, the head: a small case for ncu."""
+    import synth
+    L = pkg.lib()
+    spec = synth.full_model_spec(1)
+    head = name in ("lm_head.weight", "embed_tokens.weight")
+    spec.with_head = head
+    eng = pkg.Engine(spec.cfg, spec.is_mla, spec.is_dense, 16, device)
+    eng.set_option("allow_partial", 1)
+    synth.fill_full_model(eng, spec, SEED, head=head)
+    eng.finalize()
+    table = {"layers.0." + n: (r, c, dt) for n, kind, r, c, dt, _ in synth.layer_tensor_table(spec.cfg, False, True) if kind == "mat"}
+    table.update({n: (r, c, dt) for n, kind, r, c, dt, _ in synth.model_level_tensors(spec.cfg) if kind == "mat"})
+    rows, cols, dt = table[name]
+    x = torch.randn(T, cols, device="cuda"); y = torch.empty(T, rows, device="cuda")
+    each = np.zeros(max(steps, 3), np.float32)
+    for k in (3, steps):
+        assert L.g5b_time_matvec(eng.handle, name.encode(), x.data_ptr(), T, y.data_ptr(), k, FLUSH_BYTES,
+                                 each.ctypes.data) == 0, L.g5b_last_error()
+    ms = float(np.median(each[:steps]))
+    nbytes = rows * cols * {synth.DT_F32: 4, synth.DT_BF16: 2, synth.DT_FP8: 1}[dt]
+    peak, _ = measured_peaks()
+    eng.close()
+    return {"matrix": name, "rows": rows, "cols": cols, "positions": T, "ms": ms, "algorithmic_bytes": nbytes,
+            "achieved_GBps": nbytes / (ms * 1e-3) / 1e9, "frac": nbytes / (ms * 1e-3) / 1e9 / peak}
+
+
 def synth_mod():
     import synth
     return synth
@@ -524,6 +553,98 @@ def run_full_model(pkg, torch, ranks, local: int, rank: int, world: int, peak: f
     return res
 
 
+def run_batch_decode(pkg, torch, ranks, local: int, rank: int, world: int, layers_cap: int, sequences: int = 64,
+                     context: int = 4096, new_tokens: int = 128, prefill_tokens: int = 2048):
+    """Benchmark configuration 5: the full-size random-init model with `sequences` concurrent
+    sequences at a context of `context` positions each (their KDA states, latent caches and indexer
+    states filled on the device: a stand-in for the prompts' prefill), decoding `new_tokens` tokens
+    per sequence in lockstep; routed experts split over the ranks, everything else - the attention of
+    every sequence included - on every rank. Then one `prefill_tokens`-token prompt through the
+    prefill path of sequence 0 (chunks of 64 positions). As many layers as the GPUs hold."""
+    import fullmodel
+    import synth
+    c0 = pkg.full_size_config()
+    cap = context + new_tokens + 8
+    # session state per sequence and layer (FP32 KDA state and indexer state, BF16 latents)
+    P = c0.kda_heads * c0.kda_head_dim
+    kda_bytes = 4 * (P * c0.kda_head_dim + 3 * P * (c0.conv_k - 1))
+    mla_bytes = cap * c0.kv_lora * 2 + 4 * (2 * cap * c0.index_dim + ((cap + c0.index_kpool - 1) // c0.index_kpool) * c0.index_dim)
+    free = torch.cuda.mem_get_info()[0]
+    n_layers = 0
+    for n in range(min(45, layers_cap), 0, -1):
+        spec = synth.full_model_spec(n)
+        resident, _, _ = fullmodel.model_bytes(spec, world)
+        state = sequences * sum(mla_bytes if m else kda_bytes for m in spec.is_mla)
+        if resident + state + (8 << 30) <= free * 0.94:
+            n_layers = n
+            break
+    n_layers = int(ranks.reduce(n_layers, "min"))
+    if n_layers < 4:
+        return {"error": "not enough free device memory for four layers"}
+    spec = synth.full_model_spec(n_layers)
+    c = spec.cfg
+    eng, err = None, ""
+    try:
+        eng = fullmodel.build_engine(spec, SEED, cap, local, rank, world, options={"latent_bf16": 1, "sequences": sequences})
+    except Exception as exc:                                       # noqa: BLE001
+        err = repr(exc)[:300]
+    if not ranks.all_ok(not err):
+        if eng is not None:
+            eng.close()
+        return {"error": err or "another rank could not build the model"}
+    handles = ranks.gather(eng.ep_export() if world > 1 else b"")
+    try:
+        if world > 1:
+            eng.ep_connect(handles)
+    except Exception as exc:                                       # noqa: BLE001
+        err = repr(exc)[:300]
+    if not ranks.all_ok(not err):
+        eng.close()
+        return {"error": err or "another rank could not connect"}
+    decode_s = prefill_s = 0.0
+    toks = None
+    try:
+        eng.synth_session(SEED, context)
+        ids = np.random.default_rng(SEED).integers(0, c.vocab, sequences).astype(np.int32)
+        for _ in range(3):                                         # warm-up steps (they advance the sequences too)
+            _, ids = eng.decode_batch(ids, want_logits=False)
+        ranks.barrier()
+        t0 = time.perf_counter()
+        for _ in range(new_tokens - 3):
+            _, ids = eng.decode_batch(ids, want_logits=False)
+        decode_s = time.perf_counter() - t0
+        toks = ids.tolist()
+        # prefill throughput: one prompt through sequence 0 from an empty session
+        eng.reset()
+        prompt = np.random.default_rng(SEED + 1).integers(0, c.vocab, prefill_tokens).astype(np.int32)
+        eng.use_sequence(0)
+        eng.forward(prompt[:128], want_logits=False)               # warm-up chunk pair
+        eng.reset()
+        eng.use_sequence(0)
+        ranks.barrier()
+        t0 = time.perf_counter()
+        eng.forward(prompt, want_logits=False)
+        prefill_s = time.perf_counter() - t0
+    except Exception as exc:                                       # noqa: BLE001
+        err = repr(exc)[:300]
+    ok = ranks.all_ok(not err)
+    decode_s = ranks.reduce(decode_s, "max")
+    prefill_s = ranks.reduce(prefill_s, "max")
+    all_toks = ranks.gather(toks)
+    eng.close()
+    if not ok:
+        return {"error": err or "another rank failed"}
+    steps = new_tokens - 3
+    return {"layers": n_layers, "of_layers": 45, "n_gpus": world, "sequences": sequences, "context": context,
+            "state": "synthetic session state at the stated context (filled on the device), no prompts run",
+            "timed_steps": steps, "ms_per_step": 1e3 * decode_s / steps, "tokens_per_s": sequences * steps / decode_s,
+            "tokens_per_s_per_sequence": steps / decode_s,
+            "attention": "every sequence on every rank (no sequence parallelism); routed experts split over the ranks",
+            "tokens_equal_on_all_ranks": all(t == all_toks[0] for t in all_toks),
+            "prefill": {"tokens": prefill_tokens, "ms": 1e3 * prefill_s, "tokens_per_s": prefill_tokens / prefill_s,
+                        "chunk": 64}}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -546,7 +667,12 @@ def main():
                     help="run only the timing of one mHC site of a full-size layer and print it (a small case for ncu)")
     ap.add_argument("--no-attention-layers", action="store_true",
                     help="skip the KDA / MLA single-layer and decoder-layer timings reported under 'extra'")
+    ap.add_argument("--only-projection", default="",
+                    help="time one matrix of the full-size model (e.g. layers.0.mlp.gate_proj.weight, lm_head.weight) "
+                         "times --positions positions and print it (a small case for ncu)")
+    ap.add_argument("--positions", type=int, default=64)
     ap.add_argument("--no-full-model", action="store_true", help="skip the full-size model's greedy decode")
+    ap.add_argument("--no-batch-decode", action="store_true", help="skip the 64-sequence decode of the full-size model")
     ap.add_argument("--only-full-model", action="store_true", help="run only the full-size model's greedy decode and print it")
     ap.add_argument("--full-model-layers", type=int, default=45, help="upper limit on the layers of the full-size model")
     ap.add_argument("--full-model-tokens", type=int, default=256)
@@ -573,7 +699,7 @@ def main():
     # the CPU baseline first: one rank, before any other rank's process competes for the host cores
     cpu = None
     if world == 1 and not args.no_cpu_baseline and args.experts == 288 and not (
-            args.only_mhc_site or args.only_attention_layers or args.only_full_model):
+            args.only_mhc_site or args.only_attention_layers or args.only_full_model or args.only_projection):
         cpu = cpu_reference_moe(steps=60, warmup=2)
         one = cpu_reference_moe(steps=30, warmup=1, threads=1)
         cpu = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
@@ -586,6 +712,10 @@ def main():
     peak, peak_kind = measured_peaks()
     warmup = max(3, args.warmup)
 
+    if args.only_projection:
+        print(json.dumps({"projection": time_projection(pkg, torch, args.only_projection, args.positions, max(3, args.steps), local)}),
+              flush=True)
+        return
     if args.only_mhc_site:
         print(json.dumps({"mhc_site": time_mhc_site(pkg, torch, max(3, args.steps), local)}), flush=True)
         return
@@ -596,9 +726,11 @@ def main():
         print(json.dumps(res), flush=True)
         return
     if args.only_full_model:
-        res = run_full_model(pkg, torch, ranks, local, rank, world, peak, args.full_model_layers, args.full_model_tokens)
+        res = {"full_model": run_full_model(pkg, torch, ranks, local, rank, world, peak, args.full_model_layers, args.full_model_tokens)}
+        if not args.no_batch_decode:
+            res["batch_decode"] = run_batch_decode(pkg, torch, ranks, local, rank, world, args.full_model_layers)
         if rank == 0:
-            print(json.dumps({"full_model": res}), flush=True)
+            print(json.dumps(res), flush=True)
         if world > 1:
             dist.barrier()
             dist.destroy_process_group()
@@ -729,6 +861,12 @@ def main():
                                                  args.full_model_tokens)
         except Exception as exc:                                   # noqa: BLE001
             extra["full_model"] = {"error": repr(exc)[:300]}
+
+    if not args.no_full_model and not args.no_batch_decode and args.experts == 288:
+        try:
+            extra["batch_decode"] = run_batch_decode(pkg, torch, ranks, local, rank, world, args.full_model_layers)
+        except Exception as exc:                                   # noqa: BLE001
+            extra["batch_decode"] = {"error": repr(exc)[:300]}
 
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": "tokens/s",

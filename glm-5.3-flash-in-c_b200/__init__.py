@@ -95,6 +95,8 @@ def lib() -> C.CDLL:
     L.g5b_engine_create.argtypes = [C.POINTER(Config), C.c_char_p, C.c_char_p, C.c_int, C.c_int, C.c_int, C.c_int]
     L.g5b_engine_fill_expert.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_uint64, C.c_void_p, C.c_void_p, C.c_void_p]
     L.g5b_engine_fill_matrix.argtypes = [C.c_void_p, C.c_char_p, C.c_int, C.c_uint64, C.c_float, C.c_void_p]
+    L.g5b_engine_load_checkpoint.argtypes = [C.c_void_p, C.c_char_p, C.c_int]
+    L.g5b_engine_synth_session.argtypes = [C.c_void_p, C.c_uint64, C.c_int]
     L.g5b_engine_last_picks.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
     L.g5b_engine_decode_greedy.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p]
     L.g5b_engine_ep_handle_bytes.restype = C.c_size_t
@@ -332,6 +334,16 @@ class Engine(FlatModel):
                                          sc.ctypes.data if sc is not None else None) != 0:
             self._err(f"fill_matrix({name})")
         self._rows[name] = rows
+
+    def load_checkpoint(self, directory: str, threads: int = 4):
+        """Stream every tensor this engine owns from a safetensors directory into HBM (C loader)."""
+        if self.L.g5b_engine_load_checkpoint(self.handle, directory.encode(), threads) != 0:
+            self._err("load_checkpoint")
+
+    def synth_session(self, seed: int, positions: int):
+        """Synthetic session state for every sequence at `positions` positions (g5b_engine_synth_session)."""
+        if self.L.g5b_engine_synth_session(self.handle, seed, positions) != 0:
+            self._err("synth_session")
 
     def last_picks(self, T: int = 1):
         """(idx [T][topk], w [T][topk]) of the most recent MoE pass (g5b_engine_last_picks)."""

@@ -244,6 +244,20 @@ void fill_bf16_key(cudaStream_t st, uint16_t *dst, uint64_t key, float mul, size
     G5B_LAUNCH(fill_bf16_kernel, 1184, 256, 0, st, dst, key, mul, count);
 }
 
+// The same values as FP32 (each exactly representable in BF16): synthetic session state.
+__global__ void fill_f32_kernel(float *dst, uint64_t key, float mul, size_t n)
+{
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const uint64_t h = mix64(key + i);
+        const int c = (int)((h & 0xffffu) + ((h >> 16) & 0xffffu) + ((h >> 32) & 0xffffu) + (h >> 48)) - 131070;
+        dst[i] = __bfloat162float(__float2bfloat16_rn(__fmul_rn((float)c, mul)));
+    }
+}
+void fill_f32_key(cudaStream_t st, float *dst, uint64_t key, float mul, size_t count)
+{
+    G5B_LAUNCH(fill_f32_kernel, 1184, 256, 0, st, dst, key, mul, count);
+}
+
 __global__ void f32_to_bf16_kernel(uint16_t *dst, const float *src, size_t n)
 {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)

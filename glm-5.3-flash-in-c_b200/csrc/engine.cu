@@ -448,6 +448,77 @@ extern "C" int g5b_engine_load(g5b_engine *e, const char *name, const g5b_tensor
     return upload_vec(e, tg.vec, t, (size_t)tg.rows, name);
 }
 
+// Reserve a named tensor's place in HBM and hand its device addresses to a caller that will write the
+// bytes itself (the streaming checkpoint loader, loader.cu): same names, shapes and dtypes as
+// g5b_engine_load; the tensor counts as loaded. A routed expert of another rank returns NULL
+// addresses and success. Vectors are not served here (they are widened on the host: g5b_engine_load).
+extern "C" int g5b_engine_reserve(g5b_engine *e, const char *name, int dtype, int rows, int cols, void **data_dev,
+                                  float **scale_dev)
+{
+    if (e->finalized) return fail("load after finalize");
+    CU(cudaSetDevice(e->device));
+    const g5b_config &c = e->c;
+    *data_dev = nullptr; *scale_dev = nullptr;
+    if (dtype < 0 || dtype > 2) return fail("%s has a dtype this engine cannot multiply", name);
+    DMat *m = nullptr;
+    int want_r = 0, want_c = 0;
+    if (!strcmp(name, "embed_tokens.weight")) {
+        if (dtype == G5B_DT_FP8) return fail("an FP8 embedding table is not supported");
+        m = &e->embed; want_r = c.vocab; want_c = c.hidden;
+    } else if (!strcmp(name, "lm_head.weight")) { m = &e->lm_head; want_r = c.vocab; want_c = c.hidden; }
+    else {
+        int l = -1, used = 0;
+        if (sscanf(name, "layers.%d.%n", &l, &used) != 1 || l < 0 || l >= c.n_layers) return fail("unknown tensor %s", name);
+        const char *rest = name + used;
+        int ex = -1, n2 = 0;
+        if (!e->L[l].is_dense && sscanf(rest, "mlp.experts.%d.%n", &ex, &n2) == 1) {
+            if (ex < 0 || ex >= c.n_experts) return fail("%s: expert out of range", name);
+            const char *p = rest + n2;
+            const int which = !strcmp(p, "gate_proj.weight") ? 0 : !strcmp(p, "up_proj.weight") ? 1 : !strcmp(p, "down_proj.weight") ? 2 : -1;
+            if (which < 0) return fail("unknown tensor %s", name);
+            if (ex < e->n_local0 || ex >= e->n_local0 + e->n_local) return 0;      // another rank's expert
+            const int er = which == 2 ? c.hidden : c.moe_inter, ec = which == 2 ? c.moe_inter : c.hidden;
+            if (rows != er || cols != ec) return fail("%s is %d x %d, the config implies %d x %d", name, rows, cols, er, ec);
+            Layer &w = e->L[l];
+            if (ensure_expert_slab(e, w, dtype)) return -1;
+            ExpertW &x = w.table[ex - e->n_local0];
+            *data_dev = (void *)(which == 0 ? x.gate : which == 1 ? x.up : x.down);
+            *scale_dev = (float *)(which == 0 ? x.gate_s : which == 1 ? x.up_s : x.down_s);
+            w.have[(size_t)(ex - e->n_local0) * 3 + which] = 1;
+            return 0;
+        }
+        auto it = e->names[l].find(rest);
+        if (it == e->names[l].end()) return fail("tensor %s does not belong to layer %d of this config", name, l);
+        if (it->second.kind != 0) return fail("%s is a vector: load it with g5b_engine_load", name);
+        m = it->second.mat; want_r = it->second.rows; want_c = it->second.cols;
+    }
+    if (rows != want_r || cols != want_c) return fail("%s is %d x %d, the config implies %d x %d", name, rows, cols, want_r, want_c);
+    if (m->loaded()) return fail("%s is already loaded", name);
+    m->dt = dtype; m->rows = rows; m->cols = cols;
+    if (e->dalloc(&m->w, (size_t)rows * cols * elt(dtype))) return -1;
+    if (dtype == G5B_DT_FP8) {
+        if (c.fp8_block_r < 1 || c.fp8_block_c < 1) return fail("%s is FP8 but the config has no block size", name);
+        m->br = c.fp8_block_r; m->bc = c.fp8_block_c; m->scols = (cols + m->bc - 1) / m->bc;
+        if (e->dalloc((void **)&m->s, (size_t)((rows + m->br - 1) / m->br) * m->scols * 4)) return -1;
+    }
+    CU(cudaStreamSynchronize(e->st));                // the allocation's zero fill must not overtake the loader's copies
+    *data_dev = m->w; *scale_dev = m->s;
+    return 0;
+}
+
+// Does this engine take the named vector (so that the loader reads it at all)?
+extern "C" int g5b_engine_wants_vector(g5b_engine *e, const char *name)
+{
+    if (!strcmp(name, "norm.weight")) return 1;
+    int l = -1, used = 0;
+    if (sscanf(name, "layers.%d.%n", &l, &used) != 1 || l < 0 || l >= e->c.n_layers) return 0;
+    auto it = e->names[l].find(name + used);
+    return it != e->names[l].end() && it->second.kind == 1;
+}
+
+extern "C" int g5b_engine_device(const g5b_engine *e) { return e->device; }
+extern "C" int g5b_engine_layers(const g5b_engine *e) { return e->c.n_layers; }
+
 extern "C" int g5b_engine_fill_expert(g5b_engine *e, int layer, int expert, uint64_t seed,
                                       const float *gate_s, const float *up_s, const float *down_s)
 {
@@ -1103,6 +1174,39 @@ extern "C" void g5b_engine_reset(g5b_engine *e)
     e->dirty = false;
     e->post_h = nullptr;
     for (auto &v : e->cached_seq) v = 0;
+}
+
+// Stand-in for a long prefill: every sequence's session state (KDA state ~ 0.1 N(0,1), latent cache
+// and indexer state ~ N(0,1), BF16-representable, from the hash generators) filled on the device
+// and every sequence's position set to `positions`, so that a batch decode can be measured at a
+// deep context without first running the prompts through the model.
+extern "C" int g5b_engine_synth_session(g5b_engine *e, uint64_t seed, int positions)
+{
+    if (!e || !e->finalized) return fail("synth_session before finalize");
+    if (positions < 0 || positions >= e->cap) return fail("%d positions do not leave room in a capacity of %d", positions, e->cap);
+    CU(cudaSetDevice(e->device));
+    const float unit = 1.0f / 37837.2f;
+    for (size_t l = 0; l < e->L.size(); l++) {
+        Layer &w = e->L[l];
+        char name[64];
+        if (w.kda_state) {
+            snprintf(name, sizeof name, "state.%zu.kda", l);
+            fill_f32_key(e->st, w.kda_state, synth_key(seed, name), 0.1f * unit, (size_t)e->n_seq * e->kda_seq);
+        }
+        if (w.latent) {
+            snprintf(name, sizeof name, "state.%zu.latent", l);
+            if (e->latent_bf16) fill_bf16_key(e->st, static_cast<uint16_t *>(w.latent), synth_key(seed, name), unit, (size_t)e->n_seq * e->lat_seq);
+            else                fill_f32_key(e->st, static_cast<float *>(w.latent), synth_key(seed, name), unit, (size_t)e->n_seq * e->lat_seq);
+            snprintf(name, sizeof name, "state.%zu.indexer", l);
+            fill_f32_key(e->st, w.idx_state, synth_key(seed, name), unit, (size_t)e->n_seq * e->idx_seq);
+        }
+    }
+    CU(cudaStreamSynchronize(e->st));
+    CU(cudaGetLastError());
+    e->cached = positions;
+    for (auto &v : e->cached_seq) v = positions;
+    e->dirty = false;
+    return 0;
 }
 
 // Which sequence the single-sequence calls (forward, decode_greedy, layer ops, state access) address.

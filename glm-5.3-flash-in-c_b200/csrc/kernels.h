@@ -89,6 +89,7 @@ void fill_codes(cudaStream_t st, uint8_t *dst, uint64_t seed, int layer, int exp
 uint64_t synth_key(uint64_t seed, const char *name);
 void fill_codes_key(cudaStream_t st, uint8_t *dst, uint64_t key, size_t count);      // count a multiple of 4
 void fill_bf16_key(cudaStream_t st, uint16_t *dst, uint64_t key, float mul, size_t count);
+void fill_f32_key(cudaStream_t st, float *dst, uint64_t key, float mul, size_t count);
 void f32_to_bf16(cudaStream_t st, uint16_t *dst, const float *src, size_t n);
 void bf16_to_f32(cudaStream_t st, float *dst, const uint16_t *src, size_t n);
 void flush_l2(cudaStream_t st, void *buf, size_t bytes);

@@ -109,6 +109,19 @@ g5b_engine *g5b_engine_create(const g5b_config *cfg, const uint8_t *is_mla,
  * this engine's expert-parallel range is ignored and reported as success. */
 int g5b_engine_load(g5b_engine *e, const char *name, const g5b_tensor *t);
 
+/* Stream a whole checkpoint directory (every *.safetensors file in it) into the engine: each tensor
+ * of "model.language_model." (and "lm_head.weight") that this engine owns is read in pieces of at
+ * most 32 MB by `threads` reader threads into pinned staging buffers and copied to its final place in
+ * HBM; routed experts of other expert-parallel ranks and layers beyond the engine's are never read.
+ * Names, shapes and dtypes are checked like g5b_engine_load's. Replaces the reference's load path
+ * (src/io/glm53f_st.c, src/model/glm53f_bind.c:139-206,311-331, src/io/glm53f_load.c:15-99 and the
+ * SSD expert cache they feed). Call g5b_engine_finalize afterwards. */
+int g5b_engine_load_checkpoint(g5b_engine *e, const char *directory, int threads);
+/* Lower level of the same: reserve a named matrix's place and get the device addresses to write
+ * its bytes (and FP8 scale grid) to; NULL addresses with success for another rank's expert. */
+int g5b_engine_reserve(g5b_engine *e, const char *name, int dtype, int rows, int cols, void **data_dev,
+                       float **scale_dev);
+
 /* Fill one routed expert of a MoE layer with synthetic weights generated on the GPU: E4M3
  * codes uniform over the 254 finite codes from a counter-based hash of (seed, layer, expert,
  * matrix, element index), so the CPU can regenerate any single expert bit for bit. Scale
@@ -125,6 +138,11 @@ int g5b_engine_fill_expert(g5b_engine *e, int layer, int expert, uint64_t seed,
  * trunk is built without a checkpoint (no counterpart in the reference, which loads safetensors). */
 int g5b_engine_fill_matrix(g5b_engine *e, const char *name, int dtype, uint64_t seed, float mul,
                            const float *scale_inv);
+
+/* Benchmarks only: fill every sequence's session state with synthetic values on the GPU and set every
+ * sequence's position to `positions`, standing in for prompts of that length (no counterpart in the
+ * reference; the decode kernels do the work they would do after a real prefill of that depth). */
+int g5b_engine_synth_session(g5b_engine *e, uint64_t seed, int positions);
 
 /* Engine options, by name. "latent_bf16" (before finalize): keep the MLA latent cache in BF16
  * instead of FP32, half the bytes per position. "profile": record per-phase events in MoE ops.
