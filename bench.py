@@ -539,10 +539,10 @@ def run_full_model(pkg, torch, ranks, local: int, rank: int, world: int, peak: f
         try:
             if rank == 0:
                 from oracle import binding
-                r = fullmodel.layer_parity(eng, binding, spec, SEED, layer, h, eng.cached, cap)
+                r = fullmodel.layer_parity(eng, binding, spec, SEED, layer, h, eng.cached, cap, ranks=ranks)
                 parity[f"layer{layer}"] = {"rel_err": r["rel_err"], "picks": None if r["picks"] is None else r["picks"].ravel().tolist()}
             else:
-                fullmodel.layer_parity(eng, None, spec, SEED, layer, h, eng.cached, cap, check=False)
+                fullmodel.layer_parity(eng, None, spec, SEED, layer, h, eng.cached, cap, check=False, ranks=ranks)
         except Exception as exc:                                   # noqa: BLE001
             perr = repr(exc)[:300]
         if not ranks.all_ok(not perr):

@@ -93,7 +93,11 @@ struct g5b_engine {
     std::vector<void *> ep_opened;               // peer mappings to close
     std::vector<void *> ep_standins;             // local stand-ins for peers (option ep_loopback)
     unsigned long long ep_step = 0;              // exchanges so far (both kernels): picks the row buffer
-    unsigned long long ep_decode_launches = 0;   // of them, by the one-token kernel (its arrival counters count CTAs)
+    unsigned long long ep_decode_launches = 0;
+    unsigned long long ts_launches = 0;          // all-reduces of column-split trunk products so far
+    size_t ts_area_bytes = 0;                    // one parity's [ep_size][CHUNK][hidden] floats
+    float *ts_part = nullptr;                    // this rank's partial rows [CHUNK][hidden]
+    int tensor_split = 1;                        // option "tensor_split": KDA heads and their state split over the ranks   // of them, by the one-token kernel (its arrival counters count CTAs)
     int *ep_arrive = nullptr;
     int ep_wait_ms = 5000;                       // wall-clock limit of a wait for the other ranks (option "ep_wait_ms")
     bool dirty = false;                          // a call failed half-way: session state is undefined until reset
@@ -295,6 +299,11 @@ extern "C" int g5b_engine_set_option(g5b_engine *e, const char *name, int value)
     }
     if (!strcmp(name, "tensor_gemm")) { e->tensor_gemm = value; return 0; }
     if (!strcmp(name, "mla_tensor")) { e->mla_tensor = value; return 0; }
+    if (!strcmp(name, "tensor_split")) {
+        if (e->ts_launches) return fail("tensor_split cannot change once a split layer has run (each rank holds only its heads' state)");
+        e->tensor_split = value != 0;
+        return 0;
+    }
     if (!strcmp(name, "ep_loopback")) return value ? ep_loopback(e) : 0;
     if (!strcmp(name, "ep_wait_ms")) {
         if (value < 1 || value > 600000) return fail("ep_wait_ms is 1..600000");
@@ -856,33 +865,61 @@ static int proj(g5b_engine *e, const DMat &m, const float *x, int ldx, float *y,
 
 // batch: the n rows are one new position of n different sequences (sequences 0..n-1), otherwise n
 // consecutive positions of the current sequence.
+// The sum over ranks of a column-split product's partial rows (e->ts_part -> out), in rank order.
+static void trunk_allreduce(g5b_engine *e, float *out, int ldo, int n)
+{
+    ++e->ts_launches;
+    TsReduce r{e->ts_part, out, ldo, e->ep_peers_dev, e->ep_rank, e->ep_size, n, e->c.hidden, CHUNK,
+               EP_FLAG_BYTES + 2 * e->ep_rows_bytes + (size_t)(e->ts_launches & 1) * e->ts_area_bytes, 2 * e->ep_size,
+               e->ts_launches, (unsigned long long)e->ep_wait_ms * 1000000ull, e->err_dev};
+    ts_allreduce(e->st, r);
+}
+
+// batch: the n rows are one new position of n different sequences (sequences 0..n-1), otherwise n
+// consecutive positions of the current sequence.
+// Expert-parallel engines split the layer by heads as well (option "tensor_split", on by default):
+// rank r multiplies the q / k / v / beta / low-rank rows of heads [r H / N, (r + 1) H / N), advances
+// those heads' state only, and multiplies its heads' columns of the output projection; the partial
+// output rows are summed over the ranks in rank order (ts_allreduce), so every rank continues with
+// the same bits. A rank then holds a current state for its own heads only.
 static int run_kda(g5b_engine *e, Layer &w, const float *x, int n, float *out, bool batch = false)
 {
     const g5b_config &c = e->c;
     const int E = c.hidden, H = c.kda_heads, D = c.kda_head_dim, P = H * D;
     if (!w.kq.loaded() || !w.ko.loaded() || !w.g_b.loaded() || !w.f_b.loaded() || !w.kda_state || !w.dt_bias)
         return fail("this layer's KDA weights were not loaded");
+    const bool ts = e->tensor_split && e->ep_size > 1 && e->ep_connected && H % e->ep_size == 0 && (E % 4) == 0 &&
+                    w.kq.dt != G5B_DT_FP8 && w.kk.dt != G5B_DT_FP8 && w.kv.dt != G5B_DT_FP8 && w.ko.dt != G5B_DT_FP8 &&
+                    w.f_b.dt != G5B_DT_FP8 && w.g_b.dt != G5B_DT_FP8 && w.kb.dt != G5B_DT_FP8;
+    const int Hl = ts ? H / e->ep_size : H, h0 = ts ? e->ep_rank * Hl : 0, Pl = Hl * D, p0 = h0 * D;
     float *lrf = e->klr, *lrg = e->klr + (size_t)CHUNK * D;
-    GemvSeg a[6] = {make_seg(w.kq, x, E, e->kq, P), make_seg(w.kk, x, E, e->kk, P), make_seg(w.kv, x, E, e->kv, P),
-                    make_seg(w.kb, x, E, e->kbraw, H), make_seg(w.f_a, x, E, lrf, D), make_seg(w.g_a, x, E, lrg, D)};
+    GemvSeg a[6] = {make_seg(row_slice(w.kq, p0, Pl), x, E, e->kq + p0, P), make_seg(row_slice(w.kk, p0, Pl), x, E, e->kk + p0, P),
+                    make_seg(row_slice(w.kv, p0, Pl), x, E, e->kv + p0, P), make_seg(row_slice(w.kb, h0, Hl), x, E, e->kbraw + h0, H),
+                    make_seg(w.f_a, x, E, lrf, D), make_seg(w.g_a, x, E, lrg, D)};
     if (proj_batch(e, a, 6, n, true)) return -1;
     // one new token: the recurrence kernel takes the two low-rank up-projections itself
     const bool lr_inside = n == 1 && !batch && w.f_b.dt == G5B_DT_BF16 && w.g_b.dt == G5B_DT_BF16 && (D == 64 || D == 128);
     const KdaLowRank lr{w.f_b.w, w.g_b.w, lrf, lrg};
     if (!lr_inside) {
-        GemvSeg b[2] = {make_seg(w.f_b, lrf, D, e->kz, P), make_seg(w.g_b, lrg, D, e->kgb, P)};
+        GemvSeg b[2] = {make_seg(row_slice(w.f_b, p0, Pl), lrf, D, e->kz + p0, P), make_seg(row_slice(w.g_b, p0, Pl), lrg, D, e->kgb + p0, P)};
         if (proj_batch(e, b, 2, n)) return -1;
     }
     KdaShape ks{H, D, c.conv_k, c.gate_lb, c.rms_eps};
-    if (n == 1) prefetch_beside(e, w.ko);               // the recurrence below leaves half the SMs and all of HBM idle
+    if (n == 1 && !ts) prefetch_beside(e, w.ko);        // the recurrence below leaves half the SMs and all of HBM idle
     if (batch)
         kda_core(e->st, e->ko, e->kq, e->kk, e->kv, e->kz, e->kbraw, e->kgb, w.q_conv, w.k_conv, w.v_conv,
-                 w.A_log, w.dt_bias, w.o_norm, w.kda_state, 1, ks, n, e->kda_seq);
+                 w.A_log, w.dt_bias, w.o_norm, w.kda_state, 1, ks, n, e->kda_seq, nullptr, h0, Hl);
     else
         kda_core(e->st, e->ko, e->kq, e->kk, e->kv, e->kz, e->kbraw, e->kgb, w.q_conv, w.k_conv, w.v_conv,
                  w.A_log, w.dt_bias, w.o_norm, w.kda_state + (size_t)e->cur_seq * e->kda_seq, n, ks, 1, 0,
-                 lr_inside ? &lr : nullptr);
-    return proj(e, w.ko, e->ko, P, out, E, n);
+                 lr_inside ? &lr : nullptr, h0, Hl);
+    if (!ts) return proj(e, w.ko, e->ko, P, out, E, n);
+    {
+        GemvSeg o = make_seg(col_slice(w.ko, p0, Pl), e->ko + p0, P, e->ts_part, E);
+        if (proj_batch(e, &o, 1, n)) return -1;
+    }
+    trunk_allreduce(e, out, E, n);
+    return 0;
 }
 
 static MlaShape mla_shape(const g5b_engine *e)
@@ -1857,11 +1894,13 @@ static int ep_alloc(g5b_engine *e)
 {
     if (e->ep_region) return 0;
     e->ep_rows_bytes = (size_t)CHUNK * e->c.topk * e->c.hidden * 4;
-    const size_t bytes = EP_FLAG_BYTES + 2 * e->ep_rows_bytes;
+    e->ts_area_bytes = (size_t)e->ep_size * CHUNK * e->c.hidden * 4;
+    const size_t bytes = EP_FLAG_BYTES + 2 * e->ep_rows_bytes + 2 * e->ts_area_bytes;
     CU(cudaMalloc((void **)&e->ep_region, bytes));       // an allocation of its own: it is what peers map
     CU(cudaMemset(e->ep_region, 0, bytes));
     if (e->dalloc((void **)&e->ep_peers_dev, sizeof(void *) * (size_t)e->ep_size)) return -1;
     if (e->dalloc((void **)&e->ep_arrive, sizeof(int))) return -1;
+    if (e->dalloc((void **)&e->ts_part, (size_t)CHUNK * e->c.hidden * 4)) return -1;
     CU(cudaStreamSynchronize(e->st));
     return 0;
 }
@@ -1872,6 +1911,8 @@ static int ep_publish_peers(g5b_engine *e, const std::vector<void *> &peers)
     e->ep_connected = true;
     e->ep_step = 0;
     e->ep_decode_launches = 0;
+    e->ts_launches = 0;
+    e->ts_launches = 0;
     return 0;
 }
 
@@ -1930,6 +1971,7 @@ extern "C" int g5b_engine_ep_resync(g5b_engine *e)
     if (e->err_host) *e->err_host = 0;
     e->ep_step = 0;
     e->ep_decode_launches = 0;
+    e->ts_launches = 0;
     return 0;
 }
 
@@ -1945,8 +1987,8 @@ static int ep_loopback(g5b_engine *e)
     for (int r = 0; r < e->ep_size; r++) {
         if (r == e->ep_rank) { peers[r] = e->ep_region; continue; }
         void *p = nullptr;
-        CU(cudaMalloc(&p, EP_FLAG_BYTES + 2 * e->ep_rows_bytes));
-        CU(cudaMemset(p, 0, EP_FLAG_BYTES + 2 * e->ep_rows_bytes));
+        CU(cudaMalloc(&p, EP_FLAG_BYTES + 2 * e->ep_rows_bytes + 2 * e->ts_area_bytes));
+        CU(cudaMemset(p, 0, EP_FLAG_BYTES + 2 * e->ep_rows_bytes + 2 * e->ts_area_bytes));
         e->ep_standins.push_back(p);
         peers[r] = p;
     }

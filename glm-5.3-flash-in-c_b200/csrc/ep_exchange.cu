@@ -83,6 +83,50 @@ __global__ void __launch_bounds__(256) ep_exchange_combine_kernel(const EpExchan
     }
 }
 
+// The all-reduce of a column-split trunk product (TsReduce, kernels.h). CTA b owns the float4s
+// b, b + gridDim.x, ... of the [T][E] block: it stores them into slot `rank` of every rank's buffer,
+// counts itself done on every rank (release-add, covering the CTA's stores through the barrier
+// before it), waits for every rank's counter to reach launch x CTAs and adds the slots of its own
+// float4s in rank order. All ranks run the same grid.
+constexpr int TS_CTAS = 8;
+__global__ void __launch_bounds__(256) ts_allreduce_kernel(const TsReduce a)
+{
+    __shared__ int s_ok;
+    const int tid = threadIdx.x;
+    const size_t n4 = (size_t)a.T * a.E / 4, row4 = (size_t)a.E / 4, slot4 = (size_t)a.max_t * row4;
+    const float4 *src = reinterpret_cast<const float4 *>(a.partial);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + tid; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+        const float4 v = src[i];
+        for (int r = 0; r < a.size; r++)
+            (reinterpret_cast<float4 *>(static_cast<uint8_t *>(a.peers[r]) + a.area_off) + (size_t)a.rank * slot4)[i] = v;
+    }
+    __syncthreads();
+    if (tid < a.size) red_release_sys_add(reinterpret_cast<unsigned long long *>(a.peers[tid]) + a.cnt0 + a.rank, 1ull);
+    if (tid == 0) s_ok = 1;
+    __syncthreads();
+    if (tid < a.size) {
+        const unsigned long long *mine = reinterpret_cast<const unsigned long long *>(a.peers[a.rank]) + a.cnt0 + tid;
+        if (!wait_word_sys(mine, a.launch * gridDim.x, a.wait_ns)) { atomicExch(a.err, 40 + tid); s_ok = 0; }
+    }
+    __syncthreads();
+    if (!s_ok) return;
+    const float4 *slots = reinterpret_cast<const float4 *>(static_cast<const uint8_t *>(a.peers[a.rank]) + a.area_off);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + tid; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+        float4 s = __ldcg(slots + i);
+        for (int r = 1; r < a.size; r++) {
+            const float4 v = __ldcg(slots + (size_t)r * slot4 + i);
+            s.x = __fadd_rn(s.x, v.x); s.y = __fadd_rn(s.y, v.y); s.z = __fadd_rn(s.z, v.z); s.w = __fadd_rn(s.w, v.w);
+        }
+        const size_t t = i / row4, c = (i % row4) * 4;
+        *reinterpret_cast<float4 *>(a.out + t * a.ldo + c) = s;
+    }
+}
+
+void ts_allreduce(cudaStream_t st, const TsReduce &a)
+{
+    G5B_LAUNCH(ts_allreduce_kernel, TS_CTAS, 256, 0, st, a);
+}
+
 void ep_exchange_combine(cudaStream_t st, const EpExchange &a, int ctas)
 {
     G5B_LAUNCH(ep_exchange_combine_kernel, dim3(ctas), 256, 0, st, a);

@@ -34,7 +34,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, TT == 1 ? 3 : 2) gemv_fast_kerne
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int blk = blockIdx.x - g.block0;
     const int pieces = g.C / piece_elems(g.dt);
-    const size_t row_bytes = (size_t)g.C * (g.dt == DT_FP8 ? 1 : g.dt == DT_BF16 ? 2 : 4);
+    const size_t row_bytes = (size_t)g.ldw * (g.dt == DT_FP8 ? 1 : g.dt == DT_BF16 ? 2 : 4);
 
     int r0, p0, p1;
     if (g.ksplit) {                               // the CTA's 8 warps split the columns of RW rows
@@ -129,12 +129,12 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_any_kernel(const GemvBatch 
             }
             double wv;
             if (g.dt == DT_FP8)
-                wv = (double)e4m3_to_f32(static_cast<const uint8_t *>(g.W)[(size_t)row * g.C + c]) *
+                wv = (double)e4m3_to_f32(static_cast<const uint8_t *>(g.W)[(size_t)row * g.ldw + c]) *
                      (double)g.S[(size_t)(row / g.br) * g.scols + c / g.bc];
             else if (g.dt == DT_BF16)
-                wv = (double)bf16_to_f32(static_cast<const uint16_t *>(g.W)[(size_t)row * g.C + c]);
+                wv = (double)bf16_to_f32(static_cast<const uint16_t *>(g.W)[(size_t)row * g.ldw + c]);
             else
-                wv = (double)static_cast<const float *>(g.W)[(size_t)row * g.C + c];
+                wv = (double)static_cast<const float *>(g.W)[(size_t)row * g.ldw + c];
             acc += wv * (double)xv;
         }
         acc = warp_sum(acc);
@@ -149,6 +149,7 @@ GemvSeg make_seg(const DMat &m, const float *x, int ldx, float *y, int ldy, cons
     s.W = m.w; s.S = m.s; s.x = x; s.xinv = xinv; s.xw = xw; s.y = y;
     s.dt = m.dt; s.R = m.rows; s.C = m.cols; s.br = m.br; s.bc = m.bc; s.scols = m.scols;
     s.ldx = ldx; s.ldy = ldy;
+    s.ldw = m.ld ? m.ld : m.cols;
     s.ksplit = 0; s.block0 = 0;
     return s;
 }
@@ -158,15 +159,26 @@ DMat row_slice(const DMat &m, int r0, int n)
     DMat s = m;
     s.rows = n;
     const size_t eb = m.dt == DT_FP8 ? 1 : m.dt == DT_BF16 ? 2 : 4;
-    s.w = static_cast<uint8_t *>(m.w) + (size_t)r0 * m.cols * eb;
+    s.w = static_cast<uint8_t *>(m.w) + (size_t)r0 * (m.ld ? m.ld : m.cols) * eb;
     if (m.dt == DT_FP8) s.s = m.s + (size_t)(r0 / m.br) * m.scols;
+    return s;
+}
+
+DMat col_slice(const DMat &m, int c0, int n)
+{
+    DMat s = m;
+    s.cols = n;
+    s.ld = m.ld ? m.ld : m.cols;
+    const size_t eb = m.dt == DT_FP8 ? 1 : m.dt == DT_BF16 ? 2 : 4;
+    s.w = static_cast<uint8_t *>(m.w) + (size_t)c0 * eb;
+    if (m.dt == DT_FP8) s.s = m.s + c0 / m.bc;          // same scale-row pitch (scols) as the parent
     return s;
 }
 
 static bool seg_is_fast(const GemvSeg &s)
 {
     const int pe = piece_elems(s.dt);
-    if (s.C % pe) return false;
+    if (s.C % pe || s.ldw % pe) return false;
     if (s.dt == DT_FP8 && (s.bc % 16 || s.br < 1)) return false;
     if ((reinterpret_cast<uintptr_t>(s.W) & 15) || (reinterpret_cast<uintptr_t>(s.x) & 15) || (s.ldx & 3))
         return false;

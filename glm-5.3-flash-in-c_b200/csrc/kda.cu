@@ -23,6 +23,7 @@ struct KdaArgs {
     const float *q_conv, *k_conv, *v_conv, *A_log, *dt_bias, *o_norm;
     float *state;
     int T, H, D, K;
+    int head0;                    // the grid covers heads head0 .. head0 + gridDim.x - 1 of the H heads
     float gate_lb, rms_eps;
     size_t seq_stride;            // floats between the states of consecutive sequences (grid.y > 1:
                                   // CTA (h, s) advances sequence s by the T positions at rows s*T ...)
@@ -48,7 +49,7 @@ __global__ void __launch_bounds__(DS > 0 ? DS : 512) kda_core_kernel(const KdaAr
 {
     __shared__ float sq[512], sk[512], sal[512];
     __shared__ double red[32];
-    const int h = blockIdx.x, d = threadIdx.x;
+    const int h = a.head0 + blockIdx.x, d = threadIdx.x;
     const int D = DS > 0 ? DS : a.D, P = a.H * D, K = a.K, hist = K - 1;
     const bool live = d < D;
     const int ch = h * D + (live ? d : 0);
@@ -201,14 +202,14 @@ __global__ void __launch_bounds__(DS > 0 ? DS : 512) kda_core_kernel(const KdaAr
 void kda_core(cudaStream_t st, float *o, const float *q, const float *k, const float *v, const float *z,
               const float *braw, const float *gb, const float *q_conv, const float *k_conv,
               const float *v_conv, const float *A_log, const float *dt_bias, const float *o_norm,
-              float *state, int T, const KdaShape &s, int n_seq, size_t seq_stride, const KdaLowRank *lr)
+              float *state, int T, const KdaShape &s, int n_seq, size_t seq_stride, const KdaLowRank *lr, int head0, int heads)
 {
     const bool fused = lr && T == 1 && n_seq <= 1 && (s.D == 64 || s.D == 128);
     KdaArgs a{o, q, k, v, z, braw, gb, q_conv, k_conv, v_conv, A_log, dt_bias, o_norm, state,
-              T, s.H, s.D, s.K, s.gate_lb, s.rms_eps, seq_stride,
+              T, s.H, s.D, s.K, head0, s.gate_lb, s.rms_eps, seq_stride,
               fused ? static_cast<const uint16_t *>(lr->f_b) : nullptr, fused ? static_cast<const uint16_t *>(lr->g_b) : nullptr,
               fused ? lr->lrf : nullptr, fused ? lr->lrg : nullptr};
-    const dim3 grid(s.H, n_seq < 1 ? 1 : n_seq);
+    const dim3 grid(heads > 0 ? heads : s.H, n_seq < 1 ? 1 : n_seq);
     const size_t smem = fused ? (size_t)2 * s.D * (2 * s.D + 16) : 0;
     if (s.D == 128) {
         static SmemGrant grant;

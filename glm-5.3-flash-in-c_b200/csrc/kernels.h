@@ -15,6 +15,7 @@ struct DMat {
     void  *w = nullptr;
     float *s = nullptr;        // FP8 block scales [ceil(rows/br)][scols]
     int    dt = 0, rows = 0, cols = 0, br = 0, bc = 0, scols = 0;
+    int    ld = 0;             // elements between consecutive rows; 0 = cols (a column slice keeps its parent's)
     bool   loaded() const { return w != nullptr; }
     size_t bytes() const { return (size_t)rows * cols * (dt == 0 ? 4 : dt == 1 ? 2 : 1); }
 };
@@ -42,6 +43,7 @@ struct GemvSeg {
     const float *xw;      // optional RMSNorm weight per column
     float       *y;       // [T][ldy]
     int dt, R, C, br, bc, scols, ldx, ldy;
+    int ldw;              // elements between consecutive rows of W (C unless W is a column slice)
     int ksplit;           // 1: a whole CTA shares each group of rows (few-row matrices)
     int block0;           // first block of this segment in the grid (filled by the launcher)
 };
@@ -51,6 +53,8 @@ GemvSeg make_seg(const DMat &m, const float *x, int ldx, float *y, int ldy,
                  const float *xinv = nullptr, const float *xw = nullptr);
 // Matrix restricted to rows [r0, r0+n) (FP8: r0 must lie on a scale-block row).
 DMat row_slice(const DMat &m, int r0, int n);
+// Matrix restricted to columns [c0, c0+n) (FP8: c0 must lie on a scale-block column).
+DMat col_slice(const DMat &m, int c0, int n);
 // early: one token, launched with programmatic stream serialization (the grid may be scheduled while
 // the kernel before it drains; it waits for that kernel before it reads anything)
 void gemv_batch(cudaStream_t st, const GemvSeg *segs, int n, int T, bool early = false);
@@ -203,6 +207,25 @@ struct EpExchange {
 };
 void ep_exchange_combine(cudaStream_t st, const EpExchange &a, int ctas);
 
+// All-reduce (sum, in rank order) of one partial vector per rank and position over peer mappings,
+// for a trunk product whose columns are split over the expert-parallel ranks: every rank stores its
+// partial rows [T][E] into slot `rank` of every rank's buffer, counts itself done there with one
+// release-add per CTA, waits (wall-clock limited) for all ranks' counters and adds the slots in rank
+// order, so every rank gets the same bits. peers[r] + area_off = rank r's [size][max_t][E] buffer of
+// this launch's parity; counters at word cnt0 + q of each region.
+struct TsReduce {
+    const float *partial;     // [T][E]
+    float *out; int ldo;      // [T][ldo]
+    void *const *peers;
+    int rank, size, T, E, max_t;
+    size_t area_off;
+    int cnt0;
+    unsigned long long launch;  // launches of this exchange so far, this one included
+    unsigned long long wait_ns;
+    int *err;
+};
+void ts_allreduce(cudaStream_t st, const TsReduce &a);
+
 // ---- kda.cu -------------------------------------------------------------------------------
 struct KdaShape { int H, D, K; float gate_lb, rms_eps; };
 // One new token only: the two low-rank up-projections z = f_b lrf and gb = g_b lrg (BF16 [H*D][D],
@@ -219,7 +242,7 @@ void kda_core(cudaStream_t st, float *o, const float *q, const float *k, const f
               const float *braw, const float *gb, const float *q_conv, const float *k_conv,
               const float *v_conv, const float *A_log, const float *dt_bias, const float *o_norm,
               float *state, int T, const KdaShape &s, int n_seq = 1, size_t seq_stride = 0,
-              const KdaLowRank *lr = nullptr);
+              const KdaLowRank *lr = nullptr, int head0 = 0, int heads = -1);   // heads [head0, head0 + heads) only
 
 // ---- mla.cu -------------------------------------------------------------------------------
 struct MlaShape {

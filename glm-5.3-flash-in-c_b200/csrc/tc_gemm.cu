@@ -621,12 +621,13 @@ static EncodeTiledFn encode_fn()
 
 // A [rows][cols] row-major matrix of `elt`-byte elements, copied in boxes of box_rows x 128 bytes
 // with the 128-byte swizzle. Rows past `rows` read as zero.
-static bool make_map(CUtensorMap *m, const void *base, CUtensorMapDataType dt, int elt, size_t rows, size_t cols, int box_rows)
+static bool make_map(CUtensorMap *m, const void *base, CUtensorMapDataType dt, int elt, size_t rows, size_t cols, int box_rows,
+                     size_t pitch = 0)
 {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
     const cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    const cuuint64_t gstride[1] = {(cuuint64_t)cols * elt};
+    const cuuint64_t gstride[1] = {(cuuint64_t)(pitch ? pitch : cols) * elt};
     const cuuint32_t box[2] = {(cuuint32_t)(128 / elt), (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
     return fn(m, dt, 2, const_cast<void *>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -640,7 +641,7 @@ struct TcGemm {
     // what the terms buffer holds (several matrices share one input)
     const float *x = nullptr, *xinv = nullptr, *xw = nullptr;
     int ldx = 0, C = 0, T = 0, kind = -1;
-    std::map<std::tuple<const void *, int, int, int>, CUtensorMap> amaps;   // weights by (pointer, rows, cols, dt)
+    std::map<std::tuple<const void *, int, int, int, int>, CUtensorMap> amaps;   // weights by (pointer, rows, cols, pitch, dt)
     SmemGrant grant_fp8, grant_bf16;
     float *part = nullptr;          // split-K partial results [TC_MAX_SPLIT][64][part_rows]
     int *cnt = nullptr;             // arrivals per row tile
@@ -680,7 +681,7 @@ void tc_gemm_new_input(TcGemm *g) { if (g) g->x = nullptr; }
 bool tc_gemm_takes(const TcGemm *g, const GemvSeg &s, int T)
 {
     if (!g || T < 8 || T > TC_MAX_T || s.C > g->max_c || s.R % TC_BM || s.R < TC_BM) return false;
-    if (reinterpret_cast<uintptr_t>(s.W) & 15) return false;
+    if ((reinterpret_cast<uintptr_t>(s.W) & 15) || (((size_t)s.ldw * (s.dt == DT_FP8 ? 1 : 2)) & 15)) return false;
     if (s.dt == DT_FP8) return s.C % 128 == 0 && s.br == 128 && s.bc == 128 && s.S != nullptr;
     if (s.dt == DT_BF16) return s.C % TC_ATOM_K == 0;
     return false;
@@ -697,11 +698,11 @@ int tc_gemm_run(TcGemm *g, cudaStream_t st, const GemvSeg &s, int T)
         else     G5B_LAUNCH(tc_split_bf16_kernel, Tp, 256, 0, st, static_cast<__nv_bfloat16 *>(g->terms), s.x, s.ldx, s.xinv, s.xw, s.C, T, Tp);
         g->x = s.x; g->xinv = s.xinv; g->xw = s.xw; g->ldx = s.ldx; g->C = s.C; g->T = T; g->kind = (int)fp8;
     }
-    const auto key = std::make_tuple(s.W, s.R, s.C, s.dt);
+    const auto key = std::make_tuple(s.W, s.R, s.C, s.ldw, s.dt);
     auto it = g->amaps.find(key);
     if (it == g->amaps.end()) {
         CUtensorMap m;
-        if (!make_map(&m, s.W, fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, fp8 ? 1 : 2, (size_t)s.R, (size_t)s.C, TC_BM))
+        if (!make_map(&m, s.W, fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, fp8 ? 1 : 2, (size_t)s.R, (size_t)s.C, TC_BM, (size_t)s.ldw))
             return -1;
         it = g->amaps.emplace(key, m).first;
     }

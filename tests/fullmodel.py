@@ -45,7 +45,30 @@ def model_bytes(spec, ep_size: int = 1):
     return int(resident), float(token_rank), float(token_all)
 
 
-def layer_parity(eng, binding, spec, seed: int, layer: int, h: np.ndarray, cached: int, cap: int, check: bool = True):
+def merge_kda_states(states, cfg):
+    """An expert-parallel engine with the tensor split holds a current KDA state for its own heads
+    only. `states`: every rank's full-size state array of one layer, in rank order; returns the array
+    with each rank's heads taken from that rank (layout: S [H][D][D], then the conv histories of
+    q | k | v, each [H * D][k - 1], include/glm53f/glm53f.h:363-367)."""
+    world = len(states)
+    if world == 1:
+        return states[0]
+    H, D, hist = cfg.kda_heads, cfg.kda_head_dim, cfg.conv_k - 1
+    P = H * D
+    out = np.array(states[0], copy=True)
+    per = H // world
+    for r in range(1, world):
+        src = states[r]
+        h0, h1 = r * per, (r + 1) * per
+        out[h0 * D * D:h1 * D * D] = src[h0 * D * D:h1 * D * D]
+        for part in range(3):
+            base = H * D * D + part * P * hist
+            out[base + h0 * D * hist:base + h1 * D * hist] = src[base + h0 * D * hist:base + h1 * D * hist]
+    return out
+
+
+def layer_parity(eng, binding, spec, seed: int, layer: int, h: np.ndarray, cached: int, cap: int, check: bool = True,
+                 ranks=None):
     """One decoder layer on the GPU and (when `check`) on the CPU from the same input and state.
     Returns {"rel_err", "picks", "picks_equal", "state_rel_err"}; rel_err is max |d| / max |ref| of
     the residual stream leaving the layer."""
@@ -53,13 +76,20 @@ def layer_parity(eng, binding, spec, seed: int, layer: int, h: np.ndarray, cache
     is_mla, is_dense = bool(spec.is_mla[layer]), bool(spec.is_dense[layer])
     T = h.shape[0]
     state = {}
+    if ranks is not None and ranks.world > 1 and not is_mla:
+        # every rank contributes its heads' state (a collective: all ranks call it)
+        P = c.kda_heads * c.kda_head_dim
+        mine = eng.state_read(layer, 0, 0, P * c.kda_head_dim + 3 * P * (c.conv_k - 1))
+        gathered = ranks.gather(mine)
+        if check:
+            state[0] = merge_kda_states(gathered, c)
     if check:
         if is_mla:
             if cached:
                 state[1] = eng.state_read(layer, 1, 0, cached * c.kv_lora)
             n_idx = 2 * cap * c.index_dim + ((cap + c.index_kpool - 1) // c.index_kpool) * c.index_dim
             state[2] = eng.state_read(layer, 2, 0, n_idx)
-        else:
+        elif 0 not in state:
             P = c.kda_heads * c.kda_head_dim
             state[0] = eng.state_read(layer, 0, 0, P * c.kda_head_dim + 3 * P * (c.conv_k - 1))
     got = eng.op_decoder_layer(layer, h, cached)
