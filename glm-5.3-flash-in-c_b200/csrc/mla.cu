@@ -871,7 +871,7 @@ __global__ void __launch_bounds__(FL_THREADS) mla_flash_kernel(float *part, doub
 // The chunk weights are computed once per (query, head) - one exponential per chunk, by as many
 // threads - and shared; a thread then owns latent columns.
 constexpr int FL_MAX_CHUNKS = 64;
-__global__ void __launch_bounds__(256) mla_flash_reduce_kernel(float *cb, const float *part, const double *cstat, const int *nsel,
+__global__ void __launch_bounds__(FL_KL) mla_flash_reduce_kernel(float *cb, const float *part, const double *cstat, const int *nsel,
                                                                int cached, int nchunks, MlaShape s)
 {
     pdl_trigger();
@@ -902,8 +902,13 @@ __global__ void __launch_bounds__(256) mla_flash_reduce_kernel(float *cb, const 
     const float *pr = part + ((size_t)t * s.H + h) * nchunks * FL_KL;
     for (int col = threadIdx.x; col < FL_KL; col += blockDim.x) {
         double acc = 0.0;
-#pragma unroll 4
-        for (int c = 0; c < used; c++) acc = fma(s_w[c], (double)__ldcg(pr + (size_t)c * FL_KL + col), acc);
+        for (int c0 = 0; c0 < used; c0 += 8) {                 // eight chunks' rows requested before the first is used
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) v[i] = c0 + i < used ? __ldcg(pr + (size_t)(c0 + i) * FL_KL + col) : 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; i++) if (c0 + i < used) acc = fma(s_w[c0 + i], (double)v[i], acc);
+        }
         cb[((size_t)t * s.H + h) * FL_KL + col] = (float)(acc / Z);
     }
 }
@@ -933,7 +938,7 @@ void mla_attend_flash(cudaStream_t st, float *cb, const double *qa, const void *
         G5B_LAUNCH_PDL(mla_flash_kernel, dim3(used, s.H / FL_HEADS, n), FL_THREADS, FL_SMEM, st, static_cast<float *>(part), cstat,
                        qa + (size_t)t0 * s.H * s.KL, lat0, sel ? sel + (size_t)t0 * stride : nullptr, nsel ? nsel + t0 : nullptr,
                        s.batch ? cached : cached + t0, nchunks, s);
-        G5B_LAUNCH_PDL(mla_flash_reduce_kernel, dim3(s.H, n), 256, 0, st, cb + (size_t)t0 * s.H * s.KL, static_cast<const float *>(part),
+        G5B_LAUNCH_PDL(mla_flash_reduce_kernel, dim3(s.H, n), FL_KL, 0, st, cb + (size_t)t0 * s.H * s.KL, static_cast<const float *>(part),
                        cstat, nsel ? nsel + t0 : nullptr, s.batch ? cached : cached + t0, nchunks, s);
     }
 }

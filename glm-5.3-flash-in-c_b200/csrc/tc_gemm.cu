@@ -197,8 +197,8 @@ struct TcArgs {
 
 template <bool FP8> struct TcCfg;
 template <> struct TcCfg<true> {
-    // warps: 0-3 epilogue, 4 weight producer, 5 MMA, 6-9 converters, 10 activation producer
-    static constexpr int CONV_BUFS = 2, ACCS = 4, THREADS = 11 * 32, TERMS = 2;
+    // warps: 0-3 epilogue, 4 TMA producer, 5 MMA, 6-9 converters
+    static constexpr int CONV_BUFS = 2, ACCS = 4, THREADS = 10 * 32, TERMS = 2;
 };
 template <> struct TcCfg<false> {
     // warps: 0-3 epilogue, 4 producer, 5 MMA
@@ -332,33 +332,19 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         const int KB = a.C / 128;                                         // 128-column blocks of W
 
         if (warp == 4) {
-            // ------------------------------------------------ weights: HBM -> raw FP8 tiles ----
+            // --------------------- weights: HBM -> raw FP8 tiles; activation terms: L2 -> B stages ----
             if (lane == 0) {
                 long it = 0;
                 for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
                     int tile, split, kb0, kb1;
                     item_range(item, KB, tile, split, kb0, kb1);
                     for (int kb = kb0; kb < kb1 && ok; kb++, it++) {
-                        const int rs = (int)(it % AS);
+                        const int rs = (int)(it % AS), bs = (int)(it % BS);
                         if (it >= AS) ok = mbar_wait(&raw_empty[rs], (uint32_t)((it / AS) - 1) & 1, a.err, 31);
                         if (!ok) break;
                         mbar_expect_tx(&raw_full[rs], 16384);
                         tma_load_2d(raw + (size_t)rs * 16384, &mapA, kb * 128, tile * TC_BM, &raw_full[rs]);
                         TC_TRACE(0, it);
-                    }
-                }
-                // copies in flight must land before shared memory goes away
-                if (!ok) for (long j = it - 1; j >= 0 && j >= it - AS; j--) mbar_wait(&raw_full[j % AS], (uint32_t)(j / AS) & 1, a.err, 33);
-            }
-        } else if (warp == 10) {
-            // ------------------------------------------- activation terms: L2 -> B stages ----
-            if (lane == 0) {
-                long it = 0;
-                for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-                    int tile, split, kb0, kb1;
-                    item_range(item, KB, tile, split, kb0, kb1);
-                    for (int kb = kb0; kb < kb1 && ok; kb++, it++) {
-                        const int bs = (int)(it % BS);
                         if (it >= BS) ok = mbar_wait(&b_empty[bs], (uint32_t)((it / BS) - 1) & 1, a.err, 32);
                         if (!ok) break;
                         mbar_expect_tx(&b_full[bs], (uint32_t)(2 * batom));
@@ -367,7 +353,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                         TC_TRACE(1, it);
                     }
                 }
-                if (!ok) for (long j = it - 1; j >= 0 && j >= it - BS; j--) mbar_wait(&b_full[j % BS], (uint32_t)(j / BS) & 1, a.err, 33);
+                // copies in flight must land before shared memory goes away
+                if (!ok) {
+                    for (long j = it - 1; j >= 0 && j >= it - AS; j--) mbar_wait(&raw_full[j % AS], (uint32_t)(j / AS) & 1, a.err, 33);
+                    for (long j = it - 1; j >= 0 && j >= it - BS; j--) mbar_wait(&b_full[j % BS], (uint32_t)(j / BS) & 1, a.err, 33);
+                }
             }
         } else if (warp == 5) {
             // ------------------------------------------------------------------ MMA issue ----
@@ -459,22 +449,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                     if (threadIdx.x == 0) TC_TRACE(5, it);
                     const uint32_t base = lane_addr + (uint32_t)(ai * N);
 #pragma unroll
-                    for (int g = 0; g < TC_MAX_T / 16; g++) {
-                        if (g * 16 < a.Tp) {                             // 16 positions per round trip to tensor memory
-                            float hi[2][8], mid[2][8];
-                            tmem_ld8(base + g * 16, hi[0]);
-                            tmem_ld8(base + a.Tp + g * 16, mid[0]);
-                            if (g * 16 + 8 < a.Tp) {
-                                tmem_ld8(base + g * 16 + 8, hi[1]);
-                                tmem_ld8(base + a.Tp + g * 16 + 8, mid[1]);
-                            }
+                    for (int g = 0; g < TC_MAX_T / 8; g++) {
+                        if (g * 8 < a.Tp) {
+                            float hi[8], mid[8];
+                            tmem_ld8(base + g * 8, hi);
+                            tmem_ld8(base + a.Tp + g * 8, mid);
                             tmem_ld_wait();
 #pragma unroll
-                            for (int h = 0; h < 2; h++)
-#pragma unroll
-                                for (int i = 0; i < 8; i++)
-                                    if (h == 0 || g * 16 + 8 < a.Tp)
-                                        acc[g * 16 + h * 8 + i] = fmaf(hi[h][i] + mid[h][i] * (1.0f / 2048.0f), sv, acc[g * 16 + h * 8 + i]);
+                            for (int i = 0; i < 8; i++) acc[g * 8 + i] = fmaf(hi[i] + mid[i] * (1.0f / 2048.0f), sv, acc[g * 8 + i]);
                         }
                     }
                     tc_fence_before();
@@ -718,7 +700,7 @@ int tc_gemm_run(TcGemm *g, cudaStream_t st, const GemvSeg &s, int T)
         double best = 0.0;
         for (int k = 1; k <= TC_MAX_SPLIT && k <= units; k++) {
             const int items = tiles * k, waves = (items + sms - 1) / sms;
-            const double eff = (double)items / ((double)waves * sms) - 0.03 * k;   // every split costs a pipeline fill and a partial result
+            const double eff = (double)items / ((double)waves * sms) - 0.15 * (k - 1);   // every split costs a pipeline fill, a partial result and a pass over the partials
             if (eff > best + 1e-9) { best = eff; KS = k; }
         }
     }
