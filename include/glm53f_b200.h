@@ -149,7 +149,14 @@ int g5b_engine_synth_session(g5b_engine *e, uint64_t seed, int positions);
  * "sequences" (before finalize), "ep_wait_ms", "ep_loopback": see below. "expert_path": which
  * batch-1 expert kernels run (0 register kernels, 1 tensor-core kernels as three launches, 2 the
  * whole layer as one kernel, the default); "allow_partial": finalize accepts missing tensors
- * (single-layer harnesses). */
+ * (single-layer harnesses). "tensor_gemm" (default 1): matrices times 8..64 positions go through the
+ * tcgen05 kernel instead of repeated one-token passes. "mla_tensor" (default 1): with the BF16
+ * latent cache the attention core runs on the tensor cores. "tensor_split" (default 1; it cannot
+ * change once a split layer has run): in a connected expert-parallel group every rank runs the KDA
+ * layers for its own H / ep_size heads only and the ranks sum their partial output rows in rank
+ * order; the kind-0 state keeps its full layout on every rank, but a rank advances only the
+ * entries of its own heads [rank H / ep_size, (rank + 1) H / ep_size): g5b_state_read returns stale
+ * values for the others, and a caller that wants the whole state takes each head from its rank. */
 int g5b_engine_set_option(g5b_engine *e, const char *name, int value);
 
 /* Check that every tensor the config implies has been loaded, then allocate the session
