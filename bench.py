@@ -558,9 +558,13 @@ def run_batch_decode(pkg, torch, ranks, local: int, rank: int, world: int, layer
     """Benchmark configuration 5: the full-size random-init model with `sequences` concurrent
     sequences at a context of `context` positions each (their KDA states, latent caches and indexer
     states filled on the device: a stand-in for the prompts' prefill), decoding `new_tokens` tokens
-    per sequence in lockstep; routed experts split over the ranks, everything else - the attention of
-    every sequence included - on every rank. Then one `prefill_tokens`-token prompt through the
-    prefill path of sequence 0 (chunks of 64 positions). As many layers as the GPUs hold."""
+    per sequence in lockstep; routed experts split over the ranks. Two arms at N > 1: every sequence's
+    attention on every rank (tokens replicated), and the sequences split over the ranks - each rank
+    runs attention and all other per-token work for sequences / N of them, MoE layers gather the
+    ranks' tokens and send contribution rows to the rank a token lives on. Both arms start from the
+    same synthetic state, so the split arm must reproduce the first arm's tokens. Then one
+    `prefill_tokens`-token prompt through the prefill path of sequence 0 (chunks of 64 positions).
+    As many layers as the GPUs hold."""
     import fullmodel
     import synth
     c0 = pkg.full_size_config()
@@ -583,66 +587,91 @@ def run_batch_decode(pkg, torch, ranks, local: int, rank: int, world: int, layer
         return {"error": "not enough free device memory for four layers"}
     spec = synth.full_model_spec(n_layers)
     c = spec.cfg
-    eng, err = None, ""
-    try:
-        eng = fullmodel.build_engine(spec, SEED, cap, local, rank, world, options={"latent_bf16": 1, "sequences": sequences})
-    except Exception as exc:                                       # noqa: BLE001
-        err = repr(exc)[:300]
-    if not ranks.all_ok(not err):
-        if eng is not None:
-            eng.close()
-        return {"error": err or "another rank could not build the model"}
-    handles = ranks.gather(eng.ep_export() if world > 1 else b"")
-    try:
-        if world > 1:
-            eng.ep_connect(handles)
-    except Exception as exc:                                       # noqa: BLE001
-        err = repr(exc)[:300]
-    if not ranks.all_ok(not err):
-        eng.close()
-        return {"error": err or "another rank could not connect"}
-    decode_s = prefill_s = 0.0
-    toks = None
-    try:
-        eng.synth_session(SEED, context)
-        ids = np.random.default_rng(SEED).integers(0, c.vocab, sequences).astype(np.int32)
-        for _ in range(3):                                         # warm-up steps (they advance the sequences too)
-            _, ids = eng.decode_batch(ids, want_logits=False)
-        ranks.barrier()
-        t0 = time.perf_counter()
-        for _ in range(new_tokens - 3):
-            _, ids = eng.decode_batch(ids, want_logits=False)
-        decode_s = time.perf_counter() - t0
-        toks = ids.tolist()
-        # prefill throughput: one prompt through sequence 0 from an empty session
-        eng.reset()
-        prompt = np.random.default_rng(SEED + 1).integers(0, c.vocab, prefill_tokens).astype(np.int32)
-        eng.use_sequence(0)
-        eng.forward(prompt[:128], want_logits=False)               # warm-up chunk pair
-        eng.reset()
-        eng.use_sequence(0)
-        ranks.barrier()
-        t0 = time.perf_counter()
-        eng.forward(prompt, want_logits=False)
-        prefill_s = time.perf_counter() - t0
-    except Exception as exc:                                       # noqa: BLE001
-        err = repr(exc)[:300]
-    ok = ranks.all_ok(not err)
-    decode_s = ranks.reduce(decode_s, "max")
-    prefill_s = ranks.reduce(prefill_s, "max")
-    all_toks = ranks.gather(toks)
-    eng.close()
-    if not ok:
-        return {"error": err or "another rank failed"}
+    all_ids = np.random.default_rng(SEED).integers(0, c.vocab, sequences).astype(np.int32)
     steps = new_tokens - 3
-    return {"layers": n_layers, "of_layers": 45, "n_gpus": world, "sequences": sequences, "context": context,
-            "state": "synthetic session state at the stated context (filled on the device), no prompts run",
-            "timed_steps": steps, "ms_per_step": 1e3 * decode_s / steps, "tokens_per_s": sequences * steps / decode_s,
-            "tokens_per_s_per_sequence": steps / decode_s,
-            "attention": "every sequence on every rank (no sequence parallelism); routed experts split over the ranks",
-            "tokens_equal_on_all_ranks": all(t == all_toks[0] for t in all_toks),
-            "prefill": {"tokens": prefill_tokens, "ms": 1e3 * prefill_s, "tokens_per_s": prefill_tokens / prefill_s,
-                        "chunk": 64}}
+
+    def arm(split: bool, with_prefill: bool):
+        own = sequences // world if split else sequences
+        eng, err = None, ""
+        opts = {"latent_bf16": 1, "sequences": own}
+        if split:
+            opts["sequence_split"] = 1
+        try:
+            eng = fullmodel.build_engine(spec, SEED, cap, local, rank, world, options=opts)
+        except Exception as exc:                                       # noqa: BLE001
+            err = repr(exc)[:300]
+        if not ranks.all_ok(not err):
+            if eng is not None:
+                eng.close()
+            return {"error": err or "another rank could not build the model"}, None
+        handles = ranks.gather(eng.ep_export() if world > 1 else b"")
+        try:
+            if world > 1:
+                eng.ep_connect(handles)
+        except Exception as exc:                                       # noqa: BLE001
+            err = repr(exc)[:300]
+        if not ranks.all_ok(not err):
+            eng.close()
+            return {"error": err or "another rank could not connect"}, None
+        decode_s = prefill_s = 0.0
+        toks = None
+        try:
+            eng.synth_session(SEED, context)
+            ids = all_ids[rank * own:(rank + 1) * own] if split else all_ids
+            for _ in range(3):                                         # warm-up steps (they advance the sequences too)
+                _, ids = eng.decode_batch(ids, want_logits=False)
+            ranks.barrier()
+            t0 = time.perf_counter()
+            for _ in range(steps):
+                _, ids = eng.decode_batch(ids, want_logits=False)
+            decode_s = time.perf_counter() - t0
+            toks = ids.tolist()
+            if with_prefill:
+                # prefill throughput: one prompt through sequence 0 from an empty session
+                eng.reset()
+                prompt = np.random.default_rng(SEED + 1).integers(0, c.vocab, prefill_tokens).astype(np.int32)
+                eng.use_sequence(0)
+                eng.forward(prompt[:128], want_logits=False)           # warm-up chunk pair
+                eng.reset()
+                eng.use_sequence(0)
+                ranks.barrier()
+                t0 = time.perf_counter()
+                eng.forward(prompt, want_logits=False)
+                prefill_s = time.perf_counter() - t0
+        except Exception as exc:                                       # noqa: BLE001
+            err = repr(exc)[:300]
+        ok = ranks.all_ok(not err)
+        decode_s = ranks.reduce(decode_s, "max")
+        prefill_s = ranks.reduce(prefill_s, "max")
+        all_toks = ranks.gather(toks)
+        eng.close()
+        if not ok:
+            return {"error": err or "another rank failed"}, None
+        res = {"sequences_per_rank": own, "timed_steps": steps, "ms_per_step": 1e3 * decode_s / steps,
+               "tokens_per_s": sequences * steps / decode_s, "tokens_per_s_per_sequence": steps / decode_s}
+        if with_prefill:
+            res["prefill"] = {"tokens": prefill_tokens, "ms": 1e3 * prefill_s, "tokens_per_s": prefill_tokens / prefill_s, "chunk": 64}
+        return res, all_toks
+
+    out = {"layers": n_layers, "of_layers": 45, "n_gpus": world, "sequences": sequences, "context": context,
+           "state": "synthetic session state at the stated context (filled on the device), no prompts run"}
+    rep, rep_toks = arm(False, True)
+    if "error" in rep:
+        return rep
+    out.update(rep)
+    out["attention"] = "every sequence on every rank (no sequence parallelism); routed experts split over the ranks"
+    out["tokens_equal_on_all_ranks"] = all(t == rep_toks[0] for t in rep_toks)
+    if world > 1 and sequences % world == 0:
+        sp, sp_toks = arm(True, False)
+        if "error" not in sp:
+            sp["attention"] = ("sequences split over the ranks: attention and every per-token kernel for sequences / N per rank; MoE "
+                               "layers gather the ranks' tokens over peer stores (dispatch) and send contribution rows to the token's rank (combine)")
+            flat = [t for ts in sp_toks for t in ts]
+            # (the unsplit arm sums the KDA output projection over the ranks, this arm does not: a last-bit
+            # difference can flip an arg-max of a random-init model's near-uniform logits after many steps)
+            sp["sequences_with_the_unsplit_arm_s_last_token"] = int(sum(a == b for a, b in zip(flat, rep_toks[0])))
+        out["sequence_split"] = sp
+    return out
 
 
 def main():

@@ -156,6 +156,9 @@ def _declare(L, prefix: str, handle):
     sig("op_decoder_layer", [handle, C.c_int, f32p, C.c_int, C.c_int])
     sig("state_write", [handle, C.c_int, C.c_int, C.c_size_t, f32p, C.c_size_t])
     sig("state_read", [handle, C.c_int, C.c_int, C.c_size_t, f32p, C.c_size_t])
+    sig(f"{model}_enable_mtp", [handle])
+    sig("mtp_feed", [handle, f32p, C.c_void_p, C.c_int, C.c_void_p, f32p])
+    sig("mtp_hidden", [handle, C.c_int, C.c_int, f32p])
 
 
 def _f32(a) -> np.ndarray:
@@ -209,6 +212,34 @@ class FlatModel:
 
     def reset(self):
         self._fn(f"{self.model_word}_reset")(self.handle)
+
+    # ---- the multi-token-prediction layer (src/model/glm53f_mtp.h)
+    def enable_mtp(self):
+        """Before loading: the model then also takes the tensors of checkpoint layer n_layers."""
+        if self._fn(f"{self.model_word}_enable_mtp")(self.handle) != 0:
+            self._err("enable_mtp")
+
+    def mtp_feed(self, next_ids, h=None, want_draft=True):
+        """glm53f_mtp_feed: T positions' hidden states (None: the ones the last forward call kept)
+        and the tokens that follow them. Returns (draft token or None, the layer's output rows [T][hidden])."""
+        ids = np.ascontiguousarray(next_ids, dtype=np.int32)
+        T = int(ids.size)
+        hp = None
+        if h is not None:
+            h = _f32(h).reshape(T, self.cfg.hidden)
+            hp = h.ctypes.data
+        x = np.zeros((T, self.cfg.hidden), np.float32)
+        draft = C.c_int(-1)
+        if self._fn("mtp_feed")(self.handle, hp, ids.ctypes.data, T, C.addressof(draft) if want_draft else None,
+                                x.ctypes.data) != 0:
+            self._err("mtp_feed")
+        return (int(draft.value) if want_draft else None), x
+
+    def mtp_hidden(self, first: int, T: int) -> np.ndarray:
+        out = np.zeros((T, self.cfg.hidden), np.float32)
+        if self._fn("mtp_hidden")(self.handle, first, T, out.ctypes.data) != 0:
+            self._err("mtp_hidden")
+        return out
 
     @property
     def cached(self) -> int:

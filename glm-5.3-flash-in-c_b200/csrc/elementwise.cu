@@ -42,6 +42,19 @@ void rms_apply(cudaStream_t st, float *y, const float *x, const float *w, const 
     G5B_LAUNCH(rms_apply_kernel, dim3((n + 255) / 256, rows), 256, 0, st, y, x, w, inv, n, ld);
 }
 
+// x[i] += y[i], one FP32 rounding (the residual additions of the reference's MTP layer,
+// src/model/glm53f_mtp.c:124,129).
+__global__ void add_rows_kernel(float *x, const float *y, size_t n)
+{
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        x[i] = __fadd_rn(x[i], y[i]);
+}
+void add_rows(cudaStream_t st, float *x, const float *y, size_t n)
+{
+    const size_t want = (n + 255) / 256;
+    G5B_LAUNCH(add_rows_kernel, (int)(want < 1184 ? want : 1184), 256, 0, st, x, y, n);
+}
+
 // ----------------------------------------------------------------- SwiGLU ----
 // glm53f_swiglu_clamp, src/core/glm53f_ops.c:486-494: gate clamped from above only.
 __device__ __forceinline__ float swiglu_one(float g, float u, float lim)

@@ -98,6 +98,16 @@ struct g5b_engine {
     size_t ts_area_bytes = 0;                    // one parity's [ep_size][CHUNK][hidden] floats
     float *ts_part = nullptr;                    // this rank's partial rows [CHUNK][hidden]
     int tensor_split = 1;                        // option "tensor_split": KDA heads and their state split over the ranks   // of them, by the one-token kernel (its arrival counters count CTAs)
+    // the multi-token-prediction layer (checkpoint layer n_layers; g5b_engine_enable_mtp): one more
+    // Layer slot (MLA + MoE, no mHC tensors), its norms and input projection, its own position count
+    bool mtp = false;
+    int mtp_cached = 0;
+    float *enorm = nullptr, *hnorm = nullptr, *head_norm = nullptr;
+    DMat eh;
+    float *mtp_h = nullptr;                      // [cap + CHUNK][hidden]: stream means of the positions of the last forward call
+    float *mtp_cat = nullptr, *mtp_x = nullptr;  // [CHUNK][2 hidden], [CHUNK][hidden]
+    int seq_split = 0;                           // option "sequence_split": every rank runs its own sequences, MoE layers
+                                                 // gather the ranks' tokens and send contribution rows home
     int *ep_arrive = nullptr;
     int ep_wait_ms = 5000;                       // wall-clock limit of a wait for the other ranks (option "ep_wait_ms")
     bool dirty = false;                          // a call failed half-way: session state is undefined until reset
@@ -180,12 +190,20 @@ static void plan_layer(g5b_engine *e, int l)
     const int E = c.hidden, M = c.hc_mult, MIX = (2 + M) * M;
     add_vec(e, l, "input_layernorm.weight", &w.in_norm, E);
     add_vec(e, l, "post_attention_layernorm.weight", &w.post_norm, E);
-    add_mat(e, l, "hc_attn_fn", &w.hc[0].fn, MIX, M * E);
-    add_vec(e, l, "hc_attn_base", &w.hc[0].base, MIX);
-    add_vec(e, l, "hc_attn_scale", &w.hc[0].scale, 3);
-    add_mat(e, l, "hc_ffn_fn", &w.hc[1].fn, MIX, M * E);
-    add_vec(e, l, "hc_ffn_base", &w.hc[1].base, MIX);
-    add_vec(e, l, "hc_ffn_scale", &w.hc[1].scale, 3);
+    if (l == c.n_layers) {
+        // the MTP layer carries no mHC mixers (src/model/glm53f_bind.c:208-222)
+        add_vec(e, l, "enorm.weight", &e->enorm, E);
+        add_vec(e, l, "hnorm.weight", &e->hnorm, E);
+        add_vec(e, l, "shared_head.norm.weight", &e->head_norm, E);
+        add_mat(e, l, "eh_proj.weight", &e->eh, E, 2 * E);
+    } else {
+        add_mat(e, l, "hc_attn_fn", &w.hc[0].fn, MIX, M * E);
+        add_vec(e, l, "hc_attn_base", &w.hc[0].base, MIX);
+        add_vec(e, l, "hc_attn_scale", &w.hc[0].scale, 3);
+        add_mat(e, l, "hc_ffn_fn", &w.hc[1].fn, MIX, M * E);
+        add_vec(e, l, "hc_ffn_base", &w.hc[1].base, MIX);
+        add_vec(e, l, "hc_ffn_scale", &w.hc[1].scale, 3);
+    }
     if (w.is_mla) {
         const int H = c.mla_heads, IH = c.index_heads, ID = c.index_dim;
         add_mat(e, l, "self_attn.q_a_proj.weight", &w.q_a, c.q_lora, E);
@@ -281,6 +299,24 @@ extern "C" g5b_engine *g5b_engine_create(const g5b_config *cfg, const uint8_t *i
     return e;
 }
 
+// Checkpoint layer n_layers, the multi-token-prediction layer (src/model/glm53f_mtp.h): call before
+// loading; the engine then expects "layers.<n_layers>.*" (an MLA + MoE layer without mHC tensors,
+// enorm, hnorm, shared_head.norm, eh_proj) and keeps every position's stream mean for g5b_mtp_feed.
+extern "C" int g5b_engine_enable_mtp(g5b_engine *e)
+{
+    if (!e || e->finalized) return fail("enable_mtp after finalize");
+    if (e->mtp) return 0;
+    if (e->c.n_layers + 1 > G5B_MAX_LAYERS) return fail("no room for the MTP layer");
+    const int l = e->c.n_layers;
+    e->L.resize((size_t)l + 1);
+    e->names.resize((size_t)l + 1);
+    e->L[l].is_mla = true;
+    e->L[l].is_dense = false;
+    e->mtp = true;
+    plan_layer(e, l);
+    return 0;
+}
+
 static int ep_loopback(g5b_engine *e);
 extern "C" int g5b_engine_set_option(g5b_engine *e, const char *name, int value)
 {
@@ -302,6 +338,12 @@ extern "C" int g5b_engine_set_option(g5b_engine *e, const char *name, int value)
     if (!strcmp(name, "tensor_split")) {
         if (e->ts_launches) return fail("tensor_split cannot change once a split layer has run (each rank holds only its heads' state)");
         e->tensor_split = value != 0;
+        return 0;
+    }
+    if (!strcmp(name, "sequence_split")) {
+        if (e->ts_launches || e->ep_step) return fail("sequence_split cannot change once the ranks have exchanged anything");
+        if (value && e->ep_size < 2) return fail("sequence_split needs an expert-parallel engine (ep_size > 1)");
+        e->seq_split = value != 0;
         return 0;
     }
     if (!strcmp(name, "ep_loopback")) return value ? ep_loopback(e) : 0;
@@ -438,7 +480,7 @@ extern "C" int g5b_engine_load(g5b_engine *e, const char *name, const g5b_tensor
     if (!strcmp(name, "lm_head.weight")) return upload_mat(e, &e->lm_head, t, c.vocab, c.hidden, name);
     if (!strcmp(name, "norm.weight")) return upload_vec(e, &e->norm, t, (size_t)c.hidden, name);
     int l = -1, used = 0;
-    if (sscanf(name, "layers.%d.%n", &l, &used) != 1 || l < 0 || l >= c.n_layers)
+    if (sscanf(name, "layers.%d.%n", &l, &used) != 1 || l < 0 || l >= (int)e->L.size())
         return fail("unknown tensor %s", name);
     const char *rest = name + used;
     int ex = -1, n2 = 0;
@@ -477,7 +519,7 @@ extern "C" int g5b_engine_reserve(g5b_engine *e, const char *name, int dtype, in
     } else if (!strcmp(name, "lm_head.weight")) { m = &e->lm_head; want_r = c.vocab; want_c = c.hidden; }
     else {
         int l = -1, used = 0;
-        if (sscanf(name, "layers.%d.%n", &l, &used) != 1 || l < 0 || l >= c.n_layers) return fail("unknown tensor %s", name);
+        if (sscanf(name, "layers.%d.%n", &l, &used) != 1 || l < 0 || l >= (int)e->L.size()) return fail("unknown tensor %s", name);
         const char *rest = name + used;
         int ex = -1, n2 = 0;
         if (!e->L[l].is_dense && sscanf(rest, "mlp.experts.%d.%n", &ex, &n2) == 1) {
@@ -520,13 +562,13 @@ extern "C" int g5b_engine_wants_vector(g5b_engine *e, const char *name)
 {
     if (!strcmp(name, "norm.weight")) return 1;
     int l = -1, used = 0;
-    if (sscanf(name, "layers.%d.%n", &l, &used) != 1 || l < 0 || l >= e->c.n_layers) return 0;
+    if (sscanf(name, "layers.%d.%n", &l, &used) != 1 || l < 0 || l >= (int)e->L.size()) return 0;
     auto it = e->names[l].find(name + used);
     return it != e->names[l].end() && it->second.kind == 1;
 }
 
 extern "C" int g5b_engine_device(const g5b_engine *e) { return e->device; }
-extern "C" int g5b_engine_layers(const g5b_engine *e) { return e->c.n_layers; }
+extern "C" int g5b_engine_layers(const g5b_engine *e) { return (int)e->L.size(); }   // the MTP layer included once enabled
 
 extern "C" int g5b_engine_fill_expert(g5b_engine *e, int layer, int expert, uint64_t seed,
                                       const float *gate_s, const float *up_s, const float *down_s)
@@ -534,7 +576,7 @@ extern "C" int g5b_engine_fill_expert(g5b_engine *e, int layer, int expert, uint
     if (e->finalized) return fail("fill after finalize");
     CU(cudaSetDevice(e->device));
     const g5b_config &c = e->c;
-    if (layer < 0 || layer >= c.n_layers || e->L[layer].is_dense) return fail("layer %d is not a MoE layer", layer);
+    if (layer < 0 || layer >= (int)e->L.size() || e->L[layer].is_dense) return fail("layer %d is not a MoE layer", layer);
     if (expert < e->n_local0 || expert >= e->n_local0 + e->n_local) return 0;
     Layer &w = e->L[layer];
     if (ensure_expert_slab(e, w, G5B_DT_FP8)) return -1;
@@ -569,7 +611,7 @@ extern "C" int g5b_engine_fill_matrix(g5b_engine *e, const char *name, int dtype
     else if (!strcmp(name, "lm_head.weight")) { m = &e->lm_head; rows = c.vocab; cols = c.hidden; }
     else {
         int l = -1, used = 0;
-        if (sscanf(name, "layers.%d.%n", &l, &used) != 1 || l < 0 || l >= c.n_layers) return fail("unknown tensor %s", name);
+        if (sscanf(name, "layers.%d.%n", &l, &used) != 1 || l < 0 || l >= (int)e->L.size()) return fail("unknown tensor %s", name);
         auto it = e->names[l].find(name + used);
         if (it == e->names[l].end() || it->second.kind != 0) return fail("%s is not a matrix of layer %d", name, l);
         m = it->second.mat; rows = it->second.rows; cols = it->second.cols;
@@ -606,7 +648,7 @@ extern "C" int g5b_engine_finalize(g5b_engine *e)
     // A missing tensor must fail here: running with a NULL or zero weight gives plausible, wrong
     // tokens (the reference's bind refuses for the same reason, src/model/glm53f_bind.h:3-6).
     // Single-layer harnesses may leave embeddings and the head out; forward then refuses.
-    for (int l = 0; l < c.n_layers; l++) {
+    for (int l = 0; l < (int)e->L.size(); l++) {
         Layer &w = e->L[l];
         for (auto &kv : e->names[l]) {
             const Target &t = kv.second;
@@ -684,10 +726,12 @@ extern "C" int g5b_engine_finalize(g5b_engine *e)
     }
     if (walloc(e, &e->xm, N * E) || walloc(e, &e->inv_head, N) || walloc(e, &e->logits, N * (size_t)c.vocab) ||
         walloc(e, &e->am_v, N * 64) || walloc(e, &e->am_i, N * 64) || walloc(e, &e->am_out, (size_t)e->cap + N)) return -1;
+    if (e->mtp && (walloc(e, &e->mtp_h, ((size_t)e->cap + N) * E) || walloc(e, &e->mtp_cat, N * 2 * E) ||
+                   walloc(e, &e->mtp_x, N * E))) return -1;
     CU(cudaStreamSynchronize(e->st));
     {
         const int P = c.kda_heads * c.kda_head_dim;
-        int max_c = c.hidden;
+        int max_c = e->mtp ? 2 * c.hidden : c.hidden;
         for (int v : {P, c.q_lora, c.kv_lora, c.kda_head_dim, c.mla_heads * c.v_head}) max_c = v > max_c ? v : max_c;
         for (int v : {c.dense_inter, c.moe_inter * c.n_shared}) max_c = v > max_c ? v : max_c;
         e->tc = tc_gemm_create(max_c, e->err_dev);
@@ -727,6 +771,56 @@ static void prof_collect(g5b_engine *e, int nslots)
 }
 
 // x [n][E] (already normalised) -> out [n][E]. Router, plan, experts, combine.
+// A MoE layer with the sequences split over the ranks (option "sequence_split"): x holds this
+// rank's own n tokens, and every rank calls with the same n. The ranks' tokens are gathered
+// everywhere (peer stores, arrival counters: the dispatch), every rank routes the gathered tokens
+// in groups of at most CHUNK and multiplies them by the experts it owns, the contribution rows go
+// to the exchange buffer of the rank a token lives on (the combine's transfer), and that rank
+// sums its own tokens in top-k order with the shared expert, which it computed for its own tokens
+// only. The groups are taken in rotated order so that the one holding the own tokens comes last:
+// its router weights and shared rows are then still in place for the combine.
+static int run_moe_seq_split(g5b_engine *e, Layer &w, const float *x, int n, float *out, int with_shared, const MoeShape &s)
+{
+    const g5b_config &c = e->c;
+    const bool shared_in_plan = with_shared && c.n_shared == 1 && w.sh_gate.dt == s.dt;
+    if (with_shared && !shared_in_plan) return fail("sequence_split needs the shared expert in the routed experts' format");
+    const int N = e->ep_size, me = e->ep_rank;
+    prof_mark(e, 0);
+    ++e->ts_launches;
+    const size_t area_off = EP_FLAG_BYTES + 2 * e->ep_rows_bytes + (size_t)(e->ts_launches & 1) * e->ts_area_bytes;
+    TsReduce g{x, nullptr, 0, e->ep_peers_dev, me, N, n, c.hidden, n, area_off, 2 * N, e->ts_launches,
+               (unsigned long long)e->ep_wait_ms * 1000000ull, e->err_dev, 1};
+    ts_allreduce(e->st, g);
+    prof_mark(e, 1);
+    const float *all = reinterpret_cast<const float *>(e->ep_region + area_off);     // [N * n][hidden], rank order
+    const int per = CHUNK / n > 0 ? CHUNK / n : 1;                                   // ranks per group
+    const int groups = (N + per - 1) / per, mine = me / per;
+    ++e->ep_step;
+    for (int k = 1; k <= groups; k++) {
+        const int gi = (mine + k) % groups, r0 = gi * per, r1 = r0 + per < N ? r0 + per : N;
+        const int m = (r1 - r0) * n, g0 = r0 * n;
+        const bool last = gi == mine;
+        const float *xg = all + (size_t)g0 * c.hidden;
+        router_plan(e->st, e->ridx, e->rw, e->rscore, xg, c.hidden, w.router.w, w.router.dt, w.bias, m, s, e->plan,
+                    with_shared ? 1 : 0, e->counter, last ? me * n - g0 : 0, last ? n : 0);
+        if (e->expert_path >= 1 && moe_mma_batch_supported(s, m)) {
+            moe_mma_batch_gateup(e->st, e->act, e->xterms, e->xinv, xg, c.hidden, w.table_dev, e->plan, m, s, e->err_dev);
+            moe_mma_batch_down(e->st, e->contrib, e->act, w.table_dev, e->plan, m, s, e->err_dev);
+        } else {
+            moe_gateup(e->st, e->act, xg, c.hidden, w.table_dev, e->plan, m, s);
+            moe_down(e->st, e->contrib, e->act, w.table_dev, e->plan, m, s);
+        }
+        SeqExchange q{e->contrib, e->plan, e->ep_peers_dev, me, N, n, m, g0, c.topk, c.hidden, with_shared, last ? 1 : 0,
+                      EP_FLAG_BYTES + (size_t)(e->ep_step & 1) * e->ep_rows_bytes, e->ep_step, e->ep_arrive, e->rw,
+                      out, c.hidden, e->err_dev, (unsigned long long)e->ep_wait_ms * 1000000ull};
+        const int want = (int)(((size_t)m * c.hidden + 255) / 256);
+        seq_exchange(e->st, q, want < 8 ? 8 : want > 148 ? 148 : want);
+    }
+    prof_mark(e, 2); prof_mark(e, 3); prof_mark(e, 4);
+    prof_collect(e, 4);
+    return 0;
+}
+
 static int run_moe(g5b_engine *e, Layer &w, const float *x, int n, float *out, int with_shared)
 {
     const g5b_config &c = e->c;
@@ -735,6 +829,7 @@ static int run_moe(g5b_engine *e, Layer &w, const float *x, int n, float *out, i
     if (e->ep_size > 1 && !e->ep_connected)
         return fail("expert-parallel engine: connect the ranks (g5b_engine_ep_connect) before running a MoE layer");
     const MoeShape s = moe_shape(e, w);
+    if (e->seq_split && e->ep_size > 1) return run_moe_seq_split(e, w, x, n, out, with_shared, s);
     const bool shared_in_plan = with_shared && c.n_shared == 1 && w.sh_gate.dt == s.dt;
     const bool one_gpu_decode = e->ep_size == 1 && (shared_in_plan || !with_shared);
     prof_mark(e, 0);
@@ -871,7 +966,7 @@ static void trunk_allreduce(g5b_engine *e, float *out, int ldo, int n)
     ++e->ts_launches;
     TsReduce r{e->ts_part, out, ldo, e->ep_peers_dev, e->ep_rank, e->ep_size, n, e->c.hidden, CHUNK,
                EP_FLAG_BYTES + 2 * e->ep_rows_bytes + (size_t)(e->ts_launches & 1) * e->ts_area_bytes, 2 * e->ep_size,
-               e->ts_launches, (unsigned long long)e->ep_wait_ms * 1000000ull, e->err_dev};
+               e->ts_launches, (unsigned long long)e->ep_wait_ms * 1000000ull, e->err_dev, 0};
     ts_allreduce(e->st, r);
 }
 
@@ -888,7 +983,7 @@ static int run_kda(g5b_engine *e, Layer &w, const float *x, int n, float *out, b
     const int E = c.hidden, H = c.kda_heads, D = c.kda_head_dim, P = H * D;
     if (!w.kq.loaded() || !w.ko.loaded() || !w.g_b.loaded() || !w.f_b.loaded() || !w.kda_state || !w.dt_bias)
         return fail("this layer's KDA weights were not loaded");
-    const bool ts = e->tensor_split && e->ep_size > 1 && e->ep_connected && H % e->ep_size == 0 && (E % 4) == 0 &&
+    const bool ts = e->tensor_split && !e->seq_split && e->ep_size > 1 && e->ep_connected && H % e->ep_size == 0 && (E % 4) == 0 &&
                     w.kq.dt != G5B_DT_FP8 && w.kk.dt != G5B_DT_FP8 && w.kv.dt != G5B_DT_FP8 && w.ko.dt != G5B_DT_FP8 &&
                     w.f_b.dt != G5B_DT_FP8 && w.g_b.dt != G5B_DT_FP8 && w.kb.dt != G5B_DT_FP8;
     const int Hl = ts ? H / e->ep_size : H, h0 = ts ? e->ep_rank * Hl : 0, Pl = Hl * D, p0 = h0 * D;
@@ -1092,6 +1187,9 @@ static int forward_device(g5b_engine *e, const int *ids_dev, int T, bool all_pos
             if (run_layer(e, l, e->h + (size_t)t0 * M * E, n, batch ? e->cached : e->cached + t0, batch)) return -1;
         }
     flush_hc_post(e);
+    // with the MTP layer open every position's stream mean is kept, row t of this call
+    // (src/model/glm53f_model.c:460-468)
+    if (e->mtp && (size_t)T <= (size_t)e->cap + CHUNK) head_mean(e->st, e->mtp_h, e->h, T, M, E);
     const int first = all_positions ? 0 : T - 1;
     for (int t0 = first; t0 < T; t0 += CHUNK) {
         const int n = T - t0 < CHUNK ? T - t0 : CHUNK;
@@ -1208,6 +1306,7 @@ extern "C" void g5b_engine_reset(g5b_engine *e)
         if (w.kda_state) cudaMemsetAsync(w.kda_state, 0, (size_t)e->n_seq * e->kda_seq * 4, e->st);
     cudaStreamSynchronize(e->st);
     e->cached = 0;
+    e->mtp_cached = 0;
     e->dirty = false;
     e->post_h = nullptr;
     for (auto &v : e->cached_seq) v = 0;
@@ -1223,19 +1322,23 @@ extern "C" int g5b_engine_synth_session(g5b_engine *e, uint64_t seed, int positi
     if (positions < 0 || positions >= e->cap) return fail("%d positions do not leave room in a capacity of %d", positions, e->cap);
     CU(cudaSetDevice(e->device));
     const float unit = 1.0f / 37837.2f;
+    // with the sequences split over the ranks, local sequence q is sequence rank * n_seq + q of the
+    // whole batch and gets that sequence's values (an element's value is a hash of key + its index)
+    const size_t first = e->seq_split ? (size_t)e->ep_rank * e->n_seq : 0;
     for (size_t l = 0; l < e->L.size(); l++) {
         Layer &w = e->L[l];
         char name[64];
         if (w.kda_state) {
             snprintf(name, sizeof name, "state.%zu.kda", l);
-            fill_f32_key(e->st, w.kda_state, synth_key(seed, name), 0.1f * unit, (size_t)e->n_seq * e->kda_seq);
+            fill_f32_key(e->st, w.kda_state, synth_key(seed, name) + first * e->kda_seq, 0.1f * unit, (size_t)e->n_seq * e->kda_seq);
         }
         if (w.latent) {
             snprintf(name, sizeof name, "state.%zu.latent", l);
-            if (e->latent_bf16) fill_bf16_key(e->st, static_cast<uint16_t *>(w.latent), synth_key(seed, name), unit, (size_t)e->n_seq * e->lat_seq);
-            else                fill_f32_key(e->st, static_cast<float *>(w.latent), synth_key(seed, name), unit, (size_t)e->n_seq * e->lat_seq);
+            const uint64_t key = synth_key(seed, name) + first * e->lat_seq;
+            if (e->latent_bf16) fill_bf16_key(e->st, static_cast<uint16_t *>(w.latent), key, unit, (size_t)e->n_seq * e->lat_seq);
+            else                fill_f32_key(e->st, static_cast<float *>(w.latent), key, unit, (size_t)e->n_seq * e->lat_seq);
             snprintf(name, sizeof name, "state.%zu.indexer", l);
-            fill_f32_key(e->st, w.idx_state, synth_key(seed, name), unit, (size_t)e->n_seq * e->idx_seq);
+            fill_f32_key(e->st, w.idx_state, synth_key(seed, name) + first * e->idx_seq, unit, (size_t)e->n_seq * e->idx_seq);
         }
     }
     CU(cudaStreamSynchronize(e->st));
@@ -1331,7 +1434,7 @@ extern "C" void *g5b_engine_stream(g5b_engine *e) { return (void *)e->st; }
 static int check_layer(g5b_engine *e, int layer, int n)
 {
     if (!e->finalized) return fail("op before finalize");
-    if (layer < 0 || layer >= e->c.n_layers) return fail("layer %d out of range", layer);
+    if (layer < 0 || layer >= (int)e->L.size()) return fail("layer %d out of range", layer);
     if (n < 1 || n > CHUNK) return fail("ops take 1..%d positions per call, got %d", CHUNK, n);
     if (cudaSetDevice(e->device) != cudaSuccess) return fail("cudaSetDevice failed");
     return 0;
@@ -1399,6 +1502,87 @@ static int check_op(g5b_engine *e, int layer, int T)
 }
 
 #define FOR_CHUNKS(T) for (int t0 = 0, n_ = 0; (n_ = (T) - t0 < CHUNK ? (T) - t0 : CHUNK), t0 < (T); t0 += CHUNK)
+
+// glm53f_mtp_feed (src/model/glm53f_mtp.c:100-144) on the MTP layer's own caches and position
+// count: x = eh_proj([RMSNorm(embed(next), enorm), RMSNorm(h, hnorm)]); x += MLA(RMSNorm(x,
+// input_layernorm)); x += MoE(RMSNorm(x, post_attention_layernorm)); for the last position the
+// draft is the first-max arg-max of lm_head(RMSNorm(x, shared_head.norm)). h: T host rows, or NULL
+// for the rows the last forward call kept on the device. x_out: host [T][hidden] or NULL.
+extern "C" int g5b_mtp_feed(g5b_engine *e, const float *h, const int *next_ids, int T, int *draft, float *x_out)
+{
+    if (!e || !e->finalized || !e->mtp) return fail("the MTP layer is not enabled (g5b_engine_enable_mtp before loading)");
+    CU(cudaSetDevice(e->device));
+    const g5b_config &c = e->c;
+    const int E = c.hidden;
+    if (T < 1) return fail("mtp_feed needs at least one position");
+    if (e->mtp_cached + T > e->cap) return fail("%d + %d MTP positions exceed the capacity %d", e->mtp_cached, T, e->cap);
+    if (!h && T > e->cap + CHUNK) return fail("no kept hidden states for %d positions", T);
+    for (int t = 0; t < T; t++)
+        if (next_ids[t] < 0 || next_ids[t] >= c.vocab) return fail("token id %d outside the vocabulary", next_ids[t]);
+    if (!e->embed.loaded() || !e->lm_head.loaded() || !e->eh.loaded() || !e->enorm || !e->hnorm || !e->head_norm)
+        return fail("mtp_feed needs embed_tokens, lm_head and the MTP layer's tensors");
+    Layer &w = e->L[(size_t)c.n_layers];
+    if (ensure_ids(e, (size_t)T)) return -1;
+    CU(cudaMemcpyAsync(e->ids_dev, next_ids, (size_t)T * 4, cudaMemcpyHostToDevice, e->st));
+    Staged s{e};
+    const float *hd = e->mtp_h;
+    if (h) {
+        hd = s.in(h, (size_t)T * E);
+        if (!hd) return fail("out of device memory");
+    }
+    float *xo = nullptr;
+    if (x_out) {
+        xo = s.in(nullptr, (size_t)T * E);
+        if (!xo) return fail("out of device memory");
+    }
+    e->post_h = nullptr;
+    for (int t0 = 0; t0 < T; t0 += CHUNK) {
+        const int n = T - t0 < CHUNK ? T - t0 : CHUNK;
+        float *cat = e->mtp_cat, *x = e->mtp_x;
+        embed_rows(e->st, cat, e->embed, e->ids_dev + t0, n, 2);                 // both halves; the second is replaced
+        CU(cudaMemcpy2DAsync(cat + E, (size_t)2 * E * 4, hd + (size_t)t0 * E, (size_t)E * 4, (size_t)E * 4, (size_t)n,
+                             cudaMemcpyDeviceToDevice, e->st));
+        rms_factor(e->st, cat, E, 2 * E, n, c.rms_eps, e->inv0);
+        rms_apply(e->st, cat, cat, e->enorm, e->inv0, E, 2 * E, n);
+        rms_factor(e->st, cat + E, E, 2 * E, n, c.rms_eps, e->inv1);
+        rms_apply(e->st, cat + E, cat + E, e->hnorm, e->inv1, E, 2 * E, n);
+        if (proj(e, e->eh, cat, 2 * E, x, E, n)) return -1;
+        rms_factor(e->st, x, E, E, n, c.rms_eps, e->inv1);
+        rms_apply(e->st, e->xn, x, w.in_norm, e->inv1, E, E, n);
+        if (run_mla(e, w, e->xn, n, e->mtp_cached + t0, e->y)) return -1;
+        add_rows(e->st, x, e->y, (size_t)n * E);
+        rms_factor(e->st, x, E, E, n, c.rms_eps, e->inv1);
+        rms_apply(e->st, e->xn, x, w.post_norm, e->inv1, E, E, n);
+        if (run_moe(e, w, e->xn, n, e->y, 1)) return -1;
+        add_rows(e->st, x, e->y, (size_t)n * E);
+        if (xo) CU(cudaMemcpyAsync(xo + (size_t)t0 * E, x, (size_t)n * E * 4, cudaMemcpyDeviceToDevice, e->st));
+        if (draft && t0 + n == T) {
+            const float *last = x + (size_t)(n - 1) * E;
+            rms_factor(e->st, last, E, E, 1, c.rms_eps, e->inv_head);
+            if (proj(e, e->lm_head, last, E, e->logits, c.vocab, 1, e->inv_head, e->head_norm)) return -1;
+            argmax_rows(e->st, e->am_out, e->logits, c.vocab, 1, e->am_v, e->am_i);
+            CU(cudaMemcpyAsync(draft, e->am_out, 4, cudaMemcpyDeviceToHost, e->st));
+        }
+    }
+    if (x_out && s.out(x_out, xo, (size_t)T * E)) return -1;
+    CU(cudaStreamSynchronize(e->st));
+    CU(cudaGetLastError());
+    if (check_device_error(e)) return -1;
+    e->mtp_cached += T;
+    return 0;
+}
+
+// The stream means the last forward call kept: T rows from row `first`, to the host.
+extern "C" int g5b_mtp_hidden(g5b_engine *e, int first, int T, float *dst)
+{
+    if (!e || !e->finalized || !e->mtp) return fail("the MTP layer is not enabled");
+    if (first < 0 || T < 1 || first + T > e->cap + CHUNK) return fail("rows outside the kept hidden states");
+    CU(cudaSetDevice(e->device));
+    CU(cudaMemcpyAsync(dst, e->mtp_h + (size_t)first * e->c.hidden, (size_t)T * e->c.hidden * 4, cudaMemcpyDeviceToHost, e->st));
+    CU(cudaStreamSynchronize(e->st));
+    return 0;
+}
+
 
 // Host buffers through the engine's own staging rows (no allocation per call): copy a piece in,
 // run, copy the result out; one wait at the end. With pinned host memory the copies overlap the
@@ -1572,7 +1756,7 @@ static DMat *find_mat(g5b_engine *e, const char *name)
     if (!strcmp(name, "embed_tokens.weight")) return &e->embed;
     if (!strcmp(name, "lm_head.weight")) return &e->lm_head;
     int l = -1, used = 0;
-    if (sscanf(name, "layers.%d.%n", &l, &used) != 1 || l < 0 || l >= e->c.n_layers) return nullptr;
+    if (sscanf(name, "layers.%d.%n", &l, &used) != 1 || l < 0 || l >= (int)e->L.size()) return nullptr;
     auto it = e->names[l].find(name + used);
     if (it == e->names[l].end() || it->second.kind != 0 || !it->second.mat->loaded()) return nullptr;
     return it->second.mat;
@@ -1618,7 +1802,7 @@ static float *state_ptr(g5b_engine *e, int layer, int kind, size_t *n, int *bf16
 
 extern "C" int g5b_state_write(g5b_engine *e, int layer, int kind, size_t offset, const float *src, size_t count)
 {
-    if (!e->finalized || layer < 0 || layer >= e->c.n_layers) return fail("state access on a bad layer");
+    if (!e->finalized || layer < 0 || layer >= (int)e->L.size()) return fail("state access on a bad layer");
     CU(cudaSetDevice(e->device));
     size_t n = 0; int bf = 0;
     float *p = state_ptr(e, layer, kind, &n, &bf);
@@ -1638,7 +1822,7 @@ extern "C" int g5b_state_write(g5b_engine *e, int layer, int kind, size_t offset
 
 extern "C" int g5b_state_read(g5b_engine *e, int layer, int kind, size_t offset, float *dst, size_t count)
 {
-    if (!e->finalized || layer < 0 || layer >= e->c.n_layers) return fail("state access on a bad layer");
+    if (!e->finalized || layer < 0 || layer >= (int)e->L.size()) return fail("state access on a bad layer");
     CU(cudaSetDevice(e->device));
     size_t n = 0; int bf = 0;
     float *p = state_ptr(e, layer, kind, &n, &bf);

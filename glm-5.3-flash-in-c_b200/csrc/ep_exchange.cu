@@ -88,7 +88,7 @@ __global__ void __launch_bounds__(256) ep_exchange_combine_kernel(const EpExchan
 // counts itself done on every rank (release-add, covering the CTA's stores through the barrier
 // before it), waits for every rank's counter to reach launch x CTAs and adds the slots of its own
 // float4s in rank order. All ranks run the same grid.
-constexpr int TS_CTAS = 8;
+constexpr int TS_CTAS = 8, TS_GATHER_CTAS = 32;
 __global__ void __launch_bounds__(256) ts_allreduce_kernel(const TsReduce a)
 {
     __shared__ int s_ok;
@@ -109,7 +109,7 @@ __global__ void __launch_bounds__(256) ts_allreduce_kernel(const TsReduce a)
         if (!wait_word_sys(mine, a.launch * gridDim.x, a.wait_ns)) { atomicExch(a.err, 40 + tid); s_ok = 0; }
     }
     __syncthreads();
-    if (!s_ok) return;
+    if (!s_ok || a.gather_only) return;
     const float4 *slots = reinterpret_cast<const float4 *>(static_cast<const uint8_t *>(a.peers[a.rank]) + a.area_off);
     for (size_t i = (size_t)blockIdx.x * blockDim.x + tid; i < n4; i += (size_t)gridDim.x * blockDim.x) {
         float4 s = __ldcg(slots + i);
@@ -122,9 +122,73 @@ __global__ void __launch_bounds__(256) ts_allreduce_kernel(const TsReduce a)
     }
 }
 
+// The exchange of a MoE layer with the sequences split over the ranks (SeqExchange, kernels.h).
+__global__ void __launch_bounds__(256) seq_exchange_kernel(const SeqExchange a)
+{
+    __shared__ int s_flag;
+    const int tid = threadIdx.x;
+    const size_t row_f4 = (size_t)a.E / 4;
+    const int routed_rows = a.m * a.K;
+    const int ns = *a.plan.n_slots;
+    const int total = ns > 0 ? a.plan.slot_off[ns - 1] + a.plan.slot_cnt[ns - 1] : 0;
+
+    // ---- 1. every routed row goes to the rank its token lives on
+    for (int p = blockIdx.x; p < total; p += gridDim.x) {
+        const int row = a.plan.pair_dst[p];
+        if (row >= routed_rows) continue;                       // the shared expert's rows stay local
+        const int g = a.g0 + row / a.K, pick = row % a.K;
+        const int home = g / a.n, lt = g % a.n;
+        const float4 *src = reinterpret_cast<const float4 *>(a.contrib + (size_t)row * a.E);
+        float4 *dst = reinterpret_cast<float4 *>(static_cast<uint8_t *>(a.peers[home]) + a.rows_off) + ((size_t)lt * a.K + pick) * row_f4;
+        for (size_t i = tid; i < row_f4; i += blockDim.x) dst[i] = src[i];
+    }
+    if (!a.finish) return;
+    // ---- 2. the last CTA to finish publishes this rank's word on every rank; the release is
+    // cumulative, so it covers the rows that the earlier groups' launches of this call delivered
+    __threadfence_system();
+    __syncthreads();
+    if (tid == 0) {
+        const int prev = atomicAdd(a.arrive, 1);
+        s_flag = prev == (int)gridDim.x - 1;
+    }
+    __syncthreads();
+    if (s_flag) {
+        if (tid == 0) *a.arrive = 0;
+        __threadfence_system();
+        if (tid < a.size) st_release_sys(reinterpret_cast<unsigned long long *>(a.peers[tid]) + a.rank, a.step);
+    }
+    // ---- 3. wait for every rank's word
+    bool seen = true;
+    if (tid < a.size) {
+        const unsigned long long *mine = reinterpret_cast<const unsigned long long *>(a.peers[a.rank]);
+        seen = wait_word_sys(mine + tid, a.step, a.wait_ns);
+        if (!seen) atomicExch(a.err, 20 + tid);
+    }
+    if (!__syncthreads_and(seen)) return;
+    // ---- 4. combine the own tokens from the local exchange buffer (the one-GPU arithmetic)
+    const float *rows = reinterpret_cast<const float *>(static_cast<const uint8_t *>(a.peers[a.rank]) + a.rows_off);
+    const int own0 = a.rank * a.n - a.g0;                       // first own token inside the group
+    const size_t n = (size_t)a.n * a.E;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + tid; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const int t = (int)(i / a.E), d = (int)(i % a.E);
+        double s = 0.0;
+        for (int j = 0; j < a.K; j++)
+            s += (double)a.w[(size_t)(own0 + t) * a.K + j] * (double)__ldcg(rows + ((size_t)t * a.K + j) * a.E + d);
+        float o = (float)s;
+        if (a.with_shared) o = __fadd_rn(o, a.contrib[((size_t)routed_rows + own0 + t) * a.E + d]);
+        a.out[(size_t)t * a.ldo + d] = o;
+    }
+}
+
+void seq_exchange(cudaStream_t st, const SeqExchange &a, int ctas)
+{
+    G5B_LAUNCH(seq_exchange_kernel, dim3(ctas), 256, 0, st, a);
+}
+
+// Every launch of a group must use the same grid: the arrival counters count launches x CTAs.
 void ts_allreduce(cudaStream_t st, const TsReduce &a)
 {
-    G5B_LAUNCH(ts_allreduce_kernel, TS_CTAS, 256, 0, st, a);
+    G5B_LAUNCH(ts_allreduce_kernel, a.gather_only ? TS_GATHER_CTAS : TS_CTAS, 256, 0, st, a);
 }
 
 void ep_exchange_combine(cudaStream_t st, const EpExchange &a, int ctas)

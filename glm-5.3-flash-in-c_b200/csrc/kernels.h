@@ -85,6 +85,7 @@ void swiglu(cudaStream_t st, float *y, const float *gu, int n, int rows, float l
 void shortconv(cudaStream_t st, float *y, const float *x, const float *w, float *state, int channels,
                int k, int T);
 void embed_rows(cudaStream_t st, float *h, const DMat &table, const int *ids, int T, int M);
+void add_rows(cudaStream_t st, float *x, const float *y, size_t n);
 void head_mean(cudaStream_t st, float *xm, const float *h, int T, int M, int E);
 void argmax_rows(cudaStream_t st, int *out, const float *logits, int n, int rows, float *scratch_v,
                  int *scratch_i);
@@ -147,7 +148,7 @@ struct MoeShape {
 // Router scores, top-k and the expert-major plan in one launch. p.n_slots == nullptr: routing only.
 void router_plan(cudaStream_t st, int *idx, float *w, float *score, const float *x, int ldx, const void *gate,
                  int gate_dt, const float *bias, int T, const MoeShape &s, const MoePlan &p, int with_shared,
-                 int *counter);
+                 int *counter, int shared_t0 = 0, int shared_n = -1);
 // Batch-1 experts multiplied by the tensor cores from their FP8 codes (moe_mma.cu); act_terms holds
 // the SwiGLU output split into two F16 terms per element, [pairs][2][I].
 bool moe_mma_supported(const MoeShape &s, int T);
@@ -223,8 +224,34 @@ struct TsReduce {
     unsigned long long launch;  // launches of this exchange so far, this one included
     unsigned long long wait_ns;
     int *err;
+    int gather_only;            // 1: stop after the wait - the slots (max_t = T makes them one dense
+                                // [size * T][E] block in rank order) are the result, nothing is summed
 };
 void ts_allreduce(cudaStream_t st, const TsReduce &a);
+
+// The exchange of a MoE layer whose sequences are split over the ranks (each rank runs attention and
+// every other per-token kernel for its own sequences only). The tokens of all ranks were gathered
+// first (TsReduce with gather_only); this rank routed a group of them - `m` consecutive tokens of
+// the gathered block starting at global token g0, `n` tokens per rank - and computed the rows of
+// the picks it owns. The kernel stores each row into the exchange buffer of the token's home rank
+// (global token / n) at row (token % n) * K + pick. With `finish` (the last group of the call,
+// the one that holds this rank's own tokens) it then publishes the step word on every rank, waits
+// (wall-clock limited) for every rank's word and combines its own n tokens in top-k order, adding
+// the shared expert's rows, which the plan computed for the own tokens only.
+struct SeqExchange {
+    const float *contrib;          // [m*K + m][E]
+    MoePlan plan;
+    void *const *peers;
+    int rank, size, n, m, g0, K, E, with_shared, finish;
+    size_t rows_off;
+    unsigned long long step;
+    int *arrive;
+    const float *w;                // router weights of the group [m][K]
+    float *out; int ldo;           // own tokens [n][ldo]
+    int *err;
+    unsigned long long wait_ns;
+};
+void seq_exchange(cudaStream_t st, const SeqExchange &a, int ctas);
 
 // ---- kda.cu -------------------------------------------------------------------------------
 struct KdaShape { int H, D, K; float gate_lb, rms_eps; };

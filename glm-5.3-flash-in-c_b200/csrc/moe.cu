@@ -41,6 +41,7 @@ struct RouterArgs {
     MoePlan p;
     int n_local0, n_local, with_shared;
     int *counter;
+    int sh_t0, sh_n;                 // the shared expert's slot takes tokens [sh_t0, sh_t0 + sh_n)
 };
 
 // Order-preserving key of a selection score; 0 = not selectable (NaN, -inf, already taken).
@@ -214,20 +215,21 @@ __global__ void __launch_bounds__(RT_WARPS * 32) router_kernel(const RouterArgs 
         a.p.pair_tok[pos] = i / a.K;
         a.p.pair_dst[pos] = i;
     }
-    if (a.with_shared) {
-        if (tid == 0) { a.p.slot_expert[total_slots] = a.n_local; a.p.slot_off[total_slots] = total_pairs; a.p.slot_cnt[total_slots] = a.T; }
-        for (int tt = tid; tt < a.T; tt += nth) { a.p.pair_tok[total_pairs + tt] = tt; a.p.pair_dst[total_pairs + tt] = n + tt; }
+    const bool shared = a.with_shared && a.sh_n > 0;
+    if (shared) {
+        if (tid == 0) { a.p.slot_expert[total_slots] = a.n_local; a.p.slot_off[total_slots] = total_pairs; a.p.slot_cnt[total_slots] = a.sh_n; }
+        for (int tt = tid; tt < a.sh_n; tt += nth) { a.p.pair_tok[total_pairs + tt] = a.sh_t0 + tt; a.p.pair_dst[total_pairs + tt] = n + a.sh_t0 + tt; }
     }
-    if (tid == 0) *a.p.n_slots = total_slots + (a.with_shared ? 1 : 0);
+    if (tid == 0) *a.p.n_slots = total_slots + (shared ? 1 : 0);
 }
 
 // p may be null-planned (p.n_slots == nullptr) when only the routing is wanted.
 void router_plan(cudaStream_t st, int *idx, float *w, float *score, const float *x, int ldx, const void *gate,
                  int gate_dt, const float *bias, int T, const MoeShape &s, const MoePlan &p, int with_shared,
-                 int *counter)
+                 int *counter, int shared_t0, int shared_n)
 {
     RouterArgs a{idx, w, score, x, ldx, gate, gate_dt, bias, s.NE, s.E, s.K, T, s.norm_topk, s.routed_scale,
-                 p, s.n_local0, s.n_local, with_shared, counter};
+                 p, s.n_local0, s.n_local, with_shared, counter, shared_t0, shared_n < 0 ? T : shared_n};
     G5B_LAUNCH(router_kernel, dim3((s.NE + RT_WARPS - 1) / RT_WARPS, T), RT_WARPS * 32, 0, st, a);
 }
 

@@ -214,6 +214,13 @@ int g5b_engine_decode_batch(g5b_engine *e, const int *ids, float *logits, int *a
  * ends in one kernel that stores this rank's contribution rows into every rank's region through
  * the peer mappings, waits (bounded; a wait that runs out makes the call return -1) for the other
  * ranks' rows and combines in top-k order. All ranks must make the same sequence of calls.
+ * Option "sequence_split" = 1 (ep_size > 1, before the ranks exchange anything) changes what is
+ * replicated: every rank then owns its OWN sequences (option "sequences" counts the rank's own) and
+ * runs attention, mHC, norms and the head for its own tokens only; a MoE layer gathers the ranks'
+ * tokens on every rank (peer stores: the dispatch), every rank routes them and multiplies them by
+ * the experts it owns, and the contribution rows travel to the rank the token lives on, which
+ * combines in top-k order (the combine). All ranks must call with the same number of tokens per
+ * call (lockstep decode steps, prompts of equal length). The KDA head split is off in this mode.
  * Option "ep_loopback" (g5b_engine_set_option) wires stand-in peers in local memory that never
  * answer: it exists to exercise the time-out report on one GPU.
  * The wait is limited in wall-clock time (option "ep_wait_ms", default 5000): the ranks are separate
@@ -287,6 +294,22 @@ int g5b_state_write(g5b_engine *e, int layer, int kind, size_t offset, const flo
                     size_t count);
 int g5b_state_read(g5b_engine *e, int layer, int kind, size_t offset, float *dst,
                    size_t count);
+
+/* The checkpoint's multi-token-prediction layer (layer n_layers; reference src/model/glm53f_mtp.h).
+ * g5b_engine_enable_mtp (before loading) makes the engine expect "layers.<n_layers>.*": an MLA + MoE
+ * layer of the model's shapes without mHC tensors, plus enorm.weight, hnorm.weight,
+ * shared_head.norm.weight and eh_proj.weight [hidden][2 hidden] (glm53f_bind.c:208-249), with its
+ * own latent cache, indexer state and routed experts; every forward call then keeps the mean of
+ * the residual streams of each of its positions (row t = position t of the call,
+ * glm53f_model.c:460-468). g5b_mtp_feed is glm53f_mtp_feed (glm53f_mtp.c:100-144): h holds T hidden
+ * states (NULL = the rows the last forward call kept), next_ids[t] the token that follows position
+ * t; the layer advances its own position count by T and *draft (may be NULL) receives the token
+ * predicted after the last one. x_out (may be NULL) receives the layer's output rows
+ * [T][hidden]. g5b_engine_reset forgets the fed positions. The reference only scores drafts
+ * against the tokens the model produces (glm53f_mtp_score); so do the tests here. */
+int g5b_engine_enable_mtp(g5b_engine *e);
+int g5b_mtp_feed(g5b_engine *e, const float *h, const int *next_ids, int T, int *draft, float *x_out);
+int g5b_mtp_hidden(g5b_engine *e, int first, int T, float *dst);
 
 /* RMSNorm of `rows` rows of n floats on DEVICE buffers of the current CUDA device, enqueued on
  * `stream` (a cudaStream_t, NULL for the default stream) without waiting: y = w * x / sqrt(mean(x^2)

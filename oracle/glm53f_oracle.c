@@ -44,10 +44,16 @@ typedef struct {
 struct orc_model {
     g5b_config c;
     int     cap, cached, latent, finalized;
-    OLayer *L;
+    OLayer *L;                          /* n_layers entries, one more (the MTP layer) with `mtp` */
     OMat    embed, lm_head;
     float  *norm;
+    /* the multi-token-prediction layer (checkpoint layer n_layers), orc_model_enable_mtp */
+    int     mtp, mtp_cached;
+    float  *enorm, *hnorm, *head_norm;
+    OMat    eh;
+    float  *mtp_h;                      /* [cap][hidden]: mean of the streams of every position fed */
 };
+static int n_slots(const orc_model *m) { return m->c.n_layers + (m->mtp ? 1 : 0); }
 
 static float bf16f(uint16_t h)
 {
@@ -764,6 +770,23 @@ orc_model *orc_model_create(const g5b_config *cfg, const uint8_t *is_mla,
     return m;
 }
 
+/* Adds checkpoint layer n_layers, the multi-token-prediction layer: an MLA + MoE layer of the
+ * model's shapes without mHC mixers, two input norms, the projection of [norm(embedding),
+ * norm(hidden)] and the norm before the shared lm_head (plan_mtp, src/model/glm53f_bind.c:208-249).
+ * Call before loading. */
+int orc_model_enable_mtp(orc_model *m)
+{
+    if (m->finalized || m->mtp) return -1;
+    const int n = m->c.n_layers;
+    m->L = (OLayer *)realloc(m->L, (size_t)(n + 1) * sizeof *m->L);
+    memset(&m->L[n], 0, sizeof m->L[n]);
+    m->L[n].is_mla = 1;
+    m->L[n].is_dense = 0;
+    m->L[n].experts = (OMat *)calloc((size_t)m->c.n_experts * 3, sizeof(OMat));
+    m->mtp = 1;
+    return 0;
+}
+
 int orc_model_load(orc_model *m, const char *name, const g5b_tensor *t)
 {
     const g5b_config *c = &m->c;
@@ -772,12 +795,18 @@ int orc_model_load(orc_model *m, const char *name, const g5b_tensor *t)
     if (!strcmp(name, "lm_head.weight"))      return keep_mat(&m->lm_head, t, c, c->vocab, E, name);
     if (!strcmp(name, "norm.weight"))         return keep_vec(&m->norm, t, (size_t)E, name);
     int l = -1, used = 0;
-    if (sscanf(name, "layers.%d.%n", &l, &used) != 1 || l < 0 || l >= c->n_layers) {
+    if (sscanf(name, "layers.%d.%n", &l, &used) != 1 || l < 0 || l >= n_slots(m)) {
         fprintf(stderr, "oracle: unknown tensor %s\n", name);
         return -1;
     }
     const char *r = name + used;
     OLayer *w = &m->L[l];
+    if (l == c->n_layers) {
+        if (!strcmp(r, "enorm.weight")) return keep_vec(&m->enorm, t, (size_t)E, name);
+        if (!strcmp(r, "hnorm.weight")) return keep_vec(&m->hnorm, t, (size_t)E, name);
+        if (!strcmp(r, "shared_head.norm.weight")) return keep_vec(&m->head_norm, t, (size_t)E, name);
+        if (!strcmp(r, "eh_proj.weight")) return keep_mat(&m->eh, t, c, E, 2 * E, name);
+    }
     const int H = c->kda_heads, D = c->kda_head_dim, P = H * D;
     const int MH = c->mla_heads, IH = c->index_heads, ID = c->index_dim;
     const int SI = c->moe_inter * c->n_shared;
@@ -854,7 +883,8 @@ static size_t kda_floats(const g5b_config *c)
 int orc_model_finalize(orc_model *m)
 {
     const g5b_config *c = &m->c;
-    for (int l = 0; l < c->n_layers; l++) {
+    if (m->mtp) m->mtp_h = (float *)calloc((size_t)m->cap * c->hidden, sizeof(float));
+    for (int l = 0; l < n_slots(m); l++) {
         OLayer *w = &m->L[l];
         if (w->is_mla) {
             const size_t per = m->latent ? (size_t)c->kv_lora
@@ -875,6 +905,7 @@ void orc_model_reset(orc_model *m)
     for (int l = 0; l < m->c.n_layers; l++)
         if (m->L[l].kda_state) memset(m->L[l].kda_state, 0, kda_floats(&m->c) * sizeof(float));
     m->cached = 0;
+    m->mtp_cached = 0;
 }
 
 int orc_model_cached(const orc_model *m) { return m->cached; }
@@ -902,13 +933,16 @@ int orc_model_forward(orc_model *m, const int *ids, int T, float *logits, int *a
     if (rc == 0) {
         float *xm = (float *)malloc(((size_t)2 * E + c->vocab) * sizeof(float));
         float *lg = xm + 2 * E;
-        for (int t = argmax_all ? 0 : T - 1; t < T; t++) {
+        /* with the MTP layer open every position's mean is computed and kept (glm53f_model.c:460-468) */
+        for (int t = (argmax_all || m->mtp_h) ? 0 : T - 1; t < T; t++) {
             const float *ht = h + (size_t)t * M * E;
             for (int d = 0; d < E; d++) {
                 double s = 0.0;
                 for (int i = 0; i < M; i++) s += (double)ht[(size_t)i * E + d];
                 xm[d] = (float)(s / M);
             }
+            if (m->mtp_h) memcpy(m->mtp_h + (size_t)t * E, xm, (size_t)E * sizeof(float));
+            if (!argmax_all && t < T - 1) continue;
             rmsnorm(xm + E, xm, m->norm, E, c->rms_eps);
             mv(lg, xm + E, &m->lm_head);
             if (argmax_all) {
@@ -925,12 +959,68 @@ int orc_model_forward(orc_model *m, const int *ids, int T, float *logits, int *a
     return rc;
 }
 
+/* glm53f_mtp_feed, src/model/glm53f_mtp.c:100-144. h: T hidden states (means of the streams,
+ * before the final norm; NULL = the rows the last forward call kept), next_ids[t]: the token that
+ * follows position t. x = eh_proj([RMSNorm(embed(next), enorm), RMSNorm(h, hnorm)]), then a plain
+ * pre-norm residual MLA + MoE layer on the MTP layer's own caches at its own position count, and for
+ * the last position the draft = first-max arg-max of lm_head(RMSNorm(x, shared_head.norm)).
+ * x_out (may be NULL) receives the T rows of x after the layer. */
+int orc_mtp_feed(orc_model *m, const float *h, const int *next_ids, int T, int *draft, float *x_out)
+{
+    const g5b_config *c = &m->c;
+    const int E = c->hidden;
+    if (!m->mtp || !m->finalized || T < 1 || m->mtp_cached + T > m->cap) return -1;
+    if (!m->enorm || !m->hnorm || !m->head_norm || !m->eh.w) return -1;
+    if (!h) h = m->mtp_h;
+    OLayer *w = &m->L[c->n_layers];
+    float *x = (float *)malloc((size_t)T * E * 4 * sizeof(float));
+    float *y = x + (size_t)T * E, *cat = y + (size_t)T * E;        /* cat: [T][2E] */
+    for (int i = 0; i < T; i++) {
+        if (next_ids[i] < 0 || next_ids[i] >= c->vocab) { free(x); return -1; }
+        float *ci = cat + (size_t)i * 2 * E;
+        for (int d = 0; d < E; d++)
+            ci[d] = m->embed.dt == G5B_DT_BF16
+                  ? bf16f(((const uint16_t *)m->embed.w)[(size_t)next_ids[i] * E + d])
+                  : ((const float *)m->embed.w)[(size_t)next_ids[i] * E + d];
+        rmsnorm(ci, ci, m->enorm, E, c->rms_eps);
+        rmsnorm(ci + E, h + (size_t)i * E, m->hnorm, E, c->rms_eps);
+        mv(x + (size_t)i * E, ci, &m->eh);
+    }
+    for (int i = 0; i < T; i++) rmsnorm(y + (size_t)i * E, x + (size_t)i * E, w->in_norm, E, c->rms_eps);
+    mla(cat, y, w, c, T, w->kvc, m->mtp_cached, m->cap, w->idx, w->ckv, NULL, NULL);
+    for (size_t i = 0; i < (size_t)T * E; i++) x[i] += cat[i];
+    for (int i = 0; i < T; i++) rmsnorm(y + (size_t)i * E, x + (size_t)i * E, w->post_norm, E, c->rms_eps);
+    const int rc = moe(cat, y, w, c, T, 1);
+    for (size_t i = 0; i < (size_t)T * E; i++) x[i] += cat[i];
+    m->mtp_cached += T;
+    if (rc == 0 && draft) {
+        float *lg = (float *)malloc((size_t)c->vocab * sizeof(float));
+        rmsnorm(y, x + (size_t)(T - 1) * E, m->head_norm, E, c->rms_eps);
+        mv(lg, y, &m->lm_head);
+        int b = 0;
+        for (int i = 1; i < c->vocab; i++) if (lg[i] > lg[b]) b = i;
+        *draft = b;
+        free(lg);
+    }
+    if (x_out) memcpy(x_out, x, (size_t)T * E * sizeof(float));
+    free(x);
+    return rc;
+}
+
+/* The hidden states (means of the streams) the last forward call kept: T rows from row `first`. */
+int orc_mtp_hidden(const orc_model *m, int first, int T, float *dst)
+{
+    if (!m->mtp_h || first < 0 || first + T > m->cap) return -1;
+    memcpy(dst, m->mtp_h + (size_t)first * m->c.hidden, (size_t)T * m->c.hidden * sizeof(float));
+    return 0;
+}
+
 static void drop_mat(OMat *m) { free(m->w); free(m->s); }
 
 void orc_model_free(orc_model *m)
 {
     if (!m) return;
-    for (int l = 0; l < m->c.n_layers; l++) {
+    for (int l = 0; l < n_slots(m); l++) {
         OLayer *w = &m->L[l];
         OMat *mats[] = { &w->hc[0].fn, &w->hc[1].fn, &w->kq, &w->kk, &w->kv, &w->f_a, &w->f_b, &w->kb,
                          &w->g_a, &w->g_b, &w->ko, &w->q_a, &w->q_b, &w->kv_a, &w->kv_b, &w->mo,
@@ -947,7 +1037,8 @@ void orc_model_free(orc_model *m)
             free(w->experts);
         }
     }
-    drop_mat(&m->embed); drop_mat(&m->lm_head);
+    drop_mat(&m->embed); drop_mat(&m->lm_head); drop_mat(&m->eh);
+    free(m->enorm); free(m->hnorm); free(m->head_norm); free(m->mtp_h);
     free(m->norm); free(m->L); free(m);
 }
 

@@ -37,6 +37,10 @@ int  orc_model_forward(orc_model *m, const int *ids, int T, float *logits, int *
 void orc_model_reset(orc_model *m);
 void orc_model_free(orc_model *m);
 int  orc_model_cached(const orc_model *m);
+/* The multi-token-prediction layer (src/model/glm53f_mtp.c): enable before loading "layers.<n_layers>.*". */
+int  orc_model_enable_mtp(orc_model *m);
+int  orc_mtp_feed(orc_model *m, const float *h, const int *next_ids, int T, int *draft, float *x_out);
+int  orc_mtp_hidden(const orc_model *m, int first, int T, float *dst);
 
 int orc_matvec_host(const g5b_tensor *w, int br, int bc, const float *x, int T, float *y);
 int orc_rmsnorm_host(float *y, const float *x, const float *w, int n, int rows, float eps);

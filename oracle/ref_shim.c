@@ -17,6 +17,11 @@
 
 #include "glm53f_b200.h"
 #include "glm53f_model.h"      /* reference: src/model/glm53f_model.h */
+/* The reference's MTP layer keeps its struct private to its .c file and can only be opened from a
+ * checkpoint on disk. To drive glm53f_mtp_feed from tensors in memory, the reference's source file
+ * is compiled as part of this translation unit, where it lies (the Makefile leaves it out of the
+ * list of separately compiled files), and the struct is filled below by ref_model_enable_mtp. */
+#include "glm53f_mtp.c"
 
 typedef struct {
     Glm53fExpertSrc src;       /* first member: &src is what Glm53fMoeW.src points at */
@@ -27,7 +32,7 @@ typedef struct {
 typedef struct {
     Glm53fModel m;
     RamExperts  ram;
-    int         from_dir, latent, finalized;
+    int         from_dir, latent, finalized, mtp;
     void      **owned;
     size_t      n_owned, cap_owned;
 } RefModel;
@@ -82,7 +87,7 @@ void *ref_model_create(const g5b_config *cfg, const uint8_t *is_mla, const uint8
     r->latent = kv_mode == 2 || (kv_mode == 0 && m->cap > glm53f_dense_attn_limit(&m->cfg));
     r->ram.src.get = ram_get;
     r->ram.n_experts = cfg->n_experts;
-    r->ram.q = (Glm53fExpertQ *)calloc((size_t)cfg->n_layers * cfg->n_experts, sizeof(Glm53fExpertQ));
+    r->ram.q = (Glm53fExpertQ *)calloc((size_t)(cfg->n_layers + 1) * cfg->n_experts, sizeof(Glm53fExpertQ));  /* + the MTP layer */
     for (int l = 0; l < cfg->n_layers; l++) {
         Glm53fLayerW *w = &m->lay[l].w;
         w->is_mla = is_mla[l]; w->is_dense = is_dense[l];
@@ -91,6 +96,24 @@ void *ref_model_create(const g5b_config *cfg, const uint8_t *is_mla, const uint8
     }
     glm53f_quiet = 1;
     return r;
+}
+
+/* Checkpoint layer n_layers as the reference's MTP layer: the struct glm53f_mtp_open would build
+ * (src/model/glm53f_mtp.c:29-84), with weights arriving through ref_model_load and the experts in
+ * RAM like the trunk's. Call before loading. */
+int ref_model_enable_mtp(void *h)
+{
+    RefModel *r = (RefModel *)h;
+    if (r->mtp || r->finalized) return -1;
+    Glm53fMtp *t = (Glm53fMtp *)calloc(1, sizeof *t);
+    t->b.w.w.is_mla = 1;
+    t->b.w.w.is_dense = 0;
+    t->b.w.w.moe.src = &r->ram.src;
+    t->b.w.w.moe.layer = r->m.cfg.n_layers;
+    t->b.w.w.moe.prefetch_n = 0;
+    r->m.mtp = t;
+    r->mtp = 1;
+    return 0;
 }
 
 static int put_mat(RefModel *r, Glm53fMat *dst, const g5b_tensor *t, int rows, int cols)
@@ -138,9 +161,16 @@ int ref_model_load(void *h, const char *name, const g5b_tensor *t)
     if (!strcmp(name, "lm_head.weight"))      return put_mat(r, &m->mb.lm_head, t, c->vocab, E);
     if (!strcmp(name, "norm.weight"))         return put_vec(r, &m->mb.norm, t, (size_t)E);
     int l = -1, used = 0;
-    if (sscanf(name, "layers.%d.%n", &l, &used) != 1 || l < 0 || l >= c->n_layers) return -1;
+    if (sscanf(name, "layers.%d.%n", &l, &used) != 1 || l < 0 || l >= c->n_layers + (r->mtp ? 1 : 0)) return -1;
     const char *p = name + used;
-    Glm53fLayerW *w = &m->lay[l].w;
+    Glm53fLayerW *w = l < c->n_layers ? &m->lay[l].w : &m->mtp->b.w.w;
+    if (l == c->n_layers) {
+        Glm53fMtpW *mw = &m->mtp->b.w;
+        if (!strcmp(p, "enorm.weight")) return put_vec(r, &mw->enorm, t, (size_t)E);
+        if (!strcmp(p, "hnorm.weight")) return put_vec(r, &mw->hnorm, t, (size_t)E);
+        if (!strcmp(p, "shared_head.norm.weight")) return put_vec(r, &mw->head_norm, t, (size_t)E);
+        if (!strcmp(p, "eh_proj.weight")) return put_mat(r, &mw->eh, t, E, 2 * E);
+    }
     const int H = c->kda_heads, D = c->kda_head_dim, P = H * D, MH = c->n_heads;
     const int IH = c->index_heads, ID = c->index_dim, SI = c->moe_inter * c->n_shared;
 #define MAT(nm, field, R, C) if (!strcmp(p, nm)) return put_mat(r, &w->field, t, R, C)
@@ -223,7 +253,40 @@ int ref_model_finalize(void *h)
         else           m->kv[l]  = (float *)calloc(n, sizeof(float));
         m->idx[l] = (float *)calloc(glm53f_dsa_state_floats(c, m->cap), sizeof(float));
     }
+    if (r->mtp) {                       /* the buffers of glm53f_mtp_open (glm53f_mtp.c:55-73) */
+        Glm53fMtp *t = m->mtp;
+        const size_t E = (size_t)c->hidden;
+        t->cap = m->cap; t->maxT = m->cap;
+        if (r->latent) t->ckv = (float *)calloc((size_t)m->cap * c->kv_lora, sizeof(float));
+        else           t->kv  = (float *)malloc((size_t)m->cap * glm53f_kv_floats_per_pos(c) * sizeof(float));
+        t->istate = (float *)calloc(glm53f_dsa_state_floats(c, m->cap), sizeof(float));
+        t->x = (float *)malloc((size_t)t->maxT * E * sizeof(float));
+        t->y = (float *)malloc((size_t)t->maxT * E * sizeof(float));
+        t->cat = (float *)malloc((size_t)t->maxT * 2 * E * sizeof(float));
+        t->lg = (float *)malloc((size_t)c->vocab * sizeof(float));
+        t->scratch = (float *)malloc(work_floats(c, t->maxT, m->cap) * sizeof(float));
+        m->mtp_h = (float *)calloc((size_t)m->cap * E, sizeof(float));
+    }
     r->finalized = 1;
+    return 0;
+}
+
+/* glm53f_mtp_feed; h == NULL feeds the hidden states the last forward call kept. x_out: the
+ * layer's output rows (the reference's own buffer). */
+int ref_mtp_feed(void *h, const float *hid, const int *next_ids, int T, int *draft, float *x_out)
+{
+    RefModel *r = (RefModel *)h;
+    if (!r->mtp || !r->finalized) return -1;
+    const int rc = glm53f_mtp_feed(&r->m, hid ? hid : r->m.mtp_h, next_ids, T, draft);
+    if (rc == 0 && x_out) memcpy(x_out, r->m.mtp->x, (size_t)T * r->m.cfg.hidden * sizeof(float));
+    return rc;
+}
+
+int ref_mtp_hidden(void *h, int first, int T, float *dst)
+{
+    RefModel *r = (RefModel *)h;
+    if (!r->m.mtp_h || first < 0 || first + T > r->m.cap) return -1;
+    memcpy(dst, r->m.mtp_h + (size_t)first * r->m.cfg.hidden, (size_t)T * r->m.cfg.hidden * sizeof(float));
     return 0;
 }
 
@@ -246,7 +309,11 @@ int ref_model_forward(void *h, const int *ids, int T, float *logits, int *argmax
     return glm53f_model_forward(&r->m, ids, T, logits, argmax_all);
 }
 
-void ref_model_reset(void *h) { glm53f_model_reset(&((RefModel *)h)->m); }
+void ref_model_reset(void *h)
+{
+    glm53f_model_reset(&((RefModel *)h)->m);
+    glm53f_mtp_reset(&((RefModel *)h)->m);
+}
 int  ref_model_cached(void *h) { return ((RefModel *)h)->m.cached; }
 int  ref_model_vocab(void *h) { return ((RefModel *)h)->m.cfg.vocab; }
 
@@ -262,6 +329,11 @@ void ref_model_free(void *h)
         if (m->ckv) free(m->ckv[l]);
     }
     free(m->kv); free(m->idx); free(m->ckv); free(m->state); free(m->lay);
+    if (m->mtp) {
+        Glm53fMtp *t = m->mtp;
+        free(t->kv); free(t->ckv); free(t->istate); free(t->x); free(t->y); free(t->cat); free(t->lg);
+        free(t->scratch); free(t); free(m->mtp_h);
+    }
     for (size_t i = 0; i < r->n_owned; i++) free(r->owned[i]);
     free(r->owned); free(r->ram.q); free(r);
 }

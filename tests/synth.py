@@ -214,6 +214,34 @@ def make_model(spec: Spec, seed: int = 0, recipe: str = "baseline", experts: boo
     return out
 
 
+def make_mtp_layer(spec: Spec, seed: int = 0, recipe: str = "spread") -> dict:
+    """The tensors of checkpoint layer n_layers, the multi-token-prediction layer: an MLA + MoE layer
+    of the model's shapes without mHC tensors, plus enorm, hnorm, shared_head.norm and eh_proj
+    [hidden][2 hidden] (the reference's plan_mtp, src/model/glm53f_bind.c:208-249). Drawn from a
+    generator of its own, so the trunk made by make_model with the same seed is unchanged."""
+    c = spec.cfg
+    L = c.n_layers
+    one = Spec(cfg=c, is_mla=np.array([1], np.uint8), is_dense=np.array([0], np.uint8), with_head=False)
+    cfg1 = c.copy()
+    cfg1.n_layers = 1
+    one.cfg = cfg1
+    layer = make_model(one, seed=seed + 7919, recipe=recipe)
+    out = {}
+    for name, v in layer.items():
+        rest = name[len("layers.0."):]
+        if rest.startswith("hc_"):
+            continue
+        out[f"layers.{L}.{rest}"] = v
+    rng = np.random.default_rng(seed + 104729)
+    E = c.hidden
+    amp = 0.02 if recipe == "baseline" else 0.3
+    for nm in ("enorm.weight", "hnorm.weight", "shared_head.norm.weight"):
+        out[f"layers.{L}.{nm}"] = (to_bf16_bits((1.0 + amp * rng.standard_normal(E)).astype(np.float32)).reshape(E, 1), DT_BF16, None)
+    std = 0.02 if recipe == "baseline" else 0.5 / np.sqrt(2 * E)
+    out[f"layers.{L}.eh_proj.weight"] = (to_bf16_bits((rng.standard_normal((E, 2 * E)) * std).astype(np.float32)), DT_BF16, None)
+    return out
+
+
 # ------------------------------------------------- full-size MoE layer (config 2) ----
 def expert_scales(cfg, layer: int, expert: int, seed: int):
     """FP32 block scales log-uniform in [2^-12, 2^-6] for the three matrices of one expert."""

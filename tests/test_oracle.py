@@ -159,6 +159,52 @@ def test_oracle_ops_bit_identical_to_reference_on_config1(binding):
     assert same(lo, lr)
 
 
+@pytest.mark.parametrize("kv_mode", [1, 2])
+def test_oracle_mtp_layer_bit_identical_to_reference(binding, kv_mode):
+    """The multi-token-prediction layer (checkpoint layer n_layers): the oracle's restatement of
+    glm53f_mtp_feed against the reference's own function, driven the way the reference's decode
+    loop drives it (src/cli/glm53f_run.c:496-508): after the prompt the hidden states of all but
+    the last position go in with the prompt's next tokens, then every step feeds one hidden state
+    and the token the model just produced and takes a draft. Expanded and latent cache forms."""
+    if not binding.have_ref():
+        pytest.skip("reference objects not built here")
+    spec = synth.tiny_spec()
+    tensors = synth.make_model(spec, seed=0, recipe="spread")
+    tensors.update(synth.make_mtp_layer(spec, seed=0, recipe="spread"))
+    cap = 40
+    models = []
+    for cls in (binding.OracleModel, binding.RefModel):
+        m = cls(spec.cfg, spec.is_mla, spec.is_dense, cap, kv_mode)
+        m.enable_mtp()
+        m.load_all(tensors); m.finalize()
+        models.append(m)
+    same = lambda a, b: np.array_equal(np.asarray(a).view(np.uint32), np.asarray(b).view(np.uint32))
+    rng = np.random.default_rng(5)
+    prompt = rng.integers(0, spec.cfg.vocab, 21).astype(np.int32)    # 21 + steps cross the indexer's dense limit of 19
+    drafts = [[], []]
+    nexts = [[], []]
+    for k, m in enumerate(models):
+        lg, _ = m.forward(prompt)
+        nxt = int(np.argmax(lg))
+        hid = m.mtp_hidden(0, prompt.size)
+        _, x0 = m.mtp_feed(prompt[1:], hid[:-1], want_draft=False)
+        d, x1 = m.mtp_feed([nxt], hid[-1:])
+        keep = [x0, x1]
+        drafts[k].append(d); nexts[k].append(nxt)
+        for _ in range(6):
+            lg, _ = m.forward([nxt])
+            nxt = int(np.argmax(lg))
+            d, x = m.mtp_feed([nxt])                                  # h = the state the forward call kept
+            keep.append(x)
+            drafts[k].append(d); nexts[k].append(nxt)
+        m.keep = keep
+    assert drafts[0] == drafts[1] and nexts[0] == nexts[1]
+    for a, b in zip(models[0].keep, models[1].keep):
+        assert same(a, b)
+    for m in models:
+        m.close()
+
+
 def test_synthetic_codes_are_finite_and_spread(binding):
     c = binding.synth_codes(7, 3, 11, 1, 1 << 16)
     assert not np.any((c & 0x7f) == 0x7f)
