@@ -700,6 +700,8 @@ def main():
                     help="time one matrix of the full-size model (e.g. layers.0.mlp.gate_proj.weight, lm_head.weight) "
                          "times --positions positions and print it (a small case for ncu)")
     ap.add_argument("--positions", type=int, default=64)
+    ap.add_argument("--mma-rate", action="store_true",
+                    help="print the cycles per tcgen05.mma instruction (M = 128) for N = 16..256, both kinds, and exit")
     ap.add_argument("--no-full-model", action="store_true", help="skip the full-size model's greedy decode")
     ap.add_argument("--no-batch-decode", action="store_true", help="skip the 64-sequence decode of the full-size model")
     ap.add_argument("--only-full-model", action="store_true", help="run only the full-size model's greedy decode and print it")
@@ -724,6 +726,22 @@ def main():
     if not torch.cuda.is_available() or L.g5b_device_count() < 1:
         raise SystemExit("bench.py needs a CUDA device: the engine has no CPU path")
     torch.cuda.set_device(local)
+
+    if args.mma_rate:
+        # cycles per tcgen05.mma instruction, one issuing thread per SM, operands that never change
+        import ctypes as C
+        L.g5b_debug_mma_rate.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_double)]
+        sms = torch.cuda.get_device_properties(local).multi_processor_count
+        rows = []
+        for fp8 in (0, 1):
+            for n in (16, 32, 64, 128, 192, 256):
+                cyc = (C.c_double * 2)()
+                if L.g5b_debug_mma_rate(n, fp8, 1, sms, 2000, cyc) != 0:
+                    raise SystemExit("the instruction-rate probe failed")
+                rows.append({"kind": "f8f6f4, K = 32" if fp8 else "f16, K = 16", "M": 128, "N": n,
+                             "cycles_per_instruction_issued": cyc[0], "cycles_per_instruction_complete": cyc[1]})
+        print(json.dumps({"tcgen05_mma_rate": rows, "ctas": sms, "instructions_per_cta": 8000}))
+        return
 
     # the CPU baseline first: one rank, before any other rank's process competes for the host cores
     cpu = None

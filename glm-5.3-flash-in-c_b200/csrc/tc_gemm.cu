@@ -721,4 +721,90 @@ int tc_gemm_run(TcGemm *g, cudaStream_t st, const GemvSeg &s, int T)
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
+// ------------------------------------------------------------ instruction-rate probe ----
+// What one tcgen05.mma costs when nothing else uses the SM: one thread issues `reps` groups of four
+// instructions (the four K steps of a 128-byte swizzle row) on shared-memory tiles that never
+// change, M = 128, N as given, rotating over `accs` accumulators; then one commit and a bounded
+// wait. out[0] = cycles until the last instruction was issued, out[1] = until all had completed, of
+// CTA 0. The design of tc_gemm_kernel rests on these figures (an instruction costs what its 128-row
+// A operand costs, whatever N is).
+__device__ __forceinline__ void tc_mma_f8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+
+__global__ void __launch_bounds__(64) tc_mma_rate_kernel(int N, int reps, int accs, int fp8, long long *out, int *err)
+{
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint32_t s_tmem;
+    __shared__ __align__(8) uint64_t bar;
+    uint8_t *base = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t *A = base, *B = base + TC_ATOM_BYTES;                  // A: 128 rows x 128 B; B: up to 256 rows x 128 B
+    for (int i = threadIdx.x; i < (TC_ATOM_BYTES + 256 * 128) / 4; i += blockDim.x)
+        reinterpret_cast<uint32_t *>(base)[i] = fp8 ? 0x38383838u : 0x3c003c00u;      // ones
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    fence_proxy_async();
+    __syncthreads();
+    if (threadIdx.x < 32) tmem_alloc(&s_tmem, 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tm = s_tmem;
+    if (threadIdx.x == 32) {
+        const uint32_t idesc = tc_idesc(0, N);                     // format code 0: F16, or E4M3 for the 8-bit kind
+        const uint64_t ad = tc_smem_desc(A), bd = tc_smem_desc(B);
+        const long long t0 = clock64();
+        for (int r = 0; r < reps; r++) {
+            const uint32_t d = tm + (uint32_t)((r % accs) * N);
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                if (fp8) tc_mma_f8(d, ad + 2 * k, bd + 2 * k, idesc, (r >= accs || k) ? 1u : 0u);
+                else     tc_mma_f16(d, ad + 2 * k, bd + 2 * k, idesc, (r >= accs || k) ? 1u : 0u);
+            }
+        }
+        const long long t1 = clock64();
+        tc_commit(&bar);
+        const bool ok = mbar_wait(&bar, 0, err, 61);               // bounded; a wait that runs out records code 61
+        const long long t2 = clock64();
+        if (blockIdx.x == 0 && ok) { out[0] = t1 - t0; out[1] = t2 - t0; }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x < 32) tmem_dealloc(tm, 512);
+}
+
 }  // namespace g5b
+
+// Cycles per tcgen05.mma (M = 128; K = 16 for kind::f16, 32 for kind::f8f6f4) with `ctas` CTAs
+// running: cycles[0] until issued, cycles[1] until complete. Measurement aid, no counterpart in
+// the reference.
+extern "C" int g5b_debug_mma_rate(int n, int fp8, int accs, int ctas, int reps, double *cycles)
+{
+    using namespace g5b;
+    if (n < 16 || n > 256 || (n & 15) || accs < 1 || accs * n > 512 || ctas < 1 || reps < 1) return -1;
+    long long *out = nullptr;
+    int *err = nullptr;
+    if (cudaMalloc((void **)&out, 16) != cudaSuccess || cudaMalloc((void **)&err, 4) != cudaSuccess) { cudaFree(out); return -1; }
+    cudaMemset(out, 0, 16); cudaMemset(err, 0, 4);
+    const size_t smem = TC_ATOM_BYTES + 256 * 128 + 1024;
+    static SmemGrant grant;
+    int rc = -1;
+    if (dev_opt_in_smem((const void *)tc_mma_rate_kernel, smem, grant)) {
+        tc_mma_rate_kernel<<<ctas, 64, smem>>>(n, reps, accs, fp8, out, err);
+        long long h[2] = {0, 0};
+        int e = 0;
+        if (cudaDeviceSynchronize() == cudaSuccess && cudaMemcpy(h, out, 16, cudaMemcpyDeviceToHost) == cudaSuccess &&
+            cudaMemcpy(&e, err, 4, cudaMemcpyDeviceToHost) == cudaSuccess && e == 0) {
+            cycles[0] = (double)h[0] / (4.0 * reps);
+            cycles[1] = (double)h[1] / (4.0 * reps);
+            rc = 0;
+        }
+    }
+    cudaFree(out); cudaFree(err);
+    return rc;
+}

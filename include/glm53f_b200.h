@@ -311,6 +311,12 @@ int g5b_engine_enable_mtp(g5b_engine *e);
 int g5b_mtp_feed(g5b_engine *e, const float *h, const int *next_ids, int T, int *draft, float *x_out);
 int g5b_mtp_hidden(g5b_engine *e, int first, int T, float *dst);
 
+/* Measurement aid (no counterpart in the reference): SM cycles per tcgen05.mma instruction, M = 128,
+ * N = n (a multiple of 16 up to 256), kind::f16 (K = 16) or, with fp8 != 0, kind::f8f6f4 (K = 32),
+ * issued back to back by one thread of each of `ctas` CTAs on shared-memory tiles that never
+ * change, rotating over `accs` accumulators. cycles[0]: until issued, cycles[1]: until complete. */
+int g5b_debug_mma_rate(int n, int fp8, int accs, int ctas, int reps, double *cycles);
+
 /* RMSNorm of `rows` rows of n floats on DEVICE buffers of the current CUDA device, enqueued on
  * `stream` (a cudaStream_t, NULL for the default stream) without waiting: y = w * x / sqrt(mean(x^2)
  * + eps), w may be NULL. This entry point has no counterpart in the reference. It exists for
