@@ -289,6 +289,7 @@ extern "C" g5b_engine *g5b_engine_create(const g5b_config *cfg, const uint8_t *i
     }
     for (int i = 0; i <= PROF_SLOTS; i++) cudaEventCreate(&e->prof_ev[i]);
     memset(e->prof_ms, 0, sizeof e->prof_ms);
+    e->L.reserve((size_t)c.n_layers + 1);           // the name table points into L: enabling the MTP layer must not move it
     e->L.resize(c.n_layers);
     e->names.resize(c.n_layers);
     for (int l = 0; l < c.n_layers; l++) {
@@ -308,6 +309,7 @@ extern "C" int g5b_engine_enable_mtp(g5b_engine *e)
     if (e->mtp) return 0;
     if (e->c.n_layers + 1 > G5B_MAX_LAYERS) return fail("no room for the MTP layer");
     const int l = e->c.n_layers;
+    if (e->L.capacity() < (size_t)l + 1) return fail("no room for the MTP layer");
     e->L.resize((size_t)l + 1);
     e->names.resize((size_t)l + 1);
     e->L[l].is_mla = true;
@@ -970,6 +972,14 @@ static void trunk_allreduce(g5b_engine *e, float *out, int ldo, int n)
     ts_allreduce(e->st, r);
 }
 
+static bool kda_heads_split(const g5b_engine *e, const Layer &w)
+{
+    const g5b_config &c = e->c;
+    return e->tensor_split && !e->seq_split && e->ep_size > 1 && e->ep_connected && c.kda_heads % e->ep_size == 0 && (c.hidden % 4) == 0 &&
+           w.kq.dt != G5B_DT_FP8 && w.kk.dt != G5B_DT_FP8 && w.kv.dt != G5B_DT_FP8 && w.ko.dt != G5B_DT_FP8 &&
+           w.f_b.dt != G5B_DT_FP8 && w.g_b.dt != G5B_DT_FP8 && w.kb.dt != G5B_DT_FP8;
+}
+
 // batch: the n rows are one new position of n different sequences (sequences 0..n-1), otherwise n
 // consecutive positions of the current sequence.
 // Expert-parallel engines split the layer by heads as well (option "tensor_split", on by default):
@@ -983,9 +993,7 @@ static int run_kda(g5b_engine *e, Layer &w, const float *x, int n, float *out, b
     const int E = c.hidden, H = c.kda_heads, D = c.kda_head_dim, P = H * D;
     if (!w.kq.loaded() || !w.ko.loaded() || !w.g_b.loaded() || !w.f_b.loaded() || !w.kda_state || !w.dt_bias)
         return fail("this layer's KDA weights were not loaded");
-    const bool ts = e->tensor_split && !e->seq_split && e->ep_size > 1 && e->ep_connected && H % e->ep_size == 0 && (E % 4) == 0 &&
-                    w.kq.dt != G5B_DT_FP8 && w.kk.dt != G5B_DT_FP8 && w.kv.dt != G5B_DT_FP8 && w.ko.dt != G5B_DT_FP8 &&
-                    w.f_b.dt != G5B_DT_FP8 && w.g_b.dt != G5B_DT_FP8 && w.kb.dt != G5B_DT_FP8;
+    const bool ts = kda_heads_split(e, w);
     const int Hl = ts ? H / e->ep_size : H, h0 = ts ? e->ep_rank * Hl : 0, Pl = Hl * D, p0 = h0 * D;
     float *lrf = e->klr, *lrg = e->klr + (size_t)CHUNK * D;
     GemvSeg a[6] = {make_seg(row_slice(w.kq, p0, Pl), x, E, e->kq + p0, P), make_seg(row_slice(w.kk, p0, Pl), x, E, e->kk + p0, P),

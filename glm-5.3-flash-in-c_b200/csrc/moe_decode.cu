@@ -630,11 +630,6 @@ int moe_decode(cudaStream_t st, float *out, const float *x, const void *gate, in
                  ep ? ep->rows_off : 0, ep ? ep->launch : 0ull, ep ? ep->wait_ns : 0ull};
     void *params[] = {&a};
     cudaError_t rc;
-    static const bool plain = getenv("G5B_EXPERIMENT_PLAIN_LAUNCH") != nullptr;
-    if (plain) {
-        moe_decode_kernel<<<dim3(sms), dim3(MM_THREADS), decode_smem_bytes(s.I), st>>>(a);
-        rc = cudaGetLastError();
-    } else
     rc = cudaLaunchCooperativeKernel((const void *)moe_decode_kernel, dim3(sms), dim3(MM_THREADS), params,
                                      decode_smem_bytes(s.I), st);
     if (rc != cudaSuccess) { cudaGetLastError(); return -1; }
