@@ -523,7 +523,8 @@ def run_full_model(pkg, torch, ranks, local: int, rank: int, world: int, peak: f
         return {"error": err or "another rank failed while decoding"}
     ms = 1e3 * decode_s / new_tokens
     res = {"layers": n_layers, "of_layers": 45, "n_gpus": world, "new_tokens": new_tokens, "prompt_tokens": 18,
-           "trunk": "replicated on every rank", "experts_per_rank": c.n_experts // world,
+           "trunk": ("one GPU" if world == 1 else "KDA and MLA layers split by heads over the ranks (partial output rows summed in rank order), "
+                     "head split by vocabulary rows for the arg-max, mHC sites and norms replicated"), "experts_per_rank": c.n_experts // world,
            "resident_bytes_per_rank": resident, "build_s": build_s, "prefill_ms": 1e3 * prefill_s,
            "ms_per_token": ms, "tokens_per_s": 1e3 / ms,
            "algorithmic_bytes_per_token": token_all, "bytes_read_per_token_per_rank": token_rank,
@@ -603,7 +604,7 @@ def run_batch_decode(pkg, torch, ranks, local: int, rank: int, world: int, layer
         if not ranks.all_ok(not err):
             if eng is not None:
                 eng.close()
-            return {"error": err or "another rank could not build the model"}, None
+            return {"error": err or "another rank could not build the model"}, None, None
         handles = ranks.gather(eng.ep_export() if world > 1 else b"")
         try:
             if world > 1:
@@ -612,14 +613,15 @@ def run_batch_decode(pkg, torch, ranks, local: int, rank: int, world: int, layer
             err = repr(exc)[:300]
         if not ranks.all_ok(not err):
             eng.close()
-            return {"error": err or "another rank could not connect"}, None
+            return {"error": err or "another rank could not connect"}, None, None
         decode_s = prefill_s = 0.0
-        toks = None
+        toks = early = None
         try:
             eng.synth_session(SEED, context)
             ids = all_ids[rank * own:(rank + 1) * own] if split else all_ids
             for _ in range(3):                                         # warm-up steps (they advance the sequences too)
                 _, ids = eng.decode_batch(ids, want_logits=False)
+            early = ids.tolist()
             ranks.barrier()
             t0 = time.perf_counter()
             for _ in range(steps):
@@ -644,32 +646,35 @@ def run_batch_decode(pkg, torch, ranks, local: int, rank: int, world: int, layer
         decode_s = ranks.reduce(decode_s, "max")
         prefill_s = ranks.reduce(prefill_s, "max")
         all_toks = ranks.gather(toks)
+        all_early = ranks.gather(early)
         eng.close()
         if not ok:
-            return {"error": err or "another rank failed"}, None
+            return {"error": err or "another rank failed"}, None, None
         res = {"sequences_per_rank": own, "timed_steps": steps, "ms_per_step": 1e3 * decode_s / steps,
                "tokens_per_s": sequences * steps / decode_s, "tokens_per_s_per_sequence": steps / decode_s}
         if with_prefill:
             res["prefill"] = {"tokens": prefill_tokens, "ms": 1e3 * prefill_s, "tokens_per_s": prefill_tokens / prefill_s, "chunk": 64}
-        return res, all_toks
+        return res, all_toks, all_early
 
     out = {"layers": n_layers, "of_layers": 45, "n_gpus": world, "sequences": sequences, "context": context,
            "state": "synthetic session state at the stated context (filled on the device), no prompts run"}
-    rep, rep_toks = arm(False, True)
+    rep, rep_toks, rep_early = arm(False, True)
     if "error" in rep:
         return rep
     out.update(rep)
     out["attention"] = "every sequence on every rank (no sequence parallelism); routed experts split over the ranks"
     out["tokens_equal_on_all_ranks"] = all(t == rep_toks[0] for t in rep_toks)
     if world > 1 and sequences % world == 0:
-        sp, sp_toks = arm(True, False)
+        sp, sp_toks, sp_early = arm(True, False)
         if "error" not in sp:
             sp["attention"] = ("sequences split over the ranks: attention and every per-token kernel for sequences / N per rank; MoE "
                                "layers gather the ranks' tokens over peer stores (dispatch) and send contribution rows to the token's rank (combine)")
             flat = [t for ts in sp_toks for t in ts]
             # (the unsplit arm sums the KDA output projection over the ranks, this arm does not: a last-bit
             # difference can flip an arg-max of a random-init model's near-uniform logits after many steps)
-            sp["sequences_with_the_unsplit_arm_s_last_token"] = int(sum(a == b for a, b in zip(flat, rep_toks[0])))
+            sp["sequences_with_the_unsplit_arm_s_token_after_3_steps"] = int(sum(
+                a == b for a, b in zip([t for ts in sp_early for t in ts], rep_early[0])))
+            sp["sequences_with_the_unsplit_arm_s_token_after_%d_steps" % new_tokens] = int(sum(a == b for a, b in zip(flat, rep_toks[0])))
         out["sequence_split"] = sp
     return out
 

@@ -40,6 +40,7 @@ void set_last_error(const char *msg) { snprintf(g_err, sizeof g_err, "%s", msg);
     } while (0)
 
 constexpr size_t EP_FLAG_BYTES = 1024;   // exchange region: the ranks' step words, then the row buffers
+constexpr int EP_HEAD_WORD0 = 64;        // words [64, 64 + 5 x 8): the vocabulary-split head's (value, index) slots of two parities and its arrival counters (up to 8 ranks)
 constexpr int MLA_PART_TOKENS = 4;     // tokens whose attention partial sums are held at once
 constexpr int CHUNK = 64;       // positions one pass of a layer works on (the reference's MoE chunk, glm53f_ops.c:988)
 constexpr int PROF_SLOTS = 8;
@@ -94,6 +95,7 @@ struct g5b_engine {
     std::vector<void *> ep_standins;             // local stand-ins for peers (option ep_loopback)
     unsigned long long ep_step = 0;              // exchanges so far (both kernels): picks the row buffer
     unsigned long long ep_decode_launches = 0;
+    unsigned long long head_launches = 0;        // arg-max exchanges of the vocabulary-split head so far
     unsigned long long ts_launches = 0;          // all-reduces of column-split trunk products so far
     size_t ts_area_bytes = 0;                    // one parity's [ep_size][CHUNK][hidden] floats
     float *ts_part = nullptr;                    // this rank's partial rows [CHUNK][hidden]
@@ -1035,6 +1037,28 @@ static MlaShape mla_shape(const g5b_engine *e)
     return s;
 }
 
+// In a connected expert-parallel group (option "tensor_split") the MLA layer is split by heads too:
+// every rank appends the same latent and indexer rows (those caches stay replicated, the selection
+// is identical everywhere), but multiplies only its own heads' rows of q_b, absorbs, attends and
+// projects values for those heads (the kernels see a layer of H / N heads: compact buffers, kv_b
+// row-sliced to the heads' W_k | W_v rows), and multiplies its heads' columns of o_proj; the partial
+// output rows are summed in rank order like the KDA layer's. FP8 slices must start on scale-block
+// boundaries; the tensor-core attention core takes heads in groups of 16.
+static bool mla_heads_split(const g5b_engine *e, const Layer &w, const MlaShape &s)
+{
+    if (!e->tensor_split || e->seq_split || e->ep_size < 2 || !e->ep_connected) return false;
+    const int N = e->ep_size;
+    if (s.H % N || (s.E % 4)) return false;
+    const int Hl = s.H / N;
+    if (w.kv_b.dt == G5B_DT_FP8) return false;
+    if (w.q_b.dt == G5B_DT_FP8 && (Hl * s.qn) % w.q_b.br) return false;
+    if (w.mo.dt == G5B_DT_FP8 && (Hl * s.vh) % w.mo.bc) return false;
+    if (w.mo.dt != G5B_DT_FP8 && (Hl * s.vh) % 8) return false;
+    MlaShape sl = s; sl.H = Hl;
+    if (e->mla_tensor && mla_flash_takes(s) && !mla_flash_takes(sl)) return false;    // keep the tensor-core core
+    return true;
+}
+
 static int run_mla(g5b_engine *e, Layer &w, const float *x, int n, int cached, float *out, bool batch = false)
 {
     const g5b_config &c = e->c;
@@ -1047,6 +1071,12 @@ static int run_mla(g5b_engine *e, Layer &w, const float *x, int n, int cached, f
     if (!w.q_a.loaded() || !w.kv_b.loaded() || !w.mo.loaded() || !w.wq_b.loaded() || !w.ape || !w.latent)
         return fail("this layer's MLA weights were not loaded");
     if (cached + (batch ? 1 : n) > e->cap) return fail("MLA cache position %d beyond capacity %d", cached + (batch ? 1 : n) - 1, e->cap);
+    const bool ms = mla_heads_split(e, w, s);
+    const int Hl = ms ? s.H / e->ep_size : s.H, h0 = ms ? e->ep_rank * Hl : 0;
+    MlaShape sl = s;                               // what the per-head kernels see
+    sl.H = Hl;
+    const DMat qb = ms ? row_slice(w.q_b, h0 * s.qn, Hl * s.qn) : w.q_b;
+    const DMat kvb = ms ? row_slice(w.kv_b, h0 * (s.qn + s.vh), Hl * (s.qn + s.vh)) : w.kv_b;
     GemvSeg a[5] = {make_seg(w.q_a, x, E, e->mq_raw, c.q_lora), make_seg(w.kv_a, x, E, e->mct, c.kv_lora),
                     make_seg(w.wk, x, E, e->mwk, c.index_dim), make_seg(w.igate, x, E, e->mgate, c.index_dim),
                     make_seg(w.wproj, x, E, e->mwp, c.index_heads)};
@@ -1054,7 +1084,7 @@ static int run_mla(g5b_engine *e, Layer &w, const float *x, int n, int cached, f
     mla_store(e->st, lat, ist, e->mct, w.kv_a_norm, e->mwk, e->mgate, w.k_norm_w, w.k_norm_b,
               w.ape, e->mq_raw, e->minvq, n, cached, s);
     // q = q_b(RMSNorm(q_a x)) and the indexer query, the norm applied on the way into the product
-    GemvSeg b[2] = {make_seg(w.q_b, e->mq_raw, c.q_lora, e->mq, c.mla_heads * c.qk_nope, e->minvq, w.q_a_norm),
+    GemvSeg b[2] = {make_seg(qb, e->mq_raw, c.q_lora, e->mq, Hl * c.qk_nope, e->minvq, w.q_a_norm),
                     make_seg(w.wq_b, e->mq_raw, c.q_lora, e->mqidx, c.index_heads * c.index_dim, e->minvq, w.q_a_norm)};
     if (proj_batch(e, b, 2, n, true)) return -1;
     // The indexer (pool scores, top-k, expansion: two latency-bound kernels) and the absorption of
@@ -1063,20 +1093,24 @@ static int run_mla(g5b_engine *e, Layer &w, const float *x, int n, int cached, f
     bool forked = false, join = false;
     if (e->side && e->side_ev && e->side_done && cudaEventRecord(e->side_ev, e->st) == cudaSuccess &&
         cudaStreamWaitEvent(e->side, e->side_ev, 0) == cudaSuccess) {
-        mla_absorb(e->side, e->mqa, e->mq, w.kv_b, n, s);
+        mla_absorb(e->side, e->mqa, e->mq, kvb, n, sl);
         forked = true;
         join = cudaEventRecord(e->side_done, e->side) == cudaSuccess;
         if (!join) cudaStreamSynchronize(e->side);
     }
     dsa_select(e->st, e->msel, e->mnsel, ist, e->mqidx, e->mwp, e->mscore, n, cached, s);
-    if (!forked) mla_absorb(e->st, e->mqa, e->mq, w.kv_b, n, s);
+    if (!forked) mla_absorb(e->st, e->mqa, e->mq, kvb, n, sl);
     else if (join && cudaStreamWaitEvent(e->st, e->side_done, 0) != cudaSuccess) cudaStreamSynchronize(e->side);
-    if (e->mla_tensor && mla_flash_takes(s))
-        mla_attend_flash(e->st, e->mcb, e->mqa, lat, e->msel, e->mnsel, e->mpart, e->mpart_bytes, e->mdsc, n, cached, s);
+    if (e->mla_tensor && mla_flash_takes(sl))
+        mla_attend_flash(e->st, e->mcb, e->mqa, lat, e->msel, e->mnsel, e->mpart, e->mpart_bytes, e->mdsc, n, cached, sl);
     else
-        mla_attend(e->st, e->mcb, e->mqa, lat, e->msel, e->mnsel, e->mdsc, e->mpart, e->mstats, e->mcount, MLA_PART_TOKENS, n, cached, s);
-    mla_vout(e->st, e->macc, e->mcb, w.kv_b, n, s);
-    {
+        mla_attend(e->st, e->mcb, e->mqa, lat, e->msel, e->mnsel, e->mdsc, e->mpart, e->mstats, e->mcount, MLA_PART_TOKENS, n, cached, sl);
+    mla_vout(e->st, e->macc, e->mcb, kvb, n, sl);
+    if (ms) {
+        GemvSeg o = make_seg(col_slice(w.mo, h0 * s.vh, Hl * s.vh), e->macc, Hl * c.v_head, e->ts_part, E);
+        if (proj_batch(e, &o, 1, n, true)) return -1;
+        trunk_allreduce(e, out, E, n);
+    } else {
         GemvSeg o = make_seg(w.mo, e->macc, c.mla_heads * c.v_head, out, E);
         if (proj_batch(e, &o, 1, n, true)) return -1;
     }
@@ -1179,8 +1213,12 @@ static int ensure_ids(g5b_engine *e, size_t n)
 // e->am_out[t].
 // batch: the T ids are one new token for each of sequences 0..T-1 (T <= CHUNK), all at position
 // e->cached; logits_host then receives all T rows.
+// need_logits = false (greedy decode of one token): only the arg-max is wanted, so a connected
+// expert-parallel group splits the head by vocabulary rows - rank r multiplies rows [r V / N,
+// (r + 1) V / N), takes its own arg-max, and the ranks exchange (value, index) pairs and pick the
+// first maximum in index order, which is the arg-max of the whole row.
 static int forward_device(g5b_engine *e, const int *ids_dev, int T, bool all_positions, float *logits_host,
-                          int *argmax_host, bool batch = false)
+                          int *argmax_host, bool batch = false, bool need_logits = true)
 {
     const g5b_config &c = e->c;
     const int M = c.hc_mult, E = c.hidden;
@@ -1203,6 +1241,18 @@ static int forward_device(g5b_engine *e, const int *ids_dev, int T, bool all_pos
         const int n = T - t0 < CHUNK ? T - t0 : CHUNK;
         head_mean(e->st, e->xm, e->h + (size_t)t0 * M * E, n, M, E);
         rms_factor(e->st, e->xm, E, E, n, c.rms_eps, e->inv_head);
+        if (!need_logits && !logits_host && n == 1 && T == 1 && !batch && e->tensor_split && !e->seq_split && e->ep_size > 1 &&
+            e->ep_connected && e->ep_size <= 8 && c.vocab >= 8 * e->ep_size) {
+            const int per = (c.vocab + e->ep_size - 1) / e->ep_size, r0 = e->ep_rank * per;
+            const int rows = c.vocab - r0 < per ? c.vocab - r0 : per;
+            if (proj(e, row_slice(e->lm_head, r0, rows), e->xm, E, e->logits + r0, c.vocab, 1, e->inv_head, e->norm)) return -1;
+            argmax_rows(e->st, e->am_out + t0, e->logits + r0, rows, 1, e->am_v, e->am_i);
+            ++e->head_launches;
+            HeadPick hp{e->logits + r0, e->am_out + t0, r0, e->ep_peers_dev, e->ep_rank, e->ep_size, EP_HEAD_WORD0,
+                        e->head_launches, (unsigned long long)e->ep_wait_ms * 1000000ull, e->err_dev};
+            head_pick_exchange(e->st, hp);
+            continue;
+        }
         if (proj(e, e->lm_head, e->xm, E, e->logits, c.vocab, n, e->inv_head, e->norm)) return -1;
         argmax_rows(e->st, e->am_out + t0, e->logits, c.vocab, n, e->am_v, e->am_i);
         if (logits_host && batch)
@@ -1256,7 +1306,7 @@ extern "C" int g5b_engine_decode_greedy(g5b_engine *e, int first, int n, int *ou
     e->dirty = true;
     for (int i = 0; i < n; i++) {
         e->cached = start + i;
-        const int rc = forward_device(e, e->ids_dev + i, 1, false, nullptr, nullptr);
+        const int rc = forward_device(e, e->ids_dev + i, 1, false, nullptr, nullptr, false, false);
         if (rc) { e->cached = start; return -1; }
         CU(cudaMemcpyAsync(e->ids_dev + i + 1, e->am_out, 4, cudaMemcpyDeviceToDevice, e->st));
     }
@@ -2104,7 +2154,9 @@ static int ep_publish_peers(g5b_engine *e, const std::vector<void *> &peers)
     e->ep_step = 0;
     e->ep_decode_launches = 0;
     e->ts_launches = 0;
+    e->head_launches = 0;
     e->ts_launches = 0;
+    e->head_launches = 0;
     return 0;
 }
 
@@ -2164,6 +2216,7 @@ extern "C" int g5b_engine_ep_resync(g5b_engine *e)
     e->ep_step = 0;
     e->ep_decode_launches = 0;
     e->ts_launches = 0;
+    e->head_launches = 0;
     return 0;
 }
 

@@ -185,6 +185,46 @@ void seq_exchange(cudaStream_t st, const SeqExchange &a, int ctas)
     G5B_LAUNCH(seq_exchange_kernel, dim3(ctas), 256, 0, st, a);
 }
 
+// (value, index) of every rank's best vocabulary row, exchanged and reduced to the first maximum in
+// index order (HeadPick, kernels.h). One warp; lane r serves rank r.
+__global__ void __launch_bounds__(32) head_pick_kernel(const HeadPick a)
+{
+    const int lane = threadIdx.x;
+    const int parity = (int)(a.launch & 1ull);
+    const int li = a.local_idx[0];
+    const float v = a.logits[li];
+    const unsigned long long word_v = (unsigned long long)__float_as_uint(v), word_i = (unsigned long long)(a.row0 + li);
+    if (lane < a.size) {
+        unsigned long long *base = reinterpret_cast<unsigned long long *>(a.peers[lane]) + a.word0;
+        unsigned long long *slot = base + ((size_t)parity * 8 + a.rank) * 2;
+        slot[0] = word_v; slot[1] = word_i;
+        __threadfence_system();
+        red_release_sys_add(base + 32 + a.rank, 1ull);
+    }
+    bool seen = true;
+    const unsigned long long *mine = reinterpret_cast<const unsigned long long *>(a.peers[a.rank]) + a.word0;
+    if (lane < a.size) {
+        seen = wait_word_sys(mine + 32 + lane, a.launch, a.wait_ns);
+        if (!seen) atomicExch(a.err, 50 + lane);
+    }
+    if (!__all_sync(0xffffffffu, seen)) return;
+    if (lane == 0) {
+        float best = 0.f; int bi = -1;
+        for (int r = 0; r < a.size; r++) {                      // rank order = index order; strict > keeps the first maximum
+            const unsigned long long *slot = mine + ((size_t)parity * 8 + r) * 2;
+            const float vr = __uint_as_float((unsigned)ld_acquire_sys(slot));
+            const int ir = (int)ld_acquire_sys(slot + 1);
+            if (bi < 0 || vr > best) { best = vr; bi = ir; }
+        }
+        a.local_idx[0] = bi;
+    }
+}
+
+void head_pick_exchange(cudaStream_t st, const HeadPick &a)
+{
+    G5B_LAUNCH(head_pick_kernel, 1, 32, 0, st, a);
+}
+
 // Every launch of a group must use the same grid: the arrival counters count launches x CTAs.
 void ts_allreduce(cudaStream_t st, const TsReduce &a)
 {

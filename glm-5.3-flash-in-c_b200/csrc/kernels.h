@@ -229,6 +229,21 @@ struct TsReduce {
 };
 void ts_allreduce(cudaStream_t st, const TsReduce &a);
 
+// The arg-max of a head whose vocabulary rows are split over the ranks: this rank's best row is
+// local_idx[0] (an index into its own slice, whose logits start at `logits`), its first row is row0 of
+// the whole vocabulary. Every rank stores (value, global index) into its slot on every rank, counts
+// itself done there, waits (wall-clock limited) for all ranks and keeps the first maximum in index
+// order in local_idx[0]. Words of the flag region from word0: [parity][rank] pairs (2 words each),
+// then the arrival counters; at most 8 ranks.
+struct HeadPick {
+    const float *logits; int *local_idx; int row0;
+    void *const *peers;
+    int rank, size, word0;
+    unsigned long long launch, wait_ns;
+    int *err;
+};
+void head_pick_exchange(cudaStream_t st, const HeadPick &a);
+
 // The exchange of a MoE layer whose sequences are split over the ranks (each rank runs attention and
 // every other per-token kernel for its own sequences only). The tokens of all ranks were gathered
 // first (TsReduce with gather_only); this rank routed a group of them - `m` consecutive tokens of

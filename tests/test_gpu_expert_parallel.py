@@ -87,6 +87,15 @@ def _rank_main(rank, world, conn, peers_conn):
             tok = int(np.argmax(lg)); assert tok == int(np.argmax(lw))
             lg, _ = eng.forward([tok]); lw, _ = orc.forward([tok])
             steps.append(cm.rel_err(lg, lw))
+        # greedy decode on the device: the head is split by vocabulary rows, the ranks exchange their
+        # (value, index) pairs; the tokens must be the CPU path's
+        tok = int(np.argmax(lw))
+        got = eng.decode_greedy(tok, 5)
+        want = []
+        for _ in range(5):
+            lw, _ = orc.forward([tok])
+            tok = int(np.argmax(lw)); want.append(tok)
+        assert got.tolist() == want, (got.tolist(), want)
         eng.close(); orc.close()
         # the full-size layer: 144 routed experts per rank; batch 1 takes the tensor-core kernels,
         # larger batches the register kernels, both end in the exchange
