@@ -103,6 +103,7 @@ def lib() -> C.CDLL:
     L.g5b_engine_ep_export.argtypes = [C.c_void_p, C.c_void_p]
     L.g5b_engine_ep_connect.argtypes = [C.c_void_p, C.c_void_p]
     L.g5b_engine_ep_resync.argtypes = [C.c_void_p]
+    L.g5b_engine_ep_connect_local.argtypes = [C.c_void_p, C.c_int]
     L.g5b_engine_use_sequence.argtypes = [C.c_void_p, C.c_int]
     L.g5b_engine_decode_batch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
     L.g5b_engine_set_option.argtypes = [C.c_void_p, C.c_char_p, C.c_int]
@@ -410,6 +411,13 @@ class Engine(FlatModel):
         blob = b"".join(handles)
         if self.L.g5b_engine_ep_connect(self.handle, blob) != 0:
             self._err("ep_connect")
+
+    @staticmethod
+    def ep_connect_local(engines):
+        """Wire engines that live in this process, one per device, engines[r] = rank r."""
+        arr = (C.c_void_p * len(engines))(*[e.handle for e in engines])
+        if engines[0].L.g5b_engine_ep_connect_local(arr, len(engines)) != 0:
+            engines[0]._err("ep_connect_local")
 
     def ep_resync(self):
         """Re-align the ranks' step count after a failed step (collective; barriers are the caller's)."""

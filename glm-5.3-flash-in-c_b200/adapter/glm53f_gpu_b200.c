@@ -12,9 +12,13 @@
  *
  * Differences from the backend it replaces, visible to the driver: routed experts, router,
  * embedding gather and arg-max run on the GPU (the reference kept them on the CPU,
- * src/gpu/glm53f_gpu.c:1024-1040,1062-1066); one device holds the model (expert-parallel engines
- * are created through the engine API directly).
+ * src/gpu/glm53f_gpu.c:1024-1040,1062-1066). With several devices (ndev > 1) the reference places
+ * consecutive layers on consecutive devices (src/gpu/glm53f_gpu.c:758-790); here the devices form an
+ * expert-parallel group instead - one engine per device, 1 / ndev of the routed experts each, the
+ * trunk split by heads - and every call runs on all of them at once, one host thread per device.
+ * ndev <= 0 ("all" in the reference) takes device 0 only: a group is formed only when asked for.
  */
+#include <pthread.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -23,8 +27,11 @@
 #include "glm53f_gpu.h"        /* reference: src/gpu/glm53f_gpu.h   */
 #include "glm53f_model.h"      /* reference: src/model/glm53f_model.h */
 
+#define B200_MAX_DEV 8
 struct Glm53fGpu {
-    g5b_engine *e;
+    g5b_engine *e;                      /* rank 0: its logits are the call's result */
+    g5b_engine *all[B200_MAX_DEV];
+    int n;
 };
 
 int glm53f_gpu_device_count(void) { return g5b_device_count(); }
@@ -145,38 +152,78 @@ Glm53fGpu *glm53f_gpu_create(struct Glm53fModel *m, const int *devices, int ndev
     g.dense_inter = c->dense_inter; g.routed_scale = c->routed_scale; g.norm_topk = c->norm_topk;
     g.swiglu_limit = c->swiglu_limit; g.fp8_block_r = c->fp8_block_r; g.fp8_block_c = c->fp8_block_c;
 
-    const int device = (devices && ndev > 0) ? devices[0] : 0;
-    g5b_engine *e = g5b_engine_create(&g, c->is_mla, c->is_dense, m->cap, device, 0, 1);
-    if (!e) { fprintf(stderr, "glm53f_b200: %s\n", g5b_last_error()); return NULL; }
-    int rc = put_mat(e, "embed_tokens.weight", &m->mb.embed) | put_mat(e, "lm_head.weight", &m->mb.lm_head) |
+    /* one engine per device; the devices become an expert-parallel group when the experts divide */
+    int n = (devices && ndev > 1) ? ndev : 1;
+    if (n > B200_MAX_DEV) n = B200_MAX_DEV;
+    while (n > 1 && c->n_experts % n) n--;
+    Glm53fGpu *gpu = (Glm53fGpu *)calloc(1, sizeof *gpu);
+    gpu->n = n;
+    int rc = 0;
+    for (int r = 0; r < n && !rc; r++) {
+        const int device = (devices && ndev > 0) ? devices[r] : 0;
+        g5b_engine *e = g5b_engine_create(&g, c->is_mla, c->is_dense, m->cap, device, r, n);
+        if (!e) { rc = -1; break; }
+        gpu->all[r] = e;
+        /* every engine is offered every tensor; routed experts of other ranks are skipped by the engine */
+        rc = put_mat(e, "embed_tokens.weight", &m->mb.embed) | put_mat(e, "lm_head.weight", &m->mb.lm_head) |
              put_vec(e, "norm.weight", m->mb.norm, c->hidden);
-    for (int L = 0; L < m->n_bound && !rc; L++) rc = upload_layer(e, m, L);
-    if (!rc) rc = g5b_engine_finalize(e);
+        for (int L = 0; L < m->n_bound && !rc; L++) rc = upload_layer(e, m, L);
+        if (!rc) rc = g5b_engine_finalize(e);
+    }
+    if (!rc && n > 1) rc = g5b_engine_ep_connect_local(gpu->all, n);
     if (rc) {
         fprintf(stderr, "glm53f_b200: %s\n", g5b_last_error());
-        g5b_engine_free(e);
+        for (int r = 0; r < n; r++) if (gpu->all[r]) g5b_engine_free(gpu->all[r]);
+        free(gpu);
         return NULL;
     }
-    Glm53fGpu *gpu = (Glm53fGpu *)calloc(1, sizeof *gpu);
-    gpu->e = e;
-    if (!glm53f_quiet) printf("B200 engine: %d layers and every routed expert resident on device %d\n", m->n_bound, device);
+    gpu->e = gpu->all[0];
+    if (!glm53f_quiet)
+        printf("B200 engine: %d layers resident on %d device(s), %d routed experts per layer and device\n",
+               m->n_bound, n, c->n_experts / n);
     return gpu;
 }
 
 void glm53f_gpu_free(Glm53fGpu *g)
 {
     if (!g) return;
-    g5b_engine_free(g->e);
+    for (int r = 0; r < g->n; r++) g5b_engine_free(g->all[r]);
     free(g);
+}
+
+/* One rank's share of a forward call (ranks other than 0 need no logits). */
+typedef struct { g5b_engine *e; const int *ids; int T; int rc; } RankCall;
+static void *rank_forward(void *p)
+{
+    RankCall *c = (RankCall *)p;
+    c->rc = g5b_engine_forward(c->e, c->ids, c->T, NULL, NULL);
+    return NULL;
 }
 
 int glm53f_gpu_forward(Glm53fGpu *g, struct Glm53fModel *m, const int *ids, int T, float *logits, int *argmax_all)
 {
     m->layers_completed = 0;
-    if (g5b_engine_forward(g->e, ids, T, logits, argmax_all) != 0) return -1;
+    pthread_t th[B200_MAX_DEV];
+    RankCall call[B200_MAX_DEV];
+    int started = 0, rc = 0;
+    for (int r = 1; r < g->n; r++) {
+        call[r].e = g->all[r]; call[r].ids = ids; call[r].T = T; call[r].rc = -1;
+        if (pthread_create(&th[r], NULL, rank_forward, &call[r]) != 0) { rc = -1; break; }
+        started = r;
+    }
+    /* rank 0 runs even if a thread could not be started: its exchange then times out and reports */
+    if (g5b_engine_forward(g->e, ids, T, logits, argmax_all) != 0) rc = -1;
+    for (int r = 1; r <= started; r++) {
+        pthread_join(th[r], NULL);
+        if (call[r].rc != 0) rc = -1;
+    }
+    if (rc) return -1;
     m->layers_completed = m->n_bound;
     m->cached += T;
     return 0;
 }
 
-void glm53f_gpu_reset(Glm53fGpu *g) { g5b_engine_reset(g->e); }
+void glm53f_gpu_reset(Glm53fGpu *g)
+{
+    for (int r = 0; r < g->n; r++) g5b_engine_reset(g->all[r]);
+}

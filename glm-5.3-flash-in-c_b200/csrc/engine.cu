@@ -2155,8 +2155,6 @@ static int ep_publish_peers(g5b_engine *e, const std::vector<void *> &peers)
     e->ep_decode_launches = 0;
     e->ts_launches = 0;
     e->head_launches = 0;
-    e->ts_launches = 0;
-    e->head_launches = 0;
     return 0;
 }
 
@@ -2196,6 +2194,47 @@ extern "C" int g5b_engine_ep_connect(g5b_engine *e, const void *all_handles)
         peers[r] = p;
     }
     return ep_publish_peers(e, peers);
+}
+
+// The same wiring for ranks that live in ONE process, one engine per device (a host that drives
+// several GPUs from threads of one process, like the reference's own multi-device backend): no
+// handles, the devices are given access to each other's memory and every engine gets the others'
+// exchange regions directly. engines[r] must be rank r of n, each on a device of its own. The
+// caller then runs every step on all engines at the same time, one host thread per engine.
+extern "C" int g5b_engine_ep_connect_local(g5b_engine *const *engines, int n)
+{
+    if (!engines || n < 2) return fail("connect_local needs at least two engines");
+    for (int r = 0; r < n; r++) {
+        g5b_engine *e = engines[r];
+        if (!e || !e->finalized) return fail("connect_local: engine %d is not finalized", r);
+        if (e->ep_size != n || e->ep_rank != r) return fail("connect_local: engine %d is rank %d of %d", r, e ? e->ep_rank : -1, e ? e->ep_size : -1);
+        if (e->ep_connected) return fail("the ranks are already connected");
+        for (int q = 0; q < r; q++)
+            if (engines[q]->device == e->device)
+                return fail("connect_local: ranks %d and %d share device %d (kernels that wait for each other need a GPU each)", q, r, e->device);
+    }
+    for (int r = 0; r < n; r++) {
+        CU(cudaSetDevice(engines[r]->device));
+        if (ep_alloc(engines[r])) return -1;
+    }
+    for (int r = 0; r < n; r++) {
+        g5b_engine *e = engines[r];
+        CU(cudaSetDevice(e->device));
+        std::vector<void *> peers((size_t)n, nullptr);
+        for (int q = 0; q < n; q++) {
+            peers[q] = engines[q]->ep_region;
+            if (q == r) continue;
+            int can = 0;
+            CU(cudaDeviceCanAccessPeer(&can, e->device, engines[q]->device));
+            if (!can) return fail("device %d cannot access device %d's memory", e->device, engines[q]->device);
+            const cudaError_t rc = cudaDeviceEnablePeerAccess(engines[q]->device, 0);
+            if (rc != cudaSuccess && rc != cudaErrorPeerAccessAlreadyEnabled)
+                return fail("peer access from device %d to %d: %s", e->device, engines[q]->device, cudaGetErrorString(rc));
+            cudaGetLastError();
+        }
+        if (ep_publish_peers(e, peers)) return -1;
+    }
+    return 0;
 }
 
 // Re-align the ranks after a step that failed on some of them. Host-side and collective: every rank

@@ -233,6 +233,11 @@ size_t g5b_engine_ep_handle_bytes(void);
 int    g5b_engine_ep_export(g5b_engine *e, void *handle_out);
 int    g5b_engine_ep_connect(g5b_engine *e, const void *all_handles /* ep_size entries */);
 int    g5b_engine_ep_resync(g5b_engine *e);
+/* The same wiring for ranks living in one process (one engine per device, engines[r] = rank r of n;
+ * this is how the adapter serves the reference's multi-device backend call,
+ * src/gpu/glm53f_gpu.h:44-46): no handles, peer access between the devices. Every step must then be
+ * run on all engines at the same time, one host thread each. */
+int    g5b_engine_ep_connect_local(g5b_engine *const *engines, int n);
 
 /* ---------------------------------------------------------------- LAYER OPS ---- */
 /* Host buffers in and out. Activations are FP32 like the reference's. `layer` indexes the

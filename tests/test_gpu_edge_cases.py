@@ -156,3 +156,57 @@ def test_two_engines_on_two_devices_in_one_process(gpu_lib, binding):
     for e in engines:
         e.close()
     orc.close()
+
+
+def test_expert_parallel_group_inside_one_process(gpu_lib, binding):
+    """Two engines of one process, one per device, wired without handles (peer access) and driven by one
+    host thread each - what the adapter does when the reference's driver passes several devices
+    (src/gpu/glm53f_gpu.h:44-46). Logits of both ranks against the CPU path, then greedy decode."""
+    import threading
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    spec = synth.tiny_spec()
+    tensors = synth.make_model(spec, seed=11, recipe="baseline")
+    engines = []
+    for r in range(2):
+        e = pkg.Engine(spec.cfg, spec.is_mla, spec.is_dense, 32, r, r, 2)
+        e.load_all(tensors); e.finalize()
+        engines.append(e)
+    with pytest.raises(RuntimeError, match="rank"):
+        pkg.Engine.ep_connect_local(engines[::-1])
+    pkg.Engine.ep_connect_local(engines)
+    orc = binding.OracleModel(spec.cfg, spec.is_mla, spec.is_dense, 32, 2)
+    orc.load_all(tensors); orc.finalize()
+
+    def on_all(fn):
+        out, errs = [None, None], []
+
+        def run(r):
+            try:
+                out[r] = fn(engines[r])
+            except Exception as exc:                   # noqa: BLE001
+                errs.append(repr(exc))
+        ts = [threading.Thread(target=run, args=(r,)) for r in range(2)]
+        for t in ts:
+            t.start()
+        for t in ts:
+            t.join()
+        assert not errs, errs
+        return out
+
+    ids = np.random.default_rng(0).integers(0, spec.cfg.vocab, 18).tolist()
+    lw, _ = orc.forward(ids)
+    for lg, _ in on_all(lambda e: e.forward(ids)):
+        assert common.rel_err(lg, lw) < 1e-3
+    tok = int(np.argmax(lw))
+    want = []
+    t = tok
+    for _ in range(6):
+        lw, _ = orc.forward([t])
+        t = int(np.argmax(lw)); want.append(t)
+    for got in on_all(lambda e: e.decode_greedy(tok, 6)):
+        assert got.tolist() == want
+    for e in engines:
+        e.close()
+    orc.close()
