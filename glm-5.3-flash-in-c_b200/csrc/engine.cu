@@ -1043,8 +1043,11 @@ static MlaShape mla_shape(const g5b_engine *e)
 // projects values for those heads (the kernels see a layer of H / N heads: compact buffers, kv_b
 // row-sliced to the heads' W_k | W_v rows), and multiplies its heads' columns of o_proj; the partial
 // output rows are summed in rank order like the KDA layer's. FP8 slices must start on scale-block
-// boundaries; the tensor-core attention core takes heads in groups of 16.
-static bool mla_heads_split(const g5b_engine *e, const Layer &w, const MlaShape &s)
+// boundaries. The tensor-core attention core takes heads in groups of 16: a rank with fewer heads
+// (8 at N = 8) pads the group with zero queries when the call is one new token (the padding
+// relies on the single token's [heads][latent] rows being a prefix of the padded block), and keeps
+// the layer whole otherwise.
+static bool mla_heads_split(const g5b_engine *e, const Layer &w, const MlaShape &s, int n, bool batch)
 {
     if (!e->tensor_split || e->seq_split || e->ep_size < 2 || !e->ep_connected) return false;
     const int N = e->ep_size;
@@ -1055,7 +1058,10 @@ static bool mla_heads_split(const g5b_engine *e, const Layer &w, const MlaShape 
     if (w.mo.dt == G5B_DT_FP8 && (Hl * s.vh) % w.mo.bc) return false;
     if (w.mo.dt != G5B_DT_FP8 && (Hl * s.vh) % 8) return false;
     MlaShape sl = s; sl.H = Hl;
-    if (e->mla_tensor && mla_flash_takes(s) && !mla_flash_takes(sl)) return false;    // keep the tensor-core core
+    if (e->mla_tensor && mla_flash_takes(s) && !mla_flash_takes(sl)) {                // keep the tensor-core core
+        MlaShape sp = sl; sp.H = (Hl + 15) / 16 * 16;
+        if (!(n == 1 && !batch && sp.H <= s.H && mla_flash_takes(sp))) return false;
+    }
     return true;
 }
 
@@ -1071,10 +1077,17 @@ static int run_mla(g5b_engine *e, Layer &w, const float *x, int n, int cached, f
     if (!w.q_a.loaded() || !w.kv_b.loaded() || !w.mo.loaded() || !w.wq_b.loaded() || !w.ape || !w.latent)
         return fail("this layer's MLA weights were not loaded");
     if (cached + (batch ? 1 : n) > e->cap) return fail("MLA cache position %d beyond capacity %d", cached + (batch ? 1 : n) - 1, e->cap);
-    const bool ms = mla_heads_split(e, w, s);
+    const bool ms = mla_heads_split(e, w, s, n, batch);
     const int Hl = ms ? s.H / e->ep_size : s.H, h0 = ms ? e->ep_rank * Hl : 0;
     MlaShape sl = s;                               // what the per-head kernels see
     sl.H = Hl;
+    MlaShape sf = sl;                              // what the tensor-core attention core sees: heads padded to its group of 16
+    bool flash = e->mla_tensor && mla_flash_takes(sl);
+    if (!flash && ms && e->mla_tensor && n == 1 && !batch) {
+        sf.H = (Hl + 15) / 16 * 16;
+        flash = sf.H <= s.H && mla_flash_takes(sf);
+        if (flash) CU(cudaMemsetAsync(e->mqa + (size_t)Hl * s.KL, 0, (size_t)(sf.H - Hl) * s.KL * sizeof(double), e->st));
+    }
     const DMat qb = ms ? row_slice(w.q_b, h0 * s.qn, Hl * s.qn) : w.q_b;
     const DMat kvb = ms ? row_slice(w.kv_b, h0 * (s.qn + s.vh), Hl * (s.qn + s.vh)) : w.kv_b;
     GemvSeg a[5] = {make_seg(w.q_a, x, E, e->mq_raw, c.q_lora), make_seg(w.kv_a, x, E, e->mct, c.kv_lora),
@@ -1101,8 +1114,8 @@ static int run_mla(g5b_engine *e, Layer &w, const float *x, int n, int cached, f
     dsa_select(e->st, e->msel, e->mnsel, ist, e->mqidx, e->mwp, e->mscore, n, cached, s);
     if (!forked) mla_absorb(e->st, e->mqa, e->mq, kvb, n, sl);
     else if (join && cudaStreamWaitEvent(e->st, e->side_done, 0) != cudaSuccess) cudaStreamSynchronize(e->side);
-    if (e->mla_tensor && mla_flash_takes(sl))
-        mla_attend_flash(e->st, e->mcb, e->mqa, lat, e->msel, e->mnsel, e->mpart, e->mpart_bytes, e->mdsc, n, cached, sl);
+    if (flash)
+        mla_attend_flash(e->st, e->mcb, e->mqa, lat, e->msel, e->mnsel, e->mpart, e->mpart_bytes, e->mdsc, n, cached, sf);
     else
         mla_attend(e->st, e->mcb, e->mqa, lat, e->msel, e->mnsel, e->mdsc, e->mpart, e->mstats, e->mcount, MLA_PART_TOKENS, n, cached, sl);
     mla_vout(e->st, e->macc, e->mcb, kvb, n, sl);

@@ -198,7 +198,54 @@ def _seq_rank_main(rank, world, conn, peers_conn):
         conn.send(("error", repr(exc)))
 
 
-def _run_pair(target, bars):
+def _mla_rank_main(rank, world, conn, peers_conn):
+    """Child process: full-size MLA layers split by heads over two ranks, BF16 latent cache (the
+    tensor-core attention core). 64 heads: 32 per rank. 16 heads: 8 per rank, fewer than the core's
+    group of 16 - one new token pads the group with zero queries, several positions keep the layer
+    whole. Caches seeded directly; every output against the CPU path."""
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    sys.path.insert(0, os.path.dirname(here)); sys.path.insert(0, here)
+    import numpy as np
+    import synth as sy
+    import common as cm
+    from oracle import binding
+    try:
+        worst = []
+        for heads in (64, 16):
+            spec = sy.layer_spec("mla")
+            c = spec.cfg
+            c.mla_heads = heads
+            cap = 8192
+            tensors = sy.make_model(spec, seed=5, recipe="spread")
+            eng = sy.pkg.Engine(c, spec.is_mla, spec.is_dense, cap, rank, rank, world)
+            eng.set_option("allow_partial", 1)
+            eng.set_option("latent_bf16", 1)
+            eng.load_all(tensors); eng.finalize()
+            conn.send(("handle", eng.ep_export()))
+            eng.ep_connect(conn.recv())
+            orc = binding.OracleModel(c, spec.is_mla, spec.is_dense, cap, 2)
+            orc.load_all(tensors); orc.finalize()
+            rng = np.random.default_rng(5)
+            lat = sy.bf16_round(rng.standard_normal((cap, c.kv_lora)).astype(np.float32))
+            idx = rng.standard_normal(2 * cap * c.index_dim + (cap // c.index_kpool) * c.index_dim).astype(np.float32)
+            for m in (eng, orc):
+                m.state_write(0, 1, 0, lat)
+                m.state_write(0, 2, 0, idx)
+            w = 0.0
+            for ctx, T in ((2048, 1), (8000, 1), (8000, 5)):
+                x = sy.bf16_round(rng.standard_normal((T, c.hidden)).astype(np.float32))
+                (g, gs), (o, os_) = eng.op_mla(0, x, ctx - T), orc.op_mla(0, x, ctx - T)
+                assert (gs is None and os_ is None) or np.array_equal(gs, os_), (heads, ctx, T)
+                w = max(w, cm.rel_err(g, o))
+            worst.append(w)
+            eng.close(); orc.close()
+        conn.send(("ok", worst[0], worst[1]))
+    except Exception as exc:
+        conn.send(("error", repr(exc)))
+
+
+def _run_pair(target, bars, rounds=2):
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
@@ -210,7 +257,7 @@ def _run_pair(target, bars):
     for p in procs:
         p.start()
     try:
-        for _ in range(2):                                  # the tiny model's engines, then the full-size layer's
+        for _ in range(rounds):                             # one exchange of handles per engine the ranks build
             handles = []
             for r in range(world):
                 assert pipes[r][0].poll(600), "rank did not export its handle"
@@ -235,6 +282,11 @@ def test_two_ranks_split_the_sequences_and_match_the_cpu_path(gpu_lib):
     """Logits of every rank's own sequences within 1e-3 of separate CPU sessions with identical
     arg-max, MoE ops on own tokens (one group and two groups of gathered tokens) within 1e-5."""
     _run_pair(_seq_rank_main, (1e-3, 0.5, 1e-5, 1e-5))
+
+
+def test_two_ranks_split_the_mla_heads(gpu_lib):
+    """Within the BF16 latent cache's 3e-3 of the CPU path (which keeps FP32 latents), selections identical."""
+    _run_pair(_mla_rank_main, (3e-3, 3e-3), rounds=2)
 
 
 def test_two_ranks_exchange_and_match_the_cpu_path(gpu_lib):
