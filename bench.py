@@ -159,7 +159,8 @@ def bench_config(world: int) -> dict:
     """The `config` object of the JSON line: the same for this repo's arm and the reference arm."""
     return {"workload": "config 2: single MoE layer decode, hidden 4096, inter 2048, 288+1 experts, top-8, batch 1",
             "l2": f"GPU arm: flushed before every step ({FLUSH_BYTES >> 21} MiB written, then {FLUSH_BYTES >> 21} MiB "
-                  "read so that no dirty line is left); CPU arm: 4 rotating inputs, 226 MB of weights per step",
+                  "read so that no dirty line is left), the timed steps dealt over 16 different tokens; CPU arm: 4 rotating "
+                  "inputs, 226 MB of weights per step",
             "parallelism": "one GPU" if world == 1 else
                            f"expert parallel over {world} GPUs: one token stream, {288 // world} routed experts per rank"}
 
@@ -178,37 +179,46 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
-def time_batch(pkg, eng, torch, B, steps, warmup, flush=FLUSH_BYTES, phases=True):
-    """Device-resident timing of the MoE layer at batch B: (ms per step list, phase ms, launches)."""
+def time_batch(pkg, eng, torch, B, steps, warmup, flush=FLUSH_BYTES, phases=True, inputs=1):
+    """Device-resident timing of the MoE layer at batch B: (ms per step list, phase ms, launches, output, ms
+    per input). `inputs` > 1: the `steps` timed steps are dealt over that many different seeded inputs
+    (different routings: with expert parallelism a step takes what the busiest rank takes, which depends on
+    how the token's eight picks fall on the ranks)."""
     import synth
     L = pkg.lib()
-    x = torch.from_numpy(synth.moe_inputs(eng.cfg, B, SEED)).cuda()
-    out = torch.empty_like(x)
+    inputs = max(1, min(inputs, steps))
+    xs = [torch.from_numpy(synth.moe_inputs(eng.cfg, B, SEED + 1000 * k)).cuda() for k in range(inputs)]
+    out = torch.empty_like(xs[0])
     torch.cuda.synchronize()
     each = np.zeros(max(steps, warmup, 1), np.float32)
     tot = C.c_float(0)
-    assert L.g5b_time_op(eng.handle, b"moe", 0, x.data_ptr(), B, 0, out.data_ptr(), warmup, flush,
+    assert L.g5b_time_op(eng.handle, b"moe", 0, xs[0].data_ptr(), B, 0, out.data_ptr(), warmup, flush,
                          C.byref(tot), each.ctypes.data) == 0, L.g5b_last_error()
     ms4 = (C.c_float * 8)()
     cnt = C.c_long(0)
     n0 = L.g5b_launch_count()
-    assert L.g5b_time_op(eng.handle, b"moe", 0, x.data_ptr(), B, 0, out.data_ptr(), steps, flush,
-                         C.byref(tot), each.ctypes.data) == 0, L.g5b_last_error()
+    timed, per_input = [], []
+    for k, x in enumerate(xs):
+        share = steps // inputs + (1 if k < steps % inputs else 0)          # exactly `steps` timed steps in all
+        assert L.g5b_time_op(eng.handle, b"moe", 0, x.data_ptr(), B, 0, out.data_ptr(), share, flush,
+                             C.byref(tot), each.ctypes.data) == 0, L.g5b_last_error()
+        timed += each[:share].astype(float).tolist()
+        per_input.append(float(np.mean(each[:share])))
     launches = L.g5b_launch_count() - n0 - (2 * steps if flush else 0)
-    timed = each[:steps].astype(float)
+    timed = np.asarray(timed)
     if not phases:
-        return timed, [0.0] * 4, int(launches), out
+        return timed, [0.0] * 4, int(launches), out, per_input
     # per-phase times in a separate short pass: the phase events make the host wait inside every
     # step, which would inflate the step time measured above
     eng.set_option("profile", 1)
     L.g5b_engine_profile_read(eng.handle, ms4, 8, C.byref(cnt), 1)
     scratch = np.zeros(32, np.float32)
-    assert L.g5b_time_op(eng.handle, b"moe", 0, x.data_ptr(), B, 0, out.data_ptr(), min(20, max(3, steps)), flush,
+    assert L.g5b_time_op(eng.handle, b"moe", 0, xs[0].data_ptr(), B, 0, out.data_ptr(), min(20, max(3, steps)), flush,
                          C.byref(tot), scratch.ctypes.data) == 0, L.g5b_last_error()
     L.g5b_engine_profile_read(eng.handle, ms4, 8, C.byref(cnt), 1)
     eng.set_option("profile", 0)
     phases = [ms4[i] / max(1, cnt.value) for i in range(4)]
-    return timed, phases, int(launches), out
+    return timed, phases, int(launches), out, per_input
 
 
 def time_attention_layers(pkg, torch, steps: int, peak: float, device: int = 0):
@@ -826,8 +836,21 @@ def main():
     sampler.start()
     sampler.wait_first()
     ranks.barrier()
-    each, phases, launches, _ = time_batch(pkg, eng, torch, 1, args.steps, warmup, phases=not use_ep)
+    HEADLINE_INPUTS = 16          # different tokens, i.e. different routings, share the timed steps
+    each, phases, launches, _, per_input = time_batch(pkg, eng, torch, 1, args.steps, warmup, phases=not use_ep,
+                                                      inputs=HEADLINE_INPUTS)
     ranks.barrier()
+    if use_ep:
+        # how the eight picks of each of those tokens fall on the ranks: a step takes what the busiest rank takes
+        per = args.experts // world
+        busiest = []
+        for k in range(len(per_input)):
+            idx, _ = one_eng.op_router(0, synth.moe_inputs(spec.cfg, 1, SEED + 1000 * k))
+            busiest.append(int(np.bincount(idx.ravel() // per, minlength=world).max()))
+        slowest = ranks.gather(per_input)
+        extra["expert_parallel"]["tokens_timed"] = len(per_input)
+        extra["expert_parallel"]["picks_on_the_busiest_rank_per_token"] = busiest
+        extra["expert_parallel"]["ms_per_token_slowest_rank"] = [float(max(r[k] for r in slowest)) for k in range(len(per_input))]
     local_ms_per_step = float(each.sum()) / args.steps
     ms_per_step = ranks.reduce(local_ms_per_step, "max")        # the slowest rank's
     # expert parallel: all ranks serve the same token; replicas only when asked for: one stream per rank
@@ -877,14 +900,14 @@ def main():
     if use_ep:
         # N independent replicas of the layer, one token stream each (no data-path collective)
         ranks.barrier()
-        r_each, _, _, _ = time_batch(pkg, one_eng, torch, 1, args.steps, warmup, phases=False)
+        r_each, _, _, _, _ = time_batch(pkg, one_eng, torch, 1, args.steps, warmup, phases=False)
         r_ms = ranks.reduce(float(r_each.sum()) / args.steps, "max")
         extra["replicas"] = {"ranks": world, "tokens_per_s": world * 1e3 / r_ms, "ms_per_step": r_ms,
                              "note": "one whole copy of the layer and one token stream per rank"}
         ep_eng.close()
     if rank == 0 and world == 1:
         for B in [int(b) for b in args.batches.split(",") if b]:
-            eb, ph, _, _ = time_batch(pkg, one_eng, torch, B, max(10, args.steps // 10), 3)
+            eb, ph, _, _, _ = time_batch(pkg, one_eng, torch, B, max(10, args.steps // 10), 3)
             idx, _ = one_eng.op_router(0, synth.moe_inputs(spec.cfg, B, SEED))
             distinct = int(len(set(idx.ravel().tolist())))
             ms = float(eb.mean())

@@ -430,6 +430,17 @@ class Engine(FlatModel):
             self._err("decode_greedy")
         return out
 
+    def decode_speculative(self, first: int, n: int):
+        """Greedy decode with the MTP layer's drafts verified two positions per pass.
+        Returns (tokens, {"drafts", "accepted", "passes"})."""
+        fn = self.L.g5b_engine_decode_speculative
+        fn.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+        out = np.zeros(n, np.int32)
+        st = (C.c_long * 3)()
+        if fn(self.handle, first, n, out.ctypes.data, st) != 0:
+            self._err("decode_speculative")
+        return out, {"drafts": int(st[0]), "accepted": int(st[1]), "passes": int(st[2])}
+
     def decode_sampled(self, first: int, n: int, temperature: float, top_p: float, seed: int):
         out = np.zeros(n, np.int32)
         if self.L.g5b_engine_decode_sampled(self.handle, first, n, C.c_float(temperature), C.c_float(top_p), seed,

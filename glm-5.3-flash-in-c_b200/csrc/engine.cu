@@ -104,10 +104,13 @@ struct g5b_engine {
     // Layer slot (MLA + MoE, no mHC tensors), its norms and input projection, its own position count
     bool mtp = false;
     int mtp_cached = 0;
+    int last_T = 0;                              // positions of the last forward call (rows of mtp_h in use)
     float *enorm = nullptr, *hnorm = nullptr, *head_norm = nullptr;
     DMat eh;
     float *mtp_h = nullptr;                      // [cap + CHUNK][hidden]: stream means of the positions of the last forward call
     float *mtp_cat = nullptr, *mtp_x = nullptr;  // [CHUNK][2 hidden], [CHUNK][hidden]
+    std::vector<float *> kda_snap;               // speculative decode: per layer, the current sequence's KDA state as it was
+    bool snap_first = false;                     // after the first position of the two-position pass in flight
     int seq_split = 0;                           // option "sequence_split": every rank runs its own sequences, MoE layers
                                                  // gather the ranks' tokens and send contribution rows home
     int *ep_arrive = nullptr;
@@ -1017,7 +1020,8 @@ static int run_kda(g5b_engine *e, Layer &w, const float *x, int n, float *out, b
     else
         kda_core(e->st, e->ko, e->kq, e->kk, e->kv, e->kz, e->kbraw, e->kgb, w.q_conv, w.k_conv, w.v_conv,
                  w.A_log, w.dt_bias, w.o_norm, w.kda_state + (size_t)e->cur_seq * e->kda_seq, n, ks, 1, 0,
-                 lr_inside ? &lr : nullptr, h0, Hl);
+                 lr_inside ? &lr : nullptr, h0, Hl,
+                 e->snap_first && n > 1 ? e->kda_snap[(size_t)(&w - e->L.data())] : nullptr, 0);
     if (!ts) return proj(e, w.ko, e->ko, P, out, E, n);
     {
         GemvSeg o = make_seg(col_slice(w.ko, p0, Pl), e->ko + p0, P, e->ts_part, E);
@@ -1248,7 +1252,7 @@ static int forward_device(g5b_engine *e, const int *ids_dev, int T, bool all_pos
     flush_hc_post(e);
     // with the MTP layer open every position's stream mean is kept, row t of this call
     // (src/model/glm53f_model.c:460-468)
-    if (e->mtp && (size_t)T <= (size_t)e->cap + CHUNK) head_mean(e->st, e->mtp_h, e->h, T, M, E);
+    if (e->mtp && (size_t)T <= (size_t)e->cap + CHUNK) { head_mean(e->st, e->mtp_h, e->h, T, M, E); e->last_T = T; }
     const int first = all_positions ? 0 : T - 1;
     for (int t0 = first; t0 < T; t0 += CHUNK) {
         const int n = T - t0 < CHUNK ? T - t0 : CHUNK;
@@ -1579,7 +1583,7 @@ static int check_op(g5b_engine *e, int layer, int T)
 // input_layernorm)); x += MoE(RMSNorm(x, post_attention_layernorm)); for the last position the
 // draft is the first-max arg-max of lm_head(RMSNorm(x, shared_head.norm)). h: T host rows, or NULL
 // for the rows the last forward call kept on the device. x_out: host [T][hidden] or NULL.
-extern "C" int g5b_mtp_feed(g5b_engine *e, const float *h, const int *next_ids, int T, int *draft, float *x_out)
+static int mtp_feed_rows(g5b_engine *e, const float *h, const float *h_dev, const int *next_ids, int T, int *draft, float *x_out)
 {
     if (!e || !e->finalized || !e->mtp) return fail("the MTP layer is not enabled (g5b_engine_enable_mtp before loading)");
     CU(cudaSetDevice(e->device));
@@ -1596,7 +1600,7 @@ extern "C" int g5b_mtp_feed(g5b_engine *e, const float *h, const int *next_ids, 
     if (ensure_ids(e, (size_t)T)) return -1;
     CU(cudaMemcpyAsync(e->ids_dev, next_ids, (size_t)T * 4, cudaMemcpyHostToDevice, e->st));
     Staged s{e};
-    const float *hd = e->mtp_h;
+    const float *hd = h_dev ? h_dev : e->mtp_h;          // device rows: the caller's, or the kept ones from row 0
     if (h) {
         hd = s.in(h, (size_t)T * E);
         if (!hd) return fail("out of device memory");
@@ -1641,6 +1645,90 @@ extern "C" int g5b_mtp_feed(g5b_engine *e, const float *h, const int *next_ids, 
     if (check_device_error(e)) return -1;
     e->mtp_cached += T;
     return 0;
+}
+
+// Speculative greedy decode with the MTP layer as the drafter (the use glm53f_mtp.h:11-14 describes;
+// the reference itself only counts how often a draft is right). Every pass feeds the model two
+// positions, the current token and the draft of the one after it; the draft is kept only when
+// the model's own arg-max for that position is the same token, so the tokens are those of greedy
+// decode (a position verified in a two-position pass goes through the kernels for several
+// positions, whose sums can differ from the one-position kernels' in the last bits). A rejected
+// draft has already advanced the KDA states: during such a pass every KDA layer also writes its
+// state as it is after the first position to a second buffer, and a rejection copies that back;
+// latent and indexer rows of the rejected position are simply written again by the next pass. Needs the MTP layer fed up to, not including, the last cached position
+// (after a prompt: its hidden states but the last with its tokens but the first), and the hidden
+// state of the last position still kept (no other forward call in between).
+// stats: [0] drafts made, [1] drafts accepted, [2] model passes.
+extern "C" int g5b_engine_decode_speculative(g5b_engine *e, int first, int n, int *out, long *stats)
+{
+    if (!e || !e->finalized || !e->mtp) return fail("the MTP layer is not enabled (g5b_engine_enable_mtp before loading)");
+    CU(cudaSetDevice(e->device));
+    if (e->dirty) return fail("an earlier call failed half-way: reset the engine (g5b_engine_reset) first");
+    if (n < 1 || e->cached + n + 1 > e->cap) return fail("speculative decode of %d tokens exceeds the session capacity", n);
+    if (first < 0 || first >= e->c.vocab) return fail("token id %d outside the vocabulary", first);
+    if (e->cached < 1 || e->mtp_cached != e->cached - 1)
+        return fail("the MTP layer holds %d positions, the model %d: feed it the hidden states up to the last position but one first",
+                    e->mtp_cached, e->cached);
+    const g5b_config &c = e->c;
+    const size_t E = (size_t)c.hidden;
+    if (e->kda_snap.empty()) {
+        e->kda_snap.assign((size_t)c.n_layers, nullptr);
+        for (int l = 0; l < c.n_layers; l++)
+            if (e->L[l].kda_state && walloc(e, &e->kda_snap[l], e->kda_seq)) return -1;
+    }
+    long drafts = 0, right = 0, passes = 0;
+    int tok = first, got = 0;
+    int h_row = e->last_T - 1;                    // row of the kept hidden states that belongs to the last cached position
+    if (h_row < 0) return fail("no hidden state is kept: run the prompt first");
+    while (got < n) {
+        // the draft of the token after `tok`
+        int draft = -1;
+        if (mtp_feed_rows(e, nullptr, e->mtp_h + (size_t)h_row * E, &tok, 1, &draft, nullptr)) return -1;
+        drafts++;
+        if (got + 1 >= n) {
+            // one token left to produce: no use for a second position
+            int a = -1;
+            if (g5b_engine_forward(e, &tok, 1, nullptr, &a)) return -1;
+            passes++;
+            out[got++] = a;
+            right += a == draft;
+            break;
+        }
+        const int pair[2] = {tok, draft};
+        int am[2] = {-1, -1};
+        e->snap_first = true;                     // every KDA layer also leaves its state after the first position
+        const int frc = g5b_engine_forward(e, pair, 2, nullptr, am);
+        e->snap_first = false;
+        if (frc) return -1;
+        passes++;
+        if (am[0] == draft) {
+            right++;
+            out[got++] = am[0];
+            out[got++] = am[1];
+            // the MTP layer catches up with the accepted position: (its hidden state, the token after it)
+            if (mtp_feed_rows(e, nullptr, e->mtp_h, &am[0], 1, nullptr, nullptr)) return -1;
+            tok = am[1];
+            h_row = 1;
+        } else {
+            // the second position was built on a wrong token: fall back to the state after the first
+            for (int l = 0; l < c.n_layers; l++)
+                if (e->kda_snap[l])
+                    CU(cudaMemcpyAsync(e->L[l].kda_state + (size_t)e->cur_seq * e->kda_seq, e->kda_snap[l], e->kda_seq * 4,
+                                       cudaMemcpyDeviceToDevice, e->st));
+            CU(cudaStreamSynchronize(e->st));
+            e->cached -= 1;
+            out[got++] = am[0];
+            tok = am[0];
+            h_row = 0;
+        }
+    }
+    if (stats) { stats[0] = drafts; stats[1] = right; stats[2] = passes; }
+    return 0;
+}
+
+extern "C" int g5b_mtp_feed(g5b_engine *e, const float *h, const int *next_ids, int T, int *draft, float *x_out)
+{
+    return mtp_feed_rows(e, h, nullptr, next_ids, T, draft, x_out);
 }
 
 // The stream means the last forward call kept: T rows from row `first`, to the host.

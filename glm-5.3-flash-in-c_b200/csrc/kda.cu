@@ -29,6 +29,8 @@ struct KdaArgs {
                                   // CTA (h, s) advances sequence s by the T positions at rows s*T ...)
     const uint16_t *f_b, *g_b;    // optional (T == 1): z and gb are computed here from lrf / lrg
     const float *lrf, *lrg;
+    float *snap;                  // optional: a second state buffer (same layout) that receives the state as it
+    int snap_after;               // is after position snap_after of the call (speculative decode keeps it to fall back on)
 };
 
 // conv + SiLU of one channel at one position; `past` holds K-1 previous inputs, oldest first.
@@ -184,6 +186,21 @@ __global__ void __launch_bounds__(DS > 0 ? DS : 512) kda_core_kernel(const KdaAr
             const float n = __fmul_rn(onw, __fmul_rn(ov, inv));
             a.o[off] = __fmul_rn(n, sigmoid_host(a.f_b ? gb_own : a.gb[off]));
         }
+        if (a.snap && t == a.snap_after && live) {
+            float *sn = a.snap + (size_t)blockIdx.y * a.seq_stride;
+            float *Sn = sn + (size_t)h * D * D, *cn = sn + (size_t)a.H * D * D;
+            if (DS > 0) {
+#pragma unroll
+                for (int i = 0; i < DS; i++) Sn[(size_t)i * DS + d] = sreg[i];
+            } else {
+                for (int i = 0; i < D; i++) Sn[(size_t)i * D + d] = S[(size_t)i * D + d];
+            }
+            for (int j = 0; j < hist; j++) {
+                cn[(size_t)ch * hist + j] = pq[j];
+                cn[(size_t)P * hist + (size_t)ch * hist + j] = pk[j];
+                cn[(size_t)2 * P * hist + (size_t)ch * hist + j] = pv[j];
+            }
+        }
     }
 
     if (live) {
@@ -202,13 +219,14 @@ __global__ void __launch_bounds__(DS > 0 ? DS : 512) kda_core_kernel(const KdaAr
 void kda_core(cudaStream_t st, float *o, const float *q, const float *k, const float *v, const float *z,
               const float *braw, const float *gb, const float *q_conv, const float *k_conv,
               const float *v_conv, const float *A_log, const float *dt_bias, const float *o_norm,
-              float *state, int T, const KdaShape &s, int n_seq, size_t seq_stride, const KdaLowRank *lr, int head0, int heads)
+              float *state, int T, const KdaShape &s, int n_seq, size_t seq_stride, const KdaLowRank *lr, int head0, int heads,
+              float *snap, int snap_after)
 {
     const bool fused = lr && T == 1 && n_seq <= 1 && (s.D == 64 || s.D == 128);
     KdaArgs a{o, q, k, v, z, braw, gb, q_conv, k_conv, v_conv, A_log, dt_bias, o_norm, state,
               T, s.H, s.D, s.K, head0, s.gate_lb, s.rms_eps, seq_stride,
               fused ? static_cast<const uint16_t *>(lr->f_b) : nullptr, fused ? static_cast<const uint16_t *>(lr->g_b) : nullptr,
-              fused ? lr->lrf : nullptr, fused ? lr->lrg : nullptr};
+              fused ? lr->lrf : nullptr, fused ? lr->lrg : nullptr, snap, snap_after};
     const dim3 grid(heads > 0 ? heads : s.H, n_seq < 1 ? 1 : n_seq);
     const size_t smem = fused ? (size_t)2 * s.D * (2 * s.D + 16) : 0;
     if (s.D == 128) {

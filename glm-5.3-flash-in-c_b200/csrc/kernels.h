@@ -284,7 +284,7 @@ void kda_core(cudaStream_t st, float *o, const float *q, const float *k, const f
               const float *braw, const float *gb, const float *q_conv, const float *k_conv,
               const float *v_conv, const float *A_log, const float *dt_bias, const float *o_norm,
               float *state, int T, const KdaShape &s, int n_seq = 1, size_t seq_stride = 0,
-              const KdaLowRank *lr = nullptr, int head0 = 0, int heads = -1);   // heads [head0, head0 + heads) only
+              const KdaLowRank *lr = nullptr, int head0 = 0, int heads = -1, float *snap = nullptr, int snap_after = 0);   // heads [head0, head0 + heads) only
 
 // ---- mla.cu -------------------------------------------------------------------------------
 struct MlaShape {

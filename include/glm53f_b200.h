@@ -315,6 +315,16 @@ int g5b_state_read(g5b_engine *e, int layer, int kind, size_t offset, float *dst
 int g5b_engine_enable_mtp(g5b_engine *e);
 int g5b_mtp_feed(g5b_engine *e, const float *h, const int *next_ids, int T, int *draft, float *x_out);
 int g5b_mtp_hidden(g5b_engine *e, int first, int T, float *dst);
+/* Speculative greedy decode on top of it (the use glm53f_mtp.h:11-14 describes; the reference stops
+ * at counting right drafts): every pass feeds the model the current token and the MTP layer's draft
+ * of the next one; the draft is kept only when the model's own arg-max is the same token, otherwise
+ * the KDA states fall back to what they were after the first position (every KDA layer writes that
+ * to a second buffer during such a pass) and only the first position's token stands.
+ * The tokens are those of greedy decode. Needs the MTP layer fed up to, not including, the last
+ * cached position (after a prompt: g5b_mtp_feed with the kept hidden states but the last and the
+ * prompt's tokens but the first) and no forward call since the one that produced `first`.
+ * stats (may be NULL): drafts made, drafts accepted, model passes. */
+int g5b_engine_decode_speculative(g5b_engine *e, int first, int n, int *out, long *stats);
 
 /* Measurement aid (no counterpart in the reference): SM cycles per tcgen05.mma instruction, M = 128,
  * N = n (a multiple of 16 up to 256), kind::f16 (K = 16) or, with fp8 != 0, kind::f8f6f4 (K = 32),

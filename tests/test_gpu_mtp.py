@@ -86,3 +86,75 @@ def test_mtp_layer_ops_and_limits(gpu_lib, binding):
     with pytest.raises(RuntimeError, match="not enabled"):
         plain.mtp_feed([1])
     plain.close()
+
+
+SPEC_SEED = 9          # of seeds 0..15 the one with the widest arg-max margins (>= 5 % of the largest logit) and 7 of 17 drafts right
+
+
+def _speculative_on_cpu(orc, prompt, n):
+    """The speculative loop restated with the CPU path's calls: which drafts it makes, which it
+    keeps, and the tokens (those of plain greedy decode)."""
+    lw, _ = orc.forward(prompt)
+    tok = int(np.argmax(lw))
+    first = tok
+    hid = orc.mtp_hidden(0, len(prompt))
+    orc.mtp_feed(prompt[1:], hid[:-1], want_draft=False)
+    h_last = hid[-1:]
+    toks, drafts, right, passes = [], 0, 0, 0
+    while len(toks) < n:
+        d, _ = orc.mtp_feed([tok], h_last)
+        drafts += 1
+        lw, _ = orc.forward([tok])
+        a0 = int(np.argmax(lw))
+        h0 = orc.mtp_hidden(0, 1)
+        if len(toks) + 1 >= n:
+            toks.append(a0); passes += 1; right += int(a0 == d)
+            break
+        if a0 == d:
+            lw, _ = orc.forward([a0])
+            a1 = int(np.argmax(lw))
+            h1 = orc.mtp_hidden(0, 1)
+            orc.mtp_feed([a0], h0, want_draft=False)
+            toks += [a0, a1]; right += 1; passes += 1
+            tok, h_last = a1, h1
+        else:
+            toks.append(a0); passes += 1
+            tok, h_last = a0, h0
+    return first, toks, {"drafts": drafts, "accepted": right, "passes": passes}
+
+
+def _four_token_models(binding, seed):
+    """A tiny model with a vocabulary of four tokens, so that a draft is right often enough for
+    both outcomes to occur within a few steps."""
+    spec = synth.tiny_spec()
+    spec.cfg.vocab = 4
+    tensors = synth.make_model(spec, seed=seed, recipe="spread")
+    tensors.update(synth.make_mtp_layer(spec, seed=seed, recipe="spread"))
+    orc = binding.OracleModel(spec.cfg, spec.is_mla, spec.is_dense, 64, 2)
+    orc.enable_mtp()
+    orc.load_all(tensors); orc.finalize()
+    return spec, tensors, orc
+
+
+def test_speculative_decode_gives_the_greedy_tokens(gpu_lib, binding):
+    spec, tensors, orc = _four_token_models(binding, SPEC_SEED)
+    prompt = np.random.default_rng(3).integers(0, 4, 9).astype(np.int32)
+    first, want, want_stats = _speculative_on_cpu(orc, prompt, 24)
+    assert 0 < want_stats["accepted"] < want_stats["drafts"], want_stats      # both outcomes occur (the seed is chosen for it)
+    eng = pkg.Engine(spec.cfg, spec.is_mla, spec.is_dense, 64)
+    eng.enable_mtp()
+    eng.load_all(tensors); eng.finalize()
+    lg, _ = eng.forward(prompt)
+    assert int(np.argmax(lg)) == first
+    hid = eng.mtp_hidden(0, prompt.size)
+    with pytest.raises(RuntimeError, match="feed it the hidden states"):
+        eng.decode_speculative(first, 4)
+    eng.mtp_feed(prompt[1:], hid[:-1], want_draft=False)
+    got, stats = eng.decode_speculative(first, 24)
+    assert got.tolist() == want
+    assert stats == want_stats
+    # and plain greedy decode of a fresh session gives the same tokens
+    eng.reset()
+    lg, _ = eng.forward(prompt)
+    assert eng.decode_greedy(int(np.argmax(lg)), 24).tolist() == want
+    eng.close(); orc.close()
