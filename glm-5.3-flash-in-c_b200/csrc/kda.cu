@@ -216,6 +216,143 @@ __global__ void __launch_bounds__(DS > 0 ? DS : 512) kda_core_kernel(const KdaAr
     }
 }
 
+// Several positions of one sequence (prefill chunks, the two-position pass of speculative decode): the
+// same arithmetic in the same order as kda_core_kernel, regrouped so that only the state update is
+// serial. For KDA_TB positions at a time: (A) every thread runs its channel's three convolutions
+// and its gate for all of them, and the l2norm sums of all of them are reduced together (the
+// same warp tree and warp order as block_sum, so the same doubles); (B) the state column in
+// registers advances position by position from shared-memory vectors that nobody writes meanwhile -
+// no barrier inside; (C) the output norms of all of them are reduced together. Four barriers per
+// KDA_TB positions instead of eight per position.
+constexpr int KDA_TB = 8;
+template <int DS>
+__global__ void __launch_bounds__(DS) kda_chunk_kernel(const KdaArgs a)
+{
+    constexpr int NW = DS / 32;
+    __shared__ float sQ[KDA_TB][DS], sK[KDA_TB][DS], sAl[KDA_TB][DS], sV[KDA_TB][DS], sO[KDA_TB][DS], sBeta[KDA_TB];
+    __shared__ double redq[KDA_TB][NW], redk[KDA_TB][NW], redo[KDA_TB][NW];
+    const int h = a.head0 + blockIdx.x, d = threadIdx.x, lane = d & 31, wid = d >> 5;
+    constexpr int D = DS;
+    const int P = a.H * D, K = a.K, hist = K - 1;
+    const int ch = h * D + d;
+    float *state = a.state + (size_t)blockIdx.y * a.seq_stride;
+    float *S = state + (size_t)h * D * D;
+    float *cs = state + (size_t)a.H * D * D;
+    const int row0 = blockIdx.y * a.T;
+
+    float pq[16], pk[16], pv[16], wq[17], wk[17], wv[17];
+    for (int j = 0; j < hist; j++) {
+        pq[j] = cs[(size_t)ch * hist + j];
+        pk[j] = cs[(size_t)P * hist + (size_t)ch * hist + j];
+        pv[j] = cs[(size_t)2 * P * hist + (size_t)ch * hist + j];
+    }
+    for (int j = 0; j < K; j++) {
+        wq[j] = a.q_conv[(size_t)ch * K + j];
+        wk[j] = a.k_conv[(size_t)ch * K + j];
+        wv[j] = a.v_conv[(size_t)ch * K + j];
+    }
+    float sreg[DS];
+#pragma unroll
+    for (int i = 0; i < DS; i++) sreg[i] = S[(size_t)i * DS + d];
+    pdl_wait();
+    const float ea = expf_host(a.A_log[h]);
+    const float dtb = a.dt_bias[ch], onw = a.o_norm[d];
+    const float qscale = 1.0f / sqrtf((float)D);
+    float *sn = a.snap ? a.snap + (size_t)blockIdx.y * a.seq_stride : nullptr;
+
+    for (int t0 = 0; t0 < a.T; t0 += KDA_TB) {
+        const int nt = a.T - t0 < KDA_TB ? a.T - t0 : KDA_TB;
+        float qv[KDA_TB], kv[KDA_TB];
+        // ---- (A) convolutions, gates, l2norm sums of nt positions
+#pragma unroll
+        for (int j = 0; j < KDA_TB; j++) {
+            qv[j] = kv[j] = 0.f;
+            if (j < nt) {
+                const size_t off = (size_t)(row0 + t0 + j) * P + ch;
+                qv[j] = conv_step(a.q[off], wq, pq, K);
+                kv[j] = conv_step(a.k[off], wk, pk, K);
+                sV[j][d] = conv_step(a.v[off], wv, pv, K);
+                const float g = __fmul_rn(a.gate_lb, sigmoid_host(__fmul_rn(ea, __fadd_rn(a.z[off], dtb))));
+                sAl[j][d] = expf_host(g);
+                if (d == 0) sBeta[j] = sigmoid_host(a.braw[(size_t)(row0 + t0 + j) * a.H + h]);
+                if (sn && t0 + j == a.snap_after) {              // the histories as they are after this position
+                    float *cn = sn + (size_t)a.H * D * D;
+                    for (int i = 0; i < hist; i++) {
+                        cn[(size_t)ch * hist + i] = pq[i];
+                        cn[(size_t)P * hist + (size_t)ch * hist + i] = pk[i];
+                        cn[(size_t)2 * P * hist + (size_t)ch * hist + i] = pv[i];
+                    }
+                }
+            }
+            const double wqq = warp_sum((double)qv[j] * (double)qv[j]);
+            const double wkk = warp_sum((double)kv[j] * (double)kv[j]);
+            if (lane == 0) { redq[j][wid] = wqq; redk[j][wid] = wkk; }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < KDA_TB; j++) {
+            if (j < nt) {
+                double qq = 0.0, kk = 0.0;
+#pragma unroll
+                for (int w = 0; w < NW; w++) { qq += redq[j][w]; kk += redk[j][w]; }
+                const float qinv = (float)(1.0 / sqrt(qq + (double)1e-6f));
+                const float kinv = (float)(1.0 / sqrt(kk + (double)1e-6f));
+                sQ[j][d] = __fmul_rn(__fmul_rn(qv[j], qinv), qscale);
+                sK[j][d] = __fmul_rn(kv[j], kinv);
+            }
+        }
+        __syncthreads();
+        // ---- (B) the recurrence, position by position, this thread's column of the state
+        for (int j = 0; j < nt; j++) {
+            float u = 0.f, o1 = 0.f;
+#pragma unroll
+            for (int i = 0; i < DS; i++) {
+                sreg[i] = __fmul_rn(sreg[i], sAl[j][i]);
+                u = __fadd_rn(u, __fmul_rn(sreg[i], sK[j][i]));
+            }
+            u = __fmul_rn(__fsub_rn(sV[j][d], u), sBeta[j]);
+#pragma unroll
+            for (int i = 0; i < DS; i++) {
+                sreg[i] = __fadd_rn(sreg[i], __fmul_rn(sK[j][i], u));
+                o1 = __fadd_rn(o1, __fmul_rn(sreg[i], sQ[j][i]));
+            }
+            sO[j][d] = o1;
+            if (sn && t0 + j == a.snap_after) {
+                float *Sn = sn + (size_t)h * D * D;
+#pragma unroll
+                for (int i = 0; i < DS; i++) Sn[(size_t)i * DS + d] = sreg[i];
+            }
+        }
+        // ---- (C) per-head RMSNorm with weight and the output gate of nt positions
+#pragma unroll
+        for (int j = 0; j < KDA_TB; j++) {
+            const double woo = warp_sum(j < nt ? (double)sO[j][d] * (double)sO[j][d] : 0.0);
+            if (lane == 0) redo[j][wid] = woo;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < KDA_TB; j++) {
+            if (j < nt) {
+                double oo = 0.0;
+#pragma unroll
+                for (int w = 0; w < NW; w++) oo += redo[j][w];
+                const size_t off = (size_t)(row0 + t0 + j) * P + ch;
+                const float inv = (float)(1.0 / sqrt(oo / (double)D + (double)a.rms_eps));
+                const float n = __fmul_rn(onw, __fmul_rn(sO[j][d], inv));
+                a.o[off] = __fmul_rn(n, sigmoid_host(a.gb[off]));
+            }
+        }
+        __syncthreads();                                          // the vectors are rewritten by the next group
+    }
+#pragma unroll
+    for (int i = 0; i < DS; i++) S[(size_t)i * DS + d] = sreg[i];
+    for (int j = 0; j < hist; j++) {
+        cs[(size_t)ch * hist + j] = pq[j];
+        cs[(size_t)P * hist + (size_t)ch * hist + j] = pk[j];
+        cs[(size_t)2 * P * hist + (size_t)ch * hist + j] = pv[j];
+    }
+}
+
 void kda_core(cudaStream_t st, float *o, const float *q, const float *k, const float *v, const float *z,
               const float *braw, const float *gb, const float *q_conv, const float *k_conv,
               const float *v_conv, const float *A_log, const float *dt_bias, const float *o_norm,
@@ -229,6 +366,12 @@ void kda_core(cudaStream_t st, float *o, const float *q, const float *k, const f
               fused ? lr->lrf : nullptr, fused ? lr->lrg : nullptr, snap, snap_after};
     const dim3 grid(heads > 0 ? heads : s.H, n_seq < 1 ? 1 : n_seq);
     const size_t smem = fused ? (size_t)2 * s.D * (2 * s.D + 16) : 0;
+    if (T > 1 && s.K <= 17 && (s.D == 128 || s.D == 64)) {
+        // several positions: only the state update runs position by position
+        if (s.D == 128) G5B_LAUNCH_PDL(kda_chunk_kernel<128>, grid, dim3(128), 0, st, a);
+        else            G5B_LAUNCH(kda_chunk_kernel<64>, grid, 64, 0, st, a);
+        return;
+    }
     if (s.D == 128) {
         static SmemGrant grant;
         if (!dev_opt_in_smem((const void *)kda_core_kernel<128>, 2 * 128 * (2 * 128 + 16), grant)) return;
