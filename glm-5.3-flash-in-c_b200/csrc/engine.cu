@@ -1581,8 +1581,9 @@ static int check_op(g5b_engine *e, int layer, int T)
 // glm53f_mtp_feed (src/model/glm53f_mtp.c:100-144) on the MTP layer's own caches and position
 // count: x = eh_proj([RMSNorm(embed(next), enorm), RMSNorm(h, hnorm)]); x += MLA(RMSNorm(x,
 // input_layernorm)); x += MoE(RMSNorm(x, post_attention_layernorm)); for the last position the
-// draft is the first-max arg-max of lm_head(RMSNorm(x, shared_head.norm)). h: T host rows, or NULL
-// for the rows the last forward call kept on the device. x_out: host [T][hidden] or NULL.
+// draft is the first-max arg-max of lm_head(RMSNorm(x, shared_head.norm)). The hidden states: T host
+// rows `h`, else T device rows `h_dev`, else the rows the last forward call kept (from row 0).
+// x_out: host [T][hidden] or NULL.
 static int mtp_feed_rows(g5b_engine *e, const float *h, const float *h_dev, const int *next_ids, int T, int *draft, float *x_out)
 {
     if (!e || !e->finalized || !e->mtp) return fail("the MTP layer is not enabled (g5b_engine_enable_mtp before loading)");
