@@ -117,6 +117,32 @@ def _rank_main(rank, world, conn, peers_conn):
             full = max(full, cm.rel_err(big.op_moe(0, x), ref.op_moe(0, x)))
             ref.close()
         big.close()
+        # speculative greedy decode on the MTP layer's drafts across the ranks (heads split, so each rank
+        # keeps and restores only its own heads' KDA state): the tokens of plain greedy decode on the CPU
+        spec = sy.tiny_spec()
+        spec.cfg.vocab = 4                                     # a draft is right often enough for both outcomes
+        tensors = sy.make_model(spec, seed=9, recipe="spread")
+        tensors.update(sy.make_mtp_layer(spec, seed=9, recipe="spread"))
+        eng = sy.pkg.Engine(spec.cfg, spec.is_mla, spec.is_dense, 64, rank, rank, world)
+        eng.enable_mtp()
+        eng.load_all(tensors); eng.finalize()
+        conn.send(("handle", eng.ep_export()))
+        eng.ep_connect(conn.recv())
+        orc = binding.OracleModel(spec.cfg, spec.is_mla, spec.is_dense, 64, 2)
+        orc.load_all({k: v for k, v in tensors.items() if not k.startswith(f"layers.{spec.cfg.n_layers}.")}); orc.finalize()
+        prompt = np.random.default_rng(3).integers(0, 4, 9).astype(np.int32)
+        lg, _ = eng.forward(prompt); lw, _ = orc.forward(prompt)
+        tok = int(np.argmax(lw)); assert int(np.argmax(lg)) == tok
+        hid = eng.mtp_hidden(0, prompt.size)
+        eng.mtp_feed(prompt[1:], hid[:-1], want_draft=False)
+        got, stats = eng.decode_speculative(tok, 20)
+        want = []
+        for _ in range(20):
+            lw, _ = orc.forward([tok])
+            tok = int(np.argmax(lw)); want.append(tok)
+        assert got.tolist() == want, (got.tolist(), want)
+        assert 0 < stats["accepted"] < stats["drafts"], stats
+        eng.close(); orc.close()
         conn.send(("ok", worst, fw, max(steps), full))
     except Exception as exc:                                   # report instead of dying silently
         conn.send(("error", repr(exc)))
@@ -290,4 +316,4 @@ def test_two_ranks_split_the_mla_heads(gpu_lib):
 
 
 def test_two_ranks_exchange_and_match_the_cpu_path(gpu_lib):
-    _run_pair(_rank_main, (1e-5, 1e-3, 1e-3, 1e-5))
+    _run_pair(_rank_main, (1e-5, 1e-3, 1e-3, 1e-5), rounds=3)
