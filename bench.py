@@ -237,7 +237,7 @@ def time_attention_layers(pkg, torch, steps: int, peak: float, device: int = 0):
         xd = torch.from_numpy(x).cuda(); od = torch.empty_like(xd)
         each = np.zeros(max(n, 3), np.float32); tot = C.c_float(0)
         for k in (3, n):
-            assert L.g5b_time_op(eng.handle, op, 0, xd.data_ptr(), 1, cached, od.data_ptr(), k, FLUSH_BYTES,
+            assert L.g5b_time_op(eng.handle, op, 0, xd.data_ptr(), x.shape[0], cached, od.data_ptr(), k, FLUSH_BYTES,
                                  C.byref(tot), each.ctypes.data) == 0, L.g5b_last_error()
         return float(np.mean(each[:n]))
 
@@ -255,6 +255,10 @@ def time_attention_layers(pkg, torch, steps: int, peak: float, device: int = 0):
         nbytes = weight_bytes(tensors) + 2 * state_bytes
         out[f"kda_H{H}"] = {"ms": ms, "algorithmic_bytes": nbytes, "achieved_GBps": nbytes / (ms * 1e-3) / 1e9,
                             "frac": nbytes / (ms * 1e-3) / 1e9 / peak}
+        if H == 64:
+            # the same layer over a prefill chunk: 64 positions of one sequence
+            x64 = synth.bf16_round(rng.standard_normal((64, spec.cfg.hidden)).astype(np.float32))
+            out["kda_H64_64_positions"] = {"ms": run(eng, b"kda", x64, 0, max(3, steps // 4))}
         eng.close()
     spec = synth.layer_spec("mla")
     c = spec.cfg

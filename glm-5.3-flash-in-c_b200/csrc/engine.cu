@@ -134,6 +134,7 @@ struct g5b_engine {
     int   *ids_dev = nullptr; size_t ids_cap = 0;
     float *inv0, *inv1, *mix, *xc, *xn, *y, *post, *comb;
     float *kq, *kk, *kv, *kz, *kgb, *ko, *kbraw, *klr;
+    KdaScratch kscr{};                           // rows of the position-parallel part of the KDA layer for calls with several positions
     float *mq_raw, *mct, *mwk, *mgate, *mwp, *mq, *mqidx, *mcb, *macc, *mscore, *minvq;
     double *mqa, *mdsc, *mpart = nullptr, *mstats = nullptr;
     int *mcount = nullptr;
@@ -701,7 +702,9 @@ extern "C" int g5b_engine_finalize(g5b_engine *e)
         walloc(e, &e->post, N * M) || walloc(e, &e->comb, N * M * M)) return -1;
     if (walloc(e, &e->kq, N * P) || walloc(e, &e->kk, N * P) || walloc(e, &e->kv, N * P) ||
         walloc(e, &e->kz, N * P) || walloc(e, &e->kgb, N * P) || walloc(e, &e->ko, N * P) ||
-        walloc(e, &e->kbraw, N * c.kda_heads) || walloc(e, &e->klr, N * 2 * D)) return -1;
+        walloc(e, &e->kbraw, N * c.kda_heads) || walloc(e, &e->klr, N * 2 * D) ||
+        walloc(e, &e->kscr.qn, N * P) || walloc(e, &e->kscr.kn, N * P) || walloc(e, &e->kscr.vn, N * P) ||
+        walloc(e, &e->kscr.al, N * P) || walloc(e, &e->kscr.beta, N * c.kda_heads)) return -1;
     if (walloc(e, &e->mq_raw, N * c.q_lora) || walloc(e, &e->mct, N * KL) || walloc(e, &e->mwk, N * c.index_dim) ||
         walloc(e, &e->mgate, N * c.index_dim) || walloc(e, &e->mwp, N * c.index_heads) ||
         walloc(e, &e->mq, N * H * c.qk_nope) || walloc(e, &e->mqidx, N * (size_t)c.index_heads * c.index_dim) ||
@@ -1021,7 +1024,7 @@ static int run_kda(g5b_engine *e, Layer &w, const float *x, int n, float *out, b
         kda_core(e->st, e->ko, e->kq, e->kk, e->kv, e->kz, e->kbraw, e->kgb, w.q_conv, w.k_conv, w.v_conv,
                  w.A_log, w.dt_bias, w.o_norm, w.kda_state + (size_t)e->cur_seq * e->kda_seq, n, ks, 1, 0,
                  lr_inside ? &lr : nullptr, h0, Hl,
-                 e->snap_first && n > 1 ? e->kda_snap[(size_t)(&w - e->L.data())] : nullptr, 0);
+                 e->snap_first && n > 1 ? e->kda_snap[(size_t)(&w - e->L.data())] : nullptr, 0, &e->kscr);
     if (!ts) return proj(e, w.ko, e->ko, P, out, E, n);
     {
         GemvSeg o = make_seg(col_slice(w.ko, p0, Pl), e->ko + p0, P, e->ts_part, E);

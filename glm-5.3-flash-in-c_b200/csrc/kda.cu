@@ -216,114 +216,124 @@ __global__ void __launch_bounds__(DS > 0 ? DS : 512) kda_core_kernel(const KdaAr
     }
 }
 
-// Several positions of one sequence (prefill chunks, the two-position pass of speculative decode): the
-// same arithmetic in the same order as kda_core_kernel, regrouped so that only the state update is
-// serial. For KDA_TB positions at a time: (A) every thread runs its channel's three convolutions
-// and its gate for all of them, and the l2norm sums of all of them are reduced together (the
-// same warp tree and warp order as block_sum, so the same doubles); (B) the state column in
-// registers advances position by position from shared-memory vectors that nobody writes meanwhile -
-// no barrier inside; (C) the output norms of all of them are reduced together. Four barriers per
-// KDA_TB positions instead of eight per position.
-constexpr int KDA_TB = 8;
+// Several positions of one sequence (prefill chunks, the two-position pass of speculative decode).
+// Run position by position, the kernel above spends its time in what does NOT depend on the
+// previous position: three convolutions with an exactly rounded SiLU, the gate's exactly rounded
+// sigmoid and exponential, the l2norm sums in FP64 - about 8 us per position for a head, 0.5 ms for a
+// chunk of 64. Here that part runs for all positions at once (kda_prep_kernel: one CTA per head and
+// position) into scratch rows, and only the state update walks the positions (kda_scan_kernel: one
+// CTA per head, the state column in registers, eight positions' vectors in shared memory at a time,
+// their output norms reduced together). Every value is computed by the same operations in the
+// same order as in kda_core_kernel, so the results are bit-identical.
+struct KdaPrep {
+    KdaArgs a;
+    float *qn, *kn, *vn, *al, *beta;        // [T][P] normalised q (scaled), normalised k, v, exp(gate); [T][H] beta
+};
+
 template <int DS>
-__global__ void __launch_bounds__(DS) kda_chunk_kernel(const KdaArgs a)
+__global__ void __launch_bounds__(DS) kda_prep_kernel(const KdaPrep p)
 {
-    constexpr int NW = DS / 32;
-    __shared__ float sQ[KDA_TB][DS], sK[KDA_TB][DS], sAl[KDA_TB][DS], sV[KDA_TB][DS], sO[KDA_TB][DS], sBeta[KDA_TB];
-    __shared__ double redq[KDA_TB][NW], redk[KDA_TB][NW], redo[KDA_TB][NW];
-    const int h = a.head0 + blockIdx.x, d = threadIdx.x, lane = d & 31, wid = d >> 5;
+    __shared__ double red[32];
+    const KdaArgs &a = p.a;
     constexpr int D = DS;
+    const int h = a.head0 + blockIdx.x, t = blockIdx.y, d = threadIdx.x;
     const int P = a.H * D, K = a.K, hist = K - 1;
     const int ch = h * D + d;
-    float *state = a.state + (size_t)blockIdx.y * a.seq_stride;
-    float *S = state + (size_t)h * D * D;
-    float *cs = state + (size_t)a.H * D * D;
-    const int row0 = blockIdx.y * a.T;
+    const float *cs = a.state + (size_t)a.H * D * D;
+    pdl_wait();
+    // the K - 1 inputs before position t: earlier rows of this call, or the carried history (oldest first)
+    auto conv = [&](const float *x, const float *w, const float *past) {
+        float acc = __fmul_rn(w[(size_t)ch * K + hist], x[(size_t)t * P + ch]);
+        for (int j = 0; j < hist; j++) {
+            const int tt = t - hist + j;
+            const float v = tt >= 0 ? x[(size_t)tt * P + ch] : past[(size_t)ch * hist + (hist + tt)];
+            acc = mul_add_unfused(w[(size_t)ch * K + j], v, acc);
+        }
+        return __fmul_rn(acc, sigmoid_host(acc));
+    };
+    const float qv = conv(a.q, a.q_conv, cs);
+    const float kv = conv(a.k, a.k_conv, cs + (size_t)P * hist);
+    const float vv = conv(a.v, a.v_conv, cs + (size_t)2 * P * hist);
+    const double qq = block_sum((double)qv * (double)qv, red);
+    const double kk = block_sum((double)kv * (double)kv, red);
+    const float qinv = (float)(1.0 / sqrt(qq + (double)1e-6f));
+    const float kinv = (float)(1.0 / sqrt(kk + (double)1e-6f));
+    const size_t off = (size_t)t * P + ch;
+    p.qn[off] = __fmul_rn(__fmul_rn(qv, qinv), 1.0f / sqrtf((float)D));
+    p.kn[off] = __fmul_rn(kv, kinv);
+    p.vn[off] = vv;
+    const float ea = expf_host(a.A_log[h]);
+    const float g = __fmul_rn(a.gate_lb, sigmoid_host(__fmul_rn(ea, __fadd_rn(a.z[off], a.dt_bias[ch]))));
+    p.al[off] = expf_host(g);
+    if (d == 0) p.beta[(size_t)t * a.H + h] = sigmoid_host(a.braw[(size_t)t * a.H + h]);
+}
 
-    float pq[16], pk[16], pv[16], wq[17], wk[17], wv[17];
-    for (int j = 0; j < hist; j++) {
-        pq[j] = cs[(size_t)ch * hist + j];
-        pk[j] = cs[(size_t)P * hist + (size_t)ch * hist + j];
-        pv[j] = cs[(size_t)2 * P * hist + (size_t)ch * hist + j];
-    }
-    for (int j = 0; j < K; j++) {
-        wq[j] = a.q_conv[(size_t)ch * K + j];
-        wk[j] = a.k_conv[(size_t)ch * K + j];
-        wv[j] = a.v_conv[(size_t)ch * K + j];
-    }
+constexpr int KDA_TB = 8;
+template <int DS>
+__global__ void __launch_bounds__(DS) kda_scan_kernel(const KdaPrep p)
+{
+    constexpr int NW = DS / 32, D = DS;
+    __shared__ __align__(16) float sQ[KDA_TB][DS], sK[KDA_TB][DS], sAl[KDA_TB][DS];
+    __shared__ float sV[KDA_TB][DS], sO[KDA_TB][DS], sBeta[KDA_TB];
+    __shared__ double redo[KDA_TB][NW];
+    const KdaArgs &a = p.a;
+    const int h = a.head0 + blockIdx.x, d = threadIdx.x, lane = d & 31, wid = d >> 5;
+    const int P = a.H * D, K = a.K, hist = K - 1;
+    const int ch = h * D + d;
+    float *S = a.state + (size_t)h * D * D;
+    float *cs = a.state + (size_t)a.H * D * D;
     float sreg[DS];
 #pragma unroll
     for (int i = 0; i < DS; i++) sreg[i] = S[(size_t)i * DS + d];
+    const float onw = a.o_norm[d];
     pdl_wait();
-    const float ea = expf_host(a.A_log[h]);
-    const float dtb = a.dt_bias[ch], onw = a.o_norm[d];
-    const float qscale = 1.0f / sqrtf((float)D);
-    float *sn = a.snap ? a.snap + (size_t)blockIdx.y * a.seq_stride : nullptr;
-
     for (int t0 = 0; t0 < a.T; t0 += KDA_TB) {
         const int nt = a.T - t0 < KDA_TB ? a.T - t0 : KDA_TB;
-        float qv[KDA_TB], kv[KDA_TB];
-        // ---- (A) convolutions, gates, l2norm sums of nt positions
 #pragma unroll
         for (int j = 0; j < KDA_TB; j++) {
-            qv[j] = kv[j] = 0.f;
             if (j < nt) {
-                const size_t off = (size_t)(row0 + t0 + j) * P + ch;
-                qv[j] = conv_step(a.q[off], wq, pq, K);
-                kv[j] = conv_step(a.k[off], wk, pk, K);
-                sV[j][d] = conv_step(a.v[off], wv, pv, K);
-                const float g = __fmul_rn(a.gate_lb, sigmoid_host(__fmul_rn(ea, __fadd_rn(a.z[off], dtb))));
-                sAl[j][d] = expf_host(g);
-                if (d == 0) sBeta[j] = sigmoid_host(a.braw[(size_t)(row0 + t0 + j) * a.H + h]);
-                if (sn && t0 + j == a.snap_after) {              // the histories as they are after this position
-                    float *cn = sn + (size_t)a.H * D * D;
-                    for (int i = 0; i < hist; i++) {
-                        cn[(size_t)ch * hist + i] = pq[i];
-                        cn[(size_t)P * hist + (size_t)ch * hist + i] = pk[i];
-                        cn[(size_t)2 * P * hist + (size_t)ch * hist + i] = pv[i];
-                    }
+                const size_t off = (size_t)(t0 + j) * P + ch;
+                sQ[j][d] = p.qn[off]; sK[j][d] = p.kn[off]; sAl[j][d] = p.al[off];
+                sV[j][d] = p.vn[off];
+                if (d == 0) sBeta[j] = p.beta[(size_t)(t0 + j) * a.H + h];
+            }
+        }
+        __syncthreads();
+        // the recurrence: this thread's column of the state through nt positions, no barrier inside
+#pragma unroll 1
+        for (int j = 0; j < nt; j++) {
+            {
+                float u = 0.f, o1 = 0.f;
+                // (the vectors are read four elements at a time: every lane reads the same address, a broadcast)
+                const float4 *al4 = reinterpret_cast<const float4 *>(sAl[j]), *k4 = reinterpret_cast<const float4 *>(sK[j]),
+                             *q4 = reinterpret_cast<const float4 *>(sQ[j]);
+#pragma unroll
+                for (int i = 0; i < DS; i += 4) {
+                    const float4 al = al4[i / 4], kk = k4[i / 4];
+                    sreg[i] = __fmul_rn(sreg[i], al.x);         u = __fadd_rn(u, __fmul_rn(sreg[i], kk.x));
+                    sreg[i + 1] = __fmul_rn(sreg[i + 1], al.y); u = __fadd_rn(u, __fmul_rn(sreg[i + 1], kk.y));
+                    sreg[i + 2] = __fmul_rn(sreg[i + 2], al.z); u = __fadd_rn(u, __fmul_rn(sreg[i + 2], kk.z));
+                    sreg[i + 3] = __fmul_rn(sreg[i + 3], al.w); u = __fadd_rn(u, __fmul_rn(sreg[i + 3], kk.w));
+                }
+                u = __fmul_rn(__fsub_rn(sV[j][d], u), sBeta[j]);
+#pragma unroll
+                for (int i = 0; i < DS; i += 4) {
+                    const float4 kk = k4[i / 4], qq = q4[i / 4];
+                    sreg[i] = __fadd_rn(sreg[i], __fmul_rn(kk.x, u));         o1 = __fadd_rn(o1, __fmul_rn(sreg[i], qq.x));
+                    sreg[i + 1] = __fadd_rn(sreg[i + 1], __fmul_rn(kk.y, u)); o1 = __fadd_rn(o1, __fmul_rn(sreg[i + 1], qq.y));
+                    sreg[i + 2] = __fadd_rn(sreg[i + 2], __fmul_rn(kk.z, u)); o1 = __fadd_rn(o1, __fmul_rn(sreg[i + 2], qq.z));
+                    sreg[i + 3] = __fadd_rn(sreg[i + 3], __fmul_rn(kk.w, u)); o1 = __fadd_rn(o1, __fmul_rn(sreg[i + 3], qq.w));
+                }
+                sO[j][d] = o1;
+                if (a.snap && t0 + j == a.snap_after) {
+                    float *Sn = a.snap + (size_t)h * D * D;
+#pragma unroll
+                    for (int i = 0; i < DS; i++) Sn[(size_t)i * DS + d] = sreg[i];
                 }
             }
-            const double wqq = warp_sum((double)qv[j] * (double)qv[j]);
-            const double wkk = warp_sum((double)kv[j] * (double)kv[j]);
-            if (lane == 0) { redq[j][wid] = wqq; redk[j][wid] = wkk; }
         }
-        __syncthreads();
-#pragma unroll
-        for (int j = 0; j < KDA_TB; j++) {
-            if (j < nt) {
-                double qq = 0.0, kk = 0.0;
-#pragma unroll
-                for (int w = 0; w < NW; w++) { qq += redq[j][w]; kk += redk[j][w]; }
-                const float qinv = (float)(1.0 / sqrt(qq + (double)1e-6f));
-                const float kinv = (float)(1.0 / sqrt(kk + (double)1e-6f));
-                sQ[j][d] = __fmul_rn(__fmul_rn(qv[j], qinv), qscale);
-                sK[j][d] = __fmul_rn(kv[j], kinv);
-            }
-        }
-        __syncthreads();
-        // ---- (B) the recurrence, position by position, this thread's column of the state
-        for (int j = 0; j < nt; j++) {
-            float u = 0.f, o1 = 0.f;
-#pragma unroll
-            for (int i = 0; i < DS; i++) {
-                sreg[i] = __fmul_rn(sreg[i], sAl[j][i]);
-                u = __fadd_rn(u, __fmul_rn(sreg[i], sK[j][i]));
-            }
-            u = __fmul_rn(__fsub_rn(sV[j][d], u), sBeta[j]);
-#pragma unroll
-            for (int i = 0; i < DS; i++) {
-                sreg[i] = __fadd_rn(sreg[i], __fmul_rn(sK[j][i], u));
-                o1 = __fadd_rn(o1, __fmul_rn(sreg[i], sQ[j][i]));
-            }
-            sO[j][d] = o1;
-            if (sn && t0 + j == a.snap_after) {
-                float *Sn = sn + (size_t)h * D * D;
-#pragma unroll
-                for (int i = 0; i < DS; i++) Sn[(size_t)i * DS + d] = sreg[i];
-            }
-        }
-        // ---- (C) per-head RMSNorm with weight and the output gate of nt positions
+        // per-head RMSNorm with weight and the output gate of the nt positions, their sums reduced together
+        // (the warp tree and warp order of block_sum)
 #pragma unroll
         for (int j = 0; j < KDA_TB; j++) {
             const double woo = warp_sum(j < nt ? (double)sO[j][d] * (double)sO[j][d] : 0.0);
@@ -336,7 +346,7 @@ __global__ void __launch_bounds__(DS) kda_chunk_kernel(const KdaArgs a)
                 double oo = 0.0;
 #pragma unroll
                 for (int w = 0; w < NW; w++) oo += redo[j][w];
-                const size_t off = (size_t)(row0 + t0 + j) * P + ch;
+                const size_t off = (size_t)(t0 + j) * P + ch;
                 const float inv = (float)(1.0 / sqrt(oo / (double)D + (double)a.rms_eps));
                 const float n = __fmul_rn(onw, __fmul_rn(sO[j][d], inv));
                 a.o[off] = __fmul_rn(n, sigmoid_host(a.gb[off]));
@@ -346,18 +356,27 @@ __global__ void __launch_bounds__(DS) kda_chunk_kernel(const KdaArgs a)
     }
 #pragma unroll
     for (int i = 0; i < DS; i++) S[(size_t)i * DS + d] = sreg[i];
-    for (int j = 0; j < hist; j++) {
-        cs[(size_t)ch * hist + j] = pq[j];
-        cs[(size_t)P * hist + (size_t)ch * hist + j] = pk[j];
-        cs[(size_t)2 * P * hist + (size_t)ch * hist + j] = pv[j];
-    }
+    // the convolution histories: the K - 1 inputs before position `upto` (the call's rows, older ones from the old history)
+    auto histories = [&](float *dst, int upto) {
+        const float *src[3] = {a.q, a.k, a.v};
+        for (int part = 0; part < 3; part++) {
+            float nv[16];
+            for (int j = 0; j < hist; j++) {
+                const int tt = upto - hist + j;
+                nv[j] = tt >= 0 ? src[part][(size_t)tt * P + ch] : cs[(size_t)part * P * hist + (size_t)ch * hist + (hist + tt)];
+            }
+            for (int j = 0; j < hist; j++) dst[(size_t)part * P * hist + (size_t)ch * hist + j] = nv[j];
+        }
+    };
+    if (a.snap && a.snap_after + 1 <= a.T) histories(a.snap + (size_t)a.H * D * D, a.snap_after + 1);   // before cs changes
+    histories(cs, a.T);
 }
 
 void kda_core(cudaStream_t st, float *o, const float *q, const float *k, const float *v, const float *z,
               const float *braw, const float *gb, const float *q_conv, const float *k_conv,
               const float *v_conv, const float *A_log, const float *dt_bias, const float *o_norm,
               float *state, int T, const KdaShape &s, int n_seq, size_t seq_stride, const KdaLowRank *lr, int head0, int heads,
-              float *snap, int snap_after)
+              float *snap, int snap_after, const KdaScratch *scratch)
 {
     const bool fused = lr && T == 1 && n_seq <= 1 && (s.D == 64 || s.D == 128);
     KdaArgs a{o, q, k, v, z, braw, gb, q_conv, k_conv, v_conv, A_log, dt_bias, o_norm, state,
@@ -366,10 +385,17 @@ void kda_core(cudaStream_t st, float *o, const float *q, const float *k, const f
               fused ? lr->lrf : nullptr, fused ? lr->lrg : nullptr, snap, snap_after};
     const dim3 grid(heads > 0 ? heads : s.H, n_seq < 1 ? 1 : n_seq);
     const size_t smem = fused ? (size_t)2 * s.D * (2 * s.D + 16) : 0;
-    if (T > 1 && s.K <= 17 && (s.D == 128 || s.D == 64)) {
-        // several positions: only the state update runs position by position
-        if (s.D == 128) G5B_LAUNCH_PDL(kda_chunk_kernel<128>, grid, dim3(128), 0, st, a);
-        else            G5B_LAUNCH(kda_chunk_kernel<64>, grid, 64, 0, st, a);
+    if (T > 1 && n_seq <= 1 && scratch && s.K <= 17 && (s.D == 128 || s.D == 64)) {
+        // several positions: everything that does not depend on the previous position first, in parallel
+        KdaPrep p{a, scratch->qn, scratch->kn, scratch->vn, scratch->al, scratch->beta};
+        const dim3 pgrid(grid.x, T);
+        if (s.D == 128) {
+            G5B_LAUNCH_PDL(kda_prep_kernel<128>, pgrid, dim3(128), 0, st, p);
+            G5B_LAUNCH(kda_scan_kernel<128>, dim3(grid.x), dim3(128), 0, st, p);
+        } else {
+            G5B_LAUNCH(kda_prep_kernel<64>, pgrid, dim3(64), 0, st, p);
+            G5B_LAUNCH(kda_scan_kernel<64>, dim3(grid.x), dim3(64), 0, st, p);
+        }
         return;
     }
     if (s.D == 128) {

@@ -280,11 +280,14 @@ struct KdaLowRank {
 
 // q,k,v,z,gb: [T][H*D] projections (q,k,v before the short convolution); braw [T][H]; state as
 // the reference lays it out (S [H][D][D] then conv histories q|k|v, glm53f.h:363-367).
+// Rows for calls with several positions: [T][H * D] normalised q, normalised k, v, exp(gate) and [T][H] beta.
+struct KdaScratch { float *qn, *kn, *vn, *al, *beta; };
 void kda_core(cudaStream_t st, float *o, const float *q, const float *k, const float *v, const float *z,
               const float *braw, const float *gb, const float *q_conv, const float *k_conv,
               const float *v_conv, const float *A_log, const float *dt_bias, const float *o_norm,
               float *state, int T, const KdaShape &s, int n_seq = 1, size_t seq_stride = 0,
-              const KdaLowRank *lr = nullptr, int head0 = 0, int heads = -1, float *snap = nullptr, int snap_after = 0);   // heads [head0, head0 + heads) only
+              const KdaLowRank *lr = nullptr, int head0 = 0, int heads = -1, float *snap = nullptr, int snap_after = 0,
+              const struct KdaScratch *scratch = nullptr);   // heads [head0, head0 + heads) only
 
 // ---- mla.cu -------------------------------------------------------------------------------
 struct MlaShape {
