@@ -241,17 +241,18 @@ static void tc_stage_plan(bool fp8, int N, int &a_stages, int &b_stages, size_t 
 // Called by the 128 epilogue threads; acc[t] holds this item's partial sums of row `row`.
 __device__ __forceinline__ void tc_finish_tile(const TcArgs &a, int tile, int split, int row, const float (&acc)[TC_MAX_T], int *s_last)
 {
+    const bool live = tile * TC_BM + row < a.R;                  // rows of a ragged last tile beyond R do not exist
     float *yr = a.y + (size_t)tile * TC_BM + row;
     if (a.KS == 1) {
 #pragma unroll
         for (int t = 0; t < TC_MAX_T; t++)
-            if (t < a.T) yr[(size_t)t * a.ldy] = acc[t];
+            if (t < a.T && live) yr[(size_t)t * a.ldy] = acc[t];
         return;
     }
     float *pr = a.part + (size_t)split * a.T * a.R + (size_t)tile * TC_BM + row;
 #pragma unroll
     for (int t = 0; t < TC_MAX_T; t++)
-        if (t < a.T) __stcg(pr + (size_t)t * a.R, acc[t]);
+        if (t < a.T && live) __stcg(pr + (size_t)t * a.R, acc[t]);
     __threadfence();
     asm volatile("bar.sync 1, 128;" ::: "memory");
     if (threadIdx.x == 0) {
@@ -260,7 +261,7 @@ __device__ __forceinline__ void tc_finish_tile(const TcArgs &a, int tile, int sp
         if (prev == a.KS - 1) a.cnt[tile] = 0;
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");
-    if (*s_last) {
+    if (*s_last && live) {
         __threadfence();
         const float *p0 = a.part + (size_t)tile * TC_BM + row;
         // eight positions at a time, all of their partial sums requested before the first is used
@@ -290,7 +291,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n_items = (a.R / TC_BM) * a.KS;
+    const int n_items = ((a.R + TC_BM - 1) / TC_BM) * a.KS;
     const int N = a.N;
     const size_t batom = (size_t)N * 128;
     const int AS = a.a_stages, BS = a.b_stages;
@@ -662,7 +663,9 @@ void tc_gemm_new_input(TcGemm *g) { if (g) g->x = nullptr; }
 
 bool tc_gemm_takes(const TcGemm *g, const GemvSeg &s, int T)
 {
-    if (!g || T < 8 || T > TC_MAX_T || s.C > g->max_c || s.R % TC_BM || s.R < TC_BM) return false;
+    // (the last row tile may be ragged: rows beyond R are filled with zeros by the copy and never stored)
+    if (!g || T < 8 || T > TC_MAX_T || s.C > g->max_c || s.R < 16) return false;
+    if (s.dt == DT_FP8 && s.R % TC_BM) return false;
     if ((reinterpret_cast<uintptr_t>(s.W) & 15) || (((size_t)s.ldw * (s.dt == DT_FP8 ? 1 : 2)) & 15)) return false;
     if (s.dt == DT_FP8) return s.C % 128 == 0 && s.br == 128 && s.bc == 128 && s.S != nullptr;
     if (s.dt == DT_BF16) return s.C % TC_ATOM_K == 0;
@@ -693,10 +696,14 @@ int tc_gemm_run(TcGemm *g, cudaStream_t st, const GemvSeg &s, int T)
         return -1;
     // Few row tiles: split the columns so that every SM has work; pick the split that wastes the
     // least of the last wave, preferring fewer splits.
-    const int tiles = s.R / TC_BM, sms = dev_sms();
+    const int tiles = (s.R + TC_BM - 1) / TC_BM, sms = dev_sms();
     const int units = fp8 ? s.C / 128 : (s.C / TC_ATOM_K + TC_SEG_CHUNKS - 1) / TC_SEG_CHUNKS;
     int KS = 1;
-    if (tiles < sms && s.R <= TC_PART_ROWS) {
+    if (tiles <= 4 && s.R <= TC_PART_ROWS) {
+        // a matrix of a few hundred rows is a handful of CTAs walking all of K one chunk after the other:
+        // latency, not bytes - split as far as the columns allow
+        KS = units < TC_MAX_SPLIT ? units : TC_MAX_SPLIT;
+    } else if (tiles < sms && s.R <= TC_PART_ROWS) {
         double best = 0.0;
         for (int k = 1; k <= TC_MAX_SPLIT && k <= units; k++) {
             const int items = tiles * k, waves = (items + sms - 1) / sms;
