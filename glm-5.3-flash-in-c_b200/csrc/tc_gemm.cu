@@ -694,21 +694,21 @@ int tc_gemm_run(TcGemm *g, cudaStream_t st, const GemvSeg &s, int T)
     CUtensorMap mb;
     if (!make_map(&mb, g->terms, fp8 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (size_t)terms * Tp, (size_t)s.C, N))
         return -1;
-    // Few row tiles: split the columns so that every SM has work; pick the split that wastes the
-    // least of the last wave, preferring fewer splits.
+    // Fewer row tiles than SMs: split the columns over several work items per tile. The split is chosen
+    // by a small model of the launch in microseconds: waves x (pipeline fill + the item's share of the
+    // K units) + what the partial results cost (a fixed part and a pass per split). Units: a 128-column
+    // block of an FP8 matrix, a 512-column segment of a BF16 one. (With more than half of the SMs busy
+    // anyway a split measured no gain: 12288 x 4096 FP8 at 64 positions 91 us whole, 95 us in three.)
     const int tiles = (s.R + TC_BM - 1) / TC_BM, sms = dev_sms();
     const int units = fp8 ? s.C / 128 : (s.C / TC_ATOM_K + TC_SEG_CHUNKS - 1) / TC_SEG_CHUNKS;
     int KS = 1;
-    if (tiles <= 4 && s.R <= TC_PART_ROWS) {
-        // a matrix of a few hundred rows is a handful of CTAs walking all of K one chunk after the other:
-        // latency, not bytes - split as far as the columns allow
-        KS = units < TC_MAX_SPLIT ? units : TC_MAX_SPLIT;
-    } else if (tiles < sms && s.R <= TC_PART_ROWS) {
-        double best = 0.0;
+    if (2 * tiles <= sms && s.R <= TC_PART_ROWS) {
+        const double fill = 3.0, unit = fp8 ? 1.5 : 3.0;
+        double best = 1e30;
         for (int k = 1; k <= TC_MAX_SPLIT && k <= units; k++) {
             const int items = tiles * k, waves = (items + sms - 1) / sms;
-            const double eff = (double)items / ((double)waves * sms) - 0.15 * (k - 1);   // every split costs a pipeline fill, a partial result and a pass over the partials
-            if (eff > best + 1e-9) { best = eff; KS = k; }
+            const double t = waves * (fill + unit * ((units + k - 1) / k)) + (k > 1 ? 2.0 + 0.5 * k : 0.0);
+            if (t < best - 1e-9) { best = t; KS = k; }
         }
     }
     int a_stages, b_stages;
