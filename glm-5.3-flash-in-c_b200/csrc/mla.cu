@@ -767,18 +767,32 @@ __global__ void __launch_bounds__(FL_THREADS) mla_flash_kernel(float *part, doub
 
     // ---- the chunk's latent rows (16-byte pieces, four threads per row); rows past the last visible
     // position are zero so that nothing undefined enters a product
-    for (int i = tid; i < FL_POS * (FL_KL / 8); i += FL_THREADS) {
-        const int r = i / (FL_KL / 8), c8 = i % (FL_KL / 8);
-        const int jj = j0 + r;
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (jj < nvis) {
-            const int j = ns < 0 ? jj : sl[jj];
-            v = *reinterpret_cast<const uint4 *>(lat + (size_t)j * FL_KL + c8 * 8);
+    // (all of a thread's row numbers are requested first, then all of its pieces: one round trip for the
+    // selection list and one for the rows, instead of a dependent pair per piece)
+    {
+        constexpr int PER = FL_POS * (FL_KL / 8) / FL_THREADS;
+        static_assert(FL_POS * (FL_KL / 8) % FL_THREADS == 0, "pieces per thread");
+        int jrow[PER];
+#pragma unroll
+        for (int k = 0; k < PER; k++) {
+            const int jj = j0 + (tid + k * FL_THREADS) / (FL_KL / 8);
+            jrow[k] = jj < nvis ? (ns < 0 ? jj : sl[jj]) : -1;
         }
-        *reinterpret_cast<uint4 *>(cs + (size_t)r * FL_PITCH + c8 * 8) = v;
+        uint4 v[PER];
+#pragma unroll
+        for (int k = 0; k < PER; k++) {
+            const int c8 = (tid + k * FL_THREADS) % (FL_KL / 8);
+            v[k] = jrow[k] >= 0 ? *reinterpret_cast<const uint4 *>(lat + (size_t)jrow[k] * FL_KL + c8 * 8) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < PER; k++) {
+            const int i = tid + k * FL_THREADS;
+            *reinterpret_cast<uint4 *>(cs + (size_t)(i / (FL_KL / 8)) * FL_PITCH + (i % (FL_KL / 8)) * 8) = v[k];
+        }
     }
     // ---- the absorbed queries of the 16 heads, scaled, as three BF16 terms
     const double scale = (double)(1.0f / sqrtf((float)s.qn));
+#pragma unroll 8
     for (int i = tid; i < FL_HEADS * FL_KL; i += FL_THREADS) {
         const int hh = i / FL_KL, c = i % FL_KL;
         const float v = (float)(qa[((size_t)t * s.H + h0 + hh) * FL_KL + c] * scale);
