@@ -326,31 +326,47 @@ __global__ void mla_absorb_kernel(double *qa, const float *q, const DMat kv_b, M
 // The same sums with the GPU filled: a CTA takes 128 latent columns of one head, its eight row
 // groups (32 rows each at qk_nope = 256) accumulate in FP64 and are added in ascending order.
 constexpr int AB_COLS = 128, AB_GROUPS = 8;
+// TT queries per block (blockIdx.y = group of TT): a weight is read once for all of them; every query's
+// sum is taken in the same order as alone.
+template <int TT>
 __global__ void __launch_bounds__(AB_COLS * AB_GROUPS) mla_absorb_split_kernel(double *qa, const float *q, const DMat kv_b,
-                                                                              MlaShape s)
+                                                                              MlaShape s, int T)
 {
-    __shared__ double part[AB_GROUPS][AB_COLS];
-    const int h = blockIdx.x, t = blockIdx.y, c = blockIdx.z * AB_COLS + (threadIdx.x % AB_COLS), grp = threadIdx.x / AB_COLS;
+    __shared__ double part[TT][AB_GROUPS][AB_COLS];
+    const int h = blockIdx.x, t0 = blockIdx.y * TT, c = blockIdx.z * AB_COLS + (threadIdx.x % AB_COLS), grp = threadIdx.x / AB_COLS;
     const int kvd = s.qn + s.vh, per = s.qn / AB_GROUPS;
-    const float *qt = q + ((size_t)t * s.H + h) * s.qn + grp * per;
+    const float *qt[TT];
+#pragma unroll
+    for (int k = 0; k < TT; k++) qt[k] = q + ((size_t)min(t0 + k, T - 1) * s.H + h) * s.qn + grp * per;   // past the last query: repeated, unused
     const uint16_t *w = static_cast<const uint16_t *>(kv_b.w) + ((size_t)h * kvd + (size_t)grp * per) * s.KL + c;
-    double acc = 0.0;
+    double acc[TT];
+#pragma unroll
+    for (int k = 0; k < TT; k++) acc[k] = 0.0;
 #pragma unroll 8
-    for (int i = 0; i < per; i++) acc = fma((double)qt[i], (double)bf16_to_f32(w[(size_t)i * s.KL]), acc);
-    part[grp][threadIdx.x % AB_COLS] = acc;
+    for (int i = 0; i < per; i++) {
+        const double wv = (double)bf16_to_f32(w[(size_t)i * s.KL]);
+#pragma unroll
+        for (int k = 0; k < TT; k++) acc[k] = fma((double)qt[k][i], wv, acc[k]);
+    }
+#pragma unroll
+    for (int k = 0; k < TT; k++) part[k][grp][threadIdx.x % AB_COLS] = acc[k];
     __syncthreads();
     if (grp == 0) {
-        double sum = part[0][threadIdx.x];
 #pragma unroll
-        for (int g = 1; g < AB_GROUPS; g++) sum += part[g][threadIdx.x];
-        qa[((size_t)t * s.H + h) * s.KL + c] = sum;
+        for (int k = 0; k < TT; k++) {
+            double sum = part[k][0][threadIdx.x];
+#pragma unroll
+            for (int g = 1; g < AB_GROUPS; g++) sum += part[k][g][threadIdx.x];
+            if (t0 + k < T) qa[((size_t)(t0 + k) * s.H + h) * s.KL + c] = sum;
+        }
     }
 }
 
 void mla_absorb(cudaStream_t st, double *qa, const float *q, const DMat &kv_b, int T, const MlaShape &s)
 {
     if (kv_b.dt == DT_BF16 && s.KL % AB_COLS == 0 && s.qn % (AB_GROUPS * 8) == 0) {
-        G5B_LAUNCH(mla_absorb_split_kernel, dim3(s.H, T, s.KL / AB_COLS), AB_COLS * AB_GROUPS, 0, st, qa, q, kv_b, s);
+        if (T >= 4) G5B_LAUNCH(mla_absorb_split_kernel<4>, dim3(s.H, (T + 3) / 4, s.KL / AB_COLS), AB_COLS * AB_GROUPS, 0, st, qa, q, kv_b, s, T);
+        else        G5B_LAUNCH(mla_absorb_split_kernel<1>, dim3(s.H, T, s.KL / AB_COLS), AB_COLS * AB_GROUPS, 0, st, qa, q, kv_b, s, T);
         return;
     }
     G5B_LAUNCH(mla_absorb_kernel, dim3(s.H, T), s.KL >= 512 ? 512 : 128, 0, st, qa, q, kv_b, s);
@@ -960,11 +976,13 @@ void mla_attend_flash(cudaStream_t st, float *cb, const double *qa, const void *
 
 // o[t][h][r] = W_v[h][r] . cb[t][h]: the value half of kv_b applied once per query and head
 // (glm53f_ops.c:904-909). A warp takes RW rows of one head.
-__global__ void __launch_bounds__(256) mla_vout_kernel(float *acc_out, const float *cb, const DMat kv_b, MlaShape s)
+// TT queries per block (blockIdx.z = group of TT): the head's rows are read once for all of them.
+template <int TT>
+__global__ void __launch_bounds__(256) mla_vout_kernel(float *acc_out, const float *cb, const DMat kv_b, MlaShape s, int T)
 {
     pdl_trigger();
     pdl_wait();
-    const int h = blockIdx.y, t = blockIdx.z;
+    const int h = blockIdx.y, t0 = blockIdx.z * TT;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = (blockIdx.x * 8 + warp) * RW;
     if (r >= s.vh) return;
@@ -978,17 +996,26 @@ __global__ void __launch_bounds__(256) mla_vout_kernel(float *acc_out, const flo
         wrow[q] = static_cast<const uint8_t *>(kv_b.w) + (size_t)row * rb;
         srow[q] = kv_b.dt == DT_FP8 ? kv_b.s + (size_t)(row / kv_b.br) * kv_b.scols : nullptr;
     }
-    const float *xp[1] = {cb + ((size_t)t * s.H + h) * s.KL};
-    const float xinv[1] = {1.f};
-    float acc[RW][1];
+    const float *xp[TT];
+    float xinv[TT];
 #pragma unroll
-    for (int q = 0; q < RW; q++) acc[q][0] = 0.f;
-    dot_rows<1>(acc, kv_b.dt, wrow, srow, kv_b.bc, xp, xinv, nullptr, false, 0, s.KL / piece_elems(kv_b.dt), lane);
-#pragma unroll
-    for (int q = 0; q < RW; q++) {
-        const float v = warp_sum(acc[q][0]);
-        if (lane == 0 && r + q < s.vh) acc_out[((size_t)t * s.H + h) * s.vh + r + q] = v;
+    for (int i = 0; i < TT; i++) {
+        xp[i] = cb + ((size_t)min(t0 + i, T - 1) * s.H + h) * s.KL;       // queries past the last one repeat it, unused
+        xinv[i] = 1.f;
     }
+    float acc[RW][TT];
+#pragma unroll
+    for (int q = 0; q < RW; q++)
+#pragma unroll
+        for (int i = 0; i < TT; i++) acc[q][i] = 0.f;
+    dot_rows<TT>(acc, kv_b.dt, wrow, srow, kv_b.bc, xp, xinv, nullptr, false, 0, s.KL / piece_elems(kv_b.dt), lane);
+#pragma unroll
+    for (int q = 0; q < RW; q++)
+#pragma unroll
+        for (int i = 0; i < TT; i++) {
+            const float v = warp_sum(acc[q][i]);
+            if (lane == 0 && r + q < s.vh && t0 + i < T) acc_out[((size_t)(t0 + i) * s.H + h) * s.vh + r + q] = v;
+        }
 }
 
 // Same product for shapes the streaming loop cannot take (ragged columns, tiny FP8 blocks).
@@ -1007,7 +1034,8 @@ __global__ void mla_vout_any_kernel(float *acc_out, const float *cb, const DMat 
 void mla_vout(cudaStream_t st, float *acc_out, const float *cb, const DMat &kv_b, int T, const MlaShape &s)
 {
     const bool fast = s.KL % piece_elems(kv_b.dt) == 0 && (kv_b.dt != DT_FP8 || kv_b.bc % 16 == 0);
-    if (fast) G5B_LAUNCH_PDL(mla_vout_kernel, dim3((s.vh + 8 * RW - 1) / (8 * RW), s.H, T), 256, 0, st, acc_out, cb, kv_b, s);
+    if (fast && T >= 4) G5B_LAUNCH_PDL(mla_vout_kernel<4>, dim3((s.vh + 8 * RW - 1) / (8 * RW), s.H, (T + 3) / 4), 256, 0, st, acc_out, cb, kv_b, s, T);
+    else if (fast)      G5B_LAUNCH_PDL(mla_vout_kernel<1>, dim3((s.vh + 8 * RW - 1) / (8 * RW), s.H, T), 256, 0, st, acc_out, cb, kv_b, s, T);
     else      G5B_LAUNCH(mla_vout_any_kernel, dim3((s.vh + 63) / 64, s.H, T), 64, 0, st, acc_out, cb, kv_b, s);
 }
 
